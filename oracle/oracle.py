@@ -1,0 +1,217 @@
+"""ctypes front end of the CPU oracle (``libovk_oracle.so``).
+
+TEST INFRASTRUCTURE ONLY: imported by ``tests/``, by the smoke check and by the
+``cpu_baseline`` / ``--impl reference`` legs of ``bench.py``.  The product
+package never imports this module.
+
+Each wrapper takes and returns numpy arrays; dtype codes are the reference's
+``ElementType`` values (FLOAT=1, UINT8=2, INT8=3, INT32=6, FLOAT16=10,
+crates/onnx-vulkan-core/src/graph.rs:13-41).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+FLOAT, UINT8, INT8, INT32, FLOAT16 = 1, 2, 3, 6, 10
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+def build() -> str:
+    """Compile the oracle with its Makefile (gcc, no GPU needed)."""
+    subprocess.run(["make", "-C", _HERE, "-s"], check=True)
+    return os.path.join(_HERE, "libovk_oracle.so")
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "libovk_oracle.so")
+        if not os.path.exists(path):
+            build()
+        _LIB = C.CDLL(path)
+        _LIB.orc_num_threads.restype = C.c_int
+    return _LIB
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _dt(a: np.ndarray) -> int:
+    return {np.dtype(np.float32): FLOAT, np.dtype(np.float16): FLOAT16}[a.dtype]
+
+
+def num_threads() -> int:
+    return lib().orc_num_threads()
+
+
+def set_num_threads(n: int) -> None:
+    lib().orc_set_num_threads(C.c_int(n))
+
+
+def n_blocks(k: int, block_size: int) -> int:
+    return -(-k // block_size)
+
+
+def pack_nibbles(nib: np.ndarray, block_size: int) -> np.ndarray:
+    """``[N, K]`` values 0..15 -> ``[N, n_blocks, block_size/2]`` bytes, element
+    2i in the low nibble (tests/matmul_nbits.rs:19-34)."""
+    n, k = nib.shape
+    nb = n_blocks(k, block_size)
+    full = np.zeros((n, nb * block_size), dtype=np.uint8)
+    full[:, :k] = nib
+    return (full[:, 0::2] | (full[:, 1::2] << 4)).reshape(n, nb, block_size // 2)
+
+
+def pack_zero_points(zp: np.ndarray) -> np.ndarray:
+    """``[N, n_blocks]`` values 0..15 -> ``[N, ceil(n_blocks/2)]`` bytes, low
+    nibble first (tests/matmul_nbits.rs:36-46)."""
+    n, nb = zp.shape
+    full = np.zeros((n, (nb + 1) // 2 * 2), dtype=np.uint8)
+    full[:, :nb] = zp
+    return full[:, 0::2] | (full[:, 1::2] << 4)
+
+
+def matmul_nbits(a, b_packed, scales, zp_packed, k, n, block_size, out_dtype=None):
+    a = np.ascontiguousarray(a)
+    m = a.size // k
+    out_dtype = np.dtype(out_dtype or a.dtype)
+    y = np.empty((m, n), dtype=out_dtype)
+    b = np.ascontiguousarray(b_packed, dtype=np.uint8)
+    s = np.ascontiguousarray(scales)
+    z = None if zp_packed is None else np.ascontiguousarray(zp_packed, dtype=np.uint8)
+    rc = lib().orc_matmul_nbits(
+        _p(a), _dt(a), C.c_int64(m), C.c_int64(k), C.c_int64(n), C.c_int64(block_size),
+        _p(b), _p(s), _dt(s), _p(z), _p(y), _dt(y))
+    if rc:
+        raise ValueError(f"orc_matmul_nbits: status {rc}")
+    return y
+
+
+def matmul_nbits_f32_shader_order(a, b_packed, scales, zp_packed, k, n, block_size):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    m = a.size // k
+    y = np.empty((m, n), dtype=np.float32)
+    b = np.ascontiguousarray(b_packed, dtype=np.uint8)
+    s = np.ascontiguousarray(scales, dtype=np.float32)
+    z = None if zp_packed is None else np.ascontiguousarray(zp_packed, dtype=np.uint8)
+    rc = lib().orc_matmul_nbits_f32_shader_order(
+        _p(a), C.c_int64(m), C.c_int64(k), C.c_int64(n), C.c_int64(block_size),
+        _p(b), _p(s), _p(z), _p(y))
+    if rc:
+        raise ValueError(f"orc_matmul_nbits_f32_shader_order: status {rc}")
+    return y
+
+
+def dynamic_quantize(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty(x.shape, dtype=np.uint8)
+    scale = C.c_float(0)
+    zp = C.c_uint8(0)
+    lib().orc_dynamic_quantize(_p(x), C.c_size_t(x.size), _p(y), C.byref(scale), C.byref(zp))
+    return y, np.float32(scale.value), int(zp.value)
+
+
+def _bytes(a):
+    a = np.ascontiguousarray(a)
+    assert a.dtype in (np.uint8, np.int8), a.dtype
+    return a, int(a.dtype == np.int8)
+
+
+def matmul_integer(a, b, a_zp=0, b_zp=0):
+    a, a_signed = _bytes(a)
+    b, b_signed = _bytes(b)
+    k, n = b.shape
+    m = a.size // k if k else 0
+    out = np.empty(a.shape[:-1] + (n,), dtype=np.int32)
+    rc = lib().orc_matmul_integer(
+        _p(a), a_signed, _p(b), b_signed, C.c_int64(m), C.c_int64(k), C.c_int64(n),
+        C.c_int32(int(a_zp)), C.c_int32(int(b_zp)), _p(out))
+    if rc == 2:
+        raise OverflowError("MatMulInteger: i32 overflow")
+    if rc:
+        raise RuntimeError(f"orc_matmul_integer: status {rc}")
+    return out
+
+
+def scale_bias_epilogue(acc, scale, scale_step, bias, bias_step, product=None, product_step=0,
+                        relu=False, want_range=False):
+    acc = np.ascontiguousarray(acc, dtype=np.int32)
+    n = acc.shape[-1]
+    m = acc.size // n
+    scale = np.ascontiguousarray(scale, dtype=np.float32).reshape(-1)
+    bias = np.ascontiguousarray(bias, dtype=np.float32).reshape(-1)
+    if product is not None:
+        product = np.ascontiguousarray(product, dtype=np.float32).reshape(-1)
+    out = np.empty(acc.shape, dtype=np.float32)
+    rng = np.zeros(2, dtype=np.float32)
+    lib().orc_scale_bias_epilogue(
+        _p(acc), C.c_int64(m), C.c_int64(n), _p(scale), scale_step, _p(product), product_step,
+        _p(bias), bias_step, int(relu), _p(out), _p(rng) if want_range else None)
+    return (out, rng) if want_range else out
+
+
+class ConvGeom(C.Structure):
+    _fields_ = [(name, C.c_int64) for name in (
+        "n", "c_in", "c_out", "group", "gsi", "h_in", "w_in", "h_out", "w_out",
+        "kh", "kw", "sh", "sw", "dh", "dw", "phb", "phe", "pwb", "pwe")]
+
+
+_AUTO_PAD = {"NOTSET": 0, "VALID": 1, "SAME_UPPER": 2, "SAME_LOWER": 3}
+
+
+def conv_geometry(x_shape, w_shape, strides=(1, 1), dilations=(1, 1), pads=(0, 0, 0, 0),
+                  auto_pad="NOTSET", group=1) -> ConvGeom:
+    """pads = (h_begin, w_begin, h_end, w_end), the ONNX order."""
+    g = ConvGeom()
+    arr = lambda v: (C.c_int64 * len(v))(*[int(i) for i in v])
+    rc = lib().orc_conv_geometry(arr(x_shape), arr(w_shape), arr(strides), arr(dilations),
+                                 arr(pads), _AUTO_PAD[auto_pad], C.c_int64(group), C.byref(g))
+    if rc:
+        raise ValueError("conv: degenerate output shape")
+    return g
+
+
+def conv_integer(x, w, x_zp=0, w_zp=0, **geom):
+    x, x_signed = _bytes(x)
+    w, w_signed = _bytes(w)
+    g = conv_geometry(x.shape, w.shape, **geom)
+    out = np.empty((g.n, g.c_out, g.h_out, g.w_out), dtype=np.int32)
+    lib().orc_conv_integer(_p(x), x_signed, _p(w), w_signed, C.byref(g),
+                           C.c_int32(int(x_zp)), C.c_int32(int(w_zp)), _p(out))
+    return out
+
+
+def requantize_ratio(x_scale, w_scale, y_scale):
+    w = np.ascontiguousarray(w_scale, dtype=np.float32).reshape(-1)
+    ratio = np.empty_like(w)
+    lib().orc_requantize_ratio(C.c_float(x_scale), _p(w), C.c_size_t(w.size),
+                               C.c_float(y_scale), _p(ratio))
+    return ratio
+
+
+def requantize(acc, inner, ratio, y_zp, bias=None, out_signed=False):
+    acc = np.ascontiguousarray(acc, dtype=np.int32)
+    ratio = np.ascontiguousarray(ratio, dtype=np.float32)
+    if bias is not None:
+        bias = np.ascontiguousarray(bias, dtype=np.int32)
+    out = np.empty(acc.shape, dtype=np.uint8)
+    lib().orc_requantize(_p(acc), C.c_size_t(acc.size), C.c_size_t(inner),
+                         C.c_size_t(ratio.size), _p(bias), _p(ratio), C.c_int32(int(y_zp)),
+                         int(out_signed), _p(out))
+    return out.view(np.int8) if out_signed else out
+
+
+def qlinear_conv(x, x_scale, x_zp, w, w_scale, w_zp, y_scale, y_zp, bias=None, out_signed=False,
+                 **geom):
+    """QLinearConv = ConvInteger + requantize (src/interp.rs:4796-4837)."""
+    acc = conv_integer(x, w, x_zp, w_zp, **geom)
+    ratio = requantize_ratio(x_scale, w_scale, y_scale)
+    if ratio.size == 1:
+        ratio = np.repeat(ratio, acc.shape[1])
+    return requantize(acc, acc.shape[2] * acc.shape[3], ratio, y_zp, bias, out_signed)
