@@ -1,0 +1,204 @@
+/*
+ * ovk_cuda.h - C ABI of the B200 (sm_100a) quantized matrix-product library.
+ *
+ * This is the CUDA sibling of the reference's kernel-launch layer
+ * (crates/vk-compute) narrowed to the four quantized operators of
+ * crates/onnx-vulkan-core/src/interp.rs: MatMulNBits, DynamicQuantizeLinear,
+ * MatMulInteger (+ fused scale/bias epilogue) and QLinearConv / ConvInteger.
+ * Every entry point names the reference interface it replaces.
+ *
+ * Conventions
+ *  - plain pointers and sizes only; device pointers are ordinary CUDA device
+ *    addresses (they survive the pointer arithmetic ONNX Runtime performs on
+ *    allocations, so no handle table like crates/vulkan-ep/src/device_mem.rs
+ *    :100-176 is needed);
+ *  - every call returns an ovk_status; the message is read with
+ *    ovk_last_error(); nothing throws across the boundary;
+ *  - operator calls only ENQUEUE on the context's stream (as
+ *    vk-compute stream_dispatch, crates/vk-compute/src/stream.rs:370-398);
+ *    only ovk_flush and ovk_download wait (flush :702, stream_download :773);
+ *  - dtype codes are the reference's ElementType values
+ *    (crates/onnx-vulkan-core/src/graph.rs:13-41);
+ *  - there is no CPU fallback: a form the kernels do not cover returns
+ *    OVK_UNSUPPORTED before anything is launched (the reference's fail-loud
+ *    rule, README.md:328-336).
+ */
+#ifndef OVK_CUDA_H
+#define OVK_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define OVK_API
+#else
+#define OVK_API __attribute__((visibility("default")))
+#endif
+
+typedef enum ovk_status {
+    OVK_OK = 0,
+    OVK_INVALID_ARGUMENT = 1, /* bad shape / pointer / alignment (anyhow ensure! failures) */
+    OVK_UNSUPPORTED = 2,      /* a form refused at load time by the reference too */
+    OVK_BACKEND = 3,          /* a CUDA call failed (core::Error::Backend, src/error.rs:6-14) */
+    OVK_TIMEOUT = 4           /* a bounded device-side wait gave up; the context stays usable */
+} ovk_status;
+
+typedef enum ovk_dtype {
+    OVK_FLOAT = 1,
+    OVK_UINT8 = 2,
+    OVK_INT8 = 3,
+    OVK_INT32 = 6,
+    OVK_FLOAT16 = 10
+} ovk_dtype;
+
+typedef struct ovk_ctx ovk_ctx;
+typedef struct ovk_nbits_weight ovk_nbits_weight;
+typedef struct ovk_mmi_weight ovk_mmi_weight;
+typedef struct ovk_qconv_weight ovk_qconv_weight;
+
+/* ------------------------------------------------------------------ context
+ * Replaces VkContext::new (crates/vk-compute/src/context.rs:360): one device,
+ * one in-order stream.  `stream` may be an existing cudaStream_t (e.g. the
+ * stream ONNX Runtime or torch is using) or NULL to create one. */
+OVK_API int32_t ovk_ctx_create(int32_t device, void *stream, ovk_ctx **out);
+OVK_API void ovk_ctx_destroy(ovk_ctx *ctx);
+/* Message of the last failed call on this context (or on context creation when ctx is NULL). */
+OVK_API const char *ovk_last_error(const ovk_ctx *ctx);
+/* Name of the kernel variant the last operator call selected (the role of
+ * KernelCache::pipeline_keys in the reference's routing tests,
+ * crates/onnx-vulkan-core/tests/conv_integer_im2col.rs:163-178). */
+OVK_API const char *ovk_last_kernel(const ovk_ctx *ctx);
+/* Number of kernels this context has launched since it was created. */
+OVK_API uint64_t ovk_launch_count(const ovk_ctx *ctx);
+/* The cudaStream_t operator calls are enqueued on. */
+OVK_API void *ovk_stream(const ovk_ctx *ctx);
+
+/* flush (stream.rs:702): wait for everything enqueued; also reports a
+ * device-side wait that timed out (OVK_TIMEOUT). */
+OVK_API int32_t ovk_flush(ovk_ctx *ctx);
+/* create_storage_buffer (buffer.rs:239) / recycle_storage_buffer (:303) */
+OVK_API int32_t ovk_alloc(ovk_ctx *ctx, size_t bytes, void **dptr);
+OVK_API int32_t ovk_free(ovk_ctx *ctx, void *dptr);
+/* stream_upload_at (stream.rs:310-367), stream_download_into (:918, waits),
+ * stream_fill (:481; bytes and offset multiples of 4) */
+OVK_API int32_t ovk_upload(ovk_ctx *ctx, void *dst, size_t offset, const void *src, size_t bytes);
+OVK_API int32_t ovk_download(ovk_ctx *ctx, const void *src, size_t offset, void *dst, size_t bytes);
+OVK_API int32_t ovk_fill(ovk_ctx *ctx, void *dst, size_t offset, size_t bytes, uint32_t value);
+/* measure_dispatch_gpu (pipeline.rs:246): device time between the two calls, in ms. */
+OVK_API int32_t ovk_timer_start(ovk_ctx *ctx);
+OVK_API int32_t ovk_timer_stop(ovk_ctx *ctx, float *ms);
+
+/* -------------------------------------------------------------- MatMulNBits
+ * interp::matmul_nbits (crates/onnx-vulkan-core/src/interp.rs:6429-6561) and
+ * its predicate (:452-464).
+ *
+ * B is [N, n_blocks, block_size/2] u8 with element 2i in the low nibble,
+ * scales [N*n_blocks] f32 or f16, zero_points [N, ceil(n_blocks/2)] u8 nibble
+ * packed (NULL = implicit 8), all device pointers in the operator's own
+ * layout.  prepack plays the role packed_b (:2712) plays for MatMulInteger: it
+ * is called once per weight and may build a decode-friendly copy.  The
+ * original three buffers must stay alive as long as the weight object.
+ * bits must be 4, block_size a positive multiple of 8. */
+#define OVK_NBITS_DEFAULT 0u
+#define OVK_NBITS_NO_DECODE_COPY 1u /* keep only the operator layout (generic kernels) */
+OVK_API int32_t ovk_nbits_prepack(ovk_ctx *ctx, const void *b, const void *scales,
+                                  int32_t scales_dtype, const void *zero_points, int64_t n,
+                                  int64_t k, int64_t bits, int64_t block_size, uint32_t flags,
+                                  ovk_nbits_weight **out);
+OVK_API void ovk_nbits_weight_destroy(ovk_ctx *ctx, ovk_nbits_weight *w);
+/* Y[M,N] = A[M,K] x dequant(B).  a_dtype / y_dtype: OVK_FLOAT or OVK_FLOAT16.
+ * Routes M = 1 (decode, matrix-vector) and M > 1 (prefill) internally, as
+ * shaders::matmul_nbits::route (shaders/matmul_nbits.rs:430-436) does. */
+OVK_API int32_t ovk_matmul_nbits(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
+                                 int32_t a_dtype, int64_t m, void *y, int32_t y_dtype);
+
+/* ------------------------------------------------- DynamicQuantizeLinear
+ * interp::dynamic_quantize / quantize_on_device (interp.rs:1945-2085) with the
+ * PARTIAL and QUANTIZE passes of shaders/dynamic_quantize.rs:106-222.  x, y,
+ * y_scale (1 f32) and y_zero_point (1 u8) are device pointers; the results
+ * stay on the device.  n = 0 writes scale 1, zero point 0 (:1949-1966). */
+OVK_API int32_t ovk_dynamic_quantize(ovk_ctx *ctx, const float *x, int64_t n, uint8_t *y,
+                                     float *y_scale, uint8_t *y_zero_point);
+
+/* ----------------------------------------------------------- MatMulInteger
+ * packed_b (interp.rs:2712-2768, shader PACK_B shaders/matmul_integer.rs
+ * :135-158): B [K,N] u8/i8 constant -> tensor-core layout, once per weight. */
+OVK_API int32_t ovk_mmi_prepack(ovk_ctx *ctx, const void *b, int32_t b_signed, int64_t k,
+                                int64_t n, ovk_mmi_weight **out);
+OVK_API void ovk_mmi_weight_destroy(ovk_ctx *ctx, ovk_mmi_weight *w);
+/* interp::matmul_integer (interp.rs:2090-2183): out[M,N] i32 = sum_k (a - a_zp)(b - b_zp).
+ * a_zp / b_zp point to ONE byte each on the device (per-tensor, read by the
+ * kernel without a read-back); NULL means 0. */
+OVK_API int32_t ovk_matmul_integer(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a,
+                                   int32_t a_signed, int64_t m, const void *a_zp,
+                                   const void *b_zp, int32_t *out);
+/* interp::matmul_integer_scale_bias (interp.rs:2405-2572): the fused
+ * MatMulInteger -> Cast -> Mul -> Add [-> Relu] node,
+ *   out = fl(fl(float(acc) * s) + bias),  s = scale or fl(scale * product),
+ * bit-identical to the unfused graph.  A step is 0 (one value) or 1 (one per
+ * column), as interp::column_step (:2600-2610); other broadcasts are refused
+ * (the reference runs them unfused).  range (may be NULL) is a zero-initialised
+ * pair of u32 receiving the bits of max(-min,0) and max(max,0) of the stored
+ * values by atomic max, for the DynamicQuantizeLinear that follows. */
+#define OVK_EPILOGUE_RELU 1u
+#define OVK_EPILOGUE_RANGE 2u
+OVK_API int32_t ovk_matmul_integer_scale_bias(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a,
+                                              int32_t a_signed, int64_t m, const void *a_zp,
+                                              const void *b_zp, const float *scale,
+                                              int32_t scale_step, const float *product,
+                                              int32_t product_step, const float *bias,
+                                              int32_t bias_step, uint32_t flags, uint32_t *range,
+                                              float *out);
+/* interp::qlinear_matmul (interp.rs:4845-4875): MatMulInteger then
+ * requantize(inner = 1, axis_len = ratio_len); ratio is a device array of
+ * ratio_len (1 or N) floats computed by the caller as (a_scale*b_scale)/y_scale. */
+OVK_API int32_t ovk_qlinear_matmul(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a,
+                                   int32_t a_signed, int64_t m, const void *a_zp,
+                                   const void *b_zp, const float *ratio, int64_t ratio_len,
+                                   int32_t y_zp, int32_t y_signed, void *out);
+
+/* ------------------------------------------------ ConvInteger / QLinearConv
+ * Geometry follows interp::conv_geometry (interp.rs:3439-3536): x is NCHW
+ * (a 1-D convolution is passed with W = 1, KW = 1), w is
+ * [C_out, C_in/group, KH, KW]; pads = {h_begin, w_begin, h_end, w_end}
+ * already resolved from auto_pad by the caller. */
+typedef struct ovk_conv_params {
+    int64_t n, c_in, h, w;
+    int64_t pads[4];
+    int64_t strides[2];
+    int64_t dilations[2];
+} ovk_conv_params;
+OVK_API int32_t ovk_qconv_prepack(ovk_ctx *ctx, const void *w, int32_t w_signed, int64_t c_out,
+                                  int64_t c_in_per_group, int64_t kh, int64_t kw, int64_t group,
+                                  ovk_qconv_weight **out);
+OVK_API void ovk_qconv_weight_destroy(ovk_ctx *ctx, ovk_qconv_weight *w);
+/* Output spatial size for these parameters; OVK_INVALID_ARGUMENT when degenerate. */
+OVK_API int32_t ovk_conv_output_shape(const ovk_qconv_weight *w, const ovk_conv_params *p,
+                                      int64_t *h_out, int64_t *w_out);
+/* interp::conv_integer_with (interp.rs:4421-4651): i32 accumulators, NCHW. */
+OVK_API int32_t ovk_conv_integer(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x,
+                                 int32_t x_signed, const ovk_conv_params *p, int32_t x_zp,
+                                 int32_t w_zp, int32_t *out);
+/* interp::qlinear_conv (interp.rs:4796-4837) = ConvInteger + requantize
+ * (interp.rs:4714-4788, shaders/qlinear.rs:28-63):
+ *   y = sat(rne(f32(acc + bias[c]) * ratio[c]) + y_zp).
+ * ratio is a HOST array of C_out floats, (x_scale*w_scale[c])/y_scale computed
+ * in f32 left to right as interp::requantize_ratio (:4682-4694) does; bias is
+ * a device array of C_out int32 or NULL. */
+OVK_API int32_t ovk_qlinear_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x,
+                                 int32_t x_signed, const ovk_conv_params *p, int32_t x_zp,
+                                 int32_t w_zp, const float *ratio_host, const int32_t *bias,
+                                 int32_t y_zp, int32_t y_signed, void *y);
+/* The REQUANTIZE pass on its own (shaders/qlinear.rs:28-63): c = (i / inner) % axis_len. */
+OVK_API int32_t ovk_requantize(ovk_ctx *ctx, const int32_t *acc, int64_t count, int64_t inner,
+                               int64_t axis_len, const int32_t *bias, const float *ratio,
+                               int32_t y_zp, int32_t y_signed, void *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OVK_CUDA_H */

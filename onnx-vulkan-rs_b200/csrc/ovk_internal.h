@@ -1,0 +1,116 @@
+// Internal declarations shared by the translation units of libovk_cuda.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "ovk_cuda.h"
+
+// Device-side error codes written to ovk_ctx::dev_status by bounded waits.
+enum : int {
+    OVK_DEV_OK = 0,
+    OVK_DEV_TIMEOUT_TMA = 1,   // a consumer gave up waiting for a bulk copy
+    OVK_DEV_TIMEOUT_MMA = 2,   // the epilogue gave up waiting for the tensor core
+    OVK_DEV_TIMEOUT_SLOT = 3,  // a producer gave up waiting for a free stage
+};
+
+struct ovk_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    std::string err;
+    const char *last_kernel = "";
+    uint64_t launches = 0;
+    // device scratch owned by the context
+    uint32_t *range_slot = nullptr;  // 2 x u32: bits of -min, max (DynamicQuantizeLinear)
+    int *dev_status = nullptr;       // sticky error word written by bounded waits
+    int *host_status = nullptr;      // pinned mirror read by ovk_flush
+    float *params = nullptr;         // OVK_PARAM_FLOATS floats: per-call constants (requantize ratios)
+    void *scratch = nullptr;         // grow-on-demand workspace (row sums, NHWC staging, ...)
+    size_t scratch_bytes = 0;
+    cudaEvent_t t0 = nullptr, t1 = nullptr;
+};
+
+constexpr int OVK_PARAM_FLOATS = 16384;
+
+// Sets the context's (or, without a context, the thread's) error message and returns `code`.
+int32_t ovk_fail(ovk_ctx *ctx, int32_t code, const char *fmt, ...);
+
+// Grows the context workspace to at least `bytes` (stream-ordered: the old
+// block is released only after work already enqueued has finished).
+int32_t ovk_scratch(ovk_ctx *ctx, size_t bytes, void **out);
+
+#define OVK_CUDA(ctx, expr)                                                               \
+    do {                                                                                  \
+        cudaError_t e_ = (expr);                                                          \
+        if (e_ != cudaSuccess)                                                            \
+            return ovk_fail((ctx), OVK_BACKEND, "%s: %s", #expr, cudaGetErrorString(e_)); \
+    } while (0)
+
+#define OVK_REQUIRE(ctx, cond, ...)                                \
+    do {                                                           \
+        if (!(cond))                                               \
+            return ovk_fail((ctx), OVK_INVALID_ARGUMENT, __VA_ARGS__); \
+    } while (0)
+
+#define OVK_REFUSE(ctx, cond, ...)                            \
+    do {                                                      \
+        if (cond)                                             \
+            return ovk_fail((ctx), OVK_UNSUPPORTED, __VA_ARGS__); \
+    } while (0)
+
+// Records a kernel launch (name for ovk_last_kernel, count for ovk_launch_count)
+// and turns a launch error into a status.
+#define OVK_LAUNCHED(ctx, name)                                                        \
+    do {                                                                               \
+        (ctx)->last_kernel = (name);                                                   \
+        (ctx)->launches++;                                                             \
+        cudaError_t e_ = cudaGetLastError();                                           \
+        if (e_ != cudaSuccess)                                                         \
+            return ovk_fail((ctx), OVK_BACKEND, "%s: %s", (name), cudaGetErrorString(e_)); \
+    } while (0)
+
+static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// ---------------------------------------------------------------- weights
+
+struct ovk_nbits_weight {
+    const uint8_t *b = nullptr;       // operator layout [N, n_blocks, bs/2]
+    const void *scales = nullptr;     // [N, n_blocks] f32 / f16
+    const uint8_t *zp = nullptr;      // [N, ceil(n_blocks/2)] or null (implicit 8)
+    int32_t scales_dtype = OVK_FLOAT;
+    int64_t n = 0, k = 0, block_size = 0, n_blocks = 0;
+    // decode copy (built by prepack when the shape allows it)
+    void *decode = nullptr;
+    size_t decode_bytes = 0;
+    int64_t k_groups = 0;   // ceil(K / 32), padded
+    int64_t panels = 0;     // ceil(N / 16)
+};
+
+struct ovk_mmi_weight {
+    int64_t k = 0, n = 0;
+    int64_t k_pad = 0;         // row pitch of bt in bytes (multiple of 16)
+    int64_t n_pad = 0;
+    int32_t b_signed = 0;
+    uint8_t *bt = nullptr;     // [n_pad, k_pad] B transposed, K contiguous, zero padded
+    int32_t *colsum = nullptr; // [n_pad] sum over k of b[k][n] (signed interpretation applied)
+    void *tmap_b = nullptr;    // host copy of the CUtensorMap describing bt (128 bytes), or null
+};
+
+struct ovk_qconv_weight {
+    int64_t c_out = 0, cig = 0, kh = 0, kw = 0, group = 1;
+    int32_t w_signed = 0;
+    uint8_t *w = nullptr;       // copy in the operator layout [C_out, C_in/g, KH, KW]
+    uint8_t *w_taps = nullptr;  // [KH*KW, C_out_pad, C_in] tap-major copy for the tensor path (group 1)
+    int32_t *wsum = nullptr;    // [C_out] sum of all weights of a filter (group 1)
+    int64_t c_out_pad = 0;
+};

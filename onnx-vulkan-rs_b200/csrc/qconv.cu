@@ -1,0 +1,277 @@
+// ConvInteger / QLinearConv: host logic, the direct kernel that covers every
+// geometry (groups, depthwise, 1-D, strides, dilations), and REQUANTIZE.
+//
+// Host side mirrors interp::conv_integer_with (crates/onnx-vulkan-core/src/
+// interp.rs:4421-4651), conv_geometry (:3439-3536), qlinear_conv (:4796-4837)
+// and requantize (:4714-4788).  The direct kernel follows
+// src/shaders/conv_integer.rs:73-110 (one thread per output, padding
+// contributes exactly 0) with the requantising epilogue of
+// src/shaders/qlinear.rs:28-63 applied in the same pass instead of a second one.
+#include "ovk_internal.h"
+#include "epilogue.cuh"
+
+struct ConvGeom {
+    int n, c_in, c_out, group, cig;
+    int h_in, w_in, h_out, w_out;
+    int kh, kw, sh, sw, dh, dw, phb, pwb;
+};
+
+bool ovk_qconv_tc_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, const void *x);
+int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,
+                            const ConvGeom &g, int32_t x_zp, int32_t w_zp, const EpiParams &epi,
+                            void *out);
+int32_t ovk_qconv_tc_prepare_weight(ovk_ctx *ctx, ovk_qconv_weight *w);
+
+namespace {
+
+__device__ __forceinline__ int32_t sx8(uint8_t b, int is_signed)
+{
+    return is_signed ? int32_t(int8_t(b)) : int32_t(b);
+}
+
+__global__ void __launch_bounds__(256)
+conv_direct_kernel(const uint8_t *__restrict__ x, const uint8_t *__restrict__ w, ConvGeom g,
+                   int x_signed, int w_signed, int32_t x_zp, int32_t w_zp, EpiParams epi,
+                   void *out, int64_t total)
+{
+    const int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (o >= total)
+        return;
+    const int ow = int(o % g.w_out);
+    int64_t t1 = o / g.w_out;
+    const int oh = int(t1 % g.h_out);
+    t1 /= g.h_out;
+    const int m = int(t1 % g.c_out);
+    const int64_t bn = t1 / g.c_out;
+    const int gso = g.c_out / g.group;
+    const int grp = m / gso;
+    int32_t acc = 0;
+    for (int cg = 0; cg < g.cig; cg++) {
+        const int ic = grp * g.cig + cg;
+        for (int r = 0; r < g.kh; r++) {
+            const int ih = oh * g.sh - g.phb + r * g.dh;
+            if (ih < 0 || ih >= g.h_in)
+                continue;
+            for (int s = 0; s < g.kw; s++) {
+                const int iw = ow * g.sw - g.pwb + s * g.dw;
+                if (iw < 0 || iw >= g.w_in)
+                    continue;
+                const int64_t xi = ((bn * g.c_in + ic) * g.h_in + ih) * int64_t(g.w_in) + iw;
+                const int64_t wi = ((int64_t(m) * g.cig + cg) * g.kh + r) * g.kw + s;
+                acc += (sx8(x[xi], x_signed) - x_zp) * (sx8(w[wi], w_signed) - w_zp);
+            }
+        }
+    }
+    if (epi.mode == EPI_RAW)
+        static_cast<int32_t *>(out)[o] = acc;
+    else
+        static_cast<uint8_t *>(out)[o] = uint8_t(epi_requant_value(epi, m, acc));
+}
+
+// REQUANTIZE on its own (shaders/qlinear.rs:28-63): four outputs per thread.
+__global__ void __launch_bounds__(256)
+requantize_kernel(const int32_t *__restrict__ acc, int64_t n, int64_t inner, int64_t axis_len,
+                  EpiParams epi, uint8_t *__restrict__ out)
+{
+    const int64_t base = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+    if (base >= n)
+        return;
+    uint32_t packed = 0;
+    int j = 0;
+    for (; j < 4 && base + j < n; j++) {
+        const int64_t i = base + j;
+        const int64_t c = (i / inner) % axis_len;
+        packed |= (uint32_t(epi_requant_value(epi, c, acc[i])) & 0xffu) << (8 * j);
+    }
+    if (j == 4 && ((reinterpret_cast<uintptr_t>(out) & 3) == 0)) {
+        *reinterpret_cast<uint32_t *>(out + base) = packed;
+    } else {
+        for (int t = 0; t < j; t++)
+            out[base + t] = uint8_t(packed >> (8 * t));
+    }
+}
+
+int32_t make_geom(ovk_ctx *ctx, const ovk_qconv_weight *w, const ovk_conv_params *p, ConvGeom *g,
+                  const char *op)
+{
+    OVK_REQUIRE(ctx, p->n >= 0 && p->c_in > 0 && p->h > 0 && p->w > 0, "%s: bad input shape", op);
+    OVK_REQUIRE(ctx, p->c_in == w->cig * w->group, "%s: input has %lld channels, the weight expects %lld x %lld groups",
+                op, (long long)p->c_in, (long long)w->cig, (long long)w->group);
+    OVK_REQUIRE(ctx, w->c_out % w->group == 0, "%s: C_out %lld is not a multiple of group %lld", op,
+                (long long)w->c_out, (long long)w->group);
+    OVK_REQUIRE(ctx, p->strides[0] > 0 && p->strides[1] > 0 && p->dilations[0] > 0 && p->dilations[1] > 0,
+                "%s: strides and dilations must be positive", op);
+    OVK_REQUIRE(ctx, p->pads[0] >= 0 && p->pads[1] >= 0 && p->pads[2] >= 0 && p->pads[3] >= 0,
+                "%s: negative padding", op);
+    const int64_t h_out = (p->h + p->pads[0] + p->pads[2] - (p->dilations[0] * (w->kh - 1) + 1)) / p->strides[0] + 1;
+    const int64_t w_out = (p->w + p->pads[1] + p->pads[3] - (p->dilations[1] * (w->kw - 1) + 1)) / p->strides[1] + 1;
+    OVK_REQUIRE(ctx, h_out > 0 && w_out > 0, "%s: degenerate output shape", op);
+    OVK_REQUIRE(ctx, p->n * w->c_out * h_out * w_out < (int64_t(1) << 40) && p->h < (1 << 24) && p->w < (1 << 24),
+                "%s: tensor too large", op);
+    g->n = int(p->n);
+    g->c_in = int(p->c_in);
+    g->c_out = int(w->c_out);
+    g->group = int(w->group);
+    g->cig = int(w->cig);
+    g->h_in = int(p->h);
+    g->w_in = int(p->w);
+    g->h_out = int(h_out);
+    g->w_out = int(w_out);
+    g->kh = int(w->kh);
+    g->kw = int(w->kw);
+    g->sh = int(p->strides[0]);
+    g->sw = int(p->strides[1]);
+    g->dh = int(p->dilations[0]);
+    g->dw = int(p->dilations[1]);
+    g->phb = int(p->pads[0]);
+    g->pwb = int(p->pads[1]);
+    return OVK_OK;
+}
+
+int32_t run_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,
+                 const ovk_conv_params *p, int32_t x_zp, int32_t w_zp, const EpiParams &epi,
+                 void *out, const char *op)
+{
+    if (!ctx || !w || !p)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "%s: null argument", op);
+    ConvGeom g;
+    int32_t rc = make_geom(ctx, w, p, &g, op);
+    if (rc != OVK_OK)
+        return rc;
+    const int64_t total = int64_t(g.n) * g.c_out * g.h_out * g.w_out;
+    if (total == 0)
+        return OVK_OK;
+    OVK_REQUIRE(ctx, x && out, "%s: x or the output is null", op);
+    OVK_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (ovk_qconv_tc_applies(ctx, w, g, x))
+        return ovk_qconv_tc_launch(ctx, w, x, x_signed, g, x_zp, w_zp, epi, out);
+    conv_direct_kernel<<<unsigned(ceil_div64(total, 256)), 256, 0, ctx->stream>>>(
+        static_cast<const uint8_t *>(x), w->w, g, x_signed, w->w_signed, x_zp, w_zp, epi, out, total);
+    OVK_LAUNCHED(ctx, "conv_direct");
+    return OVK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t ovk_qconv_prepack(ovk_ctx *ctx, const void *wt, int32_t w_signed, int64_t c_out,
+                          int64_t c_in_per_group, int64_t kh, int64_t kw, int64_t group,
+                          ovk_qconv_weight **out)
+{
+    if (!ctx || !out)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "ovk_qconv_prepack: null argument");
+    *out = nullptr;
+    OVK_REQUIRE(ctx, wt, "ConvInteger: weight is null");
+    OVK_REQUIRE(ctx, c_out > 0 && c_in_per_group > 0 && kh > 0 && kw > 0 && group > 0,
+                "ConvInteger: bad weight shape [%lld,%lld,%lld,%lld] group %lld", (long long)c_out,
+                (long long)c_in_per_group, (long long)kh, (long long)kw, (long long)group);
+    OVK_REQUIRE(ctx, c_out * c_in_per_group * kh * kw < (int64_t(1) << 31), "ConvInteger: weight too large");
+    OVK_CUDA(ctx, cudaSetDevice(ctx->device));
+    ovk_qconv_weight *w = new ovk_qconv_weight();
+    w->c_out = c_out;
+    w->cig = c_in_per_group;
+    w->kh = kh;
+    w->kw = kw;
+    w->group = group;
+    w->w_signed = w_signed ? 1 : 0;
+    const size_t bytes = size_t(c_out * c_in_per_group * kh * kw);
+    cudaError_t e = cudaMalloc(&w->w, (bytes + 255) & ~size_t(255));
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(w->w, wt, bytes, cudaMemcpyDeviceToDevice, ctx->stream);
+    int32_t rc = OVK_OK;
+    if (e != cudaSuccess)
+        rc = ovk_fail(ctx, OVK_BACKEND, "ConvInteger: weight copy: %s", cudaGetErrorString(e));
+    if (rc == OVK_OK)
+        rc = ovk_qconv_tc_prepare_weight(ctx, w);
+    if (rc != OVK_OK) {
+        cudaFree(w->w);
+        delete w;
+        return rc;
+    }
+    *out = w;
+    return OVK_OK;
+}
+
+void ovk_qconv_weight_destroy(ovk_ctx *ctx, ovk_qconv_weight *w)
+{
+    if (!w)
+        return;
+    if (ctx)
+        cudaStreamSynchronize(ctx->stream);
+    cudaFree(w->w);
+    cudaFree(w->w_taps);
+    cudaFree(w->wsum);
+    delete w;
+}
+
+int32_t ovk_conv_output_shape(const ovk_qconv_weight *w, const ovk_conv_params *p, int64_t *h_out,
+                              int64_t *w_out)
+{
+    if (!w || !p || !h_out || !w_out)
+        return OVK_INVALID_ARGUMENT;
+    if (p->strides[0] <= 0 || p->strides[1] <= 0)
+        return OVK_INVALID_ARGUMENT;
+    *h_out = (p->h + p->pads[0] + p->pads[2] - (p->dilations[0] * (w->kh - 1) + 1)) / p->strides[0] + 1;
+    *w_out = (p->w + p->pads[1] + p->pads[3] - (p->dilations[1] * (w->kw - 1) + 1)) / p->strides[1] + 1;
+    return (*h_out > 0 && *w_out > 0) ? OVK_OK : OVK_INVALID_ARGUMENT;
+}
+
+int32_t ovk_conv_integer(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,
+                         const ovk_conv_params *p, int32_t x_zp, int32_t w_zp, int32_t *out)
+{
+    EpiParams epi = {};
+    epi.mode = EPI_RAW;
+    return run_conv(ctx, w, x, x_signed, p, x_zp, w_zp, epi, out, "ConvInteger");
+}
+
+int32_t ovk_qlinear_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,
+                         const ovk_conv_params *p, int32_t x_zp, int32_t w_zp,
+                         const float *ratio_host, const int32_t *bias, int32_t y_zp,
+                         int32_t y_signed, void *y)
+{
+    if (!ctx || !w)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "QLinearConv: null argument");
+    OVK_REQUIRE(ctx, ratio_host, "QLinearConv: ratio is null");
+    // the per-channel ratio is a graph constant: staged in the context's parameter buffer per call
+    // (the reference uploads it through its parameter cache, interp.rs:4751-4753)
+    OVK_REFUSE(ctx, w->c_out > OVK_PARAM_FLOATS, "QLinearConv: %lld output channels exceed the parameter buffer",
+               (long long)w->c_out);
+    float *ratio_dev = ctx->params;
+    OVK_CUDA(ctx, cudaMemcpyAsync(ratio_dev, ratio_host, size_t(w->c_out) * sizeof(float),
+                                  cudaMemcpyHostToDevice, ctx->stream));
+    EpiParams epi = {};
+    epi.mode = EPI_REQUANT;
+    epi.ratio = ratio_dev;
+    epi.ratio_step = 1;
+    epi.ibias = bias;
+    epi.y_zp = y_zp;
+    epi.y_signed = y_signed;
+    return run_conv(ctx, w, x, x_signed, p, x_zp, w_zp, epi, y, "QLinearConv");
+}
+
+int32_t ovk_requantize(ovk_ctx *ctx, const int32_t *acc, int64_t count, int64_t inner,
+                       int64_t axis_len, const int32_t *bias, const float *ratio, int32_t y_zp,
+                       int32_t y_signed, void *out)
+{
+    if (!ctx)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "Requantize: null context");
+    OVK_REQUIRE(ctx, count >= 0 && axis_len > 0, "Requantize: empty scale");
+    if (count == 0)
+        return OVK_OK;
+    OVK_REQUIRE(ctx, acc && ratio && out, "Requantize: null tensor");
+    OVK_CUDA(ctx, cudaSetDevice(ctx->device));
+    EpiParams epi = {};
+    epi.mode = EPI_REQUANT;
+    epi.ratio = ratio;
+    epi.ratio_step = 1;
+    epi.ibias = bias;
+    epi.y_zp = y_zp;
+    epi.y_signed = y_signed;
+    requantize_kernel<<<unsigned(ceil_div64(ceil_div64(count, 4), 256)), 256, 0, ctx->stream>>>(
+        acc, count, std::max<int64_t>(inner, 1), axis_len, epi, static_cast<uint8_t *>(out));
+    OVK_LAUNCHED(ctx, "requantize");
+    return OVK_OK;
+}
+
+}  // extern "C"

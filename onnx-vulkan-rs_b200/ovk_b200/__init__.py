@@ -1,0 +1,326 @@
+"""ctypes binding of ``libovk_cuda.so`` - the C ABI declared in ``include/ovk_cuda.h``.
+
+The library is the product; this module only loads it, declares the
+signatures and wraps device memory held in torch CUDA tensors (torch is the
+allocator and the stream provider here, nothing more).  There is no fallback:
+if the library is missing or was not built, importing the ops fails loudly.
+
+The wrappers mirror the reference's operator functions
+(crates/onnx-vulkan-core/src/interp.rs): ``matmul_nbits`` (:6429),
+``dynamic_quantize`` (:1945), ``matmul_integer`` (:2090),
+``matmul_integer_scale_bias`` (:2405), ``qlinear_matmul`` (:4845),
+``conv_integer`` (:4421), ``qlinear_conv`` (:4796).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+FLOAT, UINT8, INT8, INT32, FLOAT16 = 1, 2, 3, 6, 10
+OK, INVALID_ARGUMENT, UNSUPPORTED, BACKEND, TIMEOUT = 0, 1, 2, 3, 4
+EPILOGUE_RELU, EPILOGUE_RANGE = 1, 2
+NBITS_NO_DECODE_COPY = 1
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG, "libovk_cuda.so")
+
+
+class OvkError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"[ovk status {status}] {message}")
+        self.status = status
+        self.message = message
+
+
+class ConvParams(C.Structure):
+    _fields_ = [("n", C.c_int64), ("c_in", C.c_int64), ("h", C.c_int64), ("w", C.c_int64),
+                ("pads", C.c_int64 * 4), ("strides", C.c_int64 * 2), ("dilations", C.c_int64 * 2)]
+
+
+_lib = None
+
+# name -> (restype, argtypes); every symbol ovk_cuda.h declares
+_P, _I32, _I64, _U32, _SZ = C.c_void_p, C.c_int32, C.c_int64, C.c_uint32, C.c_size_t
+SIGNATURES = {
+    "ovk_ctx_create": (_I32, [_I32, _P, C.POINTER(_P)]),
+    "ovk_ctx_destroy": (None, [_P]),
+    "ovk_last_error": (C.c_char_p, [_P]),
+    "ovk_last_kernel": (C.c_char_p, [_P]),
+    "ovk_launch_count": (C.c_uint64, [_P]),
+    "ovk_stream": (_P, [_P]),
+    "ovk_flush": (_I32, [_P]),
+    "ovk_alloc": (_I32, [_P, _SZ, C.POINTER(_P)]),
+    "ovk_free": (_I32, [_P, _P]),
+    "ovk_upload": (_I32, [_P, _P, _SZ, _P, _SZ]),
+    "ovk_download": (_I32, [_P, _P, _SZ, _P, _SZ]),
+    "ovk_fill": (_I32, [_P, _P, _SZ, _SZ, _U32]),
+    "ovk_timer_start": (_I32, [_P]),
+    "ovk_timer_stop": (_I32, [_P, C.POINTER(C.c_float)]),
+    "ovk_nbits_prepack": (_I32, [_P, _P, _P, _I32, _P, _I64, _I64, _I64, _I64, _U32, C.POINTER(_P)]),
+    "ovk_nbits_weight_destroy": (None, [_P, _P]),
+    "ovk_matmul_nbits": (_I32, [_P, _P, _P, _I32, _I64, _P, _I32]),
+    "ovk_dynamic_quantize": (_I32, [_P, _P, _I64, _P, _P, _P]),
+    "ovk_mmi_prepack": (_I32, [_P, _P, _I32, _I64, _I64, C.POINTER(_P)]),
+    "ovk_mmi_weight_destroy": (None, [_P, _P]),
+    "ovk_matmul_integer": (_I32, [_P, _P, _P, _I32, _I64, _P, _P, _P]),
+    "ovk_matmul_integer_scale_bias": (_I32, [_P, _P, _P, _I32, _I64, _P, _P, _P, _I32, _P, _I32, _P,
+                                             _I32, _U32, _P, _P]),
+    "ovk_qlinear_matmul": (_I32, [_P, _P, _P, _I32, _I64, _P, _P, _P, _I64, _I32, _I32, _P]),
+    "ovk_qconv_prepack": (_I32, [_P, _P, _I32, _I64, _I64, _I64, _I64, _I64, C.POINTER(_P)]),
+    "ovk_qconv_weight_destroy": (None, [_P, _P]),
+    "ovk_conv_output_shape": (_I32, [_P, C.POINTER(ConvParams), C.POINTER(_I64), C.POINTER(_I64)]),
+    "ovk_conv_integer": (_I32, [_P, _P, _P, _I32, C.POINTER(ConvParams), _I32, _I32, _P]),
+    "ovk_qlinear_conv": (_I32, [_P, _P, _P, _I32, C.POINTER(ConvParams), _I32, _I32, _P, _P, _I32, _I32, _P]),
+    "ovk_requantize": (_I32, [_P, _P, _I64, _I64, _I64, _P, _P, _I32, _I32, _P]),
+}
+
+
+def lib() -> C.CDLL:
+    """Loads the shared library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise OvkError(BACKEND, f"{LIB_PATH} is missing: run `python onnx-vulkan-rs_b200/build.py` "
+                                    "(there is no CPU fallback)")
+        _lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(_lib, name)
+            fn.restype = res
+            fn.argtypes = args
+    return _lib
+
+
+def _ptr(t):
+    """Device pointer of a torch tensor, an int address, or None."""
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    assert t.is_cuda and t.is_contiguous(), "device tensors must be contiguous CUDA tensors"
+    return t.data_ptr()
+
+
+def _dtype_code(t) -> int:
+    import torch
+    return {torch.float32: FLOAT, torch.float16: FLOAT16, torch.uint8: UINT8, torch.int8: INT8,
+            torch.int32: INT32}[t.dtype]
+
+
+class Context:
+    """One device, one in-order stream (VkContext, crates/vk-compute/src/context.rs:257)."""
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        import torch
+        if not torch.cuda.is_available():
+            raise OvkError(BACKEND, "no CUDA device: the quantized-matmul path has no CPU fallback")
+        h = _P()
+        if stream is None:
+            # share torch's current stream so torch allocations, copies and
+            # CUDA events are ordered with the kernels
+            with torch.cuda.device(device):
+                stream = torch.cuda.current_stream().cuda_stream
+        rc = lib().ovk_ctx_create(device, _P(stream) if stream else None, C.byref(h))
+        if rc:
+            raise OvkError(rc, lib().ovk_last_error(None).decode())
+        self.h = h
+        self.device = device
+
+    def check(self, rc: int):
+        if rc:
+            raise OvkError(rc, lib().ovk_last_error(self.h).decode())
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().ovk_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def flush(self):
+        self.check(lib().ovk_flush(self.h))
+
+    @property
+    def last_kernel(self) -> str:
+        return lib().ovk_last_kernel(self.h).decode()
+
+    @property
+    def launches(self) -> int:
+        return int(lib().ovk_launch_count(self.h))
+
+    # ---------------------------------------------------------- MatMulNBits
+    def nbits_prepack(self, b, scales, zero_points, n, k, block_size, bits=4, flags=0):
+        return NBitsWeight(self, b, scales, zero_points, n, k, block_size, bits, flags)
+
+    def matmul_nbits(self, w: "NBitsWeight", a, out=None, out_dtype=None):
+        import torch
+        m = a.numel() // w.k
+        if a.numel() != m * w.k or (a.dim() and a.shape[-1] != w.k):
+            raise OvkError(INVALID_ARGUMENT, f"MatMulNBits: A's last dimension {tuple(a.shape)} disagrees with K={w.k}")
+        if out is None:
+            out = torch.empty(tuple(a.shape[:-1]) + (w.n,), dtype=out_dtype or a.dtype, device=a.device)
+        self.check(lib().ovk_matmul_nbits(self.h, w.h, _ptr(a), _dtype_code(a), m, _ptr(out), _dtype_code(out)))
+        return out
+
+    # ------------------------------------------------- DynamicQuantizeLinear
+    def dynamic_quantize(self, x):
+        import torch
+        y = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+        scale = torch.empty((), dtype=torch.float32, device=x.device)
+        zp = torch.empty((), dtype=torch.uint8, device=x.device)
+        self.check(lib().ovk_dynamic_quantize(self.h, _ptr(x), x.numel(), _ptr(y), _ptr(scale), _ptr(zp)))
+        return y, scale, zp
+
+    # --------------------------------------------------------- MatMulInteger
+    def mmi_prepack(self, b):
+        return MmiWeight(self, b)
+
+    def matmul_integer(self, w: "MmiWeight", a, a_zp=None, b_zp=None):
+        import torch
+        m = a.numel() // max(w.k, 1)
+        out = torch.empty(tuple(a.shape[:-1]) + (w.n,), dtype=torch.int32, device=a.device)
+        self.check(lib().ovk_matmul_integer(self.h, w.h, _ptr(a), int(a.dtype == torch.int8), m,
+                                            _ptr(a_zp), _ptr(b_zp), _ptr(out)))
+        return out
+
+    def matmul_integer_scale_bias(self, w: "MmiWeight", a, a_zp, b_zp, scale, bias, product=None,
+                                  relu=False, range_slot=None):
+        import torch
+        m = a.numel() // max(w.k, 1)
+        out = torch.empty(tuple(a.shape[:-1]) + (w.n,), dtype=torch.float32, device=a.device)
+        step = lambda t: 0 if t is None or t.numel() == 1 else (1 if t.numel() == w.n and t.shape[-1] == w.n else 2)
+        flags = (EPILOGUE_RELU if relu else 0) | (EPILOGUE_RANGE if range_slot is not None else 0)
+        self.check(lib().ovk_matmul_integer_scale_bias(
+            self.h, w.h, _ptr(a), int(a.dtype == torch.int8), m, _ptr(a_zp), _ptr(b_zp),
+            _ptr(scale), step(scale), _ptr(product), step(product), _ptr(bias), step(bias), flags,
+            _ptr(range_slot), _ptr(out)))
+        return out
+
+    def qlinear_matmul(self, w: "MmiWeight", a, a_zp, b_zp, ratio, y_zp, y_signed=False):
+        import torch
+        m = a.numel() // max(w.k, 1)
+        out = torch.empty(tuple(a.shape[:-1]) + (w.n,), dtype=torch.int8 if y_signed else torch.uint8,
+                          device=a.device)
+        self.check(lib().ovk_qlinear_matmul(self.h, w.h, _ptr(a), int(a.dtype == torch.int8), m,
+                                            _ptr(a_zp), _ptr(b_zp), _ptr(ratio), ratio.numel(),
+                                            int(y_zp), int(y_signed), _ptr(out)))
+        return out
+
+    # ------------------------------------------- ConvInteger / QLinearConv
+    def qconv_prepack(self, w, group=1):
+        return QConvWeight(self, w, group)
+
+    @staticmethod
+    def _conv_params(x, pads, strides, dilations) -> ConvParams:
+        n, c, h, wd = x.shape
+        return ConvParams(n, c, h, wd, (C.c_int64 * 4)(*pads), (C.c_int64 * 2)(*strides),
+                          (C.c_int64 * 2)(*dilations))
+
+    def conv_output_shape(self, w: "QConvWeight", x, pads, strides, dilations):
+        p = self._conv_params(x, pads, strides, dilations)
+        ho, wo = _I64(), _I64()
+        rc = lib().ovk_conv_output_shape(w.h, C.byref(p), C.byref(ho), C.byref(wo))
+        if rc:
+            raise OvkError(rc, "Conv: degenerate output shape")
+        return ho.value, wo.value
+
+    def conv_integer(self, w: "QConvWeight", x, x_zp=0, w_zp=0, pads=(0, 0, 0, 0), strides=(1, 1),
+                     dilations=(1, 1)):
+        import torch
+        ho, wo = self.conv_output_shape(w, x, pads, strides, dilations)
+        out = torch.empty((x.shape[0], w.c_out, ho, wo), dtype=torch.int32, device=x.device)
+        p = self._conv_params(x, pads, strides, dilations)
+        self.check(lib().ovk_conv_integer(self.h, w.h, _ptr(x), int(x.dtype == torch.int8), C.byref(p),
+                                          int(x_zp), int(w_zp), _ptr(out)))
+        return out
+
+    def qlinear_conv(self, w: "QConvWeight", x, x_zp, w_zp, ratio, bias, y_zp, y_signed=False,
+                     pads=(0, 0, 0, 0), strides=(1, 1), dilations=(1, 1), out=None):
+        """ratio: host float32 array of C_out values, (x_scale*w_scale[c])/y_scale."""
+        import numpy as np
+        import torch
+        ho, wo = self.conv_output_shape(w, x, pads, strides, dilations)
+        if out is None:
+            out = torch.empty((x.shape[0], w.c_out, ho, wo), dtype=torch.int8 if y_signed else torch.uint8,
+                              device=x.device)
+        ratio = np.ascontiguousarray(ratio, dtype=np.float32)
+        if ratio.size == 1:
+            ratio = np.repeat(ratio, w.c_out)
+        assert ratio.size == w.c_out
+        p = self._conv_params(x, pads, strides, dilations)
+        self.check(lib().ovk_qlinear_conv(self.h, w.h, _ptr(x), int(x.dtype == torch.int8), C.byref(p),
+                                          int(x_zp), int(w_zp), ratio.ctypes.data, _ptr(bias),
+                                          int(y_zp), int(y_signed), _ptr(out)))
+        return out
+
+    def requantize(self, acc, inner, ratio, y_zp, bias=None, y_signed=False):
+        import torch
+        out = torch.empty(acc.shape, dtype=torch.int8 if y_signed else torch.uint8, device=acc.device)
+        self.check(lib().ovk_requantize(self.h, _ptr(acc), acc.numel(), int(inner), ratio.numel(),
+                                        _ptr(bias), _ptr(ratio), int(y_zp), int(y_signed), _ptr(out)))
+        return out
+
+
+class NBitsWeight:
+    """A MatMulNBits weight prepared once (the role packed_b plays, interp.rs:2712)."""
+
+    def __init__(self, ctx: Context, b, scales, zero_points, n, k, block_size, bits=4, flags=0):
+        self.ctx, self.n, self.k, self.block_size = ctx, int(n), int(k), int(block_size)
+        self._keep = (b, scales, zero_points)  # the operator-layout buffers must outlive the handle
+        h = _P()
+        ctx.check(lib().ovk_nbits_prepack(ctx.h, _ptr(b), _ptr(scales), _dtype_code(scales),
+                                          _ptr(zero_points), n, k, bits, block_size, flags, C.byref(h)))
+        self.h = h
+
+    def __del__(self):
+        try:
+            if self.h and self.ctx.h:
+                lib().ovk_nbits_weight_destroy(self.ctx.h, self.h)
+        except Exception:
+            pass
+
+
+class MmiWeight:
+    """B [K,N] of MatMulInteger in the tensor-core layout (packed_b, interp.rs:2712)."""
+
+    def __init__(self, ctx: Context, b):
+        import torch
+        assert b.dim() == 2
+        self.ctx, self.k, self.n = ctx, int(b.shape[0]), int(b.shape[1])
+        self.signed = b.dtype == torch.int8
+        h = _P()
+        ctx.check(lib().ovk_mmi_prepack(ctx.h, _ptr(b), int(self.signed), self.k, self.n, C.byref(h)))
+        self.h = h
+
+    def __del__(self):
+        try:
+            if self.h and self.ctx.h:
+                lib().ovk_mmi_weight_destroy(self.ctx.h, self.h)
+        except Exception:
+            pass
+
+
+class QConvWeight:
+    """A ConvInteger / QLinearConv filter bank [C_out, C_in/group, KH, KW]."""
+
+    def __init__(self, ctx: Context, w, group=1):
+        import torch
+        if w.dim() == 3:  # 1-D convolution: W = 1
+            w = w.unsqueeze(-1)
+        self.ctx = ctx
+        self.c_out, self.cig, self.kh, self.kw = (int(v) for v in w.shape)
+        self.group = int(group)
+        h = _P()
+        ctx.check(lib().ovk_qconv_prepack(ctx.h, _ptr(w.contiguous()), int(w.dtype == torch.int8),
+                                          self.c_out, self.cig, self.kh, self.kw, self.group, C.byref(h)))
+        self.h = h
+
+    def __del__(self):
+        try:
+            if self.h and self.ctx.h:
+                lib().ovk_qconv_weight_destroy(self.ctx.h, self.h)
+        except Exception:
+            pass

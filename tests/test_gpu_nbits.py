@@ -1,0 +1,117 @@
+"""MatMulNBits parity through the C ABI against the CPU oracle (B200 only)."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+import oracle as orc
+from gpu_util import assert_close, ctx, dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+def run_gpu(a, nib, zp, scale, k, n, bs, out_dtype=None, flags=0):
+    b = dev(orc.pack_nibbles(nib, bs))
+    s = dev(scale.reshape(-1))
+    z = None if zp is None else dev(orc.pack_zero_points(zp))
+    w = ctx().nbits_prepack(b, s, z, n, k, bs, flags=flags)
+    y = ctx().matmul_nbits(w, dev(a), out_dtype=out_dtype)
+    return host(y), ctx().last_kernel
+
+
+@pytest.mark.parametrize("m,k,n,bs", cases.NBITS_REFERENCE_CASES)
+def test_reference_cases(m, k, n, bs):
+    """crates/onnx-vulkan-core/tests/matmul_nbits.rs:167-252, same tolerance (:159-164)."""
+    a, nib, zp, scale = cases.nbits_reference_case(m, k, n, bs)
+    got, _ = run_gpu(a, nib, zp, scale, k, n, bs)
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, bs), scale, orc.pack_zero_points(zp), k, n, bs)
+    assert got.shape == (m, n)
+    assert np.all(np.abs(got - want) <= 1e-4 * np.maximum(np.abs(want), 1.0))
+
+
+@pytest.mark.parametrize("m,k,n,bs", cases.NBITS_REFERENCE_CASES)
+def test_reference_cases_general_kernel(m, k, n, bs):
+    """The same cases forced onto the general kernel (operator layout only)."""
+    import ovk_b200
+    a, nib, zp, scale = cases.nbits_reference_case(m, k, n, bs)
+    got, kern = run_gpu(a, nib, zp, scale, k, n, bs, flags=ovk_b200.NBITS_NO_DECODE_COPY)
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, bs), scale, orc.pack_zero_points(zp), k, n, bs)
+    assert np.all(np.abs(got - want) <= 1e-4 * np.maximum(np.abs(want), 1.0))
+    if m == 1:
+        assert kern == "nbits_rows"
+
+
+def test_config1_single_op_fp32_no_zero_point():
+    """M=1 K=N=2048 bs=32 f32, zero points absent (implicit 8); atol=rtol=1e-4."""
+    a, nib, _, scale = cases.nbits_synthetic(1, 1, 2048, 2048, 32, real=np.float32,
+                                             scale_lo=0.005, scale_hi=0.02, with_zp=False)
+    got, _ = run_gpu(a, nib, None, scale, 2048, 2048, 32)
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, 32), scale, None, 2048, 2048, 32)
+    assert_close(got, want, 1e-4, 1e-4, "config 1")
+
+
+GEMMA = [(1152, 1024), (1152, 256), (1024, 1152), (1152, 6912), (6912, 1152)]
+
+
+@pytest.mark.parametrize("k,n", GEMMA)
+@pytest.mark.parametrize("m", [1, 3, 8])
+def test_gemma_projections_decode_fp16(k, n, m):
+    """Gemma3-1B-shaped projections, fp16 in/out, atol=rtol=1e-3."""
+    a, nib, zp, scale = cases.nbits_synthetic(2, m, k, n, 32)
+    got, _ = run_gpu(a, nib, zp, scale, k, n, 32)
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, 32), scale, orc.pack_zero_points(zp), k, n, 32)
+    assert_close(got, want, 1e-3, 1e-3, f"gemma {k}->{n} M={m}")
+
+
+def test_gemma_lm_head_decode_full_size():
+    """K=1152 N=262144 (151 MB of weights), M=1, every output checked."""
+    k, n = 1152, 262144
+    a, nib, zp, scale = cases.nbits_synthetic(2, 1, k, n, 32)
+    got, _ = run_gpu(a, nib, zp, scale, k, n, 32)
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, 32), scale, orc.pack_zero_points(zp), k, n, 32)
+    assert_close(got, want, 1e-3, 1e-3, "gemma lm_head")
+
+
+@pytest.mark.parametrize("bs", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("real", [np.float32, np.float16])
+def test_block_sizes_and_ragged_k(bs, real):
+    """K not a multiple of the block or of 32, N not a multiple of any tile."""
+    m, k, n = 2, 3 * bs + 40, 77
+    a, nib, zp, scale = cases.nbits_synthetic(7, m, k, n, bs, real=real)
+    got, _ = run_gpu(a, nib, zp, scale, k, n, bs)
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, bs), scale, orc.pack_zero_points(zp), k, n, bs)
+    tol = 1e-3 if real == np.float16 else 1e-4
+    assert_close(got, want, tol, tol, f"bs={bs}")
+
+
+def test_linearity_in_the_activations_full_size():
+    """y(a1 + a2) == y(a1) + y(a2) within float error: a size-independent check
+    on the Qwen-sized decode shape K=3584 N=18944 bs=128."""
+    k, n, bs = 3584, 18944, 128
+    a, nib, zp, scale = cases.nbits_synthetic(5, 2, k, n, bs, real=np.float32, scale_lo=0.001, scale_hi=0.01)
+    b = dev(orc.pack_nibbles(nib, bs)); s = dev(scale.reshape(-1)); z = dev(orc.pack_zero_points(zp))
+    w = ctx().nbits_prepack(b, s, z, n, k, bs)
+    y1 = host(ctx().matmul_nbits(w, dev(a[0:1])))
+    y2 = host(ctx().matmul_nbits(w, dev(a[1:2])))
+    y12 = host(ctx().matmul_nbits(w, dev(a[0:1] + a[1:2])))
+    assert_close(y12, y1 + y2, 2e-4, 2e-4, "linearity")
+    cols = np.arange(0, n, 37)
+    want = orc.matmul_nbits(a[0:1], orc.pack_nibbles(nib[cols], bs), scale[cols],
+                            orc.pack_zero_points(zp[cols]), k, cols.size, bs)
+    assert_close(y1[:, cols], want, 1e-4, 1e-4, "sampled columns")
+
+
+def test_refusals_match_the_reference_predicate():
+    """interp.rs:452-464: bits 4 only, block_size a multiple of 8."""
+    import ovk_b200
+    b = torch.zeros(64, dtype=torch.uint8, device="cuda")
+    s = torch.ones(4, dtype=torch.float32, device="cuda")
+    for kwargs in ({"bits": 8}, {"block_size": 12}):
+        args = dict(n=4, k=32, block_size=32, bits=4)
+        args.update(kwargs)
+        with pytest.raises(ovk_b200.OvkError) as e:
+            ctx().nbits_prepack(b, s, None, args["n"], args["k"], args["block_size"], bits=args["bits"])
+        assert e.value.status == ovk_b200.UNSUPPORTED
+    w = ctx().nbits_prepack(b, s, None, 4, 32, 32)
+    with pytest.raises(ovk_b200.OvkError):
+        ctx().matmul_nbits(w, torch.zeros(1, 31, device="cuda"))

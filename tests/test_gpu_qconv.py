@@ -1,0 +1,117 @@
+"""ConvInteger / QLinearConv parity: int32 accumulators and requantised bytes equal."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import cases
+import oracle as orc
+from gpu_util import ctx, dev, host
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.mark.parametrize("c_in,c_out,h,w,stride,dil,pads,xs,ws", [
+    (64, 32, 20, 20, 1, 1, (1, 1, 1, 1), False, False),
+    (32, 48, 18, 22, 2, 2, (2, 0, 1, 3), True, True),
+    (32, 16, 15, 15, 1, 1, (1, 1, 1, 1), False, True),
+])
+def test_reference_geometries(c_in, c_out, h, w, stride, dil, pads, xs, ws):
+    """crates/onnx-vulkan-core/tests/conv_integer_im2col.rs:185-247."""
+    x = cases.lcg_bytes_fast(c_in * h * w, 11).reshape(1, c_in, h, w)
+    wt = cases.lcg_bytes_fast(c_out * c_in * 9, 5).reshape(c_out, c_in, 3, 3)
+    x = x.view(np.int8) if xs else x
+    wt = wt.view(np.int8) if ws else wt
+    x_zp = -5 if xs else 129
+    wq = ctx().qconv_prepack(dev(wt))
+    got = ctx().conv_integer(wq, dev(x), x_zp, 7, pads=pads, strides=(stride, stride), dilations=(dil, dil))
+    want = orc.conv_integer(x, wt, x_zp, 7, strides=(stride, stride), dilations=(dil, dil), pads=pads)
+    assert np.array_equal(host(got), want)
+
+
+def test_literal_vectors():
+    """crates/onnx-vulkan-core/tests/qlinear.rs:106-236."""
+    v = json.load(open(os.path.join(GOLDEN, "qlinear_literal_vectors.json")))
+    for name, xs, ws in (("conv_per_channel", (1, 1, 3, 3), (2, 1, 2, 2)),
+                         ("conv_per_tensor", (1, 1, 3, 3), (2, 1, 2, 2)),
+                         ("conv_no_bias", (1, 1, 2, 2), (1, 1, 2, 2))):
+        c = v[name]
+        x = np.array(c["x"], dtype=np.uint8).reshape(xs)
+        w = np.array(c["w"], dtype=np.int8).reshape(ws)
+        w_scale = np.atleast_1d(np.array(c["w_scale"], dtype=np.float32))
+        bias = np.array(c["bias"], dtype=np.int32) if "bias" in c else None
+        want = orc.qlinear_conv(x, c["x_scale"], c["x_zp"], w, w_scale, 0, c["y_scale"], c["y_zp"], bias=bias)
+        ratio = orc.requantize_ratio(c["x_scale"], w_scale, c["y_scale"])
+        wq = ctx().qconv_prepack(dev(w))
+        got = ctx().qlinear_conv(wq, dev(x), c["x_zp"], 0, ratio, None if bias is None else dev(bias), c["y_zp"])
+        assert np.array_equal(host(got), want), name
+
+
+def _resnet_block(batch, seed_cfg=4):
+    x = cases.rng_for(seed_cfg, 0).integers(0, 256, size=(batch, 64, 56, 56), dtype=np.uint8)
+    w = cases.rng_for(seed_cfg, 1).integers(-127, 128, size=(64, 64, 3, 3), dtype=np.int8)
+    w_scale = cases.rng_for(seed_cfg, 2).uniform(0.001, 0.01, size=64).astype(np.float32)
+    bias = cases.rng_for(seed_cfg, 3).integers(-1000, 1001, size=64, dtype=np.int32)
+    return x, w, w_scale, bias
+
+
+def test_resnet_block_small_batch_every_output():
+    """Config 4 at batch 2: u8 NCHW 64ch 56x56, int8 3x3 per-channel weights,
+    int32 bias, pad 1; uint8 outputs and int32 accumulators equal."""
+    x, w, w_scale, bias = _resnet_block(2)
+    wq = ctx().qconv_prepack(dev(w))
+    acc = ctx().conv_integer(wq, dev(x), 128, 0, pads=(1, 1, 1, 1))
+    want_acc = orc.conv_integer(x, w, 128, 0, pads=(1, 1, 1, 1))
+    assert np.array_equal(host(acc), want_acc)
+    ratio = orc.requantize_ratio(0.02, w_scale, 0.05)
+    got = ctx().qlinear_conv(wq, dev(x), 128, 0, ratio, dev(bias), 128, pads=(1, 1, 1, 1))
+    want = orc.requantize(want_acc, 56 * 56, ratio, 128, bias)
+    assert np.array_equal(host(got), want)
+
+
+def test_resnet_block_full_batch_sampled_images_and_batch_independence():
+    """Config 4 at batch 64: images 0, 31 and 63 against the oracle, and the
+    batched result equal to the same images run one at a time."""
+    x, w, w_scale, bias = _resnet_block(64)
+    ratio = orc.requantize_ratio(0.02, w_scale, 0.05)
+    wq = ctx().qconv_prepack(dev(w))
+    xd = dev(x)
+    got = host(ctx().qlinear_conv(wq, xd, 128, 0, ratio, dev(bias), 128, pads=(1, 1, 1, 1)))
+    for i in (0, 31, 63):
+        want = orc.qlinear_conv(x[i:i + 1], 0.02, 128, w, w_scale, 0, 0.05, 128, bias=bias, pads=(1, 1, 1, 1))
+        assert np.array_equal(got[i:i + 1], want), i
+        single = host(ctx().qlinear_conv(wq, xd[i:i + 1].contiguous(), 128, 0, ratio, dev(bias), 128, pads=(1, 1, 1, 1)))
+        assert np.array_equal(single, got[i:i + 1])
+
+
+@pytest.mark.parametrize("group,c_in,c_out", [(4, 16, 8), (16, 16, 16)])
+def test_grouped_and_depthwise(group, c_in, c_out):
+    """src/shaders/conv_integer.rs:73-110: the direct form is the only one groups can use."""
+    x = cases.lcg_bytes_fast(2 * c_in * 9 * 11, 3).reshape(2, c_in, 9, 11)
+    w = cases.lcg_bytes_fast(c_out * (c_in // group) * 9, 4).reshape(c_out, c_in // group, 3, 3).view(np.int8)
+    wq = ctx().qconv_prepack(dev(w), group=group)
+    got = ctx().conv_integer(wq, dev(x), 120, 3, pads=(1, 1, 1, 1), strides=(2, 1))
+    want = orc.conv_integer(x, w, 120, 3, pads=(1, 1, 1, 1), strides=(2, 1), group=group)
+    assert np.array_equal(host(got), want)
+
+
+def test_signed_output_and_one_dimensional_conv():
+    x = cases.lcg_bytes_fast(3 * 8 * 40, 6).reshape(3, 8, 40, 1).view(np.int8)
+    w = cases.lcg_bytes_fast(12 * 8 * 5, 8).reshape(12, 8, 5, 1).view(np.int8)
+    w_scale = np.linspace(0.002, 0.02, 12).astype(np.float32)
+    ratio = orc.requantize_ratio(0.05, w_scale, 0.4)
+    wq = ctx().qconv_prepack(dev(w))
+    got = ctx().qlinear_conv(wq, dev(x), -3, 0, ratio, None, -11, y_signed=True, pads=(2, 0, 2, 0))
+    want = orc.qlinear_conv(x, 0.05, -3, w, w_scale, 0, 0.4, -11, out_signed=True, pads=(2, 0, 2, 0))
+    assert np.array_equal(host(got), want)
+
+
+def test_requantize_pass_matches():
+    """src/shaders/qlinear.rs:28-63 on its own, ragged length."""
+    acc = cases.rng_for(4, 9).integers(-2 ** 20, 2 ** 20, size=(3, 5, 7), dtype=np.int32)
+    ratio = np.linspace(1e-4, 3e-3, 5).astype(np.float32)
+    bias = np.arange(-2, 3, dtype=np.int32) * 1000
+    got = ctx().requantize(dev(acc), 7, dev(ratio), 17, bias=dev(bias))
+    assert np.array_equal(host(got), orc.requantize(acc, 7, ratio, 17, bias))
