@@ -1,0 +1,319 @@
+// MatMulInteger on the 5th-generation tensor cores: tcgen05.mma kind::i8 with
+// int32 accumulators in tensor memory, operands staged by TMA, fused epilogue.
+//
+// This is the successor of the reference's production int8 GEMM
+// (crates/onnx-vulkan-core/src/shaders/glsl/matmul_integer_coop_smem.comp:
+// a 128x128 shared-memory block of 16x16x32 cooperative-matrix tiles with the
+// zero-point algebra applied at the store, :306-345) and of its epilogue
+// (matmul_integer_coop.comp:156-196).
+//
+// One CTA computes a 128 x BN tile of A[M,K] (u8/i8, row major) times
+// Bt[N,K] (the packed weight, K contiguous):
+//   warp 0    TMA producer: 128-byte K slabs of A and Bt into a ring of
+//             128B-swizzled stages, completion on an mbarrier per stage
+//   warp 1    allocates tensor memory, issues four K=32 MMAs per stage from one
+//             thread, frees the stage with tcgen05.commit
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (one row per thread),
+//             sum ab - za*sum_k b - zb*sum_k a + K*za*zb, then the store
+//             selected by EpiParams (int32 / dequantised f32 / requantised u8)
+// kind::i8 takes signed and unsigned bytes per operand, so nothing is flipped
+// (the reference's FLIP_BYTES pass, shaders/matmul_integer.rs:25-38, is not needed).
+// Ragged M, N and K are handled by TMA zero fill plus store predicates.
+#include "ovk_internal.h"
+#include "epilogue.cuh"
+#include "umma.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 128;  // bytes of K per stage = one 128-byte swizzle row
+constexpr int A_BYTES = BM * BK;
+constexpr int THREADS = 192;
+constexpr long long WAIT_CYCLES = 2000000000ll;  // about a second
+
+struct TcParams {
+    int64_t M;
+    int N, K, num_kb;
+    const int32_t *colsum;
+    const int32_t *rowsum;  // valid when b_zp may be non-zero
+    const void *a_zp, *b_zp;
+    int a_signed, b_signed;
+    EpiParams epi;
+    void *out;
+    int vec_ok;  // output rows may be written with 16-byte (int32/f32) or 4-byte (u8) stores
+    int *status;
+};
+
+__device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
+{
+    const long long t0 = clock64();
+    while (!umma::mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > WAIT_CYCLES)
+            return false;
+    }
+    return true;
+}
+
+template <int BN> constexpr int stages_for() { return BN == 256 ? 4 : (BN == 128 ? 6 : 8); }
+template <int BN> constexpr size_t smem_for()
+{
+    return size_t(stages_for<BN>()) * (A_BYTES + BN * BK) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TcParams p)
+{
+    constexpr int STAGES = stages_for<BN>();
+    constexpr int B_BYTES = BN * BK;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *sA = smem;
+    uint8_t *sB = smem + STAGES * A_BYTES;
+    uint64_t *full = reinterpret_cast<uint64_t *>(sB + STAGES * B_BYTES);
+    uint64_t *empty = full + STAGES;
+    uint64_t *acc_ready = empty + STAGES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t m0 = int64_t(blockIdx.y) * BM;
+    const int n0 = blockIdx.x * BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            umma::mbar_init(&full[s], 1);
+            umma::mbar_init(&empty[s], 1);
+        }
+        umma::mbar_init(acc_ready, 1);
+        umma::fence_barrier_init();
+    }
+    if (warp == 1) {
+        umma::tmem_alloc(tmem_slot, BN);
+        umma::tmem_relinquish();
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            umma::prefetch_tmap(&tmA);
+            umma::prefetch_tmap(&tmB);
+            for (int kb = 0; kb < p.num_kb; kb++) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!wait_bounded(&empty[s], ph ^ 1)) {
+                    atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
+                    break;
+                }
+                umma::mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                umma::tma_load_2d(sA + s * A_BYTES, &tmA, &full[s], kb * BK, int(m0));
+                umma::tma_load_2d(sB + s * B_BYTES, &tmB, &full[s], kb * BK, n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma::instr_desc(2, p.a_signed ? 1 : 0, p.b_signed ? 1 : 0, BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < p.num_kb && ok; kb++) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!wait_bounded(&full[s], ph)) {
+                    atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
+                    ok = false;
+                    break;
+                }
+                umma::tc_fence_after();
+                const uint32_t a_addr = umma::smem_u32(sA + s * A_BYTES);
+                const uint32_t b_addr = umma::smem_u32(sB + s * B_BYTES);
+#pragma unroll
+                for (int j = 0; j < BK / 32; j++) {
+                    const uint64_t da = umma::smem_desc(a_addr + j * 32, 1024, umma::LAYOUT_SW128);
+                    const uint64_t db = umma::smem_desc(b_addr + j * 32, 1024, umma::LAYOUT_SW128);
+                    umma::mma_i8(tmem_base, da, db, idesc, (kb | j) != 0);
+                }
+                umma::mma_commit(&empty[s]);
+            }
+            if (ok)
+                umma::mma_commit(acc_ready);
+        }
+    } else {
+        // Epilogue: warp w may read tensor-memory lanes 32*(w % 4) .. +31.
+        const int q = warp & 3;
+        const bool ready = wait_bounded(acc_ready, 0);
+        if (!ready && lane == 0)
+            atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
+        umma::tc_fence_after();
+        const int64_t row = m0 + q * 32 + lane;
+        const bool row_ok = ready && row < p.M;
+        const int32_t za = load_zp(p.a_zp, p.a_signed), zb = load_zp(p.b_zp, p.b_signed);
+        const uint32_t row_term = uint32_t(p.K) * uint32_t(za) * uint32_t(zb) -
+                                  ((zb != 0 && p.rowsum && row_ok) ? uint32_t(zb) * uint32_t(p.rowsum[row]) : 0u);
+        float run_max = 0.0f, run_neg = 0.0f;
+        const bool vec4 = p.vec_ok != 0;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            umma::tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c0), r);
+            umma::tmem_ld_wait();
+            if (!row_ok || n0 + c0 >= p.N)
+                continue;
+            const int col0 = n0 + c0;
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const int col = col0 + j;
+                const int32_t cs = col < p.N ? p.colsum[col] : 0;
+                r[j] = r[j] - uint32_t(za) * uint32_t(cs) + row_term;
+            }
+            if (p.epi.mode == EPI_RAW) {
+                int32_t *o = static_cast<int32_t *>(p.out) + row * p.N + col0;
+                if (vec4 && col0 + 32 <= p.N) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<int4 *>(o + j) = make_int4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                } else {
+                    for (int j = 0; j < 32 && col0 + j < p.N; j++)
+                        o[j] = int32_t(r[j]);
+                }
+            } else if (p.epi.mode == EPI_SCALE) {
+                float *o = static_cast<float *>(p.out) + row * p.N + col0;
+                float f[32];
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    if (col0 + j < p.N) {
+                        f[j] = epi_scale_value(p.epi, col0 + j, float(int32_t(r[j])));
+                        run_max = fmaxf(run_max, f[j]);
+                        run_neg = fmaxf(run_neg, -f[j]);
+                    } else {
+                        f[j] = 0.0f;
+                    }
+                }
+                if (vec4 && col0 + 32 <= p.N) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<float4 *>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                } else {
+                    for (int j = 0; j < 32 && col0 + j < p.N; j++)
+                        o[j] = f[j];
+                }
+            } else {
+                uint8_t *o = static_cast<uint8_t *>(p.out) + row * p.N + col0;
+                if (vec4 && col0 + 32 <= p.N) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        uint32_t w = 0;
+#pragma unroll
+                        for (int t = 0; t < 4; t++)
+                            w |= (uint32_t(epi_requant_value(p.epi, col0 + j + t, int32_t(r[j + t]))) & 0xffu) << (8 * t);
+                        *reinterpret_cast<uint32_t *>(o + j) = w;
+                    }
+                } else {
+                    for (int j = 0; j < 32 && col0 + j < p.N; j++)
+                        o[j] = uint8_t(epi_requant_value(p.epi, col0 + j, int32_t(r[j])));
+                }
+            }
+        }
+        if (p.epi.mode == EPI_SCALE)
+            epi_fold_range(p.epi, run_max, run_neg);
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    if (warp == 1)
+        umma::tmem_dealloc(tmem_base, BN);
+}
+
+// sum_k a[m][k] per row, needed only when the weight's zero point is not 0:
+// exits at once otherwise (the zero point is read on the device, never on the host).
+__global__ void __launch_bounds__(256)
+mmi_rowsum_kernel(const uint8_t *__restrict__ a, int64_t M, int K, int a_signed, const void *b_zp,
+                  int b_signed, int32_t *__restrict__ rowsum)
+{
+    if (load_zp(b_zp, b_signed) == 0)
+        return;
+    const int64_t row = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= M)
+        return;
+    const uint32_t *aw = reinterpret_cast<const uint32_t *>(a + row * K);  // K % 16 == 0, base 16-byte aligned
+    int32_t s = 0;
+    for (int w = lane; w < K / 4; w += 32) {
+        const uint32_t x = aw[w];
+        s = a_signed ? __dp4a(int(x), int(0x01010101), s) : int32_t(__dp4a(x, 0x01010101u, uint32_t(s)));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0)
+        rowsum[row] = s;
+}
+
+template <int BN>
+int32_t launch(ovk_ctx *ctx, const CUtensorMap &tmA, const ovk_mmi_weight *w, const TcParams &p)
+{
+    CUtensorMap tmB;
+    if (!ovk_make_tmap_2d(&tmB, w->bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(w->k_pad), uint64_t(w->n_pad),
+                          uint64_t(w->k_pad), BK, BN, CU_TENSOR_MAP_SWIZZLE_128B))
+        return ovk_fail(ctx, OVK_BACKEND, "MatMulInteger: cuTensorMapEncodeTiled failed for the packed weight");
+    OVK_CUDA(ctx, cudaFuncSetAttribute(mmi_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       int(smem_for<BN>())));
+    dim3 grid(unsigned(ceil_div64(p.N, BN)), unsigned(ceil_div64(p.M, BM)));
+    mmi_tc_kernel<BN><<<grid, THREADS, smem_for<BN>(), ctx->stream>>>(tmA, tmB, p);
+    OVK_LAUNCHED(ctx, BN == 256 ? "mmi_tc_128x256" : (BN == 128 ? "mmi_tc_128x128" : "mmi_tc_128x64"));
+    return OVK_OK;
+}
+
+}  // namespace
+
+// The tensor-core tiles need whole 16-byte rows of A for TMA and enough work
+// to fill a tile; everything else stays on the small-shape kernel
+// (the split the reference makes with coop_applies, shaders/matmul_integer.rs:501-512).
+bool ovk_mmi_tc_applies(const ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int64_t m)
+{
+    (void)ctx;
+    return m >= 16 && w->n >= 16 && w->k >= 32 && (w->k % 16) == 0 && aligned_to(a, 16) &&
+           ceil_div64(m, BM) <= 65535 && m < (int64_t(1) << 31);
+}
+
+int32_t ovk_mmi_tc_prepare_weight(ovk_ctx *, ovk_mmi_weight *) { return OVK_OK; }
+
+int32_t ovk_mmi_tc_launch(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int32_t a_signed, int64_t m,
+                          const void *a_zp, const void *b_zp, const EpiParams &epi, void *out)
+{
+    TcParams p = {};
+    p.M = m;
+    p.N = int(w->n);
+    p.K = int(w->k);
+    p.num_kb = int(ceil_div64(w->k, BK));
+    p.colsum = w->colsum;
+    p.a_zp = a_zp;
+    p.b_zp = b_zp;
+    p.a_signed = a_signed ? 1 : 0;
+    p.b_signed = w->b_signed;
+    p.epi = epi;
+    p.out = out;
+    p.vec_ok = (w->n % 4) == 0 && aligned_to(out, epi.mode == EPI_REQUANT ? 4 : 16);
+    p.status = ctx->dev_status;
+    if (b_zp) {
+        void *ws = nullptr;
+        int32_t rc = ovk_scratch(ctx, size_t(m) * sizeof(int32_t), &ws);
+        if (rc != OVK_OK)
+            return rc;
+        p.rowsum = static_cast<int32_t *>(ws);
+        mmi_rowsum_kernel<<<unsigned(ceil_div64(m * 32, 256)), 256, 0, ctx->stream>>>(
+            static_cast<const uint8_t *>(a), m, p.K, p.a_signed, b_zp, p.b_signed, static_cast<int32_t *>(ws));
+        OVK_LAUNCHED(ctx, "mmi_rowsum");
+    }
+    CUtensorMap tmA;
+    if (!ovk_make_tmap_2d(&tmA, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(w->k), uint64_t(m), uint64_t(w->k), BK,
+                          BM, CU_TENSOR_MAP_SWIZZLE_128B))
+        return ovk_fail(ctx, OVK_BACKEND, "MatMulInteger: cuTensorMapEncodeTiled failed for A");
+    // Largest tile that still gives every SM a CTA; the smallest one otherwise
+    // (the reference picks 64x64 blocks under 64 workgroups, shaders/matmul_integer.rs:467-487).
+    const int64_t mt = ceil_div64(m, BM);
+    if (w->n >= 256 && mt * ceil_div64(w->n, 256) >= ctx->sm_count)
+        return launch<256>(ctx, tmA, w, p);
+    if (w->n >= 128 && mt * ceil_div64(w->n, 128) >= ctx->sm_count)
+        return launch<128>(ctx, tmA, w, p);
+    return launch<64>(ctx, tmA, w, p);
+}

@@ -119,6 +119,8 @@ class Context:
             # CUDA events are ordered with the kernels
             with torch.cuda.device(device):
                 stream = torch.cuda.current_stream().cuda_stream
+            if stream == 0:
+                stream = 1  # cudaStreamLegacy: the default stream by its explicit handle
         rc = lib().ovk_ctx_create(device, _P(stream) if stream else None, C.byref(h))
         if rc:
             raise OvkError(rc, lib().ovk_last_error(None).decode())
