@@ -1,0 +1,603 @@
+// MatMulNBits decode (M <= 8): the HBM-bound matrix-vector product.
+//
+// Successor of the reference's wide-column decode kernel
+// (crates/onnx-vulkan-core/src/shaders/matmul_nbits.rs:458-516: whole blocks
+// read as 128-bit vectors, four accumulators, scale applied once per block).
+// The arithmetic per block is the same - an exact sum of (nibble - zero point)
+// * a over the block, then ONE multiply by the block's scale accumulated in
+// f32 - but the machinery is built for a 6.5 TB/s memory system:
+//
+//  * ovk_nbits_prepack re-tiles the weight once (the role packed_b plays for
+//    MatMulInteger, src/interp.rs:2712): tiles of P 16-column panels x KC
+//    quantization blocks, each tile ONE contiguous, 16-byte aligned range that
+//    holds its nibbles, scales and zero points, the nibbles already in the
+//    order the math unit wants them.  Bytes per weight are unchanged (4 bits
+//    + scale + 4-bit zero point).
+//  * a persistent CTA per SM streams its tiles with cp.async.bulk into a
+//    3-stage shared-memory ring (one producer thread, mbarrier completion), so
+//    ~130 KB per SM are in flight without spending registers on it;
+//  * eight consumer warps unpack with two logic ops per pair of nibbles
+//    (the 0x6400 "1024 + n" fp16 trick; (n - z) is exact) and feed
+//    mma.sync.m16n8k16: 16 weight columns x 16 k x up to 8 activation rows per
+//    instruction, products exact, f32 accumulation.  A block's partial sum is
+//    then scaled and added in f32 on the CUDA cores, as the reference does.
+//  * f32 activations are split into an fp16 high and low part (two of the
+//    eight batch columns), after an exact power-of-two row normalisation, so
+//    the result keeps ~22 bits of the activation.
+// Without tensor cores the unpack + convert + FMA chain costs ~3 issue slots
+// per nibble and caps the kernel well below the memory roofline.
+#include "ovk_internal.h"
+#include "umma.cuh"
+
+namespace {
+
+constexpr int CONSUMER_WARPS = 16;
+constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int STAGES = 3;
+constexpr uint32_t STAGE_MAX = 48 * 1024;
+constexpr size_t ACT_MAX = 64 * 1024;
+constexpr long long WAIT_CYCLES = 2000000000ll;
+
+struct DecParams {
+    const uint8_t *packed;
+    const void *a;
+    void *y;
+    int M, K, N;
+    int P, KC, GB, NKC, ntiles;
+    uint32_t s_off, z_off, tile_bytes;
+    int g_pad;  // k32 groups covered by the tiles (>= ceil(K/32))
+    int rows;   // batch columns in use: M, or 2M for split f32 activations
+    int *status;
+};
+
+__device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
+{
+    if (umma::mbar_try_wait(bar, parity))
+        return true;
+    const long long t0 = clock64();
+    for (uint32_t spins = 0;; spins++) {
+        if (umma::mbar_try_wait(bar, parity))
+            return true;
+        if ((spins & 63u) == 63u && clock64() - t0 > WAIT_CYCLES)
+            return false;
+    }
+}
+
+__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b)
+{
+    __half2 r = __hsub2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi)
+{
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+
+__device__ __forceinline__ uint2 lds64(uint32_t addr)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds8(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// d = A x B (C = 0)
+__device__ __forceinline__ void mma16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+// One quantization block of one 16-column panel: GB k32-groups, two chains of
+// MMAs (even / odd halves of each weight word), then the block's scale in f32.
+template <bool SCALE_F32, int GB>
+__device__ __forceinline__ void do_block(float (&acc)[4], uint32_t wa, uint32_t sa, uint32_t za, uint32_t aa)
+{
+    float s_lo, s_hi;  // scales of columns g and g+8
+    if constexpr (SCALE_F32) {
+        const uint2 sv = lds64(sa);
+        s_lo = __uint_as_float(sv.x);
+        s_hi = __uint_as_float(sv.y);
+    } else {
+        uint32_t sv = lds32(sa);
+        const __half2 h = *reinterpret_cast<__half2 *>(&sv);
+        s_lo = __low2float(h);
+        s_hi = __high2float(h);
+    }
+    const uint32_t zb = lds8(za);
+    const uint32_t z_lo = zb & 15u, z_hi = zb >> 4;
+    const uint32_t zs_lo = z_lo * 0x00010001u + 0x64006400u, zs16_lo = z_lo * 0x00100010u + 0x64006400u;
+    const uint32_t zs_hi = z_hi * 0x00010001u + 0x64006400u, zs16_hi = z_hi * 0x00100010u + 0x64006400u;
+    float d0[4], d1[4];
+#pragma unroll
+    for (int gi = 0; gi < GB; gi++) {
+        const uint2 wv = lds64(wa + gi * 256);
+        const uint4 av = lds128(aa + gi * 64);
+        const uint32_t x8 = wv.x >> 8, y8 = wv.y >> 8;
+        const uint32_t a0 = h2_sub((wv.x & 0x000F000Fu) | 0x64006400u, zs_lo);
+        const uint32_t a1 = h2_sub((wv.y & 0x000F000Fu) | 0x64006400u, zs_hi);
+        const uint32_t a2 = h2_sub((wv.x & 0x00F000F0u) | 0x64006400u, zs16_lo);
+        const uint32_t a3 = h2_sub((wv.y & 0x00F000F0u) | 0x64006400u, zs16_hi);
+        const uint32_t c0 = h2_sub((x8 & 0x000F000Fu) | 0x64006400u, zs_lo);
+        const uint32_t c1 = h2_sub((y8 & 0x000F000Fu) | 0x64006400u, zs_hi);
+        const uint32_t c2 = h2_sub((x8 & 0x00F000F0u) | 0x64006400u, zs16_lo);
+        const uint32_t c3 = h2_sub((y8 & 0x00F000F0u) | 0x64006400u, zs16_hi);
+        if (gi == 0) {
+            mma16816_zero(d0, a0, a1, a2, a3, av.x, av.y);
+            mma16816_zero(d1, c0, c1, c2, c3, av.z, av.w);
+        } else {
+            mma16816(d0, a0, a1, a2, a3, av.x, av.y);
+            mma16816(d1, c0, c1, c2, c3, av.z, av.w);
+        }
+    }
+    acc[0] = fmaf(d0[0] + d1[0], s_lo, acc[0]);
+    acc[1] = fmaf(d0[1] + d1[1], s_lo, acc[1]);
+    acc[2] = fmaf(d0[2] + d1[2], s_hi, acc[2]);
+    acc[3] = fmaf(d0[3] + d1[3], s_hi, acc[3]);
+}
+
+template <bool SCALE_F32, bool A_F32, bool Y_F32, int GBT, int UNROLL>
+__global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t *stage_base = smem;
+    uint4 *acts = reinterpret_cast<uint4 *>(smem + size_t(STAGES) * p.tile_bytes);
+    float4 *red = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(acts) + size_t(p.rows) * p.g_pad * 64);
+    float *row_pow2 = reinterpret_cast<float *>(red + CONSUMER_WARPS * 32);
+    uint64_t *full = reinterpret_cast<uint64_t *>(row_pow2 + 8);
+    uint64_t *empty = full + STAGES;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            umma::mbar_init(&full[s], 1);
+            umma::mbar_init(&empty[s], CONSUMER_WARPS);
+        }
+        umma::fence_barrier_init();
+    }
+
+    // ---- activations -> shared memory, in the order the fragments are read
+    // unit (row, group, t): k = 32*group + 8*t + {0,4,1,5,2,6,3,7}; odd positions
+    // carry 1/16 because their nibbles are unpacked as 16*(n - z)
+    if constexpr (A_F32) {
+        const float *a = static_cast<const float *>(p.a);
+        __shared__ float warp_max[THREADS / 32];
+        for (int m = 0; m < p.M; m++) {
+            float mx = 0.0f;
+            for (int k = threadIdx.x; k < p.K; k += THREADS)
+                mx = fmaxf(mx, fabsf(a[int64_t(m) * p.K + k]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            if (lane == 0)
+                warp_max[warp] = mx;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                for (int w = 1; w < THREADS / 32; w++)
+                    mx = fmaxf(mx, warp_max[w]);
+                int e = 0;
+                if (mx > 0.0f && mx < 3.0e38f)
+                    frexpf(mx, &e);
+                e = max(-100, min(100, e));
+                row_pow2[m] = ldexpf(1.0f, e);
+            }
+            __syncthreads();
+        }
+        const int units = p.M * p.g_pad * 4;
+        for (int u = threadIdx.x; u < units; u += THREADS) {
+            const int t = u & 3, grp = (u >> 2) % p.g_pad, m = (u >> 2) / p.g_pad;
+            const float inv = 1.0f / row_pow2[m];  // exact power of two
+            float hi[8], lo[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int k = grp * 32 + t * 8 + i;
+                const float v = k < p.K ? a[int64_t(m) * p.K + k] * inv : 0.0f;
+                const float h = __half2float(__float2half_rn(v));
+                const float sc = (i & 1) ? 0.0625f : 1.0f;
+                hi[i] = h * sc;
+                lo[i] = (v - h) * sc;
+            }
+            acts[(size_t(2 * m) * p.g_pad + grp) * 4 + t] =
+                make_uint4(pack_h2(hi[0], hi[4]), pack_h2(hi[1], hi[5]), pack_h2(hi[2], hi[6]), pack_h2(hi[3], hi[7]));
+            acts[(size_t(2 * m + 1) * p.g_pad + grp) * 4 + t] =
+                make_uint4(pack_h2(lo[0], lo[4]), pack_h2(lo[1], lo[5]), pack_h2(lo[2], lo[6]), pack_h2(lo[3], lo[7]));
+        }
+    } else {
+        const __half *a = static_cast<const __half *>(p.a);
+        const int units = p.M * p.g_pad * 4;
+        for (int u = threadIdx.x; u < units; u += THREADS) {
+            const int t = u & 3, grp = (u >> 2) % p.g_pad, m = (u >> 2) / p.g_pad;
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int k = grp * 32 + t * 8 + i;
+                v[i] = k < p.K ? __half2float(a[int64_t(m) * p.K + k]) : 0.0f;
+                if (i & 1)
+                    v[i] *= 0.0625f;
+            }
+            acts[(size_t(m) * p.g_pad + grp) * 4 + t] =
+                make_uint4(pack_h2(v[0], v[4]), pack_h2(v[1], v[5]), pack_h2(v[2], v[6]), pack_h2(v[3], v[7]));
+        }
+    }
+    __syncthreads();
+
+    if (warp == CONSUMER_WARPS) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            int seq = 0;
+            for (int u = blockIdx.x; u < p.ntiles; u += gridDim.x) {
+                for (int kc = 0; kc < p.NKC; kc++, seq++) {
+                    const int s = seq % STAGES;
+                    const uint32_t ph = (seq / STAGES) & 1;
+                    if (!wait_bounded(&empty[s], ph ^ 1)) {
+                        atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
+                        u = p.ntiles;
+                        break;
+                    }
+                    umma::mbar_expect_tx(&full[s], p.tile_bytes);
+                    umma::bulk_load_1d(stage_base + size_t(s) * p.tile_bytes,
+                                       p.packed + (size_t(u) * p.NKC + kc) * p.tile_bytes, p.tile_bytes, &full[s]);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    const int g = lane >> 2, t = lane & 3;
+    const int wp = CONSUMER_WARPS / p.P;  // warps sharing one panel
+    const int panel = warp % p.P;
+    const int b_first = warp / p.P;
+    const int act_row = min(g, p.rows - 1);
+    // 32-bit shared-window addresses; every load below is an explicit ld.shared
+    const uint32_t stage0 = umma::smem_u32(stage_base);
+    const uint32_t act0 = umma::smem_u32(acts) + uint32_t((act_row * p.g_pad) * 4 + t) * 16u;
+    constexpr uint32_t SCALE_PAIR = SCALE_F32 ? 8u : 4u;
+    const uint32_t w_rel = uint32_t((panel * p.KC + b_first) * GBT * 32 + lane) * 8u;
+    const uint32_t s_rel = p.s_off + uint32_t((panel * p.KC + b_first) * 8 + g) * SCALE_PAIR;
+    const uint32_t z_rel = p.z_off + uint32_t((panel * p.KC + b_first) * 8 + g);
+    const uint32_t w_step = uint32_t(wp) * GBT * 256u, s_step = uint32_t(wp) * 8u * SCALE_PAIR, z_step = uint32_t(wp) * 8u;
+    const uint32_t a_step = uint32_t(wp) * GBT * 64u;
+    const int my_blocks = (p.KC - b_first + wp - 1) / wp;  // blocks of a chunk this warp owns
+    bool dead = false;
+    int seq = 0;
+    for (int u = blockIdx.x; u < p.ntiles; u += gridDim.x) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int kc = 0; kc < p.NKC; kc++, seq++) {
+            const int s = seq % STAGES;
+            const uint32_t ph = (seq / STAGES) & 1;
+            if (!dead && !wait_bounded(&full[s], ph)) {
+                dead = true;
+                if (lane == 0)
+                    atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
+            }
+            if (!dead) {
+                const uint32_t tile = stage0 + uint32_t(s) * p.tile_bytes;
+                uint32_t wa = tile + w_rel, sa = tile + s_rel, za = tile + z_rel;
+                uint32_t aa = act0 + uint32_t((kc * p.KC + b_first) * GBT) * 64u;
+                int left = my_blocks;
+                for (; left >= UNROLL; left -= UNROLL) {
+#pragma unroll
+                    for (int j = 0; j < UNROLL; j++)
+                        do_block<SCALE_F32, GBT>(acc, wa + j * w_step, sa + j * s_step, za + j * z_step, aa + j * a_step);
+                    wa += UNROLL * w_step;
+                    sa += UNROLL * s_step;
+                    za += UNROLL * z_step;
+                    aa += UNROLL * a_step;
+                }
+                for (; left > 0; left--) {
+                    do_block<SCALE_F32, GBT>(acc, wa, sa, za, aa);
+                    wa += w_step;
+                    sa += s_step;
+                    za += z_step;
+                    aa += a_step;
+                }
+                __syncwarp();
+                if (lane == 0)
+                    umma::mbar_arrive(&empty[s]);
+            }
+        }
+        // ---- combine the warps that shared a panel, then store
+        red[warp * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
+        if (warp < p.P && !dead) {
+            float4 v = red[warp * 32 + lane];
+            for (int j = 1; j < wp; j++) {
+                const float4 o = red[(warp + j * p.P) * 32 + lane];
+                v.x += o.x;
+                v.y += o.y;
+                v.z += o.z;
+                v.w += o.w;
+            }
+            const int col_lo = (u * p.P + warp) * 16 + g, col_hi = col_lo + 8;
+            if constexpr (A_F32) {
+                // batch columns 2t (high part) and 2t+1 (low part) belong to row t
+                if (t < p.M) {
+                    const float sc = row_pow2[t];
+                    const float y_lo = (v.x + v.y) * sc, y_hi = (v.z + v.w) * sc;
+                    if (col_lo < p.N) {
+                        if constexpr (Y_F32) static_cast<float *>(p.y)[int64_t(t) * p.N + col_lo] = y_lo;
+                        else static_cast<__half *>(p.y)[int64_t(t) * p.N + col_lo] = __float2half_rn(y_lo);
+                    }
+                    if (col_hi < p.N) {
+                        if constexpr (Y_F32) static_cast<float *>(p.y)[int64_t(t) * p.N + col_hi] = y_hi;
+                        else static_cast<__half *>(p.y)[int64_t(t) * p.N + col_hi] = __float2half_rn(y_hi);
+                    }
+                }
+            } else {
+                const float vals[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int m = 2 * t + (i & 1);
+                    const int col = (i < 2) ? col_lo : col_hi;
+                    if (m < p.M && col < p.N) {
+                        if constexpr (Y_F32) static_cast<float *>(p.y)[int64_t(m) * p.N + col] = vals[i];
+                        else static_cast<__half *>(p.y)[int64_t(m) * p.N + col] = __float2half_rn(vals[i]);
+                    }
+                }
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------- prepack
+// One thread per 8-byte weight element, per scale pair, per zero-point byte.
+template <bool SCALE_F32>
+__global__ void __launch_bounds__(256)
+nbits_decode_pack_kernel(const uint32_t *__restrict__ src_w, const void *__restrict__ src_s,
+                         const uint8_t *__restrict__ src_z, uint8_t *__restrict__ dst, int N, int n_blocks,
+                         int P, int KC, int GB, int NKC, int ntiles, uint32_t s_off, uint32_t z_off,
+                         uint32_t tile_bytes)
+{
+    const int64_t per_tile_w = int64_t(P) * KC * GB * 32;  // 8-byte elements
+    const int64_t per_tile_s = int64_t(P) * KC * 8;        // scale pairs
+    const int64_t per_tile = per_tile_w + 2 * per_tile_s;  // + zero-point bytes (one per pair)
+    const int64_t total = per_tile * ntiles * NKC;
+    const int words_per_row = n_blocks * GB * 4;
+    const int zp_row = (n_blocks + 1) / 2;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t tile_id = i / per_tile;
+        int64_t r = i % per_tile;
+        const int nt = int(tile_id / NKC), kc = int(tile_id % NKC);
+        uint8_t *tile = dst + size_t(tile_id) * tile_bytes;
+        if (r < per_tile_w) {
+            const int lane = int(r & 31);
+            int64_t q = r >> 5;
+            const int gi = int(q % GB);
+            q /= GB;
+            const int b = int(q % KC), pnl = int(q / KC);
+            const int g = lane >> 2, t = lane & 3;
+            const int blk = kc * KC + b;
+            const int col_lo = (nt * P + pnl) * 16 + g, col_hi = col_lo + 8;
+            const int word = (blk * GB + gi) * 4 + t;
+            uint2 v = make_uint2(0u, 0u);
+            if (blk < n_blocks) {
+                if (col_lo < N) v.x = src_w[int64_t(col_lo) * words_per_row + word];
+                if (col_hi < N) v.y = src_w[int64_t(col_hi) * words_per_row + word];
+            }
+            reinterpret_cast<uint2 *>(tile)[r] = v;
+        } else {
+            r -= per_tile_w;
+            const bool is_zp = r >= per_tile_s;
+            if (is_zp)
+                r -= per_tile_s;
+            const int g = int(r & 7);
+            const int64_t pb = r >> 3;
+            const int b = int(pb % KC), pnl = int(pb / KC);
+            const int blk = kc * KC + b;
+            const int col_lo = (nt * P + pnl) * 16 + g, col_hi = col_lo + 8;
+            const bool lo_ok = blk < n_blocks && col_lo < N, hi_ok = blk < n_blocks && col_hi < N;
+            if (is_zp) {
+                uint32_t zl = 0, zh = 0;
+                if (lo_ok) zl = src_z ? (src_z[int64_t(col_lo) * zp_row + blk / 2] >> (4 * (blk & 1))) & 15u : 8u;
+                if (hi_ok) zh = src_z ? (src_z[int64_t(col_hi) * zp_row + blk / 2] >> (4 * (blk & 1))) & 15u : 8u;
+                tile[z_off + r] = uint8_t(zl | (zh << 4));
+            } else if constexpr (SCALE_F32) {
+                const float *sp = static_cast<const float *>(src_s);
+                reinterpret_cast<float2 *>(tile + s_off)[r] =
+                    make_float2(lo_ok ? sp[int64_t(col_lo) * n_blocks + blk] : 0.0f,
+                                hi_ok ? sp[int64_t(col_hi) * n_blocks + blk] : 0.0f);
+            } else {
+                const __half *sp = static_cast<const __half *>(src_s);
+                const __half zero = __float2half(0.0f);
+                reinterpret_cast<__half2 *>(tile + s_off)[r] =
+                    __halves2half2(lo_ok ? sp[int64_t(col_lo) * n_blocks + blk] : zero,
+                                   hi_ok ? sp[int64_t(col_hi) * n_blocks + blk] : zero);
+            }
+        }
+    }
+}
+
+size_t decode_smem(const ovk_nbits_weight *w, int rows)
+{
+    const size_t g_pad = size_t(w->dec_nkc) * w->dec_kc * w->dec_gb;
+    return size_t(STAGES) * w->dec_tile_bytes + size_t(rows) * g_pad * 64 + CONSUMER_WARPS * 32 * 16 + 32 + 64 + 128;
+}
+
+template <bool SF, bool AF, bool YF, int GB, int UN>
+int32_t launch_decode_gb(ovk_ctx *ctx, const DecParams &p, size_t smem)
+{
+    OVK_CUDA(ctx, cudaFuncSetAttribute(nbits_decode_kernel<SF, AF, YF, GB, UN>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    const unsigned grid = unsigned(std::min<int>(p.ntiles, ctx->sm_count));
+    nbits_decode_kernel<SF, AF, YF, GB, UN><<<grid, THREADS, smem, ctx->stream>>>(p);
+    OVK_LAUNCHED(ctx, "nbits_decode_mma");
+    return OVK_OK;
+}
+
+template <bool SF, bool AF, bool YF>
+int32_t launch_decode(ovk_ctx *ctx, const DecParams &p, size_t smem)
+{
+    switch (p.GB) {
+    case 1: return launch_decode_gb<SF, AF, YF, 1, 3>(ctx, p, smem);
+    case 2: return launch_decode_gb<SF, AF, YF, 2, 2>(ctx, p, smem);
+    case 4: return launch_decode_gb<SF, AF, YF, 4, 1>(ctx, p, smem);
+    case 8: return launch_decode_gb<SF, AF, YF, 8, 1>(ctx, p, smem);
+    default: return ovk_fail(ctx, OVK_UNSUPPORTED, "MatMulNBits decode: block size %d has no tuned kernel", p.GB * 32);
+    }
+}
+
+}  // namespace
+
+// Builds the decode copy for block sizes 32, 64, 128 and 256 (a 32-wide k group
+// must not straddle two blocks).  Other block sizes keep only the operator layout.
+int32_t ovk_nbits_decode_prepack(ovk_ctx *ctx, ovk_nbits_weight *w)
+{
+    const int64_t bs = w->block_size;
+    if ((bs != 32 && bs != 64 && bs != 128 && bs != 256) || !aligned_to(w->b, 4))
+        return OVK_OK;
+    const int sz = w->scales_dtype == OVK_FLOAT ? 4 : 2;
+    if (!aligned_to(w->scales, sz))
+        return OVK_OK;
+    const int gb = int(w->block_size / 32);
+    const int64_t nb = w->n_blocks;
+    const uint32_t pb_bytes = uint32_t(gb) * 256u + 16u * sz + 8u;  // one panel x one block
+    const int64_t np = ceil_div64(w->n, 16);
+    int P = 1, KC, NKC;
+    if (nb * pb_bytes <= STAGE_MAX) {
+        KC = int(nb);
+        NKC = 1;
+        // as many panels per tile as fit, but not so many that SMs go without a tile
+        while (P < CONSUMER_WARPS && int64_t(2 * P) * nb * pb_bytes <= STAGE_MAX &&
+               ceil_div64(np, 2 * P) >= ctx->sm_count)
+            P *= 2;
+    } else {
+        const int kc_max = int(STAGE_MAX / pb_bytes);
+        if (kc_max < 1)
+            return OVK_OK;
+        NKC = int(ceil_div64(nb, kc_max));
+        KC = int(ceil_div64(nb, NKC));
+    }
+    const int ntiles = int(ceil_div64(np, P));
+    const uint32_t s_off = uint32_t(P) * KC * gb * 256u;
+    const uint32_t z_off = s_off + uint32_t(P) * KC * 16u * sz;
+    const uint32_t tile_bytes = (z_off + uint32_t(P) * KC * 8u + 127u) & ~127u;
+    const size_t bytes = size_t(ntiles) * NKC * tile_bytes;
+    void *dst = nullptr;
+    OVK_CUDA(ctx, cudaMalloc(&dst, bytes));
+    // padding bytes at the end of a tile are never read, but keep the copy deterministic
+    OVK_CUDA(ctx, cudaMemsetAsync(dst, 0, bytes, ctx->stream));
+    const int64_t total = (int64_t(P) * KC * gb * 32 + 2 * int64_t(P) * KC * 8) * ntiles * NKC;
+    const unsigned blocks = unsigned(std::min<int64_t>(ceil_div64(total, 256), int64_t(ctx->sm_count) * 16));
+    if (sz == 4)
+        nbits_decode_pack_kernel<true><<<blocks, 256, 0, ctx->stream>>>(
+            reinterpret_cast<const uint32_t *>(w->b), w->scales, w->zp, static_cast<uint8_t *>(dst), int(w->n),
+            int(nb), P, KC, gb, NKC, ntiles, s_off, z_off, tile_bytes);
+    else
+        nbits_decode_pack_kernel<false><<<blocks, 256, 0, ctx->stream>>>(
+            reinterpret_cast<const uint32_t *>(w->b), w->scales, w->zp, static_cast<uint8_t *>(dst), int(w->n),
+            int(nb), P, KC, gb, NKC, ntiles, s_off, z_off, tile_bytes);
+    ctx->last_kernel = "nbits_decode_pack";
+    ctx->launches++;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        cudaFree(dst);
+        return ovk_fail(ctx, OVK_BACKEND, "nbits_decode_pack: %s", cudaGetErrorString(e));
+    }
+    w->decode = dst;
+    w->decode_bytes = bytes;
+    w->dec_p = P;
+    w->dec_kc = KC;
+    w->dec_gb = gb;
+    w->dec_nkc = NKC;
+    w->dec_ntiles = ntiles;
+    w->dec_s_off = s_off;
+    w->dec_z_off = z_off;
+    w->dec_tile_bytes = tile_bytes;
+    return OVK_OK;
+}
+
+// Up to 8 fp16 rows (4 f32 rows, which take two batch columns each) per
+// launch; more rows than that belong to the prefill kernel.
+bool ovk_nbits_decode_applies(const ovk_nbits_weight *w, int64_t m, int32_t a_dtype, int32_t y_dtype)
+{
+    (void)y_dtype;
+    if (!w->decode || m > 8)
+        return false;
+    // at least one row of activations must fit beside the weight stages
+    const int rows1 = a_dtype == OVK_FLOAT ? 2 : 1;
+    const size_t g_pad = size_t(w->dec_nkc) * w->dec_kc * w->dec_gb;
+    return size_t(rows1) * g_pad * 64 <= ACT_MAX;
+}
+
+int32_t ovk_nbits_decode(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype, int64_t m,
+                         void *y, int32_t y_dtype)
+{
+    const bool af = a_dtype == OVK_FLOAT, yf = y_dtype == OVK_FLOAT, sf = w->scales_dtype == OVK_FLOAT;
+    OVK_REQUIRE(ctx, aligned_to(a, af ? 4 : 2) && aligned_to(y, yf ? 4 : 2), "MatMulNBits: A or Y is misaligned");
+    const size_t g_pad = size_t(w->dec_nkc) * w->dec_kc * w->dec_gb;
+    const int per_row = af ? 2 : 1;
+    int rows_max = int(std::min<size_t>(8, ACT_MAX / (g_pad * 64))) / per_row;  // rows of A per launch
+    rows_max = std::max(rows_max, 1);
+    const size_t a_row = size_t(w->k) * (af ? 4 : 2), y_row = size_t(w->n) * (yf ? 4 : 2);
+    for (int64_t m0 = 0; m0 < m; m0 += rows_max) {
+        DecParams p = {};
+        p.packed = static_cast<const uint8_t *>(w->decode);
+        p.a = static_cast<const uint8_t *>(a) + size_t(m0) * a_row;
+        p.y = static_cast<uint8_t *>(y) + size_t(m0) * y_row;
+        p.M = int(std::min<int64_t>(rows_max, m - m0));
+        p.K = int(w->k);
+        p.N = int(w->n);
+        p.P = w->dec_p;
+        p.KC = w->dec_kc;
+        p.GB = w->dec_gb;
+        p.NKC = w->dec_nkc;
+        p.ntiles = w->dec_ntiles;
+        p.s_off = w->dec_s_off;
+        p.z_off = w->dec_z_off;
+        p.tile_bytes = w->dec_tile_bytes;
+        p.g_pad = int(g_pad);
+        p.rows = p.M * per_row;
+        p.status = ctx->dev_status;
+        const size_t smem = decode_smem(w, p.rows);
+        OVK_REQUIRE(ctx, smem <= ctx->smem_optin, "MatMulNBits decode: %zu bytes of shared memory needed", smem);
+        int32_t rc;
+#define GO(SF, AF, YF) rc = launch_decode<SF, AF, YF>(ctx, p, smem)
+        if (sf && af && yf) GO(true, true, true);
+        else if (sf && af && !yf) GO(true, true, false);
+        else if (sf && !af && yf) GO(true, false, true);
+        else if (sf && !af && !yf) GO(true, false, false);
+        else if (!sf && af && yf) GO(false, true, true);
+        else if (!sf && af && !yf) GO(false, true, false);
+        else if (!sf && !af && yf) GO(false, false, true);
+        else GO(false, false, false);
+#undef GO
+        if (rc != OVK_OK)
+            return rc;
+    }
+    return OVK_OK;
+}

@@ -89,11 +89,12 @@ struct ovk_nbits_weight {
     const uint8_t *zp = nullptr;      // [N, ceil(n_blocks/2)] or null (implicit 8)
     int32_t scales_dtype = OVK_FLOAT;
     int64_t n = 0, k = 0, block_size = 0, n_blocks = 0;
-    // decode copy (built by prepack when the shape allows it)
+    // decode copy (built by prepack when block_size is a multiple of 32): tiles of
+    // dec_p 16-column panels x dec_kc quantization blocks, each tile contiguous
     void *decode = nullptr;
     size_t decode_bytes = 0;
-    int64_t k_groups = 0;   // ceil(K / 32), padded
-    int64_t panels = 0;     // ceil(N / 16)
+    int dec_p = 0, dec_kc = 0, dec_gb = 0, dec_nkc = 0, dec_ntiles = 0;
+    uint32_t dec_s_off = 0, dec_z_off = 0, dec_tile_bytes = 0;
 };
 
 struct ovk_mmi_weight {
