@@ -7,7 +7,8 @@
 int32_t ovk_nbits_rows(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype,
                        int64_t m, void *y, int32_t y_dtype);
 int32_t ovk_nbits_decode_prepack(ovk_ctx *ctx, ovk_nbits_weight *w);
-bool ovk_nbits_decode_applies(const ovk_nbits_weight *w, int64_t m, int32_t a_dtype, int32_t y_dtype);
+bool ovk_nbits_decode_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int64_t m, int32_t a_dtype,
+                              int32_t y_dtype);
 int32_t ovk_nbits_decode(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype,
                          int64_t m, void *y, int32_t y_dtype);
 bool ovk_nbits_gemm_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int64_t m, int32_t a_dtype,
@@ -78,7 +79,7 @@ int32_t ovk_matmul_nbits(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
         return OVK_OK;
     OVK_REQUIRE(ctx, a && y, "MatMulNBits: A or Y is null");
     OVK_CUDA(ctx, cudaSetDevice(ctx->device));
-    if (ovk_nbits_decode_applies(w, m, a_dtype, y_dtype))
+    if (ovk_nbits_decode_applies(ctx, w, m, a_dtype, y_dtype))
         return ovk_nbits_decode(ctx, w, a, a_dtype, m, y, y_dtype);
     if (ovk_nbits_gemm_applies(ctx, w, m, a_dtype, y_dtype, a, y))
         return ovk_nbits_gemm(ctx, w, a, a_dtype, m, y, y_dtype);

@@ -14,8 +14,8 @@
 //    order the math unit wants them.  Bytes per weight are unchanged (4 bits
 //    + scale + 4-bit zero point).
 //  * a persistent CTA per SM streams its tiles with cp.async.bulk into a
-//    3-stage shared-memory ring (one producer thread, mbarrier completion), so
-//    ~130 KB per SM are in flight without spending registers on it;
+//    4-stage shared-memory ring (a producer warp, mbarrier completion), so
+//    ~170 KB per SM are in flight without spending registers on it;
 //  * eight consumer warps unpack with two logic ops per pair of nibbles
 //    (the 0x6400 "1024 + n" fp16 trick; (n - z) is exact) and feed
 //    mma.sync.m16n8k16: 16 weight columns x 16 k x up to 8 activation rows per
@@ -33,8 +33,9 @@ namespace {
 
 constexpr int CONSUMER_WARPS = 16;
 constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
-constexpr int STAGES = 3;
-constexpr uint32_t STAGE_MAX = 48 * 1024;
+constexpr int STAGES = 4;
+constexpr int SLICES = 8;  // bulk copies per tile
+constexpr uint32_t STAGE_MAX = 44 * 1024;
 constexpr size_t ACT_MAX = 64 * 1024;
 constexpr long long WAIT_CYCLES = 2000000000ll;
 
@@ -120,10 +121,25 @@ __device__ __forceinline__ void mma16816_zero(float (&d)[4], uint32_t a0, uint32
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
-// One quantization block of one 16-column panel: GB k32-groups, two chains of
-// MMAs (even / odd halves of each weight word), then the block's scale in f32.
+// (a & b) | c with all three operands in registers: one LOP3 (two immediates would need two)
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c)
+{
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+struct UnpackConsts {
+    uint32_t lo_mask, hi_mask, magic;  // 0x000F000F, 0x00F000F0, 0x64006400 held in registers
+};
+
+// One quantization block of one 16-column panel: GB k32-groups, 2*GB chained
+// MMAs, then the block's scale in f32.  Addresses are 32-bit shared-window
+// offsets; consecutive blocks of a warp are contiguous, so the offsets fold
+// into the load instructions.
 template <bool SCALE_F32, int GB>
-__device__ __forceinline__ void do_block(float (&acc)[4], uint32_t wa, uint32_t sa, uint32_t za, uint32_t aa)
+__device__ __forceinline__ void do_block(float (&acc)[4], const UnpackConsts &uc, uint32_t wa, uint32_t sa,
+                                         uint32_t za, uint32_t aa)
 {
     float s_lo, s_hi;  // scales of columns g and g+8
     if constexpr (SCALE_F32) {
@@ -138,34 +154,32 @@ __device__ __forceinline__ void do_block(float (&acc)[4], uint32_t wa, uint32_t 
     }
     const uint32_t zb = lds8(za);
     const uint32_t z_lo = zb & 15u, z_hi = zb >> 4;
-    const uint32_t zs_lo = z_lo * 0x00010001u + 0x64006400u, zs16_lo = z_lo * 0x00100010u + 0x64006400u;
-    const uint32_t zs_hi = z_hi * 0x00010001u + 0x64006400u, zs16_hi = z_hi * 0x00100010u + 0x64006400u;
-    float d0[4], d1[4];
+    const uint32_t zs_lo = z_lo * 0x00010001u + uc.magic, zs16_lo = z_lo * 0x00100010u + uc.magic;
+    const uint32_t zs_hi = z_hi * 0x00010001u + uc.magic, zs16_hi = z_hi * 0x00100010u + uc.magic;
+    float d[4];
 #pragma unroll
     for (int gi = 0; gi < GB; gi++) {
         const uint2 wv = lds64(wa + gi * 256);
         const uint4 av = lds128(aa + gi * 64);
         const uint32_t x8 = wv.x >> 8, y8 = wv.y >> 8;
-        const uint32_t a0 = h2_sub((wv.x & 0x000F000Fu) | 0x64006400u, zs_lo);
-        const uint32_t a1 = h2_sub((wv.y & 0x000F000Fu) | 0x64006400u, zs_hi);
-        const uint32_t a2 = h2_sub((wv.x & 0x00F000F0u) | 0x64006400u, zs16_lo);
-        const uint32_t a3 = h2_sub((wv.y & 0x00F000F0u) | 0x64006400u, zs16_hi);
-        const uint32_t c0 = h2_sub((x8 & 0x000F000Fu) | 0x64006400u, zs_lo);
-        const uint32_t c1 = h2_sub((y8 & 0x000F000Fu) | 0x64006400u, zs_hi);
-        const uint32_t c2 = h2_sub((x8 & 0x00F000F0u) | 0x64006400u, zs16_lo);
-        const uint32_t c3 = h2_sub((y8 & 0x00F000F0u) | 0x64006400u, zs16_hi);
-        if (gi == 0) {
-            mma16816_zero(d0, a0, a1, a2, a3, av.x, av.y);
-            mma16816_zero(d1, c0, c1, c2, c3, av.z, av.w);
-        } else {
-            mma16816(d0, a0, a1, a2, a3, av.x, av.y);
-            mma16816(d1, c0, c1, c2, c3, av.z, av.w);
-        }
+        const uint32_t a0 = h2_sub(and_or(wv.x, uc.lo_mask, uc.magic), zs_lo);
+        const uint32_t a1 = h2_sub(and_or(wv.y, uc.lo_mask, uc.magic), zs_hi);
+        const uint32_t a2 = h2_sub(and_or(wv.x, uc.hi_mask, uc.magic), zs16_lo);
+        const uint32_t a3 = h2_sub(and_or(wv.y, uc.hi_mask, uc.magic), zs16_hi);
+        const uint32_t c0 = h2_sub(and_or(x8, uc.lo_mask, uc.magic), zs_lo);
+        const uint32_t c1 = h2_sub(and_or(y8, uc.lo_mask, uc.magic), zs_hi);
+        const uint32_t c2 = h2_sub(and_or(x8, uc.hi_mask, uc.magic), zs16_lo);
+        const uint32_t c3 = h2_sub(and_or(y8, uc.hi_mask, uc.magic), zs16_hi);
+        if (gi == 0)
+            mma16816_zero(d, a0, a1, a2, a3, av.x, av.y);
+        else
+            mma16816(d, a0, a1, a2, a3, av.x, av.y);
+        mma16816(d, c0, c1, c2, c3, av.z, av.w);
     }
-    acc[0] = fmaf(d0[0] + d1[0], s_lo, acc[0]);
-    acc[1] = fmaf(d0[1] + d1[1], s_lo, acc[1]);
-    acc[2] = fmaf(d0[2] + d1[2], s_hi, acc[2]);
-    acc[3] = fmaf(d0[3] + d1[3], s_hi, acc[3]);
+    acc[0] = fmaf(d[0], s_lo, acc[0]);
+    acc[1] = fmaf(d[1], s_lo, acc[1]);
+    acc[2] = fmaf(d[2], s_hi, acc[2]);
+    acc[3] = fmaf(d[3], s_hi, acc[3]);
 }
 
 template <bool SCALE_F32, bool A_F32, bool Y_F32, int GBT, int UNROLL>
@@ -256,21 +270,33 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
 
     if (warp == CONSUMER_WARPS) {
         // ------------------------------------------------------------ producer
-        if (lane == 0) {
-            int seq = 0;
-            for (int u = blockIdx.x; u < p.ntiles; u += gridDim.x) {
-                for (int kc = 0; kc < p.NKC; kc++, seq++) {
-                    const int s = seq % STAGES;
-                    const uint32_t ph = (seq / STAGES) & 1;
-                    if (!wait_bounded(&empty[s], ph ^ 1)) {
+        // the tile is fetched as SLICES bulk copies issued by as many lanes, all
+        // completing on the stage's barrier: more requests in flight per SM
+        const uint32_t slice = ((p.tile_bytes / SLICES) + 15u) & ~15u;
+        const uint32_t my_off = min(uint32_t(lane) * slice, p.tile_bytes);
+        const uint32_t my_len = lane < SLICES ? min(slice, p.tile_bytes - my_off) : 0u;
+        int seq = 0;
+        bool alive = true;
+        for (int u = blockIdx.x; u < p.ntiles && alive; u += gridDim.x) {
+            for (int kc = 0; kc < p.NKC; kc++, seq++) {
+                const int s = seq % STAGES;
+                const uint32_t ph = (seq / STAGES) & 1;
+                bool ok = true;
+                if (lane == 0) {
+                    ok = wait_bounded(&empty[s], ph ^ 1);
+                    if (ok)
+                        umma::mbar_expect_tx(&full[s], p.tile_bytes);
+                    else
                         atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
-                        u = p.ntiles;
-                        break;
-                    }
-                    umma::mbar_expect_tx(&full[s], p.tile_bytes);
-                    umma::bulk_load_1d(stage_base + size_t(s) * p.tile_bytes,
-                                       p.packed + (size_t(u) * p.NKC + kc) * p.tile_bytes, p.tile_bytes, &full[s]);
                 }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    alive = false;
+                    break;
+                }
+                if (my_len)
+                    umma::bulk_load_1d(stage_base + size_t(s) * p.tile_bytes + my_off,
+                                       p.packed + (size_t(u) * p.NKC + kc) * p.tile_bytes + my_off, my_len, &full[s]);
             }
         }
         return;
@@ -280,18 +306,23 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
     const int g = lane >> 2, t = lane & 3;
     const int wp = CONSUMER_WARPS / p.P;  // warps sharing one panel
     const int panel = warp % p.P;
-    const int b_first = warp / p.P;
+    // each warp owns a contiguous run of the chunk's blocks
+    const int per_warp = (p.KC + wp - 1) / wp;
+    const int b_first = min((warp / p.P) * per_warp, p.KC);
+    const int my_blocks = min(per_warp, p.KC - b_first);
     const int act_row = min(g, p.rows - 1);
     // 32-bit shared-window addresses; every load below is an explicit ld.shared
     const uint32_t stage0 = umma::smem_u32(stage_base);
     const uint32_t act0 = umma::smem_u32(acts) + uint32_t((act_row * p.g_pad) * 4 + t) * 16u;
     constexpr uint32_t SCALE_PAIR = SCALE_F32 ? 8u : 4u;
+    constexpr uint32_t W_STEP = GBT * 256u, S_STEP = 8u * SCALE_PAIR, Z_STEP = 8u, A_STEP = GBT * 64u;
     const uint32_t w_rel = uint32_t((panel * p.KC + b_first) * GBT * 32 + lane) * 8u;
     const uint32_t s_rel = p.s_off + uint32_t((panel * p.KC + b_first) * 8 + g) * SCALE_PAIR;
     const uint32_t z_rel = p.z_off + uint32_t((panel * p.KC + b_first) * 8 + g);
-    const uint32_t w_step = uint32_t(wp) * GBT * 256u, s_step = uint32_t(wp) * 8u * SCALE_PAIR, z_step = uint32_t(wp) * 8u;
-    const uint32_t a_step = uint32_t(wp) * GBT * 64u;
-    const int my_blocks = (p.KC - b_first + wp - 1) / wp;  // blocks of a chunk this warp owns
+    UnpackConsts uc;
+    // opaque to the optimiser, so the three constants stay in registers
+    asm volatile("mov.u32 %0, 0x000F000F;\n\tmov.u32 %1, 0x00F000F0;\n\tmov.u32 %2, 0x64006400;"
+                 : "=r"(uc.lo_mask), "=r"(uc.hi_mask), "=r"(uc.magic));
     bool dead = false;
     int seq = 0;
     for (int u = blockIdx.x; u < p.ntiles; u += gridDim.x) {
@@ -312,18 +343,19 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
                 for (; left >= UNROLL; left -= UNROLL) {
 #pragma unroll
                     for (int j = 0; j < UNROLL; j++)
-                        do_block<SCALE_F32, GBT>(acc, wa + j * w_step, sa + j * s_step, za + j * z_step, aa + j * a_step);
-                    wa += UNROLL * w_step;
-                    sa += UNROLL * s_step;
-                    za += UNROLL * z_step;
-                    aa += UNROLL * a_step;
+                        do_block<SCALE_F32, GBT>(acc, uc, wa + j * W_STEP, sa + j * S_STEP, za + j * Z_STEP,
+                                                 aa + j * A_STEP);
+                    wa += UNROLL * W_STEP;
+                    sa += UNROLL * S_STEP;
+                    za += UNROLL * Z_STEP;
+                    aa += UNROLL * A_STEP;
                 }
                 for (; left > 0; left--) {
-                    do_block<SCALE_F32, GBT>(acc, wa, sa, za, aa);
-                    wa += w_step;
-                    sa += s_step;
-                    za += z_step;
-                    aa += a_step;
+                    do_block<SCALE_F32, GBT>(acc, uc, wa, sa, za, aa);
+                    wa += W_STEP;
+                    sa += S_STEP;
+                    za += Z_STEP;
+                    aa += A_STEP;
                 }
                 __syncwarp();
                 if (lane == 0)
@@ -541,17 +573,25 @@ int32_t ovk_nbits_decode_prepack(ovk_ctx *ctx, ovk_nbits_weight *w)
     return OVK_OK;
 }
 
-// Up to 8 fp16 rows (4 f32 rows, which take two batch columns each) per
-// launch; more rows than that belong to the prefill kernel.
-bool ovk_nbits_decode_applies(const ovk_nbits_weight *w, int64_t m, int32_t a_dtype, int32_t y_dtype)
+// Rows of A one launch can take: what fits in shared memory beside the weight
+// ring, at most 8 batch columns (an f32 row takes two).
+static int decode_rows_per_launch(const ovk_ctx *ctx, const ovk_nbits_weight *w, int32_t a_dtype)
+{
+    const size_t g_pad = size_t(w->dec_nkc) * w->dec_kc * w->dec_gb;
+    const size_t fixed = decode_smem(w, 0);
+    if (fixed >= ctx->smem_optin)
+        return 0;
+    const size_t cols = std::min<size_t>(8, std::min(ACT_MAX, ctx->smem_optin - fixed) / (g_pad * 64));
+    return int(cols) / (a_dtype == OVK_FLOAT ? 2 : 1);
+}
+
+// Up to 8 fp16 rows (4 f32 rows) per launch; more rows than that belong to
+// the prefill kernel.
+bool ovk_nbits_decode_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int64_t m, int32_t a_dtype,
+                              int32_t y_dtype)
 {
     (void)y_dtype;
-    if (!w->decode || m > 8)
-        return false;
-    // at least one row of activations must fit beside the weight stages
-    const int rows1 = a_dtype == OVK_FLOAT ? 2 : 1;
-    const size_t g_pad = size_t(w->dec_nkc) * w->dec_kc * w->dec_gb;
-    return size_t(rows1) * g_pad * 64 <= ACT_MAX;
+    return w->decode && m <= 8 && decode_rows_per_launch(ctx, w, a_dtype) >= 1;
 }
 
 int32_t ovk_nbits_decode(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype, int64_t m,
@@ -561,8 +601,7 @@ int32_t ovk_nbits_decode(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
     OVK_REQUIRE(ctx, aligned_to(a, af ? 4 : 2) && aligned_to(y, yf ? 4 : 2), "MatMulNBits: A or Y is misaligned");
     const size_t g_pad = size_t(w->dec_nkc) * w->dec_kc * w->dec_gb;
     const int per_row = af ? 2 : 1;
-    int rows_max = int(std::min<size_t>(8, ACT_MAX / (g_pad * 64))) / per_row;  // rows of A per launch
-    rows_max = std::max(rows_max, 1);
+    const int rows_max = std::max(1, decode_rows_per_launch(ctx, w, a_dtype));  // rows of A per launch
     const size_t a_row = size_t(w->k) * (af ? 4 : 2), y_row = size_t(w->n) * (yf ? 4 : 2);
     for (int64_t m0 = 0; m0 < m; m0 += rows_max) {
         DecParams p = {};
