@@ -362,18 +362,23 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
                     umma::mbar_arrive(&empty[s]);
             }
         }
-        // ---- combine the warps that shared a panel, then store
-        red[warp * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
-        if (warp < p.P && !dead) {
-            float4 v = red[warp * 32 + lane];
-            for (int j = 1; j < wp; j++) {
-                const float4 o = red[(warp + j * p.P) * 32 + lane];
-                v.x += o.x;
-                v.y += o.y;
-                v.z += o.z;
-                v.w += o.w;
+        // ---- combine the warps that shared a panel (none when a warp owns a
+        // whole panel: then nothing is exchanged and no barrier is taken), then store
+        float4 v = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        if (wp > 1) {
+            red[warp * 32 + lane] = v;
+            asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
+            if (warp < p.P) {
+                for (int j = 1; j < wp; j++) {
+                    const float4 o = red[(warp + j * p.P) * 32 + lane];
+                    v.x += o.x;
+                    v.y += o.y;
+                    v.z += o.z;
+                    v.w += o.w;
+                }
             }
+        }
+        if (warp < p.P && !dead) {
             const int col_lo = (u * p.P + warp) * 16 + g, col_hi = col_lo + 8;
             if constexpr (A_F32) {
                 // batch columns 2t (high part) and 2t+1 (low part) belong to row t
@@ -402,7 +407,8 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
                 }
             }
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
+        if (wp > 1)
+            asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
     }
 }
 
@@ -520,11 +526,18 @@ int32_t ovk_nbits_decode_prepack(ovk_ctx *ctx, ovk_nbits_weight *w)
     const uint32_t pb_bytes = uint32_t(gb) * 256u + 16u * sz + 8u;  // one panel x one block
     const int64_t np = ceil_div64(w->n, 16);
     int P = 1, KC, NKC;
-    if (nb * pb_bytes <= STAGE_MAX) {
+    if (ceil_div64(np, CONSUMER_WARPS) * 2 >= ctx->sm_count && uint32_t(CONSUMER_WARPS) * pb_bytes <= STAGE_MAX) {
+        // wide weights: one panel per warp, K cut into chunks that fit a stage;
+        // a warp keeps its columns for the whole of K, so warps never exchange anything
+        P = CONSUMER_WARPS;
+        const int kc_max = int(STAGE_MAX / (uint32_t(P) * pb_bytes));
+        NKC = int(ceil_div64(nb, kc_max));
+        KC = int(ceil_div64(nb, NKC));
+    } else if (nb * pb_bytes <= STAGE_MAX) {
         KC = int(nb);
         NKC = 1;
         // as many panels per tile as fit, but not so many that SMs go without a tile
-        while (P < CONSUMER_WARPS && int64_t(2 * P) * nb * pb_bytes <= STAGE_MAX &&
+        while (2 * P < CONSUMER_WARPS && int64_t(2 * P) * nb * pb_bytes <= STAGE_MAX &&
                ceil_div64(np, 2 * P) >= ctx->sm_count)
             P *= 2;
     } else {
