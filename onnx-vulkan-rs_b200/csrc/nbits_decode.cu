@@ -16,11 +16,13 @@
 //  * a persistent CTA per SM streams its tiles with cp.async.bulk into a
 //    4-stage shared-memory ring (a producer warp, mbarrier completion), so
 //    ~170 KB per SM are in flight without spending registers on it;
-//  * eight consumer warps unpack with two logic ops per pair of nibbles
-//    (the 0x6400 "1024 + n" fp16 trick; (n - z) is exact) and feed
+//  * sixteen consumer warps unpack with ONE logic op per pair of nibbles (a
+//    nibble at bits 4-7 OR-ed with 0x5400 is the fp16 number 64 + n) and feed
 //    mma.sync.m16n8k16: 16 weight columns x 16 k x up to 8 activation rows per
-//    instruction, products exact, f32 accumulation.  A block's partial sum is
-//    then scaled and added in f32 on the CUDA cores, as the reference does.
+//    instruction, products exact, f32 accumulation; the bias and the zero
+//    point leave through one more MMA per block (see do_block).  A block's
+//    partial sum is then scaled and added in f32 on the CUDA cores, as the
+//    reference does.
 //  * f32 activations are split into an fp16 high and low part (two of the
 //    eight batch columns), after an exact power-of-two row normalisation, so
 //    the result keeps ~22 bits of the activation.
@@ -113,12 +115,12 @@ __device__ __forceinline__ uint32_t lds8(uint32_t addr)
 
 // d = A x B (C = 0)
 __device__ __forceinline__ void mma16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                              uint32_t b0, uint32_t b1)
+                                              uint32_t b0, uint32_t b1, uint32_t zero)
 {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(__uint_as_float(zero)));
 }
 
 // (a & b) | c with all three operands in registers: one LOP3 (two immediates would need two)
@@ -130,16 +132,23 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c)
 }
 
 struct UnpackConsts {
-    uint32_t lo_mask, hi_mask, magic;  // 0x000F000F, 0x00F000F0, 0x64006400 held in registers
+    uint32_t mask, magic, zero;  // 0x00F000F0, 0x54005400 and 0, held in registers
 };
 
-// One quantization block of one 16-column panel: GB k32-groups, 2*GB chained
-// MMAs, then the block's scale in f32.  Addresses are 32-bit shared-window
-// offsets; consecutive blocks of a warp are contiguous, so the offsets fold
-// into the load instructions.
+// One quantization block of one 16-column panel.
+//
+// A nibble n sitting at bits 4-7 (20-23) of a word, OR-ed with 0x5400, IS the
+// fp16 number 64 + n: no subtraction is needed to unpack it.  The block's sum
+//     sum_k a_k (n_k - z)  =  sum_k a_k (64 + n_k)  -  (64 + z) * sum_k a_k
+// is formed entirely on the tensor cores: 2*GB MMAs over the nibbles plus ONE
+// more whose weight operand is (64 + z) (again just bits: 0x5400 | z << 4) and
+// whose activation operand is minus the block's activation sum, split into
+// three fp16 parts so that it is exact to ~2^-33.  All products are exact and
+// the f32 accumulator only ever holds values of a few hundred, so the result
+// differs from the exact sum by ~1e-6 relative.  Then the block's scale, in f32.
 template <bool SCALE_F32, int GB>
 __device__ __forceinline__ void do_block(float (&acc)[4], const UnpackConsts &uc, uint32_t wa, uint32_t sa,
-                                         uint32_t za, uint32_t aa)
+                                         uint32_t za, uint32_t aa, uint32_t ca)
 {
     float s_lo, s_hi;  // scales of columns g and g+8
     if constexpr (SCALE_F32) {
@@ -152,29 +161,19 @@ __device__ __forceinline__ void do_block(float (&acc)[4], const UnpackConsts &uc
         s_lo = __low2float(h);
         s_hi = __high2float(h);
     }
-    const uint32_t zb = lds8(za);
-    const uint32_t z_lo = zb & 15u, z_hi = zb >> 4;
-    const uint32_t zs_lo = z_lo * 0x00010001u + uc.magic, zs16_lo = z_lo * 0x00100010u + uc.magic;
-    const uint32_t zs_hi = z_hi * 0x00010001u + uc.magic, zs16_hi = z_hi * 0x00100010u + uc.magic;
+    const uint32_t zb = lds8(za);    // z(col g) | z(col g+8) << 4
+    const uint32_t corr = lds32(ca);  // half2(-part_t of the block's activation sum, 0)
     float d[4];
+    mma16816_zero(d, and_or(zb << 4, uc.mask, uc.magic), and_or(zb, uc.mask, uc.magic), uc.zero, uc.zero, corr,
+                  uc.zero, uc.zero);
 #pragma unroll
     for (int gi = 0; gi < GB; gi++) {
         const uint2 wv = lds64(wa + gi * 256);
         const uint4 av = lds128(aa + gi * 64);
-        const uint32_t x8 = wv.x >> 8, y8 = wv.y >> 8;
-        const uint32_t a0 = h2_sub(and_or(wv.x, uc.lo_mask, uc.magic), zs_lo);
-        const uint32_t a1 = h2_sub(and_or(wv.y, uc.lo_mask, uc.magic), zs_hi);
-        const uint32_t a2 = h2_sub(and_or(wv.x, uc.hi_mask, uc.magic), zs16_lo);
-        const uint32_t a3 = h2_sub(and_or(wv.y, uc.hi_mask, uc.magic), zs16_hi);
-        const uint32_t c0 = h2_sub(and_or(x8, uc.lo_mask, uc.magic), zs_lo);
-        const uint32_t c1 = h2_sub(and_or(y8, uc.lo_mask, uc.magic), zs_hi);
-        const uint32_t c2 = h2_sub(and_or(x8, uc.hi_mask, uc.magic), zs16_lo);
-        const uint32_t c3 = h2_sub(and_or(y8, uc.hi_mask, uc.magic), zs16_hi);
-        if (gi == 0)
-            mma16816_zero(d, a0, a1, a2, a3, av.x, av.y);
-        else
-            mma16816(d, a0, a1, a2, a3, av.x, av.y);
-        mma16816(d, c0, c1, c2, c3, av.z, av.w);
+        mma16816(d, and_or(wv.x << 4, uc.mask, uc.magic), and_or(wv.y << 4, uc.mask, uc.magic),
+                 and_or(wv.x, uc.mask, uc.magic), and_or(wv.y, uc.mask, uc.magic), av.x, av.y);
+        mma16816(d, and_or(wv.x >> 4, uc.mask, uc.magic), and_or(wv.y >> 4, uc.mask, uc.magic),
+                 and_or(wv.x >> 8, uc.mask, uc.magic), and_or(wv.y >> 8, uc.mask, uc.magic), av.z, av.w);
     }
     acc[0] = fmaf(d[0], s_lo, acc[0]);
     acc[1] = fmaf(d[1], s_lo, acc[1]);
@@ -188,7 +187,9 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t *stage_base = smem;
     uint4 *acts = reinterpret_cast<uint4 *>(smem + size_t(STAGES) * p.tile_bytes);
-    float4 *red = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(acts) + size_t(p.rows) * p.g_pad * 64);
+    // per (batch column, block): half2(-part_t, 0) for t = 0..3, the three fp16 parts of the block's activation sum
+    uint32_t *corr = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(acts) + size_t(p.rows) * p.g_pad * 64);
+    float4 *red = reinterpret_cast<float4 *>(corr + size_t(p.rows) * (p.g_pad / GBT) * 4);
     float *row_pow2 = reinterpret_cast<float *>(red + CONSUMER_WARPS * 32);
     uint64_t *full = reinterpret_cast<uint64_t *>(row_pow2 + 8);
     uint64_t *empty = full + STAGES;
@@ -204,8 +205,7 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
     }
 
     // ---- activations -> shared memory, in the order the fragments are read
-    // unit (row, group, t): k = 32*group + 8*t + {0,4,1,5,2,6,3,7}; odd positions
-    // carry 1/16 because their nibbles are unpacked as 16*(n - z)
+    // unit (row, group, t): k = 32*group + 8*t + {0,4,1,5,2,6,3,7}
     if constexpr (A_F32) {
         const float *a = static_cast<const float *>(p.a);
         __shared__ float warp_max[THREADS / 32];
@@ -240,9 +240,8 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
                 const int k = grp * 32 + t * 8 + i;
                 const float v = k < p.K ? a[int64_t(m) * p.K + k] * inv : 0.0f;
                 const float h = __half2float(__float2half_rn(v));
-                const float sc = (i & 1) ? 0.0625f : 1.0f;
-                hi[i] = h * sc;
-                lo[i] = (v - h) * sc;
+                hi[i] = h;
+                lo[i] = v - h;
             }
             acts[(size_t(2 * m) * p.g_pad + grp) * 4 + t] =
                 make_uint4(pack_h2(hi[0], hi[4]), pack_h2(hi[1], hi[5]), pack_h2(hi[2], hi[6]), pack_h2(hi[3], hi[7]));
@@ -259,11 +258,37 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
             for (int i = 0; i < 8; i++) {
                 const int k = grp * 32 + t * 8 + i;
                 v[i] = k < p.K ? __half2float(a[int64_t(m) * p.K + k]) : 0.0f;
-                if (i & 1)
-                    v[i] *= 0.0625f;
             }
             acts[(size_t(m) * p.g_pad + grp) * 4 + t] =
                 make_uint4(pack_h2(v[0], v[4]), pack_h2(v[1], v[5]), pack_h2(v[2], v[6]), pack_h2(v[3], v[7]));
+        }
+    }
+    __syncthreads();
+    {
+        // block sums of the staged (fp16) activations, negated and split in three
+        const int nblk = p.g_pad / GBT;
+        const __half *ah = reinterpret_cast<const __half *>(acts);
+        for (int u = warp; u < p.rows * nblk; u += THREADS / 32) {
+            const int row = u / nblk, blk = u % nblk;
+            const __half *src = ah + (size_t(row) * p.g_pad + size_t(blk) * GBT) * 32;
+            double sum = 0.0;  // exact: fp16 terms span fewer than 53 bits
+#pragma unroll
+            for (int i = 0; i < GBT; i++)
+                sum += double(__half2float(src[i * 32 + lane]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) {
+                const __half h0 = __double2half(sum);
+                const double r1 = sum - double(__half2float(h0));
+                const __half h1 = __double2half(r1);
+                const __half h2 = __double2half(r1 - double(__half2float(h1)));
+                uint32_t *dst = corr + size_t(u) * 4;
+                dst[0] = uint32_t(__half_as_ushort(__hneg(h0)));
+                dst[1] = uint32_t(__half_as_ushort(__hneg(h1)));
+                dst[2] = uint32_t(__half_as_ushort(__hneg(h2)));
+                dst[3] = 0u;
+            }
         }
     }
     __syncthreads();
@@ -320,9 +345,12 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
     const uint32_t s_rel = p.s_off + uint32_t((panel * p.KC + b_first) * 8 + g) * SCALE_PAIR;
     const uint32_t z_rel = p.z_off + uint32_t((panel * p.KC + b_first) * 8 + g);
     UnpackConsts uc;
-    // opaque to the optimiser, so the three constants stay in registers
-    asm volatile("mov.u32 %0, 0x000F000F;\n\tmov.u32 %1, 0x00F000F0;\n\tmov.u32 %2, 0x64006400;"
-                 : "=r"(uc.lo_mask), "=r"(uc.hi_mask), "=r"(uc.magic));
+    // opaque to the optimiser, so the two constants stay in registers
+    asm volatile("mov.u32 %0, 0x00F000F0;\n\tmov.u32 %1, 0x54005400;\n\tmov.u32 %2, 0;"
+                 : "=r"(uc.mask), "=r"(uc.magic), "=r"(uc.zero));
+    const uint32_t corr0 = umma::smem_u32(corr) + uint32_t((act_row * (p.g_pad / GBT)) * 4 + t) * 4u;
+    constexpr uint32_t C_STEP = 16u;
+    constexpr int BIG = GBT == 1 ? 9 : (GBT == 2 ? 4 : 2);
     bool dead = false;
     int seq = 0;
     for (int u = blockIdx.x; u < p.ntiles; u += gridDim.x) {
@@ -339,24 +367,25 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
                 const uint32_t tile = stage0 + uint32_t(s) * p.tile_bytes;
                 uint32_t wa = tile + w_rel, sa = tile + s_rel, za = tile + z_rel;
                 uint32_t aa = act0 + uint32_t((kc * p.KC + b_first) * GBT) * 64u;
+                uint32_t ca = corr0 + uint32_t(kc * p.KC + b_first) * 16u;
                 int left = my_blocks;
-                for (; left >= UNROLL; left -= UNROLL) {
-#pragma unroll
-                    for (int j = 0; j < UNROLL; j++)
-                        do_block<SCALE_F32, GBT>(acc, uc, wa + j * W_STEP, sa + j * S_STEP, za + j * Z_STEP,
-                                                 aa + j * A_STEP);
-                    wa += UNROLL * W_STEP;
-                    sa += UNROLL * S_STEP;
-                    za += UNROLL * Z_STEP;
-                    aa += UNROLL * A_STEP;
-                }
-                for (; left > 0; left--) {
-                    do_block<SCALE_F32, GBT>(acc, uc, wa, sa, za, aa);
-                    wa += W_STEP;
-                    sa += S_STEP;
-                    za += Z_STEP;
-                    aa += A_STEP;
-                }
+                // runs of BIG, then UNROLL, then single blocks: the offsets of a
+                // run are immediates of the loads, only the bases are bumped
+#define OVK_RUN(COUNT)                                                                                      \
+    for (; left >= (COUNT); left -= (COUNT)) {                                                              \
+        _Pragma("unroll") for (int j = 0; j < (COUNT); j++)                                                 \
+            do_block<SCALE_F32, GBT>(acc, uc, wa + j * W_STEP, sa + j * S_STEP, za + j * Z_STEP,            \
+                                     aa + j * A_STEP, ca + j * C_STEP);                                     \
+        wa += (COUNT) * W_STEP;                                                                             \
+        sa += (COUNT) * S_STEP;                                                                             \
+        za += (COUNT) * Z_STEP;                                                                             \
+        aa += (COUNT) * A_STEP;                                                                             \
+        ca += (COUNT) * C_STEP;                                                                             \
+    }
+                OVK_RUN(BIG)
+                OVK_RUN(UNROLL)
+                OVK_RUN(1)
+#undef OVK_RUN
                 __syncwarp();
                 if (lane == 0)
                     umma::mbar_arrive(&empty[s]);
@@ -483,7 +512,8 @@ nbits_decode_pack_kernel(const uint32_t *__restrict__ src_w, const void *__restr
 size_t decode_smem(const ovk_nbits_weight *w, int rows)
 {
     const size_t g_pad = size_t(w->dec_nkc) * w->dec_kc * w->dec_gb;
-    return size_t(STAGES) * w->dec_tile_bytes + size_t(rows) * g_pad * 64 + CONSUMER_WARPS * 32 * 16 + 32 + 64 + 128;
+    return size_t(STAGES) * w->dec_tile_bytes + size_t(rows) * g_pad * 64 + size_t(rows) * (g_pad / w->dec_gb) * 16 +
+           CONSUMER_WARPS * 32 * 16 + 32 + 64 + 128;
 }
 
 template <bool SF, bool AF, bool YF, int GB, int UN>
@@ -594,7 +624,7 @@ static int decode_rows_per_launch(const ovk_ctx *ctx, const ovk_nbits_weight *w,
     const size_t fixed = decode_smem(w, 0);
     if (fixed >= ctx->smem_optin)
         return 0;
-    const size_t cols = std::min<size_t>(8, std::min(ACT_MAX, ctx->smem_optin - fixed) / (g_pad * 64));
+    const size_t cols = std::min<size_t>(8, std::min(ACT_MAX, ctx->smem_optin - fixed) / (g_pad * 64 + (g_pad / w->dec_gb) * 16));
     return int(cols) / (a_dtype == OVK_FLOAT ? 2 : 1);
 }
 
