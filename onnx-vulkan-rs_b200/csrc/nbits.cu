@@ -59,10 +59,10 @@ void ovk_nbits_weight_destroy(ovk_ctx *ctx, ovk_nbits_weight *w)
 {
     if (!w)
         return;
-    if (w->decode && ctx) {
+    if (ctx)
         cudaStreamSynchronize(ctx->stream);
-        cudaFree(w->decode);
-    }
+    cudaFree(w->decode);
+    cudaFree(w->gemm_w);
     delete w;
 }
 

@@ -95,6 +95,12 @@ struct ovk_nbits_weight {
     size_t decode_bytes = 0;
     int dec_p = 0, dec_kc = 0, dec_gb = 0, dec_nkc = 0, dec_ntiles = 0;
     uint32_t dec_s_off = 0, dec_z_off = 0, dec_tile_bytes = 0;
+    // prefill copy (built on the first prefill call): nibble-permuted rows, f32 scales [block, n_pad],
+    // one zero-point byte per block [n_pad, zp_pitch]
+    void *gemm_w = nullptr;
+    float *gemm_scales_t = nullptr;
+    uint8_t *gemm_zp_t = nullptr;
+    int64_t gemm_k_pad = 0, gemm_n_pad = 0, gemm_zp_pitch = 0;
 };
 
 struct ovk_mmi_weight {

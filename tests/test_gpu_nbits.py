@@ -115,3 +115,51 @@ def test_refusals_match_the_reference_predicate():
     w = ctx().nbits_prepack(b, s, None, 4, 32, 32)
     with pytest.raises(ovk_b200.OvkError):
         ctx().matmul_nbits(w, torch.zeros(1, 31, device="cuda"))
+
+
+# ------------------------------------------------------------------ prefill
+
+@pytest.mark.parametrize("k,n,bs", [(1152, 1024, 32), (1152, 256, 32), (1024, 1152, 32), (1152, 6912, 32),
+                                    (6912, 1152, 32), (512, 384, 64), (3584, 512, 128), (1024, 200, 256)])
+@pytest.mark.parametrize("m", [9, 130, 512])
+def test_prefill_against_the_oracle(k, n, bs, m):
+    """M > 8 takes the tensor-core dequant-GEMM; fp16, atol=rtol=1e-3.  The
+    Gemma3-shaped projections at M=512 are config 2's prefill case."""
+    if m == 512 and k * n > 1152 * 6912:
+        pytest.skip("covered by the sampled full-size test")
+    a, nib, zp, scale = cases.nbits_synthetic(2, m, k, n, bs)
+    got, kern = run_gpu(a, nib, zp, scale, k, n, bs)
+    assert kern == "nbits_gemm_tc"
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, bs), scale, orc.pack_zero_points(zp), k, n, bs)
+    assert_close(got, want, 1e-3, 1e-3, f"prefill {k}->{n} bs={bs} M={m}")
+
+
+def test_prefill_f32_output_and_missing_zero_points():
+    a, nib, _, scale = cases.nbits_synthetic(6, 77, 640, 300, 32, with_zp=False)
+    got, kern = run_gpu(a, nib, None, scale, 640, 300, 32, out_dtype=torch.float32)
+    assert kern == "nbits_gemm_tc" and got.dtype == np.float32
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, 32), scale, None, 640, 300, 32, out_dtype=np.float32)
+    assert_close(got, want, 1e-4, 1e-4, "prefill f32 out")
+
+
+def test_prefill_ragged_k_and_f32_activations_fall_back_to_the_general_kernel():
+    a, nib, zp, scale = cases.nbits_synthetic(6, 20, 100, 48, 32, real=np.float32)
+    got, kern = run_gpu(a, nib, zp, scale, 100, 48, 32)
+    assert kern == "nbits_rows"
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, 32), scale, orc.pack_zero_points(zp), 100, 48, 32)
+    assert_close(got, want, 1e-4, 1e-4, "general kernel, M=20")
+
+
+def test_qwen_prefill_full_size_sampled():
+    """Config 5's gate/up shape at M=4096: K=3584 N=18944 bs=128, fp16; the
+    oracle checks 48 token rows x 296 weight columns spread over every tile."""
+    m, k, n, bs = 4096, 3584, 18944, 128
+    a, nib, zp, scale = cases.nbits_synthetic(5, m, k, n, bs, scale_lo=0.001, scale_hi=0.01)
+    got, kern = run_gpu(a, nib, zp, scale, k, n, bs)
+    assert kern == "nbits_gemm_tc"
+    rows = np.arange(5, m, 86)
+    cols = np.arange(3, n, 64)
+    want = orc.matmul_nbits(a[rows], orc.pack_nibbles(nib[cols], bs), scale[cols],
+                            orc.pack_zero_points(zp[cols]), k, cols.size, bs)
+    assert_close(got[np.ix_(rows, cols)], want, 1e-3, 1e-3, "qwen gate/up prefill")
+    assert np.isfinite(got.astype(np.float32)).all()
