@@ -113,11 +113,18 @@ struct ovk_mmi_weight {
     void *tmap_b = nullptr;    // host copy of the CUtensorMap describing bt (128 bytes), or null
 };
 
+// Resolved geometry of one convolution call (interp::ConvGeom, src/interp.rs:3361-3384).
+struct ConvGeom {
+    int n, c_in, c_out, group, cig;
+    int h_in, w_in, h_out, w_out;
+    int kh, kw, sh, sw, dh, dw, phb, pwb, phe, pwe;
+};
+
 struct ovk_qconv_weight {
     int64_t c_out = 0, cig = 0, kh = 0, kw = 0, group = 1;
     int32_t w_signed = 0;
     uint8_t *w = nullptr;       // copy in the operator layout [C_out, C_in/g, KH, KW]
     uint8_t *w_taps = nullptr;  // [KH*KW, C_out_pad, C_in] tap-major copy for the tensor path (group 1)
-    int32_t *wsum = nullptr;    // [C_out] sum of all weights of a filter (group 1)
+    int32_t *wsum = nullptr;    // [C_out_pad] sum of all weights of a filter (group 1)
     int64_t c_out_pad = 0;
 };

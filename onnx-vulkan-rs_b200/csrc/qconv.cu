@@ -10,12 +10,6 @@
 #include "ovk_internal.h"
 #include "epilogue.cuh"
 
-struct ConvGeom {
-    int n, c_in, c_out, group, cig;
-    int h_in, w_in, h_out, w_out;
-    int kh, kw, sh, sw, dh, dw, phb, pwb;
-};
-
 bool ovk_qconv_tc_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, const void *x);
 int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,
                             const ConvGeom &g, int32_t x_zp, int32_t w_zp, const EpiParams &epi,
@@ -125,6 +119,8 @@ int32_t make_geom(ovk_ctx *ctx, const ovk_qconv_weight *w, const ovk_conv_params
     g->dw = int(p->dilations[1]);
     g->phb = int(p->pads[0]);
     g->pwb = int(p->pads[1]);
+    g->phe = int(p->pads[2]);
+    g->pwe = int(p->pads[3]);
     return OVK_OK;
 }
 
@@ -143,8 +139,11 @@ int32_t run_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t
         return OVK_OK;
     OVK_REQUIRE(ctx, x && out, "%s: x or the output is null", op);
     OVK_CUDA(ctx, cudaSetDevice(ctx->device));
-    if (ovk_qconv_tc_applies(ctx, w, g, x))
-        return ovk_qconv_tc_launch(ctx, w, x, x_signed, g, x_zp, w_zp, epi, out);
+    if (ovk_qconv_tc_applies(ctx, w, g, x)) {
+        const int32_t rc_tc = ovk_qconv_tc_launch(ctx, w, x, x_signed, g, x_zp, w_zp, epi, out);
+        if (rc_tc != OVK_UNSUPPORTED)  // an asymmetric weight or no room for the stages: the direct kernel runs
+            return rc_tc;
+    }
     conv_direct_kernel<<<unsigned(ceil_div64(total, 256)), 256, 0, ctx->stream>>>(
         static_cast<const uint8_t *>(x), w->w, g, x_signed, w->w_signed, x_zp, w_zp, epi, out, total);
     OVK_LAUNCHED(ctx, "conv_direct");

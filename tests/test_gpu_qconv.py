@@ -115,3 +115,39 @@ def test_requantize_pass_matches():
     bias = np.arange(-2, 3, dtype=np.int32) * 1000
     got = ctx().requantize(dev(acc), 7, dev(ratio), 17, bias=dev(bias))
     assert np.array_equal(host(got), orc.requantize(acc, 7, ratio, 17, bias))
+
+
+def test_resnet_block_takes_the_tensor_core_kernel():
+    """Which kernel ran (the role of pipeline_keys in
+    crates/onnx-vulkan-core/tests/conv_integer_im2col.rs:163-178): stride 1,
+    group 1, symmetric weights -> tcgen05; an asymmetric weight or a stride -> direct."""
+    x, w, w_scale, bias = _resnet_block(2)
+    wq = ctx().qconv_prepack(dev(w))
+    ctx().conv_integer(wq, dev(x), 128, 0, pads=(1, 1, 1, 1))
+    assert ctx().last_kernel.startswith("qconv_tc")
+    ctx().conv_integer(wq, dev(x), 128, 5, pads=(1, 1, 1, 1))
+    assert ctx().last_kernel == "conv_direct"
+    ctx().conv_integer(wq, dev(x), 128, 0, pads=(1, 1, 1, 1), strides=(2, 2))
+    assert ctx().last_kernel == "conv_direct"
+
+
+@pytest.mark.parametrize("c_in,c_out,h,w,k,dil,pads,xs", [
+    (32, 40, 20, 20, 3, 1, (1, 1, 1, 1), False),
+    (64, 48, 24, 24, 1, 1, (0, 0, 0, 0), False),
+    (128, 64, 14, 18, 3, 2, (2, 2, 2, 2), True),
+    (256, 32, 12, 12, 3, 1, (1, 0, 2, 1), False),
+    (64, 100, 9, 33, 3, 1, (1, 1, 1, 1), True),
+    (32, 24, 11, 13, 5, 1, (2, 2, 2, 2), False),
+])
+def test_tensor_core_geometries(c_in, c_out, h, w, k, dil, pads, xs):
+    """Channel counts 32/64/128/256 (one to two K slices per tap), dilation,
+    uneven pads, pointwise and 5x5 filters, signed x, C_out off the tile size."""
+    x = cases.lcg_bytes_fast(3 * c_in * h * w, 21).reshape(3, c_in, h, w)
+    wt = cases.lcg_bytes_fast(c_out * c_in * k * k, 23).reshape(c_out, c_in, k, k).view(np.int8)
+    x = x.view(np.int8) if xs else x
+    x_zp = -9 if xs else 131
+    wq = ctx().qconv_prepack(dev(wt))
+    got = ctx().conv_integer(wq, dev(x), x_zp, 0, pads=pads, dilations=(dil, dil))
+    assert ctx().last_kernel.startswith("qconv_tc"), ctx().last_kernel
+    want = orc.conv_integer(x, wt, x_zp, 0, dilations=(dil, dil), pads=pads)
+    assert np.array_equal(host(got), want)
