@@ -9,6 +9,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <string>
+#include <vector>
 
 #include "ovk_cuda.h"
 
@@ -127,4 +128,9 @@ struct ovk_qconv_weight {
     uint8_t *w_taps = nullptr;  // [KH*KW, C_out_pad, C_in] tap-major copy for the tensor path (group 1)
     int32_t *wsum = nullptr;    // [C_out_pad] sum of all weights of a filter (group 1)
     int64_t c_out_pad = 0;
+    // the last requantisation ratios uploaded for this filter bank (a content-keyed
+    // parameter cache, as interp::param_buffer in the reference): constants of the
+    // graph are uploaded once, not per call
+    std::vector<float> ratio_host;
+    float *ratio_dev = nullptr;
 };

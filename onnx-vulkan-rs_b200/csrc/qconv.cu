@@ -10,6 +10,8 @@
 #include "ovk_internal.h"
 #include "epilogue.cuh"
 
+#include <cstring>
+
 bool ovk_qconv_tc_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, const void *x);
 int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,
                             const ConvGeom &g, int32_t x_zp, int32_t w_zp, const EpiParams &epi,
@@ -201,6 +203,7 @@ void ovk_qconv_weight_destroy(ovk_ctx *ctx, ovk_qconv_weight *w)
     cudaFree(w->w);
     cudaFree(w->w_taps);
     cudaFree(w->wsum);
+    cudaFree(w->ratio_dev);
     delete w;
 }
 
@@ -232,13 +235,19 @@ int32_t ovk_qlinear_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x,
     if (!ctx || !w)
         return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "QLinearConv: null argument");
     OVK_REQUIRE(ctx, ratio_host, "QLinearConv: ratio is null");
-    // the per-channel ratio is a graph constant: staged in the context's parameter buffer per call
-    // (the reference uploads it through its parameter cache, interp.rs:4751-4753)
-    OVK_REFUSE(ctx, w->c_out > OVK_PARAM_FLOATS, "QLinearConv: %lld output channels exceed the parameter buffer",
-               (long long)w->c_out);
-    float *ratio_dev = ctx->params;
-    OVK_CUDA(ctx, cudaMemcpyAsync(ratio_dev, ratio_host, size_t(w->c_out) * sizeof(float),
-                                  cudaMemcpyHostToDevice, ctx->stream));
+    // the per-channel ratio is a graph constant: uploaded when its content changes
+    // (the reference keys its parameter cache by content, interp.rs:4751-4753)
+    ovk_qconv_weight *wm = const_cast<ovk_qconv_weight *>(w);
+    const size_t nratio = size_t(w->c_out);
+    if (!wm->ratio_dev)
+        OVK_CUDA(ctx, cudaMalloc(&wm->ratio_dev, nratio * sizeof(float)));
+    if (wm->ratio_host.size() != nratio || memcmp(wm->ratio_host.data(), ratio_host, nratio * sizeof(float)) != 0) {
+        wm->ratio_host.assign(ratio_host, ratio_host + nratio);
+        // ordered after the kernels already enqueued, which may still read the old values
+        OVK_CUDA(ctx, cudaMemcpyAsync(wm->ratio_dev, wm->ratio_host.data(), nratio * sizeof(float),
+                                      cudaMemcpyHostToDevice, ctx->stream));
+    }
+    float *ratio_dev = wm->ratio_dev;
     EpiParams epi = {};
     epi.mode = EPI_REQUANT;
     epi.ratio = ratio_dev;

@@ -31,7 +31,8 @@
 namespace {
 
 constexpr int BM = 128;  // pixels per tile
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 16;            // four per tensor-memory lane quarter
+constexpr int THREADS = (2 + EPI_WARPS) * 32;
 constexpr long long WAIT_CYCLES = 2000000000ll;
 constexpr size_t W_SMEM_MAX = 112 * 1024;
 
@@ -55,6 +56,7 @@ struct ConvTcParams {
     void *out;
     int *status;
     int m_tiles;
+    int nacc;
 };
 
 __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
@@ -62,15 +64,16 @@ __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
     if (umma::mbar_try_wait(bar, parity))
         return true;
     const long long t0 = clock64();
-    for (uint32_t spins = 0;; spins++) {
-        if (umma::mbar_try_wait(bar, parity))
+    for (;;) {
+        if (umma::mbar_try_wait_hint(bar, parity, 1000u))  // parked for up to a microsecond, not spinning
             return true;
-        if ((spins & 63u) == 63u && clock64() - t0 > WAIT_CYCLES)
+        if (clock64() - t0 > WAIT_CYCLES)
             return false;
     }
 }
 
 constexpr int MAX_STAGES = 8;
+constexpr int MAX_ACC = 8;  // tensor-memory accumulators in flight (512 columns / co_pad, at most 8)
 
 __global__ void __launch_bounds__(THREADS, 1)
 qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, ConvTcParams p)
@@ -81,14 +84,23 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     uint8_t *sA = smem + size_t(slices) * p.w_slice;       // stages x a_stage: pixel tiles
     uint64_t *bars = reinterpret_cast<uint64_t *>(sA + size_t(p.stages) * p.a_stage);
     uint64_t *a_full = bars, *a_empty = bars + MAX_STAGES;
-    uint64_t *acc_full = a_empty + MAX_STAGES, *acc_empty = acc_full + 2;
-    uint64_t *w_full = acc_empty + 2;
+    uint64_t *acc_full = a_empty + MAX_STAGES, *acc_empty = acc_full + MAX_ACC;
+    uint64_t *w_full = acc_empty + MAX_ACC;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(w_full + 1);
     // per-channel constants of the epilogue, staged once: bias - zp * sum(w) and the requantisation ratio
     int32_t *s_corr = reinterpret_cast<int32_t *>(tmem_slot + 2);
     float *s_ratio = reinterpret_cast<float *>(s_corr + 256);
+    // per tap: offset of its first pixel row inside a halo tile and start of its filter slice, both in
+    // 16-byte units (the unit of a descriptor's address field)
+    uint32_t *s_tap_a = reinterpret_cast<uint32_t *>(s_ratio + 256);
+    uint32_t *s_tap_w = s_tap_a + 64;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int tap = threadIdx.x; tap < p.taps && tap < 64; tap += THREADS) {
+        const int off = (tap / p.kw) * p.dh * p.wp + (tap % p.kw) * p.dw;
+        s_tap_a[tap] = uint32_t(off) * uint32_t(p.kch) >> 4;
+        s_tap_w[tap] = (umma::smem_u32(sWt) + uint32_t(tap) * p.w_slice) >> 4;
+    }
     for (int co = threadIdx.x; co < p.co_pad; co += THREADS) {
         int32_t corr = 0;
         float ratio = 0.0f;
@@ -103,8 +115,9 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         s_corr[co] = corr;
         s_ratio[co] = ratio;
     }
+    const int nacc = p.nacc;  // power of two
     uint32_t tmem_cols = 32;
-    while (tmem_cols < uint32_t(2 * p.co_pad))
+    while (tmem_cols < uint32_t(nacc * p.co_pad))
         tmem_cols <<= 1;
 
     if (threadIdx.x == 0) {
@@ -112,9 +125,9 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
             umma::mbar_init(&a_full[s], 1);
             umma::mbar_init(&a_empty[s], 1);
         }
-        for (int b = 0; b < 2; b++) {
+        for (int b = 0; b < nacc; b++) {
             umma::mbar_init(&acc_full[b], 1);
-            umma::mbar_init(&acc_empty[b], 4);
+            umma::mbar_init(&acc_empty[b], EPI_WARPS);
         }
         umma::mbar_init(w_full, 1);
         umma::fence_barrier_init();
@@ -169,9 +182,13 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                 atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
             int seq = 0, tile_seq = 0;
             const int ksteps = p.kch / 32;
+            // descriptor halves that never change: LBO = 1 (unused by swizzled K-major), version 1,
+            // stride between 8-row groups, swizzle mode
+            const uint32_t desc_lo_flags = 1u << 16;
+            const uint32_t desc_hi = ((uint32_t(p.sbo) >> 4) & 0x3fffu) | (1u << 14) | (uint32_t(p.sw_layout) << 29);
             for (int tile = blockIdx.x; tile < p.m_tiles && ok; tile += gridDim.x, tile_seq++) {
-                const int b = tile_seq & 1;
-                if (!wait_bounded(&acc_empty[b], ((tile_seq >> 1) & 1) ^ 1)) {
+                const int b = tile_seq & (nacc - 1);
+                if (!wait_bounded(&acc_empty[b], ((tile_seq / nacc) & 1) ^ 1)) {
                     atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
                     ok = false;
                     break;
@@ -186,18 +203,17 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                         break;
                     }
                     umma::tc_fence_after();
-                    const uint32_t a_base = umma::smem_u32(sA + size_t(s) * p.a_stage);
+                    // The tap's rows start some rows into the halo tile.  The swizzle is a function of the
+                    // absolute shared-memory address (TMA wrote the tile with the same function), so the
+                    // descriptor needs no base offset: measured bit-exact with 0, wrong otherwise.
+                    const uint32_t a16 = umma::smem_u32(sA + size_t(s) * p.a_stage) >> 4;
+                    uint32_t accumulate = 0;
                     for (int tap = 0; tap < p.taps; tap++) {
-                        const int off = (tap / p.kw) * p.dh * p.wp + (tap % p.kw) * p.dw;
-                        const uint32_t a_addr = a_base + uint32_t(off) * uint32_t(p.kch);
-                        const uint32_t w_addr = umma::smem_u32(sWt + size_t(tap) * p.w_slice);
+                        const uint32_t a_lo = ((a16 + s_tap_a[tap]) & 0x3fffu) | desc_lo_flags;
+                        const uint32_t w_lo = (s_tap_w[tap] & 0x3fffu) | desc_lo_flags;
                         for (int j = 0; j < ksteps; j++) {
-                            // The tap's rows start `off` rows into the halo tile.  The swizzle is a function of
-                            // the absolute shared-memory address (TMA wrote the tile with the same function),
-                            // so the descriptor needs no base offset: measured bit-exact with 0, wrong otherwise.
-                            const uint64_t da = umma::smem_desc(a_addr + j * 32, p.sbo, p.sw_layout);
-                            const uint64_t dw = umma::smem_desc(w_addr + j * 32, p.sbo, p.sw_layout);
-                            umma::mma_i8(d_tmem, da, dw, idesc, (tap | j) != 0);
+                            umma::mma_i8_lohi(d_tmem, a_lo + 2u * j, desc_hi, w_lo + 2u * j, desc_hi, idesc, accumulate);
+                            accumulate = 1;
                         }
                     }
                     umma::mma_commit(&a_empty[s]);
@@ -227,29 +243,45 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         }
     } else {
         // ---------------------------------------------------------------- epilogue
+        // warp w reads lane quarter w % 4 (a hardware rule); the four warps of a
+        // quarter take the 16-channel column groups round robin
         const int q = warp & 3;
+        const int sub = (warp - 2) >> 2;
+        constexpr int SUBS = EPI_WARPS / 4;
         int tile_seq = 0;
         bool ok = true;
+        const int64_t plane = int64_t(p.h_out) * p.w_out;
+        const int lo = p.epi.y_signed ? -128 : 0, hi = p.epi.y_signed ? 127 : 255;
         for (int tile = blockIdx.x; tile < p.m_tiles; tile += gridDim.x, tile_seq++) {
-            const int b = tile_seq & 1;
-            if (ok && !wait_bounded(&acc_full[b], (tile_seq >> 1) & 1)) {
+            const int b = tile_seq & (nacc - 1);
+            if (ok && !wait_bounded(&acc_full[b], (tile_seq / nacc) & 1)) {
                 if (lane == 0)
                     atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
                 ok = false;
             }
             umma::tc_fence_after();
-            const int64_t v = int64_t(tile) * BM + q * 32 + lane;
-            const int64_t img = v / p.hpwp;
-            const int rem = int(v % p.hpwp);
-            const int oh = rem / p.wp, ow = rem % p.wp;
-            const bool valid = ok && v < p.v_total && oh < p.h_out && ow < p.w_out;
-            const int64_t plane = int64_t(p.h_out) * p.w_out;
-            const int64_t o_base = img * p.c_out * plane + int64_t(oh) * p.w_out + ow;
-            for (int c0 = 0; c0 < p.co_pad; c0 += 32) {
-                uint32_t r[32];
-                umma::tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * p.co_pad + c0), r);
+            // pixel coordinates in 32-bit arithmetic (v_total < 2^31 is checked on the host)
+            const uint32_t v = uint32_t(tile) * BM + q * 32 + lane;
+            const uint32_t img = v / uint32_t(p.hpwp);
+            const uint32_t rem = v - img * uint32_t(p.hpwp);
+            const uint32_t oh = rem / uint32_t(p.wp), ow = rem - oh * uint32_t(p.wp);
+            const bool valid = ok && int64_t(v) < p.v_total && int(oh) < p.h_out && int(ow) < p.w_out;
+            const int64_t o_base = int64_t(img) * p.c_out * plane + int64_t(oh) * p.w_out + ow;
+            // this warp's last column group: after reading it the accumulator is handed back
+            int last_c0 = -1;
+            for (int c0 = sub * 16; c0 < p.co_pad; c0 += SUBS * 16)
+                last_c0 = c0;
+            if (last_c0 < 0) {
+                umma::tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    umma::mbar_arrive(&acc_empty[b]);
+            }
+            for (int c0 = sub * 16; c0 < p.co_pad; c0 += SUBS * 16) {
+                uint32_t r[16];
+                umma::tmem_ld_32x16(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * p.co_pad + c0), r);
                 umma::tmem_ld_wait();
-                if (c0 + 32 >= p.co_pad) {  // last read of this accumulator: hand it back
+                if (c0 == last_c0) {
                     umma::tc_fence_before();
                     __syncwarp();
                     if (lane == 0)
@@ -257,24 +289,34 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                 }
                 if (!valid)
                     continue;
+                // constants of the 16 channels: four 128-bit shared loads each
+                int32_t corr[16];
+                float ratio[16];
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) {
+                    const int4 cv = *reinterpret_cast<const int4 *>(s_corr + c0 + j);
+                    const float4 rv = *reinterpret_cast<const float4 *>(s_ratio + c0 + j);
+                    corr[j] = cv.x; corr[j + 1] = cv.y; corr[j + 2] = cv.z; corr[j + 3] = cv.w;
+                    ratio[j] = rv.x; ratio[j + 1] = rv.y; ratio[j + 2] = rv.z; ratio[j + 3] = rv.w;
+                }
+                const int nch = min(16, p.c_out - c0);  // channels of this group that exist
                 if (p.epi.mode == EPI_RAW) {
                     int32_t *o = static_cast<int32_t *>(p.out) + o_base + int64_t(c0) * plane;
 #pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (c0 + j < p.c_out)
-                            o[j * plane] = int32_t(r[j] + uint32_t(s_corr[c0 + j]));
+                    for (int j = 0; j < 16; j++)
+                        if (j < nch)
+                            o[int64_t(j) * plane] = int32_t(r[j] + uint32_t(corr[j]));
                 } else {
                     uint8_t *o = static_cast<uint8_t *>(p.out) + o_base + int64_t(c0) * plane;
-                    const int lo = p.epi.y_signed ? -128 : 0, hi = p.epi.y_signed ? 127 : 255;
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        if (c0 + j < p.c_out) {
-                            // sat(rne(f32(acc + bias) * ratio) + y_zp), shaders/qlinear.rs:28-63
-                            const int32_t acc = int32_t(r[j] + uint32_t(s_corr[c0 + j]));
-                            const float f = rintf(__fmul_rn(float(acc), s_ratio[c0 + j]));
-                            const int32_t qv = int32_t(uint32_t(__float2int_rn(f)) + uint32_t(p.epi.y_zp));
-                            o[j * plane] = uint8_t(max(lo, min(hi, qv)));
-                        }
+                    for (int j = 0; j < 16; j++) {
+                        // sat(rne(f32(acc + bias) * ratio) + y_zp), shaders/qlinear.rs:28-63;
+                        // the f32 -> i32 conversion itself rounds to nearest even and saturates
+                        const int32_t acc = int32_t(r[j] + uint32_t(corr[j]));
+                        const int32_t qv = int32_t(uint32_t(__float2int_rn(__fmul_rn(float(acc), ratio[j]))) +
+                                                   uint32_t(p.epi.y_zp));
+                        if (j < nch)
+                            o[int64_t(j) * plane] = uint8_t(max(lo, min(hi, qv)));
                     }
                 }
             }
@@ -288,38 +330,47 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
 
 // NCHW -> padded NHWC with the padding set to the zero point.  One block per
 // padded image row; channels go through shared memory in groups so that reads
-// run along W and writes along C.
+// run along W (32-bit when the rows allow it) and writes along C (32-bit, 64+
+// contiguous bytes per pixel).
 __global__ void __launch_bounds__(256)
 conv_pad_nhwc_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ xp, int C, int H, int W, int HP, int WP,
-                     int pt, int pl, uint32_t zp_byte, int cgroup)
+                     int pt, int pl, uint32_t zp_byte, int cgroup, int pitch, int words_ok)
 {
-    extern __shared__ uint8_t tile[];  // [W][cgroup + 4]
+    extern __shared__ __align__(16) uint8_t tile[];  // [cgroup][pitch]
     const int hp = blockIdx.x, n = blockIdx.y;
     uint8_t *dst_row = xp + (size_t(n) * HP + hp) * size_t(WP) * C;
     const int h = hp - pt;
+    const uint32_t zp4 = zp_byte * 0x01010101u;
     if (h < 0 || h >= H) {
-        const uint32_t w4 = zp_byte * 0x01010101u;
         for (int i = threadIdx.x; i < WP * C / 4; i += blockDim.x)
-            reinterpret_cast<uint32_t *>(dst_row)[i] = w4;
+            reinterpret_cast<uint32_t *>(dst_row)[i] = zp4;
         return;
     }
-    const int pitch = cgroup + 4;
     for (int c0 = 0; c0 < C; c0 += cgroup) {
         const int cg = min(cgroup, C - c0);
-        for (int i = threadIdx.x; i < cg * W; i += blockDim.x) {
-            const int c = i / W, w = i % W;
-            tile[w * pitch + c] = x[((size_t(n) * C + c0 + c) * H + h) * W + w];
+        if (words_ok) {
+            const int wpr = W >> 2;
+            for (int i = threadIdx.x; i < cg * wpr; i += blockDim.x) {
+                const int c = i / wpr, ww = i - c * wpr;
+                const uint32_t *src = reinterpret_cast<const uint32_t *>(x + ((size_t(n) * C + c0 + c) * H + h) * W);
+                reinterpret_cast<uint32_t *>(tile + c * pitch)[ww] = __ldg(src + ww);
+            }
+        } else {
+            for (int i = threadIdx.x; i < cg * W; i += blockDim.x) {
+                const int c = i / W, w = i - c * W;
+                tile[c * pitch + w] = x[((size_t(n) * C + c0 + c) * H + h) * W + w];
+            }
         }
         __syncthreads();
-        // cg is a multiple of 4: write words
-        const int words = cg / 4;
+        const int words = cg >> 2;  // channel groups are multiples of 4
         for (int i = threadIdx.x; i < WP * words; i += blockDim.x) {
-            const int wpix = i / words, cw = i % words;
+            const int wpix = i / words, cw = i - wpix * words;
             const int w = wpix - pl;
-            uint32_t v = zp_byte * 0x01010101u;
+            uint32_t v = zp4;
             if (w >= 0 && w < W) {
-                const uint8_t *t = tile + w * pitch + cw * 4;
-                v = uint32_t(t[0]) | (uint32_t(t[1]) << 8) | (uint32_t(t[2]) << 16) | (uint32_t(t[3]) << 24);
+                const uint8_t *t = tile + (cw * 4) * pitch + w;
+                v = uint32_t(t[0]) | (uint32_t(t[pitch]) << 8) | (uint32_t(t[2 * pitch]) << 16) |
+                    (uint32_t(t[3 * pitch]) << 24);
             }
             reinterpret_cast<uint32_t *>(dst_row + size_t(wpix) * C + c0)[cw] = v;
         }
@@ -371,7 +422,7 @@ int conv_mode()
 int32_t ovk_qconv_tc_prepare_weight(ovk_ctx *ctx, ovk_qconv_weight *w)
 {
     const int64_t c_in = w->cig, taps = w->kh * w->kw;
-    if (w->group != 1 || (c_in != 32 && c_in != 64 && c_in % 128 != 0) || w->c_out > 256)
+    if (w->group != 1 || (c_in != 32 && c_in != 64 && c_in % 128 != 0) || w->c_out > 256 || taps > 64)
         return OVK_OK;  // the direct kernel takes these
     const int64_t co_pad = ceil_div64(w->c_out, 32) * 32;
     if (size_t(taps) * co_pad * c_in > W_SMEM_MAX)
@@ -413,13 +464,16 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
         return rc;
     uint8_t *xp = static_cast<uint8_t *>(ws);
     {
+        const int pitch = ((g.w_in + 3) & ~3) + 4;
         int cgroup = C;
-        while (size_t(g.w_in) * (cgroup + 4) > 40 * 1024 && cgroup > 4)
+        while (size_t(cgroup) * pitch > 40 * 1024 && cgroup > 4)
             cgroup = ((cgroup / 2) + 3) & ~3;
-        const size_t sm = size_t(g.w_in) * (cgroup + 4);
+        const size_t sm = size_t(cgroup) * pitch;
         OVK_REQUIRE(ctx, sm <= 48 * 1024, "ConvInteger: input rows of %d pixels are too wide for the layout pass", g.w_in);
+        const int words_ok = (g.w_in % 4) == 0 && aligned_to(x, 4);
         conv_pad_nhwc_kernel<<<dim3(unsigned(HP), unsigned(g.n)), 256, sm, ctx->stream>>>(
-            static_cast<const uint8_t *>(x), xp, C, g.h_in, g.w_in, HP, WP, g.phb, g.pwb, uint32_t(x_zp) & 0xffu, cgroup);
+            static_cast<const uint8_t *>(x), xp, C, g.h_in, g.w_in, HP, WP, g.phb, g.pwb, uint32_t(x_zp) & 0xffu, cgroup,
+            pitch, words_ok);
         OVK_LAUNCHED(ctx, "conv_pad_nhwc");
     }
     ConvTcParams p = {};
@@ -444,7 +498,7 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
     p.a_stage = uint32_t((size_t(p.halo_rows) * p.kch + 1023) & ~size_t(1023));
     p.w_slice = uint32_t((size_t(p.co_pad) * p.kch + 1023) & ~size_t(1023));
     const size_t w_bytes = size_t(p.taps) * p.chunks * p.w_slice;
-    const size_t avail = ctx->smem_optin - w_bytes - 1024 - 2048;
+    const size_t avail = ctx->smem_optin - w_bytes - 1024 - 2048 - 512;
     p.stages = int(std::min<size_t>(MAX_STAGES, avail / p.a_stage));
     if (p.stages < 2)
         return OVK_UNSUPPORTED;
@@ -456,6 +510,9 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
     p.out = out;
     p.status = ctx->dev_status;
     p.m_tiles = int(ceil_div64(v_total, BM));
+    p.nacc = 2;
+    while (p.nacc * 2 <= MAX_ACC && p.nacc * 2 * p.co_pad <= 512)
+        p.nacc *= 2;
     const CUtensorMapSwizzle swz = p.kch == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                                 : (p.kch == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
     CUtensorMap tmX, tmW;
@@ -464,7 +521,7 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
         !ovk_make_tmap_2d(&tmW, w->w_taps, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(C), uint64_t(p.taps) * p.co_pad,
                           uint64_t(C), uint32_t(p.kch), uint32_t(p.co_pad), swz))
         return ovk_fail(ctx, OVK_BACKEND, "ConvInteger: cuTensorMapEncodeTiled failed");
-    const size_t smem = w_bytes + size_t(p.stages) * p.a_stage + 512 + 2048;
+    const size_t smem = w_bytes + size_t(p.stages) * p.a_stage + 512 + 2048 + 512;
     OVK_CUDA(ctx, cudaFuncSetAttribute(qconv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     const unsigned grid = unsigned(std::min<int>(p.m_tiles, ctx->sm_count));
     qconv_tc_kernel<<<grid, THREADS, smem, ctx->stream>>>(tmX, tmW, p);
