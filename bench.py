@@ -107,12 +107,118 @@ class ClockSampler:
 
 # --------------------------------------------------------------------- GPU arm
 
-def make_weight(torch, ctx, k, n, bs, gen):
+def make_weight(torch, ctx, k, n, bs, gen, scale_lo=0.002, scale_hi=0.02, rows=None):
+    """Random int4 weight in the operator layout; `rows` keeps only a column shard."""
     nb = -(-k // bs)
-    b = torch.randint(0, 256, (n, nb, bs // 2), dtype=torch.uint8, device="cuda", generator=gen)
-    scales = (torch.rand((n * nb,), device="cuda", generator=gen) * 0.018 + 0.002).to(torch.float16)
-    zp = torch.randint(0, 256, (n, (nb + 1) // 2), dtype=torch.uint8, device="cuda", generator=gen)
-    return ctx.nbits_prepack(b, scales, zp, n, k, bs)
+    n_local = n if rows is None else rows.count
+    b = torch.randint(0, 256, (n_local, nb, bs // 2), dtype=torch.uint8, device="cuda", generator=gen)
+    scales = (torch.rand((n_local * nb,), device="cuda", generator=gen) * (scale_hi - scale_lo) + scale_lo).to(torch.float16)
+    zp = torch.randint(0, 256, (n_local, (nb + 1) // 2), dtype=torch.uint8, device="cuda", generator=gen)
+    return ctx.nbits_prepack(b, scales, zp, n_local, k, bs)
+
+
+def timed(torch, dist, world, fn, iters, warm=3):
+    """ms per call of fn, CUDA events on the current stream, max over ranks."""
+    for _ in range(warm):
+        fn()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
+    """The other operators of the path, one line each.  With more than one GPU
+    the prefill is split by weight columns (all-gather of the outputs) and the
+    convolution by batch (no exchange)."""
+    import numpy as np
+    from ovk_b200 import shard
+    out = {}
+    bf16_peak = peaks["bf16_tflops"]
+
+    # ---- int4 prefill, Qwen2.5-7B-shaped (config 5), M = 4096, block 128
+    m = 4096
+    for name, k, n in (("gate_up", 3584, 18944), ("down", 18944, 3584)):
+        sh = shard.column_shard(n, world, rank)
+        w = make_weight(torch, ctx, k, n, 128, gen, 0.001, 0.01, rows=sh)
+        a = torch.randn((m, k), device="cuda", generator=gen).to(torch.float16)
+        y = torch.empty((m, sh.count), dtype=torch.float16, device="cuda")
+        ms_c = timed(torch, dist, world, lambda: ctx.matmul_nbits(w, a, out=y), 5)
+        entry = {"M": m, "K": k, "N": n, "block_size": 128, "kernel": ctx.last_kernel, "ms_compute": ms_c,
+                 "tflops_compute": 2.0 * m * k * n / (ms_c * 1e-3) / 1e12}
+        entry["frac_of_measured_bf16_peak_per_gpu"] = entry["tflops_compute"] / world / bf16_peak
+        if world > 1:
+            def step():
+                ctx.matmul_nbits(w, a, out=y)
+                shard.all_gather_columns(y, n, world)
+            ms_e = timed(torch, dist, world, step, 5)
+            entry.update({"ms_with_all_gather": ms_e, "tflops_with_all_gather": 2.0 * m * k * n / (ms_e * 1e-3) / 1e12,
+                          "parallelism": "N-split x%d + NCCL all-gather of fp16 outputs" % world})
+        out["int4_prefill_qwen7b_" + name] = entry
+        del w, a, y
+    # ---- int4 prefill, Gemma3-1B-shaped lm_head (config 2), M = 512, block 32: rank-local
+    if world == 1:
+        w = make_weight(torch, ctx, HIDDEN, VOCAB, BLOCK, gen)
+        a = torch.randn((512, HIDDEN), device="cuda", generator=gen).to(torch.float16)
+        y = torch.empty((512, VOCAB), dtype=torch.float16, device="cuda")
+        ms_c = timed(torch, dist, 1, lambda: ctx.matmul_nbits(w, a, out=y), 5)
+        out["int4_prefill_gemma3_lm_head"] = {"M": 512, "K": HIDDEN, "N": VOCAB, "block_size": 32,
+                                              "kernel": ctx.last_kernel, "ms_compute": ms_c,
+                                              "tflops_compute": 2.0 * 512 * HIDDEN * VOCAB / (ms_c * 1e-3) / 1e12}
+        del w, a, y
+
+    # ---- dynamic int8 encoder GEMMs, Parakeet-shaped (config 3): replicas
+    t = 1000
+    layer = [(1024, 1024)] * 4 + [(1024, 4096), (4096, 1024)]
+    ws, xs, scs, bis = [], {}, [], []
+    for k, n in layer:
+        ws.append(ctx.mmi_prepack(torch.randint(-127, 128, (k, n), dtype=torch.int8, device="cuda", generator=gen)))
+        scs.append(torch.rand((n,), device="cuda", generator=gen) * 0.009 + 0.001)
+        bis.append(torch.zeros((n,), device="cuda"))
+        if k not in xs:
+            xs[k] = torch.randn((t, k), device="cuda", generator=gen)
+
+    def layer_step():
+        for (k, n), w, sc, bi in zip(layer, ws, scs, bis):
+            xq, a_scale, a_zp = ctx.dynamic_quantize(xs[k])
+            ctx.matmul_integer_scale_bias(w, xq, a_zp, None, sc, bi, product=a_scale.reshape(1))
+    ms_l = timed(torch, dist, world, layer_step, 10)
+    ops = sum(2.0 * t * k * n for k, n in layer)
+    out["int8_dynamic_parakeet_layer"] = {"T": t, "gemms": len(layer), "ms_per_layer": ms_l, "kernel": ctx.last_kernel,
+                                          "tops": world * ops / (ms_l * 1e-3) / 1e12,
+                                          "note": "DynamicQuantizeLinear + MatMulInteger with the fused f32 epilogue; "
+                                                  "2-8 GOP per GEMM, latency/HBM-bound; replicas at N > 1"}
+    big = ctx.mmi_prepack(torch.randint(-127, 128, (8192, 8192), dtype=torch.int8, device="cuda", generator=gen))
+    xa = torch.randint(0, 256, (8192, 8192), dtype=torch.uint8, device="cuda", generator=gen)
+    zp8 = torch.full((1,), 128, dtype=torch.uint8, device="cuda")
+    ms_b = timed(torch, dist, world, lambda: ctx.matmul_integer(big, xa, zp8, None), 5)
+    out["int8_gemm_8192"] = {"ms": ms_b, "kernel": ctx.last_kernel, "tops_per_gpu": 2.0 * 8192 ** 3 / (ms_b * 1e-3) / 1e12,
+                             "frac_of_2x_measured_bf16_peak": 2.0 * 8192 ** 3 / (ms_b * 1e-3) / 1e12 / (2 * bf16_peak)}
+    del ws, xs, big, xa
+
+    # ---- static int8 QLinearConv, ResNet block (config 4): batch 64 split over the ranks
+    bsh = shard.batch_shard(64, world, rank)
+    x = torch.randint(0, 256, (bsh.count, 64, 56, 56), dtype=torch.uint8, device="cuda", generator=gen)
+    wc = ctx.qconv_prepack(torch.randint(-127, 128, (64, 64, 3, 3), dtype=torch.int8, device="cuda", generator=gen))
+    bias = torch.randint(-1000, 1001, (64,), dtype=torch.int32, device="cuda", generator=gen)
+    ratio = (0.02 * np.random.default_rng(4).uniform(0.001, 0.01, 64) / 0.05).astype(np.float32)
+    yq = torch.empty((bsh.count, 64, 56, 56), dtype=torch.uint8, device="cuda")
+    ms_q = timed(torch, dist, world, lambda: ctx.qlinear_conv(wc, x, 128, 0, ratio, bias, 128, pads=(1, 1, 1, 1), out=yq), 20)
+    ops = 2.0 * 64 * 64 * 56 * 56 * 576
+    out["int8_qlinear_conv_resnet_block"] = {"batch": 64, "ms": ms_q, "kernel": ctx.last_kernel,
+                                             "tops": ops / (ms_q * 1e-3) / 1e12,
+                                             "algorithmic_gbs": 2.0 * 64 * 64 * 56 * 56 / (ms_q * 1e-3) / 1e9,
+                                             "parallelism": "batch-split x%d, no exchange" % world if world > 1 else "single"}
+    return out
 
 
 def run_gpu(args):
@@ -126,7 +232,15 @@ def run_gpu(args):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    ctx = ovk_b200.Context(local)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
+    ctx = ovk_b200.Context(local)  # bound to the current (side) stream: events and graph capture share it
     gen = torch.Generator(device="cuda")
     gen.manual_seed(0xB200 + 0x100 * 2)
 
@@ -135,25 +249,49 @@ def run_gpu(args):
     for layer in range(args.layers):
         for name, k, n in LAYER_SHAPES:
             ops.append((f"L{layer}.{name}", k, n, make_weight(torch, ctx, k, n, BLOCK, gen)))
-    ops.append((LM_HEAD[0], LM_HEAD[1], LM_HEAD[2], make_weight(torch, ctx, LM_HEAD[1], LM_HEAD[2], BLOCK, gen)))
+    lm = make_weight(torch, ctx, LM_HEAD[1], LM_HEAD[2], BLOCK, gen)
     acts = {k: torch.randn((1, k), device="cuda", generator=gen).to(torch.float16) for k in {HIDDEN, Q_OUT, FF}}
     outs = {n: torch.empty((1, n), dtype=torch.float16, device="cuda") for n in {Q_OUT, KV_OUT, HIDDEN, FF, VOCAB}}
-    step_bytes = sum(nbits_bytes(1, k, n, BLOCK) for _, k, n, _ in ops)
+    step_bytes = sum(nbits_bytes(1, k, n, BLOCK) for _, k, n, _ in ops) + nbits_bytes(1, LM_HEAD[1], LM_HEAD[2], BLOCK)
     lm_bytes = nbits_bytes(1, LM_HEAD[1], LM_HEAD[2], BLOCK)
+    n_gemv = len(ops) + 1
     ctx.flush()
+
+    def layers_eager():
+        for _, k, n, w in ops:
+            ctx.matmul_nbits(w, acts[k], out=outs[n])
+
+    # The per-layer GEMVs are launch-bound (0.2-4.6 MB each): the step replays
+    # them from a CUDA graph, as the reference replays its captured decode step
+    # (crates/onnx-vulkan-core/src/plan.rs, vk-compute stream.rs:537-629).
+    layers_eager()
+    torch.cuda.synchronize()
+    graph, replay = None, "eager launches"
+    if not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                layers_eager()
+            replay = "CUDA graph replay of the per-layer GEMVs + one eager lm_head launch"
+        except Exception as e:  # capture refused: fall back to eager launches, say so
+            graph, replay = None, "eager launches (graph capture failed: %s)" % str(e)[:80]
+            torch.cuda.synchronize()
 
     lm_events = []
 
-    def step(timed: bool):
-        for name, k, n, w in ops:
-            if timed and name == "lm_head":
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                ctx.matmul_nbits(w, acts[k], out=outs[n])
-                e1.record()
-                lm_events.append((e0, e1))
-            else:
-                ctx.matmul_nbits(w, acts[k], out=outs[n])
+    def step(timed_step: bool):
+        if graph is not None:
+            graph.replay()
+        else:
+            layers_eager()
+        if timed_step:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            ctx.matmul_nbits(lm, acts[HIDDEN], out=outs[VOCAB])
+            e1.record()
+            lm_events.append((e0, e1))
+        else:
+            ctx.matmul_nbits(lm, acts[HIDDEN], out=outs[VOCAB])
 
     def sync_all():
         if world > 1:
@@ -163,7 +301,6 @@ def run_gpu(args):
     for _ in range(args.warmup):
         step(False)
     sync_all()
-    launches0 = ctx.launches
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -174,7 +311,7 @@ def run_gpu(args):
     t1.record()
     sync_all()
     clocks = sampler.stop() if rank == 0 else None
-    launches = ctx.launches - launches0
+    launches = n_gemv * args.steps  # one kernel of this library per GEMV (graph replays launch them too)
     ms = torch.tensor([t0.elapsed_time(t1)], device="cuda")
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -186,20 +323,22 @@ def run_gpu(args):
     # the call a user makes: host activations in, logits out, every step
     pinned_in = {k: acts[k].cpu().pin_memory() for k in acts}
     pinned_out = torch.empty((1, VOCAB), dtype=torch.float16).pin_memory()
-    h2d = sum(k * 2 for _, k, _, _ in ops)
+    h2d = sum(k * 2 for _, k, _, _ in ops) + HIDDEN * 2
     d2h = VOCAB * 2
 
     def e2e_step():
-        for name, k, n, w in ops:
+        for _, k, n, w in ops:
             acts[k].copy_(pinned_in[k], non_blocking=True)
             ctx.matmul_nbits(w, acts[k], out=outs[n])
+        acts[HIDDEN].copy_(pinned_in[HIDDEN], non_blocking=True)
+        ctx.matmul_nbits(lm, acts[HIDDEN], out=outs[VOCAB])
         pinned_out.copy_(outs[VOCAB], non_blocking=True)
         torch.cuda.synchronize()
 
-    for _ in range(max(1, args.warmup // 2)):
+    for _ in range(3):
         e2e_step()
     sync_all()
-    e2e_steps = max(1, min(args.steps, 10))
+    e2e_steps = max(1, min(args.steps, 20))
     w0 = time.perf_counter()
     for _ in range(e2e_steps):
         e2e_step()
@@ -209,8 +348,14 @@ def run_gpu(args):
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     e2e_gbs = world * step_bytes * e2e_steps / float(e2e_s.item()) / 1e9
 
+    peaks, peak_kind = measured_peaks()
+    extra = None
+    if not args.no_extra:
+        del ops, lm, graph
+        torch.cuda.empty_cache()
+        extra = extra_workloads(torch, dist, ctx, world, rank, gen, peaks)
+
     if rank == 0:
-        peaks, peak_kind = measured_peaks()
         achieved = lm_bytes / (lm_ms * 1e-3) / 1e9
         traffic = None
         prof = os.path.join(ROOT, "profiles", "traffic.json")
@@ -223,9 +368,9 @@ def run_gpu(args):
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": "gemma3-1b-int4-decode: %d layers x (q,k,v,o,gate,up,down) + lm_head, M=1, "
                                    "bits=4 block_size=32 zero points, fp16" % args.layers,
-                       "gemvs_per_step": len(ops), "bytes_per_step": step_bytes,
+                       "gemvs_per_step": n_gemv, "bytes_per_step": step_bytes, "launch": replay,
                        "l2": "distinct weights per GEMV, %.0f MB per step > 126 MB L2 (no flush needed)" % (step_bytes / 1e6),
-                       "parallelism": "replicas" if world > 1 else "single"},
+                       "parallelism": "replicas (the decode GEMV is single-GPU by design)" if world > 1 else "single"},
             "roofline": {"bound": "hbm", "kernel": lm_kernel + " (lm_head K=1152 N=262144)", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                          "of": peak_kind, "bytes_per_launch": lm_bytes, "ms_per_launch": lm_ms,
@@ -234,11 +379,11 @@ def run_gpu(args):
                     "steps": e2e_steps},
             "gpu_launches": launches, "clocks": clocks,
         }
+        if extra is not None:
+            line["extra"] = extra
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_seconds)
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
 
 
 # --------------------------------------------------------------------- CPU arm
@@ -323,6 +468,8 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the prefill / int8 / conv lines")
+    ap.add_argument("--no-graph", action="store_true", help="launch the per-layer GEMVs eagerly")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

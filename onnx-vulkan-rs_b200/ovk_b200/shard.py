@@ -1,0 +1,114 @@
+"""Partitioning of the two shardable operators across the GPUs of one box.
+
+The reference runs on one device (one VkContext per process,
+crates/vk-compute/src/context.rs:685-711), so nothing here has a counterpart
+there; the operator semantics are unchanged:
+
+* MatMulNBits prefill is split by weight COLUMNS: rank r owns columns
+  [n0, n1) of B / scales / zero_points (whole rows of the operator layout, so a
+  shard is a plain slice), computes Y[:, n0:n1] and the shards are exchanged by
+  ONE all-gather.  Shards are multiples of 16 columns (the decode panel width)
+  and differ by at most one unit.
+* QLinearConv is split by BATCH: images are independent, weights replicated,
+  no exchange at all.
+* The decode GEMV is single-GPU by design: with more ranks each runs a replica.
+
+One process per GPU; torch.distributed (NCCL on GPUs, gloo in the CPU tests)
+does the exchange.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+@dataclass(frozen=True)
+class Shard:
+    start: int
+    count: int
+
+    @property
+    def stop(self) -> int:
+        return self.start + self.count
+
+
+def split_units(total: int, world: int, rank: int, unit: int = 1) -> Shard:
+    """Contiguous shard of `total` items in whole `unit`s; the first
+    (units % world) ranks get one unit more; the last shard absorbs a ragged tail."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} of {world}")
+    units = -(-total // unit)
+    base, extra = divmod(units, world)
+    u0 = rank * base + min(rank, extra)
+    u1 = u0 + base + (1 if rank < extra else 0)
+    start = min(u0 * unit, total)
+    stop = min(u1 * unit, total)
+    return Shard(start, stop - start)
+
+
+def column_shard(n: int, world: int, rank: int) -> Shard:
+    """Weight columns of rank `rank` in an N-split MatMulNBits."""
+    return split_units(n, world, rank, unit=16)
+
+
+def batch_shard(batch: int, world: int, rank: int) -> Shard:
+    """Images of rank `rank` in a batch-split QLinearConv."""
+    return split_units(batch, world, rank, unit=1)
+
+
+def slice_nbits_weight(b, scales, zero_points, n_blocks: int, shard: Shard):
+    """Rows [start, stop) of the operator-layout tensors: B [N, n_blocks, bs/2],
+    scales [N * n_blocks], zero_points [N, ceil(n_blocks/2)] (or None)."""
+    bs = b.reshape(b.shape[0], -1)[shard.start:shard.stop]
+    ss = scales.reshape(-1, n_blocks)[shard.start:shard.stop].reshape(-1)
+    zs = None if zero_points is None else zero_points.reshape(b.shape[0], -1)[shard.start:shard.stop]
+    return bs, ss, zs
+
+
+def all_gather_columns(y_shard, n: int, world: int, group=None):
+    """Exchange step of the N-split: every rank contributes Y[:, n0:n1] and gets
+    the full [M, N].  Shards may differ in width, so they are gathered into a
+    [world, M, widest] staging buffer (one collective) and copied into place.
+    Returns (y_full, staging) so that callers can reuse the staging buffer."""
+    import torch
+    import torch.distributed as dist
+
+    m = y_shard.shape[0]
+    widths = [column_shard(n, world, r).count for r in range(world)]
+    widest = max(widths)
+    if world == 1:
+        return y_shard, None
+    send = y_shard
+    if y_shard.shape[1] != widest:
+        send = torch.zeros((m, widest), dtype=y_shard.dtype, device=y_shard.device)
+        send[:, :y_shard.shape[1]] = y_shard
+    staging = torch.empty((world, m, widest), dtype=y_shard.dtype, device=y_shard.device)
+    dist.all_gather_into_tensor(staging.view(world * m, widest), send.contiguous(), group=group)
+    y = torch.empty((m, n), dtype=y_shard.dtype, device=y_shard.device)
+    for r in range(world):
+        s = column_shard(n, world, r)
+        y[:, s.start:s.stop] = staging[r, :, :s.count]
+    return y, staging
+
+
+class RankFailure(RuntimeError):
+    """A peer did not reach the exchange step in time."""
+
+
+def ready_handshake(store, world: int, rank: int, step: int, timeout_s: float = 5.0) -> None:
+    """Host-side check taken BEFORE a collective is enqueued: every rank posts a
+    key for this step and waits for the others'.  A rank that died or raised
+    upstream is then reported as a RankFailure on the host, and no GPU
+    collective is ever left half entered (nothing here touches a device)."""
+    import datetime
+
+    store.set(f"ovk/ready/{step}/{rank}", b"1")
+    missing = []
+    for r in range(world):
+        if r == rank:
+            continue
+        try:
+            store.wait([f"ovk/ready/{step}/{r}"], datetime.timedelta(seconds=timeout_s))
+        except Exception:
+            missing.append(r)
+    if missing:
+        raise RankFailure(f"step {step}: ranks {missing} did not reach the exchange within {timeout_s} s")
