@@ -136,6 +136,26 @@ OVK_API void ovk_mmi_weight_destroy(ovk_ctx *ctx, ovk_mmi_weight *w);
 OVK_API int32_t ovk_matmul_integer(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a,
                                    int32_t a_signed, int64_t m, const void *a_zp,
                                    const void *b_zp, int32_t *out);
+/* The same product for callers that must not allocate device memory (this
+ * entry point has no counterpart in the reference).  ovk_matmul_integer keeps
+ * the row sums it needs for a non-zero weight zero point in the context's
+ * workspace, which grows with cudaMallocAsync on demand; hosts that hand out
+ * every device byte from their own arena, or that cannot take an allocation
+ * (and the synchronisation it may bring) inside a request, call this instead.
+ * The row sums then live in a fixed array of 65536 int32 (256 KB) that is part
+ * of the library image on every GPU that loads it.  It calls no cudaMalloc,
+ * cudaFree or allocating library routine.
+ *  - m above 65536 rows is refused with OVK_INVALID_ARGUMENT;
+ *  - the first call on a device looks up the array's device address
+ *    (cudaGetSymbolAddress); make that first call before any stream capture;
+ *  - all calls share the one array: calls whose kernels may overlap on the GPU
+ *    (different streams or contexts) race on it - serialise them.  The array
+ *    keeps the previous call's row sums; they are rewritten before they are
+ *    read, so nothing has to be cleared.
+ * Results are identical to ovk_matmul_integer. */
+OVK_API int32_t ovk_matmul_integer_static_scratch(ovk_ctx *ctx, const ovk_mmi_weight *w,
+                                                  const void *a, int32_t a_signed, int64_t m,
+                                                  const void *a_zp, const void *b_zp, int32_t *out);
 /* interp::matmul_integer_scale_bias (interp.rs:2405-2572): the fused
  * MatMulInteger -> Cast -> Mul -> Add [-> Relu] node,
  *   out = fl(fl(float(acc) * s) + bias),  s = scale or fl(scale * product),

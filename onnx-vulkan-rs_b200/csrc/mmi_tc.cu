@@ -317,3 +317,87 @@ int32_t ovk_mmi_tc_launch(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, 
         return launch<128>(ctx, tmA, w, p);
     return launch<64>(ctx, tmA, w, p);
 }
+
+// ---------------------------------------------------------------------------
+// MatMulInteger for callers that may not allocate device memory.
+//
+// Some hosts hand out all device memory themselves (an inference runtime whose
+// plugin must take every byte from the runtime's own arena, an embedded
+// serving loop with a fixed memory plan) or cannot afford the device-wide
+// synchronisation an allocation may imply in the middle of a latency-critical
+// request.  For them the one piece of scratch this operator needs - the row
+// sums of A that enter the zero-point correction when the weight's zero point
+// is not 0 - lives in a fixed array inside the library image instead of the
+// context's grow-on-demand workspace.  Every GPU that loads the library holds
+// these 256 KB until the process exits.
+constexpr int64_t OVK_STATIC_ROWS = 65536;  // most rows of A one call may bring
+static __device__ __align__(256) int32_t g_static_rowsum[OVK_STATIC_ROWS];
+
+namespace {
+constexpr int OVK_MAX_DEVICES = 64;
+int32_t *g_static_rowsum_addr[OVK_MAX_DEVICES] = {};  // device address of the array, per device
+}  // namespace
+
+extern "C" int32_t ovk_matmul_integer_static_scratch(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a,
+                                                     int32_t a_signed, int64_t m, const void *a_zp,
+                                                     const void *b_zp, int32_t *out)
+{
+    if (!ctx || !w)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "MatMulInteger (static scratch): null argument");
+    OVK_REQUIRE(ctx, m >= 0, "MatMulInteger (static scratch): %lld rows of A", (long long)m);
+    OVK_REQUIRE(ctx, m <= OVK_STATIC_ROWS,
+                "MatMulInteger (static scratch): %lld rows of A exceed the fixed scratch of %lld rows; "
+                "split the call or use ovk_matmul_integer",
+                (long long)m, (long long)OVK_STATIC_ROWS);
+    if (m == 0 || w->n == 0)
+        return OVK_OK;
+    OVK_REQUIRE(ctx, a && out, "MatMulInteger (static scratch): A or the output is null");
+    OVK_REFUSE(ctx, w->k > 33025, "MatMulInteger (static scratch): K=%lld could overflow the int32 accumulator",
+               (long long)w->k);
+    OVK_REQUIRE(ctx, ctx->device >= 0 && ctx->device < OVK_MAX_DEVICES, "MatMulInteger (static scratch): device %d",
+                ctx->device);
+    OVK_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (!ovk_mmi_tc_applies(ctx, w, a, m))
+        return ovk_matmul_integer(ctx, w, a, a_signed, m, a_zp, b_zp, out);  // one output per thread: no scratch at all
+    // Set-up, once per device, with that device current: in host code the
+    // array's name is only a stand-in, the kernels need its device address.
+    if (!g_static_rowsum_addr[ctx->device]) {
+        void *addr = nullptr;
+        OVK_CUDA(ctx, cudaGetSymbolAddress(&addr, g_static_rowsum));
+        g_static_rowsum_addr[ctx->device] = static_cast<int32_t *>(addr);
+    }
+    int32_t *rowsum = g_static_rowsum_addr[ctx->device];
+    TcParams p = {};
+    p.M = m;
+    p.N = int(w->n);
+    p.K = int(w->k);
+    p.num_kb = int(ceil_div64(w->k, BK));
+    p.colsum = w->colsum;
+    p.a_zp = a_zp;
+    p.b_zp = b_zp;
+    p.a_signed = a_signed ? 1 : 0;
+    p.b_signed = w->b_signed;
+    p.epi = EpiParams{};
+    p.epi.mode = EPI_RAW;
+    p.out = out;
+    p.vec_ok = (w->n % 4) == 0 && aligned_to(out, 16);
+    p.status = ctx->dev_status;
+    if (b_zp) {
+        // rows [0, m) are rewritten whenever the zero point is not 0, and read only then:
+        // nothing left over from an earlier call is ever used, so nothing needs clearing
+        p.rowsum = rowsum;
+        mmi_rowsum_kernel<<<unsigned(ceil_div64(m * 32, 256)), 256, 0, ctx->stream>>>(
+            static_cast<const uint8_t *>(a), m, p.K, p.a_signed, b_zp, p.b_signed, rowsum);
+        OVK_LAUNCHED(ctx, "mmi_rowsum");
+    }
+    CUtensorMap tmA;
+    if (!ovk_make_tmap_2d(&tmA, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(w->k), uint64_t(m), uint64_t(w->k), BK,
+                          BM, CU_TENSOR_MAP_SWIZZLE_128B))
+        return ovk_fail(ctx, OVK_BACKEND, "MatMulInteger (static scratch): cuTensorMapEncodeTiled failed for A");
+    const int64_t mt = ceil_div64(m, BM);
+    if (w->n >= 256 && mt * ceil_div64(w->n, 256) >= ctx->sm_count)
+        return launch<256>(ctx, tmA, w, p);
+    if (w->n >= 128 && mt * ceil_div64(w->n, 128) >= ctx->sm_count)
+        return launch<128>(ctx, tmA, w, p);
+    return launch<64>(ctx, tmA, w, p);
+}

@@ -63,6 +63,7 @@ SIGNATURES = {
     "ovk_mmi_prepack": (_I32, [_P, _P, _I32, _I64, _I64, C.POINTER(_P)]),
     "ovk_mmi_weight_destroy": (None, [_P, _P]),
     "ovk_matmul_integer": (_I32, [_P, _P, _P, _I32, _I64, _P, _P, _P]),
+    "ovk_matmul_integer_static_scratch": (_I32, [_P, _P, _P, _I32, _I64, _P, _P, _P]),
     "ovk_matmul_integer_scale_bias": (_I32, [_P, _P, _P, _I32, _I64, _P, _P, _P, _I32, _P, _I32, _P,
                                              _I32, _U32, _P, _P]),
     "ovk_qlinear_matmul": (_I32, [_P, _P, _P, _I32, _I64, _P, _P, _P, _I64, _I32, _I32, _P]),
@@ -186,6 +187,18 @@ class Context:
         out = torch.empty(tuple(a.shape[:-1]) + (w.n,), dtype=torch.int32, device=a.device)
         self.check(lib().ovk_matmul_integer(self.h, w.h, _ptr(a), int(a.dtype == torch.int8), m,
                                             _ptr(a_zp), _ptr(b_zp), _ptr(out)))
+        return out
+
+    def matmul_integer_static_scratch(self, w: "MmiWeight", a, a_zp=None, b_zp=None, out=None):
+        """MatMulInteger through the entry point that allocates nothing: for hosts
+        that own all device memory themselves.  `out` must be supplied by such a
+        caller; it is created here only as a convenience for tests."""
+        import torch
+        m = a.numel() // max(w.k, 1)
+        if out is None:
+            out = torch.empty(tuple(a.shape[:-1]) + (w.n,), dtype=torch.int32, device=a.device)
+        self.check(lib().ovk_matmul_integer_static_scratch(self.h, w.h, _ptr(a), int(a.dtype == torch.int8), m,
+                                                           _ptr(a_zp), _ptr(b_zp), _ptr(out)))
         return out
 
     def matmul_integer_scale_bias(self, w: "MmiWeight", a, a_zp, b_zp, scale, bias, product=None,
