@@ -386,6 +386,40 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
         print(json.dumps(line), flush=True)
 
 
+def run_one(which):
+    """One operator, three launches, no timing: a bounded target for ncu."""
+    import numpy as np
+    import torch
+    import ovk_b200
+    torch.cuda.set_device(0)
+    ctx = ovk_b200.Context(0)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0xB200)
+    if which == "lm_head":
+        w = make_weight(torch, ctx, HIDDEN, VOCAB, BLOCK, gen)
+        a = torch.randn((1, HIDDEN), device="cuda", generator=gen).to(torch.float16)
+        fn = lambda: ctx.matmul_nbits(w, a)
+    elif which == "prefill":
+        w = make_weight(torch, ctx, 3584, 18944, 128, gen, 0.001, 0.01)
+        a = torch.randn((1024, 3584), device="cuda", generator=gen).to(torch.float16)
+        fn = lambda: ctx.matmul_nbits(w, a)
+    elif which == "int8":
+        w = ctx.mmi_prepack(torch.randint(-127, 128, (4096, 4096), dtype=torch.int8, device="cuda", generator=gen))
+        a = torch.randint(0, 256, (4096, 4096), dtype=torch.uint8, device="cuda", generator=gen)
+        zp = torch.full((1,), 128, dtype=torch.uint8, device="cuda")
+        fn = lambda: ctx.matmul_integer(w, a, zp, None)
+    else:
+        w = ctx.qconv_prepack(torch.randint(-127, 128, (64, 64, 3, 3), dtype=torch.int8, device="cuda", generator=gen))
+        x = torch.randint(0, 256, (64, 64, 56, 56), dtype=torch.uint8, device="cuda", generator=gen)
+        bias = torch.zeros((64,), dtype=torch.int32, device="cuda")
+        ratio = np.full(64, 0.002, dtype=np.float32)
+        fn = lambda: ctx.qlinear_conv(w, x, 128, 0, ratio, bias, 128, pads=(1, 1, 1, 1))
+    for _ in range(3):
+        fn()
+    ctx.flush()
+    print("ran", which, ctx.last_kernel)
+
+
 # --------------------------------------------------------------------- CPU arm
 
 def cpu_sample(n_cols):
@@ -470,9 +504,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the prefill / int8 / conv lines")
     ap.add_argument("--no-graph", action="store_true", help="launch the per-layer GEMVs eagerly")
+    ap.add_argument("--one", default=None, choices=["lm_head", "prefill", "int8", "conv"],
+                    help="run one operator three times and exit (small target for an ncu capture)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.one:
+        run_one(args.one)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)

@@ -204,93 +204,8 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
         umma::fence_barrier_init();
     }
 
-    // ---- activations -> shared memory, in the order the fragments are read
-    // unit (row, group, t): k = 32*group + 8*t + {0,4,1,5,2,6,3,7}
-    if constexpr (A_F32) {
-        const float *a = static_cast<const float *>(p.a);
-        __shared__ float warp_max[THREADS / 32];
-        for (int m = 0; m < p.M; m++) {
-            float mx = 0.0f;
-            for (int k = threadIdx.x; k < p.K; k += THREADS)
-                mx = fmaxf(mx, fabsf(a[int64_t(m) * p.K + k]));
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1)
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            if (lane == 0)
-                warp_max[warp] = mx;
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                for (int w = 1; w < THREADS / 32; w++)
-                    mx = fmaxf(mx, warp_max[w]);
-                int e = 0;
-                if (mx > 0.0f && mx < 3.0e38f)
-                    frexpf(mx, &e);
-                e = max(-100, min(100, e));
-                row_pow2[m] = ldexpf(1.0f, e);
-            }
-            __syncthreads();
-        }
-        const int units = p.M * p.g_pad * 4;
-        for (int u = threadIdx.x; u < units; u += THREADS) {
-            const int t = u & 3, grp = (u >> 2) % p.g_pad, m = (u >> 2) / p.g_pad;
-            const float inv = 1.0f / row_pow2[m];  // exact power of two
-            float hi[8], lo[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const int k = grp * 32 + t * 8 + i;
-                const float v = k < p.K ? a[int64_t(m) * p.K + k] * inv : 0.0f;
-                const float h = __half2float(__float2half_rn(v));
-                hi[i] = h;
-                lo[i] = v - h;
-            }
-            acts[(size_t(2 * m) * p.g_pad + grp) * 4 + t] =
-                make_uint4(pack_h2(hi[0], hi[4]), pack_h2(hi[1], hi[5]), pack_h2(hi[2], hi[6]), pack_h2(hi[3], hi[7]));
-            acts[(size_t(2 * m + 1) * p.g_pad + grp) * 4 + t] =
-                make_uint4(pack_h2(lo[0], lo[4]), pack_h2(lo[1], lo[5]), pack_h2(lo[2], lo[6]), pack_h2(lo[3], lo[7]));
-        }
-    } else {
-        const __half *a = static_cast<const __half *>(p.a);
-        const int units = p.M * p.g_pad * 4;
-        for (int u = threadIdx.x; u < units; u += THREADS) {
-            const int t = u & 3, grp = (u >> 2) % p.g_pad, m = (u >> 2) / p.g_pad;
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const int k = grp * 32 + t * 8 + i;
-                v[i] = k < p.K ? __half2float(a[int64_t(m) * p.K + k]) : 0.0f;
-            }
-            acts[(size_t(m) * p.g_pad + grp) * 4 + t] =
-                make_uint4(pack_h2(v[0], v[4]), pack_h2(v[1], v[5]), pack_h2(v[2], v[6]), pack_h2(v[3], v[7]));
-        }
-    }
-    __syncthreads();
-    {
-        // block sums of the staged (fp16) activations, negated and split in three
-        const int nblk = p.g_pad / GBT;
-        const __half *ah = reinterpret_cast<const __half *>(acts);
-        for (int u = warp; u < p.rows * nblk; u += THREADS / 32) {
-            const int row = u / nblk, blk = u % nblk;
-            const __half *src = ah + (size_t(row) * p.g_pad + size_t(blk) * GBT) * 32;
-            double sum = 0.0;  // exact: fp16 terms span fewer than 53 bits
-#pragma unroll
-            for (int i = 0; i < GBT; i++)
-                sum += double(__half2float(src[i * 32 + lane]));
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1)
-                sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (lane == 0) {
-                const __half h0 = __double2half(sum);
-                const double r1 = sum - double(__half2float(h0));
-                const __half h1 = __double2half(r1);
-                const __half h2 = __double2half(r1 - double(__half2float(h1)));
-                uint32_t *dst = corr + size_t(u) * 4;
-                dst[0] = uint32_t(__half_as_ushort(__hneg(h0)));
-                dst[1] = uint32_t(__half_as_ushort(__hneg(h1)));
-                dst[2] = uint32_t(__half_as_ushort(__hneg(h2)));
-                dst[3] = 0u;
-            }
-        }
-    }
+    // barriers visible to everyone, then the producer starts streaming weights at once:
+    // the first tiles are in flight while the consumer warps stage the activations
     __syncthreads();
 
     if (warp == CONSUMER_WARPS) {
@@ -326,6 +241,95 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
         }
         return;
     }
+
+    // ---- activations -> shared memory, in the order the fragments are read
+    // unit (row, group, t): k = 32*group + 8*t + {0,4,1,5,2,6,3,7}
+    if constexpr (A_F32) {
+        const float *a = static_cast<const float *>(p.a);
+        __shared__ float warp_max[CONSUMER_WARPS];
+        for (int m = 0; m < p.M; m++) {
+            float mx = 0.0f;
+            for (int k = threadIdx.x; k < p.K; k += CONSUMER_WARPS * 32)
+                mx = fmaxf(mx, fabsf(a[int64_t(m) * p.K + k]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            if (lane == 0)
+                warp_max[warp] = mx;
+            asm volatile("bar.sync 2, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
+            if (threadIdx.x == 0) {
+                for (int w = 1; w < CONSUMER_WARPS; w++)
+                    mx = fmaxf(mx, warp_max[w]);
+                int e = 0;
+                if (mx > 0.0f && mx < 3.0e38f)
+                    frexpf(mx, &e);
+                e = max(-100, min(100, e));
+                row_pow2[m] = ldexpf(1.0f, e);
+            }
+            asm volatile("bar.sync 2, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
+        }
+        const int units = p.M * p.g_pad * 4;
+        for (int u = threadIdx.x; u < units; u += CONSUMER_WARPS * 32) {
+            const int t = u & 3, grp = (u >> 2) % p.g_pad, m = (u >> 2) / p.g_pad;
+            const float inv = 1.0f / row_pow2[m];  // exact power of two
+            float hi[8], lo[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int k = grp * 32 + t * 8 + i;
+                const float v = k < p.K ? a[int64_t(m) * p.K + k] * inv : 0.0f;
+                const float h = __half2float(__float2half_rn(v));
+                hi[i] = h;
+                lo[i] = v - h;
+            }
+            acts[(size_t(2 * m) * p.g_pad + grp) * 4 + t] =
+                make_uint4(pack_h2(hi[0], hi[4]), pack_h2(hi[1], hi[5]), pack_h2(hi[2], hi[6]), pack_h2(hi[3], hi[7]));
+            acts[(size_t(2 * m + 1) * p.g_pad + grp) * 4 + t] =
+                make_uint4(pack_h2(lo[0], lo[4]), pack_h2(lo[1], lo[5]), pack_h2(lo[2], lo[6]), pack_h2(lo[3], lo[7]));
+        }
+    } else {
+        const __half *a = static_cast<const __half *>(p.a);
+        const int units = p.M * p.g_pad * 4;
+        for (int u = threadIdx.x; u < units; u += CONSUMER_WARPS * 32) {
+            const int t = u & 3, grp = (u >> 2) % p.g_pad, m = (u >> 2) / p.g_pad;
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int k = grp * 32 + t * 8 + i;
+                v[i] = k < p.K ? __half2float(a[int64_t(m) * p.K + k]) : 0.0f;
+            }
+            acts[(size_t(m) * p.g_pad + grp) * 4 + t] =
+                make_uint4(pack_h2(v[0], v[4]), pack_h2(v[1], v[5]), pack_h2(v[2], v[6]), pack_h2(v[3], v[7]));
+        }
+    }
+    asm volatile("bar.sync 2, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
+    {
+        // block sums of the staged (fp16) activations, negated and split in three
+        const int nblk = p.g_pad / GBT;
+        const __half *ah = reinterpret_cast<const __half *>(acts);
+        for (int u = warp; u < p.rows * nblk; u += CONSUMER_WARPS) {
+            const int row = u / nblk, blk = u % nblk;
+            const __half *src = ah + (size_t(row) * p.g_pad + size_t(blk) * GBT) * 32;
+            double sum = 0.0;  // exact: fp16 terms span fewer than 53 bits
+#pragma unroll
+            for (int i = 0; i < GBT; i++)
+                sum += double(__half2float(src[i * 32 + lane]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) {
+                const __half h0 = __double2half(sum);
+                const double r1 = sum - double(__half2float(h0));
+                const __half h1 = __double2half(r1);
+                const __half h2 = __double2half(r1 - double(__half2float(h1)));
+                uint32_t *dst = corr + size_t(u) * 4;
+                dst[0] = uint32_t(__half_as_ushort(__hneg(h0)));
+                dst[1] = uint32_t(__half_as_ushort(__hneg(h1)));
+                dst[2] = uint32_t(__half_as_ushort(__hneg(h2)));
+                dst[3] = 0u;
+            }
+        }
+    }
+    asm volatile("bar.sync 2, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
 
     // ---------------------------------------------------------------- consumers
     const int g = lane >> 2, t = lane & 3;
