@@ -12,30 +12,34 @@
 // weights instead would round every weight and fail the 1e-3 tolerance at
 // large K.
 //
-// One CTA computes 128 weight columns (UMMA M) x 128 tokens (UMMA N):
-//   warp 0      TMA: token tiles [128 x 64 k] fp16 into a 128B-swizzled ring,
+// One CTA computes 128 weight columns (UMMA M) x 256 tokens (UMMA N), so every
+// unpacked weight tile is used by 256 tokens:
+//   warp 0      TMA: token tiles [256 x 64 k] fp16 into a 128B-swizzled ring,
 //               plus the packed nibbles of the same slab [128 rows x 32 bytes]
 //   warp 1      tcgen05.mma kind::f16, four K=16 steps per 64-k slab, one
-//               tensor-memory accumulator per quantization block (ring of 4)
-//   warps 2-5   unpack: thread r owns weight row r of the tile; 32 bytes of
+//               tensor-memory accumulator (256 columns) per quantization block,
+//               two in flight
+//   warps 4-7   unpack: thread r owns weight row r of the tile; 32 bytes of
 //               nibbles per slab -> 64 fp16 integers -> the swizzled operand stage
-//   warps 6-13  promotion: tcgen05.ld a block's partial sums (one weight column
-//               per thread, 64 tokens per warp), acc += partial * scale[n, block]
+//   warps 8-15  promotion: tcgen05.ld a block's partial sums (one weight column
+//               per thread, 128 tokens per warp), acc += partial * scale[n, block]
 //               in registers, final store of Y
 // Weight columns sit on tensor-memory LANES so the scale is one scalar per thread.
+// The promotion warps hold 128 accumulators each: the register file is
+// re-divided between the warpgroups with setmaxnreg.
 #include "ovk_internal.h"
 #include "umma.cuh"
 
 namespace {
 
 constexpr int BW = 128;    // weight columns per tile (UMMA M)
-constexpr int BT = 128;    // tokens per tile (UMMA N)
+constexpr int BT = 256;    // tokens per tile (UMMA N)
 constexpr int SLAB = 64;   // k per stage: 128 bytes of fp16
-constexpr int STAGES = 6;
-constexpr int ACC_RING = 4;
+constexpr int STAGES = 4;
+constexpr int ACC_RING = 2;
 constexpr int A_BYTES = BW * 128, B_BYTES = BT * 128;
 constexpr int RAW_BYTES = BW * 32;  // packed nibbles of one slab: 32 bytes per weight row
-constexpr int THREADS = 14 * 32;
+constexpr int THREADS = 16 * 32;  // four warpgroups: control, unpack, promotion x2
 constexpr long long WAIT_CYCLES = 2000000000ll;
 
 struct GemmParams {
@@ -66,6 +70,22 @@ __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
     }
 }
 
+// For warps that wait on someone else's progress: the hardware parks the
+// thread (up to a microsecond per attempt) instead of letting it spin in the
+// issue slots of the warp that feeds the tensor core.
+__device__ __forceinline__ bool wait_parked(uint64_t *bar, uint32_t parity)
+{
+    if (umma::mbar_try_wait(bar, parity))
+        return true;
+    const long long t0 = clock64();
+    for (;;) {
+        if (umma::mbar_try_wait_hint(bar, parity, 1000u))
+            return true;
+        if (clock64() - t0 > WAIT_CYCLES)
+            return false;
+    }
+}
+
 __device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b)
 {
     __half2 r = __hsub2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
@@ -87,14 +107,24 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint4 v)
 }
 
 // eight nibbles of a permuted word -> 8 fp16 integers (nibble - z), k ascending
-__device__ __forceinline__ uint4 unpack8(uint32_t w, uint32_t c_lo, uint32_t c_hi)
+struct UnpackConsts {
+    uint32_t m_lo, m_hi, k_lo, k_hi;  // 0x000F000F, 0x00F000F0, 0x64006400, 0x54005400 held in registers
+};
+// (a & b) | c with all operands in registers: one LOP3
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c)
+{
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint4 unpack8(uint32_t w, uint32_t c_lo, uint32_t c_hi, const UnpackConsts &u)
 {
     const uint32_t w8 = w >> 8;
     uint4 o;
-    o.x = h2_sub((w & 0x000F000Fu) | 0x64006400u, c_lo);
-    o.y = h2_sub((w & 0x00F000F0u) | 0x54005400u, c_hi);
-    o.z = h2_sub((w8 & 0x000F000Fu) | 0x64006400u, c_lo);
-    o.w = h2_sub((w8 & 0x00F000F0u) | 0x54005400u, c_hi);
+    o.x = h2_sub(and_or(w, u.m_lo, u.k_lo), c_lo);
+    o.y = h2_sub(and_or(w, u.m_hi, u.k_hi), c_hi);
+    o.z = h2_sub(and_or(w8, u.m_lo, u.k_lo), c_lo);
+    o.w = h2_sub(and_or(w8, u.m_hi, u.k_hi), c_hi);
     return o;
 }
 
@@ -140,6 +170,10 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
     const int blocks_per_slab = p.bs >= SLAB ? 1 : SLAB / p.bs;  // 2 when block_size is 32
     const int slabs_per_block = p.bs >= SLAB ? p.bs / SLAB : 1;
 
+    // 512 threads x 128 registers fill the register file; control and unpack warps give
+    // registers back, the promotion warps take them (56*128 + 88*128 + 184*256 = 65536)
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 0) {
         // ------------------------------------------------------------ tokens by TMA
         if (lane == 0) {
@@ -151,7 +185,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                 const int n0 = (tile / p.m_tiles) * BW;
                 for (int sl = 0; sl < p.slabs; sl++, seq++) {
                     const int s = seq % STAGES;
-                    if (!wait_bounded(&empty[s], ((seq / STAGES) & 1) ^ 1)) {
+                    if (!wait_parked(&empty[s], ((seq / STAGES) & 1) ^ 1)) {
                         atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
                         tile = total_tiles;
                         break;
@@ -164,55 +198,88 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issue
+        // One thread feeds the tensor core, so its loop is kept to a few instructions per
+        // MMA: descriptor high words are constants, low words advance by additions, block
+        // boundaries are tracked with counters instead of divisions.
         if (lane == 0) {
             const uint32_t idesc = umma::instr_desc(1 /*f32*/, 0 /*f16*/, 0 /*f16*/, BW, BT);
-            int seq = 0, acc_seq = 0;
+            const uint32_t desc_hi = ((1024u >> 4) & 0x3fffu) | (1u << 14) | (umma::LAYOUT_SW128 << 29);
+            const uint32_t w16 = umma::smem_u32(sW) >> 4, x16 = umma::smem_u32(sX) >> 4;
+            int s = 0, b = 0, slab_in_block = 0;
+            uint32_t ph = 0, acc_ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                for (int sl = 0; sl < p.slabs && ok; sl++, seq++) {
-                    const int s = seq % STAGES;
-                    const uint32_t ph = (seq / STAGES) & 1;
+                for (int sl = 0; sl < p.slabs && ok; sl++) {
                     if (!wait_bounded(&full_x[s], ph) || !wait_bounded(&full_w[s], ph)) {
                         atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
                         ok = false;
                         break;
                     }
                     umma::tc_fence_after();
-                    const uint32_t w_addr = umma::smem_u32(sW + s * A_BYTES);
-                    const uint32_t x_addr = umma::smem_u32(sX + s * B_BYTES);
-                    const int steps_per_block = p.bs >= SLAB ? 4 : (4 / blocks_per_slab);
-                    for (int j = 0; j < 4; j++) {
-                        const bool first = (p.bs >= SLAB) ? ((sl % slabs_per_block) == 0 && j == 0)
-                                                          : ((j % steps_per_block) == 0);
-                        const int b = acc_seq % ACC_RING;
-                        if (first) {
-                            // the promotion warps must have drained this accumulator
-                            if (!wait_bounded(&acc_empty[b], ((acc_seq / ACC_RING) & 1) ^ 1)) {
+                    const uint32_t w_lo = ((w16 + uint32_t(s) * (A_BYTES >> 4)) & 0x3fffu) | (1u << 16);
+                    const uint32_t x_lo = ((x16 + uint32_t(s) * (B_BYTES >> 4)) & 0x3fffu) | (1u << 16);
+                    if (p.bs >= SLAB) {
+                        const bool first = slab_in_block == 0;
+                        if (first) {  // the promotion warps must have drained this accumulator
+                            if (!wait_bounded(&acc_empty[b], acc_ph ^ 1)) {
                                 atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
                                 ok = false;
                                 break;
                             }
                             umma::tc_fence_after();
                         }
-                        const uint64_t dw = umma::smem_desc(w_addr + j * 32, 1024, umma::LAYOUT_SW128);
-                        const uint64_t dx = umma::smem_desc(x_addr + j * 32, 1024, umma::LAYOUT_SW128);
-                        umma::mma_f16(tmem_base + uint32_t(b * BT), dw, dx, idesc, first ? 0u : 1u);
-                        const bool last = (p.bs >= SLAB) ? ((sl % slabs_per_block) == slabs_per_block - 1 && j == 3)
-                                                         : ((j % steps_per_block) == steps_per_block - 1);
-                        if (last) {
+                        const uint32_t d = tmem_base + uint32_t(b * BT);
+                        umma::mma_f16_lohi(d, w_lo, desc_hi, x_lo, desc_hi, idesc, first ? 0u : 1u);
+                        umma::mma_f16_lohi(d, w_lo + 2, desc_hi, x_lo + 2, desc_hi, idesc, 1u);
+                        umma::mma_f16_lohi(d, w_lo + 4, desc_hi, x_lo + 4, desc_hi, idesc, 1u);
+                        umma::mma_f16_lohi(d, w_lo + 6, desc_hi, x_lo + 6, desc_hi, idesc, 1u);
+                        umma::mma_commit(&empty[s]);
+                        if (++slab_in_block == slabs_per_block) {
                             umma::mma_commit(&acc_full[b]);
-                            acc_seq++;
+                            slab_in_block = 0;
+                            if (++b == ACC_RING) {
+                                b = 0;
+                                acc_ph ^= 1;
+                            }
                         }
+                    } else {
+                        // block_size 32: two blocks per slab, two K=16 steps each
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            if (!wait_bounded(&acc_empty[b], acc_ph ^ 1)) {
+                                atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
+                                ok = false;
+                                break;
+                            }
+                            umma::tc_fence_after();
+                            const uint32_t d = tmem_base + uint32_t(b * BT);
+                            umma::mma_f16_lohi(d, w_lo + 4 * h, desc_hi, x_lo + 4 * h, desc_hi, idesc, 0u);
+                            umma::mma_f16_lohi(d, w_lo + 4 * h + 2, desc_hi, x_lo + 4 * h + 2, desc_hi, idesc, 1u);
+                            umma::mma_commit(&acc_full[b]);
+                            if (++b == ACC_RING) {
+                                b = 0;
+                                acc_ph ^= 1;
+                            }
+                        }
+                        umma::mma_commit(&empty[s]);
                     }
-                    umma::mma_commit(&empty[s]);
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
             }
         }
-    } else if (warp >= 2 && warp < 6) {
+    }
+    } else if (warp < 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
         // ------------------------------------------------------------------- unpack
-        const int r = (warp - 2) * 32 + lane;  // weight row of the tile
+        const int r = (warp - 4) * 32 + lane;  // weight row of the tile
         const uint32_t row_off = uint32_t(r) * 128u;
         const uint32_t swz = uint32_t(r & 7);
+        UnpackConsts uc;
+        asm volatile("mov.u32 %0, 0x000F000F;\n\tmov.u32 %1, 0x00F000F0;\n\tmov.u32 %2, 0x64006400;\n\tmov.u32 %3, 0x54005400;"
+                     : "=r"(uc.m_lo), "=r"(uc.m_hi), "=r"(uc.k_lo), "=r"(uc.k_hi));
         int seq = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -236,7 +303,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                 const uint32_t lo1 = z1 * 0x00010001u + 0x64006400u, hi1 = z1 * 0x00100010u + 0x54005400u;
                 const int s = seq % STAGES;
                 // the nibbles have landed; the producer waited for the stage to be free before loading them
-                if (!wait_bounded(&full_x[s], (seq / STAGES) & 1)) {
+                if (!wait_parked(&full_x[s], (seq / STAGES) & 1)) {
                     if (lane == 0)
                         atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
                     ok = false;
@@ -246,70 +313,71 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                 const uint4 c0 = raw[0], c1 = raw[1];
                 const uint32_t base = umma::smem_u32(sW + s * A_BYTES) + row_off;
                 // chunk c (8 k) lands at 16-byte slot c ^ (row & 7): the 128B swizzle
-                sts128(base + ((0u ^ swz) << 4), unpack8(c0.x, lo0, hi0));
-                sts128(base + ((1u ^ swz) << 4), unpack8(c0.y, lo0, hi0));
-                sts128(base + ((2u ^ swz) << 4), unpack8(c0.z, lo0, hi0));
-                sts128(base + ((3u ^ swz) << 4), unpack8(c0.w, lo0, hi0));
-                sts128(base + ((4u ^ swz) << 4), unpack8(c1.x, lo1, hi1));
-                sts128(base + ((5u ^ swz) << 4), unpack8(c1.y, lo1, hi1));
-                sts128(base + ((6u ^ swz) << 4), unpack8(c1.z, lo1, hi1));
-                sts128(base + ((7u ^ swz) << 4), unpack8(c1.w, lo1, hi1));
+                sts128(base + ((0u ^ swz) << 4), unpack8(c0.x, lo0, hi0, uc));
+                sts128(base + ((1u ^ swz) << 4), unpack8(c0.y, lo0, hi0, uc));
+                sts128(base + ((2u ^ swz) << 4), unpack8(c0.z, lo0, hi0, uc));
+                sts128(base + ((3u ^ swz) << 4), unpack8(c0.w, lo0, hi0, uc));
+                sts128(base + ((4u ^ swz) << 4), unpack8(c1.x, lo1, hi1, uc));
+                sts128(base + ((5u ^ swz) << 4), unpack8(c1.y, lo1, hi1, uc));
+                sts128(base + ((6u ^ swz) << 4), unpack8(c1.z, lo1, hi1, uc));
+                sts128(base + ((7u ^ swz) << 4), unpack8(c1.w, lo1, hi1, uc));
                 umma::fence_proxy_async();  // generic-proxy stores -> visible to the tensor core
                 umma::mbar_arrive(&full_w[s]);
             }
         }
-    } else if (warp >= 6) {
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
         // ---------------------------------------------------------------- promotion
         const int q = warp & 3;            // tensor-memory lane quarter this warp may read
-        const int half = (warp - 6) >> 2;  // which 64 of the 128 tokens
+        const int half = (warp - 8) >> 2;  // which 128 of the 256 tokens
         int acc_seq = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int n = (tile / p.m_tiles) * BW + q * 32 + lane;
-            const int m0 = (tile % p.m_tiles) * BT + half * 64;
-            float acc[64];
+            const int m0 = (tile % p.m_tiles) * BT + half * 128;
+            float acc[128];
 #pragma unroll
-            for (int j = 0; j < 64; j++)
+            for (int j = 0; j < 128; j++)
                 acc[j] = 0.0f;
             float scale = p.scales_t[n];
             for (int blk = 0; blk < p.n_blocks; blk++, acc_seq++) {
                 const float scale_next = blk + 1 < p.n_blocks ? p.scales_t[size_t(blk + 1) * p.n_pad + n] : 0.0f;
                 const int b = acc_seq % ACC_RING;
-                if (ok && !wait_bounded(&acc_full[b], (acc_seq / ACC_RING) & 1)) {
+                if (ok && !wait_parked(&acc_full[b], (acc_seq / ACC_RING) & 1)) {
                     if (lane == 0)
                         atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
                     ok = false;
                 }
                 umma::tc_fence_after();
-                const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BT + half * 64);
-                uint32_t d[32];
-                umma::tmem_ld_32x32(taddr, d);
-                umma::tmem_ld_wait();
+                const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BT + half * 128);
 #pragma unroll
-                for (int j = 0; j < 32; j++)
-                    acc[j] = fmaf(__uint_as_float(d[j]), scale, acc[j]);
-                umma::tmem_ld_32x32(taddr + 32, d);
-                umma::tmem_ld_wait();
-                umma::tc_fence_before();
-                __syncwarp();
-                if (lane == 0)
-                    umma::mbar_arrive(&acc_empty[b]);
+                for (int c = 0; c < 4; c++) {
+                    uint32_t d[32];
+                    umma::tmem_ld_32x32(taddr + c * 32, d);
+                    umma::tmem_ld_wait();
+                    if (c == 3) {  // everything of this accumulator has been read: hand it back
+                        umma::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0)
+                            umma::mbar_arrive(&acc_empty[b]);
+                    }
 #pragma unroll
-                for (int j = 0; j < 32; j++)
-                    acc[32 + j] = fmaf(__uint_as_float(d[j]), scale, acc[32 + j]);
+                    for (int j = 0; j < 32; j++)
+                        acc[c * 32 + j] = fmaf(__uint_as_float(d[j]), scale, acc[c * 32 + j]);
+                }
                 scale = scale_next;
             }
             if (ok && n < p.N) {
                 if (p.y_f32) {
                     float *y = static_cast<float *>(p.y);
 #pragma unroll
-                    for (int j = 0; j < 64; j++)
+                    for (int j = 0; j < 128; j++)
                         if (m0 + j < p.M)
                             y[size_t(m0 + j) * p.N + n] = acc[j];
                 } else {
                     __half *y = static_cast<__half *>(p.y);
 #pragma unroll
-                    for (int j = 0; j < 64; j++)
+                    for (int j = 0; j < 128; j++)
                         if (m0 + j < p.M)
                             y[size_t(m0 + j) * p.N + n] = __float2half_rn(acc[j]);
                 }
