@@ -7,8 +7,9 @@
 // zero-point algebra applied at the store, :306-345) and of its epilogue
 // (matmul_integer_coop.comp:156-196).
 //
-// One CTA computes a 128 x BN tile of A[M,K] (u8/i8, row major) times
-// Bt[N,K] (the packed weight, K contiguous):
+// A persistent CTA per SM computes 128 x BN tiles of A[M,K] (u8/i8, row major)
+// times Bt[N,K] (the packed weight, K contiguous), two tensor-memory
+// accumulators so that a tile's epilogue overlaps the next tile's MMAs:
 //   warp 0    TMA producer: 128-byte K slabs of A and Bt into a ring of
 //             128B-swizzled stages, completion on an mbarrier per stage
 //   warp 1    allocates tensor memory, issues four K=32 MMAs per stage from one
@@ -54,6 +55,21 @@ __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
     return true;
 }
 
+// For warps that wait on someone else's progress: parked by the hardware (up to a
+// microsecond per attempt) instead of spinning in the issue slots of the MMA warp.
+__device__ __forceinline__ bool wait_parked(uint64_t *bar, uint32_t parity)
+{
+    if (umma::mbar_try_wait(bar, parity))
+        return true;
+    const long long t0 = clock64();
+    for (;;) {
+        if (umma::mbar_try_wait_hint(bar, parity, 1000u))
+            return true;
+        if (clock64() - t0 > WAIT_CYCLES)
+            return false;
+    }
+}
+
 template <int BN> constexpr int stages_for() { return BN == 256 ? 4 : (BN == 128 ? 6 : 8); }
 template <int BN> constexpr size_t smem_for()
 {
@@ -66,29 +82,33 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 {
     constexpr int STAGES = stages_for<BN>();
     constexpr int B_BYTES = BN * BK;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *sA = smem;
     uint8_t *sB = smem + STAGES * A_BYTES;
     uint64_t *full = reinterpret_cast<uint64_t *>(sB + STAGES * B_BYTES);
     uint64_t *empty = full + STAGES;
-    uint64_t *acc_ready = empty + STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
+    uint64_t *acc_full = empty + STAGES;   // [2] a tile's accumulator is complete
+    uint64_t *acc_empty = acc_full + 2;    // [2] the four epilogue warps have read it
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t m0 = int64_t(blockIdx.y) * BM;
-    const int n0 = blockIdx.x * BN;
+    // persistent: tiles are taken round robin, N fastest so that CTAs running together share rows of A
+    const int n_tiles = (p.N + BN - 1) / BN;
+    const int total_tiles = n_tiles * int((p.M + BM - 1) / BM);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             umma::mbar_init(&full[s], 1);
             umma::mbar_init(&empty[s], 1);
         }
-        umma::mbar_init(acc_ready, 1);
+        for (int b = 0; b < 2; b++) {
+            umma::mbar_init(&acc_full[b], 1);
+            umma::mbar_init(&acc_empty[b], 4);
+        }
         umma::fence_barrier_init();
     }
     if (warp == 1) {
-        umma::tmem_alloc(tmem_slot, BN);
+        umma::tmem_alloc(tmem_slot, 2 * BN);  // two accumulators: the epilogue of a tile overlaps the next tile's MMAs
         umma::tmem_relinquish();
     }
     umma::tc_fence_before();
@@ -100,118 +120,163 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         if (lane == 0) {
             umma::prefetch_tmap(&tmA);
             umma::prefetch_tmap(&tmB);
-            for (int kb = 0; kb < p.num_kb; kb++) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                if (!wait_bounded(&empty[s], ph ^ 1)) {
-                    atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
-                    break;
+            int s = 0;
+            uint32_t ph = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+                for (int kb = 0; kb < p.num_kb; kb++) {
+                    if (!wait_parked(&empty[s], ph ^ 1)) {
+                        atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
+                        tile = total_tiles;
+                        break;
+                    }
+                    umma::mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                    umma::tma_load_2d(sA + s * A_BYTES, &tmA, &full[s], kb * BK, m0);
+                    umma::tma_load_2d(sB + s * B_BYTES, &tmB, &full[s], kb * BK, n0);
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
-                umma::mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                umma::tma_load_2d(sA + s * A_BYTES, &tmA, &full[s], kb * BK, int(m0));
-                umma::tma_load_2d(sB + s * B_BYTES, &tmB, &full[s], kb * BK, n0);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = umma::instr_desc(2, p.a_signed ? 1 : 0, p.b_signed ? 1 : 0, BM, BN);
+            // descriptor high words are constants and low words advance by additions, so
+            // the one issuing thread spends a few instructions per MMA
+            const uint32_t desc_hi = ((1024u >> 4) & 0x3fffu) | (1u << 14) | (umma::LAYOUT_SW128 << 29);
+            const uint32_t a16 = umma::smem_u32(sA) >> 4, b16 = umma::smem_u32(sB) >> 4;
             bool ok = true;
-            for (int kb = 0; kb < p.num_kb && ok; kb++) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                if (!wait_bounded(&full[s], ph)) {
-                    atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
-                    ok = false;
+            int s = 0, b = 0;
+            uint32_t ph = 0, acc_ph = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (!wait_bounded(&acc_empty[b], acc_ph ^ 1)) {
+                    atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
                     break;
                 }
                 umma::tc_fence_after();
-                const uint32_t a_addr = umma::smem_u32(sA + s * A_BYTES);
-                const uint32_t b_addr = umma::smem_u32(sB + s * B_BYTES);
-#pragma unroll
-                for (int j = 0; j < BK / 32; j++) {
-                    const uint64_t da = umma::smem_desc(a_addr + j * 32, 1024, umma::LAYOUT_SW128);
-                    const uint64_t db = umma::smem_desc(b_addr + j * 32, 1024, umma::LAYOUT_SW128);
-                    umma::mma_i8(tmem_base, da, db, idesc, (kb | j) != 0);
+                const uint32_t d = tmem_base + uint32_t(b * BN);
+                for (int kb = 0; kb < p.num_kb; kb++) {
+                    if (!wait_bounded(&full[s], ph)) {
+                        atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
+                        ok = false;
+                        break;
+                    }
+                    umma::tc_fence_after();
+                    const uint32_t a_lo = ((a16 + uint32_t(s) * (A_BYTES >> 4)) & 0x3fffu) | (1u << 16);
+                    const uint32_t b_lo = ((b16 + uint32_t(s) * (B_BYTES >> 4)) & 0x3fffu) | (1u << 16);
+                    umma::mma_i8_lohi(d, a_lo, desc_hi, b_lo, desc_hi, idesc, kb != 0);
+                    umma::mma_i8_lohi(d, a_lo + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
+                    umma::mma_i8_lohi(d, a_lo + 4, desc_hi, b_lo + 4, desc_hi, idesc, 1u);
+                    umma::mma_i8_lohi(d, a_lo + 6, desc_hi, b_lo + 6, desc_hi, idesc, 1u);
+                    umma::mma_commit(&empty[s]);
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
-                umma::mma_commit(&empty[s]);
+                if (ok)
+                    umma::mma_commit(&acc_full[b]);
+                if (++b == 2) {
+                    b = 0;
+                    acc_ph ^= 1;
+                }
             }
-            if (ok)
-                umma::mma_commit(acc_ready);
         }
     } else {
         // Epilogue: warp w may read tensor-memory lanes 32*(w % 4) .. +31.
         const int q = warp & 3;
-        const bool ready = wait_bounded(acc_ready, 0);
-        if (!ready && lane == 0)
-            atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
-        umma::tc_fence_after();
-        const int64_t row = m0 + q * 32 + lane;
-        const bool row_ok = ready && row < p.M;
         const int32_t za = load_zp(p.a_zp, p.a_signed), zb = load_zp(p.b_zp, p.b_signed);
-        const uint32_t row_term = uint32_t(p.K) * uint32_t(za) * uint32_t(zb) -
-                                  ((zb != 0 && p.rowsum && row_ok) ? uint32_t(zb) * uint32_t(p.rowsum[row]) : 0u);
         float run_max = 0.0f, run_neg = 0.0f;
         const bool vec4 = p.vec_ok != 0;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-            uint32_t r[32];
-            umma::tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c0), r);
-            umma::tmem_ld_wait();
-            if (!row_ok || n0 + c0 >= p.N)
-                continue;
-            const int col0 = n0 + c0;
-#pragma unroll
-            for (int j = 0; j < 32; j++) {
-                const int col = col0 + j;
-                const int32_t cs = col < p.N ? p.colsum[col] : 0;
-                r[j] = r[j] - uint32_t(za) * uint32_t(cs) + row_term;
+        bool ready = true;
+        int b = 0;
+        uint32_t acc_ph = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            const int64_t m0 = int64_t(tile / n_tiles) * BM;
+            const int n0 = (tile % n_tiles) * BN;
+            if (ready && !wait_parked(&acc_full[b], acc_ph)) {
+                ready = false;
+                if (lane == 0)
+                    atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
             }
-            if (p.epi.mode == EPI_RAW) {
-                int32_t *o = static_cast<int32_t *>(p.out) + row * p.N + col0;
-                if (vec4 && col0 + 32 <= p.N) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<int4 *>(o + j) = make_int4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                } else {
-                    for (int j = 0; j < 32 && col0 + j < p.N; j++)
-                        o[j] = int32_t(r[j]);
+            umma::tc_fence_after();
+            const int64_t row = m0 + q * 32 + lane;
+            const bool row_ok = ready && row < p.M;
+            const uint32_t row_term = uint32_t(p.K) * uint32_t(za) * uint32_t(zb) -
+                                      ((zb != 0 && p.rowsum && row_ok) ? uint32_t(zb) * uint32_t(p.rowsum[row]) : 0u);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                umma::tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BN + c0), r);
+                umma::tmem_ld_wait();
+                if (c0 + 32 == BN) {  // the whole accumulator has been read: hand it back
+                    umma::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0)
+                        umma::mbar_arrive(&acc_empty[b]);
                 }
-            } else if (p.epi.mode == EPI_SCALE) {
-                float *o = static_cast<float *>(p.out) + row * p.N + col0;
-                float f[32];
+                if (!row_ok || n0 + c0 >= p.N)
+                    continue;
+                const int col0 = n0 + c0;
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
-                    if (col0 + j < p.N) {
-                        f[j] = epi_scale_value(p.epi, col0 + j, float(int32_t(r[j])));
-                        run_max = fmaxf(run_max, f[j]);
-                        run_neg = fmaxf(run_neg, -f[j]);
+                    const int col = col0 + j;
+                    const int32_t cs = col < p.N ? p.colsum[col] : 0;
+                    r[j] = r[j] - uint32_t(za) * uint32_t(cs) + row_term;
+                }
+                if (p.epi.mode == EPI_RAW) {
+                    int32_t *o = static_cast<int32_t *>(p.out) + row * p.N + col0;
+                    if (vec4 && col0 + 32 <= p.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<int4 *>(o + j) = make_int4(r[j], r[j + 1], r[j + 2], r[j + 3]);
                     } else {
-                        f[j] = 0.0f;
+                        for (int j = 0; j < 32 && col0 + j < p.N; j++)
+                            o[j] = int32_t(r[j]);
+                    }
+                } else if (p.epi.mode == EPI_SCALE) {
+                    float *o = static_cast<float *>(p.out) + row * p.N + col0;
+                    float f[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        if (col0 + j < p.N) {
+                            f[j] = epi_scale_value(p.epi, col0 + j, float(int32_t(r[j])));
+                            run_max = fmaxf(run_max, f[j]);
+                            run_neg = fmaxf(run_neg, -f[j]);
+                        } else {
+                            f[j] = 0.0f;
+                        }
+                    }
+                    if (vec4 && col0 + 32 <= p.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4 *>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < p.N; j++)
+                            o[j] = f[j];
+                    }
+                } else {
+                    uint8_t *o = static_cast<uint8_t *>(p.out) + row * p.N + col0;
+                    if (vec4 && col0 + 32 <= p.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            uint32_t w = 0;
+#pragma unroll
+                            for (int t = 0; t < 4; t++)
+                                w |= (uint32_t(epi_requant_value(p.epi, col0 + j + t, int32_t(r[j + t]))) & 0xffu) << (8 * t);
+                            *reinterpret_cast<uint32_t *>(o + j) = w;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < p.N; j++)
+                            o[j] = uint8_t(epi_requant_value(p.epi, col0 + j, int32_t(r[j])));
                     }
                 }
-                if (vec4 && col0 + 32 <= p.N) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<float4 *>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-                } else {
-                    for (int j = 0; j < 32 && col0 + j < p.N; j++)
-                        o[j] = f[j];
-                }
-            } else {
-                uint8_t *o = static_cast<uint8_t *>(p.out) + row * p.N + col0;
-                if (vec4 && col0 + 32 <= p.N) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        uint32_t w = 0;
-#pragma unroll
-                        for (int t = 0; t < 4; t++)
-                            w |= (uint32_t(epi_requant_value(p.epi, col0 + j + t, int32_t(r[j + t]))) & 0xffu) << (8 * t);
-                        *reinterpret_cast<uint32_t *>(o + j) = w;
-                    }
-                } else {
-                    for (int j = 0; j < 32 && col0 + j < p.N; j++)
-                        o[j] = uint8_t(epi_requant_value(p.epi, col0 + j, int32_t(r[j])));
-                }
+            }
+            if (++b == 2) {
+                b = 0;
+                acc_ph ^= 1;
             }
         }
         if (p.epi.mode == EPI_SCALE)
@@ -220,7 +285,7 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     umma::tc_fence_before();
     __syncthreads();
     if (warp == 1)
-        umma::tmem_dealloc(tmem_base, BN);
+        umma::tmem_dealloc(tmem_base, 2 * BN);
 }
 
 // sum_k a[m][k] per row, needed only when the weight's zero point is not 0:
@@ -257,7 +322,8 @@ int32_t launch(ovk_ctx *ctx, const CUtensorMap &tmA, const ovk_mmi_weight *w, co
         return ovk_fail(ctx, OVK_BACKEND, "MatMulInteger: cuTensorMapEncodeTiled failed for the packed weight");
     OVK_CUDA(ctx, cudaFuncSetAttribute(mmi_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        int(smem_for<BN>())));
-    dim3 grid(unsigned(ceil_div64(p.N, BN)), unsigned(ceil_div64(p.M, BM)));
+    const int64_t tiles = ceil_div64(p.N, BN) * ceil_div64(p.M, BM);
+    const unsigned grid = unsigned(std::min<int64_t>(tiles, ctx->sm_count));
     mmi_tc_kernel<BN><<<grid, THREADS, smem_for<BN>(), ctx->stream>>>(tmA, tmB, p);
     OVK_LAUNCHED(ctx, BN == 256 ? "mmi_tc_128x256" : (BN == 128 ? "mmi_tc_128x128" : "mmi_tc_128x64"));
     return OVK_OK;
@@ -272,7 +338,7 @@ bool ovk_mmi_tc_applies(const ovk_ctx *ctx, const ovk_mmi_weight *w, const void 
 {
     (void)ctx;
     return m >= 16 && w->n >= 16 && w->k >= 32 && (w->k % 16) == 0 && aligned_to(a, 16) &&
-           ceil_div64(m, BM) <= 65535 && m < (int64_t(1) << 31);
+           m < (int64_t(1) << 31) - BM && ceil_div64(m, BM) * ceil_div64(w->n, 64) < (int64_t(1) << 31);
 }
 
 int32_t ovk_mmi_tc_prepare_weight(ovk_ctx *, ovk_mmi_weight *) { return OVK_OK; }
