@@ -50,6 +50,14 @@ int32_t ovk_nbits_prepack(ovk_ctx *ctx, const void *b, const void *scales, int32
             delete w;
             return rc;
         }
+        // a load-time call: wait for the copy, so that the decode kernel (which starts
+        // streaming weights before its stream predecessors have finished) never sees it half written
+        cudaError_t e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) {
+            cudaFree(w->decode);
+            delete w;
+            return ovk_fail(ctx, OVK_BACKEND, "MatMulNBits: weight preparation: %s", cudaGetErrorString(e));
+        }
     }
     *out = w;
     return OVK_OK;

@@ -53,15 +53,17 @@ struct DecParams {
     int *status;
 };
 
+// Bounded wait; while the phase is incomplete the hardware parks the thread
+// (up to a microsecond per attempt) instead of letting it spin in the issue slots.
 __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
 {
     if (umma::mbar_try_wait(bar, parity))
         return true;
     const long long t0 = clock64();
-    for (uint32_t spins = 0;; spins++) {
-        if (umma::mbar_try_wait(bar, parity))
+    for (;;) {
+        if (umma::mbar_try_wait_hint(bar, parity, 1000u))
             return true;
-        if ((spins & 63u) == 63u && clock64() - t0 > WAIT_CYCLES)
+        if (clock64() - t0 > WAIT_CYCLES)
             return false;
     }
 }
@@ -207,6 +209,11 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
     // barriers visible to everyone, then the producer starts streaming weights at once:
     // the first tiles are in flight while the consumer warps stage the activations
     __syncthreads();
+    // Programmatic dependent launch: the next kernel of the stream may start its own
+    // prologue and weight streaming now (weights are constants); like this one, it
+    // touches activations and outputs only after griddepcontrol.wait, i.e. after
+    // every earlier kernel has completed and flushed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == CONSUMER_WARPS) {
         // ------------------------------------------------------------ producer
@@ -242,6 +249,7 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
         return;
     }
 
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the producers of A have finished
     // ---- activations -> shared memory, in the order the fragments are read
     // unit (row, group, t): k = 32*group + 8*t + {0,4,1,5,2,6,3,7}
     if constexpr (A_F32) {
@@ -526,7 +534,17 @@ int32_t launch_decode_gb(ovk_ctx *ctx, const DecParams &p, size_t smem)
     OVK_CUDA(ctx, cudaFuncSetAttribute(nbits_decode_kernel<SF, AF, YF, GB, UN>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     const unsigned grid = unsigned(std::min<int>(p.ntiles, ctx->sm_count));
-    nbits_decode_kernel<SF, AF, YF, GB, UN><<<grid, THREADS, smem, ctx->stream>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    OVK_CUDA(ctx, cudaLaunchKernelEx(&cfg, nbits_decode_kernel<SF, AF, YF, GB, UN>, p));
     OVK_LAUNCHED(ctx, "nbits_decode_mma");
     return OVK_OK;
 }
