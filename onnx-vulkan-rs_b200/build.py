@@ -1,4 +1,5 @@
-"""Builds libovk_cuda.so (every .cu under csrc/) for sm_100a with nvcc.
+"""Builds libovk_cuda.so (every .cu under csrc/) for sm_100a with nvcc, then
+libovk_host.so (host/*.cpp, the node-level layer above the C ABI) with g++.
 
 Usage: python build.py [--force] [--verbose]
 nvcc cross-compiles without a GPU; objects are cached under csrc/build/ by
@@ -17,6 +18,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libovk_cuda.so")
+HOST_DIR = os.path.join(HERE, "host")
+HOST_OUT = os.path.join(HERE, "libovk_host.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -64,7 +67,23 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if r.returncode:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+    build_host(force)
     return OUT
+
+
+def build_host(force: bool = False) -> str:
+    """The C++ host layer: plain g++, linked against libovk_cuda.so beside it."""
+    srcs = sorted(glob.glob(os.path.join(HOST_DIR, "*.cpp")))
+    deps = srcs + glob.glob(os.path.join(HOST_DIR, "*.hpp")) + glob.glob(os.path.join(ROOT, "include", "*.h")) + [OUT]
+    if force or _stale(HOST_OUT, deps):
+        cmd = ["/usr/bin/g++", "-std=c++17", "-O2", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wextra", "-shared",
+               "-I", os.path.join(ROOT, "include"), *srcs, "-o", HOST_OUT, "-L", HERE, "-lovk_cuda",
+               "-Wl,-rpath,$ORIGIN"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("host layer build failed")
+    return HOST_OUT
 
 
 if __name__ == "__main__":

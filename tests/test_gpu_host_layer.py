@@ -1,0 +1,223 @@
+"""Node-level parity: the operators driven the way the reference's interpreter
+drives them - a node, named tensors in an environment - against the CPU port."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import cases
+import oracle as orc
+from gpu_util import assert_close
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.fixture(scope="module")
+def hl():
+    from ovk_b200 import host_layer
+    return host_layer
+
+
+@pytest.fixture()
+def env(hl):
+    e = hl.Env(0)
+    yield e
+    e.close()
+
+
+def set_nbits(env, a, nib, zp, scale, block_size):
+    env.set("a", a)
+    env.set("quant", orc.pack_nibbles(nib, block_size), initializer=True)
+    env.set("scales", scale.reshape(-1), initializer=True)
+    if zp is not None:
+        env.set("zp", orc.pack_zero_points(zp), initializer=True)
+
+
+@pytest.mark.parametrize("m,k,n,bs", cases.NBITS_REFERENCE_CASES[:4] + [(3, 128, 4096, 32), (1, 80, 33, 16)])
+def test_matmul_nbits_reference_cases(hl, env, m, k, n, bs):
+    """crates/onnx-vulkan-core/tests/matmul_nbits.rs:64-127: same node, same closed-form inputs, 1e-4."""
+    a, nib, zp, scale = cases.nbits_reference_case(m, k, n, bs)
+    set_nbits(env, a, nib, zp, scale, bs)
+    node = hl.Node("MatMulNBits", ["a", "quant", "scales", "zp"], ["y"], domain="com.microsoft",
+                   K=k, N=n, bits=4, block_size=bs)
+    env.execute(node)
+    got = env.host("y")
+    assert got.shape == (m, n) and got.dtype == np.float32
+    assert_close(got, cases.nbits_expected_f64(a, nib, zp, scale, bs), 1e-4, 1e-4)
+
+
+def test_matmul_nbits_weight_prepared_once_and_leading_dims(hl, env):
+    """The packed weight is cached by initializer name (cache.rs:231); A keeps its leading dimensions."""
+    a, nib, zp, scale = cases.nbits_synthetic(21, 6, 256, 96, 32)
+    set_nbits(env, a.reshape(2, 3, 256), nib, zp, scale, 32)
+    node = hl.Node("MatMulNBits", ["a", "quant", "scales", "zp"], ["y"], K=256, N=96, bits=4, block_size=32)
+    env.execute(node)
+    first = env.host("y")
+    assert first.shape == (2, 3, 96) and first.dtype == np.float16
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, 32), scale, orc.pack_zero_points(zp), 256, 96, 32)
+    assert_close(first.reshape(6, 96), want, 1e-3, 1e-3)
+    env.set("a", a[:1])
+    env.execute(node)
+    assert_close(env.host("y"), want[:1], 1e-3, 1e-3)
+
+
+def test_matmul_nbits_k_mismatch_is_an_error(hl, env):
+    """interp.rs:6441-6447."""
+    a, nib, zp, scale = cases.nbits_reference_case(1, 64, 8, 32)
+    set_nbits(env, a, nib, zp, scale, 32)
+    node = hl.Node("MatMulNBits", ["a", "quant", "scales", "zp"], ["y"], K=96, N=8, bits=4, block_size=32)
+    with pytest.raises(hl.OvkError, match="disagrees with K=96"):
+        env.execute(node)
+
+
+def test_dynamic_quantize_then_matmul_integer_chain(hl, env):
+    """DynamicQuantizeLinear -> MatMulInteger with the zero point staying on the device (interp.rs:1945-2183)."""
+    x = cases.rng_for(22, 0).standard_normal((70, 96), dtype=np.float32)
+    b = cases.lcg_bytes_fast(96 * 50, 9).reshape(96, 50).view(np.int8)
+    env.set("x", x)
+    env.set("b", b, initializer=True)
+    env.execute(hl.Node("DynamicQuantizeLinear", ["x"], ["xq", "xs", "xz"]))
+    env.execute(hl.Node("MatMulInteger", ["xq", "b", "xz"], ["acc"]))
+    yq, scale, zp = orc.dynamic_quantize(x)
+    assert np.array_equal(env.host("xq"), yq)
+    assert env.host("xs").reshape(()) == scale and int(env.host("xz").reshape(())) == zp
+    assert np.array_equal(env.host("acc"), orc.matmul_integer(yq, b, zp, 0))
+
+
+@pytest.mark.parametrize("relu,col_scale", [(0, True), (1, False)])
+def test_matmul_integer_scale_bias(hl, env, relu, col_scale):
+    """crates/onnx-vulkan-core/tests/integer_epilogue.rs: bit-equal to the unfused Cast, Mul, Add [, Relu]."""
+    m, k, n = 33, 64, 40
+    a = cases.lcg_bytes_fast(m * k, 5).reshape(m, k)
+    b = cases.lcg_bytes_fast(k * n, 17).reshape(k, n).view(np.int8)
+    scale = cases.rng_for(23, 0).uniform(1e-3, 2e-2, size=n if col_scale else 1).astype(np.float32)
+    bias = cases.rng_for(23, 1).standard_normal(n, dtype=np.float32)
+    env.set("a", a)
+    env.set("b", b, initializer=True)
+    env.set("az", np.array([121], dtype=np.uint8))
+    env.set("s", scale, initializer=True)
+    env.set("bias", bias, initializer=True)
+    env.execute(hl.Node("MatMulIntegerScaleBias", ["a", "b", "az", "", "s", "bias"], ["y"], relu=relu))
+    acc = orc.matmul_integer(a, b, 121, 0)
+    want = orc.scale_bias_epilogue(acc, scale, int(col_scale), bias, 1, relu=bool(relu))
+    assert np.array_equal(env.host("y").view(np.uint32), want.view(np.uint32))
+
+
+def test_scale_bias_row_broadcast_is_left_to_the_unfused_nodes(hl, env):
+    """interp.rs:2600-2610: a scale that broadcasts over rows has no column step."""
+    env.set("a", np.zeros((4, 8), dtype=np.uint8))
+    env.set("b", np.zeros((8, 6), dtype=np.int8), initializer=True)
+    env.set("s", np.ones((4, 1), dtype=np.float32), initializer=True)
+    env.set("bias", np.zeros(6, dtype=np.float32), initializer=True)
+    with pytest.raises(hl.OvkError) as err:
+        env.execute(hl.Node("MatMulIntegerScaleBias", ["a", "b", "", "", "s", "bias"], ["y"]))
+    assert err.value.status == 2
+
+
+def literal(name):
+    return json.load(open(os.path.join(GOLDEN, "qlinear_literal_vectors.json")))[name]
+
+
+def set_qlinear_conv(env, c, x_shape, w_shape):
+    env.set("x", np.array(c["x"], dtype=np.uint8).reshape(x_shape))
+    env.set("xs", np.array(c["x_scale"], dtype=np.float32), initializer=True)
+    env.set("xz", np.array(c["x_zp"], dtype=np.uint8), initializer=True)
+    env.set("w", np.array(c["w"], dtype=np.int8).reshape(w_shape), initializer=True)
+    ws = np.array(c["w_scale"], dtype=np.float32)
+    env.set("ws", ws, initializer=True)
+    env.set("wz", np.zeros(ws.shape, dtype=np.int8), initializer=True)
+    env.set("ys", np.array(c["y_scale"], dtype=np.float32), initializer=True)
+    env.set("yz", np.array(c["y_zp"], dtype=np.uint8), initializer=True)
+    if "bias" in c:
+        env.set("bias", np.array(c["bias"], dtype=np.int32), initializer=True)
+
+
+@pytest.mark.parametrize("name,xs,ws", [("conv_per_channel", (1, 1, 3, 3), (2, 1, 2, 2)),
+                                        ("conv_per_tensor", (1, 1, 3, 3), (2, 1, 2, 2)),
+                                        ("conv_no_bias", (1, 1, 2, 2), (1, 1, 2, 2))])
+def test_qlinear_conv_literal_vectors(hl, env, name, xs, ws):
+    """crates/onnx-vulkan-core/tests/qlinear.rs:106-236, driven as a node."""
+    c = literal(name)
+    set_qlinear_conv(env, c, xs, ws)
+    ins = ["x", "xs", "xz", "w", "ws", "wz", "ys", "yz"] + (["bias"] if "bias" in c else [])
+    node = hl.Node("QLinearConv", ins, ["y"], kernel_shape=list(ws[2:]))
+    assert env.unsupported_quantization(node) is None
+    env.execute(node)
+    w_scale = np.atleast_1d(np.array(c["w_scale"], dtype=np.float32))
+    want = orc.qlinear_conv(np.array(c["x"], dtype=np.uint8).reshape(xs), c["x_scale"], c["x_zp"],
+                            np.array(c["w"], dtype=np.int8).reshape(ws), w_scale, 0, c["y_scale"], c["y_zp"],
+                            bias=np.array(c["bias"], dtype=np.int32) if "bias" in c else None)
+    assert np.array_equal(env.host("y"), want)
+
+
+def test_qlinear_conv_refusals_use_the_reference_wording(hl, env):
+    """interp.rs:781-847 and tests/qlinear.rs:238-330."""
+    c = literal("conv_per_channel")
+    set_qlinear_conv(env, c, (1, 1, 3, 3), (2, 1, 2, 2))
+    ins = ["x", "xs", "xz", "w", "ws", "wz", "ys", "yz", "bias"]
+    node = hl.Node("QLinearConv", ins, ["y"])
+    env.set("wz", np.array([0, 3], dtype=np.int8), initializer=True)
+    assert env.unsupported_quantization(node) == \
+        "QLinearConv: w per-channel zero point is not zero (asymmetric weights)"
+    with pytest.raises(hl.OvkError, match="asymmetric weights"):
+        env.execute(node)
+    env.set("wz", np.zeros(1, dtype=np.int8), initializer=True)
+    assert env.unsupported_quantization(node) == "QLinearConv: w scale and zero point have different lengths"
+    env.set("wz", np.zeros(2, dtype=np.int8), initializer=True)
+    env.set("xs", np.array(c["x_scale"], dtype=np.float32), initializer=False)
+    assert env.unsupported_quantization(node) == "QLinearConv: x scale or zero point is not a constant"
+    env.set("xs", np.array([0.1, 0.2], dtype=np.float32), initializer=True)
+    assert env.unsupported_quantization(node) == "QLinearConv: x scale or zero point is not per-tensor"
+    env.set("xs", np.array(c["x_scale"], dtype=np.float32), initializer=True)
+    env.set("bias", np.zeros(2, dtype=np.float32), initializer=True)
+    assert env.unsupported_quantization(node) == "QLinearConv: B bias is not int32"
+
+
+@pytest.mark.parametrize("auto_pad", ["SAME_UPPER", "SAME_LOWER", "VALID"])
+def test_conv_integer_auto_pad(hl, env, auto_pad):
+    """conv_geometry resolves auto_pad on the host (interp.rs:3425-3536)."""
+    x = cases.lcg_bytes_fast(2 * 16 * 13 * 10, 3).reshape(2, 16, 13, 10)
+    w = cases.lcg_bytes_fast(24 * 16 * 3 * 4, 8).reshape(24, 16, 3, 4).view(np.int8)
+    env.set("x", x)
+    env.set("w", w, initializer=True)
+    env.set("xz", np.array(131, dtype=np.uint8), initializer=True)
+    env.execute(hl.Node("ConvInteger", ["x", "w", "xz"], ["y"], strides=[2, 1], auto_pad=auto_pad))
+    want = orc.conv_integer(x, w, 131, 0, strides=(2, 1), auto_pad=auto_pad)
+    assert np.array_equal(env.host("y"), want)
+
+
+def test_conv_integer_one_dimensional(hl, env):
+    """A 1-D convolution runs as H x 1 (interp.rs:3455-3470)."""
+    x = cases.lcg_bytes_fast(3 * 8 * 50, 4).reshape(3, 8, 50)
+    w = cases.lcg_bytes_fast(12 * 8 * 5, 6).reshape(12, 8, 5)
+    env.set("x", x)
+    env.set("w", w, initializer=True)
+    env.set("xz", np.array(7, dtype=np.uint8), initializer=True)
+    env.set("wz", np.array(100, dtype=np.uint8), initializer=True)
+    env.execute(hl.Node("ConvInteger", ["x", "w", "xz", "wz"], ["y"], pads=[2, 1], strides=[2]))
+    want = orc.conv_integer(x[..., None], w[..., None], 7, 100, strides=(2, 1), pads=(2, 0, 1, 0))
+    got = env.host("y")
+    assert got.shape == want.shape[:3] and np.array_equal(got, want[..., 0])
+
+
+def test_qlinear_matmul(hl, env):
+    """interp.rs:4845-4875: MatMulInteger then requantize with one ratio per column."""
+    m, k, n = 19, 48, 24
+    a = cases.lcg_bytes_fast(m * k, 2).reshape(m, k)
+    b = cases.lcg_bytes_fast(k * n, 7).reshape(k, n).view(np.int8)
+    bs = cases.rng_for(24, 0).uniform(0.01, 0.03, size=n).astype(np.float32)
+    env.set("a", a)
+    env.set("as", np.array(0.02, dtype=np.float32), initializer=True)
+    env.set("az", np.array(128, dtype=np.uint8), initializer=True)
+    env.set("b", b, initializer=True)
+    env.set("bs", bs, initializer=True)
+    env.set("bz", np.zeros(n, dtype=np.int8), initializer=True)
+    env.set("ys", np.array(0.5, dtype=np.float32), initializer=True)
+    env.set("yz", np.array(-3, dtype=np.int8), initializer=True)
+    env.execute(hl.Node("QLinearMatMul", ["a", "as", "az", "b", "bs", "bz", "ys", "yz"], ["y"]))
+    acc = orc.matmul_integer(a, b, 128, 0)
+    want = orc.requantize(acc, 1, orc.requantize_ratio(0.02, bs, 0.5), -3, out_signed=True)
+    got = env.host("y")
+    assert got.dtype == np.int8 and np.array_equal(got, want)
