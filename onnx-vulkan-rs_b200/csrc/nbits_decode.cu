@@ -17,9 +17,11 @@
 //    4-stage shared-memory ring (a producer warp, mbarrier completion), so
 //    ~170 KB per SM are in flight without spending registers on it;
 //  * sixteen consumer warps unpack with ONE logic op per pair of nibbles (a
-//    nibble at bits 4-7 OR-ed with 0x5400 is the fp16 number 64 + n) and feed
+//    nibble sitting in the mantissa of an fp16 number whose exponent bits are
+//    OR-ed in IS the number bias + n; the prepack rotates every word by two
+//    bits so that one rotation per word serves all eight nibbles) and feed
 //    mma.sync.m16n8k16: 16 weight columns x 16 k x up to 8 activation rows per
-//    instruction, products exact, f32 accumulation; the bias and the zero
+//    instruction, products exact, f32 accumulation; the biases and the zero
 //    point leave through one more MMA per block (see do_block).  A block's
 //    partial sum is then scaled and added in f32 on the CUDA cores, as the
 //    reference does.
@@ -50,6 +52,7 @@ struct DecParams {
     uint32_t s_off, z_off, tile_bytes;
     int g_pad;  // k32 groups covered by the tiles (>= ceil(K/32))
     int rows;   // batch columns in use: M, or 2M for split f32 activations
+    int vec_a;  // rows of A start on 16-byte boundaries: groups are read as 128-bit vectors
     int *status;
 };
 
@@ -115,14 +118,13 @@ __device__ __forceinline__ uint32_t lds8(uint32_t addr)
     return v;
 }
 
-// d = A x B (C = 0)
-__device__ __forceinline__ void mma16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                              uint32_t b0, uint32_t b1, uint32_t zero)
+// d = A x B (C = 0) for the 16 x 8 (k = 8) shape: two A registers, one B register
+__device__ __forceinline__ void mma1688_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0)
 {
     asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        "mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(__uint_as_float(zero)));
+        : "r"(a0), "r"(a1), "r"(b0), "f"(0.0f));
 }
 
 // (a & b) | c with all three operands in registers: one LOP3 (two immediates would need two)
@@ -134,21 +136,34 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c)
 }
 
 struct UnpackConsts {
-    uint32_t mask, magic, zero;  // 0x00F000F0, 0x54005400 and 0, held in registers
+    // held in registers (an immediate pair would cost a second logic op each):
+    //   even k: nibble at bits 2-5,  0x003C003C / 0x5C005C00 -> 256 + n
+    //   odd k:  nibble at bits 6-9,  0x03C003C0 / 0x4C004C00 ->  16 + n
+    //   zero point: bits 4-7,        0x00F000F0 / 0x54005400 ->  64 + z
+    uint32_t mask_e, magic_e, mask_o, magic_o, mask_z, magic_z;
 };
 
 // One quantization block of one 16-column panel.
 //
-// A nibble n sitting at bits 4-7 (20-23) of a word, OR-ed with 0x5400, IS the
-// fp16 number 64 + n: no subtraction is needed to unpack it.  The block's sum
-//     sum_k a_k (n_k - z)  =  sum_k a_k (64 + n_k)  -  (64 + z) * sum_k a_k
-// is formed entirely on the tensor cores: 2*GB MMAs over the nibbles plus ONE
-// more whose weight operand is (64 + z) (again just bits: 0x5400 | z << 4) and
-// whose activation operand is minus the block's activation sum, split into
-// three fp16 parts so that it is exact to ~2^-33.  All products are exact and
-// the f32 accumulator only ever holds values of a few hundred, so the result
-// differs from the exact sum by ~1e-6 relative.  Then the block's scale, in f32.
-template <bool SCALE_F32, int GB>
+// A nibble n that sits inside the mantissa field of an fp16 number whose
+// exponent bits say "2^e" IS the number 2^e + n when it starts at mantissa bit
+// 10 - e: nothing has to be subtracted or converted to unpack it.  The prepack
+// stores every 32-bit word of eight nibbles rotated left by two bits, which puts
+// nibbles 0 and 4 at bits 2-5 of the two halves (256 + n) and nibbles 1 and 5
+// at bits 6-9 (16 + n); ONE rotation by eight bits brings nibbles 2, 6 and 3, 7
+// to the same places.  So a word costs one shift and four logic ops.
+//
+// The block's sum
+//     sum_k a_k (n_k - z) = sum_odd a_k (16 + n_k) + sum_even a_k (256 + n_k)
+//                           - (64 + z) S + 64 (0.75 S_odd - 3 S_even),   S = S_odd + S_even
+// (S_* = sums of the block's activations over odd / even k) is formed entirely
+// on the tensor cores: 2*GB MMAs over the nibbles plus ONE k = 8 MMA whose weight
+// operand is half2(64 + z, 64) (again just bits) and whose activation operand
+// is half2(-S, 0.75 S_odd - 3 S_even), each split into three fp16 parts so that
+// it is exact to ~2^-33.  All products are exact and the f32 accumulator only
+// ever holds values of about a thousand, so the result differs from the exact
+// sum by a few 1e-6 relative.  Then the block's scale, in f32.
+template <bool SCALE_F32, int GB, bool ONE>
 __device__ __forceinline__ void do_block(float (&acc)[4], const UnpackConsts &uc, uint32_t wa, uint32_t sa,
                                          uint32_t za, uint32_t aa, uint32_t ca)
 {
@@ -164,26 +179,77 @@ __device__ __forceinline__ void do_block(float (&acc)[4], const UnpackConsts &uc
         s_hi = __high2float(h);
     }
     const uint32_t zb = lds8(za);    // z(col g) | z(col g+8) << 4
-    const uint32_t corr = lds32(ca);  // half2(-part_t of the block's activation sum, 0)
+    const uint32_t corr = lds32(ca);  // half2(-S part_t, (0.75 S_odd - 3 S_even) part_t)
     float d[4];
-    mma16816_zero(d, and_or(zb << 4, uc.mask, uc.magic), and_or(zb, uc.mask, uc.magic), uc.zero, uc.zero, corr,
-                  uc.zero, uc.zero);
+    mma1688_zero(d, and_or(zb << 4, uc.mask_z, uc.magic_z), and_or(zb, uc.mask_z, uc.magic_z), corr);
 #pragma unroll
     for (int gi = 0; gi < GB; gi++) {
         const uint2 wv = lds64(wa + gi * 256);
         const uint4 av = lds128(aa + gi * 64);
-        mma16816(d, and_or(wv.x << 4, uc.mask, uc.magic), and_or(wv.y << 4, uc.mask, uc.magic),
-                 and_or(wv.x, uc.mask, uc.magic), and_or(wv.y, uc.mask, uc.magic), av.x, av.y);
-        mma16816(d, and_or(wv.x >> 4, uc.mask, uc.magic), and_or(wv.y >> 4, uc.mask, uc.magic),
-                 and_or(wv.x >> 8, uc.mask, uc.magic), and_or(wv.y >> 8, uc.mask, uc.magic), av.z, av.w);
+        const uint32_t xr = __funnelshift_r(wv.x, wv.x, 8), yr = __funnelshift_r(wv.y, wv.y, 8);
+        mma16816(d, and_or(wv.x, uc.mask_e, uc.magic_e), and_or(wv.y, uc.mask_e, uc.magic_e),
+                 and_or(wv.x, uc.mask_o, uc.magic_o), and_or(wv.y, uc.mask_o, uc.magic_o), av.x, av.y);
+        mma16816(d, and_or(xr, uc.mask_e, uc.magic_e), and_or(yr, uc.mask_e, uc.magic_e),
+                 and_or(xr, uc.mask_o, uc.magic_o), and_or(yr, uc.mask_o, uc.magic_o), av.z, av.w);
     }
     acc[0] = fmaf(d[0], s_lo, acc[0]);
-    acc[1] = fmaf(d[1], s_lo, acc[1]);
     acc[2] = fmaf(d[2], s_hi, acc[2]);
-    acc[3] = fmaf(d[3], s_hi, acc[3]);
+    if constexpr (!ONE) {  // batch columns 1, 3, 5, 7 exist only with more than one row
+        acc[1] = fmaf(d[1], s_lo, acc[1]);
+        acc[3] = fmaf(d[3], s_hi, acc[3]);
+    }
 }
 
-template <bool SCALE_F32, bool A_F32, bool Y_F32, int GBT, int UNROLL>
+// The three fp16 parts of x, to ~2^-33 relative.
+__device__ __forceinline__ void split3(double x, __half (&h)[3])
+{
+    h[0] = __double2half(x);
+    const double r1 = x - double(__half2float(h[0]));
+    h[1] = __double2half(r1);
+    h[2] = __double2half(r1 - double(__half2float(h[1])));
+}
+
+// Exact sums of a group's staged (fp16) activations over even and odd k,
+// in two chains each; fp16 terms span fewer than 53 bits, so doubles are exact.
+struct GroupSums {
+    double e0 = 0.0, e1 = 0.0, o0 = 0.0, o1 = 0.0;
+};
+
+// Stages eight consecutive k (already rounded to fp16, held as float) as the
+// 16-byte unit the fragments read: half2 pairs (0,4) (1,5) (2,6) (3,7).
+__device__ __forceinline__ void stage_unit(uint4 *dst, const float (&w)[8], GroupSums &s)
+{
+    *dst = make_uint4(pack_h2(w[0], w[4]), pack_h2(w[1], w[5]), pack_h2(w[2], w[6]), pack_h2(w[3], w[7]));
+    s.e0 += double(w[0]) + double(w[4]);
+    s.o0 += double(w[1]) + double(w[5]);
+    s.e1 += double(w[2]) + double(w[6]);
+    s.o1 += double(w[3]) + double(w[7]);
+}
+
+// Sums of a block = of GBT adjacent groups, held by GBT adjacent lanes; the
+// first lane of the block writes the correction entry (four words, one per t).
+template <int GBT>
+__device__ __forceinline__ void finish_block(uint32_t *corr_entry, double s_even, double s_odd, int lane, bool valid)
+{
+#pragma unroll
+    for (int o = 1; o < GBT; o <<= 1) {
+        s_even += __shfl_xor_sync(0xffffffffu, s_even, o);
+        s_odd += __shfl_xor_sync(0xffffffffu, s_odd, o);
+    }
+    if (valid && (lane & (GBT - 1)) == 0) {
+        __half a[3], b[3];
+        split3(-(s_even + s_odd), a);
+        split3(0.75 * s_odd - 3.0 * s_even, b);
+        uint4 e;
+        e.x = uint32_t(__half_as_ushort(a[0])) | uint32_t(__half_as_ushort(b[0])) << 16;
+        e.y = uint32_t(__half_as_ushort(a[1])) | uint32_t(__half_as_ushort(b[1])) << 16;
+        e.z = uint32_t(__half_as_ushort(a[2])) | uint32_t(__half_as_ushort(b[2])) << 16;
+        e.w = 0u;
+        *reinterpret_cast<uint4 *>(corr_entry) = e;
+    }
+}
+
+template <bool SCALE_F32, bool A_F32, bool Y_F32, int GBT, int UNROLL, bool ONE>
 __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -250,8 +316,12 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
     }
 
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the producers of A have finished
-    // ---- activations -> shared memory, in the order the fragments are read
-    // unit (row, group, t): k = 32*group + 8*t + {0,4,1,5,2,6,3,7}
+    // ---- activations -> shared memory in the order the fragments are read, one
+    // thread per 32-wide k group (unit t of a group: k = 32*group + 8*t + {0,4,1,5,2,6,3,7}),
+    // together with the correction entries of do_block: the GBT lanes that hold a
+    // block's groups are adjacent, so its sums need at most three shuffle steps
+    const int nblk = p.g_pad / GBT;
+    const int total_groups = p.M * p.g_pad;
     if constexpr (A_F32) {
         const float *a = static_cast<const float *>(p.a);
         __shared__ float warp_max[CONSUMER_WARPS];
@@ -276,65 +346,73 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
             }
             asm volatile("bar.sync 2, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
         }
-        const int units = p.M * p.g_pad * 4;
-        for (int u = threadIdx.x; u < units; u += CONSUMER_WARPS * 32) {
-            const int t = u & 3, grp = (u >> 2) % p.g_pad, m = (u >> 2) / p.g_pad;
-            const float inv = 1.0f / row_pow2[m];  // exact power of two
-            float hi[8], lo[8];
+        for (int base = warp * 32; base < total_groups; base += CONSUMER_WARPS * 32) {
+            const int idx = base + lane;
+            const bool valid = idx < total_groups;
+            const int grp = valid ? idx % p.g_pad : 0, m = valid ? idx / p.g_pad : 0;
+            GroupSums sh, sl;
+            if (valid) {
+                const float inv = 1.0f / row_pow2[m];  // exact power of two
+                const float *src = a + int64_t(m) * p.K + grp * 32;
+                const bool whole = p.vec_a && grp * 32 + 32 <= p.K;
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const int k = grp * 32 + t * 8 + i;
-                const float v = k < p.K ? a[int64_t(m) * p.K + k] * inv : 0.0f;
-                const float h = __half2float(__float2half_rn(v));
-                hi[i] = h;
-                lo[i] = v - h;
+                for (int t = 0; t < 4; t++) {
+                    float v[8], hi[8], lo[8];
+                    if (whole) {
+                        const float4 q0 = reinterpret_cast<const float4 *>(src)[2 * t];
+                        const float4 q1 = reinterpret_cast<const float4 *>(src)[2 * t + 1];
+                        v[0] = q0.x, v[1] = q0.y, v[2] = q0.z, v[3] = q0.w;
+                        v[4] = q1.x, v[5] = q1.y, v[6] = q1.z, v[7] = q1.w;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; i++)
+                            v[i] = grp * 32 + t * 8 + i < p.K ? src[t * 8 + i] : 0.0f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const float x = v[i] * inv;
+                        hi[i] = __half2float(__float2half_rn(x));
+                        lo[i] = __half2float(__float2half_rn(x - hi[i]));
+                    }
+                    stage_unit(&acts[(size_t(2 * m) * p.g_pad + grp) * 4 + t], hi, sh);
+                    stage_unit(&acts[(size_t(2 * m + 1) * p.g_pad + grp) * 4 + t], lo, sl);
+                }
             }
-            acts[(size_t(2 * m) * p.g_pad + grp) * 4 + t] =
-                make_uint4(pack_h2(hi[0], hi[4]), pack_h2(hi[1], hi[5]), pack_h2(hi[2], hi[6]), pack_h2(hi[3], hi[7]));
-            acts[(size_t(2 * m + 1) * p.g_pad + grp) * 4 + t] =
-                make_uint4(pack_h2(lo[0], lo[4]), pack_h2(lo[1], lo[5]), pack_h2(lo[2], lo[6]), pack_h2(lo[3], lo[7]));
+            const int blk = grp / GBT;
+            finish_block<GBT>(corr + (size_t(2 * m) * nblk + blk) * 4, sh.e0 + sh.e1, sh.o0 + sh.o1, lane, valid);
+            finish_block<GBT>(corr + (size_t(2 * m + 1) * nblk + blk) * 4, sl.e0 + sl.e1, sl.o0 + sl.o1, lane, valid);
         }
     } else {
         const __half *a = static_cast<const __half *>(p.a);
-        const int units = p.M * p.g_pad * 4;
-        for (int u = threadIdx.x; u < units; u += CONSUMER_WARPS * 32) {
-            const int t = u & 3, grp = (u >> 2) % p.g_pad, m = (u >> 2) / p.g_pad;
-            float v[8];
+        for (int base = warp * 32; base < total_groups; base += CONSUMER_WARPS * 32) {
+            const int idx = base + lane;
+            const bool valid = idx < total_groups;
+            const int grp = valid ? idx % p.g_pad : 0, m = valid ? idx / p.g_pad : 0;
+            GroupSums sg;
+            if (valid) {
+                const __half *src = a + int64_t(m) * p.K + grp * 32;
+                const bool whole = p.vec_a && grp * 32 + 32 <= p.K;
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const int k = grp * 32 + t * 8 + i;
-                v[i] = k < p.K ? __half2float(a[int64_t(m) * p.K + k]) : 0.0f;
+                for (int t = 0; t < 4; t++) {
+                    float v[8];
+                    if (whole) {
+                        const uint4 q = reinterpret_cast<const uint4 *>(src)[t];
+                        const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&qw[i]));
+                            v[2 * i] = f.x;
+                            v[2 * i + 1] = f.y;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; i++)
+                            v[i] = grp * 32 + t * 8 + i < p.K ? __half2float(src[t * 8 + i]) : 0.0f;
+                    }
+                    stage_unit(&acts[(size_t(m) * p.g_pad + grp) * 4 + t], v, sg);
+                }
             }
-            acts[(size_t(m) * p.g_pad + grp) * 4 + t] =
-                make_uint4(pack_h2(v[0], v[4]), pack_h2(v[1], v[5]), pack_h2(v[2], v[6]), pack_h2(v[3], v[7]));
-        }
-    }
-    asm volatile("bar.sync 2, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
-    {
-        // block sums of the staged (fp16) activations, negated and split in three
-        const int nblk = p.g_pad / GBT;
-        const __half *ah = reinterpret_cast<const __half *>(acts);
-        for (int u = warp; u < p.rows * nblk; u += CONSUMER_WARPS) {
-            const int row = u / nblk, blk = u % nblk;
-            const __half *src = ah + (size_t(row) * p.g_pad + size_t(blk) * GBT) * 32;
-            double sum = 0.0;  // exact: fp16 terms span fewer than 53 bits
-#pragma unroll
-            for (int i = 0; i < GBT; i++)
-                sum += double(__half2float(src[i * 32 + lane]));
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1)
-                sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (lane == 0) {
-                const __half h0 = __double2half(sum);
-                const double r1 = sum - double(__half2float(h0));
-                const __half h1 = __double2half(r1);
-                const __half h2 = __double2half(r1 - double(__half2float(h1)));
-                uint32_t *dst = corr + size_t(u) * 4;
-                dst[0] = uint32_t(__half_as_ushort(__hneg(h0)));
-                dst[1] = uint32_t(__half_as_ushort(__hneg(h1)));
-                dst[2] = uint32_t(__half_as_ushort(__hneg(h2)));
-                dst[3] = 0u;
-            }
+            finish_block<GBT>(corr + (size_t(m) * nblk + grp / GBT) * 4, sg.e0 + sg.e1, sg.o0 + sg.o1, lane, valid);
         }
     }
     asm volatile("bar.sync 2, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
@@ -357,9 +435,11 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
     const uint32_t s_rel = p.s_off + uint32_t((panel * p.KC + b_first) * 8 + g) * SCALE_PAIR;
     const uint32_t z_rel = p.z_off + uint32_t((panel * p.KC + b_first) * 8 + g);
     UnpackConsts uc;
-    // opaque to the optimiser, so the two constants stay in registers
-    asm volatile("mov.u32 %0, 0x00F000F0;\n\tmov.u32 %1, 0x54005400;\n\tmov.u32 %2, 0;"
-                 : "=r"(uc.mask), "=r"(uc.magic), "=r"(uc.zero));
+    // opaque to the optimiser, so the constants stay in registers
+    asm volatile("mov.u32 %0, 0x003C003C;\n\tmov.u32 %1, 0x5C005C00;\n\tmov.u32 %2, 0x03C003C0;\n\t"
+                 "mov.u32 %3, 0x4C004C00;\n\tmov.u32 %4, 0x00F000F0;\n\tmov.u32 %5, 0x54005400;"
+                 : "=r"(uc.mask_e), "=r"(uc.magic_e), "=r"(uc.mask_o), "=r"(uc.magic_o), "=r"(uc.mask_z),
+                   "=r"(uc.magic_z));
     const uint32_t corr0 = umma::smem_u32(corr) + uint32_t((act_row * (p.g_pad / GBT)) * 4 + t) * 4u;
     constexpr uint32_t C_STEP = 16u;
     constexpr int BIG = GBT == 1 ? 9 : (GBT == 2 ? 4 : 2);
@@ -386,7 +466,7 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
 #define OVK_RUN(COUNT)                                                                                      \
     for (; left >= (COUNT); left -= (COUNT)) {                                                              \
         _Pragma("unroll") for (int j = 0; j < (COUNT); j++)                                                 \
-            do_block<SCALE_F32, GBT>(acc, uc, wa + j * W_STEP, sa + j * S_STEP, za + j * Z_STEP,            \
+            do_block<SCALE_F32, GBT, ONE>(acc, uc, wa + j * W_STEP, sa + j * S_STEP, za + j * Z_STEP,            \
                                      aa + j * A_STEP, ca + j * C_STEP);                                     \
         wa += (COUNT) * W_STEP;                                                                             \
         sa += (COUNT) * S_STEP;                                                                             \
@@ -487,6 +567,9 @@ nbits_decode_pack_kernel(const uint32_t *__restrict__ src_w, const void *__restr
             if (blk < n_blocks) {
                 if (col_lo < N) v.x = src_w[int64_t(col_lo) * words_per_row + word];
                 if (col_hi < N) v.y = src_w[int64_t(col_hi) * words_per_row + word];
+                // nibble j of a word moves from bits 4j.. to bits 4j+2.. (mod 32), see do_block
+                v.x = __funnelshift_l(v.x, v.x, 2);
+                v.y = __funnelshift_l(v.y, v.y, 2);
             }
             reinterpret_cast<uint2 *>(tile)[r] = v;
         } else {
@@ -528,10 +611,10 @@ size_t decode_smem(const ovk_nbits_weight *w, int rows)
            CONSUMER_WARPS * 32 * 16 + 32 + 64 + 128;
 }
 
-template <bool SF, bool AF, bool YF, int GB, int UN>
-int32_t launch_decode_gb(ovk_ctx *ctx, const DecParams &p, size_t smem)
+template <bool SF, bool AF, bool YF, int GB, int UN, bool ONE>
+int32_t launch_decode_one(ovk_ctx *ctx, const DecParams &p, size_t smem)
 {
-    OVK_CUDA(ctx, cudaFuncSetAttribute(nbits_decode_kernel<SF, AF, YF, GB, UN>,
+    OVK_CUDA(ctx, cudaFuncSetAttribute(nbits_decode_kernel<SF, AF, YF, GB, UN, ONE>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     const unsigned grid = unsigned(std::min<int>(p.ntiles, ctx->sm_count));
     cudaLaunchConfig_t cfg = {};
@@ -544,9 +627,19 @@ int32_t launch_decode_gb(ovk_ctx *ctx, const DecParams &p, size_t smem)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    OVK_CUDA(ctx, cudaLaunchKernelEx(&cfg, nbits_decode_kernel<SF, AF, YF, GB, UN>, p));
+    OVK_CUDA(ctx, cudaLaunchKernelEx(&cfg, nbits_decode_kernel<SF, AF, YF, GB, UN, ONE>, p));
     OVK_LAUNCHED(ctx, "nbits_decode_mma");
     return OVK_OK;
+}
+
+template <bool SF, bool AF, bool YF, int GB, int UN>
+int32_t launch_decode_gb(ovk_ctx *ctx, const DecParams &p, size_t smem)
+{
+    if constexpr (!AF) {
+        if (p.rows == 1)  // one fp16 row: the odd batch columns are never stored
+            return launch_decode_one<SF, AF, YF, GB, UN, true>(ctx, p, smem);
+    }
+    return launch_decode_one<SF, AF, YF, GB, UN, false>(ctx, p, smem);
 }
 
 template <bool SF, bool AF, bool YF>
@@ -686,6 +779,7 @@ int32_t ovk_nbits_decode(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
         p.tile_bytes = w->dec_tile_bytes;
         p.g_pad = int(g_pad);
         p.rows = p.M * per_row;
+        p.vec_a = aligned_to(p.a, 16) && (a_row % 16 == 0);
         p.status = ctx->dev_status;
         const size_t smem = decode_smem(w, p.rows);
         OVK_REQUIRE(ctx, smem <= ctx->smem_optin, "MatMulNBits decode: %zu bytes of shared memory needed", smem);
