@@ -37,9 +37,9 @@ namespace {
 
 constexpr int CONSUMER_WARPS = 16;
 constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
-constexpr int STAGES = 4;
-constexpr int SLICES = 8;  // bulk copies per tile
-constexpr uint32_t STAGE_MAX = 44 * 1024;
+constexpr int MAX_STAGES = 4;  // ring depth is chosen per launch: as many tiles as fit beside the activations
+constexpr int SLICES = 8;      // bulk copies per tile
+constexpr uint32_t STAGE_MAX = 70 * 1024;
 constexpr size_t ACT_MAX = 64 * 1024;
 constexpr long long WAIT_CYCLES = 2000000000ll;
 
@@ -53,6 +53,7 @@ struct DecParams {
     int g_pad;  // k32 groups covered by the tiles (>= ceil(K/32))
     int rows;   // batch columns in use: M, or 2M for split f32 activations
     int vec_a;  // rows of A start on 16-byte boundaries: groups are read as 128-bit vectors
+    int stages; // depth of the weight ring, 2..MAX_STAGES
     int *status;
 };
 
@@ -69,12 +70,6 @@ __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
         if (clock64() - t0 > WAIT_CYCLES)
             return false;
     }
-}
-
-__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b)
-{
-    __half2 r = __hsub2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
-    return *reinterpret_cast<uint32_t *>(&r);
 }
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -254,18 +249,18 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t *stage_base = smem;
-    uint4 *acts = reinterpret_cast<uint4 *>(smem + size_t(STAGES) * p.tile_bytes);
+    uint4 *acts = reinterpret_cast<uint4 *>(smem + size_t(p.stages) * p.tile_bytes);
     // per (batch column, block): half2(-part_t, 0) for t = 0..3, the three fp16 parts of the block's activation sum
     uint32_t *corr = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(acts) + size_t(p.rows) * p.g_pad * 64);
     float4 *red = reinterpret_cast<float4 *>(corr + size_t(p.rows) * (p.g_pad / GBT) * 4);
     float *row_pow2 = reinterpret_cast<float *>(red + CONSUMER_WARPS * 32);
     uint64_t *full = reinterpret_cast<uint64_t *>(row_pow2 + 8);
-    uint64_t *empty = full + STAGES;
+    uint64_t *empty = full + MAX_STAGES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
+        for (int s = 0; s < p.stages; s++) {
             umma::mbar_init(&full[s], 1);
             umma::mbar_init(&empty[s], CONSUMER_WARPS);
         }
@@ -288,12 +283,11 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
         const uint32_t slice = ((p.tile_bytes / SLICES) + 15u) & ~15u;
         const uint32_t my_off = min(uint32_t(lane) * slice, p.tile_bytes);
         const uint32_t my_len = lane < SLICES ? min(slice, p.tile_bytes - my_off) : 0u;
-        int seq = 0;
+        int s = 0;
+        uint32_t ph = 0;
         bool alive = true;
         for (int u = blockIdx.x; u < p.ntiles && alive; u += gridDim.x) {
-            for (int kc = 0; kc < p.NKC; kc++, seq++) {
-                const int s = seq % STAGES;
-                const uint32_t ph = (seq / STAGES) & 1;
+            for (int kc = 0; kc < p.NKC; kc++) {
                 bool ok = true;
                 if (lane == 0) {
                     ok = wait_bounded(&empty[s], ph ^ 1);
@@ -310,6 +304,10 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
                 if (my_len)
                     umma::bulk_load_1d(stage_base + size_t(s) * p.tile_bytes + my_off,
                                        p.packed + (size_t(u) * p.NKC + kc) * p.tile_bytes + my_off, my_len, &full[s]);
+                if (++s == p.stages) {
+                    s = 0;
+                    ph ^= 1;
+                }
             }
         }
         return;
@@ -444,12 +442,11 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
     constexpr uint32_t C_STEP = 16u;
     constexpr int BIG = GBT == 1 ? 9 : (GBT == 2 ? 4 : 2);
     bool dead = false;
-    int seq = 0;
+    int s = 0;
+    uint32_t ph = 0;
     for (int u = blockIdx.x; u < p.ntiles; u += gridDim.x) {
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (int kc = 0; kc < p.NKC; kc++, seq++) {
-            const int s = seq % STAGES;
-            const uint32_t ph = (seq / STAGES) & 1;
+        for (int kc = 0; kc < p.NKC; kc++) {
             if (!dead && !wait_bounded(&full[s], ph)) {
                 dead = true;
                 if (lane == 0)
@@ -481,6 +478,10 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
                 __syncwarp();
                 if (lane == 0)
                     umma::mbar_arrive(&empty[s]);
+            }
+            if (++s == p.stages) {
+                s = 0;
+                ph ^= 1;
             }
         }
         // ---- combine the warps that shared a panel (none when a warp owns a
@@ -604,10 +605,10 @@ nbits_decode_pack_kernel(const uint32_t *__restrict__ src_w, const void *__restr
     }
 }
 
-size_t decode_smem(const ovk_nbits_weight *w, int rows)
+size_t decode_smem(const ovk_nbits_weight *w, int rows, int stages)
 {
     const size_t g_pad = size_t(w->dec_nkc) * w->dec_kc * w->dec_gb;
-    return size_t(STAGES) * w->dec_tile_bytes + size_t(rows) * g_pad * 64 + size_t(rows) * (g_pad / w->dec_gb) * 16 +
+    return size_t(stages) * w->dec_tile_bytes + size_t(rows) * g_pad * 64 + size_t(rows) * (g_pad / w->dec_gb) * 16 +
            CONSUMER_WARPS * 32 * 16 + 32 + 64 + 128;
 }
 
@@ -670,28 +671,49 @@ int32_t ovk_nbits_decode_prepack(ovk_ctx *ctx, ovk_nbits_weight *w)
     const int64_t nb = w->n_blocks;
     const uint32_t pb_bytes = uint32_t(gb) * 256u + 16u * sz + 8u;  // one panel x one block
     const int64_t np = ceil_div64(w->n, 16);
-    int P = 1, KC, NKC;
-    if (ceil_div64(np, CONSUMER_WARPS) * 2 >= ctx->sm_count && uint32_t(CONSUMER_WARPS) * pb_bytes <= STAGE_MAX) {
-        // wide weights: one panel per warp, K cut into chunks that fit a stage;
-        // a warp keeps its columns for the whole of K, so warps never exchange anything
-        P = CONSUMER_WARPS;
-        const int kc_max = int(STAGE_MAX / (uint32_t(P) * pb_bytes));
-        NKC = int(ceil_div64(nb, kc_max));
-        KC = int(ceil_div64(nb, NKC));
-    } else if (nb * pb_bytes <= STAGE_MAX) {
-        KC = int(nb);
-        NKC = 1;
-        // as many panels per tile as fit, but not so many that SMs go without a tile
-        while (2 * P < CONSUMER_WARPS && int64_t(2 * P) * nb * pb_bytes <= STAGE_MAX &&
-               ceil_div64(np, 2 * P) >= ctx->sm_count)
-            P *= 2;
-    } else {
-        const int kc_max = int(STAGE_MAX / pb_bytes);
-        if (kc_max < 1)
-            return OVK_OK;
-        NKC = int(ceil_div64(nb, kc_max));
-        KC = int(ceil_div64(nb, NKC));
+    // Tile shape: P panels (a power of two up to the warp count; 16 / P warps share
+    // a panel and split its blocks) x KC blocks, K cut into NKC chunks that fit a
+    // stage.  Chosen for the shortest critical path, counted in blocks the
+    // busiest warp of the busiest CTA works through: per chunk its share of the
+    // blocks plus ~0.4 for the hand-over, per tile ~2 for the exchange between
+    // warps that share a panel (~0.5 for the store alone when a warp keeps its
+    // columns for the whole of K).  A CTA with a single tile gets chunks of at
+    // most 32 KB so that arrival and arithmetic overlap.  A larger P is given up
+    // only for a gain of more than a tenth: its copies are larger.
+    if (pb_bytes > STAGE_MAX)
+        return OVK_OK;
+    int P = 0, KC = 0, NKC = 0;
+    double best = 0.0;
+    for (int cand = CONSUMER_WARPS; cand >= 1; cand /= 2) {
+        const uint32_t chunk_block = uint32_t(cand) * pb_bytes;  // bytes of one block across the tile's panels
+        if (chunk_block > STAGE_MAX)
+            continue;
+        const int wp = CONSUMER_WARPS / cand;
+        const int64_t waves = ceil_div64(ceil_div64(np, cand), ctx->sm_count);
+        int64_t kc_cap = STAGE_MAX / chunk_block;
+        if (waves == 1)
+            kc_cap = std::max<int64_t>(1, std::min<int64_t>(kc_cap, 32768 / chunk_block));
+        const int nkc_min = int(ceil_div64(nb, kc_cap));
+        int nkc_best = nkc_min;
+        double chunk_cost = 0.0;
+        for (int nkc = nkc_min; nkc <= nkc_min + 7 && nkc <= nb; nkc++) {
+            const int64_t kc = ceil_div64(nb, nkc);
+            const double c = double(nkc) * (double(ceil_div64(kc, wp)) + 0.4);
+            if (nkc == nkc_min || c < chunk_cost) {
+                chunk_cost = c;
+                nkc_best = nkc;
+            }
+        }
+        const double cost = double(waves) * (chunk_cost + (wp > 1 ? 2.0 : 0.5));
+        if (P == 0 || cost < 0.9 * best) {
+            best = cost;
+            P = cand;
+            NKC = nkc_best;
+            KC = int(ceil_div64(nb, nkc_best));
+        }
     }
+    if (P == 0)
+        return OVK_OK;
     const int ntiles = int(ceil_div64(np, P));
     const uint32_t s_off = uint32_t(P) * KC * gb * 256u;
     const uint32_t z_off = s_off + uint32_t(P) * KC * 16u * sz;
@@ -731,16 +753,39 @@ int32_t ovk_nbits_decode_prepack(ovk_ctx *ctx, ovk_nbits_weight *w)
     return OVK_OK;
 }
 
-// Rows of A one launch can take: what fits in shared memory beside the weight
-// ring, at most 8 batch columns (an f32 row takes two).
-static int decode_rows_per_launch(const ovk_ctx *ctx, const ovk_nbits_weight *w, int32_t a_dtype)
+// How one call is cut into launches: batch columns per launch (at most 8; an
+// f32 row takes two) and the depth of the weight ring.  Every launch streams
+// the whole weight, so all rows in one launch comes first, then a deeper ring.
+struct DecodePlan {
+    int rows = 0;  // rows of A per launch, 0 = does not fit
+    int stages = 0;
+};
+static DecodePlan decode_plan(const ovk_ctx *ctx, const ovk_nbits_weight *w, int32_t a_dtype, int64_t m)
 {
+    const int per_row = a_dtype == OVK_FLOAT ? 2 : 1;
     const size_t g_pad = size_t(w->dec_nkc) * w->dec_kc * w->dec_gb;
-    const size_t fixed = decode_smem(w, 0);
-    if (fixed >= ctx->smem_optin)
-        return 0;
-    const size_t cols = std::min<size_t>(8, std::min(ACT_MAX, ctx->smem_optin - fixed) / (g_pad * 64 + (g_pad / w->dec_gb) * 16));
-    return int(cols) / (a_dtype == OVK_FLOAT ? 2 : 1);
+    const size_t per_col = g_pad * 64 + (g_pad / w->dec_gb) * 16;
+    const int want = int(std::min<int64_t>(std::max<int64_t>(m, 1), 8 / per_row));
+    const int work = w->dec_nkc * int((w->dec_ntiles + ctx->sm_count - 1) / ctx->sm_count);  // tiles of the busiest CTA
+    DecodePlan best;
+    for (int stages = std::min(MAX_STAGES, std::max(2, work)); stages >= 2; stages--) {
+        const size_t fixed = decode_smem(w, 0, stages);
+        if (fixed >= ctx->smem_optin)
+            continue;
+        const size_t cols = std::min<size_t>(8, std::min(ACT_MAX, ctx->smem_optin - fixed) / per_col);
+        const int rows = std::min(want, int(cols) / per_row);
+        if (rows > best.rows) {
+            best.rows = rows;
+            best.stages = stages;
+        }
+        if (rows == want)
+            break;
+    }
+    if (best.rows == 0 && decode_smem(w, per_row, 1) <= ctx->smem_optin) {
+        best.rows = 1;  // a single stage still beats the general kernel
+        best.stages = 1;
+    }
+    return best;
 }
 
 // Up to 8 fp16 rows (4 f32 rows) per launch; more rows than that belong to
@@ -749,7 +794,7 @@ bool ovk_nbits_decode_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int
                               int32_t y_dtype)
 {
     (void)y_dtype;
-    return w->decode && m <= 8 && decode_rows_per_launch(ctx, w, a_dtype) >= 1;
+    return w->decode && m <= 8 && decode_plan(ctx, w, a_dtype, m).rows >= 1;
 }
 
 int32_t ovk_nbits_decode(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype, int64_t m,
@@ -759,7 +804,9 @@ int32_t ovk_nbits_decode(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
     OVK_REQUIRE(ctx, aligned_to(a, af ? 4 : 2) && aligned_to(y, yf ? 4 : 2), "MatMulNBits: A or Y is misaligned");
     const size_t g_pad = size_t(w->dec_nkc) * w->dec_kc * w->dec_gb;
     const int per_row = af ? 2 : 1;
-    const int rows_max = std::max(1, decode_rows_per_launch(ctx, w, a_dtype));  // rows of A per launch
+    const DecodePlan plan = decode_plan(ctx, w, a_dtype, m);
+    OVK_REQUIRE(ctx, plan.rows >= 1, "MatMulNBits decode: the tile does not fit in shared memory");
+    const int rows_max = plan.rows;  // rows of A per launch
     const size_t a_row = size_t(w->k) * (af ? 4 : 2), y_row = size_t(w->n) * (yf ? 4 : 2);
     for (int64_t m0 = 0; m0 < m; m0 += rows_max) {
         DecParams p = {};
@@ -781,7 +828,8 @@ int32_t ovk_nbits_decode(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
         p.rows = p.M * per_row;
         p.vec_a = aligned_to(p.a, 16) && (a_row % 16 == 0);
         p.status = ctx->dev_status;
-        const size_t smem = decode_smem(w, p.rows);
+        p.stages = plan.stages;
+        const size_t smem = decode_smem(w, p.rows, plan.stages);
         OVK_REQUIRE(ctx, smem <= ctx->smem_optin, "MatMulNBits decode: %zu bytes of shared memory needed", smem);
         int32_t rc;
 #define GO(SF, AF, YF) rc = launch_decode<SF, AF, YF>(ctx, p, smem)
