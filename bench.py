@@ -71,12 +71,26 @@ class ClockSampler:
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def lines(self) -> int:
+        try:
+            return sum(1 for _ in open(self.path))
+        except Exception:
+            return 0
+
+    def wait_first_sample(self, keep_busy, limit_s: float = 4.0) -> int:
+        """Runs `keep_busy` until nvidia-smi has written its first line; returns the line count."""
+        t0 = time.perf_counter()
+        while self.proc is not None and self.lines() == 0 and time.perf_counter() - t0 < limit_s:
+            keep_busy()
+        return self.lines()
+
+    def stop(self, skip: int = 0):
+        """Summary of the samples after the first `skip` lines."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -86,7 +100,7 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in open(self.path):
+        for line in list(open(self.path))[skip:]:
             f = [c.strip() for c in line.split(",")]
             if len(f) < 9:
                 continue
@@ -251,45 +265,83 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
             ops.append((f"L{layer}.{name}", k, n, make_weight(torch, ctx, k, n, BLOCK, gen)))
     lm = make_weight(torch, ctx, LM_HEAD[1], LM_HEAD[2], BLOCK, gen)
     acts = {k: torch.randn((1, k), device="cuda", generator=gen).to(torch.float16) for k in {HIDDEN, Q_OUT, FF}}
-    outs = {n: torch.empty((1, n), dtype=torch.float16, device="cuda") for n in {Q_OUT, KV_OUT, HIDDEN, FF, VOCAB}}
+    # one output buffer per projection of a layer (k/v and gate/up run side by side) + the logits
+    outs = {name: torch.empty((1, n), dtype=torch.float16, device="cuda") for name, _, n in LAYER_SHAPES}
+    outs[VOCAB] = torch.empty((1, VOCAB), dtype=torch.float16, device="cuda")
     step_bytes = sum(nbits_bytes(1, k, n, BLOCK) for _, k, n, _ in ops) + nbits_bytes(1, LM_HEAD[1], LM_HEAD[2], BLOCK)
     lm_bytes = nbits_bytes(1, LM_HEAD[1], LM_HEAD[2], BLOCK)
     n_gemv = len(ops) + 1
     ctx.flush()
 
+    # A decoder layer's data flow: q, k and v read the same hidden state, and so
+    # do gate and up, so those launches are independent and are put on parallel
+    # branches (side streams that fork from and join the main one: in the
+    # captured graph these are just edges); o waits for q/k/v, down for gate/up.
+    side = []
+    if not args.serial:
+        for _ in range(2):
+            s_side = torch.cuda.Stream()
+            with torch.cuda.stream(s_side):
+                side.append((s_side, ovk_b200.Context(local)))
+    BRANCHES = {"k": 0, "v": 1, "up": 0}   # projection -> side branch; the rest stay on the main stream
+    FORK_BEFORE = {"q": (0, 1), "gate": (0,)}
+    JOIN_BEFORE = {"o": (0, 1), "down": (0,)}
+
     def layers_eager():
-        for _, k, n, w in ops:
-            ctx.matmul_nbits(w, acts[k], out=outs[n])
+        for label, k, n, w in ops:
+            name = label.split(".", 1)[1]
+            if side:
+                for b in FORK_BEFORE.get(name, ()):
+                    side[b][0].wait_stream(stream)
+                for b in JOIN_BEFORE.get(name, ()):
+                    stream.wait_stream(side[b][0])
+            if side and name in BRANCHES:
+                side[BRANCHES[name]][1].matmul_nbits(w, acts[k], out=outs[name])
+            else:
+                ctx.matmul_nbits(w, acts[k], out=outs[name])
 
     # The per-layer GEMVs are launch-bound (0.2-4.6 MB each): the step replays
     # them from a CUDA graph, as the reference replays its captured decode step
     # (crates/onnx-vulkan-core/src/plan.rs, vk-compute stream.rs:537-629).
     layers_eager()
     torch.cuda.synchronize()
-    graph, replay = None, "eager launches"
+    # The whole step is one CUDA graph.  A second graph of the same step has the
+    # lm_head launch between two event-record nodes: it is replayed after the
+    # timed region to read that launch's duration from inside a step.
+    graph, probe, replay = None, None, "eager launches"
+    g0 = torch.cuda.Event(enable_timing=True, external=True)
+    g1 = torch.cuda.Event(enable_timing=True, external=True)
     if not args.no_graph:
         try:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 layers_eager()
-            replay = "CUDA graph replay of the per-layer GEMVs + one eager lm_head launch"
+                ctx.matmul_nbits(lm, acts[HIDDEN], out=outs[VOCAB])
+            probe = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(probe, stream=stream):
+                layers_eager()
+                g0.record(stream)
+                ctx.matmul_nbits(lm, acts[HIDDEN], out=outs[VOCAB])
+                g1.record(stream)
+            replay = "one CUDA graph replay per step (%s)" % (
+                "q|k|v and gate|up on parallel branches" if side else "one serial chain")
         except Exception as e:  # capture refused: fall back to eager launches, say so
             graph, replay = None, "eager launches (graph capture failed: %s)" % str(e)[:80]
             torch.cuda.synchronize()
 
-    lm_events = []
+    lm_samples = []
 
     def step(timed_step: bool):
         if graph is not None:
             graph.replay()
-        else:
-            layers_eager()
+            return
+        layers_eager()
         if timed_step:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             ctx.matmul_nbits(lm, acts[HIDDEN], out=outs[VOCAB])
             e1.record()
-            lm_events.append((e0, e1))
+            lm_samples.append((e0, e1))
         else:
             ctx.matmul_nbits(lm, acts[HIDDEN], out=outs[VOCAB])
 
@@ -301,37 +353,85 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
     for _ in range(args.warmup):
         step(False)
     sync_all()
+    # clocks are sampled while the GPU runs these steps: nvidia-smi takes a few
+    # hundred ms to produce its first line, so the same steps keep running
+    # (untimed) until it has, and for 0.4 s after the timed region; only lines
+    # written from the start of the timed region on are summarised
     sampler = ClockSampler(local)
+    skip = 0
     if rank == 0:
         sampler.start()
+
+        def busy():
+            for _ in range(20):
+                step(False)
+            torch.cuda.synchronize()
+        skip = sampler.wait_first_sample(busy)
+    sync_all()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     for _ in range(args.steps):
         step(True)
     t1.record()
+    if rank == 0:
+        w0 = time.perf_counter()
+        while time.perf_counter() - w0 < 0.4:
+            for _ in range(20):
+                step(False)
+            torch.cuda.synchronize()
     sync_all()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(skip) if rank == 0 else None
+    if clocks is not None:
+        clocks["window"] = "the timed steps and 0.4 s of the same steps after them"
     launches = n_gemv * args.steps  # one kernel of this library per GEMV (graph replays launch them too)
     ms = torch.tensor([t0.elapsed_time(t1)], device="cuda")
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_total = float(ms.item())
-    lm_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in lm_events)
+    # ---- the dominant launch on its own: the lm_head GEMV (30 % of the step's bytes)
+    # (a) inside a step, between two event-record nodes (which also keep it from
+    #     overlapping its neighbours): the record nodes hold the last replay's stamps
+    if probe is not None:
+        lm_times = []
+        for _ in range(8):
+            probe.replay()
+            torch.cuda.synchronize()
+            lm_times.append(g0.elapsed_time(g1))
+        lm_in_step_ms = statistics.median(lm_times)
+    else:
+        lm_in_step_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in lm_samples)
+    # (b) back to back: launches over distinct copies of the weight (3 x 175 MB > L2),
+    #     one event pair around the run; consecutive launches overlap their ramps
+    lm_copies = [lm] + [make_weight(torch, ctx, LM_HEAD[1], LM_HEAD[2], BLOCK, gen) for _ in range(2)]
+    ctx.flush()
+    for w in lm_copies:
+        ctx.matmul_nbits(w, acts[HIDDEN], out=outs[VOCAB])
+    b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    lm_reps = 8
+    torch.cuda.synchronize()
+    b0.record()
+    for _ in range(lm_reps):
+        for w in lm_copies:
+            ctx.matmul_nbits(w, acts[HIDDEN], out=outs[VOCAB])
+    b1.record()
+    torch.cuda.synchronize()
+    lm_ms = b0.elapsed_time(b1) / (lm_reps * len(lm_copies))
+    del lm_copies
     lm_kernel = ctx.last_kernel
 
     # ------------------------------------------------------------ end to end
-    # the call a user makes: host activations in, logits out, every step
+    # the call a user makes, every step: the step's inputs (the three activation
+    # vectors the GEMVs read; the weights are resident, as in any decode loop)
+    # come from pinned host memory, the step runs, the logits go back to the host
     pinned_in = {k: acts[k].cpu().pin_memory() for k in acts}
     pinned_out = torch.empty((1, VOCAB), dtype=torch.float16).pin_memory()
-    h2d = sum(k * 2 for _, k, _, _ in ops) + HIDDEN * 2
+    h2d = sum(k * 2 for k in acts)
     d2h = VOCAB * 2
 
     def e2e_step():
-        for _, k, n, w in ops:
+        for k in acts:
             acts[k].copy_(pinned_in[k], non_blocking=True)
-            ctx.matmul_nbits(w, acts[k], out=outs[n])
-        acts[HIDDEN].copy_(pinned_in[HIDDEN], non_blocking=True)
-        ctx.matmul_nbits(lm, acts[HIDDEN], out=outs[VOCAB])
+        step(False)
         pinned_out.copy_(outs[VOCAB], non_blocking=True)
         torch.cuda.synchronize()
 
@@ -351,7 +451,7 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
     peaks, peak_kind = measured_peaks()
     extra = None
     if not args.no_extra:
-        del ops, lm, graph
+        del ops, lm, graph, probe
         torch.cuda.empty_cache()
         extra = extra_workloads(torch, dist, ctx, world, rank, gen, peaks)
 
@@ -373,6 +473,10 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
             "roofline": {"bound": "hbm", "kernel": lm_kernel + " (lm_head K=1152 N=262144)", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                          "of": peak_kind, "bytes_per_launch": lm_bytes, "ms_per_launch": lm_ms,
+                         "timing": "24 launches back to back over 3 copies of the weight, one CUDA event pair",
+                         "ms_per_launch_inside_step": lm_in_step_ms,
+                         "frac_inside_step": lm_bytes / (lm_in_step_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                         "whole_step_frac": world * step_bytes * args.steps / (ms_total * 1e-3) / 1e9 / (world * peaks["hbm_gbs"]),
                          "frac_of_nominal_8tbs": achieved / 8000.0, "traffic": traffic},
             "e2e": {"value": e2e_gbs, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps},
@@ -503,6 +607,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the prefill / int8 / conv lines")
     ap.add_argument("--no-graph", action="store_true", help="launch the per-layer GEMVs eagerly")
+    ap.add_argument("--serial", action="store_true", help="one serial chain of GEMVs instead of parallel q|k|v and gate|up")
     ap.add_argument("--one", default=None, choices=["lm_head", "prefill", "int8", "conv"],
                     help="run one operator three times and exit (small target for an ncu capture)")
     args = ap.parse_args()
