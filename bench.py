@@ -189,6 +189,30 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
                                               "kernel": ctx.last_kernel, "ms_compute": ms_c,
                                               "tflops_compute": 2.0 * 512 * HIDDEN * VOCAB / (ms_c * 1e-3) / 1e12}
         del w, a, y
+        # ---- the launches either side of the lm_head GEMV in a decode step: greedy ArgMax over the
+        # logits and the int4 embedding row of the token it picked (read on the device, no round trip)
+        nb = HIDDEN // BLOCK
+        table = torch.randint(0, 256, (VOCAB, HIDDEN // 2), dtype=torch.uint8, device="cuda", generator=gen)
+        sc = (torch.rand((VOCAB, nb), device="cuda", generator=gen) * 0.018 + 0.002).to(torch.float16)
+        zp = torch.randint(0, 256, (VOCAB, (nb + 1) // 2), dtype=torch.uint8, device="cuda", generator=gen)
+        logits = torch.randn((1, VOCAB), device="cuda", generator=gen).to(torch.float16)
+        tok = torch.empty((1,), dtype=torch.int64, device="cuda")
+        row = torch.empty((1, HIDDEN), dtype=torch.float16, device="cuda")
+
+        def neighbours():
+            ctx.argmax(logits, out=tok)
+            ctx.gather_block_quantized(table, tok, sc, zp, BLOCK, out=row)
+        g = torch.cuda.CUDAGraph()
+        neighbours()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=torch.cuda.current_stream()):
+            for _ in range(20):
+                neighbours()
+        ms_n = timed(torch, dist, 1, g.replay, 10) / 20
+        out["decode_step_neighbours"] = {"ops": "ArgMax over 262144 fp16 logits + GatherBlockQuantized of one 1152-wide int4 row",
+                                         "kernels": ["argmax", ctx.last_kernel], "us_per_pair": ms_n * 1e3,
+                                         "bytes": VOCAB * 2 + HIDDEN // 2 + nb * 2 + HIDDEN * 2}
+        del g, table, sc, zp, logits
 
     # ---- dynamic int8 encoder GEMMs, Parakeet-shaped (config 3): replicas
     t = 1000

@@ -52,6 +52,7 @@ typedef enum ovk_dtype {
     OVK_UINT8 = 2,
     OVK_INT8 = 3,
     OVK_INT32 = 6,
+    OVK_INT64 = 7,
     OVK_FLOAT16 = 10
 } ovk_dtype;
 
@@ -217,6 +218,34 @@ OVK_API int32_t ovk_qlinear_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const 
 OVK_API int32_t ovk_requantize(ovk_ctx *ctx, const int32_t *acc, int64_t count, int64_t inner,
                                int64_t axis_len, const int32_t *bias, const float *ratio,
                                int32_t y_zp, int32_t y_signed, void *out);
+
+/* ------------------------------------- neighbours of the lm_head product
+ * interp::gather_block_quantized (interp.rs:2874-2990, kernel
+ * shaders/gather_block_quantized.rs:26-57): out[j, c] = (unpack(table[idx[j], c])
+ * - zp) * scale for a [rows, cols/2] u8 table of 4-bit elements (element 2i in
+ * the low nibble), scales [rows, cols/block_size] f32 or f16, zero points
+ * [rows, ceil(n_blocks/2)] u8 nibble packed (NULL = implicit 8).  Negative
+ * indices count from the end.  out is [count, cols] f32 or f16.
+ * indices are int32 or int64 (indices_dtype).  With indices_on_host = 1 they
+ * are a HOST array: an index outside the table is refused before anything is
+ * enqueued, as the reference does.  With 0 they are read on the device (the
+ * token a previous ovk_argmax produced, no round trip): an index outside the
+ * table writes a row of zeros and makes the next ovk_flush return
+ * OVK_INVALID_ARGUMENT. */
+OVK_API int32_t ovk_gather_block_quantized(ovk_ctx *ctx, const void *table, const void *scales,
+                                           int32_t scales_dtype, const void *zero_points,
+                                           int64_t rows, int64_t cols, int64_t bits,
+                                           int64_t block_size, const void *indices,
+                                           int32_t indices_dtype, int32_t indices_on_host,
+                                           int64_t count, void *out, int32_t out_dtype);
+/* ArgMax over one axis, first occurrence (interp::arg_extreme_axis, interp.rs
+ * :8552-8690; Outputs::argmax executor.rs:379; kernels shaders/reduction.rs
+ * :76-190): x is [outer, c, inner] f32 or f16 on the device, out [outer*inner]
+ * int64 on the device.  As in the reference's kernels a value is a candidate
+ * only if it is greater than -FLT_MAX (NaN and -inf never are) and a row
+ * without candidates answers 0. */
+OVK_API int32_t ovk_argmax(ovk_ctx *ctx, const void *x, int32_t x_dtype, int64_t outer, int64_t c,
+                           int64_t inner, int64_t *out);
 
 #ifdef __cplusplus
 }

@@ -128,6 +128,10 @@ int32_t ovk_flush(ovk_ctx *ctx)
     int st = ctx->host_status[0];
     if (st != OVK_DEV_OK) {
         OVK_CUDA(ctx, cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream));
+        if (st == OVK_DEV_BAD_INDEX)
+            return ovk_fail(ctx, OVK_INVALID_ARGUMENT,
+                            "GatherBlockQuantized: an index read on the device fell outside the table "
+                            "(its row was written as zeros)");
         return ovk_fail(ctx, OVK_TIMEOUT, "a device-side wait gave up (code %d: %s)", st,
                         st == OVK_DEV_TIMEOUT_TMA   ? "bulk copy never arrived"
                         : st == OVK_DEV_TIMEOUT_MMA ? "tensor core never signalled"

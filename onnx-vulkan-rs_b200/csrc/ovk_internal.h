@@ -19,6 +19,7 @@ enum : int {
     OVK_DEV_TIMEOUT_TMA = 1,   // a consumer gave up waiting for a bulk copy
     OVK_DEV_TIMEOUT_MMA = 2,   // the epilogue gave up waiting for the tensor core
     OVK_DEV_TIMEOUT_SLOT = 3,  // a producer gave up waiting for a free stage
+    OVK_DEV_BAD_INDEX = 4,     // a gather index read on the device fell outside the table
 };
 
 struct ovk_ctx {

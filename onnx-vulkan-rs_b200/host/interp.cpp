@@ -452,6 +452,77 @@ Result qlinear_conv(Env &env, const NodeIr &node)
                                      out_dtype == OVK_INT8, out->dev));
 }
 
+// ---------------------------------------------------- GatherBlockQuantized / ArgMax
+// interp::gather_block_quantized (interp.rs:2874-2990)
+Result gather_block_quantized(Env &env, const NodeIr &node)
+{
+    const int64_t block_size = node.int_attr("block_size", 0);
+    const Tensor *table = env.find(node.inputs[0]);
+    const Tensor *indices = env.find(node.inputs[1]);
+    const Tensor *scales = env.find(node.inputs[2]);
+    const Tensor *zp = env.find(node.inputs[3]);
+    OVKH_ENSURE(table && indices && scales && zp, "GatherBlockQuantized: an input is missing");
+    OVKH_ENSURE(table->shape.size() == 2, "GatherBlockQuantized: expected a 2-D table, got rank %zu", table->shape.size());
+    const int64_t rows = std::max<int64_t>(table->shape[0], 0), cols = std::max<int64_t>(table->shape[1], 0) * 2;
+    OVKH_ENSURE(cols > 0 && cols % block_size == 0, "GatherBlockQuantized: %lld columns is not a multiple of block_size %lld",
+                (long long)cols, (long long)block_size);
+    const int64_t n_blocks = cols / block_size;
+    OVKH_ENSURE(table->dtype == OVK_UINT8 && zp->dtype == OVK_UINT8 &&
+                    (scales->dtype == OVK_FLOAT || scales->dtype == OVK_FLOAT16),
+                "GatherBlockQuantized: expected a u8 table and zero point with f32 scales, got %d/%d/%d", table->dtype,
+                zp->dtype, scales->dtype);
+    OVKH_ENSURE(scales->elem_count() >= rows * n_blocks && zp->elem_count() >= rows * ((n_blocks + 1) / 2),
+                "GatherBlockQuantized: scales or zero points are short for %lldx%lld blocks", (long long)rows,
+                (long long)n_blocks);
+    OVKH_ENSURE(indices->dtype == OVK_INT64 || indices->dtype == OVK_INT32, "GatherBlockQuantized: indices have dtype %d",
+                indices->dtype);
+    std::vector<int64_t> out_shape = indices->shape;
+    out_shape.push_back(cols);
+    const int64_t count = indices->elem_count();
+    // indices that came from the host are checked there, as the reference does; a
+    // device-only tensor (the token an ArgMax node produced) is read in place
+    const bool on_host = !indices->host.empty() || count == 0;
+    const int32_t idx_dtype = indices->dtype;
+    Tensor *out = nullptr;
+    OVKH_TRY(env.alloc(node.outputs[0], OVK_FLOAT, out_shape, &out));
+    indices = env.find(node.inputs[1]);
+    return from_abi(env.context(),
+                    ovk_gather_block_quantized(env.context(), table->dev, scales->dev, scales->dtype, zp->dev, rows, cols, 4,
+                                               block_size, on_host ? static_cast<const void *>(indices->host.data())
+                                                                   : indices->dev,
+                                               idx_dtype, on_host ? 1 : 0, count, out->dev, OVK_FLOAT));
+}
+
+// interp::argmax (interp.rs:8493-8527) over arg_extreme_axis (:8552)
+Result argmax(Env &env, const NodeIr &node)
+{
+    const Tensor *x = env.find(node.inputs[0]);
+    OVKH_ENSURE(x, "ArgMax: x is missing");
+    const int64_t rank = int64_t(x->shape.size());
+    OVKH_ENSURE(rank > 0, "ArgMax: x is a scalar: it has no axis");
+    int64_t axis = node.int_attr("axis", 0);
+    if (axis < 0)
+        axis += rank;
+    OVKH_ENSURE(axis >= 0 && axis < rank, "ArgMax: axis %lld of a rank-%lld tensor", (long long)node.int_attr("axis", 0),
+                (long long)rank);
+    if (x->dtype != OVK_FLOAT && x->dtype != OVK_FLOAT16)
+        return fail(OVK_UNSUPPORTED, "ArgMax: dtype %d is reduced on the host by the reference, not by this layer", x->dtype);
+    const bool keepdims = node.int_attr("keepdims", 1) == 1;
+    std::vector<int64_t> out_shape = x->shape;
+    if (keepdims)
+        out_shape[size_t(axis)] = 1;
+    else
+        out_shape.erase(out_shape.begin() + axis);
+    const int64_t outer = product(x->shape, 0, size_t(axis)), c = x->shape[size_t(axis)],
+                  inner = product(x->shape, size_t(axis) + 1, x->shape.size());
+    const int32_t dtype = x->dtype;
+    Tensor *out = nullptr;
+    OVKH_TRY(env.alloc(node.outputs[0], OVK_INT64, out_shape, &out));
+    x = env.find(node.inputs[0]);
+    return from_abi(env.context(), ovk_argmax(env.context(), x->dev, dtype, outer, c, std::max<int64_t>(inner, 1),
+                                              static_cast<int64_t *>(out->dev)));
+}
+
 }  // namespace
 
 // ----------------------------------------------------------------------- types
@@ -482,6 +553,8 @@ int64_t Tensor::elem_count() const
 size_t dtype_size(int32_t dtype)
 {
     switch (dtype) {
+    case OVK_INT64:
+        return 8;
     case OVK_FLOAT:
     case OVK_INT32:
         return 4;
@@ -580,6 +653,15 @@ bool is_implemented_node(const NodeIr &node)
                node.int_attr("N", 0) > 0 && node.present(2) && !node.present(4) && !node.present(5) &&
                node.outputs.size() == 1;
     }
+    if (op == "GatherBlockQuantized") {  // interp.rs:470-480
+        const int64_t bs = node.int_attr("block_size", 0);
+        return node.int_attr("bits", 4) == 4 && bs > 0 && bs % 2 == 0 && node.int_attr("gather_axis", 0) == 0 &&
+               node.int_attr("quantize_axis", 1) == 1 && node.present(0) && node.present(1) && node.present(2) &&
+               node.present(3) && node.outputs.size() == 1;
+    }
+    if (op == "ArgMax")  // the reversed tie-break is refused (tests/argmax.rs:192)
+        return node.inputs.size() == 1 && node.outputs.size() == 1 && node.int_attr("select_last_index", 0) == 0 &&
+               (node.int_attr("keepdims", 1) == 0 || node.int_attr("keepdims", 1) == 1);
     if (op == "DynamicQuantizeLinear")
         return node.inputs.size() == 1 && node.outputs.size() == 3;
     if (op == "MatMulInteger")
@@ -650,7 +732,7 @@ std::string unsupported_quantization(const NodeIr &node, const Env &env)
     return "";
 }
 
-// interp::exec_dispatch (interp.rs:1071-1196), the seven operators of the path
+// interp::exec_dispatch (interp.rs:1071-1196), the operators of the path and its two decode-step neighbours
 Result exec_dispatch(Env &env, const NodeIr &node)
 {
     if (!is_implemented_node(node))
@@ -671,6 +753,10 @@ Result exec_dispatch(Env &env, const NodeIr &node)
     }
     if (node.op == "ConvInteger")
         return conv_integer(env, node);
+    if (node.op == "GatherBlockQuantized")
+        return gather_block_quantized(env, node);
+    if (node.op == "ArgMax")
+        return argmax(env, node);
     return qlinear_conv(env, node);
 }
 

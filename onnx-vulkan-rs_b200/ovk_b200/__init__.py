@@ -16,7 +16,7 @@ from __future__ import annotations
 import ctypes as C
 import os
 
-FLOAT, UINT8, INT8, INT32, FLOAT16 = 1, 2, 3, 6, 10
+FLOAT, UINT8, INT8, INT32, INT64, FLOAT16 = 1, 2, 3, 6, 7, 10
 OK, INVALID_ARGUMENT, UNSUPPORTED, BACKEND, TIMEOUT = 0, 1, 2, 3, 4
 EPILOGUE_RELU, EPILOGUE_RANGE = 1, 2
 NBITS_NO_DECODE_COPY = 1
@@ -73,6 +73,8 @@ SIGNATURES = {
     "ovk_conv_integer": (_I32, [_P, _P, _P, _I32, C.POINTER(ConvParams), _I32, _I32, _P]),
     "ovk_qlinear_conv": (_I32, [_P, _P, _P, _I32, C.POINTER(ConvParams), _I32, _I32, _P, _P, _I32, _I32, _P]),
     "ovk_requantize": (_I32, [_P, _P, _I64, _I64, _I64, _P, _P, _I32, _I32, _P]),
+    "ovk_gather_block_quantized": (_I32, [_P, _P, _P, _I32, _P, _I64, _I64, _I64, _I64, _P, _I32, _I32, _I64, _P, _I32]),
+    "ovk_argmax": (_I32, [_P, _P, _I32, _I64, _I64, _I64, _P]),
 }
 
 
@@ -104,7 +106,7 @@ def _ptr(t):
 def _dtype_code(t) -> int:
     import torch
     return {torch.float32: FLOAT, torch.float16: FLOAT16, torch.uint8: UINT8, torch.int8: INT8,
-            torch.int32: INT32}[t.dtype]
+            torch.int32: INT32, torch.int64: INT64}[t.dtype]
 
 
 class Context:
@@ -276,6 +278,38 @@ class Context:
         out = torch.empty(acc.shape, dtype=torch.int8 if y_signed else torch.uint8, device=acc.device)
         self.check(lib().ovk_requantize(self.h, _ptr(acc), acc.numel(), int(inner), ratio.numel(),
                                         _ptr(bias), _ptr(ratio), int(y_zp), int(y_signed), _ptr(out)))
+        return out
+
+    # ------------------------------------- neighbours of the lm_head product
+    def gather_block_quantized(self, table, indices, scales, zero_points, block_size, out_dtype=None, out=None):
+        """interp::gather_block_quantized (interp.rs:2874).  `indices`: a torch CUDA tensor (read on the
+        device), or a CPU tensor / numpy array / list (checked on the host first, as the reference does)."""
+        import numpy as np
+        import torch
+        rows, cols = int(table.shape[0]), int(table.shape[1]) * 2
+        on_host = not (isinstance(indices, torch.Tensor) and indices.is_cuda)
+        if on_host:
+            idx = np.ascontiguousarray(np.asarray(indices, dtype=np.int64))
+            shape, count, ptr, code = idx.shape, idx.size, idx.ctypes.data, INT64
+        else:
+            idx = indices.contiguous()
+            shape, count, ptr, code = tuple(idx.shape), idx.numel(), _ptr(idx), _dtype_code(idx)
+        if out is None:
+            out = torch.empty(tuple(shape) + (cols,), dtype=out_dtype or torch.float32, device=table.device)
+        self.check(lib().ovk_gather_block_quantized(self.h, _ptr(table), _ptr(scales), _dtype_code(scales),
+                                                    _ptr(zero_points), rows, cols, 4, int(block_size), ptr, code,
+                                                    int(on_host), count, _ptr(out), _dtype_code(out)))
+        return out
+
+    def argmax(self, x, axis=-1, out=None):
+        """interp::arg_extreme_axis (interp.rs:8552): first-occurrence ArgMax over `axis`, int64, on the device."""
+        import math
+        import torch
+        axis = axis % x.dim()
+        outer, c, inner = math.prod(x.shape[:axis]), x.shape[axis], math.prod(x.shape[axis + 1:])
+        if out is None:
+            out = torch.empty(tuple(x.shape[:axis]) + tuple(x.shape[axis + 1:]), dtype=torch.int64, device=x.device)
+        self.check(lib().ovk_argmax(self.h, _ptr(x), _dtype_code(x), outer, c, inner, _ptr(out)))
         return out
 
 

@@ -15,7 +15,7 @@ import os
 
 import numpy as np
 
-from . import FLOAT, FLOAT16, INT8, INT32, UINT8, OvkError
+from . import FLOAT, FLOAT16, INT8, INT32, INT64, UINT8, OvkError
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(_PKG, "libovk_host.so")
@@ -41,7 +41,7 @@ SIGNATURES = {
     "ovkh_execute": (_I32, [_P, _P]),
 }
 
-_NP = {FLOAT: np.float32, UINT8: np.uint8, INT8: np.int8, INT32: np.int32, FLOAT16: np.float16}
+_NP = {FLOAT: np.float32, UINT8: np.uint8, INT8: np.int8, INT32: np.int32, INT64: np.int64, FLOAT16: np.float16}
 _CODE = {np.dtype(v): k for k, v in _NP.items()}
 _lib = None
 

@@ -215,3 +215,32 @@ def qlinear_conv(x, x_scale, x_zp, w, w_scale, w_zp, y_scale, y_zp, bias=None, o
     if ratio.size == 1:
         ratio = np.repeat(ratio, acc.shape[1])
     return requantize(acc, acc.shape[2] * acc.shape[3], ratio, y_zp, bias, out_signed)
+
+
+def gather_block_quantized(table, indices, scales, zero_points, block_size):
+    """GatherBlockQuantized (src/interp.rs:2874-2990): f32 rows of a 4-bit table."""
+    table = np.ascontiguousarray(table, dtype=np.uint8)
+    idx = np.ascontiguousarray(indices, dtype=np.int64)
+    scales = np.ascontiguousarray(scales)
+    rows, cols = table.shape[0], table.shape[1] * 2
+    if zero_points is not None:
+        zero_points = np.ascontiguousarray(zero_points, dtype=np.uint8)
+    out = np.empty(idx.shape + (cols,), dtype=np.float32)
+    rc = lib().orc_gather_block_quantized(_p(table), _p(idx), C.c_size_t(idx.size), _p(scales), _dt(scales),
+                                          _p(zero_points), C.c_int64(rows), C.c_int64(cols),
+                                          C.c_int64(block_size), _p(out))
+    if rc:
+        raise IndexError(f"GatherBlockQuantized: an index falls outside the {rows}-row table")
+    return out
+
+
+def argmax(x, axis=-1):
+    """First-occurrence ArgMax over one axis with the device kernels' candidate rule."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    axis = axis % x.ndim
+    outer = int(np.prod(x.shape[:axis], dtype=np.int64))
+    c = x.shape[axis]
+    inner = int(np.prod(x.shape[axis + 1:], dtype=np.int64))
+    out = np.empty(x.shape[:axis] + x.shape[axis + 1:], dtype=np.int64)
+    lib().orc_argmax(_p(x), C.c_int64(outer), C.c_int64(c), C.c_int64(inner), _p(out))
+    return out

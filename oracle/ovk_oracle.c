@@ -535,3 +535,64 @@ ORC_EXPORT void orc_requantize(const int32_t *acc, size_t n, size_t inner, size_
         }
     }
 }
+
+/* ------------------------------------------------------------------------
+ * GatherBlockQuantized: out[j, c] = (unpack(table[idx[j], c]) - zp) * scale in
+ * f32 (crates/onnx-vulkan-core/src/shaders/gather_block_quantized.rs:40-57);
+ * negative indices count from the end and an index outside the table is an
+ * error (src/interp.rs:2896-2911).  table [rows, cols/2] u8 with element 2i in
+ * the low nibble, scales [rows, cols/block_size] (f32 or f16), zero points
+ * [rows, ceil(n_blocks/2)] u8 nibble packed or NULL (8).  out f32.
+ * Returns 0, or 1 when an index is outside the table.
+ */
+ORC_EXPORT int orc_gather_block_quantized(const uint8_t *table, const int64_t *indices, size_t count,
+                                          const void *scales, int scales_dtype, const uint8_t *zp,
+                                          int64_t rows, int64_t cols, int64_t block_size, float *out)
+{
+    const size_t row_bytes = (size_t)cols / 2;
+    const size_t n_blocks = (size_t)(cols / block_size);
+    const size_t zp_row = (n_blocks + 1) / 2;
+    for (size_t j = 0; j < count; j++) {
+        int64_t r = indices[j];
+        if (r < 0)
+            r += rows;
+        if (r < 0 || r >= rows)
+            return 1;
+    }
+    for (size_t j = 0; j < count; j++) {
+        int64_t r = indices[j] < 0 ? indices[j] + rows : indices[j];
+        for (int64_t c = 0; c < cols; c++) {
+            size_t block = (size_t)(c / block_size);
+            float q = (float)nib_at(table, row_bytes, (size_t)r, (size_t)c);
+            float z = zp ? (float)zp_at(zp, zp_row, (size_t)r, block) : 8.0f;
+            float s = (float)load_real(scales, scales_dtype, (size_t)r * n_blocks + block);
+            volatile float d = q - z;
+            out[j * (size_t)cols + (size_t)c] = d * s;
+        }
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------
+ * ArgMax over one axis, first occurrence, as the device kernels decide it
+ * (shaders/reduction.rs:97-131, :156-186): a value is a candidate only if it
+ * is greater than -FLT_MAX (so NaN and -inf never are), larger wins, equal
+ * values go to the smaller index, no candidate answers 0.  x is
+ * [outer, c, inner] f32, out [outer*inner] int64.
+ */
+ORC_EXPORT void orc_argmax(const float *x, int64_t outer, int64_t c, int64_t inner, int64_t *out)
+{
+    for (int64_t r = 0; r < outer * inner; r++) {
+        const int64_t base = (r / inner) * c * inner + r % inner;
+        float best = -3.4028235e38f;
+        int64_t at = 0;
+        for (int64_t k = 0; k < c; k++) {
+            float v = x[base + k * inner];
+            if (v > best) {
+                best = v;
+                at = k;
+            }
+        }
+        out[r] = at;
+    }
+}

@@ -221,3 +221,39 @@ def test_qlinear_matmul(hl, env):
     want = orc.requantize(acc, 1, orc.requantize_ratio(0.02, bs, 0.5), -3, out_signed=True)
     got = env.host("y")
     assert got.dtype == np.int8 and np.array_equal(got, want)
+
+
+def test_gather_block_quantized_node(hl, env):
+    """crates/onnx-vulkan-core/tests/gather_block_quantized.rs:85-160: the same node, attributes and inputs."""
+    from test_oracle_golden import gbq_case
+    _, _, scale, table, zpk = gbq_case(32, 128, 32)
+    idx = np.array([[0, 31, 7, 7, -1]], dtype=np.int64)
+    env.set("table", table, initializer=True)
+    env.set("indices", idx)
+    env.set("scales", scale, initializer=True)
+    env.set("zp", zpk, initializer=True)
+    node = hl.Node("GatherBlockQuantized", ["table", "indices", "scales", "zp"], ["out"], domain="com.microsoft",
+                   bits=4, block_size=32, gather_axis=0, quantize_axis=1)
+    assert node.implemented
+    env.execute(node)
+    got = env.host("out")
+    assert got.shape == (1, 5, 128) and np.array_equal(got, orc.gather_block_quantized(table, idx, scale, zpk, 32))
+    env.set("indices", np.array([32], dtype=np.int64))
+    with pytest.raises(hl.OvkError, match="outside the 32-row table"):
+        env.execute(node)
+    assert not hl.Node("GatherBlockQuantized", ["table", "indices", "scales", "zp"], ["out"], block_size=32,
+                       gather_axis=1).implemented
+
+
+@pytest.mark.parametrize("shape,axis,keepdims", [((4, 1000), 1, 1), ((2, 5, 3, 3), 1, 0), ((1, 1, 151936), -1, 0)])
+def test_argmax_node(hl, env, shape, axis, keepdims):
+    """crates/onnx-vulkan-core/tests/argmax.rs:90-164."""
+    x = cases.rng_for(25, 0).standard_normal(shape, dtype=np.float32)
+    env.set("x", x)
+    node = hl.Node("ArgMax", ["x"], ["out"], axis=axis, keepdims=keepdims)
+    env.execute(node)
+    got = env.host("out")
+    want = orc.argmax(x, axis)
+    assert got.dtype == np.int64
+    assert np.array_equal(got, np.expand_dims(want, axis % x.ndim) if keepdims else want)
+    assert not hl.Node("ArgMax", ["x"], ["out"], axis=axis, select_last_index=1).implemented

@@ -312,3 +312,58 @@ def test_conv_geometry_auto_pad():
 
 def test_lcg_fast_equals_scalar():
     assert np.array_equal(cases.lcg_bytes_fast(10000, 11), cases.lcg_bytes(10000, 11))
+
+
+# ------------------------------------------------ GatherBlockQuantized / ArgMax
+
+def gbq_case(rows, cols, block_size):
+    """The closed-form table of tests/gather_block_quantized.rs:57-66."""
+    r = np.arange(rows)[:, None]
+    c = np.arange(cols)[None, :]
+    nb = cols // block_size
+    b = np.arange(nb)[None, :]
+    nib = ((r * 5 + c * 3) % 16).astype(np.uint8)
+    zp = ((r + b * 7) % 16).astype(np.uint8)
+    scale = (((r * 3 + b) % 11).astype(np.float32) / np.float32(32.0) - np.float32(0.15)).astype(np.float32)
+    table = (nib[:, 0::2] | (nib[:, 1::2] << 4)).astype(np.uint8)
+    zpad = np.zeros((rows, nb + (nb & 1)), dtype=np.uint8)
+    zpad[:, :nb] = zp
+    zpk = (zpad[:, 0::2] | (zpad[:, 1::2] << 4)).astype(np.uint8)
+    return nib, zp, scale, table, zpk
+
+
+@pytest.mark.parametrize("rows,cols,bs,indices", [
+    (64, 1152, 32, [[37]]),                 # tests/gather_block_quantized.rs:163-172
+    (32, 128, 32, [[0, 31, 7, 7, 1]]),      # :175-183
+    (16, 64, 16, [-1, -16, 3]),             # :186-194
+    (9, 80, 16, [8, 0, 5]),                 # :197-207
+])
+def test_gather_block_quantized_reference_cases(rows, cols, bs, indices):
+    nib, zp, scale, table, zpk = gbq_case(rows, cols, bs)
+    idx = np.array(indices, dtype=np.int64)
+    got = orc.gather_block_quantized(table, idx, scale, zpk, bs)
+    assert got.shape == idx.shape + (cols,)
+    rr = np.where(idx < 0, idx + rows, idx).reshape(-1)
+    blk = np.arange(cols) // bs
+    want = (nib[rr].astype(np.float32) - zp[rr][:, blk].astype(np.float32)) * scale[rr][:, blk]
+    assert np.array_equal(got.reshape(-1, cols), want)
+
+
+def test_gather_block_quantized_refuses_an_index_outside_the_table():
+    _, _, scale, table, zpk = gbq_case(16, 64, 16)
+    with pytest.raises(IndexError):
+        orc.gather_block_quantized(table, np.array([16]), scale, zpk, 16)
+    with pytest.raises(IndexError):
+        orc.gather_block_quantized(table, np.array([-17]), scale, zpk, 16)
+
+
+def test_argmax_first_occurrence_and_candidates():
+    """tests/argmax.rs:126-147 (ties) and the kernels' candidate rule (shaders/reduction.rs:101-107)."""
+    assert orc.argmax(np.full(4096, 0.5, dtype=np.float32), 0) == 0
+    twice = np.zeros(4096, dtype=np.float32)
+    twice[700] = twice[3000] = 2.0
+    assert orc.argmax(twice, 0) == 700
+    x = np.random.Generator(np.random.PCG64(5)).standard_normal((2, 5, 3, 3)).astype(np.float32)
+    assert np.array_equal(orc.argmax(x, 1), np.argmax(x, axis=1))
+    odd = np.array([[np.nan, -np.inf, -3.0], [-np.inf, -np.inf, np.nan]], dtype=np.float32)
+    assert orc.argmax(odd, 1).tolist() == [2, 0]
