@@ -32,7 +32,8 @@ namespace {
 
 constexpr int BM = 128;  // pixels per tile
 constexpr int EPI_WARPS = 16;            // four per tensor-memory lane quarter
-constexpr int THREADS = (2 + EPI_WARPS) * 32;
+constexpr int MMA_WARPS = 2;              // two issuing threads on different schedulers take alternate tiles
+constexpr int THREADS = (2 + EPI_WARPS + (MMA_WARPS - 1)) * 32;  // TMA, issuer 0, epilogue warps, issuer 1
 constexpr long long WAIT_CYCLES = 2000000000ll;
 constexpr size_t W_SMEM_MAX = 112 * 1024;
 
@@ -57,6 +58,8 @@ struct ConvTcParams {
     int *status;
     int m_tiles;
     int nacc;
+    int issuers;  // 1 or 2 MMA-issuing threads
+    uint64_t magic_hpwp, magic_wp;  // ceil(2^64 / divisor), 0 for a divisor of 1
 };
 
 __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
@@ -67,6 +70,7 @@ __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
     for (;;) {
         if (umma::mbar_try_wait_hint(bar, parity, 1000u))  // parked for up to a microsecond, not spinning
             return true;
+        __nanosleep(64);  // and out of the issue slots of the thread that feeds the tensor core
         if (clock64() - t0 > WAIT_CYCLES)
             return false;
     }
@@ -151,6 +155,9 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                 const int tap = sl / p.chunks, ch = sl % p.chunks;
                 umma::tma_load_2d(sWt + size_t(sl) * p.w_slice, &tmW, w_full, ch * p.kch, tap * p.co_pad);
             }
+            // launched with programmatic stream serialization: everything above ran while the layout
+            // pass was still draining; its output is read from here on
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             int seq = 0;
             for (int tile = blockIdx.x; tile < p.m_tiles; tile += gridDim.x) {
                 const int64_t v0 = int64_t(tile) * BM;
@@ -174,19 +181,31 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 2 + EPI_WARPS) {
+        // The issue of a tcgen05.mma blocks until the tensor core takes it, and between two of them this
+        // thread competes with the epilogue warps of its scheduler for issue slots.  Two issuers on two
+        // schedulers, each with its own tiles (and accumulators), keep the tensor core fed.
         if (lane == 0) {
+            const int me = warp == 1 ? 0 : 1;
+            const int issuers = p.issuers;
             const uint32_t idesc = umma::instr_desc(2, p.x_signed ? 1 : 0, p.w_signed ? 1 : 0, BM, uint32_t(p.co_pad));
             bool ok = wait_bounded(w_full, 0);
             if (!ok)
                 atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
-            int seq = 0, tile_seq = 0;
+            const int loads_per_tile = p.halo ? 1 : slices;
             const int ksteps = p.kch / 32;
             // descriptor halves that never change: LBO = 1 (unused by swizzled K-major), version 1,
             // stride between 8-row groups, swizzle mode
             const uint32_t desc_lo_flags = 1u << 16;
             const uint32_t desc_hi = ((uint32_t(p.sbo) >> 4) & 0x3fffu) | (1u << 14) | (uint32_t(p.sw_layout) << 29);
-            for (int tile = blockIdx.x; tile < p.m_tiles && ok; tile += gridDim.x, tile_seq++) {
+            const uint32_t a_unit = uint32_t(p.kch) >> 4;  // 16-byte units per pixel row
+            const uint32_t a_step_w = uint32_t(p.dw) * a_unit, a_step_h = uint32_t(p.dh * p.wp) * a_unit;
+            const uint32_t w16 = umma::smem_u32(sWt) >> 4, w_step = p.w_slice >> 4;
+            const int khn = p.taps / p.kw;
+            int tile_seq = me;
+            for (int tile = me < issuers ? int(blockIdx.x) + me * int(gridDim.x) : p.m_tiles; tile < p.m_tiles && ok;
+                 tile += issuers * int(gridDim.x), tile_seq += issuers) {
+                int seq = tile_seq * loads_per_tile;  // position of the tile's first load in the stage ring
                 const int b = tile_seq & (nacc - 1);
                 if (!wait_bounded(&acc_empty[b], ((tile_seq / nacc) & 1) ^ 1)) {
                     atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
@@ -207,13 +226,34 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                     // absolute shared-memory address (TMA wrote the tile with the same function), so the
                     // descriptor needs no base offset: measured bit-exact with 0, wrong otherwise.
                     const uint32_t a16 = umma::smem_u32(sA + size_t(s) * p.a_stage) >> 4;
-                    uint32_t accumulate = 0;
-                    for (int tap = 0; tap < p.taps; tap++) {
-                        const uint32_t a_lo = ((a16 + s_tap_a[tap]) & 0x3fffu) | desc_lo_flags;
-                        const uint32_t w_lo = (s_tap_w[tap] & 0x3fffu) | desc_lo_flags;
-                        for (int j = 0; j < ksteps; j++) {
-                            umma::mma_i8_lohi(d_tmem, a_lo + 2u * j, desc_hi, w_lo + 2u * j, desc_hi, idesc, accumulate);
-                            accumulate = 1;
+                    // tap (kh, kw) starts (kh*dh*WP + kw*dw) pixel rows into the halo tile and one filter
+                    // slice further.  The issuing thread shares its scheduler with waiting warps, so the
+                    // loop is kept to an add or two per MMA: shared-memory addresses are below 2^18, so
+                    // (address >> 4) + offset never carries into the descriptor's flag bits, and the
+                    // common 3x3 filter over 64 channels is unrolled completely.
+                    const uint32_t a0 = a16 | desc_lo_flags, w0 = w16 | desc_lo_flags;
+                    if (khn == 3 && p.kw == 3 && ksteps == 2) {
+#pragma unroll
+                        for (int kh = 0; kh < 3; kh++) {
+#pragma unroll
+                            for (int kw = 0; kw < 3; kw++) {
+                                const uint32_t a_lo = a0 + uint32_t(kh) * a_step_h + uint32_t(kw) * a_step_w;
+                                const uint32_t w_lo = w0 + uint32_t(kh * 3 + kw) * w_step;
+                                umma::mma_i8_lohi(d_tmem, a_lo, desc_hi, w_lo, desc_hi, idesc, (kh | kw) ? 1u : 0u);
+                                umma::mma_i8_lohi(d_tmem, a_lo + 2u, desc_hi, w_lo + 2u, desc_hi, idesc, 1u);
+                            }
+                        }
+                    } else {
+                        uint32_t accumulate = 0;
+                        uint32_t a_h = a0, w_cur = w0;
+                        for (int kh = 0; kh < khn; kh++, a_h += a_step_h) {
+                            uint32_t a_t = a_h;
+                            for (int kw = 0; kw < p.kw; kw++, a_t += a_step_w, w_cur += w_step) {
+                                for (int j = 0; j < ksteps; j++) {
+                                    umma::mma_i8_lohi(d_tmem, a_t + 2u * j, desc_hi, w_cur + 2u * j, desc_hi, idesc, accumulate);
+                                    accumulate = 1;
+                                }
+                            }
                         }
                     }
                     umma::mma_commit(&a_empty[s]);
@@ -241,7 +281,7 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                     umma::mma_commit(&acc_full[b]);
             }
         }
-    } else {
+    } else if (warp < 2 + EPI_WARPS) {
         // ---------------------------------------------------------------- epilogue
         // warp w reads lane quarter w % 4 (a hardware rule); the four warps of a
         // quarter take the 16-channel column groups round robin
@@ -252,6 +292,8 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         bool ok = true;
         const int64_t plane = int64_t(p.h_out) * p.w_out;
         const int lo = p.epi.y_signed ? -128 : 0, hi = p.epi.y_signed ? 127 : 255;
+        const float clamp_lo = float(lo - p.epi.y_zp), clamp_hi = float(hi - p.epi.y_zp);
+        const int32_t round_fix = p.epi.y_zp - 0x4B400000;
         for (int tile = blockIdx.x; tile < p.m_tiles; tile += gridDim.x, tile_seq++) {
             const int b = tile_seq & (nacc - 1);
             if (ok && !wait_bounded(&acc_full[b], (tile_seq / nacc) & 1)) {
@@ -260,11 +302,13 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                 ok = false;
             }
             umma::tc_fence_after();
-            // pixel coordinates in 32-bit arithmetic (v_total < 2^31 is checked on the host)
+            // pixel coordinates without a division: the high half of n * ceil(2^64 / d) is floor(n / d)
+            // for every 32-bit n (a divisor of 1 has no such constant and is passed as 0)
             const uint32_t v = uint32_t(tile) * BM + q * 32 + lane;
-            const uint32_t img = v / uint32_t(p.hpwp);
+            const uint32_t img = p.magic_hpwp ? uint32_t(__umul64hi(uint64_t(v), p.magic_hpwp)) : v;
             const uint32_t rem = v - img * uint32_t(p.hpwp);
-            const uint32_t oh = rem / uint32_t(p.wp), ow = rem - oh * uint32_t(p.wp);
+            const uint32_t oh = p.magic_wp ? uint32_t(__umul64hi(uint64_t(rem), p.magic_wp)) : rem;
+            const uint32_t ow = rem - oh * uint32_t(p.wp);
             const bool valid = ok && int64_t(v) < p.v_total && int(oh) < p.h_out && int(ow) < p.w_out;
             const int64_t o_base = int64_t(img) * p.c_out * plane + int64_t(oh) * p.w_out + ow;
             // this warp's last column group: after reading it the accumulator is handed back
@@ -310,13 +354,17 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                     uint8_t *o = static_cast<uint8_t *>(p.out) + o_base + int64_t(c0) * plane;
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
-                        // sat(rne(f32(acc + bias) * ratio) + y_zp), shaders/qlinear.rs:28-63;
-                        // the f32 -> i32 conversion itself rounds to nearest even and saturates
+                        // sat(rne(f32(acc + bias) * ratio) + y_zp), shaders/qlinear.rs:28-63.  The bounds
+                        // are integers, so clamping x to [lo - zp, hi - zp] first and rounding after gives
+                        // the same byte; the rounding is the 1.5 * 2^23 trick (adds on the full-rate
+                        // pipes instead of a quarter-rate conversion), exact for the clamped range.
                         const int32_t acc = int32_t(r[j] + uint32_t(corr[j]));
-                        const int32_t qv = int32_t(uint32_t(__float2int_rn(__fmul_rn(float(acc), ratio[j]))) +
-                                                   uint32_t(p.epi.y_zp));
+                        const float x = __fmul_rn(float(acc), ratio[j]);
+                        const float xc = fminf(fmaxf(x, clamp_lo), clamp_hi);
+                        const int32_t qv = __float_as_int(__fadd_rn(xc, 12582912.0f)) + round_fix;
                         if (j < nch)
-                            o[int64_t(j) * plane] = uint8_t(max(lo, min(hi, qv)));
+                            o[0] = uint8_t(qv);
+                        o += plane;
                     }
                 }
             }
@@ -337,6 +385,7 @@ conv_pad_nhwc_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ xp, in
                      int pt, int pl, uint32_t zp_byte, int cgroup, int pitch, int words_ok)
 {
     extern __shared__ __align__(16) uint8_t tile[];  // [cgroup][pitch]
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // see conv_pad_nhwc_fast_kernel
     const int hp = blockIdx.x, n = blockIdx.y;
     uint8_t *dst_row = xp + (size_t(n) * HP + hp) * size_t(WP) * C;
     const int h = hp - pt;
@@ -375,6 +424,119 @@ conv_pad_nhwc_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ xp, in
             reinterpret_cast<uint32_t *>(dst_row + size_t(wpix) * C + c0)[cw] = v;
         }
         __syncthreads();
+    }
+}
+
+// The same pass for the common aligned case (W a multiple of 4, C a multiple of
+// 16, 4-byte aligned input): one block per image and group of R input rows.  A
+// channel's R rows are one contiguous run of R*W bytes, read as 32-bit words
+// into shared memory [C][R*W + 4]; then every thread takes four pixels x sixteen
+// channels - sixteen words, four 4x4 byte transposes (byte permutes), four
+// 128-bit stores of 16 channels each, the four threads of a pixel quad writing
+// one pixel's 64 contiguous bytes.  About a twentieth of the instructions of the
+// general kernel above.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
+{
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// (a, b, c, d) = four channels x four pixels (pixel p in byte p)  ->  out[p] = the four channels of pixel p
+__device__ __forceinline__ void transpose4x4(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&out)[4])
+{
+    const uint32_t ab_lo = prmt(a, b, 0x5140), ab_hi = prmt(a, b, 0x7362);  // a0 b0 a1 b1 | a2 b2 a3 b3
+    const uint32_t cd_lo = prmt(c, d, 0x5140), cd_hi = prmt(c, d, 0x7362);
+    out[0] = prmt(ab_lo, cd_lo, 0x5410);  // a0 b0 c0 d0
+    out[1] = prmt(ab_lo, cd_lo, 0x7632);  // a1 b1 c1 d1
+    out[2] = prmt(ab_hi, cd_hi, 0x5410);
+    out[3] = prmt(ab_hi, cd_hi, 0x7632);
+}
+
+__global__ void __launch_bounds__(256)
+conv_pad_nhwc_fast_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ xp, int C, int H, int W, int HP, int WP,
+                          int pt, int pl, uint32_t zp_byte, int R, int pitch_words)
+{
+    extern __shared__ __align__(16) uint32_t slab[];  // [C][pitch_words]
+    // the convolution kernel may start its prologue (barriers, tensor memory, filter bank) now; it
+    // reads this kernel's output only after griddepcontrol.wait
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int n = blockIdx.y, h0 = blockIdx.x * R;
+    const int rows = min(R, H - h0);
+    const int words_per_ch = rows * W / 4;
+    const uint32_t zp4 = zp_byte * 0x01010101u;
+    const uint4 zp16 = make_uint4(zp4, zp4, zp4, zp4);
+    // ---- read: a warp per channel, its lanes over the words of the channel's run
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    // (a run is at most 64 words; four channels are fetched before anything is stored, so that a
+    // warp has eight loads in flight instead of one)
+    const size_t ch_stride = size_t(H) * W / 4;  // words between channels
+    const uint32_t *src0 = reinterpret_cast<const uint32_t *>(x + (size_t(n) * C * H + h0) * W);
+    const bool has0 = lane < words_per_ch, has1 = lane + 32 < words_per_ch;
+    for (int c = warp * 4; c < C; c += nwarps * 4) {
+        uint32_t v[4][2];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint32_t *src = src0 + size_t(c + k) * ch_stride;
+            v[k][0] = (c + k < C && has0) ? __ldg(src + lane) : 0u;
+            v[k][1] = (c + k < C && has1) ? __ldg(src + lane + 32) : 0u;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            if (c + k < C && has0)
+                slab[(c + k) * pitch_words + lane] = v[k][0];
+            if (c + k < C && has1)
+                slab[(c + k) * pitch_words + lane + 32] = v[k][1];
+        }
+    }
+    // ---- the padding this block owns: left/right columns of its rows (a warp per row), and the
+    // rows above the first / below the last group
+    uint8_t *img = xp + size_t(n) * HP * WP * C;
+    const int c16 = C / 16;
+    const int pr = WP - pl - W;  // padding columns on the right
+    for (int r = warp; r < rows; r += nwarps) {
+        uint4 *row = reinterpret_cast<uint4 *>(img + size_t(pt + h0 + r) * WP * C);
+        for (int i = lane; i < pl * c16; i += 32)
+            row[i] = zp16;
+        uint4 *right = row + size_t(pl + W) * c16;
+        for (int i = lane; i < pr * c16; i += 32)
+            right[i] = zp16;
+    }
+    if (blockIdx.x == 0)
+        for (int i = threadIdx.x; i < pt * WP * c16; i += blockDim.x)
+            reinterpret_cast<uint4 *>(img)[i] = zp16;
+    if (h0 + rows == H) {
+        const int below = HP - pt - H;
+        uint4 *dst = reinterpret_cast<uint4 *>(img + size_t(pt + H) * WP * C);
+        for (int i = threadIdx.x; i < below * WP * c16; i += blockDim.x)
+            dst[i] = zp16;
+    }
+    __syncthreads();
+    // ---- transpose and write
+    // one item = (pixel quad, group of 16 channels); the threads of a quad are neighbours so that
+    // they write one pixel's contiguous bytes.  c16 is a power of two for the channel counts the
+    // tensor path takes (32, 64, 128, 256, ...) or small; the row of a quad comes from one multiply.
+    const int quads_per_row = W / 4;
+    const int quads = rows * quads_per_row;
+    const uint32_t inv_qpr = (65536u + uint32_t(quads_per_row) - 1u) / uint32_t(quads_per_row);  // quads < 2^10
+    const bool c16_pow2 = (c16 & (c16 - 1)) == 0;
+    const int c16_shift = 31 - __clz(c16);
+    for (int i = threadIdx.x; i < quads * c16; i += blockDim.x) {
+        const int quad = c16_pow2 ? i >> c16_shift : i / c16;
+        const int cq = i - quad * c16;
+        int r = int((uint32_t(quad) * inv_qpr) >> 16);
+        if (r * quads_per_row > quad)
+            r--;  // the rounded-up reciprocal overshoots by at most one
+        const int qw = quad - r * quads_per_row;
+        const uint32_t *src = slab + (cq * 16) * pitch_words + quad;
+        uint32_t t[4][4];
+#pragma unroll
+        for (int g = 0; g < 4; g++)
+            transpose4x4(src[(4 * g) * pitch_words], src[(4 * g + 1) * pitch_words], src[(4 * g + 2) * pitch_words],
+                         src[(4 * g + 3) * pitch_words], t[g]);
+        uint8_t *dst = img + (size_t(pt + h0 + r) * WP + pl + qw * 4) * C + cq * 16;
+#pragma unroll
+        for (int px = 0; px < 4; px++)
+            *reinterpret_cast<uint4 *>(dst + size_t(px) * C) = make_uint4(t[0][px], t[1][px], t[2][px], t[3][px]);
     }
 }
 
@@ -463,7 +625,19 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
     if (rc != OVK_OK)
         return rc;
     uint8_t *xp = static_cast<uint8_t *>(ws);
-    {
+    const bool fast_layout = (g.w_in % 4) == 0 && (C % 16) == 0 && aligned_to(x, 4) && g.w_in <= 1024;
+    if (fast_layout) {
+        const int R = std::max(1, std::min(g.h_in, 256 / g.w_in));  // about 256 pixels per block
+        const int pitch_words = R * g.w_in / 4 + 1;
+        const size_t sm = size_t(C) * pitch_words * 4;
+        if (sm > 48 * 1024)
+            OVK_CUDA(ctx, cudaFuncSetAttribute(conv_pad_nhwc_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sm)));
+        OVK_REQUIRE(ctx, sm <= ctx->smem_optin, "ConvInteger: %d channels are too many for the layout pass", C);
+        conv_pad_nhwc_fast_kernel<<<dim3(unsigned(ceil_div64(g.h_in, R)), unsigned(g.n)), 256, sm, ctx->stream>>>(
+            static_cast<const uint8_t *>(x), xp, C, g.h_in, g.w_in, HP, WP, g.phb, g.pwb, uint32_t(x_zp) & 0xffu, R,
+            pitch_words);
+        OVK_LAUNCHED(ctx, "conv_pad_nhwc_fast");
+    } else {
         const int pitch = ((g.w_in + 3) & ~3) + 4;
         int cgroup = C;
         while (size_t(cgroup) * pitch > 40 * 1024 && cgroup > 4)
@@ -502,6 +676,14 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
     p.stages = int(std::min<size_t>(MAX_STAGES, avail / p.a_stage));
     if (p.stages < 2)
         return OVK_UNSUPPORTED;
+    // With two issuers taking alternate tiles every stage and accumulator must always come back to
+    // the same issuer (a waiter may be at most one phase behind its barrier): an even ring, one load
+    // per tile.  Otherwise one thread issues everything.
+    p.issuers = 1;
+    if (p.halo) {
+        p.stages &= ~1;
+        p.issuers = MMA_WARPS;
+    }
     p.x_signed = x_signed ? 1 : 0;
     p.w_signed = w->w_signed;
     p.x_zp = x_zp;
@@ -510,6 +692,8 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
     p.out = out;
     p.status = ctx->dev_status;
     p.m_tiles = int(ceil_div64(v_total, BM));
+    p.magic_hpwp = p.hpwp > 1 ? ~uint64_t(0) / uint64_t(p.hpwp) + 1 : 0;
+    p.magic_wp = p.wp > 1 ? ~uint64_t(0) / uint64_t(p.wp) + 1 : 0;
     p.nacc = 2;
     while (p.nacc * 2 <= MAX_ACC && p.nacc * 2 * p.co_pad <= 512)
         p.nacc *= 2;
@@ -524,7 +708,19 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
     const size_t smem = w_bytes + size_t(p.stages) * p.a_stage + 512 + 2048 + 512;
     OVK_CUDA(ctx, cudaFuncSetAttribute(qconv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     const unsigned grid = unsigned(std::min<int>(p.m_tiles, ctx->sm_count));
-    qconv_tc_kernel<<<grid, THREADS, smem, ctx->stream>>>(tmX, tmW, p);
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        OVK_CUDA(ctx, cudaLaunchKernelEx(&cfg, qconv_tc_kernel, tmX, tmW, p));
+    }
     OVK_LAUNCHED(ctx, p.halo ? "qconv_tc_halo" : "qconv_tc_taps");
     return OVK_OK;
 }
