@@ -20,6 +20,8 @@
 // kind::i8 takes signed and unsigned bytes per operand, so nothing is flipped
 // (the reference's FLIP_BYTES pass, shaders/matmul_integer.rs:25-38, is not needed).
 // Ragged M, N and K are handled by TMA zero fill plus store predicates.
+#include <cstdlib>
+
 #include "ovk_internal.h"
 #include "epilogue.cuh"
 #include "umma.cuh"
@@ -67,6 +69,85 @@ __device__ __forceinline__ bool wait_parked(uint64_t *bar, uint32_t parity)
             return true;
         if (clock64() - t0 > WAIT_CYCLES)
             return false;
+    }
+}
+
+// The columns of one accumulator row block: tcgen05.ld 32 columns at a time (one row per thread),
+// the zero-point terms, then the store selected by EpiParams.  `hand_back` gets this warp's arrival
+// as soon as the last columns have been read, before they are processed.
+template <int BN>
+__device__ __forceinline__ void epilogue_columns(const TcParams &p, uint32_t taddr, uint64_t *hand_back, int lane,
+                                                 int64_t row, bool row_ok, int n0, uint32_t row_term, int32_t za,
+                                                 float &run_max, float &run_neg)
+{
+    const bool vec4 = p.vec_ok != 0;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        umma::tmem_ld_32x32(taddr + uint32_t(c0), r);
+        umma::tmem_ld_wait();
+        if (c0 + 32 == BN) {  // the whole accumulator has been read: hand it back
+            umma::tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                umma::mbar_arrive(hand_back);
+        }
+        if (!row_ok || n0 + c0 >= p.N)
+            continue;
+        const int col0 = n0 + c0;
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const int col = col0 + j;
+            const int32_t cs = col < p.N ? p.colsum[col] : 0;
+            r[j] = r[j] - uint32_t(za) * uint32_t(cs) + row_term;
+        }
+        if (p.epi.mode == EPI_RAW) {
+            int32_t *o = static_cast<int32_t *>(p.out) + row * p.N + col0;
+            if (vec4 && col0 + 32 <= p.N) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<int4 *>(o + j) = make_int4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else {
+                for (int j = 0; j < 32 && col0 + j < p.N; j++)
+                    o[j] = int32_t(r[j]);
+            }
+        } else if (p.epi.mode == EPI_SCALE) {
+            float *o = static_cast<float *>(p.out) + row * p.N + col0;
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                if (col0 + j < p.N) {
+                    f[j] = epi_scale_value(p.epi, col0 + j, float(int32_t(r[j])));
+                    run_max = fmaxf(run_max, f[j]);
+                    run_neg = fmaxf(run_neg, -f[j]);
+                } else {
+                    f[j] = 0.0f;
+                }
+            }
+            if (vec4 && col0 + 32 <= p.N) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4 *>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+            } else {
+                for (int j = 0; j < 32 && col0 + j < p.N; j++)
+                    o[j] = f[j];
+            }
+        } else {
+            uint8_t *o = static_cast<uint8_t *>(p.out) + row * p.N + col0;
+            if (vec4 && col0 + 32 <= p.N) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    uint32_t w = 0;
+#pragma unroll
+                    for (int t = 0; t < 4; t++)
+                        w |= (uint32_t(epi_requant_value(p.epi, col0 + j + t, int32_t(r[j + t]))) & 0xffu) << (8 * t);
+                    *reinterpret_cast<uint32_t *>(o + j) = w;
+                }
+            } else {
+                for (int j = 0; j < 32 && col0 + j < p.N; j++)
+                    o[j] = uint8_t(epi_requant_value(p.epi, col0 + j, int32_t(r[j])));
+            }
+        }
     }
 }
 
@@ -189,7 +270,6 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         const int q = warp & 3;
         const int32_t za = load_zp(p.a_zp, p.a_signed), zb = load_zp(p.b_zp, p.b_signed);
         float run_max = 0.0f, run_neg = 0.0f;
-        const bool vec4 = p.vec_ok != 0;
         bool ready = true;
         int b = 0;
         uint32_t acc_ph = 0;
@@ -206,74 +286,8 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             const bool row_ok = ready && row < p.M;
             const uint32_t row_term = uint32_t(p.K) * uint32_t(za) * uint32_t(zb) -
                                       ((zb != 0 && p.rowsum && row_ok) ? uint32_t(zb) * uint32_t(p.rowsum[row]) : 0u);
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                umma::tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BN + c0), r);
-                umma::tmem_ld_wait();
-                if (c0 + 32 == BN) {  // the whole accumulator has been read: hand it back
-                    umma::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0)
-                        umma::mbar_arrive(&acc_empty[b]);
-                }
-                if (!row_ok || n0 + c0 >= p.N)
-                    continue;
-                const int col0 = n0 + c0;
-#pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    const int col = col0 + j;
-                    const int32_t cs = col < p.N ? p.colsum[col] : 0;
-                    r[j] = r[j] - uint32_t(za) * uint32_t(cs) + row_term;
-                }
-                if (p.epi.mode == EPI_RAW) {
-                    int32_t *o = static_cast<int32_t *>(p.out) + row * p.N + col0;
-                    if (vec4 && col0 + 32 <= p.N) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<int4 *>(o + j) = make_int4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < p.N; j++)
-                            o[j] = int32_t(r[j]);
-                    }
-                } else if (p.epi.mode == EPI_SCALE) {
-                    float *o = static_cast<float *>(p.out) + row * p.N + col0;
-                    float f[32];
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        if (col0 + j < p.N) {
-                            f[j] = epi_scale_value(p.epi, col0 + j, float(int32_t(r[j])));
-                            run_max = fmaxf(run_max, f[j]);
-                            run_neg = fmaxf(run_neg, -f[j]);
-                        } else {
-                            f[j] = 0.0f;
-                        }
-                    }
-                    if (vec4 && col0 + 32 <= p.N) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<float4 *>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < p.N; j++)
-                            o[j] = f[j];
-                    }
-                } else {
-                    uint8_t *o = static_cast<uint8_t *>(p.out) + row * p.N + col0;
-                    if (vec4 && col0 + 32 <= p.N) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            uint32_t w = 0;
-#pragma unroll
-                            for (int t = 0; t < 4; t++)
-                                w |= (uint32_t(epi_requant_value(p.epi, col0 + j + t, int32_t(r[j + t]))) & 0xffu) << (8 * t);
-                            *reinterpret_cast<uint32_t *>(o + j) = w;
-                        }
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < p.N; j++)
-                            o[j] = uint8_t(epi_requant_value(p.epi, col0 + j, int32_t(r[j])));
-                    }
-                }
-            }
+            epilogue_columns<BN>(p, tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BN), &acc_empty[b], lane, row,
+                                 row_ok, n0, row_term, za, run_max, run_neg);
             if (++b == 2) {
                 b = 0;
                 acc_ph ^= 1;
@@ -286,6 +300,156 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     __syncthreads();
     if (warp == 1)
         umma::tmem_dealloc(tmem_base, 2 * BN);
+}
+
+// ---------------------------------------------------------------------------
+// 256 x 256 tiles for large products.  A 128 x 256 tile takes 12 KB of operands
+// per K = 32 step, which at the tensor core's rate is more than the shared-memory
+// ring can keep in flight over the latency of the L2; a 256 x 256 tile (two
+// M = 128 MMAs per step sharing the B stage, the two accumulators filling all 512
+// tensor-memory columns) takes 16 KB per TWO steps' worth of MACs.  With no
+// spare accumulator a tile's epilogue does not overlap the next tile's MMAs,
+// which is cheap for the long K this kernel is chosen for.  Stages are 64 bytes
+// of K (six of 32 KB, 64B swizzle) so that five can be in flight.
+//   warp 0      TMA producer
+//   warp 1      tensor-memory allocation, MMA issue
+//   warps 2-9   epilogue: warps 2-5 the upper 128 rows, 6-9 the lower
+constexpr int BM2 = 256, BN2 = 256, BK2 = 64, STAGES2 = 6;
+constexpr int A2_BYTES = BM2 * BK2, B2_BYTES = BN2 * BK2;
+constexpr int THREADS2 = 10 * 32;
+constexpr size_t SMEM2 = size_t(STAGES2) * (A2_BYTES + B2_BYTES) + 1024 + 256;
+
+__global__ void __launch_bounds__(THREADS2, 1)
+mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TcParams p)
+{
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t *sA = smem;
+    uint8_t *sB = smem + STAGES2 * A2_BYTES;
+    uint64_t *full = reinterpret_cast<uint64_t *>(sB + STAGES2 * B2_BYTES);
+    uint64_t *empty = full + STAGES2;
+    uint64_t *acc_full = empty + STAGES2;  // the tile's accumulators are complete
+    uint64_t *acc_empty = acc_full + 1;    // the eight epilogue warps have read them
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tiles = (p.N + BN2 - 1) / BN2;
+    const int total_tiles = n_tiles * int((p.M + BM2 - 1) / BM2);
+    const int num_kb = (p.K + BK2 - 1) / BK2;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES2; s++) {
+            umma::mbar_init(&full[s], 1);
+            umma::mbar_init(&empty[s], 1);
+        }
+        umma::mbar_init(acc_full, 1);
+        umma::mbar_init(acc_empty, 8);
+        umma::fence_barrier_init();
+    }
+    if (warp == 1) {
+        umma::tmem_alloc(tmem_slot, 512);
+        umma::tmem_relinquish();
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            umma::prefetch_tmap(&tmA);
+            umma::prefetch_tmap(&tmB);
+            int s = 0;
+            uint32_t ph = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                const int m0 = (tile / n_tiles) * BM2, n0 = (tile % n_tiles) * BN2;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!wait_parked(&empty[s], ph ^ 1)) {
+                        atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
+                        tile = total_tiles;
+                        break;
+                    }
+                    umma::mbar_expect_tx(&full[s], A2_BYTES + B2_BYTES);
+                    umma::tma_load_2d(sA + s * A2_BYTES, &tmA, &full[s], kb * BK2, m0);
+                    umma::tma_load_2d(sB + s * B2_BYTES, &tmB, &full[s], kb * BK2, n0);
+                    if (++s == STAGES2) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma::instr_desc(2, p.a_signed ? 1 : 0, p.b_signed ? 1 : 0, 128, BN2);
+            // 64-byte rows, 64B swizzle: 512 bytes between 8-row groups
+            const uint32_t desc_hi = ((512u >> 4) & 0x3fffu) | (1u << 14) | (umma::LAYOUT_SW64 << 29);
+            const uint32_t a16 = (umma::smem_u32(sA) >> 4) | (1u << 16), b16 = (umma::smem_u32(sB) >> 4) | (1u << 16);
+            constexpr uint32_t HALF = (128 * BK2) >> 4;  // the lower 128 rows of a stage of A
+            bool ok = true;
+            int s = 0;
+            uint32_t ph = 0, acc_ph = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (!wait_bounded(acc_empty, acc_ph ^ 1)) {
+                    atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
+                    break;
+                }
+                umma::tc_fence_after();
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!wait_bounded(&full[s], ph)) {
+                        atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
+                        ok = false;
+                        break;
+                    }
+                    umma::tc_fence_after();
+                    const uint32_t a_lo = a16 + uint32_t(s) * (A2_BYTES >> 4);
+                    const uint32_t b_lo = b16 + uint32_t(s) * (B2_BYTES >> 4);
+                    const uint32_t acc = kb != 0;
+                    umma::mma_i8_lohi(tmem_base, a_lo, desc_hi, b_lo, desc_hi, idesc, acc);
+                    umma::mma_i8_lohi(tmem_base + BN2, a_lo + HALF, desc_hi, b_lo, desc_hi, idesc, acc);
+                    umma::mma_i8_lohi(tmem_base, a_lo + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
+                    umma::mma_i8_lohi(tmem_base + BN2, a_lo + HALF + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
+                    umma::mma_commit(&empty[s]);
+                    if (++s == STAGES2) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (ok)
+                    umma::mma_commit(acc_full);
+                acc_ph ^= 1;
+            }
+        }
+    } else {
+        const int q = warp & 3;           // tensor-memory lane quarter this warp may read
+        const int half = (warp - 2) >> 2;  // upper or lower 128 rows of the tile
+        const int32_t za = load_zp(p.a_zp, p.a_signed), zb = load_zp(p.b_zp, p.b_signed);
+        float run_max = 0.0f, run_neg = 0.0f;
+        bool ready = true;
+        uint32_t acc_ph = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            const int64_t m0 = int64_t(tile / n_tiles) * BM2 + half * 128;
+            const int n0 = (tile % n_tiles) * BN2;
+            if (ready && !wait_parked(acc_full, acc_ph)) {
+                ready = false;
+                if (lane == 0)
+                    atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
+            }
+            umma::tc_fence_after();
+            const int64_t row = m0 + q * 32 + lane;
+            const bool row_ok = ready && row < p.M;
+            const uint32_t row_term = uint32_t(p.K) * uint32_t(za) * uint32_t(zb) -
+                                      ((zb != 0 && p.rowsum && row_ok) ? uint32_t(zb) * uint32_t(p.rowsum[row]) : 0u);
+            epilogue_columns<BN2>(p, tmem_base + (uint32_t(q * 32) << 16) + uint32_t(half * BN2), acc_empty, lane, row,
+                                  row_ok, n0, row_term, za, run_max, run_neg);
+            acc_ph ^= 1;
+        }
+        if (p.epi.mode == EPI_SCALE)
+            epi_fold_range(p.epi, run_max, run_neg);
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    if (warp == 1)
+        umma::tmem_dealloc(tmem_base, 512);
 }
 
 // sum_k a[m][k] per row, needed only when the weight's zero point is not 0:
@@ -329,6 +493,42 @@ int32_t launch(ovk_ctx *ctx, const CUtensorMap &tmA, const ovk_mmi_weight *w, co
     return OVK_OK;
 }
 
+// 256 x 256 tiles: chosen for long K (the epilogue is not overlapped) and enough tiles to keep the
+// SMs in whole waves.
+int32_t launch256(ovk_ctx *ctx, const void *a, const ovk_mmi_weight *w, const TcParams &p)
+{
+    CUtensorMap tmA, tmB;
+    if (!ovk_make_tmap_2d(&tmA, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(w->k), uint64_t(p.M), uint64_t(w->k), BK2,
+                          BM2, CU_TENSOR_MAP_SWIZZLE_64B) ||
+        !ovk_make_tmap_2d(&tmB, w->bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(w->k_pad), uint64_t(w->n_pad),
+                          uint64_t(w->k_pad), BK2, BN2, CU_TENSOR_MAP_SWIZZLE_64B))
+        return ovk_fail(ctx, OVK_BACKEND, "MatMulInteger: cuTensorMapEncodeTiled failed (256 x 256 tiles)");
+    OVK_CUDA(ctx, cudaFuncSetAttribute(mmi_tc256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM2)));
+    const int64_t tiles = ceil_div64(p.N, BN2) * ceil_div64(p.M, BM2);
+    const unsigned grid = unsigned(std::min<int64_t>(tiles, ctx->sm_count));
+    mmi_tc256_kernel<<<grid, THREADS2, SMEM2, ctx->stream>>>(tmA, tmB, p);
+    OVK_LAUNCHED(ctx, "mmi_tc_256x256");
+    return OVK_OK;
+}
+
+bool wants256(const ovk_ctx *ctx, const ovk_mmi_weight *w, int64_t m)
+{
+    // OVK_MMI_TILE=128 / 256 pins the choice (for tests that compare the two kernels)
+    static const char *pin = getenv("OVK_MMI_TILE");
+    if (pin && pin[0] == '1')
+        return false;
+    if (SMEM2 > ctx->smem_optin || m >= (int64_t(1) << 31) - BM2)
+        return false;
+    if (pin && pin[0] == '2')
+        return true;
+    if (w->k < 2048 || w->n < 256 || m < 256)
+        return false;
+    const int64_t tiles = ceil_div64(w->n, BN2) * ceil_div64(m, BM2);
+    // at least three waves, or an almost full last wave
+    const int64_t waves = ceil_div64(tiles, ctx->sm_count);
+    return tiles >= 3 * int64_t(ctx->sm_count) || (tiles >= ctx->sm_count && tiles * 10 >= waves * ctx->sm_count * 9);
+}
+
 }  // namespace
 
 // The tensor-core tiles need whole 16-byte rows of A for TMA and enough work
@@ -370,6 +570,8 @@ int32_t ovk_mmi_tc_launch(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, 
             static_cast<const uint8_t *>(a), m, p.K, p.a_signed, b_zp, p.b_signed, static_cast<int32_t *>(ws));
         OVK_LAUNCHED(ctx, "mmi_rowsum");
     }
+    if (wants256(ctx, w, m))
+        return launch256(ctx, a, w, p);
     CUtensorMap tmA;
     if (!ovk_make_tmap_2d(&tmA, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(w->k), uint64_t(m), uint64_t(w->k), BK,
                           BM, CU_TENSOR_MAP_SWIZZLE_128B))

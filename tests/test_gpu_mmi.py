@@ -174,3 +174,16 @@ def test_accumulator_overflow_guard():
     w = ctx().mmi_prepack(b)
     with pytest.raises(ovk_b200.OvkError):
         ctx().matmul_integer(w, torch.zeros((1, 33026), dtype=torch.uint8, device="cuda"))
+
+
+@pytest.mark.parametrize("m,k,n,a_signed,b_signed", [(1000, 2064, 9470, 0, 1), (1024, 2048, 9472, 1, 0)])
+def test_large_product_takes_256_tiles(m, k, n, a_signed, b_signed):
+    """Long K and exactly one wave of 256 x 256 tiles: ragged edges in M, N and K, both zero points."""
+    a = cases.lcg_bytes_fast(m * k, 19).reshape(m, k)
+    b = cases.lcg_bytes_fast(k * n, 23).reshape(k, n)
+    a = a.view(np.int8) if a_signed else a
+    b = b.view(np.int8) if b_signed else b
+    azp, bzp = (-5 if a_signed else 131), (-7 if b_signed else 121)
+    got, kernel = run_mmi(a, b, azp, bzp)
+    assert kernel == "mmi_tc_256x256"
+    assert np.array_equal(got, orc.matmul_integer(a, b, azp, bzp))
