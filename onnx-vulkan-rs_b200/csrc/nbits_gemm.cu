@@ -27,6 +27,8 @@
 // Weight columns sit on tensor-memory LANES so the scale is one scalar per thread.
 // The promotion warps hold 128 accumulators each: the register file is
 // re-divided between the warpgroups with setmaxnreg.
+#include <cstdlib>
+
 #include "ovk_internal.h"
 #include "umma.cuh"
 
@@ -491,10 +493,17 @@ bool ovk_nbits_gemm_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int64
            aligned_to(w->scales, w->scales_dtype == OVK_FLOAT ? 4 : 2);
 }
 
+bool ovk_nbits_gemm_split_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w);
+int32_t ovk_nbits_gemm_split(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int64_t m, void *y, int32_t y_dtype);
+
 int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, int32_t a_dtype, int64_t m,
                        void *y, int32_t y_dtype)
 {
     (void)a_dtype;
+    // small blocks with fp16 scales: the scale goes into the weight (exactly, as two fp16 terms)
+    static const char *pin = getenv("OVK_NBITS_GEMM");  // "blocks" pins the per-block kernel (for comparisons)
+    if (!(pin && pin[0] == 'b') && ovk_nbits_gemm_split_applies(ctx, wc))
+        return ovk_nbits_gemm_split(ctx, wc, a, m, y, y_dtype);
     ovk_nbits_weight *w = const_cast<ovk_nbits_weight *>(wc);  // the prefill copy is built lazily
     int32_t rc = ovk_nbits_gemm_prepack(ctx, w);
     if (rc != OVK_OK)

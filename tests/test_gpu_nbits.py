@@ -129,7 +129,9 @@ def test_prefill_against_the_oracle(k, n, bs, m):
         pytest.skip("covered by the sampled full-size test")
     a, nib, zp, scale = cases.nbits_synthetic(2, m, k, n, bs)
     got, kern = run_gpu(a, nib, zp, scale, k, n, bs)
-    assert kern == "nbits_gemm_tc"
+    # blocks of 32 and 64 with fp16 scales: the scale goes into the weight as two exact fp16 terms;
+    # larger blocks: integer weights, each block's partial sum scaled in f32
+    assert kern == ("nbits_gemm_tc_split" if bs <= 64 else "nbits_gemm_tc")
     want = orc.matmul_nbits(a, orc.pack_nibbles(nib, bs), scale, orc.pack_zero_points(zp), k, n, bs)
     assert_close(got, want, 1e-3, 1e-3, f"prefill {k}->{n} bs={bs} M={m}")
 
@@ -137,9 +139,19 @@ def test_prefill_against_the_oracle(k, n, bs, m):
 def test_prefill_f32_output_and_missing_zero_points():
     a, nib, _, scale = cases.nbits_synthetic(6, 77, 640, 300, 32, with_zp=False)
     got, kern = run_gpu(a, nib, None, scale, 640, 300, 32, out_dtype=torch.float32)
-    assert kern == "nbits_gemm_tc" and got.dtype == np.float32
+    assert kern == "nbits_gemm_tc_split" and got.dtype == np.float32
     want = orc.matmul_nbits(a, orc.pack_nibbles(nib, 32), scale, None, 640, 300, 32, out_dtype=np.float32)
     assert_close(got, want, 1e-4, 1e-4, "prefill f32 out")
+
+
+def test_prefill_small_blocks_with_f32_scales_keep_the_per_block_kernel():
+    """An f32 scale is not one fp16 number: the scale stays outside the MMA."""
+    a, nib, zp, scale = cases.nbits_synthetic(6, 40, 256, 200, 32)
+    scale32 = (scale.astype(np.float32) * np.float32(1.0001)).astype(np.float32)
+    got, kern = run_gpu(a, nib, zp, scale32, 256, 200, 32)
+    assert kern == "nbits_gemm_tc"
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, 32), scale32, orc.pack_zero_points(zp), 256, 200, 32)
+    assert_close(got, want, 1e-3, 1e-3, "prefill, f32 scales")
 
 
 def test_prefill_ragged_k_and_f32_activations_fall_back_to_the_general_kernel():
