@@ -538,9 +538,15 @@ def run_one(which):
         w = make_weight(torch, ctx, 3584, 18944, 128, gen, 0.001, 0.01)
         a = torch.randn((1024, 3584), device="cuda", generator=gen).to(torch.float16)
         fn = lambda: ctx.matmul_nbits(w, a)
-    elif which == "int8":
-        w = ctx.mmi_prepack(torch.randint(-127, 128, (4096, 4096), dtype=torch.int8, device="cuda", generator=gen))
-        a = torch.randint(0, 256, (4096, 4096), dtype=torch.uint8, device="cuda", generator=gen)
+    elif which == "prefill32":
+        w = make_weight(torch, ctx, HIDDEN, VOCAB, BLOCK, gen)
+        a = torch.randn((512, HIDDEN), device="cuda", generator=gen).to(torch.float16)
+        y = torch.empty((512, VOCAB), dtype=torch.float16, device="cuda")
+        fn = lambda: ctx.matmul_nbits(w, a, out=y)
+    elif which in ("int8", "int8big"):
+        d = 4096 if which == "int8" else 8192
+        w = ctx.mmi_prepack(torch.randint(-127, 128, (d, d), dtype=torch.int8, device="cuda", generator=gen))
+        a = torch.randint(0, 256, (d, d), dtype=torch.uint8, device="cuda", generator=gen)
         zp = torch.full((1,), 128, dtype=torch.uint8, device="cuda")
         fn = lambda: ctx.matmul_integer(w, a, zp, None)
     else:
@@ -640,7 +646,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the prefill / int8 / conv lines")
     ap.add_argument("--no-graph", action="store_true", help="launch the per-layer GEMVs eagerly")
     ap.add_argument("--serial", action="store_true", help="one serial chain of GEMVs instead of parallel q|k|v and gate|up")
-    ap.add_argument("--one", default=None, choices=["lm_head", "prefill", "int8", "conv"],
+    ap.add_argument("--one", default=None, choices=["lm_head", "prefill", "prefill32", "int8", "int8big", "conv"],
                     help="run one operator three times and exit (small target for an ncu capture)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -83,6 +83,7 @@ __device__ __forceinline__ bool wait_parked(uint64_t *bar, uint32_t parity)
     for (;;) {
         if (umma::mbar_try_wait_hint(bar, parity, 1000u))
             return true;
+        __nanosleep(64);  // out of the issue slots of the thread that feeds the tensor core
         if (clock64() - t0 > WAIT_CYCLES)
             return false;
     }
