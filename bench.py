@@ -259,6 +259,15 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
         for _ in range(10):
             conv()
     ms_q = timed(torch, dist, world, gq.replay, 10) / 10
+    if world == 1:
+        # the residual add that follows a quantized block (resnet50: 256 x 56 x 56), one byte per element and side
+        qa = torch.randint(0, 256, (64, 256, 56, 56), dtype=torch.uint8, device="cuda", generator=gen)
+        qb = torch.randint(0, 256, (64, 256, 56, 56), dtype=torch.uint8, device="cuda", generator=gen)
+        ms_a = timed(torch, dist, 1, lambda: ctx.qlinear_add(qa, 0.02, 128, qb, 0.05, 100, 0.03, 30), 10)
+        out["int8_qlinear_add_resnet"] = {"shape": [64, 256, 56, 56], "ms": ms_a, "kernel": ctx.last_kernel,
+                                          "algorithmic_gbs": 3.0 * qa.numel() / (ms_a * 1e-3) / 1e9,
+                                          "frac_of_measured_hbm": 3.0 * qa.numel() / (ms_a * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        del qa, qb
     ops = 2.0 * 64 * 64 * 56 * 56 * 576
     out["int8_qlinear_conv_resnet_block"] = {"batch": 64, "ms": ms_q, "kernel": ctx.last_kernel,
                                              "tops": ops / (ms_q * 1e-3) / 1e12,

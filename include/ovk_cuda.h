@@ -247,6 +247,45 @@ OVK_API int32_t ovk_gather_block_quantized(ovk_ctx *ctx, const void *table, cons
 OVK_API int32_t ovk_argmax(ovk_ctx *ctx, const void *x, int32_t x_dtype, int64_t outer, int64_t c,
                            int64_t inner, int64_t *out);
 
+/* ------------------------- the rest of the QOperator chain around QLinearConv
+ * interp::qlinear_add (interp.rs:4878-4962, kernel shaders/qlinear.rs:69-143):
+ * C = saturate(rne(fma(A, ra, fma(B, rb, fixed)))) with ra = A_scale/C_scale,
+ * rb = B_scale/C_scale, fixed = c_zp - fma(ra, a_zp, rb*b_zp) in f32 - MLAS's
+ * kernel operation for operation, including ORT's exchange of the operands when
+ * A is constant along the innermost broadcast span.  General ONNX broadcasting up
+ * to rank 8; shapes, scales and zero points are host values.  a, b, out are
+ * device pointers to u8 (is_signed = 0) or i8 codes; out_shape (8 entries) and
+ * out_rank receive the broadcast shape (may be NULL). */
+OVK_API int32_t ovk_qlinear_add(ovk_ctx *ctx, const void *a, const int64_t *a_shape, int32_t a_rank,
+                                float a_scale, int32_t a_zp, const void *b, const int64_t *b_shape,
+                                int32_t b_rank, float b_scale, int32_t b_zp, float c_scale,
+                                int32_t c_zp, int32_t is_signed, void *out, int64_t *out_shape,
+                                int32_t *out_rank);
+/* MaxPool on quantized codes (shaders/qlinear.rs:145-211): x is [n, c, h, w]
+ * u8 / i8; kernel, strides, dilations have 2 entries, pads 4 (h_begin, w_begin,
+ * h_end, w_end); floor mode; padding taps are skipped.  h_out / w_out receive
+ * the output size. */
+OVK_API int32_t ovk_maxpool_q(ovk_ctx *ctx, const void *x, int32_t is_signed, int64_t n, int64_t c,
+                              int64_t h, int64_t w, const int64_t *kernel, const int64_t *strides,
+                              const int64_t *pads, const int64_t *dilations, void *out,
+                              int64_t *h_out, int64_t *w_out);
+/* QuantizeLinear / DequantizeLinear (interp.rs:5055-5177, shaders/quantize_linear.rs):
+ * channel of element i is (i / inner) % axis_len (per-tensor: inner = axis_len = 1);
+ * scale is a device array of axis_len floats, zero_point a device array of
+ * axis_len codes of the quantized type (int32 for int32 input) or NULL. */
+OVK_API int32_t ovk_quantize_linear(ovk_ctx *ctx, const float *x, int64_t n, int64_t inner,
+                                    int64_t axis_len, const float *scale, const void *zero_point,
+                                    int32_t is_signed, void *out);
+OVK_API int32_t ovk_dequantize_linear(ovk_ctx *ctx, const void *x, int32_t x_dtype, int64_t n,
+                                      int64_t inner, int64_t axis_len, const float *scale,
+                                      const void *zero_point, float *out);
+/* interp::qlinear_global_average_pool (interp.rs:4975-5000): dequantize, average
+ * over the hw elements of each of the n*c planes (a sequential f32 sum, as the
+ * reference's pooling kernel forms it, shaders/pooling.rs:38-54), quantize. */
+OVK_API int32_t ovk_qlinear_global_average_pool(ovk_ctx *ctx, const void *x, int32_t is_signed,
+                                                int64_t n, int64_t c, int64_t hw, float x_scale,
+                                                int32_t x_zp, float y_scale, int32_t y_zp, void *out);
+
 #ifdef __cplusplus
 }
 #endif

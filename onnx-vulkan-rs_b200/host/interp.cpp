@@ -523,6 +523,191 @@ Result argmax(Env &env, const NodeIr &node)
                                               static_cast<int64_t *>(out->dev)));
 }
 
+// ------------------------------------------ the QOperator chain around QLinearConv
+Result scalar_f32(const Env &env, const std::string &name, const char *what, float *out)
+{
+    std::vector<float> v;
+    OVKH_TRY(floats_of(env, name, what, &v));
+    OVKH_ENSURE(v.size() == 1, "%s: %s is not per-tensor", what, name.c_str());
+    *out = v[0];
+    return Result{};
+}
+
+// interp::qlinear_add (interp.rs:4878-4962)
+Result qlinear_add(Env &env, const NodeIr &node)
+{
+    const Tensor *a = env.find(node.inputs[0]);
+    const Tensor *b = env.find(node.inputs[3]);
+    OVKH_ENSURE(a && b, "QLinearAdd: an operand is missing");
+    float a_scale, b_scale, c_scale;
+    int32_t a_zp, b_zp, c_zp;
+    OVKH_TRY(scalar_f32(env, node.inputs[1], "QLinearAdd", &a_scale));
+    OVKH_TRY(scalar_f32(env, node.inputs[4], "QLinearAdd", &b_scale));
+    OVKH_TRY(scalar_f32(env, node.inputs[6], "QLinearAdd", &c_scale));
+    OVKH_ENSURE(c_scale != 0.0f, "QLinearAdd: C_scale is zero");
+    OVKH_TRY(scalar_i32(env, node.inputs[2], "QLinearAdd", &a_zp));
+    OVKH_TRY(scalar_i32(env, node.inputs[5], "QLinearAdd", &b_zp));
+    OVKH_TRY(scalar_i32(env, node.inputs[7], "QLinearAdd", &c_zp));
+    const int32_t out_dtype = env.find(node.inputs[7])->dtype;
+    OVKH_ENSURE((a->dtype == OVK_UINT8 || a->dtype == OVK_INT8) && a->dtype == b->dtype && a->dtype == out_dtype,
+                "QLinearAdd: operand dtypes %d/%d/%d", a->dtype, b->dtype, out_dtype);
+    OVKH_ENSURE(a->shape.size() <= 8 && b->shape.size() <= 8, "QLinearAdd: rank %zu > 8",
+                std::max(a->shape.size(), b->shape.size()));
+    // the broadcast shape first (the entry point computes it again and checks it)
+    const size_t rank = std::max(a->shape.size(), b->shape.size());
+    std::vector<int64_t> out_shape(rank);
+    for (size_t d = 0; d < rank; d++) {
+        const int64_t ea = d + a->shape.size() >= rank ? a->shape[d + a->shape.size() - rank] : 1;
+        const int64_t eb = d + b->shape.size() >= rank ? b->shape[d + b->shape.size() - rank] : 1;
+        OVKH_ENSURE(ea == eb || ea == 1 || eb == 1, "QLinearAdd: shapes do not broadcast");
+        out_shape[d] = ea == 1 ? eb : ea;
+    }
+    Tensor *out = nullptr;
+    OVKH_TRY(env.alloc(node.outputs[0], out_dtype, out_shape, &out));
+    a = env.find(node.inputs[0]);
+    b = env.find(node.inputs[3]);
+    return from_abi(env.context(),
+                    ovk_qlinear_add(env.context(), a->dev, a->shape.data(), int32_t(a->shape.size()), a_scale, a_zp, b->dev,
+                                    b->shape.data(), int32_t(b->shape.size()), b_scale, b_zp, c_scale, c_zp,
+                                    out_dtype == OVK_INT8, out->dev, nullptr, nullptr));
+}
+
+// MaxPool on a quantized tensor (interp.rs: pool() takes the MAXPOOL_Q kernel for u8 / i8 input)
+Result maxpool_q(Env &env, const NodeIr &node)
+{
+    const Tensor *x = env.find(node.inputs[0]);
+    OVKH_ENSURE(x, "MaxPool: x is missing");
+    if (x->dtype != OVK_UINT8 && x->dtype != OVK_INT8)
+        return fail(OVK_UNSUPPORTED, "MaxPool: dtype %d is pooled by the host runtime's float kernel, not by this layer", x->dtype);
+    OVKH_ENSURE(x->shape.size() == 4, "MaxPool: only NCHW (rank %zu)", x->shape.size());
+    std::vector<int64_t> ks = node.ints_attr("kernel_shape"), st = node.ints_attr("strides"), dl = node.ints_attr("dilations"),
+                         pd = node.ints_attr("pads");
+    OVKH_ENSURE(ks.size() == 2, "MaxPool: kernel_shape must have two entries");
+    if (st.empty())
+        st.assign(2, 1);
+    if (dl.empty())
+        dl.assign(2, 1);
+    if (pd.empty())
+        pd.assign(4, 0);
+    OVKH_ENSURE(st.size() == 2 && dl.size() == 2 && pd.size() == 4, "MaxPool: strides/dilations/pads of wrong length");
+    const std::string auto_pad = node.str_attr("auto_pad", "NOTSET");
+    if (auto_pad == "VALID") {
+        pd.assign(4, 0);
+    } else if (auto_pad == "SAME_UPPER" || auto_pad == "SAME_LOWER") {
+        for (size_t d = 0; d < 2; d++)
+            same_pads(auto_pad == "SAME_UPPER", x->shape[2 + d], ks[d], st[d], dl[d], &pd[d], &pd[2 + d]);
+    } else if (auto_pad != "NOTSET") {
+        return fail(OVK_UNSUPPORTED, "MaxPool: auto_pad '%s' not supported", auto_pad.c_str());
+    }
+    const int64_t ho = (x->shape[2] + pd[0] + pd[2] - (dl[0] * (ks[0] - 1) + 1)) / st[0] + 1;
+    const int64_t wo = (x->shape[3] + pd[1] + pd[3] - (dl[1] * (ks[1] - 1) + 1)) / st[1] + 1;
+    OVKH_ENSURE(ho > 0 && wo > 0, "MaxPool: degenerate output shape");
+    const int32_t dtype = x->dtype;
+    const std::vector<int64_t> shape = x->shape;
+    Tensor *out = nullptr;
+    OVKH_TRY(env.alloc(node.outputs[0], dtype, {shape[0], shape[1], ho, wo}, &out));
+    x = env.find(node.inputs[0]);
+    return from_abi(env.context(), ovk_maxpool_q(env.context(), x->dev, dtype == OVK_INT8, shape[0], shape[1], shape[2],
+                                                 shape[3], ks.data(), st.data(), pd.data(), dl.data(), out->dev, nullptr,
+                                                 nullptr));
+}
+
+// qdq_layout (interp.rs:5006-5035)
+Result qdq_layout(const NodeIr &node, const std::vector<int64_t> &x_shape, const Tensor &scale, int64_t *inner, int64_t *axis_len)
+{
+    const int64_t len = std::max<int64_t>(scale.elem_count(), 1);
+    *inner = 1;
+    *axis_len = 1;
+    if (scale.shape.empty() || len == 1)
+        return Result{};
+    OVKH_ENSURE(scale.shape.size() == 1, "%s: per-axis scale must be 1-D", node.op.c_str());
+    const int64_t rank = int64_t(x_shape.size());
+    int64_t axis = node.int_attr("axis", 1);
+    if (axis < 0)
+        axis += rank;
+    OVKH_ENSURE(axis >= 0 && axis < rank, "%s: axis %lld out of rank %lld", node.op.c_str(), (long long)axis, (long long)rank);
+    OVKH_ENSURE(x_shape[size_t(axis)] == len, "%s: scale of length %lld, axis %lld of dimension %lld", node.op.c_str(),
+                (long long)len, (long long)axis, (long long)x_shape[size_t(axis)]);
+    *inner = std::max<int64_t>(product(x_shape, size_t(axis) + 1, x_shape.size()), 1);
+    *axis_len = len;
+    return Result{};
+}
+
+// interp::quantize_linear (interp.rs:5117-5177)
+Result quantize_linear(Env &env, const NodeIr &node)
+{
+    const Tensor *x = env.find(node.inputs[0]);
+    const Tensor *scale = env.find(node.inputs[1]);
+    const Tensor *zp = node.present(2) ? env.find(node.inputs[2]) : nullptr;
+    OVKH_ENSURE(x && scale && (zp || !node.present(2)), "QuantizeLinear: an input is missing");
+    OVKH_ENSURE(x->dtype == OVK_FLOAT && scale->dtype == OVK_FLOAT, "QuantizeLinear: x and scale must be float32");
+    const int32_t out_dtype = zp ? zp->dtype : int32_t(node.int_attr("output_dtype", OVK_UINT8));
+    OVKH_ENSURE(out_dtype == OVK_UINT8 || out_dtype == OVK_INT8,
+                "QuantizeLinear: output dtype %d not supported (only uint8/int8)", out_dtype);
+    int64_t inner, axis_len;
+    OVKH_TRY(qdq_layout(node, x->shape, *scale, &inner, &axis_len));
+    const std::vector<int64_t> shape = x->shape;
+    const int64_t n = x->elem_count();
+    Tensor *out = nullptr;
+    OVKH_TRY(env.alloc(node.outputs[0], out_dtype, shape, &out));
+    x = env.find(node.inputs[0]);
+    scale = env.find(node.inputs[1]);
+    zp = node.present(2) ? env.find(node.inputs[2]) : nullptr;
+    return from_abi(env.context(), ovk_quantize_linear(env.context(), static_cast<const float *>(x->dev), n, inner, axis_len,
+                                                       static_cast<const float *>(scale->dev), zp ? zp->dev : nullptr,
+                                                       out_dtype == OVK_INT8, out->dev));
+}
+
+// interp::dequantize_linear (interp.rs:5055-5115)
+Result dequantize_linear(Env &env, const NodeIr &node)
+{
+    const Tensor *x = env.find(node.inputs[0]);
+    const Tensor *scale = env.find(node.inputs[1]);
+    const Tensor *zp = node.present(2) ? env.find(node.inputs[2]) : nullptr;
+    OVKH_ENSURE(x && scale && (zp || !node.present(2)), "DequantizeLinear: an input is missing");
+    OVKH_ENSURE(x->dtype == OVK_UINT8 || x->dtype == OVK_INT8 || x->dtype == OVK_INT32,
+                "DequantizeLinear: dtype %d not supported (only uint8/int8/int32)", x->dtype);
+    OVKH_ENSURE(scale->dtype == OVK_FLOAT && (!zp || zp->dtype == x->dtype), "DequantizeLinear: scale or zero point dtype");
+    int64_t inner, axis_len;
+    OVKH_TRY(qdq_layout(node, x->shape, *scale, &inner, &axis_len));
+    const std::vector<int64_t> shape = x->shape;
+    const int64_t n = x->elem_count();
+    const int32_t dtype = x->dtype;
+    Tensor *out = nullptr;
+    OVKH_TRY(env.alloc(node.outputs[0], OVK_FLOAT, shape, &out));
+    x = env.find(node.inputs[0]);
+    scale = env.find(node.inputs[1]);
+    zp = node.present(2) ? env.find(node.inputs[2]) : nullptr;
+    return from_abi(env.context(), ovk_dequantize_linear(env.context(), x->dev, dtype, n, inner, axis_len,
+                                                         static_cast<const float *>(scale->dev), zp ? zp->dev : nullptr,
+                                                         static_cast<float *>(out->dev)));
+}
+
+// interp::qlinear_global_average_pool (interp.rs:4975-5000)
+Result qlinear_global_average_pool(Env &env, const NodeIr &node)
+{
+    const Tensor *x = env.find(node.inputs[0]);
+    OVKH_ENSURE(x && x->shape.size() >= 2, "QLinearGlobalAveragePool: x is missing or has rank < 2");
+    OVKH_ENSURE(node.int_attr("channels_last", 0) == 0, "QLinearGlobalAveragePool: channels_last is not supported");
+    float x_scale, y_scale;
+    int32_t x_zp, y_zp;
+    OVKH_TRY(scalar_f32(env, node.inputs[1], "QLinearGlobalAveragePool", &x_scale));
+    OVKH_TRY(scalar_i32(env, node.inputs[2], "QLinearGlobalAveragePool", &x_zp));
+    OVKH_TRY(scalar_f32(env, node.inputs[3], "QLinearGlobalAveragePool", &y_scale));
+    OVKH_TRY(scalar_i32(env, node.inputs[4], "QLinearGlobalAveragePool", &y_zp));
+    OVKH_ENSURE(x->dtype == OVK_UINT8 || x->dtype == OVK_INT8, "QLinearGlobalAveragePool: x has dtype %d", x->dtype);
+    std::vector<int64_t> out_shape = x->shape;
+    for (size_t d = 2; d < out_shape.size(); d++)
+        out_shape[d] = 1;
+    const int64_t n = x->shape[0], c = x->shape[1], hw = product(x->shape, 2, x->shape.size());
+    const int32_t dtype = x->dtype;
+    Tensor *out = nullptr;
+    OVKH_TRY(env.alloc(node.outputs[0], dtype, out_shape, &out));
+    x = env.find(node.inputs[0]);
+    return from_abi(env.context(), ovk_qlinear_global_average_pool(env.context(), x->dev, dtype == OVK_INT8, n, c, hw, x_scale,
+                                                                   x_zp, y_scale, y_zp, out->dev));
+}
+
 }  // namespace
 
 // ----------------------------------------------------------------------- types
@@ -662,6 +847,19 @@ bool is_implemented_node(const NodeIr &node)
     if (op == "ArgMax")  // the reversed tie-break is refused (tests/argmax.rs:192)
         return node.inputs.size() == 1 && node.outputs.size() == 1 && node.int_attr("select_last_index", 0) == 0 &&
                (node.int_attr("keepdims", 1) == 0 || node.int_attr("keepdims", 1) == 1);
+    if (op == "QLinearAdd" || op == "QLinearGlobalAveragePool") {
+        const size_t want = op == "QLinearAdd" ? 8 : 5;
+        bool all = node.inputs.size() == want;
+        for (size_t i = 0; all && i < want; i++)
+            all = node.present(i);
+        return all && node.outputs.size() == 1;
+    }
+    if (op == "QuantizeLinear" || op == "DequantizeLinear")
+        return node.inputs.size() >= 2 && node.inputs.size() <= 3 && node.present(0) && node.present(1) &&
+               node.outputs.size() == 1 && node.int_attr("block_size", 0) == 0;
+    if (op == "MaxPool")  // the quantized-domain pooling; a float input is refused at dispatch
+        return node.inputs.size() == 1 && node.outputs.size() == 1 && node.int_attr("ceil_mode", 0) == 0 &&
+               node.int_attr("storage_order", 0) == 0;
     if (op == "DynamicQuantizeLinear")
         return node.inputs.size() == 1 && node.outputs.size() == 3;
     if (op == "MatMulInteger")
@@ -694,10 +892,6 @@ std::string unsupported_quantization(const NodeIr &node, const Env &env)
         size_t scale, zero;
         const char *slot;
     };
-    if (node.op != "QLinearConv" && node.op != "QLinearMatMul")
-        return "";
-    const bool conv = node.op == "QLinearConv";
-    const Pair scalar_pairs[2] = {{1, 2, conv ? "x" : "a"}, {6, 7, "y"}};
     auto constant = [&](size_t index) -> const Tensor * {
         if (!node.present(index))
             return nullptr;
@@ -705,7 +899,7 @@ std::string unsupported_quantization(const NodeIr &node, const Env &env)
         return t && t->initializer ? t : nullptr;
     };
     auto refuse = [&](const char *slot, const char *why) { return node.op + ": " + slot + " " + why; };
-    for (const Pair &p : scalar_pairs) {
+    auto check_scalar = [&](const Pair &p) -> std::string {
         const Tensor *scale = constant(p.scale), *zero = constant(p.zero);
         if (!scale || !zero)
             return refuse(p.slot, "scale or zero point is not a constant");
@@ -713,6 +907,28 @@ std::string unsupported_quantization(const NodeIr &node, const Env &env)
             return refuse(p.slot, "scale is not float32");
         if (std::max<int64_t>(scale->elem_count(), 1) != 1 || std::max<int64_t>(zero->elem_count(), 1) != 1)
             return refuse(p.slot, "scale or zero point is not per-tensor");
+        return "";
+    };
+    if (node.op == "QLinearAdd" || node.op == "QLinearGlobalAveragePool") {
+        const Pair add_pairs[3] = {{1, 2, "A"}, {4, 5, "B"}, {6, 7, "C"}};
+        const Pair gap_pairs[2] = {{1, 2, "x"}, {3, 4, "y"}};
+        const Pair *pairs = node.op == "QLinearAdd" ? add_pairs : gap_pairs;
+        const int count = node.op == "QLinearAdd" ? 3 : 2;
+        for (int i = 0; i < count; i++) {
+            const std::string why = check_scalar(pairs[i]);
+            if (!why.empty())
+                return why;
+        }
+        return "";
+    }
+    if (node.op != "QLinearConv" && node.op != "QLinearMatMul")
+        return "";
+    const bool conv = node.op == "QLinearConv";
+    const Pair scalar_pairs[2] = {{1, 2, conv ? "x" : "a"}, {6, 7, "y"}};
+    for (const Pair &p : scalar_pairs) {
+        const std::string why = check_scalar(p);
+        if (!why.empty())
+            return why;
     }
     const char *slot = conv ? "w" : "b";
     const Tensor *scale = constant(4), *zero = constant(5);
@@ -757,6 +973,18 @@ Result exec_dispatch(Env &env, const NodeIr &node)
         return gather_block_quantized(env, node);
     if (node.op == "ArgMax")
         return argmax(env, node);
+    if (node.op == "QLinearAdd" || node.op == "QLinearGlobalAveragePool") {
+        const std::string refusal = unsupported_quantization(node, env);
+        if (!refusal.empty())
+            return fail(OVK_UNSUPPORTED, "%s", refusal.c_str());
+        return node.op == "QLinearAdd" ? qlinear_add(env, node) : qlinear_global_average_pool(env, node);
+    }
+    if (node.op == "MaxPool")
+        return maxpool_q(env, node);
+    if (node.op == "QuantizeLinear")
+        return quantize_linear(env, node);
+    if (node.op == "DequantizeLinear")
+        return dequantize_linear(env, node);
     return qlinear_conv(env, node);
 }
 

@@ -75,6 +75,13 @@ SIGNATURES = {
     "ovk_requantize": (_I32, [_P, _P, _I64, _I64, _I64, _P, _P, _I32, _I32, _P]),
     "ovk_gather_block_quantized": (_I32, [_P, _P, _P, _I32, _P, _I64, _I64, _I64, _I64, _P, _I32, _I32, _I64, _P, _I32]),
     "ovk_argmax": (_I32, [_P, _P, _I32, _I64, _I64, _I64, _P]),
+    "ovk_qlinear_add": (_I32, [_P, _P, C.POINTER(_I64), _I32, C.c_float, _I32, _P, C.POINTER(_I64), _I32, C.c_float, _I32,
+                               C.c_float, _I32, _I32, _P, C.POINTER(_I64), C.POINTER(_I32)]),
+    "ovk_maxpool_q": (_I32, [_P, _P, _I32, _I64, _I64, _I64, _I64, C.POINTER(_I64), C.POINTER(_I64), C.POINTER(_I64),
+                             C.POINTER(_I64), _P, C.POINTER(_I64), C.POINTER(_I64)]),
+    "ovk_quantize_linear": (_I32, [_P, _P, _I64, _I64, _I64, _P, _P, _I32, _P]),
+    "ovk_dequantize_linear": (_I32, [_P, _P, _I32, _I64, _I64, _I64, _P, _P, _P]),
+    "ovk_qlinear_global_average_pool": (_I32, [_P, _P, _I32, _I64, _I64, _I64, C.c_float, _I32, C.c_float, _I32, _P]),
 }
 
 
@@ -310,6 +317,71 @@ class Context:
         if out is None:
             out = torch.empty(tuple(x.shape[:axis]) + tuple(x.shape[axis + 1:]), dtype=torch.int64, device=x.device)
         self.check(lib().ovk_argmax(self.h, _ptr(x), _dtype_code(x), outer, c, inner, _ptr(out)))
+        return out
+
+    # ------------------------------------ the QOperator chain around QLinearConv
+    def qlinear_add(self, a, a_scale, a_zp, b, b_scale, b_zp, c_scale, c_zp):
+        """interp::qlinear_add (interp.rs:4878); a and b are u8 or i8 tensors that broadcast."""
+        import torch
+        shape = torch.broadcast_shapes(a.shape, b.shape)
+        out = torch.empty(shape, dtype=a.dtype, device=a.device)
+        a, b = a.contiguous(), b.contiguous()
+        sa, sb = (_I64 * max(a.dim(), 1))(*a.shape), (_I64 * max(b.dim(), 1))(*b.shape)
+        self.check(lib().ovk_qlinear_add(self.h, _ptr(a), sa, a.dim(), float(a_scale), int(a_zp), _ptr(b), sb, b.dim(),
+                                         float(b_scale), int(b_zp), float(c_scale), int(c_zp),
+                                         int(a.dtype == torch.int8), _ptr(out), None, None))
+        return out
+
+    def maxpool_q(self, x, kernel, strides=None, pads=(0, 0, 0, 0), dilations=(1, 1)):
+        """MaxPool in the quantized domain (shaders/qlinear.rs:145); x is [N, C, H, W] u8 or i8."""
+        import torch
+        n, c, h, w = x.shape
+        strides = strides or (1, 1)
+        arr = lambda v: (_I64 * len(v))(*[int(i) for i in v])
+        dil = arr(dilations)
+        ho = (h + pads[0] + pads[2] - (dilations[0] * (kernel[0] - 1) + 1)) // strides[0] + 1
+        wo = (w + pads[1] + pads[3] - (dilations[1] * (kernel[1] - 1) + 1)) // strides[1] + 1
+        out = torch.empty((n, c, max(ho, 0), max(wo, 0)), dtype=x.dtype, device=x.device)
+        self.check(lib().ovk_maxpool_q(self.h, _ptr(x.contiguous()), int(x.dtype == torch.int8), n, c, h, w, arr(kernel),
+                                       arr(strides), arr(pads), dil, _ptr(out), None, None))
+        return out
+
+    @staticmethod
+    def _qdq_layout(shape, scale, axis):
+        import math
+        if scale.numel() <= 1:
+            return 1, 1
+        axis = axis % len(shape)
+        return max(math.prod(shape[axis + 1:]), 1), scale.numel()
+
+    def quantize_linear(self, x, scale, zero_point=None, axis=1, signed=False):
+        """interp::quantize_linear (interp.rs:5117): saturate(rne(x / scale) + zero_point)."""
+        import torch
+        signed = signed if zero_point is None else zero_point.dtype == torch.int8
+        inner, axis_len = self._qdq_layout(x.shape, scale, axis)
+        out = torch.empty(x.shape, dtype=torch.int8 if signed else torch.uint8, device=x.device)
+        self.check(lib().ovk_quantize_linear(self.h, _ptr(x.contiguous()), x.numel(), inner, axis_len, _ptr(scale),
+                                             _ptr(zero_point), int(signed), _ptr(out)))
+        return out
+
+    def dequantize_linear(self, x, scale, zero_point=None, axis=1):
+        """interp::dequantize_linear (interp.rs:5055): (x - zero_point) * scale, u8 / i8 / i32 input."""
+        import torch
+        inner, axis_len = self._qdq_layout(x.shape, scale, axis)
+        out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        self.check(lib().ovk_dequantize_linear(self.h, _ptr(x.contiguous()), _dtype_code(x), x.numel(), inner, axis_len,
+                                               _ptr(scale), _ptr(zero_point), _ptr(out)))
+        return out
+
+    def qlinear_global_average_pool(self, x, x_scale, x_zp, y_scale, y_zp):
+        """interp::qlinear_global_average_pool (interp.rs:4975); x is [N, C, ...] u8 or i8."""
+        import math
+        import torch
+        n, c = x.shape[0], x.shape[1]
+        out = torch.empty((n, c) + (1,) * (x.dim() - 2), dtype=x.dtype, device=x.device)
+        self.check(lib().ovk_qlinear_global_average_pool(self.h, _ptr(x.contiguous()), int(x.dtype == torch.int8), n, c,
+                                                         math.prod(x.shape[2:]), float(x_scale), int(x_zp),
+                                                         float(y_scale), int(y_zp), _ptr(out)))
         return out
 
 

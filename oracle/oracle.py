@@ -244,3 +244,79 @@ def argmax(x, axis=-1):
     out = np.empty(x.shape[:axis] + x.shape[axis + 1:], dtype=np.int64)
     lib().orc_argmax(_p(x), C.c_int64(outer), C.c_int64(c), C.c_int64(inner), _p(out))
     return out
+
+
+def _codes(a):
+    a = np.ascontiguousarray(a)
+    assert a.dtype in (np.uint8, np.int8), a.dtype
+    return a, int(a.dtype == np.int8)
+
+
+def _i64s(v):
+    return (C.c_int64 * max(len(v), 1))(*[int(i) for i in v])
+
+
+def qlinear_add(a, a_scale, a_zp, b, b_scale, b_zp, c_scale, c_zp):
+    """QLinearAdd with MLAS's rounding and ORT's operand exchange (src/interp.rs:4878-4962)."""
+    a, signed = _codes(a)
+    b, _ = _codes(b)
+    out = np.empty(np.broadcast_shapes(a.shape, b.shape), dtype=a.dtype)
+    rc = lib().orc_qlinear_add(_p(a), _i64s(a.shape), a.ndim, C.c_float(a_scale), C.c_int32(int(a_zp)),
+                               _p(b), _i64s(b.shape), b.ndim, C.c_float(b_scale), C.c_int32(int(b_zp)),
+                               C.c_float(c_scale), C.c_int32(int(c_zp)), signed, _p(out))
+    if rc:
+        raise ValueError("QLinearAdd: shapes do not broadcast")
+    return out
+
+
+def maxpool_q(x, kernel, strides=(1, 1), pads=(0, 0, 0, 0), dilations=(1, 1)):
+    x, signed = _codes(x)
+    n, c, h, w = x.shape
+    ho = (h + pads[0] + pads[2] - (dilations[0] * (kernel[0] - 1) + 1)) // strides[0] + 1
+    wo = (w + pads[1] + pads[3] - (dilations[1] * (kernel[1] - 1) + 1)) // strides[1] + 1
+    out = np.empty((n, c, ho, wo), dtype=x.dtype)
+    lib().orc_maxpool_q(_p(x), signed, C.c_int64(n), C.c_int64(c), C.c_int64(h), C.c_int64(w), _i64s(kernel),
+                        _i64s(strides), _i64s(pads), _i64s(dilations), _p(out))
+    return out
+
+
+def _qdq_layout(shape, scale, axis):
+    if scale.size <= 1:
+        return 1, 1
+    axis = axis % len(shape)
+    return max(int(np.prod(shape[axis + 1:], dtype=np.int64)), 1), scale.size
+
+
+def quantize_linear(x, scale, zero_point=None, axis=1, signed=False):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    scale = np.ascontiguousarray(scale, dtype=np.float32).reshape(-1)
+    if zero_point is not None:
+        zero_point, signed = _codes(np.asarray(zero_point).reshape(-1))
+    inner, axis_len = _qdq_layout(x.shape, scale, axis)
+    out = np.empty(x.shape, dtype=np.int8 if signed else np.uint8)
+    lib().orc_quantize_linear(_p(x), C.c_int64(x.size), C.c_int64(inner), C.c_int64(axis_len), _p(scale),
+                              _p(zero_point), int(signed), _p(out))
+    return out
+
+
+def dequantize_linear(x, scale, zero_point=None, axis=1):
+    x = np.ascontiguousarray(x)
+    kind = {np.dtype(np.uint8): 0, np.dtype(np.int8): 1, np.dtype(np.int32): 2}[x.dtype]
+    scale = np.ascontiguousarray(scale, dtype=np.float32).reshape(-1)
+    if zero_point is not None:
+        zero_point = np.ascontiguousarray(np.asarray(zero_point, dtype=x.dtype).reshape(-1))
+    inner, axis_len = _qdq_layout(x.shape, scale, axis)
+    out = np.empty(x.shape, dtype=np.float32)
+    lib().orc_dequantize_linear(_p(x), kind, C.c_int64(x.size), C.c_int64(inner), C.c_int64(axis_len), _p(scale),
+                                _p(zero_point), _p(out))
+    return out
+
+
+def qlinear_global_average_pool(x, x_scale, x_zp, y_scale, y_zp):
+    x, signed = _codes(x)
+    n, c = x.shape[:2]
+    hw = int(np.prod(x.shape[2:], dtype=np.int64))
+    out = np.empty((n, c) + (1,) * (x.ndim - 2), dtype=x.dtype)
+    lib().orc_qlinear_global_average_pool(_p(x), signed, C.c_int64(n * c), C.c_int64(hw), C.c_float(x_scale),
+                                          C.c_int32(int(x_zp)), C.c_float(y_scale), C.c_int32(int(y_zp)), _p(out))
+    return out

@@ -596,3 +596,164 @@ ORC_EXPORT void orc_argmax(const float *x, int64_t outer, int64_t c, int64_t inn
         out[r] = at;
     }
 }
+
+/* ------------------------------------------------------------------------
+ * QLinearAdd, MLAS's kernel operation for operation (shaders/qlinear.rs:69-143,
+ * src/interp.rs:4878-4962, tests/qlinear.rs:317-322):
+ *   ra = A_scale / C_scale, rb = B_scale / C_scale,
+ *   fixed = c_zp - fma(ra, a_zp, rb * b_zp),
+ *   C = saturate(rne(fma(A, ra, fma(B, rb, fixed)))),
+ * the operands exchanged when A is constant along the innermost broadcast span
+ * (or the output is one element).  Shapes broadcast numpy-style, rank <= 8.
+ * out must hold the broadcast element count.  Returns 0, 1 on a shape error.
+ */
+ORC_EXPORT int orc_qlinear_add(const uint8_t *a, const int64_t *a_shape, int a_rank, float a_scale, int32_t a_zp,
+                               const uint8_t *b, const int64_t *b_shape, int b_rank, float b_scale, int32_t b_zp,
+                               float c_scale, int32_t c_zp, int is_signed, uint8_t *out)
+{
+    int rank = a_rank > b_rank ? a_rank : b_rank;
+    int64_t shape[8], sa[8], sb[8], run_a = 1, run_b = 1, n = 1;
+    if (rank > 8)
+        return 1;
+    for (int d = rank - 1; d >= 0; d--) {
+        int da = d - (rank - a_rank), db = d - (rank - b_rank);
+        int64_t ea = da >= 0 ? a_shape[da] : 1, eb = db >= 0 ? b_shape[db] : 1;
+        if (ea != eb && ea != 1 && eb != 1)
+            return 1;
+        shape[d] = ea == 1 ? eb : ea;
+        sa[d] = ea == 1 ? 0 : run_a;
+        sb[d] = eb == 1 ? 0 : run_b;
+        run_a *= ea;
+        run_b *= eb;
+        n *= shape[d];
+    }
+    float ra = a_scale / c_scale, rb = b_scale / c_scale;
+    int inner = -1;
+    for (int d = rank - 1; d >= 0; d--)
+        if (shape[d] > 1) {
+            inner = d;
+            break;
+        }
+    if (inner < 0 || sa[inner] == 0) {
+        const uint8_t *tp = a; a = b; b = tp;
+        for (int d = 0; d < rank; d++) { int64_t t = sa[d]; sa[d] = sb[d]; sb[d] = t; }
+        float tf = ra; ra = rb; rb = tf;
+        int32_t tz = a_zp; a_zp = b_zp; b_zp = tz;
+    }
+    volatile float rbz = rb * (float)b_zp;
+    float fixed = (float)c_zp - fmaf(ra, (float)a_zp, rbz);
+    for (int64_t i = 0; i < n; i++) {
+        int64_t rem = i, oa = 0, ob = 0, run = n;
+        for (int d = 0; d < rank; d++) {
+            run /= shape[d];
+            int64_t c = rem / run;
+            rem -= c * run;
+            oa += c * sa[d];
+            ob += c * sb[d];
+        }
+        int32_t av = is_signed ? (int8_t)a[oa] : a[oa], bv = is_signed ? (int8_t)b[ob] : b[ob];
+        float y = nearbyintf(fmaf((float)av, ra, fmaf((float)bv, rb, fixed)));
+        float lo = is_signed ? -128.0f : 0.0f, hi = is_signed ? 127.0f : 255.0f;
+        y = y < lo ? lo : (y > hi ? hi : y);
+        out[i] = (uint8_t)(int32_t)y;
+    }
+    return 0;
+}
+
+/* MaxPool on quantized codes (shaders/qlinear.rs:160-211): floor mode, padding taps skipped. */
+ORC_EXPORT void orc_maxpool_q(const uint8_t *x, int is_signed, int64_t n, int64_t c, int64_t h, int64_t w,
+                              const int64_t *kernel, const int64_t *strides, const int64_t *pads,
+                              const int64_t *dilations, uint8_t *out)
+{
+    int64_t ho = (h + pads[0] + pads[2] - (dilations[0] * (kernel[0] - 1) + 1)) / strides[0] + 1;
+    int64_t wo = (w + pads[1] + pads[3] - (dilations[1] * (kernel[1] - 1) + 1)) / strides[1] + 1;
+    for (int64_t p = 0; p < n * c; p++)
+        for (int64_t oh = 0; oh < ho; oh++)
+            for (int64_t ow = 0; ow < wo; ow++) {
+                int32_t acc = INT32_MIN;
+                for (int64_t r = 0; r < kernel[0]; r++) {
+                    int64_t ih = oh * strides[0] - pads[0] + r * dilations[0];
+                    if (ih < 0 || ih >= h)
+                        continue;
+                    for (int64_t s = 0; s < kernel[1]; s++) {
+                        int64_t iw = ow * strides[1] - pads[1] + s * dilations[1];
+                        if (iw < 0 || iw >= w)
+                            continue;
+                        int32_t v = (int32_t)byte_val(x, (size_t)((p * h + ih) * w + iw), is_signed);
+                        if (v > acc)
+                            acc = v;
+                    }
+                }
+                out[(p * ho + oh) * wo + ow] = (uint8_t)((uint32_t)acc & 0xffu);
+            }
+}
+
+static inline int32_t sat_i32(float r)
+{
+    if (r != r)
+        return 0;
+    if (r >= 2147483648.0f)
+        return INT32_MAX;
+    if (r <= -2147483648.0f)
+        return INT32_MIN;
+    return (int32_t)r;
+}
+
+/* QuantizeLinear: saturate(rne(x / scale) + zero_point), channel (i / inner) % axis_len
+ * (shaders/quantize_linear.rs:72-121).  zp may be NULL. */
+ORC_EXPORT void orc_quantize_linear(const float *x, int64_t n, int64_t inner, int64_t axis_len, const float *scale,
+                                    const uint8_t *zp, int is_signed, uint8_t *out)
+{
+    for (int64_t i = 0; i < n; i++) {
+        int64_t c = (i / inner) % axis_len;
+        int32_t zero = zp ? (int32_t)byte_val(zp, (size_t)c, is_signed) : 0;
+        volatile float quot = x[i] / scale[c];
+        int32_t q = (int32_t)((uint32_t)sat_i32(nearbyintf(quot)) + (uint32_t)zero);
+        int32_t lo = is_signed ? -128 : 0, hi = is_signed ? 127 : 255;
+        q = q < lo ? lo : (q > hi ? hi : q);
+        out[i] = (uint8_t)((uint32_t)q & 0xffu);
+    }
+}
+
+/* DequantizeLinear: (x - zero_point) * scale; kind 0 u8, 1 i8, 2 i32 (quantize_linear.rs:16-70). */
+ORC_EXPORT void orc_dequantize_linear(const void *x, int kind, int64_t n, int64_t inner, int64_t axis_len,
+                                      const float *scale, const void *zp, float *out)
+{
+    for (int64_t i = 0; i < n; i++) {
+        int64_t c = (i / inner) % axis_len;
+        int32_t q, zero = 0;
+        if (kind == 2) {
+            q = ((const int32_t *)x)[i];
+            if (zp)
+                zero = ((const int32_t *)zp)[c];
+        } else {
+            q = (int32_t)byte_val((const uint8_t *)x, (size_t)i, kind);
+            if (zp)
+                zero = (int32_t)byte_val((const uint8_t *)zp, (size_t)c, kind);
+        }
+        volatile float d = (float)(int32_t)((uint32_t)q - (uint32_t)zero);
+        out[i] = d * scale[c];
+    }
+}
+
+/* QLinearGlobalAveragePool = DequantizeLinear, GlobalAveragePool (a sequential f32 sum in
+ * row-major order divided by the count, shaders/pooling.rs:38-54), QuantizeLinear
+ * (src/interp.rs:4975-5000, tests/qlinear.rs:419-452). */
+ORC_EXPORT void orc_qlinear_global_average_pool(const uint8_t *x, int is_signed, int64_t planes, int64_t hw,
+                                                float x_scale, int32_t x_zp, float y_scale, int32_t y_zp,
+                                                uint8_t *out)
+{
+    for (int64_t p = 0; p < planes; p++) {
+        volatile float acc = 0.0f;
+        for (int64_t i = 0; i < hw; i++) {
+            volatile float v = (float)((int32_t)byte_val(x, (size_t)(p * hw + i), is_signed) - x_zp) * x_scale;
+            acc = acc + v;
+        }
+        volatile float mean = acc / (float)(uint32_t)(hw > 0 ? hw : 1);
+        volatile float quot = mean / y_scale;
+        int32_t q = (int32_t)((uint32_t)sat_i32(nearbyintf(quot)) + (uint32_t)y_zp);
+        int32_t lo = is_signed ? -128 : 0, hi = is_signed ? 127 : 255;
+        q = q < lo ? lo : (q > hi ? hi : q);
+        out[p] = (uint8_t)((uint32_t)q & 0xffu);
+    }
+}

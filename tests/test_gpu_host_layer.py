@@ -257,3 +257,45 @@ def test_argmax_node(hl, env, shape, axis, keepdims):
     assert got.dtype == np.int64
     assert np.array_equal(got, np.expand_dims(want, axis % x.ndim) if keepdims else want)
     assert not hl.Node("ArgMax", ["x"], ["out"], axis=axis, select_last_index=1).implemented
+
+
+def test_quantized_residual_tail_as_nodes(hl, env):
+    """QLinearAdd -> MaxPool -> QLinearGlobalAveragePool -> DequantizeLinear -> QuantizeLinear, driven as the
+    reference's tests drive them (crates/onnx-vulkan-core/tests/qlinear.rs:279-452): bytes equal to the port."""
+    rng = cases.rng_for(26, 0)
+    a = rng.integers(0, 256, size=(2, 16, 8, 8)).astype(np.uint8)
+    b = rng.integers(0, 256, size=(1, 16, 1, 1)).astype(np.uint8)
+    env.set("A", a)
+    env.set("B", b, initializer=True)
+    for name, value, dt in (("A_scale", 0.02, np.float32), ("A_zp", 128, np.uint8), ("B_scale", 0.05, np.float32),
+                            ("B_zp", 100, np.uint8), ("C_scale", 0.03, np.float32), ("C_zp", 30, np.uint8),
+                            ("y_scale", 0.07, np.float32), ("y_zp", 3, np.uint8)):
+        env.set(name, np.array(value, dtype=dt), initializer=True)
+    add = hl.Node("QLinearAdd", ["A", "A_scale", "A_zp", "B", "B_scale", "B_zp", "C_scale", "C_zp"], ["sum"],
+                  domain="com.microsoft")
+    assert add.implemented and env.unsupported_quantization(add) is None
+    env.execute(add)
+    want_sum = orc.qlinear_add(a, 0.02, 128, b, 0.05, 100, 0.03, 30)
+    assert np.array_equal(env.host("sum"), want_sum)
+    env.execute(hl.Node("MaxPool", ["sum"], ["pooled"], kernel_shape=[3, 3], strides=[2, 2], pads=[1, 1, 1, 1]))
+    want_pool = orc.maxpool_q(want_sum, (3, 3), (2, 2), (1, 1, 1, 1))
+    assert np.array_equal(env.host("pooled"), want_pool)
+    env.execute(hl.Node("QLinearGlobalAveragePool", ["pooled", "C_scale", "C_zp", "y_scale", "y_zp"], ["gap"],
+                        domain="com.microsoft"))
+    want_gap = orc.qlinear_global_average_pool(want_pool, 0.03, 30, 0.07, 3)
+    got_gap = env.host("gap")
+    assert got_gap.shape == (2, 16, 1, 1) and np.array_equal(got_gap, want_gap)
+    env.execute(hl.Node("DequantizeLinear", ["gap", "y_scale", "y_zp"], ["real"]))
+    want_real = orc.dequantize_linear(want_gap, np.array([0.07], dtype=np.float32), np.array([3], dtype=np.uint8))
+    assert np.array_equal(env.host("real"), want_real)
+    env.execute(hl.Node("QuantizeLinear", ["real", "C_scale", "C_zp"], ["again"]))
+    assert np.array_equal(env.host("again"), orc.quantize_linear(want_real, np.array([0.03], dtype=np.float32),
+                                                                 np.array([30], dtype=np.uint8)))
+    # a scale that is not a constant is refused with the reference's wording (interp.rs:781-812)
+    env.set("A_scale", np.array(0.02, dtype=np.float32), initializer=False)
+    assert env.unsupported_quantization(add) == "QLinearAdd: A scale or zero point is not a constant"
+    # float pooling is not this layer's
+    env.set("f", np.zeros((1, 1, 4, 4), dtype=np.float32))
+    with pytest.raises(hl.OvkError) as err:
+        env.execute(hl.Node("MaxPool", ["f"], ["g"], kernel_shape=[2, 2]))
+    assert err.value.status == 2

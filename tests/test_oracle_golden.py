@@ -367,3 +367,90 @@ def test_argmax_first_occurrence_and_candidates():
     assert np.array_equal(orc.argmax(x, 1), np.argmax(x, axis=1))
     odd = np.array([[np.nan, -np.inf, -3.0], [-np.inf, -np.inf, np.nan]], dtype=np.float32)
     assert orc.argmax(odd, 1).tolist() == [2, 0]
+
+
+# ------------------------------------------ the QOperator chain around QLinearConv
+
+def mlas_add(a, b, scales, zps):
+    """tests/qlinear.rs:317-322, in float32 with explicit fused multiply-adds (via float64, which
+    holds the exact product of two float32 values and rounds the sum once)."""
+    sa, sb, sc = (np.float32(v) for v in scales)
+    za, zb, zc = zps
+    ra, rb = np.float32(sa / sc), np.float32(sb / sc)
+    fma = lambda x, y, z: np.float32(np.float64(x) * np.float64(y) + np.float64(z))
+    fixed = np.float32(np.float32(zc) - fma(ra, np.float32(za), np.float32(rb * np.float32(zb))))
+    y = fma(np.float32(a), ra, fma(np.float32(b), rb, fixed))
+    return int(np.clip(np.rint(y), 0, 255))
+
+
+def test_qlinear_add_broadcast_literal():
+    """tests/qlinear.rs:279-314."""
+    a = np.array([[200, 10, 50], [128, 255, 0]], dtype=np.uint8)
+    b = np.array([100, 130, 20], dtype=np.uint8)
+    got = orc.qlinear_add(a, 0.02, 128, b, 0.05, 100, 0.03, 30)
+    want = [mlas_add(int(a.reshape(-1)[i]), int(b[i % 3]), (0.02, 0.05, 0.03), (128, 100, 30)) for i in range(6)]
+    assert got.reshape(-1).tolist() == want
+
+
+def test_qlinear_add_rounds_like_the_cpu_reference_on_every_input_pair():
+    """tests/qlinear.rs:356-373: the three pairs ORT maps to 82, 148, 214."""
+    scales, zps = (0.03207505, 0.061237868, 0.067996934), (116, 145, 125)
+    a = (np.arange(65536) % 256).astype(np.uint8)
+    b = (np.arange(65536) // 256).astype(np.uint8)
+    got = orc.qlinear_add(a, scales[0], zps[0], b, scales[1], zps[1], scales[2], zps[2])
+    for av, bv, cpu in [(129, 91, 82), (162, 147, 148), (195, 203, 214)]:
+        assert got[bv * 256 + av] == cpu
+    idx = np.arange(0, 65536, 97)
+    assert got[idx].tolist() == [mlas_add(int(a[i]), int(b[i]), scales, zps) for i in idx]
+
+
+def test_qlinear_add_exchanges_a_broadcast_first_operand():
+    """tests/qlinear.rs:376-392: at B = 195 the unexchanged formula gives 41, ORT 40."""
+    scales, zps = (0.264079, 0.081802, 0.010314), (128, 205, 43)
+    b = np.arange(256, dtype=np.uint8)
+    got = orc.qlinear_add(np.array([131], dtype=np.uint8), scales[0], zps[0], b, scales[1], zps[1], scales[2], zps[2])
+    assert got[195] == 40
+    sa, sb, sc = scales
+    za, zb, zc = zps
+    assert got.tolist() == [mlas_add(v, 131, (sb, sa, sc), (zb, za, zc)) for v in range(256)]
+
+
+def test_maxpool_q_literal():
+    """tests/qlinear.rs:395-416."""
+    x = np.array([10, 200, 30, 40, 50, 60, 250, 80, 90, 100, 110, 120, 130, 140, 150, 160], dtype=np.uint8)
+    got = orc.maxpool_q(x.reshape(1, 1, 4, 4), (2, 2), strides=(2, 2))
+    assert got.reshape(-1).tolist() == [200, 250, 140, 160]
+
+
+def test_qlinear_global_average_pool_literal():
+    """tests/qlinear.rs:419-452."""
+    x = np.array([10, 20, 30, 40, 200, 210, 220, 230], dtype=np.uint8).reshape(1, 2, 2, 2)
+    got = orc.qlinear_global_average_pool(x, 0.02, 15, 0.05, 7)
+    want = []
+    for plane in x.reshape(2, 4):
+        acc = np.float32(0)
+        for v in plane:
+            acc = np.float32(acc + np.float32(np.float32(int(v) - 15) * np.float32(0.02)))
+        mean = np.float32(acc / np.float32(4.0))
+        want.append(int(np.clip(int(np.rint(np.float32(mean / np.float32(0.05)))) + 7, 0, 255)))
+    assert got.reshape(-1).tolist() == want
+
+
+def test_quantize_dequantize_linear_per_tensor_and_per_axis():
+    """shaders/quantize_linear.rs: ties to even, saturation, per-axis channel = (i / inner) % axis_len."""
+    x = np.array([-13.5, -12.5, 0.49, 0.5, 1.5, 2.5, 300.0, -300.0], dtype=np.float32)
+    q = orc.quantize_linear(x, np.array([1.0], dtype=np.float32), np.array([10], dtype=np.uint8))
+    assert q.tolist() == [0, 0, 10, 10, 12, 12, 255, 0]
+    qs = orc.quantize_linear(x, np.array([1.0], dtype=np.float32), np.array([-3], dtype=np.int8))
+    assert qs.tolist() == [-17, -15, -3, -3, -1, -1, 127, -128]
+    xa = np.arange(24, dtype=np.float32).reshape(2, 3, 4) - 11.0
+    scale = np.array([0.5, 1.0, 2.0], dtype=np.float32)
+    zp = np.array([1, 2, 3], dtype=np.uint8)
+    qa = orc.quantize_linear(xa, scale, zp, axis=1)
+    want = np.clip(np.rint(xa / scale[None, :, None]) + zp[None, :, None], 0, 255).astype(np.uint8)
+    assert np.array_equal(qa, want)
+    back = orc.dequantize_linear(qa, scale, zp, axis=1)
+    assert np.array_equal(back, (qa.astype(np.float32) - zp[None, :, None].astype(np.float32)) * scale[None, :, None])
+    bias = np.array([-70000, 5, 123456], dtype=np.int32)
+    assert np.array_equal(orc.dequantize_linear(bias, np.array([0.25], dtype=np.float32)),
+                          bias.astype(np.float32) * np.float32(0.25))
