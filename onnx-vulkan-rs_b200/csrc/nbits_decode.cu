@@ -313,6 +313,36 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
         return;
     }
 
+    // ---- everything a consumer needs that does not depend on the activations is computed here, while
+    // the kernel that produces them may still be running
+    const int g = lane >> 2, t = lane & 3;
+    // P is a power of two up to the warp count: shifts and masks, no divisions
+    const int p_shift = 31 - __clz(p.P);
+    const int wp = CONSUMER_WARPS >> p_shift;  // warps sharing one panel
+    const int wp_shift = 31 - __clz(wp);
+    const int panel = warp & (p.P - 1);
+    // each warp owns a contiguous run of the chunk's blocks
+    const int per_warp = (p.KC + wp - 1) >> wp_shift;
+    const int b_first = min((warp >> p_shift) * per_warp, p.KC);
+    const int my_blocks = min(per_warp, p.KC - b_first);
+    const int act_row = min(g, p.rows - 1);
+    // 32-bit shared-window addresses; every load below is an explicit ld.shared
+    const uint32_t stage0 = umma::smem_u32(stage_base);
+    const uint32_t act0 = umma::smem_u32(acts) + uint32_t((act_row * p.g_pad) * 4 + t) * 16u;
+    constexpr uint32_t SCALE_PAIR = SCALE_F32 ? 8u : 4u;
+    constexpr uint32_t W_STEP = GBT * 256u, S_STEP = 8u * SCALE_PAIR, Z_STEP = 8u, A_STEP = GBT * 64u;
+    const uint32_t w_rel = uint32_t((panel * p.KC + b_first) * GBT * 32 + lane) * 8u;
+    const uint32_t s_rel = p.s_off + uint32_t((panel * p.KC + b_first) * 8 + g) * SCALE_PAIR;
+    const uint32_t z_rel = p.z_off + uint32_t((panel * p.KC + b_first) * 8 + g);
+    UnpackConsts uc;
+    // opaque to the optimiser, so the constants stay in registers
+    asm volatile("mov.u32 %0, 0x003C003C;\n\tmov.u32 %1, 0x5C005C00;\n\tmov.u32 %2, 0x03C003C0;\n\t"
+                 "mov.u32 %3, 0x4C004C00;\n\tmov.u32 %4, 0x00F000F0;\n\tmov.u32 %5, 0x54005400;"
+                 : "=r"(uc.mask_e), "=r"(uc.magic_e), "=r"(uc.mask_o), "=r"(uc.magic_o), "=r"(uc.mask_z),
+                   "=r"(uc.magic_z));
+    const uint32_t corr0 = umma::smem_u32(corr) + uint32_t((act_row * (p.g_pad / GBT)) * 4 + t) * 4u;
+    constexpr uint32_t C_STEP = 16u;
+    constexpr int BIG = GBT == 1 ? 9 : (GBT == 2 ? 4 : 2);
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the producers of A have finished
     // ---- activations -> shared memory in the order the fragments are read, one
     // thread per 32-wide k group (unit t of a group: k = 32*group + 8*t + {0,4,1,5,2,6,3,7}),
@@ -347,28 +377,31 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
         for (int base = warp * 32; base < total_groups; base += CONSUMER_WARPS * 32) {
             const int idx = base + lane;
             const bool valid = idx < total_groups;
-            const int grp = valid ? idx % p.g_pad : 0, m = valid ? idx / p.g_pad : 0;
+            const int m = (valid && p.M > 1) ? idx / p.g_pad : 0;
+            const int grp = valid ? idx - m * p.g_pad : 0;
             GroupSums sh, sl;
             if (valid) {
                 const float inv = 1.0f / row_pow2[m];  // exact power of two
                 const float *src = a + int64_t(m) * p.K + grp * 32;
                 const bool whole = p.vec_a && grp * 32 + 32 <= p.K;
+                float raw[32];  // fetched before anything is stored (see the fp16 path)
+                if (whole) {
+#pragma unroll
+                    for (int t = 0; t < 8; t++) {
+                        const float4 f = __ldcg(reinterpret_cast<const float4 *>(src) + t);
+                        raw[4 * t] = f.x, raw[4 * t + 1] = f.y, raw[4 * t + 2] = f.z, raw[4 * t + 3] = f.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        raw[i] = grp * 32 + i < p.K ? src[i] : 0.0f;
+                }
 #pragma unroll
                 for (int t = 0; t < 4; t++) {
-                    float v[8], hi[8], lo[8];
-                    if (whole) {
-                        const float4 q0 = reinterpret_cast<const float4 *>(src)[2 * t];
-                        const float4 q1 = reinterpret_cast<const float4 *>(src)[2 * t + 1];
-                        v[0] = q0.x, v[1] = q0.y, v[2] = q0.z, v[3] = q0.w;
-                        v[4] = q1.x, v[5] = q1.y, v[6] = q1.z, v[7] = q1.w;
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 8; i++)
-                            v[i] = grp * 32 + t * 8 + i < p.K ? src[t * 8 + i] : 0.0f;
-                    }
+                    float hi[8], lo[8];
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
-                        const float x = v[i] * inv;
+                        const float x = raw[8 * t + i] * inv;
                         hi[i] = __half2float(__float2half_rn(x));
                         lo[i] = __half2float(__float2half_rn(x - hi[i]));
                     }
@@ -385,27 +418,42 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
         for (int base = warp * 32; base < total_groups; base += CONSUMER_WARPS * 32) {
             const int idx = base + lane;
             const bool valid = idx < total_groups;
-            const int grp = valid ? idx % p.g_pad : 0, m = valid ? idx / p.g_pad : 0;
+            const int m = (valid && p.M > 1) ? idx / p.g_pad : 0;
+            const int grp = valid ? idx - m * p.g_pad : 0;
             GroupSums sg;
             if (valid) {
                 const __half *src = a + int64_t(m) * p.K + grp * 32;
                 const bool whole = p.vec_a && grp * 32 + 32 <= p.K;
+                // all four loads are issued before anything is stored: stores to shared memory in
+                // between would serialise them into four round trips to the L2
+                uint4 q[4];
+                if (whole) {
+#pragma unroll
+                    for (int t = 0; t < 4; t++)
+                        q[t] = __ldcg(reinterpret_cast<const uint4 *>(src) + t);
+                } else {
+#pragma unroll
+                    for (int t = 0; t < 4; t++) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int k = grp * 32 + t * 8 + 2 * i;
+                            const uint32_t lo = k < p.K ? uint32_t(__half_as_ushort(src[t * 8 + 2 * i])) : 0u;
+                            const uint32_t hi = k + 1 < p.K ? uint32_t(__half_as_ushort(src[t * 8 + 2 * i + 1])) : 0u;
+                            w[i] = lo | (hi << 16);
+                        }
+                        q[t] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
 #pragma unroll
                 for (int t = 0; t < 4; t++) {
                     float v[8];
-                    if (whole) {
-                        const uint4 q = reinterpret_cast<const uint4 *>(src)[t];
-                        const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+                    const uint32_t qw[4] = {q[t].x, q[t].y, q[t].z, q[t].w};
 #pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&qw[i]));
-                            v[2 * i] = f.x;
-                            v[2 * i + 1] = f.y;
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 8; i++)
-                            v[i] = grp * 32 + t * 8 + i < p.K ? __half2float(src[t * 8 + i]) : 0.0f;
+                    for (int i = 0; i < 4; i++) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&qw[i]));
+                        v[2 * i] = f.x;
+                        v[2 * i + 1] = f.y;
                     }
                     stage_unit(&acts[(size_t(m) * p.g_pad + grp) * 4 + t], v, sg);
                 }
@@ -416,31 +464,6 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
     asm volatile("bar.sync 2, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
 
     // ---------------------------------------------------------------- consumers
-    const int g = lane >> 2, t = lane & 3;
-    const int wp = CONSUMER_WARPS / p.P;  // warps sharing one panel
-    const int panel = warp % p.P;
-    // each warp owns a contiguous run of the chunk's blocks
-    const int per_warp = (p.KC + wp - 1) / wp;
-    const int b_first = min((warp / p.P) * per_warp, p.KC);
-    const int my_blocks = min(per_warp, p.KC - b_first);
-    const int act_row = min(g, p.rows - 1);
-    // 32-bit shared-window addresses; every load below is an explicit ld.shared
-    const uint32_t stage0 = umma::smem_u32(stage_base);
-    const uint32_t act0 = umma::smem_u32(acts) + uint32_t((act_row * p.g_pad) * 4 + t) * 16u;
-    constexpr uint32_t SCALE_PAIR = SCALE_F32 ? 8u : 4u;
-    constexpr uint32_t W_STEP = GBT * 256u, S_STEP = 8u * SCALE_PAIR, Z_STEP = 8u, A_STEP = GBT * 64u;
-    const uint32_t w_rel = uint32_t((panel * p.KC + b_first) * GBT * 32 + lane) * 8u;
-    const uint32_t s_rel = p.s_off + uint32_t((panel * p.KC + b_first) * 8 + g) * SCALE_PAIR;
-    const uint32_t z_rel = p.z_off + uint32_t((panel * p.KC + b_first) * 8 + g);
-    UnpackConsts uc;
-    // opaque to the optimiser, so the constants stay in registers
-    asm volatile("mov.u32 %0, 0x003C003C;\n\tmov.u32 %1, 0x5C005C00;\n\tmov.u32 %2, 0x03C003C0;\n\t"
-                 "mov.u32 %3, 0x4C004C00;\n\tmov.u32 %4, 0x00F000F0;\n\tmov.u32 %5, 0x54005400;"
-                 : "=r"(uc.mask_e), "=r"(uc.magic_e), "=r"(uc.mask_o), "=r"(uc.magic_o), "=r"(uc.mask_z),
-                   "=r"(uc.magic_z));
-    const uint32_t corr0 = umma::smem_u32(corr) + uint32_t((act_row * (p.g_pad / GBT)) * 4 + t) * 4u;
-    constexpr uint32_t C_STEP = 16u;
-    constexpr int BIG = GBT == 1 ? 9 : (GBT == 2 ? 4 : 2);
     bool dead = false;
     int s = 0;
     uint32_t ph = 0;
