@@ -319,7 +319,7 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
     # branches (side streams that fork from and join the main one: in the
     # captured graph these are just edges); o waits for q/k/v, down for gate/up.
     side = []
-    if not args.serial:
+    if args.launch == "branches":
         for _ in range(2):
             s_side = torch.cuda.Stream()
             with torch.cuda.stream(s_side):
@@ -328,7 +328,24 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
     FORK_BEFORE = {"q": (0, 1), "gate": (0,)}
     JOIN_BEFORE = {"o": (0, 1), "down": (0,)}
 
+    GROUPS = {"q": ("q", "k", "v"), "gate": ("gate", "up")}   # members that read the same activations
+    by_label = {label: (k, n, w) for label, k, n, w in ops}
+
+    def layers_grouped():
+        """q|k|v and gate|up as one launch each: one serial chain of four dependent launches per layer,
+        every launch overlapping its predecessor's tail (programmatic dependent launch)."""
+        for label, k, n, w in ops:
+            layer, name = label.split(".", 1)
+            if name in GROUPS:
+                members = GROUPS[name]
+                ctx.matmul_nbits_group([by_label[f"{layer}.{mname}"][2] for mname in members], acts[k],
+                                       outs=[outs[mname] for mname in members])
+            elif not any(name in g[1:] for g in GROUPS.values()):
+                ctx.matmul_nbits(w, acts[k], out=outs[name])
+
     def layers_eager():
+        if args.launch == "grouped":
+            return layers_grouped()
         for label, k, n, w in ops:
             name = label.split(".", 1)[1]
             if side:
@@ -364,8 +381,9 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
                 g0.record(stream)
                 ctx.matmul_nbits(lm, acts[HIDDEN], out=outs[VOCAB])
                 g1.record(stream)
-            replay = "one CUDA graph replay per step (%s)" % (
-                "q|k|v and gate|up on parallel branches" if side else "one serial chain")
+            replay = "one CUDA graph replay per step (%s)" % {
+                "grouped": "q|k|v and gate|up as one launch each", "branches": "q|k|v and gate|up on parallel branches",
+                "serial": "one launch per GEMV in one chain"}[args.launch]
         except Exception as e:  # capture refused: fall back to eager launches, say so
             graph, replay = None, "eager launches (graph capture failed: %s)" % str(e)[:80]
             torch.cuda.synchronize()
@@ -424,7 +442,8 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
     clocks = sampler.stop(skip) if rank == 0 else None
     if clocks is not None:
         clocks["window"] = "the timed steps and 0.4 s of the same steps after them"
-    launches = n_gemv * args.steps  # one kernel of this library per GEMV (graph replays launch them too)
+    per_step = n_gemv if args.launch != "grouped" else n_gemv - 3 * args.layers  # q|k|v and gate|up share a launch
+    launches = per_step * args.steps  # kernels of this library (graph replays launch them too)
     ms = torch.tensor([t0.elapsed_time(t1)], device="cuda")
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -672,7 +691,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the prefill / int8 / conv lines")
     ap.add_argument("--no-graph", action="store_true", help="launch the per-layer GEMVs eagerly")
-    ap.add_argument("--serial", action="store_true", help="one serial chain of GEMVs instead of parallel q|k|v and gate|up")
+    ap.add_argument("--launch", default="grouped", choices=["grouped", "branches", "serial"],
+                    help="how the independent GEMVs of a layer (q|k|v, gate|up) are launched: one launch per group, "
+                         "parallel graph branches, or one launch per GEMV in a single chain")
     ap.add_argument("--one", default=None, choices=["lm_head", "prefill", "prefill32", "int8", "int8big", "conv"],
                     help="run one operator three times and exit (small target for an ncu capture)")
     args = ap.parse_args()

@@ -117,6 +117,18 @@ OVK_API void ovk_nbits_weight_destroy(ovk_ctx *ctx, ovk_nbits_weight *w);
 OVK_API int32_t ovk_matmul_nbits(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
                                  int32_t a_dtype, int64_t m, void *y, int32_t y_dtype);
 
+/* The same product for up to four weights that read the SAME activations (the
+ * q, k and v projections of a decoder layer, gate and up): Y_j = A x dequant(B_j).
+ * Results are those of one ovk_matmul_nbits call per weight.  When the decode
+ * kernel applies (M <= 8) and the weights share K, block size and tile shape,
+ * all of them run in ONE launch, which in a decode step saves a dependent
+ * launch per extra weight; otherwise the calls are made one by one.  This entry
+ * point has no counterpart in the reference, whose interpreter dispatches
+ * MatMulNBits nodes one at a time (interp.rs:1071). */
+OVK_API int32_t ovk_matmul_nbits_group(ovk_ctx *ctx, int32_t count,
+                                       const ovk_nbits_weight *const *weights, const void *a,
+                                       int32_t a_dtype, int64_t m, void *const *ys, int32_t y_dtype);
+
 /* ------------------------------------------------- DynamicQuantizeLinear
  * interp::dynamic_quantize / quantize_on_device (interp.rs:1945-2085) with the
  * PARTIAL and QUANTIZE passes of shaders/dynamic_quantize.rs:106-222.  x, y,

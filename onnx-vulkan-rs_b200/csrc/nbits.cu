@@ -11,6 +11,9 @@ bool ovk_nbits_decode_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int
                               int32_t y_dtype);
 int32_t ovk_nbits_decode(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype,
                          int64_t m, void *y, int32_t y_dtype);
+bool ovk_nbits_decode_group_compatible(const ovk_nbits_weight *a, const ovk_nbits_weight *b);
+int32_t ovk_nbits_decode_group(ovk_ctx *ctx, int count, const ovk_nbits_weight *const *ws, const void *a, int32_t a_dtype,
+                               int64_t m, void *const *ys, int32_t y_dtype);
 bool ovk_nbits_gemm_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int64_t m, int32_t a_dtype,
                             int32_t y_dtype, const void *a, const void *y);
 int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype,
@@ -92,6 +95,36 @@ int32_t ovk_matmul_nbits(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
     if (ovk_nbits_gemm_applies(ctx, w, m, a_dtype, y_dtype, a, y))
         return ovk_nbits_gemm(ctx, w, a, a_dtype, m, y, y_dtype);
     return ovk_nbits_rows(ctx, w, a, a_dtype, m, y, y_dtype);
+}
+
+// Several weights over the same activations in one launch where the decode kernel applies and the
+// weights have the same tile shape; otherwise one call per weight.
+int32_t ovk_matmul_nbits_group(ovk_ctx *ctx, int32_t count, const ovk_nbits_weight *const *weights, const void *a,
+                               int32_t a_dtype, int64_t m, void *const *ys, int32_t y_dtype)
+{
+    if (!ctx || !weights || !ys)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "ovk_matmul_nbits_group: null argument");
+    OVK_REQUIRE(ctx, count >= 1 && count <= 4, "MatMulNBits: a group of %d weights (1 to 4)", count);
+    for (int j = 0; j < count; j++)
+        OVK_REQUIRE(ctx, weights[j] && (ys[j] || m == 0), "MatMulNBits: member %d of the group is null", j);
+    for (int j = 1; j < count; j++)
+        OVK_REQUIRE(ctx, weights[j]->k == weights[0]->k, "MatMulNBits: member %d of the group has K=%lld, member 0 K=%lld", j,
+                    (long long)weights[j]->k, (long long)weights[0]->k);
+    bool together = count > 1 && m >= 1 && m <= 8 && a &&
+                    (a_dtype == OVK_FLOAT || a_dtype == OVK_FLOAT16) && (y_dtype == OVK_FLOAT || y_dtype == OVK_FLOAT16);
+    for (int j = 0; together && j < count; j++)
+        together = ovk_nbits_decode_applies(ctx, weights[j], m, a_dtype, y_dtype) &&
+                   ovk_nbits_decode_group_compatible(weights[0], weights[j]);
+    if (together) {
+        OVK_CUDA(ctx, cudaSetDevice(ctx->device));
+        return ovk_nbits_decode_group(ctx, count, weights, a, a_dtype, m, ys, y_dtype);
+    }
+    for (int j = 0; j < count; j++) {
+        const int32_t rc = ovk_matmul_nbits(ctx, weights[j], a, a_dtype, m, ys[j], y_dtype);
+        if (rc != OVK_OK)
+            return rc;
+    }
+    return OVK_OK;
 }
 
 }  // extern "C"

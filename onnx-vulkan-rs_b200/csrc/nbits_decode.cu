@@ -54,6 +54,13 @@ struct DecParams {
     int rows;   // batch columns in use: M, or 2M for split f32 activations
     int vec_a;  // rows of A start on 16-byte boundaries: groups are read as 128-bit vectors
     int stages; // depth of the weight ring, 2..MAX_STAGES
+    // a group of weights that share the activations and the tile shape (q|k|v, gate|up): `ntiles` counts
+    // the tiles of all of them, member j owns the tiles below tile_end[j]; member 0 is packed / y / N above
+    int members;
+    const uint8_t *packed_g[3];
+    void *y_g[3];
+    int n_g[3];
+    int tile_end[4];
     int *status;
 };
 
@@ -244,6 +251,27 @@ __device__ __forceinline__ void finish_block(uint32_t *corr_entry, double s_even
     }
 }
 
+// Which member of the group owns tile u, and which of its tiles that is.
+struct TileOf {
+    const uint8_t *packed;
+    void *y;
+    int n, u;
+};
+__device__ __forceinline__ TileOf tile_of(const DecParams &p, int u)
+{
+    TileOf t{p.packed, p.y, p.N, u};
+    if (p.members > 1 && u >= p.tile_end[0]) {
+        int j = 1;
+        while (j + 1 < p.members && u >= p.tile_end[j])
+            j++;
+        t.packed = p.packed_g[j - 1];
+        t.y = p.y_g[j - 1];
+        t.n = p.n_g[j - 1];
+        t.u = u - p.tile_end[j - 1];
+    }
+    return t;
+}
+
 template <bool SCALE_F32, bool A_F32, bool Y_F32, int GBT, int UNROLL, bool ONE>
 __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
 {
@@ -286,7 +314,9 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
         int s = 0;
         uint32_t ph = 0;
         bool alive = true;
-        for (int u = blockIdx.x; u < p.ntiles && alive; u += gridDim.x) {
+        for (int ug = blockIdx.x; ug < p.ntiles && alive; ug += gridDim.x) {
+            const TileOf tl = tile_of(p, ug);
+            const int u = tl.u;
             for (int kc = 0; kc < p.NKC; kc++) {
                 bool ok = true;
                 if (lane == 0) {
@@ -303,7 +333,7 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
                 }
                 if (my_len)
                     umma::bulk_load_1d(stage_base + size_t(s) * p.tile_bytes + my_off,
-                                       p.packed + (size_t(u) * p.NKC + kc) * p.tile_bytes + my_off, my_len, &full[s]);
+                                       tl.packed + (size_t(u) * p.NKC + kc) * p.tile_bytes + my_off, my_len, &full[s]);
                 if (++s == p.stages) {
                     s = 0;
                     ph ^= 1;
@@ -467,7 +497,9 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
     bool dead = false;
     int s = 0;
     uint32_t ph = 0;
-    for (int u = blockIdx.x; u < p.ntiles; u += gridDim.x) {
+    for (int ug = blockIdx.x; ug < p.ntiles; ug += gridDim.x) {
+        const TileOf tl = tile_of(p, ug);
+        const int u = tl.u;
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         for (int kc = 0; kc < p.NKC; kc++) {
             if (!dead && !wait_bounded(&full[s], ph)) {
@@ -530,13 +562,13 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
                 if (t < p.M) {
                     const float sc = row_pow2[t];
                     const float y_lo = (v.x + v.y) * sc, y_hi = (v.z + v.w) * sc;
-                    if (col_lo < p.N) {
-                        if constexpr (Y_F32) static_cast<float *>(p.y)[int64_t(t) * p.N + col_lo] = y_lo;
-                        else static_cast<__half *>(p.y)[int64_t(t) * p.N + col_lo] = __float2half_rn(y_lo);
+                    if (col_lo < tl.n) {
+                        if constexpr (Y_F32) static_cast<float *>(tl.y)[int64_t(t) * tl.n + col_lo] = y_lo;
+                        else static_cast<__half *>(tl.y)[int64_t(t) * tl.n + col_lo] = __float2half_rn(y_lo);
                     }
-                    if (col_hi < p.N) {
-                        if constexpr (Y_F32) static_cast<float *>(p.y)[int64_t(t) * p.N + col_hi] = y_hi;
-                        else static_cast<__half *>(p.y)[int64_t(t) * p.N + col_hi] = __float2half_rn(y_hi);
+                    if (col_hi < tl.n) {
+                        if constexpr (Y_F32) static_cast<float *>(tl.y)[int64_t(t) * tl.n + col_hi] = y_hi;
+                        else static_cast<__half *>(tl.y)[int64_t(t) * tl.n + col_hi] = __float2half_rn(y_hi);
                     }
                 }
             } else {
@@ -545,9 +577,9 @@ __global__ void __launch_bounds__(THREADS, 1) nbits_decode_kernel(DecParams p)
                 for (int i = 0; i < 4; i++) {
                     const int m = 2 * t + (i & 1);
                     const int col = (i < 2) ? col_lo : col_hi;
-                    if (m < p.M && col < p.N) {
-                        if constexpr (Y_F32) static_cast<float *>(p.y)[int64_t(m) * p.N + col] = vals[i];
-                        else static_cast<__half *>(p.y)[int64_t(m) * p.N + col] = __float2half_rn(vals[i]);
+                    if (m < p.M && col < tl.n) {
+                        if constexpr (Y_F32) static_cast<float *>(tl.y)[int64_t(m) * tl.n + col] = vals[i];
+                        else static_cast<__half *>(tl.y)[int64_t(m) * tl.n + col] = __float2half_rn(vals[i]);
                     }
                 }
             }
@@ -820,11 +852,24 @@ bool ovk_nbits_decode_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int
     return w->decode && m <= 8 && decode_plan(ctx, w, a_dtype, m).rows >= 1;
 }
 
-int32_t ovk_nbits_decode(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype, int64_t m,
-                         void *y, int32_t y_dtype)
+// Weights that can share one launch: same K, block size, scale type and tile shape (then the staged
+// activations, the ring slots and every offset inside a tile are the same for all of them).
+bool ovk_nbits_decode_group_compatible(const ovk_nbits_weight *a, const ovk_nbits_weight *b)
 {
+    return a->decode && b->decode && a->k == b->k && a->block_size == b->block_size && a->scales_dtype == b->scales_dtype &&
+           a->dec_p == b->dec_p && a->dec_kc == b->dec_kc && a->dec_gb == b->dec_gb && a->dec_nkc == b->dec_nkc &&
+           a->dec_s_off == b->dec_s_off && a->dec_z_off == b->dec_z_off && a->dec_tile_bytes == b->dec_tile_bytes;
+}
+
+int32_t ovk_nbits_decode_group(ovk_ctx *ctx, int count, const ovk_nbits_weight *const *ws, const void *a, int32_t a_dtype,
+                               int64_t m, void *const *ys, int32_t y_dtype)
+{
+    const ovk_nbits_weight *w = ws[0];
+    void *y = ys[0];
+    OVK_REQUIRE(ctx, count >= 1 && count <= 4, "MatMulNBits: a group of %d weights", count);
     const bool af = a_dtype == OVK_FLOAT, yf = y_dtype == OVK_FLOAT, sf = w->scales_dtype == OVK_FLOAT;
-    OVK_REQUIRE(ctx, aligned_to(a, af ? 4 : 2) && aligned_to(y, yf ? 4 : 2), "MatMulNBits: A or Y is misaligned");
+    for (int j = 0; j < count; j++)
+        OVK_REQUIRE(ctx, aligned_to(a, af ? 4 : 2) && aligned_to(ys[j], yf ? 4 : 2), "MatMulNBits: A or Y is misaligned");
     const size_t g_pad = size_t(w->dec_nkc) * w->dec_kc * w->dec_gb;
     const int per_row = af ? 2 : 1;
     const DecodePlan plan = decode_plan(ctx, w, a_dtype, m);
@@ -844,6 +889,15 @@ int32_t ovk_nbits_decode(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
         p.GB = w->dec_gb;
         p.NKC = w->dec_nkc;
         p.ntiles = w->dec_ntiles;
+        p.members = count;
+        p.tile_end[0] = w->dec_ntiles;
+        for (int j = 1; j < count; j++) {
+            p.packed_g[j - 1] = static_cast<const uint8_t *>(ws[j]->decode);
+            p.y_g[j - 1] = static_cast<uint8_t *>(ys[j]) + size_t(m0) * size_t(ws[j]->n) * (yf ? 4 : 2);
+            p.n_g[j - 1] = int(ws[j]->n);
+            p.tile_end[j] = p.tile_end[j - 1] + ws[j]->dec_ntiles;
+            p.ntiles = p.tile_end[j];
+        }
         p.s_off = w->dec_s_off;
         p.z_off = w->dec_z_off;
         p.tile_bytes = w->dec_tile_bytes;
@@ -869,4 +923,10 @@ int32_t ovk_nbits_decode(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
             return rc;
     }
     return OVK_OK;
+}
+
+int32_t ovk_nbits_decode(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype, int64_t m,
+                         void *y, int32_t y_dtype)
+{
+    return ovk_nbits_decode_group(ctx, 1, &w, a, a_dtype, m, &y, y_dtype);
 }

@@ -59,6 +59,7 @@ SIGNATURES = {
     "ovk_nbits_prepack": (_I32, [_P, _P, _P, _I32, _P, _I64, _I64, _I64, _I64, _U32, C.POINTER(_P)]),
     "ovk_nbits_weight_destroy": (None, [_P, _P]),
     "ovk_matmul_nbits": (_I32, [_P, _P, _P, _I32, _I64, _P, _I32]),
+    "ovk_matmul_nbits_group": (_I32, [_P, _I32, C.POINTER(_P), _P, _I32, _I64, C.POINTER(_P), _I32]),
     "ovk_dynamic_quantize": (_I32, [_P, _P, _I64, _P, _P, _P]),
     "ovk_mmi_prepack": (_I32, [_P, _P, _I32, _I64, _I64, C.POINTER(_P)]),
     "ovk_mmi_weight_destroy": (None, [_P, _P]),
@@ -176,6 +177,18 @@ class Context:
             out = torch.empty(tuple(a.shape[:-1]) + (w.n,), dtype=out_dtype or a.dtype, device=a.device)
         self.check(lib().ovk_matmul_nbits(self.h, w.h, _ptr(a), _dtype_code(a), m, _ptr(out), _dtype_code(out)))
         return out
+
+    def matmul_nbits_group(self, ws, a, outs=None, out_dtype=None):
+        """Several weights over the same activations (q|k|v, gate|up): one launch where the decode kernel
+        applies and the weights share their tile shape, one call per weight otherwise."""
+        import torch
+        m = a.numel() // ws[0].k
+        if outs is None:
+            outs = [torch.empty(tuple(a.shape[:-1]) + (w.n,), dtype=out_dtype or a.dtype, device=a.device) for w in ws]
+        wp = (_P * len(ws))(*[w.h for w in ws])
+        yp = (_P * len(ws))(*[_ptr(o) for o in outs])
+        self.check(lib().ovk_matmul_nbits_group(self.h, len(ws), wp, _ptr(a), _dtype_code(a), m, yp, _dtype_code(outs[0])))
+        return outs
 
     # ------------------------------------------------- DynamicQuantizeLinear
     def dynamic_quantize(self, x):

@@ -5,6 +5,7 @@ import torch
 
 import cases
 import oracle as orc
+import ovk_b200
 from gpu_util import assert_close, ctx, dev, host
 
 pytestmark = pytest.mark.gpu
@@ -175,3 +176,35 @@ def test_qwen_prefill_full_size_sampled():
                             orc.pack_zero_points(zp[cols]), k, cols.size, bs)
     assert_close(got[np.ix_(rows, cols)], want, 1e-3, 1e-3, "qwen gate/up prefill")
     assert np.isfinite(got.astype(np.float32)).all()
+
+
+@pytest.mark.parametrize("shapes,m", [(((1152, 1024), (1152, 256), (1152, 256)), 1), (((1152, 6912), (1152, 6912)), 1),
+                                      (((1152, 1024), (1152, 256), (1152, 256)), 3),
+                                      (((256, 96), (128, 96)), 1), (((640, 300), (640, 80)), 20)])
+def test_group_of_weights_over_the_same_activations(shapes, m):
+    """q|k|v and gate|up in one launch: every member's result is that of its own call (bit for bit when
+    the group runs as one launch, which a decode kernel name after the call shows)."""
+    k0 = shapes[0][0]
+    ws, packed = [], []
+    a = None
+    for j, (k, n) in enumerate(shapes):
+        aj, nib, zp, scale = cases.nbits_synthetic(30 + j, m, k, n, 32)
+        a = aj if a is None else a
+        packed.append((nib, zp, scale, k, n))
+        ws.append(ctx().nbits_prepack(dev(orc.pack_nibbles(nib, 32)), dev(scale.reshape(-1)),
+                                      dev(orc.pack_zero_points(zp)), n, k, 32))
+    same_k = all(k == k0 for k, _ in shapes)
+    if not same_k:
+        with pytest.raises(ovk_b200.OvkError):
+            ctx().matmul_nbits_group(ws, dev(a))
+        return
+    before = ctx().launches
+    outs = ctx().matmul_nbits_group(ws, dev(a))
+    launched = ctx().launches - before
+    if m <= 8:
+        assert launched == 1 and ctx().last_kernel == "nbits_decode_mma"
+    else:
+        assert launched >= len(ws)  # one prefill launch per member (plus the lazy prefill copies)
+    for w, y in zip(ws, outs):
+        alone = ctx().matmul_nbits(w, dev(a))
+        assert np.array_equal(host(y).view(np.uint16), host(alone).view(np.uint16))
