@@ -35,24 +35,29 @@ __device__ __forceinline__ uint32_t add_code(int32_t av, int32_t bv, float ra, f
     return uint32_t(int32_t(c)) & 0xffu;
 }
 
-// same shape on both sides: four elements per thread, one word in, one word out
+// same shape on both sides: sixteen elements per thread, 128 bits in from each side, 128 bits out
 __global__ void __launch_bounds__(256)
-qlinear_add_flat_kernel(const uint32_t *__restrict__ a, const uint32_t *__restrict__ b, uint32_t *__restrict__ out,
-                        int64_t words, float ra, float rb, float fixed, int is_signed)
+qlinear_add_flat_kernel(const uint4 *__restrict__ a, const uint4 *__restrict__ b, uint4 *__restrict__ out,
+                        int64_t vecs, float ra, float rb, float fixed, int is_signed)
 {
     const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= words)
+    if (i >= vecs)
         return;
-    const uint32_t aw = a[i], bw = b[i];
-    uint32_t o = 0;
+    const uint4 av4 = __ldcs(a + i), bv4 = __ldcs(b + i);
+    const uint32_t aw[4] = {av4.x, av4.y, av4.z, av4.w}, bw[4] = {bv4.x, bv4.y, bv4.z, bv4.w};
+    uint32_t o[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const uint32_t ab = (aw >> (8 * j)) & 0xffu, bb = (bw >> (8 * j)) & 0xffu;
-        const int32_t av = is_signed ? int32_t(int8_t(ab)) : int32_t(ab);
-        const int32_t bv = is_signed ? int32_t(int8_t(bb)) : int32_t(bb);
-        o |= add_code(av, bv, ra, rb, fixed, is_signed) << (8 * j);
+    for (int w = 0; w < 4; w++) {
+        o[w] = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint32_t ab = (aw[w] >> (8 * j)) & 0xffu, bb = (bw[w] >> (8 * j)) & 0xffu;
+            const int32_t av = is_signed ? int32_t(int8_t(ab)) : int32_t(ab);
+            const int32_t bv = is_signed ? int32_t(int8_t(bb)) : int32_t(bb);
+            o[w] |= add_code(av, bv, ra, rb, fixed, is_signed) << (8 * j);
+        }
     }
-    out[i] = o;
+    __stcs(out + i, make_uint4(o[0], o[1], o[2], o[3]));
 }
 
 // general ONNX broadcasting, one element per thread
@@ -223,10 +228,10 @@ extern "C" int32_t ovk_qlinear_add(ovk_ctx *ctx, const void *a, const int64_t *a
     // MLAS folds the zero points into one addend, with this contraction (interp.rs:4918)
     volatile float rbz = rb * float(b_zp);
     const float fixed = float(c_zp) - std::fmaf(ra, float(a_zp), rbz);
-    const bool flat = run_a == n && run_b == n && (n % 4) == 0 && aligned_to(a, 4) && aligned_to(b, 4) && aligned_to(out, 4);
+    const bool flat = run_a == n && run_b == n && (n % 16) == 0 && aligned_to(a, 16) && aligned_to(b, 16) && aligned_to(out, 16);
     if (flat) {
-        qlinear_add_flat_kernel<<<blocks_for(n / 4, 256), 256, 0, ctx->stream>>>(
-            static_cast<const uint32_t *>(a), static_cast<const uint32_t *>(b), static_cast<uint32_t *>(out), n / 4, ra, rb,
+        qlinear_add_flat_kernel<<<blocks_for(n / 16, 256), 256, 0, ctx->stream>>>(
+            static_cast<const uint4 *>(a), static_cast<const uint4 *>(b), static_cast<uint4 *>(out), n / 16, ra, rb,
             fixed, is_signed ? 1 : 0);
         OVK_LAUNCHED(ctx, "qlinear_add");
     } else {
