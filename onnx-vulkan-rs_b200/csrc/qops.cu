@@ -35,6 +35,36 @@ __device__ __forceinline__ uint32_t add_code(int32_t av, int32_t bv, float ra, f
     return uint32_t(int32_t(c)) & 0xffu;
 }
 
+// Byte -> float and float -> byte without the quarter-rate conversion instructions: a byte put into
+// the low mantissa bits of 2^23 is the float 2^23 + b, and adding 1.5 * 2^23 to a value already clamped to
+// the byte range rounds it to nearest-even with the result in the low byte.  Clamping before rounding gives
+// the same code as rounding before clamping because the bounds are integers.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
+{
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+template <int J>
+__device__ __forceinline__ float byte_to_float(uint32_t word, float bias)
+{
+    // byte J of `word` under the exponent of 2^23; `word` already has its sign bits flipped for int8
+    return __fsub_rn(__uint_as_float(prmt(word, 0x4B000000u, 0x7650u | J)), bias);
+}
+__device__ __forceinline__ uint32_t add_word(uint32_t aw, uint32_t bw, float ra, float rb, float fixed, float bias, float lo,
+                                             float hi)
+{
+    uint32_t r[4];
+#define OVK_ADD_ONE(J)                                                                                        \
+    {                                                                                                         \
+        const float y = fmaf(byte_to_float<J>(aw, bias), ra, fmaf(byte_to_float<J>(bw, bias), rb, fixed));    \
+        r[J] = __float_as_uint(__fadd_rn(fminf(fmaxf(y, lo), hi), 12582912.0f));                              \
+    }
+    OVK_ADD_ONE(0) OVK_ADD_ONE(1) OVK_ADD_ONE(2) OVK_ADD_ONE(3)
+#undef OVK_ADD_ONE
+    return prmt(prmt(r[0], r[1], 0x0040u), prmt(r[2], r[3], 0x0040u), 0x5410u);  // the four low bytes
+}
+
 // same shape on both sides: sixteen elements per thread, 128 bits in from each side, 128 bits out
 __global__ void __launch_bounds__(256)
 qlinear_add_flat_kernel(const uint4 *__restrict__ a, const uint4 *__restrict__ b, uint4 *__restrict__ out,
@@ -43,21 +73,17 @@ qlinear_add_flat_kernel(const uint4 *__restrict__ a, const uint4 *__restrict__ b
     const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= vecs)
         return;
-    const uint4 av4 = __ldcs(a + i), bv4 = __ldcs(b + i);
-    const uint32_t aw[4] = {av4.x, av4.y, av4.z, av4.w}, bw[4] = {bv4.x, bv4.y, bv4.z, bv4.w};
-    uint32_t o[4];
-#pragma unroll
-    for (int w = 0; w < 4; w++) {
-        o[w] = 0;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const uint32_t ab = (aw[w] >> (8 * j)) & 0xffu, bb = (bw[w] >> (8 * j)) & 0xffu;
-            const int32_t av = is_signed ? int32_t(int8_t(ab)) : int32_t(ab);
-            const int32_t bv = is_signed ? int32_t(int8_t(bb)) : int32_t(bb);
-            o[w] |= add_code(av, bv, ra, rb, fixed, is_signed) << (8 * j);
-        }
-    }
-    __stcs(out + i, make_uint4(o[0], o[1], o[2], o[3]));
+    uint4 av = __ldcs(a + i), bv = __ldcs(b + i);
+    // int8: b ^ 0x80 is the byte b + 128, so the bias grows by 128
+    const uint32_t flip = is_signed ? 0x80808080u : 0u;
+    const float bias = is_signed ? 8388736.0f : 8388608.0f;
+    const float lo = is_signed ? -128.0f : 0.0f, hi = is_signed ? 127.0f : 255.0f;
+    uint4 o;
+    o.x = add_word(av.x ^ flip, bv.x ^ flip, ra, rb, fixed, bias, lo, hi);
+    o.y = add_word(av.y ^ flip, bv.y ^ flip, ra, rb, fixed, bias, lo, hi);
+    o.z = add_word(av.z ^ flip, bv.z ^ flip, ra, rb, fixed, bias, lo, hi);
+    o.w = add_word(av.w ^ flip, bv.w ^ flip, ra, rb, fixed, bias, lo, hi);
+    __stcs(out + i, o);
 }
 
 // general ONNX broadcasting, one element per thread
