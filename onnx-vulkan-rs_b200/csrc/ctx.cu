@@ -84,6 +84,7 @@ int32_t ovk_ctx_create(int32_t device, void *stream, ovk_ctx **out)
     CTX_CUDA(cudaMalloc(&ctx->dev_status, 256));
     CTX_CUDA(cudaMalloc(&ctx->params, OVK_PARAM_FLOATS * sizeof(float)));
     CTX_CUDA(cudaMemset(ctx->dev_status, 0, 256));
+    CTX_CUDA(cudaMemset(ctx->range_slot, 0, 256));  // DynamicQuantizeLinear leaves it zeroed after every call
     CTX_CUDA(cudaMallocHost(&ctx->host_status, 64));
     ctx->host_status[0] = 0;
     CTX_CUDA(cudaEventCreate(&ctx->t0));

@@ -19,10 +19,13 @@ __device__ __forceinline__ void fold(float v, float &mn, float &mx)
 }
 
 // range[0] = bits of -min, range[1] = bits of max, both >= 0 so that unsigned
-// order is float order; the slot is zeroed before the launch (= range [0,0]).
+// order is float order; the slot is zero when the kernel starts (= range [0,0]): it is zeroed when
+// the context is created and again by the last block of every quantize pass (range[2] counts them).
 __global__ void __launch_bounds__(256)
 dql_range_kernel(const float *__restrict__ x, int64_t n, uint32_t *__restrict__ range, int vec_ok)
 {
+    OVK_PDL_LAUNCH_DEPENDENTS();
+    OVK_PDL_WAIT();
     float mn = 0.0f, mx = 0.0f;  // 0 is always part of the range
     const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
@@ -82,10 +85,12 @@ __device__ __forceinline__ uint32_t quant1(float v, float scale, float zp)
 }
 
 __global__ void __launch_bounds__(256)
-dql_quantize_kernel(const float *__restrict__ x, int64_t n, const uint32_t *__restrict__ range,
+dql_quantize_kernel(const float *__restrict__ x, int64_t n, uint32_t *__restrict__ range,
                     float *__restrict__ scale_out, uint8_t *__restrict__ zp_out,
                     uint8_t *__restrict__ y, int vec_ok)
 {
+    OVK_PDL_LAUNCH_DEPENDENTS();
+    OVK_PDL_WAIT();
     __shared__ float s_scale, s_zp;
     if (threadIdx.x == 0) {
         float scale, zp;
@@ -95,6 +100,13 @@ dql_quantize_kernel(const float *__restrict__ x, int64_t n, const uint32_t *__re
         if (blockIdx.x == 0) {
             scale_out[0] = scale;
             zp_out[0] = uint8_t(zp);
+        }
+        // the block that reads the range last leaves the slot zeroed for the next call
+        __threadfence();
+        if (atomicAdd(range + 2, 1u) == gridDim.x - 1) {
+            range[0] = 0u;
+            range[1] = 0u;
+            range[2] = 0u;
         }
     }
     __syncthreads();
@@ -143,15 +155,14 @@ extern "C" int32_t ovk_dynamic_quantize(ovk_ctx *ctx, const float *x, int64_t n,
     OVK_REQUIRE(ctx, x && y, "DynamicQuantizeLinear: x or y is null");
     OVK_REQUIRE(ctx, aligned_to(x, 4), "DynamicQuantizeLinear: x is not 4-byte aligned");
     const int vec_ok = aligned_to(x, 16) && aligned_to(y, 4);
-    OVK_CUDA(ctx, cudaMemsetAsync(ctx->range_slot, 0, 8, ctx->stream));
     const int64_t work = vec_ok ? (n + 3) / 4 : n;
     // pass 1: a few resident blocks per SM, grid-stride
     unsigned blocks1 = unsigned(std::min<int64_t>(ceil_div64(work, 256), int64_t(ctx->sm_count) * 8));
-    dql_range_kernel<<<blocks1, 256, 0, ctx->stream>>>(x, n, ctx->range_slot, vec_ok);
+    OVK_CUDA(ctx, ovk_launch_pdl(dql_range_kernel, dim3(blocks1), dim3(256), 0, ctx->stream, x, n, ctx->range_slot, vec_ok));
     OVK_LAUNCHED(ctx, "dql_range");
     unsigned blocks2 = unsigned(std::min<int64_t>(ceil_div64(work, 256), int64_t(ctx->sm_count) * 8));
-    dql_quantize_kernel<<<blocks2, 256, 0, ctx->stream>>>(x, n, ctx->range_slot, y_scale,
-                                                          y_zero_point, y, vec_ok);
+    OVK_CUDA(ctx, ovk_launch_pdl(dql_quantize_kernel, dim3(blocks2), dim3(256), 0, ctx->stream, x, n, ctx->range_slot, y_scale,
+                                 y_zero_point, y, vec_ok));
     OVK_LAUNCHED(ctx, "dql_quantize");
     return OVK_OK;
 }

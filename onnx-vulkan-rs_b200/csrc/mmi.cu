@@ -71,6 +71,8 @@ mmi_small_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ bt,
                  int a_signed, int b_signed, const void *a_zp_p, const void *b_zp_p, EpiParams epi,
                  void *out, int words_ok)
 {
+    OVK_PDL_LAUNCH_DEPENDENTS();
+    OVK_PDL_WAIT();
     const int64_t row = int64_t(blockIdx.y) * 16 + (threadIdx.x >> 4);
     const int col = blockIdx.x * 16 + (threadIdx.x & 15);
     float run_max = 0.0f, run_neg = 0.0f;
@@ -135,9 +137,9 @@ int32_t run_mmi(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int32_t a_
     OVK_REQUIRE(ctx, ceil_div64(m, 16) <= 65535, "%s: %lld rows exceed the small-shape grid", op, (long long)m);
     dim3 grid(unsigned(ceil_div64(w->n, 16)), unsigned(ceil_div64(m, 16)));
     const int words_ok = aligned_to(a, 4) && (w->k % 4 == 0);
-    mmi_small_kernel<<<grid, 256, 0, ctx->stream>>>(
-        static_cast<const uint8_t *>(a), w->bt, w->colsum, m, int(w->k), int(w->n), int(w->k_pad),
-        a_signed, w->b_signed, a_zp, b_zp, epi, out, words_ok);
+    OVK_CUDA(ctx, ovk_launch_pdl(mmi_small_kernel, grid, dim3(256), 0, ctx->stream, static_cast<const uint8_t *>(a),
+                                 static_cast<const uint8_t *>(w->bt), static_cast<const int32_t *>(w->colsum), m, int(w->k),
+                                 int(w->n), int(w->k_pad), int(a_signed), int(w->b_signed), a_zp, b_zp, epi, out, words_ok));
     OVK_LAUNCHED(ctx, "mmi_small");
     return OVK_OK;
 }

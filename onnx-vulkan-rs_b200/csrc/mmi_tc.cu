@@ -173,6 +173,7 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     uint64_t *acc_empty = acc_full + 2;    // [2] the four epilogue warps have read it
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
 
+    OVK_PDL_LAUNCH_DEPENDENTS();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // persistent: tiles are taken round robin, N fastest so that CTAs running together share rows of A
     const int n_tiles = (p.N + BN - 1) / BN;
@@ -197,6 +198,7 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     __syncthreads();
     umma::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    OVK_PDL_WAIT();  // barriers and tensor memory were set up while the previous kernel drained
 
     if (warp == 0) {
         if (lane == 0) {
@@ -332,6 +334,7 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint64_t *acc_empty = acc_full + 1;    // the eight epilogue warps have read them
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 1);
 
+    OVK_PDL_LAUNCH_DEPENDENTS();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = (p.N + BN2 - 1) / BN2;
     const int total_tiles = n_tiles * int((p.M + BM2 - 1) / BM2);
@@ -354,6 +357,7 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __syncthreads();
     umma::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    OVK_PDL_WAIT();  // barriers and tensor memory were set up while the previous kernel drained
 
     if (warp == 0) {
         if (lane == 0) {
@@ -459,6 +463,8 @@ __global__ void __launch_bounds__(256)
 mmi_rowsum_kernel(const uint8_t *__restrict__ a, int64_t M, int K, int a_signed, const void *b_zp,
                   int b_signed, int32_t *__restrict__ rowsum)
 {
+    OVK_PDL_LAUNCH_DEPENDENTS();
+    OVK_PDL_WAIT();
     if (load_zp(b_zp, b_signed) == 0)
         return;
     const int64_t row = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -489,7 +495,7 @@ int32_t launch(ovk_ctx *ctx, const CUtensorMap &tmA, const ovk_mmi_weight *w, co
                                        int(smem_for<BN>())));
     const int64_t tiles = ceil_div64(p.N, BN) * ceil_div64(p.M, BM);
     const unsigned grid = unsigned(std::min<int64_t>(tiles, ctx->sm_count));
-    mmi_tc_kernel<BN><<<grid, THREADS, smem_for<BN>(), ctx->stream>>>(tmA, tmB, p);
+    OVK_CUDA(ctx, ovk_launch_pdl(mmi_tc_kernel<BN>, dim3(grid), dim3(THREADS), smem_for<BN>(), ctx->stream, tmA, tmB, p));
     OVK_LAUNCHED(ctx, BN == 256 ? "mmi_tc_128x256" : (BN == 128 ? "mmi_tc_128x128" : "mmi_tc_128x64"));
     return OVK_OK;
 }
@@ -507,7 +513,7 @@ int32_t launch256(ovk_ctx *ctx, const void *a, const ovk_mmi_weight *w, const Tc
     OVK_CUDA(ctx, cudaFuncSetAttribute(mmi_tc256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM2)));
     const int64_t tiles = ceil_div64(p.N, BN2) * ceil_div64(p.M, BM2);
     const unsigned grid = unsigned(std::min<int64_t>(tiles, ctx->sm_count));
-    mmi_tc256_kernel<<<grid, THREADS2, SMEM2, ctx->stream>>>(tmA, tmB, p);
+    OVK_CUDA(ctx, ovk_launch_pdl(mmi_tc256_kernel, dim3(grid), dim3(THREADS2), SMEM2, ctx->stream, tmA, tmB, p));
     OVK_LAUNCHED(ctx, "mmi_tc_256x256");
     return OVK_OK;
 }
@@ -567,8 +573,9 @@ int32_t ovk_mmi_tc_launch(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, 
         if (rc != OVK_OK)
             return rc;
         p.rowsum = static_cast<int32_t *>(ws);
-        mmi_rowsum_kernel<<<unsigned(ceil_div64(m * 32, 256)), 256, 0, ctx->stream>>>(
-            static_cast<const uint8_t *>(a), m, p.K, p.a_signed, b_zp, p.b_signed, static_cast<int32_t *>(ws));
+        OVK_CUDA(ctx, ovk_launch_pdl(mmi_rowsum_kernel, dim3(unsigned(ceil_div64(m * 32, 256))), dim3(256), 0, ctx->stream,
+                                     static_cast<const uint8_t *>(a), m, p.K, p.a_signed, b_zp, p.b_signed,
+                                     static_cast<int32_t *>(ws)));
         OVK_LAUNCHED(ctx, "mmi_rowsum");
     }
     if (wants256(ctx, w, m))

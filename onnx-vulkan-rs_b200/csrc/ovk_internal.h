@@ -9,6 +9,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "ovk_cuda.h"
@@ -81,6 +82,31 @@ int32_t ovk_scratch(ovk_ctx *ctx, size_t bytes, void **out);
     } while (0)
 
 static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// A launch that may begin while the previous kernel of the stream is still draining (programmatic
+// dependent launch).  Kernels launched this way call griddepcontrol.launch_dependents early and touch
+// nothing another kernel produces, and write nothing, before griddepcontrol.wait: only their prologue
+// (barriers, tensor memory, index arithmetic) and the launch latency overlap the predecessor.
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+static inline cudaError_t ovk_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                         Args &&...args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#define OVK_PDL_LAUNCH_DEPENDENTS() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+#define OVK_PDL_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
+#endif
 static inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 // ---------------------------------------------------------------- weights
