@@ -216,6 +216,19 @@ OVK_API int32_t ovk_conv_output_shape(const ovk_qconv_weight *w, const ovk_conv_
 OVK_API int32_t ovk_conv_integer(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x,
                                  int32_t x_signed, const ovk_conv_params *p, int32_t x_zp,
                                  int32_t w_zp, int32_t *out);
+/* interp::conv_integer_scale_bias (interp.rs:4359-4420): the fused
+ * ConvInteger -> Cast -> Mul -> Add [-> Relu] node,
+ *   out[n,c,h,w] = fl(fl(float(acc) * s[c]) + bias[c]),  s = scale or fl(scale * product),
+ * bit-identical to the unfused graph.  A step is 0 (one value) or 1 (one per
+ * output channel), the two broadcasts interp::channel_step (:4404-4417) takes;
+ * others are refused (the reference runs them unfused).  flags and range as in
+ * ovk_matmul_integer_scale_bias. */
+OVK_API int32_t ovk_conv_integer_scale_bias(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x,
+                                            int32_t x_signed, const ovk_conv_params *p, int32_t x_zp,
+                                            int32_t w_zp, const float *scale, int32_t scale_step,
+                                            const float *product, int32_t product_step,
+                                            const float *bias, int32_t bias_step, uint32_t flags,
+                                            uint32_t *range, float *out);
 /* interp::qlinear_conv (interp.rs:4796-4837) = ConvInteger + requantize
  * (interp.rs:4714-4788, shaders/qlinear.rs:28-63):
  *   y = sat(rne(f32(acc + bias[c]) * ratio[c]) + y_zp).

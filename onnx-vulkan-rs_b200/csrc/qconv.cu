@@ -25,14 +25,10 @@ __device__ __forceinline__ int32_t sx8(uint8_t b, int is_signed)
     return is_signed ? int32_t(int8_t(b)) : int32_t(b);
 }
 
-__global__ void __launch_bounds__(256)
-conv_direct_kernel(const uint8_t *__restrict__ x, const uint8_t *__restrict__ w, ConvGeom g,
-                   int x_signed, int w_signed, int32_t x_zp, int32_t w_zp, EpiParams epi,
-                   void *out, int64_t total)
+__device__ __forceinline__ int32_t conv_point(const uint8_t *__restrict__ x, const uint8_t *__restrict__ w,
+                                              const ConvGeom &g, int x_signed, int w_signed, int32_t x_zp,
+                                              int32_t w_zp, int64_t o, int *channel)
 {
-    const int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (o >= total)
-        return;
     const int ow = int(o % g.w_out);
     int64_t t1 = o / g.w_out;
     const int oh = int(t1 % g.h_out);
@@ -58,10 +54,31 @@ conv_direct_kernel(const uint8_t *__restrict__ x, const uint8_t *__restrict__ w,
             }
         }
     }
-    if (epi.mode == EPI_RAW)
-        static_cast<int32_t *>(out)[o] = acc;
-    else
-        static_cast<uint8_t *>(out)[o] = uint8_t(epi_requant_value(epi, m, acc));
+    *channel = m;
+    return acc;
+}
+
+__global__ void __launch_bounds__(256)
+conv_direct_kernel(const uint8_t *__restrict__ x, const uint8_t *__restrict__ w, ConvGeom g,
+                   int x_signed, int w_signed, int32_t x_zp, int32_t w_zp, EpiParams epi,
+                   void *out, int64_t total)
+{
+    const int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    float v = 0.0f;  // what a thread past the end contributes to the range fold
+    if (o < total) {
+        int m;
+        const int32_t acc = conv_point(x, w, g, x_signed, w_signed, x_zp, w_zp, o, &m);
+        if (epi.mode == EPI_RAW) {
+            static_cast<int32_t *>(out)[o] = acc;
+        } else if (epi.mode == EPI_SCALE) {
+            v = epi_scale_value(epi, m, float(acc));
+            static_cast<float *>(out)[o] = v;
+        } else {
+            static_cast<uint8_t *>(out)[o] = uint8_t(epi_requant_value(epi, m, acc));
+        }
+    }
+    if (epi.mode == EPI_SCALE)  // uniform over the grid: the fold's warp exchange sees all 32 lanes
+        epi_fold_range(epi, fmaxf(v, 0.0f), fmaxf(-v, 0.0f));
 }
 
 // REQUANTIZE on its own (shaders/qlinear.rs:28-63): four outputs per thread.
@@ -225,6 +242,31 @@ int32_t ovk_conv_integer(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x,
     EpiParams epi = {};
     epi.mode = EPI_RAW;
     return run_conv(ctx, w, x, x_signed, p, x_zp, w_zp, epi, out, "ConvInteger");
+}
+
+int32_t ovk_conv_integer_scale_bias(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x,
+                                    int32_t x_signed, const ovk_conv_params *p, int32_t x_zp,
+                                    int32_t w_zp, const float *scale, int32_t scale_step,
+                                    const float *product, int32_t product_step, const float *bias,
+                                    int32_t bias_step, uint32_t flags, uint32_t *range, float *out)
+{
+    if (!ctx)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "ConvIntegerScaleBias: null context");
+    OVK_REQUIRE(ctx, scale && bias, "ConvIntegerScaleBias: scale or bias is null");
+    OVK_REQUIRE(ctx, (scale_step | 1) == 1 && (bias_step | 1) == 1 && (product_step | 1) == 1,
+                "ConvIntegerScaleBias: a step is 0 (per tensor) or 1 (per channel)");
+    OVK_REQUIRE(ctx, !(flags & OVK_EPILOGUE_RANGE) || range, "ConvIntegerScaleBias: range requested without a slot");
+    EpiParams epi = {};
+    epi.mode = EPI_SCALE;
+    epi.scale = scale;
+    epi.scale_step = scale_step;
+    epi.product = product;
+    epi.product_step = product ? product_step : 0;
+    epi.fbias = bias;
+    epi.bias_step = bias_step;
+    epi.flags = flags;
+    epi.range = range;
+    return run_conv(ctx, w, x, x_signed, p, x_zp, w_zp, epi, out, "ConvIntegerScaleBias");
 }
 
 int32_t ovk_qlinear_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,

@@ -98,6 +98,7 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     // 16-byte units (the unit of a descriptor's address field)
     uint32_t *s_tap_a = reinterpret_cast<uint32_t *>(s_ratio + 256);
     uint32_t *s_tap_w = s_tap_a + 64;
+    float *s_fbias = reinterpret_cast<float *>(s_tap_w + 64);  // present only for the scale-and-bias store
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int tap = threadIdx.x; tap < p.taps && tap < 64; tap += THREADS) {
@@ -114,10 +115,17 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                 if (p.epi.ibias)
                     corr = int32_t(uint32_t(corr) + uint32_t(p.epi.ibias[co]));
                 ratio = p.epi.ratio[co * p.epi.ratio_step];
+            } else if (p.epi.mode == EPI_SCALE) {
+                // s = scale or fl(scale * product), as epi_scale_value computes it per element
+                ratio = p.epi.scale[co * p.epi.scale_step];
+                if (p.epi.product)
+                    ratio = __fmul_rn(ratio, p.epi.product[co * p.epi.product_step]);
             }
         }
         s_corr[co] = corr;
         s_ratio[co] = ratio;
+        if (p.epi.mode == EPI_SCALE)
+            s_fbias[co] = co < p.c_out ? p.epi.fbias[co * p.epi.bias_step] : 0.0f;
     }
     const int nacc = p.nacc;  // power of two
     uint32_t tmem_cols = 32;
@@ -294,6 +302,7 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         const int lo = p.epi.y_signed ? -128 : 0, hi = p.epi.y_signed ? 127 : 255;
         const float clamp_lo = float(lo - p.epi.y_zp), clamp_hi = float(hi - p.epi.y_zp);
         const int32_t round_fix = p.epi.y_zp - 0x4B400000;
+        float run_max = 0.0f, run_neg = 0.0f;  // extrema of the scale-and-bias store, folded once at the end
         for (int tile = blockIdx.x; tile < p.m_tiles; tile += gridDim.x, tile_seq++) {
             const int b = tile_seq & (nacc - 1);
             if (ok && !wait_bounded(&acc_full[b], (tile_seq / nacc) & 1)) {
@@ -350,6 +359,23 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                     for (int j = 0; j < 16; j++)
                         if (j < nch)
                             o[int64_t(j) * plane] = int32_t(r[j] + uint32_t(corr[j]));
+                } else if (p.epi.mode == EPI_SCALE) {
+                    // fl(fl(float(acc) * s) + bias) [Relu], every step separately rounded
+                    // (glsl/matmul_integer_coop.comp:156-196)
+                    float *o = static_cast<float *>(p.out) + o_base + int64_t(c0) * plane;
+                    const bool relu = p.epi.flags & 1u;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int32_t acc = int32_t(r[j] + uint32_t(corr[j]));
+                        float z = __fadd_rn(__fmul_rn(float(acc), ratio[j]), s_fbias[c0 + j]);
+                        if (relu)
+                            z = fmaxf(z, 0.0f);
+                        if (j < nch) {
+                            o[int64_t(j) * plane] = z;
+                            run_max = fmaxf(run_max, z);
+                            run_neg = fmaxf(run_neg, -z);
+                        }
+                    }
                 } else {
                     uint8_t *o = static_cast<uint8_t *>(p.out) + o_base + int64_t(c0) * plane;
 #pragma unroll
@@ -369,6 +395,8 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                 }
             }
         }
+        if (p.epi.mode == EPI_SCALE)
+            epi_fold_range(p.epi, run_max, run_neg);
     }
     umma::tc_fence_before();
     __syncthreads();
@@ -672,7 +700,8 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
     p.a_stage = uint32_t((size_t(p.halo_rows) * p.kch + 1023) & ~size_t(1023));
     p.w_slice = uint32_t((size_t(p.co_pad) * p.kch + 1023) & ~size_t(1023));
     const size_t w_bytes = size_t(p.taps) * p.chunks * p.w_slice;
-    const size_t avail = ctx->smem_optin - w_bytes - 1024 - 2048 - 512;
+    const size_t epi_extra = epi.mode == EPI_SCALE ? 1024 : 0;  // the per-channel float bias
+    const size_t avail = ctx->smem_optin - w_bytes - 1024 - 2048 - 512 - epi_extra;
     p.stages = int(std::min<size_t>(MAX_STAGES, avail / p.a_stage));
     if (p.stages < 2)
         return OVK_UNSUPPORTED;
@@ -705,7 +734,7 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
         !ovk_make_tmap_2d(&tmW, w->w_taps, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(C), uint64_t(p.taps) * p.co_pad,
                           uint64_t(C), uint32_t(p.kch), uint32_t(p.co_pad), swz))
         return ovk_fail(ctx, OVK_BACKEND, "ConvInteger: cuTensorMapEncodeTiled failed");
-    const size_t smem = w_bytes + size_t(p.stages) * p.a_stage + 512 + 2048 + 512;
+    const size_t smem = w_bytes + size_t(p.stages) * p.a_stage + 512 + 2048 + 512 + epi_extra;
     OVK_CUDA(ctx, cudaFuncSetAttribute(qconv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     const unsigned grid = unsigned(std::min<int>(p.m_tiles, ctx->sm_count));
     {

@@ -419,6 +419,66 @@ Result conv_integer(Env &env, const NodeIr &node)
                                                     static_cast<int32_t *>(out->dev)));
 }
 
+// channel_step (interp.rs:4404-4417): how an operand broadcasts against an [N, C_out, ..] output of
+// this rank: 0 one value, 1 one per channel, -1 anything else
+int channel_step(const std::vector<int64_t> &shape, int64_t c_out, size_t rank)
+{
+    if (shape.size() > rank)
+        return -1;
+    bool ones = true;
+    for (int64_t d : shape)
+        ones = ones && d == 1;
+    if (ones)
+        return 0;
+    if (rank < 2 || shape.size() < rank - 1)  // the channel axis, counted from the right
+        return -1;
+    const size_t channel = shape.size() - (rank - 1);
+    for (size_t i = 0; i < shape.size(); i++)
+        if (i != channel && shape[i] != 1)
+            return -1;
+    return shape[channel] == c_out ? 1 : -1;
+}
+
+// interp::conv_integer_scale_bias (interp.rs:4359-4371): ConvInteger with the Cast, Mul, Add [, Relu]
+// that follow it applied to each accumulator
+Result conv_integer_scale_bias(Env &env, const NodeIr &node)
+{
+    const Tensor *scale = env.find(node.inputs[4]);
+    const Tensor *bias = env.find(node.inputs[5]);
+    const Tensor *prod = node.present(6) ? env.find(node.inputs[6]) : nullptr;
+    OVKH_ENSURE(scale && bias && (prod || !node.present(6)), "ConvIntegerScaleBias: an input is missing");
+    ConvCall c;
+    OVKH_TRY(conv_setup(env, node, node.inputs[0], node.inputs[1], &c));
+    const std::vector<int64_t> out_shape = conv_out_shape(c);
+    const int ss = channel_step(scale->shape, c.c_out, out_shape.size());
+    const int bs = channel_step(bias->shape, c.c_out, out_shape.size());
+    const int ps = prod ? channel_step(prod->shape, c.c_out, out_shape.size()) : 0;
+    if (ss < 0 || bs < 0 || ps < 0 || scale->dtype != OVK_FLOAT || bias->dtype != OVK_FLOAT ||
+        (prod && prod->dtype != OVK_FLOAT))
+        return fail(OVK_UNSUPPORTED,
+                    "ConvIntegerScaleBias: not fused (a scale, product or bias that is not f32 or broadcasts other "
+                    "than per tensor or per channel): the reference runs ConvInteger, Cast, Mul, Add as separate "
+                    "nodes here");
+    int32_t x_zp = 0, w_zp = 0;
+    if (node.present(2))
+        OVKH_TRY(scalar_i32(env, node.inputs[2], "ConvInteger", &x_zp));
+    if (node.present(3))
+        OVKH_TRY(scalar_i32(env, node.inputs[3], "ConvInteger", &w_zp));
+    uint32_t flags = node.int_attr("relu", 0) == 1 ? OVK_EPILOGUE_RELU : 0;
+    Tensor *out = nullptr;
+    OVKH_TRY(env.alloc(node.outputs[0], OVK_FLOAT, out_shape, &out));
+    const Tensor *x = env.find(node.inputs[0]);
+    scale = env.find(node.inputs[4]);
+    bias = env.find(node.inputs[5]);
+    prod = node.present(6) ? env.find(node.inputs[6]) : nullptr;
+    return from_abi(env.context(),
+                    ovk_conv_integer_scale_bias(env.context(), c.w, x->dev, x->dtype == OVK_INT8, &c.p, x_zp, w_zp,
+                                                static_cast<const float *>(scale->dev), ss,
+                                                prod ? static_cast<const float *>(prod->dev) : nullptr, ps,
+                                                static_cast<const float *>(bias->dev), bs, flags, nullptr,
+                                                static_cast<float *>(out->dev)));
+}
+
 // interp::qlinear_conv (interp.rs:4796-4837)
 Result qlinear_conv(Env &env, const NodeIr &node)
 {
@@ -868,6 +928,9 @@ bool is_implemented_node(const NodeIr &node)
         return node.inputs.size() >= 6 && node.inputs.size() <= 7 && node.outputs.size() == 1;
     if (op == "ConvInteger")
         return node.inputs.size() >= 2 && node.inputs.size() <= 4 && node.outputs.size() == 1;
+    if (op == "ConvIntegerScaleBias")
+        return node.inputs.size() >= 6 && node.inputs.size() <= 7 && node.present(4) && node.present(5) &&
+               node.outputs.size() == 1;
     if (op == "QLinearConv") {
         const std::string ap = node.str_attr("auto_pad", "NOTSET");
         bool all = node.inputs.size() >= 8 && node.inputs.size() <= 9;
@@ -969,6 +1032,8 @@ Result exec_dispatch(Env &env, const NodeIr &node)
     }
     if (node.op == "ConvInteger")
         return conv_integer(env, node);
+    if (node.op == "ConvIntegerScaleBias")
+        return conv_integer_scale_bias(env, node);
     if (node.op == "GatherBlockQuantized")
         return gather_block_quantized(env, node);
     if (node.op == "ArgMax")

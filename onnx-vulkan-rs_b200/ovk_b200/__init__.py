@@ -72,6 +72,8 @@ SIGNATURES = {
     "ovk_qconv_weight_destroy": (None, [_P, _P]),
     "ovk_conv_output_shape": (_I32, [_P, C.POINTER(ConvParams), C.POINTER(_I64), C.POINTER(_I64)]),
     "ovk_conv_integer": (_I32, [_P, _P, _P, _I32, C.POINTER(ConvParams), _I32, _I32, _P]),
+    "ovk_conv_integer_scale_bias": (_I32, [_P, _P, _P, _I32, C.POINTER(ConvParams), _I32, _I32, _P, _I32, _P, _I32,
+                                           _P, _I32, _U32, _P, _P]),
     "ovk_qlinear_conv": (_I32, [_P, _P, _P, _I32, C.POINTER(ConvParams), _I32, _I32, _P, _P, _I32, _I32, _P]),
     "ovk_requantize": (_I32, [_P, _P, _I64, _I64, _I64, _P, _P, _I32, _I32, _P]),
     "ovk_gather_block_quantized": (_I32, [_P, _P, _P, _I32, _P, _I64, _I64, _I64, _I64, _P, _I32, _I32, _I64, _P, _I32]),
@@ -272,6 +274,21 @@ class Context:
         p = self._conv_params(x, pads, strides, dilations)
         self.check(lib().ovk_conv_integer(self.h, w.h, _ptr(x), int(x.dtype == torch.int8), C.byref(p),
                                           int(x_zp), int(w_zp), _ptr(out)))
+        return out
+
+    def conv_integer_scale_bias(self, w: "QConvWeight", x, x_zp, w_zp, scale, bias, product=None, relu=False,
+                                range_slot=None, pads=(0, 0, 0, 0), strides=(1, 1), dilations=(1, 1)):
+        """scale, bias, product: float32 device tensors of 1 or C_out values."""
+        import torch
+        ho, wo = self.conv_output_shape(w, x, pads, strides, dilations)
+        out = torch.empty((x.shape[0], w.c_out, ho, wo), dtype=torch.float32, device=x.device)
+        p = self._conv_params(x, pads, strides, dilations)
+        step = lambda t: 0 if t is None or t.numel() == 1 else (1 if t.numel() == w.c_out else 2)
+        flags = (EPILOGUE_RELU if relu else 0) | (EPILOGUE_RANGE if range_slot is not None else 0)
+        self.check(lib().ovk_conv_integer_scale_bias(
+            self.h, w.h, _ptr(x), int(x.dtype == torch.int8), C.byref(p), int(x_zp), int(w_zp),
+            _ptr(scale), step(scale), _ptr(product), step(product), _ptr(bias), step(bias), flags,
+            _ptr(range_slot), _ptr(out)))
         return out
 
     def qlinear_conv(self, w: "QConvWeight", x, x_zp, w_zp, ratio, bias, y_zp, y_signed=False,

@@ -116,6 +116,33 @@ def test_scale_bias_row_broadcast_is_left_to_the_unfused_nodes(hl, env):
     assert err.value.status == 2
 
 
+@pytest.mark.parametrize("bias_shape,fused", [((1, 40, 1, 1), True), ((40, 1, 1), True), ((1, 1, 1, 20), False)])
+def test_conv_integer_scale_bias_node(hl, env, bias_shape, fused):
+    """crates/onnx-vulkan-core/tests/conv_integer_epilogue.rs:248-311: a bias per
+    channel fuses; one along the width has no channel step and stays four nodes."""
+    x = cases.lcg_bytes_fast(64 * 20 * 20, 1).reshape(1, 64, 20, 20)
+    w = cases.lcg_bytes_fast(40 * 64 * 9, 2).reshape(40, 64, 3, 3).view(np.int8)
+    bias = np.random.default_rng(3).uniform(-0.5, 0.5, bias_shape).astype(np.float32)
+    env.set("x", x)
+    env.set("w", w, initializer=True)
+    env.set("xz", np.array(131, dtype=np.uint8), initializer=True)
+    env.set("s", np.array(0.0123, dtype=np.float32))
+    env.set("s2", np.array(3.1e-3, dtype=np.float32), initializer=True)
+    env.set("bias", bias, initializer=True)
+    node = hl.Node("ConvIntegerScaleBias", ["x", "w", "xz", "", "s", "bias", "s2"], ["y"], kernel_shape=[3, 3],
+                   pads=[1, 1, 1, 1])
+    if not fused:
+        with pytest.raises(hl.OvkError) as err:
+            env.execute(node)
+        assert err.value.status == 2 and "not fused" in str(err.value)
+        return
+    env.execute(node)
+    acc = np.ascontiguousarray(np.moveaxis(orc.conv_integer(x, w, 131, 0, pads=(1, 1, 1, 1)), 1, -1))
+    want = orc.scale_bias_epilogue(acc, np.array([0.0123], np.float32), 0, bias.reshape(-1), 1,
+                                   product=np.array([3.1e-3], np.float32), product_step=0)
+    assert np.array_equal(env.host("y").view(np.uint32), np.moveaxis(want, -1, 1).view(np.uint32))
+
+
 def literal(name):
     return json.load(open(os.path.join(GOLDEN, "qlinear_literal_vectors.json")))[name]
 

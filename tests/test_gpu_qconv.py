@@ -7,6 +7,7 @@ import pytest
 
 import cases
 import oracle as orc
+import ovk_b200
 from gpu_util import ctx, dev, host
 
 pytestmark = pytest.mark.gpu
@@ -151,3 +152,87 @@ def test_tensor_core_geometries(c_in, c_out, h, w, k, dil, pads, xs):
     assert ctx().last_kernel.startswith("qconv_tc"), ctx().last_kernel
     want = orc.conv_integer(x, wt, x_zp, 0, dilations=(dil, dil), pads=pads)
     assert np.array_equal(host(got), want)
+
+
+def _fused_layer(c_in, c_out, hw, k, x_signed, w_signed):
+    x = cases.lcg_bytes_fast(c_in * hw[0] * hw[1], 1).reshape(1, c_in, *hw)
+    wt = cases.lcg_bytes_fast(c_out * c_in * k * k, 2).reshape(c_out, c_in, k, k)
+    rng = np.random.default_rng(c_in * 131 + c_out)
+    bias = rng.uniform(-0.5, 0.5, c_out).astype(np.float32)
+    scale = (np.abs(rng.uniform(-1e-4, 1e-4, c_out)) + 1e-5).astype(np.float32)
+    return (x.view(np.int8) if x_signed else x), (wt.view(np.int8) if w_signed else wt), scale, bias
+
+
+def _fused_oracle(acc, scale, bias, product=None, relu=False):
+    """The four unfused steps on channel-last data: Cast, Mul [by fl(scale*product)], Add, [Relu]."""
+    last = np.ascontiguousarray(np.moveaxis(acc, 1, -1))
+    out = orc.scale_bias_epilogue(last, scale, int(scale.size > 1), bias, int(bias.size > 1), product=product,
+                                  product_step=0, relu=relu)
+    return np.ascontiguousarray(np.moveaxis(out, -1, 1))
+
+
+@pytest.mark.parametrize("c_in,c_out,hw,k,stride,pad,ws,xs,per_channel_scale,kernel", [
+    (64, 40, (20, 20), 3, 1, 1, True, False, False, "conv_direct"),
+    (32, 24, (15, 15), 3, 2, 1, False, True, True, "conv_direct"),
+    (64, 48, (24, 24), 1, 1, 0, True, False, False, "qconv_tc"),
+    (64, 1, (24, 24), 1, 1, 0, True, False, False, ""),
+    (256, 32, (88, 88), 3, 1, 1, True, False, False, "qconv_tc"),
+    (4096, 16, (10, 13), 7, 1, 3, False, False, True, "conv_direct"),
+])
+def test_conv_integer_scale_bias_is_bit_identical_to_the_four_nodes(c_in, c_out, hw, k, stride, pad, ws, xs,
+                                                                    per_channel_scale, kernel):
+    """The layers of crates/onnx-vulkan-core/tests/conv_integer_epilogue.rs:248-372:
+    ConvInteger -> Cast -> Mul -> Add fused must answer bit for bit like the
+    four nodes, with a scalar scale that is the product of two scales or one
+    scale per channel, on both kernels."""
+    import torch
+    x, wt, scale, bias = _fused_layer(c_in, c_out, hw, k, xs, ws)
+    x_zp, w_zp = (-5 if xs else 131), (0 if ws else 121)
+    pads, strides = (pad,) * 4, (stride, stride)
+    wq = ctx().qconv_prepack(dev(wt))
+    if per_channel_scale:
+        s_dev, prod, prod_dev = dev(scale), None, None
+    else:
+        scale, prod = np.array([0.0123], dtype=np.float32), np.array([3.1e-3], dtype=np.float32)
+        s_dev, prod_dev = dev(scale), dev(prod)
+    got = ctx().conv_integer_scale_bias(wq, dev(x), x_zp, w_zp, s_dev, dev(bias), product=prod_dev, pads=pads,
+                                        strides=strides)
+    assert ctx().last_kernel.startswith(kernel), ctx().last_kernel
+    acc = ctx().conv_integer(wq, dev(x), x_zp, w_zp, pads=pads, strides=strides)
+    s_eff = (s_dev * prod_dev if prod_dev is not None else s_dev).reshape(1, -1, 1, 1)
+    unfused = acc.to(torch.float32) * s_eff + dev(bias).reshape(1, -1, 1, 1)
+    assert torch.equal(got.view(torch.int32), unfused.view(torch.int32))
+    want = _fused_oracle(orc.conv_integer(x, wt, x_zp, w_zp, strides=strides, pads=pads), scale, bias, product=prod)
+    assert np.array_equal(host(got).view(np.uint32), want.view(np.uint32))
+
+
+def test_conv_integer_scale_bias_relu_range_and_batch():
+    """Relu and the range slot of the DynamicQuantizeLinear that follows, batch 3, on both kernels."""
+    import torch
+    x = cases.lcg_bytes_fast(3 * 64 * 18 * 18, 7).reshape(3, 64, 18, 18)
+    wt = cases.lcg_bytes_fast(40 * 64 * 9, 9).reshape(40, 64, 3, 3).view(np.int8)
+    rng = np.random.default_rng(5)
+    scale = rng.uniform(1e-5, 1e-4, 40).astype(np.float32)
+    bias = rng.uniform(-0.5, 0.5, 40).astype(np.float32)
+    wq = ctx().qconv_prepack(dev(wt))
+    for strides, kernel in (((1, 1), "qconv_tc"), ((2, 2), "conv_direct")):
+        for relu in (False, True):
+            slot = torch.zeros(2, dtype=torch.int32, device="cuda")
+            got = ctx().conv_integer_scale_bias(wq, dev(x), 128, 0, dev(scale), dev(bias), relu=relu, range_slot=slot,
+                                                pads=(1, 1, 1, 1), strides=strides)
+            assert ctx().last_kernel.startswith(kernel), ctx().last_kernel
+            want = _fused_oracle(orc.conv_integer(x, wt, 128, 0, pads=(1, 1, 1, 1), strides=strides), scale, bias,
+                                 relu=relu)
+            assert np.array_equal(host(got).view(np.uint32), want.view(np.uint32))
+            lo_hi = host(slot).view(np.float32)
+            assert lo_hi[0] == max(-want.min(), 0.0) and lo_hi[1] == max(want.max(), 0.0)
+
+
+def test_conv_integer_scale_bias_refusals():
+    wt = np.zeros((8, 16, 3, 3), dtype=np.int8)
+    wq = ctx().qconv_prepack(dev(wt))
+    x = dev(np.zeros((1, 16, 6, 6), dtype=np.uint8))
+    ok = dev(np.ones(8, dtype=np.float32))
+    with pytest.raises(ovk_b200.OvkError) as err:
+        ctx().conv_integer_scale_bias(wq, x, 0, 0, dev(np.ones(6, dtype=np.float32)), ok)
+    assert "step" in str(err.value)

@@ -62,6 +62,9 @@ def test_other_operators_of_the_path(hl):
     assert hl.Node("MatMulInteger", ["a", "b", "az", "bz"], ["y"]).implemented
     assert hl.Node("MatMulIntegerScaleBias", ["a", "b", "az", "bz", "s", "bias"], ["y"], relu=1).implemented
     assert hl.Node("ConvInteger", ["x", "w", "xz"], ["y"]).implemented
+    assert hl.Node("ConvIntegerScaleBias", ["x", "w", "xz", "wz", "s", "bias"], ["y"]).implemented
+    assert hl.Node("ConvIntegerScaleBias", ["x", "w", "xz", "wz", "s", "bias", "s2"], ["y"], relu=1).implemented
+    assert not hl.Node("ConvIntegerScaleBias", ["x", "w", "xz", "wz", "s"], ["y"]).implemented
     assert hl.Node("QLinearMatMul", ["a", "as", "az", "b", "bs", "bz", "ys", "yz"], ["y"]).implemented
     assert not hl.Node("QLinearMatMul", ["a", "as", "az", "b"], ["y"]).implemented
     # everything outside the quantized matrix products stays with the host runtime
