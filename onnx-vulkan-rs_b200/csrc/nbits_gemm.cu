@@ -174,9 +174,9 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
     const int slabs_per_block = p.bs >= SLAB ? p.bs / SLAB : 1;
 
     // 512 threads x 128 registers fill the register file; control and unpack warps give
-    // registers back, the promotion warps take them (56*128 + 88*128 + 184*256 = 65536)
+    // registers back, the promotion warps take them (40*128 + 56*128 + 208*256 = 65536)
     if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
         // ------------------------------------------------------------ tokens by TMA
         if (lane == 0) {
@@ -275,7 +275,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         }
     }
     } else if (warp < 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         // ------------------------------------------------------------------- unpack
         const int r = (warp - 4) * 32 + lane;  // weight row of the tile
         const uint32_t row_off = uint32_t(r) * 128u;
@@ -329,7 +329,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
             }
         }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
         // ---------------------------------------------------------------- promotion
         const int q = warp & 3;            // tensor-memory lane quarter this warp may read
         const int half = (warp - 8) >> 2;  // which 128 of the 256 tokens
@@ -353,36 +353,56 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                 }
                 umma::tc_fence_after();
                 const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BT + half * 128);
+                // two reads of 64 columns: both loads of a pair are in flight together, and the
+                // accumulator goes back to the tensor core after two load latencies instead of four
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    uint32_t d[32];
-                    umma::tmem_ld_32x32(taddr + c * 32, d);
+                for (int c = 0; c < 2; c++) {
+                    uint32_t d0[32], d1[32];
+                    umma::tmem_ld_32x32(taddr + c * 64, d0);
+                    umma::tmem_ld_32x32(taddr + c * 64 + 32, d1);
                     umma::tmem_ld_wait();
-                    if (c == 3) {  // everything of this accumulator has been read: hand it back
+                    if (c == 1) {  // everything of this accumulator has been read: hand it back
                         umma::tc_fence_before();
                         __syncwarp();
                         if (lane == 0)
                             umma::mbar_arrive(&acc_empty[b]);
                     }
 #pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        acc[c * 32 + j] = fmaf(__uint_as_float(d[j]), scale, acc[c * 32 + j]);
+                    for (int j = 0; j < 32; j++) {
+                        acc[c * 64 + j] = fmaf(__uint_as_float(d0[j]), scale, acc[c * 64 + j]);
+                        acc[c * 64 + 32 + j] = fmaf(__uint_as_float(d1[j]), scale, acc[c * 64 + 32 + j]);
+                    }
                 }
                 scale = scale_next;
             }
             if (ok && n < p.N) {
+                // the MMA thread can run only two blocks ahead while this store lasts: a row
+                // pointer stepped by N and no bound test when all 128 token rows exist
+                const bool whole = m0 + 128 <= p.M;
                 if (p.y_f32) {
-                    float *y = static_cast<float *>(p.y);
+                    float *y = static_cast<float *>(p.y) + size_t(m0) * p.N + n;
+                    if (whole) {
 #pragma unroll
-                    for (int j = 0; j < 128; j++)
-                        if (m0 + j < p.M)
-                            y[size_t(m0 + j) * p.N + n] = acc[j];
+                        for (int j = 0; j < 128; j++, y += p.N)
+                            *y = acc[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 128; j++, y += p.N)
+                            if (m0 + j < p.M)
+                                *y = acc[j];
+                    }
                 } else {
-                    __half *y = static_cast<__half *>(p.y);
+                    __half *y = static_cast<__half *>(p.y) + size_t(m0) * p.N + n;
+                    if (whole) {
 #pragma unroll
-                    for (int j = 0; j < 128; j++)
-                        if (m0 + j < p.M)
-                            y[size_t(m0 + j) * p.N + n] = __float2half_rn(acc[j]);
+                        for (int j = 0; j < 128; j++, y += p.N)
+                            *y = __float2half_rn(acc[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 128; j++, y += p.N)
+                            if (m0 + j < p.M)
+                                *y = __float2half_rn(acc[j]);
+                    }
                 }
             }
         }
