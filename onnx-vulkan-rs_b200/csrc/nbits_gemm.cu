@@ -12,20 +12,35 @@
 // weights instead would round every weight and fail the 1e-3 tolerance at
 // large K.
 //
-// One CTA computes 128 weight columns (UMMA M) x 256 tokens (UMMA N), so every
-// unpacked weight tile is used by 256 tokens:
-//   warp 0      TMA: token tiles [256 x 64 k] fp16 into a 128B-swizzled ring,
-//               plus the packed nibbles of the same slab [128 rows x 32 bytes]
-//   warp 1      tcgen05.mma kind::f16, four K=16 steps per 64-k slab, one
-//               tensor-memory accumulator (256 columns) per quantization block,
-//               two in flight
-//   warps 4-7   unpack: thread r owns weight row r of the tile; 32 bytes of
-//               nibbles per slab -> 64 fp16 integers -> the swizzled operand stage
-//   warps 8-15  promotion: tcgen05.ld a block's partial sums (one weight column
-//               per thread, 128 tokens per warp), acc += partial * scale[n, block]
+// One CTA computes 128 weight columns (UMMA M) x up to 192 tokens (UMMA N):
+//   warp 0      TMA: token tiles [192 x 64 k] fp16 into a 128B-swizzled ring of
+//               eight stages, plus the packed nibbles of the same slab
+//               [128 rows x 32 bytes]
+//   warps 1-2   tcgen05.mma kind::f16, four K=16 steps per 64-k slab, the A
+//               operand read from tensor memory; one accumulator (192 columns)
+//               per quantization block, two in flight, one per issuing warp
+//   warps 4-11  unpack, two groups of four warps on alternate slabs: thread r
+//               owns weight row r of the tile; 32 bytes of nibbles per slab ->
+//               64 fp16 integers -> one tcgen05.st of 32 columns into the
+//               tensor-memory ring of four A stages
+//   warps 12-19 promotion: tcgen05.ld a block's partial sums (one weight column
+//               per thread, 96 tokens per warp), acc += partial * scale[n, block]
 //               in registers, final store of Y
+// The unpacked weights never touch shared memory: they go from registers to
+// tensor memory and the MMA takes its A operand from there.  At equal token
+// width that was 18 % faster than writing them to a swizzled shared-memory stage
+// (which the MMA then reads back at 32 bytes per clock next to 64 for the
+// tokens); the price is the tile width, since the A stages share the 512 columns
+// with the accumulators: 2 x 192 + 4 x 32.
+// What sets the pace is not the tensor core (384 clocks per slab at 192 tokens)
+// but the chains of long-latency steps each role runs per slab - barrier polls of
+// ~100 clocks, tcgen05.st, fences, commits: ~700 clocks for an unpack warp, ~800
+// for an issuing warp, measured with clock64 stamps.  Hence two issuing warps,
+// two unpack groups, a store that is announced one slab late, and one barrier
+// arrival per warp.  TMA itself needs ~500 clocks for the 28 KB of a slab
+// (57 bytes per clock per SM, 14 TB/s over the GPU), the next ceiling.
 // Weight columns sit on tensor-memory LANES so the scale is one scalar per thread.
-// The promotion warps hold 128 accumulators each: the register file is
+// The promotion warps hold 96 accumulators each: the register file is
 // re-divided between the warpgroups with setmaxnreg.
 #include <cstdlib>
 
@@ -35,13 +50,19 @@
 namespace {
 
 constexpr int BW = 128;    // weight columns per tile (UMMA M)
-constexpr int BT = 256;    // tokens per tile (UMMA N)
+constexpr int BT = 192;    // most tokens per tile (UMMA N)
+constexpr int HALF = BT / 2;  // token rows per promotion warp
 constexpr int SLAB = 64;   // k per stage: 128 bytes of fp16
-constexpr int STAGES = 4;
+constexpr int STAGES = 8;    // shared-memory ring: tokens + packed nibbles of a slab (TMA)
+constexpr int A_STAGES = 4;  // tensor-memory ring: unpacked weights of a slab
 constexpr int ACC_RING = 2;
-constexpr int A_BYTES = BW * 128, B_BYTES = BT * 128;
+constexpr int B_BYTES = BT * 128;
+constexpr int A_COLS = 32;                        // tensor-memory columns of one A stage: 64 k as fp16 pairs
+constexpr int A_BASE = ACC_RING * BT;             // the A stages follow the accumulators
+constexpr int TMEM_COLS = 512;
+static_assert(A_BASE + A_STAGES * A_COLS <= TMEM_COLS, "tensor memory: accumulators + A stages");
 constexpr int RAW_BYTES = BW * 32;  // packed nibbles of one slab: 32 bytes per weight row
-constexpr int THREADS = 16 * 32;  // four warpgroups: control, unpack, promotion x2
+constexpr int THREADS = 20 * 32;  // five warpgroups: control, unpack x2, promotion x2
 constexpr long long WAIT_CYCLES = 2000000000ll;
 
 struct GemmParams {
@@ -55,6 +76,7 @@ struct GemmParams {
     int slabs;             // k_pad / 64
     int bs;                // block size (32, 64, 128, 256)
     int m_tiles, n_tiles;
+    int bt;                // tokens per tile: a multiple of 32 up to BT, chosen per launch
     int y_f32;
     int *status;
 };
@@ -104,10 +126,6 @@ __device__ __forceinline__ uint4 ldg_nc16(const void *p)
     return v;
 }
 
-__device__ __forceinline__ void sts128(uint32_t addr, uint4 v)
-{
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
 
 // eight nibbles of a permuted word -> 8 fp16 integers (nibble - z), k ascending
 struct UnpackConsts {
@@ -135,13 +153,12 @@ __global__ void __launch_bounds__(THREADS, 1)
 nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_constant__ CUtensorMap tmRaw, GemmParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t *sW = smem;                       // STAGES x 16 KB: unpacked weights (UMMA A operand)
-    uint8_t *sX = smem + STAGES * A_BYTES;    // STAGES x 16 KB: tokens (UMMA B operand)
+    uint8_t *sX = smem;                       // STAGES x 24 KB: tokens (UMMA B operand)
     uint8_t *sR = sX + STAGES * B_BYTES;      // STAGES x 4 KB: packed nibbles as loaded
     uint64_t *bars = reinterpret_cast<uint64_t *>(sR + STAGES * RAW_BYTES);
     uint64_t *full_x = bars;                  // TMA landed
-    uint64_t *full_w = full_x + STAGES;       // 128 unpack threads arrived
-    uint64_t *empty = full_w + STAGES;        // MMAs of the stage finished
+    uint64_t *full_w = full_x + STAGES;       // [A_STAGES] the four unpack warps arrived
+    uint64_t *empty = full_w + A_STAGES;      // [STAGES] MMAs of the slab finished: its shared-memory AND its A stage are free
     uint64_t *acc_full = empty + STAGES;      // a block's partial sums are complete
     uint64_t *acc_empty = acc_full + ACC_RING;// all 8 promotion warps have read them
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + ACC_RING);
@@ -151,9 +168,10 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             umma::mbar_init(&full_x[s], 1);
-            umma::mbar_init(&full_w[s], 128);
             umma::mbar_init(&empty[s], 1);
         }
+        for (int s = 0; s < A_STAGES; s++)
+            umma::mbar_init(&full_w[s], 4);  // one arrival per unpack warp
         for (int b = 0; b < ACC_RING; b++) {
             umma::mbar_init(&acc_full[b], 1);
             umma::mbar_init(&acc_empty[b], 8);
@@ -161,7 +179,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         umma::fence_barrier_init();
     }
     if (warp == 1) {
-        umma::tmem_alloc(tmem_slot, ACC_RING * BT);
+        umma::tmem_alloc(tmem_slot, TMEM_COLS);
         umma::tmem_relinquish();
     }
     umma::tc_fence_before();
@@ -173,8 +191,8 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
     const int blocks_per_slab = p.bs >= SLAB ? 1 : SLAB / p.bs;  // 2 when block_size is 32
     const int slabs_per_block = p.bs >= SLAB ? p.bs / SLAB : 1;
 
-    // 512 threads x 128 registers fill the register file; control and unpack warps give
-    // registers back, the promotion warps take them (40*128 + 56*128 + 208*256 = 65536)
+    // 640 threads start with 96 registers each; control and unpack warps give registers back,
+    // the promotion warps take them (40*128 + 64*256 + 152*256 = 60416 of the 61440)
     if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
@@ -184,7 +202,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
             umma::prefetch_tmap(&tmRaw);
             int seq = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-                const int m0 = (tile % p.m_tiles) * BT;
+                const int m0 = (tile % p.m_tiles) * p.bt;
                 const int n0 = (tile / p.m_tiles) * BW;
                 for (int sl = 0; sl < p.slabs; sl++, seq++) {
                     const int s = seq % STAGES;
@@ -193,52 +211,71 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                         tile = total_tiles;
                         break;
                     }
-                    umma::mbar_expect_tx(&full_x[s], B_BYTES + RAW_BYTES);
+                    umma::mbar_expect_tx(&full_x[s], uint32_t(p.bt) * 128u + RAW_BYTES);
                     umma::tma_load_2d(sX + s * B_BYTES, &tmAct, &full_x[s], sl * SLAB, m0);
                     umma::tma_load_2d(sR + s * RAW_BYTES, &tmRaw, &full_x[s], sl * 32, n0);
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 2) {
         // ------------------------------------------------------------------ MMA issue
-        // One thread feeds the tensor core, so its loop is kept to a few instructions per
-        // MMA: descriptor high words are constants, low words advance by additions, block
-        // boundaries are tracked with counters instead of divisions.
-        if (lane == 0) {
-            const uint32_t idesc = umma::instr_desc(1 /*f32*/, 0 /*f16*/, 0 /*f16*/, BW, BT);
+        // A timeline of this loop showed ~800 clocks of its own instructions per slab (barrier
+        // polls, fences, commits: a chain of shared-memory and uniform-datapath latencies), of
+        // which the four MMAs are 80 - the tensor core, which needs 384, was waiting for its
+        // issuer.  So two warps issue, on two schedulers: warp 1 takes the even quantization
+        // blocks into accumulator 0, warp 2 the odd ones into accumulator 1.  Each commit covers
+        // the MMAs of its own thread, each accumulator has one writer, and the sums do not
+        // depend on how the two streams interleave.
+        // The whole warp runs the loop and stays converged; one elected lane issues the
+        // tcgen05 instructions, so loop state and descriptors are warp-uniform values.
+        const int me = warp - 1;
+        const int issuers = p.bs >= SLAB ? 2 : 1;  // smaller blocks: two per slab, one issuer
+        if (me < issuers) {
+            const bool leader = umma::elect_one();
+            const uint32_t idesc = umma::instr_desc(1 /*f32*/, 0 /*f16*/, 0 /*f16*/, BW, p.bt);
             const uint32_t desc_hi = ((1024u >> 4) & 0x3fffu) | (1u << 14) | (umma::LAYOUT_SW128 << 29);
-            const uint32_t w16 = umma::smem_u32(sW) >> 4, x16 = umma::smem_u32(sX) >> 4;
-            int s = 0, b = 0, slab_in_block = 0;
-            uint32_t ph = 0, acc_ph = 0;
+            const uint32_t x16 = umma::smem_u32(sX) >> 4;
+            int s = 0, a = 0, b = 0, slab_in_block = 0;
+            uint32_t a_ph = 0, acc_ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 for (int sl = 0; sl < p.slabs && ok; sl++) {
-                    if (!wait_bounded(&full_x[s], ph) || !wait_bounded(&full_w[s], ph)) {
-                        atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
-                        ok = false;
-                        break;
-                    }
-                    umma::tc_fence_after();
-                    const uint32_t w_lo = ((w16 + uint32_t(s) * (A_BYTES >> 4)) & 0x3fffu) | (1u << 16);
+                    const uint32_t a_t = tmem_base + uint32_t(A_BASE + a * A_COLS);  // 8 columns per K=16 step
                     const uint32_t x_lo = ((x16 + uint32_t(s) * (B_BYTES >> 4)) & 0x3fffu) | (1u << 16);
                     if (p.bs >= SLAB) {
                         const bool first = slab_in_block == 0;
-                        if (first) {  // the promotion warps must have drained this accumulator
-                            if (!wait_bounded(&acc_empty[b], acc_ph ^ 1)) {
-                                atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
+                        const bool last = ++slab_in_block == slabs_per_block;
+                        // The unpack warps arrive on full_w after they have seen the slab's TMA land
+                        // (tokens and nibbles complete the same barrier), so this one wait covers both
+                        // operands.  Both issuers wait for every slab, also the other one's: a parity
+                        // wait is only meaningful one phase behind its barrier, and a warp that ran
+                        // ahead over the slabs it skips could fall two behind.
+                        if (!wait_bounded(&full_w[a], a_ph)) {
+                            if (leader)
+                                atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
+                            ok = false;
+                            break;
+                        }
+                        if (b == me) {
+                            if (first && !wait_bounded(&acc_empty[b], acc_ph ^ 1)) {  // drained by the promotion warps
+                                if (leader)
+                                    atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
                                 ok = false;
                                 break;
                             }
                             umma::tc_fence_after();
+                            const uint32_t d = tmem_base + uint32_t(b * BT);
+                            if (leader) {
+                                umma::mma_f16_ts(d, a_t, x_lo, desc_hi, idesc, first ? 0u : 1u);
+                                umma::mma_f16_ts(d, a_t + 8, x_lo + 2, desc_hi, idesc, 1u);
+                                umma::mma_f16_ts(d, a_t + 16, x_lo + 4, desc_hi, idesc, 1u);
+                                umma::mma_f16_ts(d, a_t + 24, x_lo + 6, desc_hi, idesc, 1u);
+                                umma::mma_commit(&empty[s]);
+                                if (last)
+                                    umma::mma_commit(&acc_full[b]);
+                            }
                         }
-                        const uint32_t d = tmem_base + uint32_t(b * BT);
-                        umma::mma_f16_lohi(d, w_lo, desc_hi, x_lo, desc_hi, idesc, first ? 0u : 1u);
-                        umma::mma_f16_lohi(d, w_lo + 2, desc_hi, x_lo + 2, desc_hi, idesc, 1u);
-                        umma::mma_f16_lohi(d, w_lo + 4, desc_hi, x_lo + 4, desc_hi, idesc, 1u);
-                        umma::mma_f16_lohi(d, w_lo + 6, desc_hi, x_lo + 6, desc_hi, idesc, 1u);
-                        umma::mma_commit(&empty[s]);
-                        if (++slab_in_block == slabs_per_block) {
-                            umma::mma_commit(&acc_full[b]);
+                        if (last) {
                             slab_in_block = 0;
                             if (++b == ACC_RING) {
                                 b = 0;
@@ -247,100 +284,148 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                         }
                     } else {
                         // block_size 32: two blocks per slab, two K=16 steps each
+                        if (!wait_bounded(&full_w[a], a_ph)) {
+                            if (leader)
+                                atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
+                            ok = false;
+                            break;
+                        }
 #pragma unroll
                         for (int h = 0; h < 2; h++) {
                             if (!wait_bounded(&acc_empty[b], acc_ph ^ 1)) {
-                                atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
+                                if (leader)
+                                    atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
                                 ok = false;
                                 break;
                             }
                             umma::tc_fence_after();
                             const uint32_t d = tmem_base + uint32_t(b * BT);
-                            umma::mma_f16_lohi(d, w_lo + 4 * h, desc_hi, x_lo + 4 * h, desc_hi, idesc, 0u);
-                            umma::mma_f16_lohi(d, w_lo + 4 * h + 2, desc_hi, x_lo + 4 * h + 2, desc_hi, idesc, 1u);
-                            umma::mma_commit(&acc_full[b]);
+                            if (leader) {
+                                umma::mma_f16_ts(d, a_t + 16 * h, x_lo + 4 * h, desc_hi, idesc, 0u);
+                                umma::mma_f16_ts(d, a_t + 16 * h + 8, x_lo + 4 * h + 2, desc_hi, idesc, 1u);
+                                umma::mma_commit(&acc_full[b]);
+                            }
                             if (++b == ACC_RING) {
                                 b = 0;
                                 acc_ph ^= 1;
                             }
                         }
-                        umma::mma_commit(&empty[s]);
+                        if (leader)
+                            umma::mma_commit(&empty[s]);
                     }
-                    if (++s == STAGES) {
+                    if (++s == STAGES)
                         s = 0;
-                        ph ^= 1;
+                    if (++a == A_STAGES) {
+                        a = 0;
+                        a_ph ^= 1;
                     }
                 }
             }
         }
     }
-    } else if (warp < 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    } else if (warp < 12) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
         // ------------------------------------------------------------------- unpack
-        const int r = (warp - 4) * 32 + lane;  // weight row of the tile
-        const uint32_t row_off = uint32_t(r) * 128u;
-        const uint32_t swz = uint32_t(r & 7);
+        // two groups of four warps take alternate slabs (warps 4-7 the even ones, 8-11 the odd ones);
+        // within a group, warp w owns the 32 weight rows of tensor-memory lane quarter w % 4
+        const int group = (warp - 4) >> 2;
+        const int r = (warp & 3) * 32 + lane;  // weight row of the tile = tensor-memory lane
+        const uint32_t a_lane = tmem_base + (uint32_t((warp & 3) * 32) << 16) + uint32_t(A_BASE);
         UnpackConsts uc;
         asm volatile("mov.u32 %0, 0x000F000F;\n\tmov.u32 %1, 0x00F000F0;\n\tmov.u32 %2, 0x64006400;\n\tmov.u32 %3, 0x54005400;"
                      : "=r"(uc.m_lo), "=r"(uc.m_hi), "=r"(uc.k_lo), "=r"(uc.k_hi));
-        int seq = 0;
+        // One slab is ~120 instructions per thread, but as a chain (barrier poll, shared-memory
+        // load, unpack, tensor-memory store, wait for the store, arrive) it took ~650 clocks, and
+        // all four warps work on the same slab: that, not the tensor core, set the pace.  So the
+        // store of slab j is announced only after slab j + 1 has been unpacked - by then it has
+        // completed and the wait costs nothing - and block indices are shifts, not divisions.
+        const int bs_shift = 31 - __clz(p.bs);  // block sizes are powers of two
+        int seq = 0;       // global index of the current tile's first slab
+        int pending = -1;  // A stage stored to but not yet announced
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, seq += p.slabs) {
             const int n = (tile / p.m_tiles) * BW + r;
-            // zero points: 8 blocks per 64-bit load, fetched one group ahead
-            const uint2 *zrow = reinterpret_cast<const uint2 *>(p.zp_t + size_t(n) * p.zp_pitch);
-            uint2 zcur = zrow[0], znext = zcur;
-            int zgroup = 0;
-            for (int sl = 0; sl < p.slabs; sl++, seq++) {
-                const int blk0 = (sl * SLAB) / p.bs;
-                if ((blk0 >> 3) != zgroup) {
-                    zgroup = blk0 >> 3;
-                    zcur = znext;
-                }
-                if ((blk0 & 7) == 0 && (zgroup + 1) * 8 < p.zp_pitch && (sl * SLAB) % p.bs == 0)
-                    znext = zrow[zgroup + 1];
-                const uint64_t zbits = (uint64_t(zcur.y) << 32) | zcur.x;
-                const uint32_t z0 = uint32_t(zbits >> (8 * (blk0 & 7))) & 0xffu;
-                const uint32_t z1 = blocks_per_slab == 2 ? uint32_t(zbits >> (8 * ((blk0 + 1) & 7))) & 0xffu : z0;
+            // zero points: one byte per block, fetched one slab of this group ahead
+            const uint8_t *zrow = p.zp_t + size_t(n) * p.zp_pitch;
+            auto zero_points = [&](int sl) -> uint32_t {
+                const int blk = (sl * SLAB) >> bs_shift;
+                const uint32_t z0 = zrow[blk];
+                return z0 | (blocks_per_slab == 2 ? uint32_t(zrow[blk + 1]) << 8 : z0 << 8);
+            };
+            int sl = (seq ^ group) & 1;  // the first slab of this tile that this group takes
+            uint32_t z_next = sl < p.slabs ? zero_points(sl) : 0u;
+            for (; sl < p.slabs; sl += 2) {
+                const int g = seq + sl;
+                const uint32_t z0 = z_next & 0xffu, z1 = z_next >> 8;
+                if (sl + 2 < p.slabs)
+                    z_next = zero_points(sl + 2);
                 const uint32_t lo0 = z0 * 0x00010001u + 0x64006400u, hi0 = z0 * 0x00100010u + 0x54005400u;
                 const uint32_t lo1 = z1 * 0x00010001u + 0x64006400u, hi1 = z1 * 0x00100010u + 0x54005400u;
-                const int s = seq % STAGES;
-                // the nibbles have landed; the producer waited for the stage to be free before loading them
-                if (!wait_parked(&full_x[s], (seq / STAGES) & 1)) {
+                const int s = g % STAGES;
+                // the nibbles have landed
+                if (!wait_parked(&full_x[s], (g / STAGES) & 1)) {
                     if (lane == 0)
                         atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
                     ok = false;
                     break;
                 }
+                // announce this group's previous slab: its store was issued a barrier wait ago
+                if (pending >= 0) {
+                    umma::tmem_st_wait();
+                    umma::tc_fence_before();  // the store is ordered before the MMA warp's wait on full_w
+                    // one arrival per warp: 32 lanes arriving on the same barrier word are 32 serialised
+                    // shared-memory atomics
+                    __syncwarp();
+                    if (lane == 0)
+                        umma::mbar_arrive(&full_w[pending]);
+                }
                 const uint4 *raw = reinterpret_cast<const uint4 *>(sR + s * RAW_BYTES + r * 32);
                 const uint4 c0 = raw[0], c1 = raw[1];
-                const uint32_t base = umma::smem_u32(sW + s * A_BYTES) + row_off;
-                // chunk c (8 k) lands at 16-byte slot c ^ (row & 7): the 128B swizzle
-                sts128(base + ((0u ^ swz) << 4), unpack8(c0.x, lo0, hi0, uc));
-                sts128(base + ((1u ^ swz) << 4), unpack8(c0.y, lo0, hi0, uc));
-                sts128(base + ((2u ^ swz) << 4), unpack8(c0.z, lo0, hi0, uc));
-                sts128(base + ((3u ^ swz) << 4), unpack8(c0.w, lo0, hi0, uc));
-                sts128(base + ((4u ^ swz) << 4), unpack8(c1.x, lo1, hi1, uc));
-                sts128(base + ((5u ^ swz) << 4), unpack8(c1.y, lo1, hi1, uc));
-                sts128(base + ((6u ^ swz) << 4), unpack8(c1.z, lo1, hi1, uc));
-                sts128(base + ((7u ^ swz) << 4), unpack8(c1.w, lo1, hi1, uc));
-                umma::fence_proxy_async();  // generic-proxy stores -> visible to the tensor core
-                umma::mbar_arrive(&full_w[s]);
+                // 64 k of this row as 32 fp16 pairs, k ascending: the 32 columns of the A stage
+                uint32_t wv[32];
+                const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    const uint4 o = c < 4 ? unpack8(words[c], lo0, hi0, uc) : unpack8(words[c], lo1, hi1, uc);
+                    wv[4 * c] = o.x;
+                    wv[4 * c + 1] = o.y;
+                    wv[4 * c + 2] = o.z;
+                    wv[4 * c + 3] = o.w;
+                }
+                // the A stage this slab goes into was read by the MMAs of the slab A_STAGES earlier,
+                // whose completion is the `empty` barrier of that slab's shared-memory stage
+                if (g >= A_STAGES && !wait_parked(&empty[(g - A_STAGES) % STAGES], ((g - A_STAGES) / STAGES) & 1)) {
+                    if (lane == 0)
+                        atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
+                    ok = false;
+                    break;
+                }
+                umma::tc_fence_after();
+                pending = g % A_STAGES;
+                umma::tmem_st_32x32(a_lane + uint32_t(pending * A_COLS), wv);
             }
         }
+        if (pending >= 0) {
+            umma::tmem_st_wait();
+            umma::tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                umma::mbar_arrive(&full_w[pending]);
+        }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
         // ---------------------------------------------------------------- promotion
         const int q = warp & 3;            // tensor-memory lane quarter this warp may read
-        const int half = (warp - 8) >> 2;  // which 128 of the 256 tokens
+        const int half = (warp - 12) >> 2;  // which half of the tile's tokens
         int acc_seq = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int n = (tile / p.m_tiles) * BW + q * 32 + lane;
-            const int m0 = (tile % p.m_tiles) * BT + half * 128;
-            float acc[128];
+            const int m0 = (tile % p.m_tiles) * p.bt + half * HALF;
+            const int rows = min(p.M - m0, p.bt - half * HALF);  // token rows of this warp that exist (may be <= 0)
+            float acc[HALF];
 #pragma unroll
-            for (int j = 0; j < 128; j++)
+            for (int j = 0; j < HALF; j++)
                 acc[j] = 0.0f;
             float scale = p.scales_t[n];
             for (int blk = 0; blk < p.n_blocks; blk++, acc_seq++) {
@@ -352,55 +437,50 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                     ok = false;
                 }
                 umma::tc_fence_after();
-                const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BT + half * 128);
-                // two reads of 64 columns: both loads of a pair are in flight together, and the
-                // accumulator goes back to the tensor core after two load latencies instead of four
+                const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BT + half * HALF);
 #pragma unroll
-                for (int c = 0; c < 2; c++) {
-                    uint32_t d0[32], d1[32];
-                    umma::tmem_ld_32x32(taddr + c * 64, d0);
-                    umma::tmem_ld_32x32(taddr + c * 64 + 32, d1);
+                for (int c = 0; c < HALF / 32; c++) {
+                    uint32_t d[32];
+                    umma::tmem_ld_32x32(taddr + c * 32, d);
                     umma::tmem_ld_wait();
-                    if (c == 1) {  // everything of this accumulator has been read: hand it back
+                    if (c == HALF / 32 - 1) {  // everything of this accumulator has been read: hand it back
                         umma::tc_fence_before();
                         __syncwarp();
                         if (lane == 0)
                             umma::mbar_arrive(&acc_empty[b]);
                     }
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        acc[c * 64 + j] = fmaf(__uint_as_float(d0[j]), scale, acc[c * 64 + j]);
-                        acc[c * 64 + 32 + j] = fmaf(__uint_as_float(d1[j]), scale, acc[c * 64 + 32 + j]);
-                    }
+                    for (int j = 0; j < 32; j++)
+                        acc[c * 32 + j] = fmaf(__uint_as_float(d[j]), scale, acc[c * 32 + j]);
                 }
                 scale = scale_next;
             }
             if (ok && n < p.N) {
                 // the MMA thread can run only two blocks ahead while this store lasts: a row
-                // pointer stepped by N and no bound test when all 128 token rows exist
-                const bool whole = m0 + 128 <= p.M;
+                // pointer stepped by N and no bound test when all token rows of this warp exist
+                const bool whole = rows >= HALF;
                 if (p.y_f32) {
                     float *y = static_cast<float *>(p.y) + size_t(m0) * p.N + n;
                     if (whole) {
 #pragma unroll
-                        for (int j = 0; j < 128; j++, y += p.N)
+                        for (int j = 0; j < HALF; j++, y += p.N)
                             *y = acc[j];
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 128; j++, y += p.N)
-                            if (m0 + j < p.M)
+                        for (int j = 0; j < HALF; j++, y += p.N)
+                            if (j < rows)
                                 *y = acc[j];
                     }
                 } else {
                     __half *y = static_cast<__half *>(p.y) + size_t(m0) * p.N + n;
                     if (whole) {
 #pragma unroll
-                        for (int j = 0; j < 128; j++, y += p.N)
+                        for (int j = 0; j < HALF; j++, y += p.N)
                             *y = __float2half_rn(acc[j]);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 128; j++, y += p.N)
-                            if (m0 + j < p.M)
+                        for (int j = 0; j < HALF; j++, y += p.N)
+                            if (j < rows)
                                 *y = __float2half_rn(acc[j]);
                     }
                 }
@@ -410,7 +490,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
     umma::tc_fence_before();
     __syncthreads();
     if (warp == 1)
-        umma::tmem_dealloc(tmem_base, ACC_RING * BT);
+        umma::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 // ------------------------------------------------------------------- prepack
@@ -455,7 +535,7 @@ nbits_gemm_pack_kernel(const uint32_t *__restrict__ src_w, const void *__restric
     }
 }
 
-size_t gemm_smem() { return size_t(STAGES) * (A_BYTES + B_BYTES + RAW_BYTES) + 512; }
+size_t gemm_smem() { return size_t(STAGES) * (B_BYTES + RAW_BYTES) + 512; }
 
 }  // namespace
 
@@ -514,6 +594,28 @@ bool ovk_nbits_gemm_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int64
            aligned_to(w->scales, w->scales_dtype == OVK_FLOAT ? 4 : 2);
 }
 
+// Tokens per tile.  A slab of a tile costs about 350 + (tokens) clocks (measured: 700, 660 and
+// 620 for 192, 160 and 128 tokens), the grid runs ceil(tiles / SMs) rounds and the last round
+// is as long as a full one: a narrower tile that fills the last round better wins when the
+// product is smaller.
+int token_tile(int64_t m, int n_tiles, int sm_count)
+{
+    static const char *pin = getenv("OVK_NBITS_BT");
+    if (pin && atoi(pin) >= 96 && atoi(pin) <= BT && atoi(pin) % 32 == 0)
+        return atoi(pin);
+    int best = BT;
+    double best_cost = 0;
+    for (int bt = BT; bt >= 96; bt -= 32) {
+        const int64_t tiles = ceil_div64(m, bt) * n_tiles;
+        const double cost = double(ceil_div64(tiles, sm_count)) * (350 + bt);
+        if (bt == BT || cost < 0.97 * best_cost) {
+            best = bt;
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
 bool ovk_nbits_gemm_split_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w);
 int32_t ovk_nbits_gemm_split(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int64_t m, void *y, int32_t y_dtype);
 
@@ -529,9 +631,11 @@ int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, 
     int32_t rc = ovk_nbits_gemm_prepack(ctx, w);
     if (rc != OVK_OK)
         return rc;
+    const int n_tiles = int(w->gemm_n_pad / BW);
+    const int bt = token_tile(m, n_tiles, ctx->sm_count);
     CUtensorMap tmAct;
     if (!ovk_make_tmap_2d(&tmAct, a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, uint64_t(w->k), uint64_t(m), uint64_t(w->k) * 2,
-                          SLAB, BT, CU_TENSOR_MAP_SWIZZLE_128B))
+                          SLAB, uint32_t(bt), CU_TENSOR_MAP_SWIZZLE_128B))
         return ovk_fail(ctx, OVK_BACKEND, "MatMulNBits: cuTensorMapEncodeTiled failed for A");
     CUtensorMap tmRaw;
     if (!ovk_make_tmap_2d(&tmRaw, w->gemm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(w->gemm_k_pad / 2),
@@ -551,8 +655,9 @@ int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, 
     p.zp_pitch = int(w->gemm_zp_pitch);
     p.slabs = int(w->gemm_k_pad / SLAB);
     p.bs = int(w->block_size);
-    p.m_tiles = int(ceil_div64(m, BT));
-    p.n_tiles = int(w->gemm_n_pad / BW);
+    p.bt = bt;
+    p.m_tiles = int(ceil_div64(m, bt));
+    p.n_tiles = n_tiles;
     p.y_f32 = y_dtype == OVK_FLOAT;
     p.status = ctx->dev_status;
     OVK_CUDA(ctx, cudaFuncSetAttribute(nbits_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gemm_smem())));

@@ -128,7 +128,7 @@ nbits_gemm_split_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             umma::mbar_init(&full_x[s], 1);
-            umma::mbar_init(&full_w[s], UNPACK_THREADS);
+            umma::mbar_init(&full_w[s], UNPACK_THREADS / 32);  // one arrival per unpack warp
             umma::mbar_init(&empty[s], 1);
         }
         for (int b = 0; b < ACC_RING; b++) {
@@ -172,7 +172,10 @@ nbits_gemm_split_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        // the whole warp runs the loop and stays converged (loop state and descriptors are then
+        // warp-uniform values); one elected lane issues the tcgen05 instructions
+        {
+            const bool leader = umma::elect_one();
             const uint32_t idesc = umma::instr_desc(1 /*f32*/, 0 /*f16*/, 0 /*f16*/, BW, BT);
             const uint32_t desc_hi = ((1024u >> 4) & 0x3fffu) | (1u << 14) | (umma::LAYOUT_SW128 << 29);
             const uint32_t wh16 = (umma::smem_u32(sWh) >> 4) | (1u << 16), wl16 = (umma::smem_u32(sWl) >> 4) | (1u << 16);
@@ -182,34 +185,40 @@ nbits_gemm_split_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 if (!wait_bounded(&acc_empty[b], acc_ph ^ 1)) {
-                    atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
+                    if (leader)
+                        atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
                     break;
                 }
                 umma::tc_fence_after();
                 const uint32_t d = tmem_base + uint32_t(b * BT);
                 for (int sl = 0; sl < p.slabs; sl++) {
-                    if (!wait_bounded(&full_x[s], ph) || !wait_bounded(&full_w[s], ph)) {
-                        atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
+                    // the unpack warps arrive on full_w after they have seen the slab's TMA land
+                    // (tokens and nibbles complete the same barrier): one wait covers both operands
+                    if (!wait_bounded(&full_w[s], ph)) {
+                        if (leader)
+                            atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
                         ok = false;
                         break;
                     }
                     umma::tc_fence_after();
                     const uint32_t h_lo = wh16 + uint32_t(s) * (W_BYTES >> 4), l_lo = wl16 + uint32_t(s) * (W_BYTES >> 4);
                     const uint32_t x_lo = x16 + uint32_t(s) * (X_BYTES >> 4);
-                    umma::mma_f16_lohi(d, h_lo, desc_hi, x_lo, desc_hi, idesc, sl != 0);
-                    umma::mma_f16_lohi(d, l_lo, desc_hi, x_lo, desc_hi, idesc, 1u);
+                    if (leader) {
+                        umma::mma_f16_lohi(d, h_lo, desc_hi, x_lo, desc_hi, idesc, sl != 0);
+                        umma::mma_f16_lohi(d, l_lo, desc_hi, x_lo, desc_hi, idesc, 1u);
 #pragma unroll
-                    for (int j = 1; j < 4; j++) {
-                        umma::mma_f16_lohi(d, h_lo + 2u * j, desc_hi, x_lo + 2u * j, desc_hi, idesc, 1u);
-                        umma::mma_f16_lohi(d, l_lo + 2u * j, desc_hi, x_lo + 2u * j, desc_hi, idesc, 1u);
+                        for (int j = 1; j < 4; j++) {
+                            umma::mma_f16_lohi(d, h_lo + 2u * j, desc_hi, x_lo + 2u * j, desc_hi, idesc, 1u);
+                            umma::mma_f16_lohi(d, l_lo + 2u * j, desc_hi, x_lo + 2u * j, desc_hi, idesc, 1u);
+                        }
+                        umma::mma_commit(&empty[s]);
                     }
-                    umma::mma_commit(&empty[s]);
                     if (++s == STAGES) {
                         s = 0;
                         ph ^= 1;
                     }
                 }
-                if (ok)
+                if (ok && leader)
                     umma::mma_commit(&acc_full[b]);
                 if (++b == ACC_RING) {
                     b = 0;
@@ -271,7 +280,10 @@ nbits_gemm_split_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_
                     sts128(base_l + slot, lo);
                 }
                 umma::fence_proxy_async();  // generic-proxy stores -> visible to the tensor core
-                umma::mbar_arrive(&full_w[s]);
+                // one arrival per warp: 32 lanes arriving on one barrier word are 32 serialised atomics
+                __syncwarp();
+                if (lane == 0)
+                    umma::mbar_arrive(&full_w[s]);
                 if (++s == STAGES) {
                     s = 0;
                     ph ^= 1;
