@@ -18,7 +18,8 @@
 //               [128 rows x 32 bytes]
 //   warps 1-2   tcgen05.mma kind::f16, four K=16 steps per 64-k slab, the A
 //               operand read from tensor memory; one accumulator (192 columns)
-//               per quantization block, two in flight, one per issuing warp
+//               per quantization block, two to four in flight, blocks alternate
+//               between the two issuing warps
 //   warps 4-11  unpack, two groups of four warps on alternate slabs: thread r
 //               owns weight row r of the tile; 32 bytes of nibbles per slab ->
 //               64 fp16 integers -> one tcgen05.st of 32 columns into the
@@ -31,7 +32,8 @@
 // width that was 18 % faster than writing them to a swizzled shared-memory stage
 // (which the MMA then reads back at 32 bytes per clock next to 64 for the
 // tokens); the price is the tile width, since the A stages share the 512 columns
-// with the accumulators: 2 x 192 + 4 x 32.
+// with the accumulators: 384 + 4 x 32 (two accumulators of 192 tokens, three of
+// 128 or four of 96, by the tile width of the launch).
 // What sets the pace is not the tensor core (384 clocks per slab at 192 tokens)
 // but the chains of long-latency steps each role runs per slab - barrier polls of
 // ~100 clocks, tcgen05.st, fences, commits: ~700 clocks for an unpack warp, ~800
@@ -55,10 +57,10 @@ constexpr int HALF = BT / 2;  // token rows per promotion warp
 constexpr int SLAB = 64;   // k per stage: 128 bytes of fp16
 constexpr int STAGES = 8;    // shared-memory ring: tokens + packed nibbles of a slab (TMA)
 constexpr int A_STAGES = 4;  // tensor-memory ring: unpacked weights of a slab
-constexpr int ACC_RING = 2;
+constexpr int ACC_RING = 4;   // most accumulators in flight: 2 x 192, 3 x 128 or 4 x 96 columns
 constexpr int B_BYTES = BT * 128;
 constexpr int A_COLS = 32;                        // tensor-memory columns of one A stage: 64 k as fp16 pairs
-constexpr int A_BASE = ACC_RING * BT;             // the A stages follow the accumulators
+constexpr int A_BASE = 2 * BT;                    // the A stages follow the accumulators
 constexpr int TMEM_COLS = 512;
 static_assert(A_BASE + A_STAGES * A_COLS <= TMEM_COLS, "tensor memory: accumulators + A stages");
 constexpr int RAW_BYTES = BW * 32;  // packed nibbles of one slab: 32 bytes per weight row
@@ -77,6 +79,7 @@ struct GemmParams {
     int bs;                // block size (32, 64, 128, 256)
     int m_tiles, n_tiles;
     int bt;                // tokens per tile: a multiple of 32 up to BT, chosen per launch
+    int ring, acc_stride;  // accumulators in flight and their distance in tensor-memory columns
     int y_f32;
     int *status;
 };
@@ -223,9 +226,9 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         // polls, fences, commits: a chain of shared-memory and uniform-datapath latencies), of
         // which the four MMAs are 80 - the tensor core, which needs 384, was waiting for its
         // issuer.  So two warps issue, on two schedulers: warp 1 takes the even quantization
-        // blocks into accumulator 0, warp 2 the odd ones into accumulator 1.  Each commit covers
-        // the MMAs of its own thread, each accumulator has one writer, and the sums do not
-        // depend on how the two streams interleave.
+        // blocks, warp 2 the odd ones.  Each commit covers the MMAs of its own thread, a block's
+        // accumulator has one writer, and the sums do not depend on how the two streams
+        // interleave.
         // The whole warp runs the loop and stays converged; one elected lane issues the
         // tcgen05 instructions, so loop state and descriptors are warp-uniform values.
         const int me = warp - 1;
@@ -235,7 +238,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
             const uint32_t idesc = umma::instr_desc(1 /*f32*/, 0 /*f16*/, 0 /*f16*/, BW, p.bt);
             const uint32_t desc_hi = ((1024u >> 4) & 0x3fffu) | (1u << 14) | (umma::LAYOUT_SW128 << 29);
             const uint32_t x16 = umma::smem_u32(sX) >> 4;
-            int s = 0, a = 0, b = 0, slab_in_block = 0;
+            int s = 0, a = 0, b = 0, slab_in_block = 0, owner = 0;
             uint32_t a_ph = 0, acc_ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -256,7 +259,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                             ok = false;
                             break;
                         }
-                        if (b == me) {
+                        if (owner == me) {
                             if (first && !wait_bounded(&acc_empty[b], acc_ph ^ 1)) {  // drained by the promotion warps
                                 if (leader)
                                     atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
@@ -264,7 +267,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                                 break;
                             }
                             umma::tc_fence_after();
-                            const uint32_t d = tmem_base + uint32_t(b * BT);
+                            const uint32_t d = tmem_base + uint32_t(b * p.acc_stride);
                             if (leader) {
                                 umma::mma_f16_ts(d, a_t, x_lo, desc_hi, idesc, first ? 0u : 1u);
                                 umma::mma_f16_ts(d, a_t + 8, x_lo + 2, desc_hi, idesc, 1u);
@@ -277,7 +280,8 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                         }
                         if (last) {
                             slab_in_block = 0;
-                            if (++b == ACC_RING) {
+                            owner ^= issuers - 1;  // blocks alternate between the issuing warps
+                            if (++b == p.ring) {
                                 b = 0;
                                 acc_ph ^= 1;
                             }
@@ -299,13 +303,13 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                                 break;
                             }
                             umma::tc_fence_after();
-                            const uint32_t d = tmem_base + uint32_t(b * BT);
+                            const uint32_t d = tmem_base + uint32_t(b * p.acc_stride);
                             if (leader) {
                                 umma::mma_f16_ts(d, a_t + 16 * h, x_lo + 4 * h, desc_hi, idesc, 0u);
                                 umma::mma_f16_ts(d, a_t + 16 * h + 8, x_lo + 4 * h + 2, desc_hi, idesc, 1u);
                                 umma::mma_commit(&acc_full[b]);
                             }
-                            if (++b == ACC_RING) {
+                            if (++b == p.ring) {
                                 b = 0;
                                 acc_ph ^= 1;
                             }
@@ -417,33 +421,39 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         // ---------------------------------------------------------------- promotion
         const int q = warp & 3;            // tensor-memory lane quarter this warp may read
         const int half = (warp - 12) >> 2;  // which half of the tile's tokens
-        int acc_seq = 0;
+        // the tile's tokens are split between the two halves in whole 32-column chunks, and a warp
+        // reads only the chunks that hold tokens
+        const int hw = ((p.bt / 2 + 31) / 32) * 32;
+        const int nchunks = (min(hw, p.bt - half * hw) + 31) / 32;
+        int b = 0;
+        uint32_t acc_ph = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int n = (tile / p.m_tiles) * BW + q * 32 + lane;
-            const int m0 = (tile % p.m_tiles) * p.bt + half * HALF;
-            const int rows = min(p.M - m0, p.bt - half * HALF);  // token rows of this warp that exist (may be <= 0)
+            const int m0 = (tile % p.m_tiles) * p.bt + half * hw;
+            const int rows = min(p.M - m0, p.bt - half * hw);  // token rows of this warp that exist (may be <= 0)
             float acc[HALF];
 #pragma unroll
             for (int j = 0; j < HALF; j++)
                 acc[j] = 0.0f;
             float scale = p.scales_t[n];
-            for (int blk = 0; blk < p.n_blocks; blk++, acc_seq++) {
+            for (int blk = 0; blk < p.n_blocks; blk++) {
                 const float scale_next = blk + 1 < p.n_blocks ? p.scales_t[size_t(blk + 1) * p.n_pad + n] : 0.0f;
-                const int b = acc_seq % ACC_RING;
-                if (ok && !wait_parked(&acc_full[b], (acc_seq / ACC_RING) & 1)) {
+                if (ok && !wait_parked(&acc_full[b], acc_ph)) {
                     if (lane == 0)
                         atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
                     ok = false;
                 }
                 umma::tc_fence_after();
-                const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BT + half * HALF);
+                const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * p.acc_stride + half * hw);
 #pragma unroll
                 for (int c = 0; c < HALF / 32; c++) {
+                    if (c >= nchunks)
+                        break;
                     uint32_t d[32];
                     umma::tmem_ld_32x32(taddr + c * 32, d);
                     umma::tmem_ld_wait();
-                    if (c == HALF / 32 - 1) {  // everything of this accumulator has been read: hand it back
+                    if (c == nchunks - 1) {  // everything of this accumulator has been read: hand it back
                         umma::tc_fence_before();
                         __syncwarp();
                         if (lane == 0)
@@ -454,6 +464,10 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                         acc[c * 32 + j] = fmaf(__uint_as_float(d[j]), scale, acc[c * 32 + j]);
                 }
                 scale = scale_next;
+                if (++b == p.ring) {
+                    b = 0;
+                    acc_ph ^= 1;
+                }
             }
             if (ok && n < p.N) {
                 // the MMA thread can run only two blocks ahead while this store lasts: a row
@@ -594,10 +608,10 @@ bool ovk_nbits_gemm_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int64
            aligned_to(w->scales, w->scales_dtype == OVK_FLOAT ? 4 : 2);
 }
 
-// Tokens per tile.  A slab of a tile costs about 350 + (tokens) clocks (measured: 700, 660 and
-// 620 for 192, 160 and 128 tokens), the grid runs ceil(tiles / SMs) rounds and the last round
-// is as long as a full one: a narrower tile that fills the last round better wins when the
-// product is smaller.
+// Tokens per tile.  A slab of a tile costs about 285 + (tokens) in units of 1.4 clocks
+// (measured: 670, 575 and 535 clocks for 192, 128 and 96 tokens), the grid runs
+// ceil(tiles / SMs) rounds and the last round is as long as a full one: a narrower tile that
+// fills the last round better wins when the product is smaller.
 int token_tile(int64_t m, int n_tiles, int sm_count)
 {
     static const char *pin = getenv("OVK_NBITS_BT");
@@ -607,7 +621,7 @@ int token_tile(int64_t m, int n_tiles, int sm_count)
     double best_cost = 0;
     for (int bt = BT; bt >= 96; bt -= 32) {
         const int64_t tiles = ceil_div64(m, bt) * n_tiles;
-        const double cost = double(ceil_div64(tiles, sm_count)) * (350 + bt);
+        const double cost = double(ceil_div64(tiles, sm_count)) * (285 + bt);
         if (bt == BT || cost < 0.97 * best_cost) {
             best = bt;
             best_cost = cost;
@@ -656,6 +670,8 @@ int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, 
     p.slabs = int(w->gemm_k_pad / SLAB);
     p.bs = int(w->block_size);
     p.bt = bt;
+    p.ring = bt > 128 ? 2 : (bt > 96 ? 3 : 4);
+    p.acc_stride = bt > 128 ? BT : (bt > 96 ? 128 : 96);
     p.m_tiles = int(ceil_div64(m, bt));
     p.n_tiles = n_tiles;
     p.y_f32 = y_dtype == OVK_FLOAT;
