@@ -431,7 +431,8 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int n = (tile / p.m_tiles) * BW + q * 32 + lane;
             const int m0 = (tile % p.m_tiles) * p.bt + half * hw;
-            const int rows = min(p.M - m0, p.bt - half * hw);  // token rows of this warp that exist (may be <= 0)
+            // token rows of this warp that exist (may be <= 0): its share of the tile, cut at the end of M
+            const int rows = min(p.M - m0, min(hw, p.bt - half * hw));
             float acc[HALF];
 #pragma unroll
             for (int j = 0; j < HALF; j++)

@@ -137,6 +137,26 @@ def test_prefill_against_the_oracle(k, n, bs, m):
     assert_close(got, want, 1e-3, 1e-3, f"prefill {k}->{n} bs={bs} M={m}")
 
 
+@pytest.mark.parametrize("m,bs", [(90, 128), (150, 128), (190, 128), (200, 128), (385, 128), (200, 256)])
+def test_prefill_every_token_tile_width(m, bs):
+    """The per-block kernel picks 96, 128, 160 or 192 tokens per tile (with 4, 3,
+    2 and 2 accumulators in flight) from the token count and the number of
+    weight tiles; with 150 weight tiles on 148 SMs these token counts reach each
+    width, every one with a ragged last tile.  Sampled columns against the oracle."""
+    k, n = 512, 150 * 128
+    a, nib, zp, scale = cases.nbits_synthetic(5, m, k, n, bs)
+    got, kern = run_gpu(a, nib, zp, scale, k, n, bs)
+    assert kern == "nbits_gemm_tc"
+    cols = np.r_[0:130, 9000:9130, n - 130:n]  # the first, a middle and the last weight tiles
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib[cols], bs), scale[cols], orc.pack_zero_points(zp[cols]), k,
+                            cols.size, bs)
+    assert_close(got[:, cols], want, 1e-3, 1e-3, f"prefill M={m} bs={bs}, sampled columns")
+    # every output was written: the rows of one ragged token tile, all columns, against a float64 product
+    rows = np.r_[0:3, m - 3:m]
+    ref = cases.nbits_expected_f64(a[rows].astype(np.float32), nib, zp, scale.astype(np.float32), bs)
+    assert_close(got[rows], ref, 2e-3, 2e-3, "prefill, whole rows")
+
+
 def test_prefill_f32_output_and_missing_zero_points():
     a, nib, _, scale = cases.nbits_synthetic(6, 77, 640, 300, 32, with_zp=False)
     got, kern = run_gpu(a, nib, None, scale, 640, 300, 32, out_dtype=torch.float32)
