@@ -165,14 +165,28 @@ def test_prefill_f32_output_and_missing_zero_points():
     assert_close(got, want, 1e-4, 1e-4, "prefill f32 out")
 
 
-def test_prefill_small_blocks_with_f32_scales_keep_the_per_block_kernel():
-    """An f32 scale is not one fp16 number: the scale stays outside the MMA."""
-    a, nib, zp, scale = cases.nbits_synthetic(6, 40, 256, 200, 32)
+@pytest.mark.parametrize("m,k,n,bs", [(40, 256, 200, 32), (70, 192, 300, 64), (300, 1088, 260, 64)])
+def test_prefill_small_blocks_with_f32_scales_keep_the_per_block_kernel(m, k, n, bs):
+    """An f32 scale is not one fp16 number: the scale stays outside the MMA.
+    Blocks of 32 are two per 64-k slab (one issuing warp), blocks of 64 one per
+    slab (two issuing warps on alternate slabs, here with an odd slab count)."""
+    a, nib, zp, scale = cases.nbits_synthetic(6, m, k, n, bs)
     scale32 = (scale.astype(np.float32) * np.float32(1.0001)).astype(np.float32)
-    got, kern = run_gpu(a, nib, zp, scale32, 256, 200, 32)
+    got, kern = run_gpu(a, nib, zp, scale32, k, n, bs)
     assert kern == "nbits_gemm_tc"
-    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, 32), scale32, orc.pack_zero_points(zp), 256, 200, 32)
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, bs), scale32, orc.pack_zero_points(zp), k, n, bs)
     assert_close(got, want, 1e-3, 1e-3, "prefill, f32 scales")
+
+
+@pytest.mark.parametrize("m,k,n,bs", [(77, 1096, 300, 128), (200, 520, 140, 256)])
+def test_prefill_per_block_kernel_f32_output_and_ragged_k(m, k, n, bs):
+    """K that ends inside a quantization block, f32 output (atol = rtol = 1e-4)."""
+    a, nib, zp, scale = cases.nbits_synthetic(6, m, k, n, bs)
+    got, kern = run_gpu(a, nib, zp, scale, k, n, bs, out_dtype=torch.float32)
+    assert kern == "nbits_gemm_tc" and got.dtype == np.float32
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, bs), scale, orc.pack_zero_points(zp), k, n, bs,
+                            out_dtype=np.float32)
+    assert_close(got, want, 1e-4, 1e-4, "prefill f32 out, ragged K")
 
 
 def test_prefill_ragged_k_and_f32_activations_fall_back_to_the_general_kernel():
