@@ -93,18 +93,36 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, uint32_t tad
             if (lane == 0)
                 umma::mbar_arrive(hand_back);
         }
-        if (!row_ok || n0 + c0 >= p.N)
+        if (n0 + c0 >= p.N)  // the same for every lane of the warp
             continue;
         const int col0 = n0 + c0;
-#pragma unroll
-        for (int j = 0; j < 32; j++) {
-            const int col = col0 + j;
-            const int32_t cs = col < p.N ? p.colsum[col] : 0;
-            r[j] = r[j] - uint32_t(za) * uint32_t(cs) + row_term;
+        // Every thread of the warp needs the constants of the same 32 columns (a thread is a row).
+        // Lane l fetches those of column col0 + l - coalesced loads, all in flight together - and the
+        // loop below takes them by shuffle; a load per element from every thread made the
+        // dequantising store several times as long as the int32 one.  All lanes take part, rows past
+        // M included; only the stores are predicated.
+        const int col_l = col0 + lane;
+        const bool col_ok = col_l < p.N;
+        const int32_t cs_l = col_ok ? p.colsum[col_l] : 0;
+        float s_l = 0.0f, b_l = 0.0f;
+        int32_t ib_l = 0;
+        if (p.epi.mode == EPI_SCALE && col_ok) {
+            s_l = p.epi.scale[col_l * p.epi.scale_step];
+            if (p.epi.product)
+                s_l = __fmul_rn(s_l, p.epi.product[col_l * p.epi.product_step]);
+            b_l = p.epi.fbias[col_l * p.epi.bias_step];
+        } else if (p.epi.mode == EPI_REQUANT && col_ok) {
+            s_l = p.epi.ratio[col_l * p.epi.ratio_step];
+            ib_l = p.epi.ibias ? p.epi.ibias[col_l] : 0;
         }
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            r[j] = r[j] - uint32_t(za) * uint32_t(__shfl_sync(0xffffffffu, cs_l, j)) + row_term;
         if (p.epi.mode == EPI_RAW) {
             int32_t *o = static_cast<int32_t *>(p.out) + row * p.N + col0;
-            if (vec4 && col0 + 32 <= p.N) {
+            if (!row_ok) {
+                // a row past M: nothing to store (no divergent `continue`: the next tcgen05.ld is warp-wide)
+            } else if (vec4 && col0 + 32 <= p.N) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
                     *reinterpret_cast<int4 *>(o + j) = make_int4(r[j], r[j + 1], r[j + 2], r[j + 3]);
@@ -113,19 +131,22 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, uint32_t tad
                     o[j] = int32_t(r[j]);
             }
         } else if (p.epi.mode == EPI_SCALE) {
-            float *o = static_cast<float *>(p.out) + row * p.N + col0;
+            // fl(fl(float(acc) * s) + bias) [Relu], as epi_scale_value computes it
+            const bool relu = p.epi.flags & 1u;
             float f[32];
 #pragma unroll
             for (int j = 0; j < 32; j++) {
-                if (col0 + j < p.N) {
-                    f[j] = epi_scale_value(p.epi, col0 + j, float(int32_t(r[j])));
+                const float sj = __shfl_sync(0xffffffffu, s_l, j), bj = __shfl_sync(0xffffffffu, b_l, j);
+                const float z = __fadd_rn(__fmul_rn(float(int32_t(r[j])), sj), bj);
+                f[j] = relu ? fmaxf(z, 0.0f) : z;
+                if (row_ok && col0 + j < p.N) {
                     run_max = fmaxf(run_max, f[j]);
                     run_neg = fmaxf(run_neg, -f[j]);
-                } else {
-                    f[j] = 0.0f;
                 }
             }
-            if (vec4 && col0 + 32 <= p.N) {
+            float *o = static_cast<float *>(p.out) + row * p.N + col0;
+            if (!row_ok) {
+            } else if (vec4 && col0 + 32 <= p.N) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
                     *reinterpret_cast<float4 *>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
@@ -134,19 +155,26 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, uint32_t tad
                     o[j] = f[j];
             }
         } else {
+            // sat(rne(f32(acc + bias) * ratio) + y_zp), as epi_requant_value computes it
+            uint32_t q8[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const float ratio = __shfl_sync(0xffffffffu, s_l, j);
+                const int32_t acc = int32_t(r[j] + uint32_t(__shfl_sync(0xffffffffu, ib_l, j)));
+                const float rr = rintf(__fmul_rn(float(acc), ratio));
+                int32_t qv = int32_t(uint32_t(__float2int_rn(rr)) + uint32_t(p.epi.y_zp));
+                qv = p.epi.y_signed ? max(-128, min(127, qv)) : max(0, min(255, qv));
+                q8[j] = uint32_t(qv) & 0xffu;
+            }
             uint8_t *o = static_cast<uint8_t *>(p.out) + row * p.N + col0;
-            if (vec4 && col0 + 32 <= p.N) {
+            if (!row_ok) {
+            } else if (vec4 && col0 + 32 <= p.N) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    uint32_t w = 0;
-#pragma unroll
-                    for (int t = 0; t < 4; t++)
-                        w |= (uint32_t(epi_requant_value(p.epi, col0 + j + t, int32_t(r[j + t]))) & 0xffu) << (8 * t);
-                    *reinterpret_cast<uint32_t *>(o + j) = w;
-                }
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<uint32_t *>(o + j) = q8[j] | (q8[j + 1] << 8) | (q8[j + 2] << 16) | (q8[j + 3] << 24);
             } else {
                 for (int j = 0; j < 32 && col0 + j < p.N; j++)
-                    o[j] = uint8_t(epi_requant_value(p.epi, col0 + j, int32_t(r[j])));
+                    o[j] = uint8_t(q8[j]);
             }
         }
     }
