@@ -32,7 +32,18 @@ dql_range_kernel(const float *__restrict__ x, int64_t n, uint32_t *__restrict__ 
     if (vec_ok) {
         const int64_t n4 = n >> 2;
         const float4 *x4 = reinterpret_cast<const float4 *>(x);
-        for (int64_t i = tid; i < n4; i += stride) {
+        // four independent 16-byte loads in flight per thread, and a quarter of the blocks: every
+        // block ends with two atomics on the same two words, which is what a short input waits for
+        int64_t i = tid;
+        for (; i + 3 * stride < n4; i += 4 * stride) {
+            const float4 v0 = __ldg(x4 + i), v1 = __ldg(x4 + i + stride), v2 = __ldg(x4 + i + 2 * stride),
+                         v3 = __ldg(x4 + i + 3 * stride);
+            fold(v0.x, mn, mx); fold(v0.y, mn, mx); fold(v0.z, mn, mx); fold(v0.w, mn, mx);
+            fold(v1.x, mn, mx); fold(v1.y, mn, mx); fold(v1.z, mn, mx); fold(v1.w, mn, mx);
+            fold(v2.x, mn, mx); fold(v2.y, mn, mx); fold(v2.z, mn, mx); fold(v2.w, mn, mx);
+            fold(v3.x, mn, mx); fold(v3.y, mn, mx); fold(v3.z, mn, mx); fold(v3.w, mn, mx);
+        }
+        for (; i < n4; i += stride) {
             const float4 v = __ldg(x4 + i);
             fold(v.x, mn, mx);
             fold(v.y, mn, mx);
@@ -117,11 +128,21 @@ dql_quantize_kernel(const float *__restrict__ x, int64_t n, uint32_t *__restrict
         const int64_t n4 = n >> 2;
         const float4 *x4 = reinterpret_cast<const float4 *>(x);
         uint32_t *y4 = reinterpret_cast<uint32_t *>(y);
-        for (int64_t i = tid; i < n4; i += stride) {
-            const float4 v = __ldg(x4 + i);
-            y4[i] = quant1(v.x, scale, zp) | (quant1(v.y, scale, zp) << 8) |
-                    (quant1(v.z, scale, zp) << 16) | (quant1(v.w, scale, zp) << 24);
+        auto pack = [&](const float4 &v) {
+            return quant1(v.x, scale, zp) | (quant1(v.y, scale, zp) << 8) | (quant1(v.z, scale, zp) << 16) |
+                   (quant1(v.w, scale, zp) << 24);
+        };
+        int64_t i = tid;
+        for (; i + 3 * stride < n4; i += 4 * stride) {
+            const float4 v0 = __ldg(x4 + i), v1 = __ldg(x4 + i + stride), v2 = __ldg(x4 + i + 2 * stride),
+                         v3 = __ldg(x4 + i + 3 * stride);
+            y4[i] = pack(v0);
+            y4[i + stride] = pack(v1);
+            y4[i + 2 * stride] = pack(v2);
+            y4[i + 3 * stride] = pack(v3);
         }
+        for (; i < n4; i += stride)
+            y4[i] = pack(__ldg(x4 + i));
         for (int64_t i = (n4 << 2) + tid; i < n; i += stride)
             y[i] = uint8_t(quant1(x[i], scale, zp));
     } else {
@@ -156,11 +177,11 @@ extern "C" int32_t ovk_dynamic_quantize(ovk_ctx *ctx, const float *x, int64_t n,
     OVK_REQUIRE(ctx, aligned_to(x, 4), "DynamicQuantizeLinear: x is not 4-byte aligned");
     const int vec_ok = aligned_to(x, 16) && aligned_to(y, 4);
     const int64_t work = vec_ok ? (n + 3) / 4 : n;
-    // pass 1: a few resident blocks per SM, grid-stride
-    unsigned blocks1 = unsigned(std::min<int64_t>(ceil_div64(work, 256), int64_t(ctx->sm_count) * 8));
+    // both passes: grid-stride, four vectors per thread and trip, at most four blocks per SM
+    unsigned blocks1 = unsigned(std::min<int64_t>(ceil_div64(work, 1024), int64_t(ctx->sm_count) * 4));
     OVK_CUDA(ctx, ovk_launch_pdl(dql_range_kernel, dim3(blocks1), dim3(256), 0, ctx->stream, x, n, ctx->range_slot, vec_ok));
     OVK_LAUNCHED(ctx, "dql_range");
-    unsigned blocks2 = unsigned(std::min<int64_t>(ceil_div64(work, 256), int64_t(ctx->sm_count) * 8));
+    unsigned blocks2 = blocks1;
     OVK_CUDA(ctx, ovk_launch_pdl(dql_quantize_kernel, dim3(blocks2), dim3(256), 0, ctx->stream, x, n, ctx->range_slot, y_scale,
                                  y_zero_point, y, vec_ok));
     OVK_LAUNCHED(ctx, "dql_quantize");
