@@ -139,7 +139,7 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         }
         for (int b = 0; b < nacc; b++) {
             umma::mbar_init(&acc_full[b], 1);
-            umma::mbar_init(&acc_empty[b], EPI_WARPS);
+            umma::mbar_init(&acc_empty[b], EPI_WARPS / min(EPI_WARPS / 4, nacc));  // the warps of one tile group
         }
         umma::mbar_init(w_full, 1);
         umma::fence_barrier_init();
@@ -291,11 +291,18 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         }
     } else if (warp < 2 + EPI_WARPS) {
         // ---------------------------------------------------------------- epilogue
-        // warp w reads lane quarter w % 4 (a hardware rule); the four warps of a
-        // quarter take the 16-channel column groups round robin
+        // warp w reads lane quarter w % 4 (a hardware rule).  The four warps of a quarter work on
+        // DIFFERENT tiles (tile sequence number mod 4, as far as there are accumulators in flight):
+        // a tile's epilogue is a chain of long-latency steps (barrier poll, tcgen05.ld, wait,
+        // arrive, stores) that took ~2000 clocks however little each warp had to do, and with all
+        // sixteen warps on the same tile that chain was the kernel's pace.  What is left of the
+        // four then shares a tile's 16-channel column groups round robin.
         const int q = warp & 3;
         const int sub = (warp - 2) >> 2;
         constexpr int SUBS = EPI_WARPS / 4;
+        const int G = min(SUBS, nacc);  // tile groups (a power of two)
+        const int CS = SUBS / G;        // warps of a quarter that share a tile
+        const int tg = sub & (G - 1), cs = sub / G;
         int tile_seq = 0;
         bool ok = true;
         const int64_t plane = int64_t(p.h_out) * p.w_out;
@@ -304,6 +311,8 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         const int32_t round_fix = p.epi.y_zp - 0x4B400000;
         float run_max = 0.0f, run_neg = 0.0f;  // extrema of the scale-and-bias store, folded once at the end
         for (int tile = blockIdx.x; tile < p.m_tiles; tile += gridDim.x, tile_seq++) {
+            if ((tile_seq & (G - 1)) != tg)
+                continue;  // another group's tile
             const int b = tile_seq & (nacc - 1);
             if (ok && !wait_bounded(&acc_full[b], (tile_seq / nacc) & 1)) {
                 if (lane == 0)
@@ -322,7 +331,7 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
             const int64_t o_base = int64_t(img) * p.c_out * plane + int64_t(oh) * p.w_out + ow;
             // this warp's last column group: after reading it the accumulator is handed back
             int last_c0 = -1;
-            for (int c0 = sub * 16; c0 < p.co_pad; c0 += SUBS * 16)
+            for (int c0 = cs * 16; c0 < p.co_pad; c0 += CS * 16)
                 last_c0 = c0;
             if (last_c0 < 0) {
                 umma::tc_fence_before();
@@ -330,7 +339,7 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                 if (lane == 0)
                     umma::mbar_arrive(&acc_empty[b]);
             }
-            for (int c0 = sub * 16; c0 < p.co_pad; c0 += SUBS * 16) {
+            for (int c0 = cs * 16; c0 < p.co_pad; c0 += CS * 16) {
                 uint32_t r[16];
                 umma::tmem_ld_32x16(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * p.co_pad + c0), r);
                 umma::tmem_ld_wait();
