@@ -31,7 +31,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 128;  // bytes of K per stage = one 128-byte swizzle row
 constexpr int A_BYTES = BM * BK;
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;  // TMA, issuer 0, four epilogue warps, issuer 1
 constexpr long long WAIT_CYCLES = 2000000000ll;  // about a second
 
 struct TcParams {
@@ -199,7 +199,8 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     uint64_t *empty = full + STAGES;
     uint64_t *acc_full = empty + STAGES;   // [2] a tile's accumulator is complete
     uint64_t *acc_empty = acc_full + 2;    // [2] the four epilogue warps have read it
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    uint64_t *started = acc_empty + 2;     // [2] the tile's first (overwriting) MMA has been issued
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(started + 2);
 
     OVK_PDL_LAUNCH_DEPENDENTS();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -213,8 +214,9 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             umma::mbar_init(&empty[s], 1);
         }
         for (int b = 0; b < 2; b++) {
-            umma::mbar_init(&acc_full[b], 1);
+            umma::mbar_init(&acc_full[b], 2);  // one arrival per issuing thread
             umma::mbar_init(&acc_empty[b], 4);
+            umma::mbar_init(&started[b], 1);
         }
         umma::fence_barrier_init();
     }
@@ -252,16 +254,26 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 6) {
+        // Two issuing threads, on two schedulers, take alternate K stages of every tile.  One
+        // thread's round per stage (barrier poll, fence, four MMAs, commit) is a chain of several
+        // hundred clocks; with narrow tiles (four 48- or 64-clock MMAs per stage) that chain is
+        // longer than the MMAs, and a single issuer set the pace of the short-K products (T=1000,
+        // K=4096, N=1024: 12.9 -> 10.9 us).  The 256-wide tiles, whose MMAs outlast the chain,
+        // measure the same with one issuer or two.  Integer accumulation is exact and commutative, so the order in
+        // which the two streams reach the tensor core does not change a bit of the result; the
+        // one MMA that must come first is the tile's overwriting one, and the other thread waits
+        // for `started` before its first MMA of the tile.
         if (lane == 0) {
+            const int me = warp == 1 ? 0 : 1;
             const uint32_t idesc = umma::instr_desc(2, p.a_signed ? 1 : 0, p.b_signed ? 1 : 0, BM, BN);
             // descriptor high words are constants and low words advance by additions, so
-            // the one issuing thread spends a few instructions per MMA
+            // an issuing thread spends a few instructions per MMA
             const uint32_t desc_hi = ((1024u >> 4) & 0x3fffu) | (1u << 14) | (umma::LAYOUT_SW128 << 29);
             const uint32_t a16 = umma::smem_u32(sA) >> 4, b16 = umma::smem_u32(sB) >> 4;
             bool ok = true;
             int s = 0, b = 0;
-            uint32_t ph = 0, acc_ph = 0;
+            uint32_t ph = 0, acc_ph = 0, turn = 0;  // turn: whose stage the next one is
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 if (!wait_bounded(&acc_empty[b], acc_ph ^ 1)) {
                     atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
@@ -269,27 +281,42 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 }
                 umma::tc_fence_after();
                 const uint32_t d = tmem_base + uint32_t(b * BN);
-                for (int kb = 0; kb < p.num_kb; kb++) {
-                    if (!wait_bounded(&full[s], ph)) {
-                        atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
-                        ok = false;
-                        break;
+                bool issued = false;
+                for (int kb = 0; kb < p.num_kb; kb++, turn ^= 1) {
+                    if (turn == uint32_t(me)) {
+                        if (!wait_bounded(&full[s], ph)) {
+                            atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
+                            ok = false;
+                            break;
+                        }
+                        if (kb != 0 && !issued && !wait_bounded(&started[b], acc_ph)) {
+                            atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
+                            ok = false;
+                            break;
+                        }
+                        umma::tc_fence_after();
+                        const uint32_t a_lo = ((a16 + uint32_t(s) * (A_BYTES >> 4)) & 0x3fffu) | (1u << 16);
+                        const uint32_t b_lo = ((b16 + uint32_t(s) * (B_BYTES >> 4)) & 0x3fffu) | (1u << 16);
+                        umma::mma_i8_lohi(d, a_lo, desc_hi, b_lo, desc_hi, idesc, kb != 0);
+                        if (kb == 0)
+                            umma::mbar_arrive(&started[b]);  // issued: the tensor core takes MMAs in issue order
+                        umma::mma_i8_lohi(d, a_lo + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
+                        umma::mma_i8_lohi(d, a_lo + 4, desc_hi, b_lo + 4, desc_hi, idesc, 1u);
+                        umma::mma_i8_lohi(d, a_lo + 6, desc_hi, b_lo + 6, desc_hi, idesc, 1u);
+                        umma::mma_commit(&empty[s]);
+                        issued = true;
                     }
-                    umma::tc_fence_after();
-                    const uint32_t a_lo = ((a16 + uint32_t(s) * (A_BYTES >> 4)) & 0x3fffu) | (1u << 16);
-                    const uint32_t b_lo = ((b16 + uint32_t(s) * (B_BYTES >> 4)) & 0x3fffu) | (1u << 16);
-                    umma::mma_i8_lohi(d, a_lo, desc_hi, b_lo, desc_hi, idesc, kb != 0);
-                    umma::mma_i8_lohi(d, a_lo + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
-                    umma::mma_i8_lohi(d, a_lo + 4, desc_hi, b_lo + 4, desc_hi, idesc, 1u);
-                    umma::mma_i8_lohi(d, a_lo + 6, desc_hi, b_lo + 6, desc_hi, idesc, 1u);
-                    umma::mma_commit(&empty[s]);
                     if (++s == STAGES) {
                         s = 0;
                         ph ^= 1;
                     }
                 }
-                if (ok)
-                    umma::mma_commit(&acc_full[b]);
+                if (ok) {
+                    if (issued)
+                        umma::mma_commit(&acc_full[b]);  // arrives when this thread's MMAs have finished
+                    else
+                        umma::mbar_arrive(&acc_full[b]);  // a tile of one stage: nothing of this thread's to wait for
+                }
                 if (++b == 2) {
                     b = 0;
                     acc_ph ^= 1;
@@ -347,7 +374,7 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 //   warps 2-9   epilogue: warps 2-5 the upper 128 rows, 6-9 the lower
 constexpr int BM2 = 256, BN2 = 256, BK2 = 64, STAGES2 = 6;
 constexpr int A2_BYTES = BM2 * BK2, B2_BYTES = BN2 * BK2;
-constexpr int THREADS2 = 10 * 32;
+constexpr int THREADS2 = 11 * 32;  // TMA, issuer 0, eight epilogue warps, issuer 1
 constexpr size_t SMEM2 = size_t(STAGES2) * (A2_BYTES + B2_BYTES) + 1024 + 256;
 
 __global__ void __launch_bounds__(THREADS2, 1)
@@ -360,7 +387,8 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint64_t *empty = full + STAGES2;
     uint64_t *acc_full = empty + STAGES2;  // the tile's accumulators are complete
     uint64_t *acc_empty = acc_full + 1;    // the eight epilogue warps have read them
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 1);
+    uint64_t *started = acc_empty + 1;     // the tile's first (overwriting) MMAs have been issued
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(started + 1);
 
     OVK_PDL_LAUNCH_DEPENDENTS();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -373,8 +401,9 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             umma::mbar_init(&full[s], 1);
             umma::mbar_init(&empty[s], 1);
         }
-        umma::mbar_init(acc_full, 1);
+        umma::mbar_init(acc_full, 2);  // one arrival per issuing thread
         umma::mbar_init(acc_empty, 8);
+        umma::mbar_init(started, 1);
         umma::fence_barrier_init();
     }
     if (warp == 1) {
@@ -411,8 +440,10 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 10) {
+        // two issuing threads on alternate K stages, as in mmi_tc_kernel
         if (lane == 0) {
+            const int me = warp == 1 ? 0 : 1;
             const uint32_t idesc = umma::instr_desc(2, p.a_signed ? 1 : 0, p.b_signed ? 1 : 0, 128, BN2);
             // 64-byte rows, 64B swizzle: 512 bytes between 8-row groups
             const uint32_t desc_hi = ((512u >> 4) & 0x3fffu) | (1u << 14) | (umma::LAYOUT_SW64 << 29);
@@ -420,35 +451,50 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             constexpr uint32_t HALF = (128 * BK2) >> 4;  // the lower 128 rows of a stage of A
             bool ok = true;
             int s = 0;
-            uint32_t ph = 0, acc_ph = 0;
+            uint32_t ph = 0, acc_ph = 0, turn = 0;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 if (!wait_bounded(acc_empty, acc_ph ^ 1)) {
                     atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
                     break;
                 }
                 umma::tc_fence_after();
-                for (int kb = 0; kb < num_kb; kb++) {
-                    if (!wait_bounded(&full[s], ph)) {
-                        atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
-                        ok = false;
-                        break;
+                bool issued = false;
+                for (int kb = 0; kb < num_kb; kb++, turn ^= 1) {
+                    if (turn == uint32_t(me)) {
+                        if (!wait_bounded(&full[s], ph)) {
+                            atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
+                            ok = false;
+                            break;
+                        }
+                        if (kb != 0 && !issued && !wait_bounded(started, acc_ph)) {
+                            atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
+                            ok = false;
+                            break;
+                        }
+                        umma::tc_fence_after();
+                        const uint32_t a_lo = a16 + uint32_t(s) * (A2_BYTES >> 4);
+                        const uint32_t b_lo = b16 + uint32_t(s) * (B2_BYTES >> 4);
+                        const uint32_t acc = kb != 0;
+                        umma::mma_i8_lohi(tmem_base, a_lo, desc_hi, b_lo, desc_hi, idesc, acc);
+                        umma::mma_i8_lohi(tmem_base + BN2, a_lo + HALF, desc_hi, b_lo, desc_hi, idesc, acc);
+                        if (kb == 0)
+                            umma::mbar_arrive(started);  // both overwriting MMAs are in the tensor core's queue
+                        umma::mma_i8_lohi(tmem_base, a_lo + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
+                        umma::mma_i8_lohi(tmem_base + BN2, a_lo + HALF + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
+                        umma::mma_commit(&empty[s]);
+                        issued = true;
                     }
-                    umma::tc_fence_after();
-                    const uint32_t a_lo = a16 + uint32_t(s) * (A2_BYTES >> 4);
-                    const uint32_t b_lo = b16 + uint32_t(s) * (B2_BYTES >> 4);
-                    const uint32_t acc = kb != 0;
-                    umma::mma_i8_lohi(tmem_base, a_lo, desc_hi, b_lo, desc_hi, idesc, acc);
-                    umma::mma_i8_lohi(tmem_base + BN2, a_lo + HALF, desc_hi, b_lo, desc_hi, idesc, acc);
-                    umma::mma_i8_lohi(tmem_base, a_lo + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
-                    umma::mma_i8_lohi(tmem_base + BN2, a_lo + HALF + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
-                    umma::mma_commit(&empty[s]);
                     if (++s == STAGES2) {
                         s = 0;
                         ph ^= 1;
                     }
                 }
-                if (ok)
-                    umma::mma_commit(acc_full);
+                if (ok) {
+                    if (issued)
+                        umma::mma_commit(acc_full);
+                    else
+                        umma::mbar_arrive(acc_full);
+                }
                 acc_ph ^= 1;
             }
         }
