@@ -77,10 +77,22 @@ OVK_API const char *ovk_last_kernel(const ovk_ctx *ctx);
 OVK_API uint64_t ovk_launch_count(const ovk_ctx *ctx);
 /* The cudaStream_t operator calls are enqueued on. */
 OVK_API void *ovk_stream(const ovk_ctx *ctx);
+/* Bytes of the context's grow-on-demand device workspace (row sums, the padded
+ * channels-last image of a convolution, split-K partial sums); 0 until an
+ * operator needed one.  A diagnostic without a counterpart in the reference,
+ * whose buffers come from a recycling pool (crates/vk-compute/src/buffer.rs:303). */
+OVK_API size_t ovk_workspace_bytes(const ovk_ctx *ctx);
 
 /* flush (stream.rs:702): wait for everything enqueued; also reports a
  * device-side wait that timed out (OVK_TIMEOUT). */
 OVK_API int32_t ovk_flush(ovk_ctx *ctx);
+/* Exercises the failure report without a failure: enqueues a one-thread kernel
+ * that waits, with a limit of 1000 polls, on a barrier nothing arrives at, and
+ * records that the wait ran out.  The next ovk_flush returns OVK_TIMEOUT with
+ * a message naming the self-test; the context stays usable.  (The reference
+ * has no device-side waits; its failure report is the Result of flush,
+ * crates/vk-compute/src/stream.rs:702.) */
+OVK_API int32_t ovk_selftest_device_timeout(ovk_ctx *ctx);
 /* create_storage_buffer (buffer.rs:239) / recycle_storage_buffer (:303) */
 OVK_API int32_t ovk_alloc(ovk_ctx *ctx, size_t bytes, void **dptr);
 OVK_API int32_t ovk_free(ovk_ctx *ctx, void *dptr);
@@ -129,6 +141,57 @@ OVK_API int32_t ovk_matmul_nbits_group(ovk_ctx *ctx, int32_t count,
                                        const ovk_nbits_weight *const *weights, const void *a,
                                        int32_t a_dtype, int64_t m, void *const *ys, int32_t y_dtype);
 
+/* ------------------------------------- several GPUs of one box (no counterpart)
+ * The reference drives one device per process (crates/vk-compute/src/context.rs
+ * :685-711) and has no exchange step; these verbs are what the column-split
+ * MatMulNBits prefill needs from a host that runs one process per GPU.
+ *
+ * Buffers that other ranks write into - every rank's copy of Y, and one flag
+ * block per rank - come from ovk_comm_alloc (cudaMalloc, zero filled).
+ * ovk_comm_export turns one into a 64-byte handle the host hands to the other
+ * processes over any channel it has (the role an ncclUniqueId plays);
+ * ovk_comm_import maps a peer's buffer here and ovk_comm_release unmaps it.
+ * ovk_comm_init then makes the context rank `rank` of `world` (at most 8):
+ * flag_blocks[r] is rank r's flag block (ovk_comm_flag_bytes() bytes, 256-byte
+ * aligned, zero), flag_blocks[rank] this context's own.  Collective calls
+ * (ovk_matmul_nbits_nsplit, ovk_allgather_cols, ovk_comm_barrier) must be made in
+ * the same order by every rank; each is enqueued like any operator call and
+ * ends with a wait, on the device, for the peers' stores - bounded by the
+ * time-out (about a second unless set), after which the stream goes on and the
+ * next ovk_flush returns OVK_TIMEOUT.  Peer memory is only ever touched by plain
+ * loads and stores of this library's own kernels. */
+#define OVK_COMM_HANDLE_BYTES 64
+#define OVK_COMM_MAX_RANKS 8
+OVK_API size_t ovk_comm_flag_bytes(void);
+OVK_API int32_t ovk_comm_alloc(ovk_ctx *ctx, size_t bytes, void **dptr);
+OVK_API int32_t ovk_comm_export(ovk_ctx *ctx, void *dptr, void *handle_out);
+OVK_API int32_t ovk_comm_import(ovk_ctx *ctx, const void *handle, void **peer_ptr);
+OVK_API int32_t ovk_comm_release(ovk_ctx *ctx, void *peer_ptr);
+OVK_API int32_t ovk_comm_init(ovk_ctx *ctx, int32_t rank, int32_t world, void *const *flag_blocks);
+OVK_API int32_t ovk_comm_set_timeout_ms(ovk_ctx *ctx, int32_t ms);
+/* Every rank's earlier work on its stream is complete when the barrier has passed. */
+OVK_API int32_t ovk_comm_barrier(ovk_ctx *ctx);
+/* The exchange step of a column split: this rank's block y_shard [m, n_shard]
+ * (contiguous; NULL = it already sits in columns [col0, col0 + n_shard) of this
+ * rank's own matrix) is stored into those columns of EVERY rank's matrix
+ * y_peers[r] ([m, n_total], row major), and the stream then waits until every
+ * peer has done the same here.  dtype: OVK_FLOAT16, OVK_FLOAT or OVK_INT32. */
+OVK_API int32_t ovk_allgather_cols(ovk_ctx *ctx, const void *y_shard, int32_t dtype, int64_t m,
+                                   int64_t n_shard, int64_t col0, int64_t n_total,
+                                   void *const *y_peers);
+/* MatMulNBits split over weight columns: w holds columns [col0, col0 + N_w) of
+ * the operator's weight (a plain slice of its three tensors), A is the whole
+ * [m, K] activation matrix on every rank, and the call leaves the whole
+ * Y [m, n_total] in every rank's y_peers[r].  For fp16 results of the prefill
+ * kernel with per-block scaling (block sizes 128 and 256, or f32 scales) the
+ * kernel's own store warp writes each finished tile into every rank's matrix,
+ * so the exchange overlaps the product; other forms compute the block and then
+ * run the exchange of ovk_allgather_cols.  Results are those of ovk_matmul_nbits
+ * on the unsplit weight (the same kernel on the same columns). */
+OVK_API int32_t ovk_matmul_nbits_nsplit(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
+                                        int32_t a_dtype, int64_t m, int64_t col0, int64_t n_total,
+                                        void *const *y_peers, int32_t y_dtype);
+
 /* ------------------------------------------------- DynamicQuantizeLinear
  * interp::dynamic_quantize / quantize_on_device (interp.rs:1945-2085) with the
  * PARTIAL and QUANTIZE passes of shaders/dynamic_quantize.rs:106-222.  x, y,
@@ -164,7 +227,12 @@ OVK_API int32_t ovk_matmul_integer(ovk_ctx *ctx, const ovk_mmi_weight *w, const 
  *  - all calls share the one array: calls whose kernels may overlap on the GPU
  *    (different streams or contexts) race on it - serialise them.  The array
  *    keeps the previous call's row sums; they are rewritten before they are
- *    read, so nothing has to be cleared.
+ *    read, so nothing has to be cleared;
+ *  - two host threads making the first call on a device at the same time both
+ *    look the address up and store the same value: harmless;
+ *  - it always runs the 128-row tiles, never the 256 x 256 tiles
+ *    ovk_matmul_integer picks for long K and many tiles, so on such shapes it
+ *    is slower.
  * Results are identical to ovk_matmul_integer. */
 OVK_API int32_t ovk_matmul_integer_static_scratch(ovk_ctx *ctx, const ovk_mmi_weight *w,
                                                   const void *a, int32_t a_signed, int64_t m,

@@ -2,6 +2,7 @@
 // reference's operators use from crates/vk-compute (context.rs, buffer.rs,
 // stream.rs, pipeline.rs:246).
 #include "ovk_internal.h"
+#include "umma.cuh"
 
 #include <algorithm>
 #include <cstring>
@@ -74,6 +75,7 @@ int32_t ovk_ctx_create(int32_t device, void *stream, ovk_ctx **out)
                 device, prop.major, prop.minor);
     ctx->sm_count = prop.multiProcessorCount;
     ctx->smem_optin = prop.sharedMemPerBlockOptin;
+    ctx->clock_khz = prop.clockRate;
     if (stream) {
         ctx->stream = static_cast<cudaStream_t>(stream);
     } else {
@@ -105,6 +107,7 @@ void ovk_ctx_destroy(ovk_ctx *ctx)
     cudaFree(ctx->range_slot);
     cudaFree(ctx->dev_status);
     cudaFree(ctx->params);
+    cudaFree(ctx->tile_counters);
     cudaFreeHost(ctx->host_status);
     cudaEventDestroy(ctx->t0);
     cudaEventDestroy(ctx->t1);
@@ -117,6 +120,7 @@ const char *ovk_last_error(const ovk_ctx *ctx) { return ctx ? ctx->err.c_str() :
 const char *ovk_last_kernel(const ovk_ctx *ctx) { return ctx ? ctx->last_kernel : ""; }
 uint64_t ovk_launch_count(const ovk_ctx *ctx) { return ctx ? ctx->launches : 0; }
 void *ovk_stream(const ovk_ctx *ctx) { return ctx ? ctx->stream : nullptr; }
+size_t ovk_workspace_bytes(const ovk_ctx *ctx) { return ctx ? ctx->scratch_bytes : 0; }
 
 int32_t ovk_flush(ovk_ctx *ctx)
 {
@@ -134,9 +138,11 @@ int32_t ovk_flush(ovk_ctx *ctx)
                             "GatherBlockQuantized: an index read on the device fell outside the table "
                             "(its row was written as zeros)");
         return ovk_fail(ctx, OVK_TIMEOUT, "a device-side wait gave up (code %d: %s)", st,
-                        st == OVK_DEV_TIMEOUT_TMA   ? "bulk copy never arrived"
-                        : st == OVK_DEV_TIMEOUT_MMA ? "tensor core never signalled"
-                                                    : "pipeline stage never freed");
+                        st == OVK_DEV_TIMEOUT_TMA    ? "bulk copy never arrived"
+                        : st == OVK_DEV_TIMEOUT_MMA  ? "tensor core never signalled"
+                        : st == OVK_DEV_TIMEOUT_SLOT ? "pipeline stage never freed"
+                        : st == OVK_DEV_TIMEOUT_PEER ? "a peer GPU never signalled"
+                                                     : "self-test wait on a barrier nothing arrives at");
     }
     return OVK_OK;
 }
@@ -222,6 +228,30 @@ int32_t ovk_timer_stop(ovk_ctx *ctx, float *ms)
 }
 
 }  // extern "C"
+
+// One thread waits, through the same bounded-wait helper the tensor-core
+// kernels use, on a barrier nothing ever arrives at; after `polls` attempts it
+// records the code in the status word and the kernel ends.  No copy and no
+// tensor memory is in flight, nothing faults, nothing spins for long.
+__global__ void selftest_timeout_kernel(int *status, uint32_t polls)
+{
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        umma::mbar_init(&bar, 1);
+        umma::fence_barrier_init();
+        if (!umma::mbar_wait_limit(&bar, 0, polls))
+            atomicExch(status, OVK_DEV_TIMEOUT_SELFTEST);
+    }
+}
+
+extern "C" int32_t ovk_selftest_device_timeout(ovk_ctx *ctx)
+{
+    if (!ctx)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "ovk_selftest_device_timeout: null context");
+    selftest_timeout_kernel<<<1, 32, 0, ctx->stream>>>(ctx->dev_status, 1000u);
+    OVK_LAUNCHED(ctx, "selftest_timeout");
+    return OVK_OK;
+}
 
 __global__ void fill_u32_kernel(uint32_t *dst, size_t words, uint32_t value)
 {

@@ -13,7 +13,6 @@ bool ovk_mmi_tc_applies(const ovk_ctx *ctx, const ovk_mmi_weight *w, const void 
 int32_t ovk_mmi_tc_launch(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int32_t a_signed,
                           int64_t m, const void *a_zp, const void *b_zp, const EpiParams &epi,
                           void *out);
-int32_t ovk_mmi_tc_prepare_weight(ovk_ctx *ctx, ovk_mmi_weight *w);
 
 namespace {
 
@@ -180,8 +179,6 @@ int32_t ovk_mmi_prepack(ovk_ctx *ctx, const void *b, int32_t b_signed, int64_t k
     int32_t rc = OVK_OK;
     if (e != cudaSuccess)
         rc = ovk_fail(ctx, OVK_BACKEND, "mmi_pack_b: %s", cudaGetErrorString(e));
-    if (rc == OVK_OK)
-        rc = ovk_mmi_tc_prepare_weight(ctx, w);
     if (rc != OVK_OK) {
         cudaFree(w->bt);
         cudaFree(w->colsum);

@@ -20,8 +20,6 @@
 // kind::i8 takes signed and unsigned bytes per operand, so nothing is flipped
 // (the reference's FLIP_BYTES pass, shaders/matmul_integer.rs:25-38, is not needed).
 // Ragged M, N and K are handled by TMA zero fill plus store predicates.
-#include <cstdlib>
-
 #include "ovk_internal.h"
 #include "epilogue.cuh"
 #include "umma.cuh"
@@ -298,8 +296,14 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                         const uint32_t a_lo = ((a16 + uint32_t(s) * (A_BYTES >> 4)) & 0x3fffu) | (1u << 16);
                         const uint32_t b_lo = ((b16 + uint32_t(s) * (B_BYTES >> 4)) & 0x3fffu) | (1u << 16);
                         umma::mma_i8_lohi(d, a_lo, desc_hi, b_lo, desc_hi, idesc, kb != 0);
-                        if (kb == 0)
-                            umma::mbar_arrive(&started[b]);  // issued: the tensor core takes MMAs in issue order
+                        if (kb == 0) {
+                            // The other thread's first MMA of this tile must reach the tensor core after this
+                            // overwriting one.  The order comes from the fence pair - before_thread_sync here,
+                            // after_thread_sync behind the other thread's wait on `started` - together with the
+                            // tensor core running the MMAs on one accumulator in the order it was given them.
+                            umma::tc_fence_before();
+                            umma::mbar_arrive(&started[b]);
+                        }
                         umma::mma_i8_lohi(d, a_lo + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
                         umma::mma_i8_lohi(d, a_lo + 4, desc_hi, b_lo + 4, desc_hi, idesc, 1u);
                         umma::mma_i8_lohi(d, a_lo + 6, desc_hi, b_lo + 6, desc_hi, idesc, 1u);
@@ -477,8 +481,10 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         const uint32_t acc = kb != 0;
                         umma::mma_i8_lohi(tmem_base, a_lo, desc_hi, b_lo, desc_hi, idesc, acc);
                         umma::mma_i8_lohi(tmem_base + BN2, a_lo + HALF, desc_hi, b_lo, desc_hi, idesc, acc);
-                        if (kb == 0)
-                            umma::mbar_arrive(started);  // both overwriting MMAs are in the tensor core's queue
+                        if (kb == 0) {
+                            umma::tc_fence_before();  // orders both overwriting MMAs before the other thread's (see mmi_tc_kernel)
+                            umma::mbar_arrive(started);
+                        }
                         umma::mma_i8_lohi(tmem_base, a_lo + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
                         umma::mma_i8_lohi(tmem_base + BN2, a_lo + HALF + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
                         umma::mma_commit(&empty[s]);
@@ -594,14 +600,8 @@ int32_t launch256(ovk_ctx *ctx, const void *a, const ovk_mmi_weight *w, const Tc
 
 bool wants256(const ovk_ctx *ctx, const ovk_mmi_weight *w, int64_t m)
 {
-    // OVK_MMI_TILE=128 / 256 pins the choice (for tests that compare the two kernels)
-    static const char *pin = getenv("OVK_MMI_TILE");
-    if (pin && pin[0] == '1')
-        return false;
     if (SMEM2 > ctx->smem_optin || m >= (int64_t(1) << 31) - BM2)
         return false;
-    if (pin && pin[0] == '2')
-        return true;
     if (w->k < 2048 || w->n < 256 || m < 256)
         return false;
     const int64_t tiles = ceil_div64(w->n, BN2) * ceil_div64(m, BM2);
@@ -621,8 +621,6 @@ bool ovk_mmi_tc_applies(const ovk_ctx *ctx, const ovk_mmi_weight *w, const void 
     return m >= 16 && w->n >= 16 && w->k >= 32 && (w->k % 16) == 0 && aligned_to(a, 16) &&
            m < (int64_t(1) << 31) - BM && ceil_div64(m, BM) * ceil_div64(w->n, 64) < (int64_t(1) << 31);
 }
-
-int32_t ovk_mmi_tc_prepare_weight(ovk_ctx *, ovk_mmi_weight *) { return OVK_OK; }
 
 int32_t ovk_mmi_tc_launch(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int32_t a_signed, int64_t m,
                           const void *a_zp, const void *b_zp, const EpiParams &epi, void *out)
@@ -736,8 +734,8 @@ extern "C" int32_t ovk_matmul_integer_static_scratch(ovk_ctx *ctx, const ovk_mmi
         // rows [0, m) are rewritten whenever the zero point is not 0, and read only then:
         // nothing left over from an earlier call is ever used, so nothing needs clearing
         p.rowsum = rowsum;
-        mmi_rowsum_kernel<<<unsigned(ceil_div64(m * 32, 256)), 256, 0, ctx->stream>>>(
-            static_cast<const uint8_t *>(a), m, p.K, p.a_signed, b_zp, p.b_signed, rowsum);
+        OVK_CUDA(ctx, ovk_launch_pdl(mmi_rowsum_kernel, dim3(unsigned(ceil_div64(m * 32, 256))), dim3(256), 0, ctx->stream,
+                                     static_cast<const uint8_t *>(a), m, p.K, p.a_signed, b_zp, p.b_signed, rowsum));
         OVK_LAUNCHED(ctx, "mmi_rowsum");
     }
     CUtensorMap tmA;

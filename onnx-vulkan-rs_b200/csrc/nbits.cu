@@ -18,6 +18,12 @@ bool ovk_nbits_gemm_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int64
                             int32_t y_dtype, const void *a, const void *y);
 int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype,
                        int64_t m, void *y, int32_t y_dtype);
+bool ovk_nbits_gemm_is_per_block(const ovk_ctx *ctx, const ovk_nbits_weight *w);
+int32_t ovk_nbits_gemm_into(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int64_t m, void *const *y_dst,
+                            int n_dst, int64_t ldy, int64_t col0, int32_t y_dtype, const OvkCommView *view);
+int32_t ovk_comm_gather_cols(ovk_ctx *ctx, const OvkCommView &view, const void *src, size_t src_pitch, int elem_bytes,
+                             int64_t m, int64_t n_shard, int64_t col0, int64_t n_total, void *const *y_peers,
+                             bool skip_self);
 
 extern "C" {
 
@@ -125,6 +131,60 @@ int32_t ovk_matmul_nbits_group(ovk_ctx *ctx, int32_t count, const ovk_nbits_weig
             return rc;
     }
     return OVK_OK;
+}
+
+// One rank's share of a MatMulNBits split over weight columns, exchange included.
+//
+// The prefill kernel with per-block scaling stores every finished tile into every rank's matrix
+// itself (the exchange rides on the product); the other kernels compute this rank's column block
+// - in place inside its own matrix where they can take a row pitch, in a temporary otherwise - and
+// the exchange kernel spreads it.  Either way the call returns with one wait enqueued behind it:
+// until every peer's stores into this rank's matrix have been announced.
+int32_t ovk_matmul_nbits_nsplit(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype, int64_t m,
+                                int64_t col0, int64_t n_total, void *const *y_peers, int32_t y_dtype)
+{
+    if (!ctx || !w || !y_peers)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "ovk_matmul_nbits_nsplit: null argument");
+    const int world = ctx->comm.world, rank = ctx->comm.rank;
+    OVK_REQUIRE(ctx, world >= 1, "MatMulNBits (column split): ovk_comm_init has not been called");
+    OVK_REQUIRE(ctx, m >= 0, "MatMulNBits: %lld rows of A", (long long)m);
+    OVK_REFUSE(ctx, (a_dtype != OVK_FLOAT && a_dtype != OVK_FLOAT16) || (y_dtype != OVK_FLOAT && y_dtype != OVK_FLOAT16),
+               "MatMulNBits: A and Y must be f32 or f16, got %d/%d", a_dtype, y_dtype);
+    OVK_REQUIRE(ctx, col0 >= 0 && col0 + w->n <= n_total && n_total < (int64_t(1) << 31),
+                "MatMulNBits (column split): columns [%lld, %lld) of %lld", (long long)col0, (long long)(col0 + w->n),
+                (long long)n_total);
+    for (int r = 0; r < world; r++)
+        OVK_REQUIRE(ctx, y_peers[r], "MatMulNBits (column split): the matrix of rank %d is null", r);
+    OVK_REQUIRE(ctx, m == 0 || a, "MatMulNBits: A is null");
+    OVK_CUDA(ctx, cudaSetDevice(ctx->device));
+    const int es = y_dtype == OVK_FLOAT16 ? 2 : 4;
+    const OvkCommView view = ovk_comm_next(ctx);  // every rank counts the call, also one with no rows
+    void *own = y_peers[rank];
+    void *own_block = static_cast<uint8_t *>(own) + size_t(col0) * es;
+    if (m == 0)
+        return ovk_comm_gather_cols(ctx, view, own_block, size_t(n_total) * es, es, 0, w->n, col0, n_total, y_peers, true);
+    const bool prefill = ovk_nbits_gemm_applies(ctx, w, m, a_dtype, y_dtype, a, own_block);
+    if (prefill && ovk_nbits_gemm_is_per_block(ctx, w) && y_dtype == OVK_FLOAT16) {
+        int32_t rc = ovk_nbits_gemm_into(ctx, w, a, m, y_peers, world, n_total, col0, y_dtype, &view);
+        if (rc != OVK_OK)
+            return rc;
+        return world > 1 ? ovk_comm_wait_done(ctx, view) : OVK_OK;
+    }
+    if (prefill) {
+        void *dst[1] = {own};
+        int32_t rc = ovk_nbits_gemm_into(ctx, w, a, m, dst, 1, n_total, col0, y_dtype, nullptr);
+        if (rc != OVK_OK)
+            return rc;
+        return ovk_comm_gather_cols(ctx, view, own_block, size_t(n_total) * es, es, m, w->n, col0, n_total, y_peers, true);
+    }
+    // kernels that write a contiguous [m, N] result: through a temporary
+    void *tmp = nullptr;
+    OVK_CUDA(ctx, cudaMallocAsync(&tmp, size_t(m) * w->n * es + 256, ctx->stream));
+    int32_t rc = ovk_matmul_nbits(ctx, w, a, a_dtype, m, tmp, y_dtype);
+    if (rc == OVK_OK)
+        rc = ovk_comm_gather_cols(ctx, view, tmp, size_t(w->n) * es, es, m, w->n, col0, n_total, y_peers, false);
+    cudaFreeAsync(tmp, ctx->stream);
+    return rc;
 }
 
 }  // extern "C"

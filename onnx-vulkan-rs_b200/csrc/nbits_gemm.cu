@@ -44,8 +44,25 @@
 // Weight columns sit on tensor-memory LANES so the scale is one scalar per thread.
 // The promotion warps hold 96 accumulators each: the register file is
 // re-divided between the warpgroups with setmaxnreg.
-#include <cstdlib>
-
+//
+// Work is handed out in UNITS of one quantization block (one 64-k slab for the
+// blocks smaller than a slab) of one tile.  A launch either gives every CTA a
+// run of whole tiles, or - when whole tiles would leave SMs idle in the last
+// round - cuts the line of all units into one contiguous run per CTA, so that a
+// tile's K range may be shared by several CTAs.  A CTA that holds only part of
+// a tile's K writes its f32 partial sums to the workspace and counts itself at
+// the tile's counter; the CTA that arrives last adds the parts in K order
+// (always the same order, so results do not depend on who was last) and stores
+// the tile.  Nobody waits for anybody.
+//
+//   warp 3      store: fp16 results go through a small shared-memory buffer so
+//               that rows leave as 16-byte stores in 256-byte segments, and this
+//               warp - not the promotion warps, which go straight on to the next
+//               tile - issues them.  In a launch that is one rank of a column
+//               split over several GPUs it stores every segment into EVERY
+//               rank's copy of Y (plain stores through peer mappings): the
+//               all-gather happens tile by tile while the tensor core works on
+//               the next tile, and ends with one flag per peer.
 #include "ovk_internal.h"
 #include "umma.cuh"
 
@@ -55,7 +72,7 @@ constexpr int BW = 128;    // weight columns per tile (UMMA M)
 constexpr int BT = 192;    // most tokens per tile (UMMA N)
 constexpr int HALF = BT / 2;  // token rows per promotion warp
 constexpr int SLAB = 64;   // k per stage: 128 bytes of fp16
-constexpr int STAGES = 8;    // shared-memory ring: tokens + packed nibbles of a slab (TMA)
+constexpr int STAGES = 7;    // shared-memory ring: tokens + packed nibbles of a slab (TMA)
 constexpr int A_STAGES = 4;  // tensor-memory ring: unpacked weights of a slab
 constexpr int ACC_RING = 4;   // most accumulators in flight: 2 x 192, 3 x 128 or 4 x 96 columns
 constexpr int B_BYTES = BT * 128;
@@ -66,12 +83,14 @@ static_assert(A_BASE + A_STAGES * A_COLS <= TMEM_COLS, "tensor memory: accumulat
 constexpr int RAW_BYTES = BW * 32;  // packed nibbles of one slab: 32 bytes per weight row
 constexpr int THREADS = 20 * 32;  // five warpgroups: control, unpack x2, promotion x2
 constexpr long long WAIT_CYCLES = 2000000000ll;
+constexpr int Y_ROWS = 48;                 // token rows of one pass through the store buffer
+constexpr int Y_BYTES = Y_ROWS * BW * 2;   // one half's buffer: 48 rows x 128 fp16
+constexpr int PART_FLOATS = HALF * BW;     // f32 partial sums one promotion half holds for a tile
 
 struct GemmParams {
     const uint8_t *wq;     // [n_pad, k_pad/2] nibble-permuted copy
     const float *scales_t; // [nb_pad, n_pad]
     const uint8_t *zp_t;   // [n_pad, zp_pitch] one byte per block, rows padded to 8
-    void *y;
     int M, N, K;
     int k_pad, n_pad, n_blocks;
     int zp_pitch;
@@ -82,7 +101,49 @@ struct GemmParams {
     int ring, acc_stride;  // accumulators in flight and their distance in tensor-memory columns
     int y_f32;
     int *status;
+    // where results go: n_dst matrices of row pitch ldy elements, this launch's columns starting at col0
+    void *y_dst[OVK_MAX_RANKS];
+    int n_dst, ldy, col0;
+    int vec_ok;            // every destination takes 16-byte stores at multiples of 8 columns
+    OvkCommView comm;      // used when n_dst > 1
+    // work units
+    int units;             // per tile
+    int unit_slabs;        // slabs of one unit (1, 2 or 4)
+    int unit_blocks;       // quantization blocks of one unit (2 for blocks of 32, else 1)
+    int shared_k;          // 1: contiguous runs of units, tiles may be shared between CTAs
+    float *partials;       // [gridDim.x][2 items][2 halves][HALF][BW] f32
+    uint32_t *counters;    // one per tile, zero between launches
 };
+
+// The run of units of this CTA and its walk, tile by tile.
+struct Run {
+    long long u, end;
+};
+__device__ __forceinline__ long long run_start(const GemmParams &p, long long cta)
+{
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    if (p.shared_k)
+        return tiles * p.units * cta / gridDim.x;
+    return (tiles * cta / gridDim.x) * p.units;
+}
+__device__ __forceinline__ Run cta_run(const GemmParams &p)
+{
+    Run r;
+    r.u = run_start(p, blockIdx.x);
+    r.end = run_start(p, blockIdx.x + 1);
+    return r;
+}
+// Next item of the run: units [ub, ue) of `tile`.  Returns false at the end.
+__device__ __forceinline__ bool next_item(const GemmParams &p, Run &r, int &tile, int &ub, int &ue)
+{
+    if (r.u >= r.end)
+        return false;
+    tile = int(r.u / p.units);
+    ub = int(r.u - (long long)tile * p.units);
+    ue = int(min((long long)p.units, ub + (r.end - r.u)));
+    r.u += ue - ub;
+    return true;
+}
 
 __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
 {
@@ -152,19 +213,39 @@ __device__ __forceinline__ uint4 unpack8(uint32_t w, uint32_t c_lo, uint32_t c_h
     return o;
 }
 
+__device__ __forceinline__ void named_bar_sync(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// What the store warp is told about one pass through a half's buffer.
+struct PassDesc {
+    int m_base;  // token row of the buffer's first row
+    int rows;    // rows of the buffer that hold results (<= 0: none); -1000000: the CTA has no more tiles
+    int n0;      // first weight column of the tile
+    int pad;
+};
+constexpr int PASS_STOP = -1000000;
+
 __global__ void __launch_bounds__(THREADS, 1)
-nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_constant__ CUtensorMap tmRaw, GemmParams p)
+nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_constant__ CUtensorMap tmRaw,
+                  const __grid_constant__ GemmParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *sX = smem;                       // STAGES x 24 KB: tokens (UMMA B operand)
     uint8_t *sR = sX + STAGES * B_BYTES;      // STAGES x 4 KB: packed nibbles as loaded
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sR + STAGES * RAW_BYTES);
+    uint8_t *sY = sR + STAGES * RAW_BYTES;    // 2 x 12 KB: results on their way out, one buffer per promotion half
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sY + 2 * Y_BYTES);
     uint64_t *full_x = bars;                  // TMA landed
     uint64_t *full_w = full_x + STAGES;       // [A_STAGES] the four unpack warps arrived
     uint64_t *empty = full_w + A_STAGES;      // [STAGES] MMAs of the slab finished: its shared-memory AND its A stage are free
     uint64_t *acc_full = empty + STAGES;      // a block's partial sums are complete
     uint64_t *acc_empty = acc_full + ACC_RING;// all 8 promotion warps have read them
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + ACC_RING);
+    uint64_t *y_full = acc_empty + ACC_RING;  // [2] a half's buffer holds a pass (its four warps arrived)
+    uint64_t *y_empty = y_full + 2;           // [2] the store warp has read it
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(y_empty + 2);
+    uint32_t *s_count = tmem_slot + 1;        // the tile counter's value, for all promotion warps
+    PassDesc *s_desc = reinterpret_cast<PassDesc *>(tmem_slot + 4);  // [2]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -179,6 +260,10 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
             umma::mbar_init(&acc_full[b], 1);
             umma::mbar_init(&acc_empty[b], 8);
         }
+        for (int h = 0; h < 2; h++) {
+            umma::mbar_init(&y_full[h], 4);  // one arrival per promotion warp of the half
+            umma::mbar_init(&y_empty[h], 1);
+        }
         umma::fence_barrier_init();
     }
     if (warp == 1) {
@@ -190,28 +275,30 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
     umma::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int total_tiles = p.m_tiles * p.n_tiles;
     const int blocks_per_slab = p.bs >= SLAB ? 1 : SLAB / p.bs;  // 2 when block_size is 32
     const int slabs_per_block = p.bs >= SLAB ? p.bs / SLAB : 1;
 
     // 640 threads start with 96 registers each; control and unpack warps give registers back,
-    // the promotion warps take them (40*128 + 64*256 + 152*256 = 60416 of the 61440)
+    // the promotion warps take them (48*128 + 64*256 + 152*256 = 61440, all there are)
     if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
     if (warp == 0) {
         // ------------------------------------------------------------ tokens by TMA
         if (lane == 0) {
             umma::prefetch_tmap(&tmAct);
             umma::prefetch_tmap(&tmRaw);
             int seq = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            Run run = cta_run(p);
+            int tile, ub, ue;
+            bool ok = true;
+            while (ok && next_item(p, run, tile, ub, ue)) {
                 const int m0 = (tile % p.m_tiles) * p.bt;
                 const int n0 = (tile / p.m_tiles) * BW;
-                for (int sl = 0; sl < p.slabs; sl++, seq++) {
+                for (int sl = ub * p.unit_slabs; sl < ue * p.unit_slabs; sl++, seq++) {
                     const int s = seq % STAGES;
                     if (!wait_parked(&empty[s], ((seq / STAGES) & 1) ^ 1)) {
                         atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
-                        tile = total_tiles;
+                        ok = false;
                         break;
                     }
                     umma::mbar_expect_tx(&full_x[s], uint32_t(p.bt) * 128u + RAW_BYTES);
@@ -231,6 +318,8 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         // interleave.
         // The whole warp runs the loop and stays converged; one elected lane issues the
         // tcgen05 instructions, so loop state and descriptors are warp-uniform values.
+        // Runs begin and end on block boundaries, so the per-block state carries over from one
+        // item to the next exactly as it does from tile to tile.
         const int me = warp - 1;
         const int issuers = p.bs >= SLAB ? 2 : 1;  // smaller blocks: two per slab, one issuer
         if (me < issuers) {
@@ -241,8 +330,10 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
             int s = 0, a = 0, b = 0, slab_in_block = 0, owner = 0;
             uint32_t a_ph = 0, acc_ph = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                for (int sl = 0; sl < p.slabs && ok; sl++) {
+            Run run = cta_run(p);
+            int tile, ub, ue;
+            while (ok && next_item(p, run, tile, ub, ue)) {
+                for (int sl = ub * p.unit_slabs; sl < ue * p.unit_slabs && ok; sl++) {
                     const uint32_t a_t = tmem_base + uint32_t(A_BASE + a * A_COLS);  // 8 columns per K=16 step
                     const uint32_t x_lo = ((x16 + uint32_t(s) * (B_BYTES >> 4)) & 0x3fffu) | (1u << 16);
                     if (p.bs >= SLAB) {
@@ -326,6 +417,105 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                 }
             }
         }
+    } else if (warp == 3) {
+        // -------------------------------------------------------------------- store
+        // Takes the passes the promotion halves leave in their buffers (half 0, half 1, half 0,
+        // ...) and writes them out: a row of the buffer is 256 contiguous bytes of a row of Y, a
+        // lane moves 16 of them, and in a column split over several GPUs every 16 bytes go to
+        // every rank's Y.  The stores are not waited for here; the promotion warps have long gone
+        // on to the next tile.
+        const bool exchange = p.n_dst > 1;
+        bool peers_ready = !exchange;
+        bool ok = true;
+        if (exchange && blockIdx.x == 0)
+            comm::announce(p.comm, false, lane);  // this rank's earlier work on the stream is complete
+        uint32_t seq = 0;
+        for (bool running = !p.y_f32; running;) {  // f32 results are stored by the promotion warps themselves
+#pragma unroll 1
+            for (int h = 0; h < 2 && running; h++) {
+                if (!wait_parked(&y_full[h], seq & 1)) {
+                    if (lane == 0)
+                        atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
+                    ok = false;
+                    running = false;
+                    break;
+                }
+                const PassDesc d = s_desc[h];
+                if (d.rows == PASS_STOP) {
+                    if (h == 1)
+                        running = false;
+                    continue;  // (the stop arrives on both halves in the same pass)
+                }
+                if (!peers_ready && d.rows > 0) {
+                    // before the first store into a peer: its stream has reached this call too, so
+                    // nothing there still reads what is about to be overwritten
+                    peers_ready = true;
+                    if (!comm::wait_all(p.comm, false, lane)) {
+                        if (lane == 0)
+                            atomicExch(p.status, OVK_DEV_TIMEOUT_PEER);
+                        ok = false;
+                    }
+                }
+                const uint8_t *buf = sY + h * Y_BYTES;
+                // 48 rows x 16 chunks of 16 bytes = 24 chunks per lane, four at a time
+#pragma unroll 1
+                for (int i = 0; i < Y_ROWS * 16 / 32; i += 4) {
+                    uint4 v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int c = lane + 32 * (i + u);
+                        v[u] = *reinterpret_cast<const uint4 *>(buf + (c >> 4) * (BW * 2) + (c & 15) * 16);
+                    }
+                    if (i + 4 == Y_ROWS * 16 / 32) {
+                        // everything of the buffer is in registers: hand it back
+                        __syncwarp();
+                        if (lane == 0)
+                            umma::mbar_arrive(&y_empty[h]);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int c = lane + 32 * (i + u);
+                        const int row = c >> 4, n = d.n0 + (c & 15) * 8;
+                        if (!ok || row >= d.rows || n >= p.N)
+                            continue;
+                        const size_t off = (size_t(d.m_base + row) * size_t(p.ldy) + size_t(p.col0 + n)) * 2;
+                        if (p.vec_ok && n + 8 <= p.N) {
+#pragma unroll
+                            for (int r = 0; r < OVK_MAX_RANKS; r++)
+                                if (r < p.n_dst)
+                                    *reinterpret_cast<uint4 *>(static_cast<uint8_t *>(p.y_dst[r]) + off) = v[u];
+                        } else {
+                            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+                            for (int r = 0; r < p.n_dst; r++) {
+                                uint16_t *o = reinterpret_cast<uint16_t *>(static_cast<uint8_t *>(p.y_dst[r]) + off);
+#pragma unroll
+                                for (int e = 0; e < 8; e++)
+                                    if (n + e < p.N)
+                                        o[e] = uint16_t(w[e >> 1] >> (16 * (e & 1)));
+                            }
+                        }
+                    }
+                }
+            }
+            seq++;
+        }
+        if (exchange) {
+            // every store of this CTA is visible everywhere before the CTA is counted; the CTA
+            // counted last announces the kernel's stores to every rank
+            __threadfence_system();
+            __syncwarp();
+            OvkCommFlags *own = p.comm.flags[p.comm.rank];
+            uint32_t last = 0;
+            if (lane == 0) {
+                last = atomicAdd(&own->cta_done, 1u) + 1u == gridDim.x;
+                if (last)
+                    own->cta_done = 0;
+                __threadfence_system();
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last && ok)
+                comm::announce(p.comm, true, lane);
+        }
     }
     } else if (warp < 12) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
@@ -344,11 +534,14 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         // store of slab j is announced only after slab j + 1 has been unpacked - by then it has
         // completed and the wait costs nothing - and block indices are shifts, not divisions.
         const int bs_shift = 31 - __clz(p.bs);  // block sizes are powers of two
-        int seq = 0;       // global index of the current tile's first slab
+        int seq = 0;       // position in the stage rings of the current item's first slab
         int pending = -1;  // A stage stored to but not yet announced
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, seq += p.slabs) {
+        Run run = cta_run(p);
+        int tile, ub, ue;
+        while (ok && next_item(p, run, tile, ub, ue)) {
             const int n = (tile / p.m_tiles) * BW + r;
+            const int sl0 = ub * p.unit_slabs, len = (ue - ub) * p.unit_slabs;
             // zero points: one byte per block, fetched one slab of this group ahead
             const uint8_t *zrow = p.zp_t + size_t(n) * p.zp_pitch;
             auto zero_points = [&](int sl) -> uint32_t {
@@ -356,13 +549,13 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                 const uint32_t z0 = zrow[blk];
                 return z0 | (blocks_per_slab == 2 ? uint32_t(zrow[blk + 1]) << 8 : z0 << 8);
             };
-            int sl = (seq ^ group) & 1;  // the first slab of this tile that this group takes
-            uint32_t z_next = sl < p.slabs ? zero_points(sl) : 0u;
-            for (; sl < p.slabs; sl += 2) {
-                const int g = seq + sl;
+            int i = (seq ^ group) & 1;  // the first slab of this item that this group takes
+            uint32_t z_next = i < len ? zero_points(sl0 + i) : 0u;
+            for (; i < len; i += 2) {
+                const int g = seq + i;
                 const uint32_t z0 = z_next & 0xffu, z1 = z_next >> 8;
-                if (sl + 2 < p.slabs)
-                    z_next = zero_points(sl + 2);
+                if (i + 2 < len)
+                    z_next = zero_points(sl0 + i + 2);
                 const uint32_t lo0 = z0 * 0x00010001u + 0x64006400u, hi0 = z0 * 0x00100010u + 0x54005400u;
                 const uint32_t lo1 = z1 * 0x00010001u + 0x64006400u, hi1 = z1 * 0x00100010u + 0x54005400u;
                 const int s = g % STAGES;
@@ -408,6 +601,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                 pending = g % A_STAGES;
                 umma::tmem_st_32x32(a_lane + uint32_t(pending * A_COLS), wv);
             }
+            seq += len;
         }
         if (pending >= 0) {
             umma::tmem_st_wait();
@@ -424,22 +618,59 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         // the tile's tokens are split between the two halves in whole 32-column chunks, and a warp
         // reads only the chunks that hold tokens
         const int hw = ((p.bt / 2 + 31) / 32) * 32;
-        const int nchunks = (min(hw, p.bt - half * hw) + 31) / 32;
+        const int half_rows = min(hw, p.bt - half * hw);
+        const int nchunks = (half_rows + 31) / 32;
         int b = 0;
         uint32_t acc_ph = 0;
+        uint32_t yseq = 0;  // passes this half has put into its buffer
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            const int n = (tile / p.m_tiles) * BW + q * 32 + lane;
+        bool first_item = true;
+        uint8_t *ybuf = sY + half * Y_BYTES + (q * 32 + lane) * 2;
+        Run run = cta_run(p);
+        int tile, ub, ue;
+        // one pass: 48 rows of this thread's column into the half's buffer, then the warp's arrival
+        auto put_pass = [&](const float (&acc)[HALF], int first_row, int m_base, int rows, int n0) {
+            if (ok && !wait_parked(&y_empty[half], (yseq & 1) ^ 1)) {
+                if (lane == 0)
+                    atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
+                ok = false;
+            }
+            if (first_row == 0) {
+#pragma unroll
+                for (int j = 0; j < Y_ROWS; j++)
+                    *reinterpret_cast<__half *>(ybuf + j * (BW * 2)) = __float2half_rn(acc[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < Y_ROWS; j++)
+                    *reinterpret_cast<__half *>(ybuf + j * (BW * 2)) = __float2half_rn(acc[Y_ROWS + j]);
+            }
+            if (q == 0 && lane == 0) {
+                PassDesc d;
+                d.m_base = m_base;
+                d.rows = ok ? rows : (rows == PASS_STOP ? PASS_STOP : 0);
+                d.n0 = n0;
+                d.pad = 0;
+                s_desc[half] = d;
+            }
+            __syncwarp();
+            if (lane == 0)
+                umma::mbar_arrive(&y_full[half]);  // release: the buffer and the descriptor are written
+            yseq++;
+        };
+        while (next_item(p, run, tile, ub, ue)) {
+            const int n0 = (tile / p.m_tiles) * BW;
+            const int n = n0 + q * 32 + lane;
             const int m0 = (tile % p.m_tiles) * p.bt + half * hw;
             // token rows of this warp that exist (may be <= 0): its share of the tile, cut at the end of M
-            const int rows = min(p.M - m0, min(hw, p.bt - half * hw));
+            const int rows = min(p.M - m0, half_rows);
             float acc[HALF];
 #pragma unroll
             for (int j = 0; j < HALF; j++)
                 acc[j] = 0.0f;
-            float scale = p.scales_t[n];
-            for (int blk = 0; blk < p.n_blocks; blk++) {
-                const float scale_next = blk + 1 < p.n_blocks ? p.scales_t[size_t(blk + 1) * p.n_pad + n] : 0.0f;
+            const int blk0 = ub * p.unit_blocks, blk1 = ue * p.unit_blocks;
+            float scale = p.scales_t[size_t(blk0) * p.n_pad + n];
+            for (int blk = blk0; blk < blk1; blk++) {
+                const float scale_next = blk + 1 < blk1 ? p.scales_t[size_t(blk + 1) * p.n_pad + n] : 0.0f;
                 if (ok && !wait_parked(&acc_full[b], acc_ph)) {
                     if (lane == 0)
                         atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
@@ -470,36 +701,85 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                     acc_ph ^= 1;
                 }
             }
-            if (ok && n < p.N) {
-                // the MMA thread can run only two blocks ahead while this store lasts: a row
-                // pointer stepped by N and no bound test when all token rows of this warp exist
-                const bool whole = rows >= HALF;
-                if (p.y_f32) {
-                    float *y = static_cast<float *>(p.y) + size_t(m0) * p.N + n;
-                    if (whole) {
+            bool store = true;
+            if (ub != 0 || ue != p.units) {
+                // Part of the tile's K: leave the partial sums in this CTA's slot (0 for the item its
+                // run begins with, 1 for any later one - a run has at most two partial items) and
+                // count this part at the tile.  The part counted last adds all parts in K order,
+                // its own read back like the others so that the order of the additions is fixed.
+                float *mine = p.partials + ((size_t(blockIdx.x) * 2 + (first_item ? 0 : 1)) * 2 + half) * PART_FLOATS +
+                              q * 32 + lane;
 #pragma unroll
-                        for (int j = 0; j < HALF; j++, y += p.N)
-                            *y = acc[j];
-                    } else {
+                for (int j = 0; j < HALF; j++)
+                    __stcg(mine + j * BW, acc[j]);
+                __threadfence();
+                named_bar_sync(1, 256);
+                if (warp == 12 && lane == 0) {
+                    // CTAs whose runs reach into this tile: from the one holding its first unit to the
+                    // one holding its last
+                    const long long total = (long long)p.m_tiles * p.n_tiles * p.units;
+                    const long long x0 = (long long)tile * p.units, x1 = x0 + p.units - 1;
+                    const long long c_first = ((x0 + 1) * gridDim.x + total - 1) / total - 1;
+                    const long long c_last = ((x1 + 1) * gridDim.x + total - 1) / total - 1;
+                    const uint32_t parts = uint32_t(c_last - c_first + 1);
+                    const uint32_t before = atomicAdd(&p.counters[tile], 1u);
+                    const bool last = before + 1u == parts;
+                    if (last)
+                        p.counters[tile] = 0;  // zero again for the next launch
+                    __threadfence();
+                    s_count[0] = last ? uint32_t(c_first) : 0xffffffffu;
+                    s_count[1] = uint32_t(c_last);
+                }
+                named_bar_sync(1, 256);
+                const uint32_t c_first = s_count[0], c_last = s_count[1];
+                named_bar_sync(1, 256);  // s_count may be rewritten for the next partial item
+                store = c_first != 0xffffffffu;
+                if (store) {
 #pragma unroll
-                        for (int j = 0; j < HALF; j++, y += p.N)
-                            if (j < rows)
-                                *y = acc[j];
-                    }
-                } else {
-                    __half *y = static_cast<__half *>(p.y) + size_t(m0) * p.N + n;
-                    if (whole) {
+                    for (int j = 0; j < HALF; j++)
+                        acc[j] = 0.0f;
+                    for (uint32_t c = c_first; c <= c_last; c++) {
+                        // the part of CTA c is the item its run begins with, unless the run began in
+                        // an earlier tile (only the first of the CTAs can)
+                        const bool begins_here = run_start(p, c) >= (long long)tile * p.units;
+                        const float *part = p.partials + ((size_t(c) * 2 + (begins_here ? 0 : 1)) * 2 + half) * PART_FLOATS +
+                                            q * 32 + lane;
 #pragma unroll
-                        for (int j = 0; j < HALF; j++, y += p.N)
-                            *y = __float2half_rn(acc[j]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < HALF; j++, y += p.N)
-                            if (j < rows)
-                                *y = __float2half_rn(acc[j]);
+                        for (int j = 0; j < HALF; j++)
+                            acc[j] += __ldcg(part + j * BW);
                     }
                 }
             }
+            first_item = false;
+            if (!store)
+                continue;
+            if (p.y_f32) {
+                if (ok && n < p.N) {
+                    // the MMA thread can run only two blocks ahead while this store lasts: a row
+                    // pointer stepped by the pitch and no bound test when all token rows of this warp exist
+                    float *y = static_cast<float *>(p.y_dst[0]) + size_t(m0) * p.ldy + p.col0 + n;
+                    if (rows >= HALF) {
+#pragma unroll
+                        for (int j = 0; j < HALF; j++, y += p.ldy)
+                            *y = acc[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < HALF; j++, y += p.ldy)
+                            if (j < rows)
+                                *y = acc[j];
+                    }
+                }
+            } else {
+                put_pass(acc, 0, m0, min(rows, Y_ROWS), n0);
+                put_pass(acc, Y_ROWS, m0 + Y_ROWS, min(rows - Y_ROWS, Y_ROWS), n0);
+            }
+        }
+        if (!p.y_f32) {
+            float none[HALF];
+#pragma unroll
+            for (int j = 0; j < HALF; j++)
+                none[j] = 0.0f;
+            put_pass(none, 0, 0, PASS_STOP, 0);  // tells the store warp that this CTA has no more tiles
         }
     }
     umma::tc_fence_before();
@@ -550,7 +830,7 @@ nbits_gemm_pack_kernel(const uint32_t *__restrict__ src_w, const void *__restric
     }
 }
 
-size_t gemm_smem() { return size_t(STAGES) * (B_BYTES + RAW_BYTES) + 512; }
+size_t gemm_smem() { return size_t(STAGES) * (B_BYTES + RAW_BYTES) + 2 * Y_BYTES + 512; }
 
 }  // namespace
 
@@ -609,45 +889,77 @@ bool ovk_nbits_gemm_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int64
            aligned_to(w->scales, w->scales_dtype == OVK_FLOAT ? 4 : 2);
 }
 
-// Tokens per tile.  A slab of a tile costs about 285 + (tokens) in units of 1.4 clocks
-// (measured: 670, 575 and 535 clocks for 192, 128 and 96 tokens), the grid runs
-// ceil(tiles / SMs) rounds and the last round is as long as a full one: a narrower tile that
-// fills the last round better wins when the product is smaller.
-int token_tile(int64_t m, int n_tiles, int sm_count)
+// The shape of a launch: tokens per tile, and whether CTAs get whole tiles or runs of units.
+// A slab of a tile costs about 285 + (tokens) in units of 1.4 clocks (measured: 670, 575 and 535
+// clocks for 192, 128 and 96 tokens).  With whole tiles the grid runs ceil(tiles / SMs) rounds and
+// the last round is as long as a full one; with runs of units every SM gets the same share of the
+// slabs, at the price of the partial sums the shared tiles go through (taken as eight slabs' time
+// per CTA).  The cheaper plan wins; whole tiles also win a near tie, since they need no workspace.
+struct Plan {
+    int bt;
+    bool shared_k;
+    unsigned grid;
+};
+Plan plan_launch(const ovk_ctx *ctx, int64_t m, int n_tiles, int units, int unit_slabs)
 {
-    static const char *pin = getenv("OVK_NBITS_BT");
-    if (pin && atoi(pin) >= 96 && atoi(pin) <= BT && atoi(pin) % 32 == 0)
-        return atoi(pin);
-    int best = BT;
+    const int sms = ctx->sm_count;
+    Plan best = {BT, false, 1};
     double best_cost = 0;
+    bool have = false;
     for (int bt = BT; bt >= 96; bt -= 32) {
         const int64_t tiles = ceil_div64(m, bt) * n_tiles;
-        const double cost = double(ceil_div64(tiles, sm_count)) * (285 + bt);
-        if (bt == BT || cost < 0.97 * best_cost) {
-            best = bt;
-            best_cost = cost;
+        const double slab = 285 + bt;
+        const double whole = double(ceil_div64(tiles, sms)) * units * unit_slabs * slab;
+        if (!have || whole < 0.97 * best_cost) {
+            best = {bt, false, unsigned(std::min<int64_t>(tiles, sms))};
+            best_cost = whole;
+            have = true;
+        }
+        const int64_t total_units = tiles * units;
+        const int64_t grid = std::min<int64_t>(sms, total_units);
+        if (tiles <= OVK_TILE_COUNTERS && units > 1 && grid > 0) {
+            const double shared = (double(ceil_div64(total_units, grid)) * unit_slabs + 8.0) * slab;
+            if (shared < 0.95 * best_cost) {
+                best = {bt, true, unsigned(grid)};
+                best_cost = shared;
+            }
         }
     }
     return best;
 }
 
 bool ovk_nbits_gemm_split_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w);
-int32_t ovk_nbits_gemm_split(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int64_t m, void *y, int32_t y_dtype);
+int32_t ovk_nbits_gemm_split(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int64_t m, void *y, int32_t y_dtype,
+                             int64_t ldy, int64_t col0);
 
-int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, int32_t a_dtype, int64_t m,
-                       void *y, int32_t y_dtype)
+// True when the prefill product of this weight would run the kernel of this file (the one that
+// can store into several ranks' matrices) rather than the two-term-scale kernel.
+bool ovk_nbits_gemm_is_per_block(const ovk_ctx *ctx, const ovk_nbits_weight *w)
 {
-    (void)a_dtype;
+    return !ovk_nbits_gemm_split_applies(ctx, w);
+}
+
+// Y[:, col0 : col0 + N] = A x dequant(B) in each of the n_dst matrices of row pitch ldy
+// (n_dst > 1: fp16 only, `view` describes the ranks and the call's epoch).
+int32_t ovk_nbits_gemm_into(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, int64_t m, void *const *y_dst,
+                            int n_dst, int64_t ldy, int64_t col0, int32_t y_dtype, const OvkCommView *view)
+{
     // small blocks with fp16 scales: the scale goes into the weight (exactly, as two fp16 terms)
-    static const char *pin = getenv("OVK_NBITS_GEMM");  // "blocks" pins the per-block kernel (for comparisons)
-    if (!(pin && pin[0] == 'b') && ovk_nbits_gemm_split_applies(ctx, wc))
-        return ovk_nbits_gemm_split(ctx, wc, a, m, y, y_dtype);
+    if (ovk_nbits_gemm_split_applies(ctx, wc)) {
+        if (n_dst != 1)
+            return ovk_fail(ctx, OVK_BACKEND, "MatMulNBits: the two-term-scale kernel stores into one matrix");
+        return ovk_nbits_gemm_split(ctx, wc, a, m, y_dst[0], y_dtype, ldy, col0);
+    }
     ovk_nbits_weight *w = const_cast<ovk_nbits_weight *>(wc);  // the prefill copy is built lazily
     int32_t rc = ovk_nbits_gemm_prepack(ctx, w);
     if (rc != OVK_OK)
         return rc;
     const int n_tiles = int(w->gemm_n_pad / BW);
-    const int bt = token_tile(m, n_tiles, ctx->sm_count);
+    const int bs = int(w->block_size);
+    const int unit_slabs = bs >= SLAB ? bs / SLAB : 1;
+    const int units = int(w->gemm_k_pad / SLAB) / unit_slabs;
+    const Plan plan = plan_launch(ctx, m, n_tiles, units, unit_slabs);
+    const int bt = plan.bt;
     CUtensorMap tmAct;
     if (!ovk_make_tmap_2d(&tmAct, a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, uint64_t(w->k), uint64_t(m), uint64_t(w->k) * 2,
                           SLAB, uint32_t(bt), CU_TENSOR_MAP_SWIZZLE_128B))
@@ -660,7 +972,6 @@ int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, 
     p.wq = static_cast<const uint8_t *>(w->gemm_w);
     p.scales_t = w->gemm_scales_t;
     p.zp_t = w->gemm_zp_t;
-    p.y = y;
     p.M = int(m);
     p.N = int(w->n);
     p.K = int(w->k);
@@ -669,7 +980,7 @@ int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, 
     p.n_blocks = int(w->gemm_k_pad / w->block_size);
     p.zp_pitch = int(w->gemm_zp_pitch);
     p.slabs = int(w->gemm_k_pad / SLAB);
-    p.bs = int(w->block_size);
+    p.bs = bs;
     p.bt = bt;
     p.ring = bt > 128 ? 2 : (bt > 96 ? 3 : 4);
     p.acc_stride = bt > 128 ? BT : (bt > 96 ? 128 : 96);
@@ -677,10 +988,42 @@ int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, 
     p.n_tiles = n_tiles;
     p.y_f32 = y_dtype == OVK_FLOAT;
     p.status = ctx->dev_status;
+    p.n_dst = n_dst;
+    p.ldy = int(ldy);
+    p.col0 = int(col0);
+    p.vec_ok = (ldy % 8) == 0 && (col0 % 8) == 0;
+    for (int r = 0; r < n_dst; r++) {
+        p.y_dst[r] = y_dst[r];
+        p.vec_ok = p.vec_ok && aligned_to(y_dst[r], 16);
+    }
+    if (view)
+        p.comm = *view;
+    p.units = units;
+    p.unit_slabs = unit_slabs;
+    p.unit_blocks = bs >= SLAB ? 1 : SLAB / bs;
+    p.shared_k = plan.shared_k ? 1 : 0;
+    if (plan.shared_k) {
+        if (!ctx->tile_counters) {
+            OVK_CUDA(ctx, cudaMalloc(&ctx->tile_counters, OVK_TILE_COUNTERS * sizeof(uint32_t)));
+            OVK_CUDA(ctx, cudaMemsetAsync(ctx->tile_counters, 0, OVK_TILE_COUNTERS * sizeof(uint32_t), ctx->stream));
+        }
+        void *ws = nullptr;
+        rc = ovk_scratch(ctx, size_t(plan.grid) * 2 * 2 * PART_FLOATS * sizeof(float), &ws);
+        if (rc != OVK_OK)
+            return rc;
+        p.partials = static_cast<float *>(ws);
+        p.counters = ctx->tile_counters;
+    }
     OVK_CUDA(ctx, cudaFuncSetAttribute(nbits_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gemm_smem())));
-    const int64_t tiles = int64_t(p.m_tiles) * p.n_tiles;
-    const unsigned grid = unsigned(std::min<int64_t>(tiles, ctx->sm_count));
-    nbits_gemm_kernel<<<grid, THREADS, gemm_smem(), ctx->stream>>>(tmAct, tmRaw, p);
-    OVK_LAUNCHED(ctx, "nbits_gemm_tc");
+    nbits_gemm_kernel<<<plan.grid, THREADS, gemm_smem(), ctx->stream>>>(tmAct, tmRaw, p);
+    OVK_LAUNCHED(ctx, plan.shared_k ? "nbits_gemm_tc_shared_k" : "nbits_gemm_tc");
     return OVK_OK;
+}
+
+int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, int32_t a_dtype, int64_t m,
+                       void *y, int32_t y_dtype)
+{
+    (void)a_dtype;
+    void *dst[1] = {y};
+    return ovk_nbits_gemm_into(ctx, wc, a, m, dst, 1, wc->n, 0, y_dtype, nullptr);
 }

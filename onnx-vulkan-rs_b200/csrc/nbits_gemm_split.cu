@@ -21,8 +21,6 @@
 //   warp 1       tensor memory, MMA issue: eight K=16 MMAs per 64-k slab
 //   warps 4-11   unpack: two threads per weight row, 32 k each
 //   warps 12-15  epilogue: the tile's accumulator (two in flight), fp16 / f32 store
-#include <cstdlib>
-
 #include "ovk_internal.h"
 #include "umma.cuh"
 
@@ -41,6 +39,7 @@ struct SplitParams {
     const uint8_t *zp_t;    // [n_pad, zp_pitch] one byte per block
     void *y;
     int M, N;
+    int ldy, col0;          // row pitch of y in elements and the column this product's results start at
     int n_pad, zp_pitch;
     int slabs;              // k_pad / 64
     int bs;                 // a power of two, 32 ... 256
@@ -317,22 +316,25 @@ nbits_gemm_split_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_
                     if (lane == 0)
                         umma::mbar_arrive(&acc_empty[b]);
                 }
-                if (!ok || n >= p.N)
-                    continue;
-                const int mc = m0 + c * 32;
-                if (p.y_f32) {
-                    float *y = static_cast<float *>(p.y);
+                // lanes whose column does not exist skip the stores and meet the others at the __syncwarp
+                // below: the next tcgen05.ld is warp-wide
+                if (ok && n < p.N) {
+                    const int mc = m0 + c * 32;
+                    if (p.y_f32) {
+                        float *y = static_cast<float *>(p.y) + p.col0;
 #pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (mc + j < p.M)
-                            y[size_t(mc + j) * p.N + n] = __uint_as_float(d[j]);
-                } else {
-                    __half *y = static_cast<__half *>(p.y);
+                        for (int j = 0; j < 32; j++)
+                            if (mc + j < p.M)
+                                y[size_t(mc + j) * p.ldy + n] = __uint_as_float(d[j]);
+                    } else {
+                        __half *y = static_cast<__half *>(p.y) + p.col0;
 #pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (mc + j < p.M)
-                            y[size_t(mc + j) * p.N + n] = __float2half_rn(__uint_as_float(d[j]));
+                        for (int j = 0; j < 32; j++)
+                            if (mc + j < p.M)
+                                y[size_t(mc + j) * p.ldy + n] = __float2half_rn(__uint_as_float(d[j]));
+                    }
                 }
+                __syncwarp();
             }
             if (++b == ACC_RING) {
                 b = 0;
@@ -353,13 +355,13 @@ size_t split_smem() { return size_t(STAGES) * (2 * W_BYTES + X_BYTES + RAW_BYTES
 // Block sizes 32 and 64 with fp16 scales (an f32 scale would need more than two fp16 terms).
 bool ovk_nbits_gemm_split_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w)
 {
-    static const char *pin = getenv("OVK_NBITS_GEMM");  // "split" extends it to every block size (for comparisons)
     const int64_t bs = w->block_size;
-    const bool small = bs == 32 || bs == 64 || (pin && pin[0] == 's' && (bs == 128 || bs == 256));
+    const bool small = bs == 32 || bs == 64;
     return small && w->scales_dtype == OVK_FLOAT16 && split_smem() <= ctx->smem_optin;
 }
 
-int32_t ovk_nbits_gemm_split(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, int64_t m, void *y, int32_t y_dtype)
+int32_t ovk_nbits_gemm_split(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, int64_t m, void *y, int32_t y_dtype,
+                             int64_t ldy, int64_t col0)
 {
     ovk_nbits_weight *w = const_cast<ovk_nbits_weight *>(wc);  // the prefill copy is built lazily
     int32_t rc = ovk_nbits_gemm_prepack(ctx, w);
@@ -377,6 +379,8 @@ int32_t ovk_nbits_gemm_split(ovk_ctx *ctx, const ovk_nbits_weight *wc, const voi
     p.y = y;
     p.M = int(m);
     p.N = int(w->n);
+    p.ldy = int(ldy);
+    p.col0 = int(col0);
     p.n_pad = int(w->gemm_n_pad);
     p.zp_pitch = int(w->gemm_zp_pitch);
     p.slabs = int(w->gemm_k_pad / SLAB);

@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "ovk_cuda.h"
+#include "comm.cuh"
 
 // Device-side error codes written to ovk_ctx::dev_status by bounded waits.
 enum : int {
@@ -21,6 +22,8 @@ enum : int {
     OVK_DEV_TIMEOUT_MMA = 2,   // the epilogue gave up waiting for the tensor core
     OVK_DEV_TIMEOUT_SLOT = 3,  // a producer gave up waiting for a free stage
     OVK_DEV_BAD_INDEX = 4,     // a gather index read on the device fell outside the table
+    OVK_DEV_TIMEOUT_PEER = 5,  // a flag another GPU writes never reached the expected value
+    OVK_DEV_TIMEOUT_SELFTEST = 6,  // ovk_selftest_device_timeout: the wait that is meant to run out
 };
 
 struct ovk_ctx {
@@ -40,7 +43,19 @@ struct ovk_ctx {
     void *scratch = nullptr;         // grow-on-demand workspace (row sums, NHWC staging, ...)
     size_t scratch_bytes = 0;
     cudaEvent_t t0 = nullptr, t1 = nullptr;
+    int clock_khz = 0;
+    // the GPUs of one box this context exchanges results with (ovk_comm_init); world == 0: none
+    struct {
+        int rank = 0, world = 0;
+        uint32_t epoch = 0;  // number of collective calls made so far; the same on every rank
+        OvkCommFlags *flags[OVK_MAX_RANKS] = {};
+        long long wait_cycles = 2000000000ll;  // about a second
+    } comm;
+    // MatMulNBits prefill with K ranges shared between CTAs: one arrival counter per output tile,
+    // zero between launches (the CTA that arrives last at a tile resets it)
+    uint32_t *tile_counters = nullptr;
 };
+constexpr int OVK_TILE_COUNTERS = 65536;
 
 constexpr int OVK_PARAM_FLOATS = 16384;
 
@@ -80,6 +95,11 @@ int32_t ovk_scratch(ovk_ctx *ctx, size_t bytes, void **out);
         if (e_ != cudaSuccess)                                                         \
             return ovk_fail((ctx), OVK_BACKEND, "%s: %s", (name), cudaGetErrorString(e_)); \
     } while (0)
+
+// Starts the next collective call on this context: bumps the call number and describes the peers to a kernel.
+OvkCommView ovk_comm_next(ovk_ctx *ctx);
+// Enqueues the wait for every peer's `done` announcement of call `view.epoch`.
+int32_t ovk_comm_wait_done(ovk_ctx *ctx, const OvkCommView &view);
 
 static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

@@ -349,8 +349,9 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                     if (lane == 0)
                         umma::mbar_arrive(&acc_empty[b]);
                 }
-                if (!valid)
-                    continue;
+                // lanes on padding positions store nothing; they skip the block below and meet the others at
+                // the __syncwarp that closes it, so the warp is whole again before the next warp-wide tcgen05.ld
+                if (valid) {
                 // constants of the 16 channels: four 128-bit shared loads each
                 int32_t corr[16];
                 float ratio[16];
@@ -402,6 +403,8 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                         o += plane;
                     }
                 }
+                }
+                __syncwarp();
             }
         }
         if (p.epi.mode == EPI_SCALE)

@@ -80,14 +80,15 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t *bar, uint32_t parit
         : "memory");
     return ok != 0;
 }
-// Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
+// Returns false when `limit` attempts have run out.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t *bar, uint32_t parity, uint32_t limit)
 {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++)
+    for (uint32_t i = 0; i < limit; i++)
         if (mbar_try_wait(bar, parity))
             return true;
     return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) { return mbar_wait_limit(bar, parity, WAIT_LIMIT); }
 
 // ----------------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *t)

@@ -141,6 +141,8 @@ Result matmul_nbits(Env &env, const NodeIr &node)
                                                             zp ? zp->dev : nullptr, n, k, node.int_attr("bits", 0), bs,
                                                             OVK_NBITS_DEFAULT, &w)));
         it = env.nbits_weights.emplace(node.inputs[1], w).first;
+        // the weight object points into the scale and zero-point tensors too
+        env.nbits_deps[node.inputs[1]] = {node.inputs[2], zp ? node.inputs[3] : std::string()};
     }
     std::vector<int64_t> out_shape(a->shape.begin(), a->shape.end() - 1);
     out_shape.push_back(n);
@@ -875,8 +877,36 @@ Result Env::host(const std::string &name, std::vector<uint8_t> *out, int32_t *dt
     return from_abi(ctx_, ovk_download(ctx_, t->dev, 0, out->data(), t->bytes));
 }
 
+// A weight prepared from this name holds pointers into the tensor's device
+// buffer (MatMulNBits) or a packed copy of its bytes (MatMulInteger, the
+// convolutions): both die with the tensor, and the next node that names it
+// prepares the weight again from the new contents.  The destroy calls wait for
+// the stream, so no kernel still reads what is freed here.
 void Env::release(const std::string &name)
 {
+    for (auto dep = nbits_deps.begin(); dep != nbits_deps.end();) {
+        const bool hit = dep->first == name || dep->second.first == name || dep->second.second == name;
+        if (hit) {
+            auto nb = nbits_weights.find(dep->first);
+            if (nb != nbits_weights.end()) {
+                ovk_nbits_weight_destroy(ctx_, nb->second);
+                nbits_weights.erase(nb);
+            }
+            dep = nbits_deps.erase(dep);
+        } else {
+            ++dep;
+        }
+    }
+    auto mm = mmi_weights.find(name);
+    if (mm != mmi_weights.end()) {
+        ovk_mmi_weight_destroy(ctx_, mm->second);
+        mmi_weights.erase(mm);
+    }
+    auto qc = qconv_weights.find(name);
+    if (qc != qconv_weights.end()) {
+        ovk_qconv_weight_destroy(ctx_, qc->second);
+        qconv_weights.erase(qc);
+    }
     auto it = tensors_.find(name);
     if (it == tensors_.end())
         return;

@@ -17,6 +17,7 @@
 #include <cstdint>
 #include <map>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "ovk_cuda.h"
@@ -86,6 +87,8 @@ public:
     std::map<std::string, ovk_nbits_weight *> nbits_weights;
     std::map<std::string, ovk_mmi_weight *> mmi_weights;
     std::map<std::string, ovk_qconv_weight *> qconv_weights;
+    // MatMulNBits weight name -> the scale and zero-point tensors its object points into
+    std::map<std::string, std::pair<std::string, std::string>> nbits_deps;
 
 private:
     ovk_ctx *ctx_;

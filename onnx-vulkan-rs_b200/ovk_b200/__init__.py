@@ -20,6 +20,7 @@ FLOAT, UINT8, INT8, INT32, INT64, FLOAT16 = 1, 2, 3, 6, 7, 10
 OK, INVALID_ARGUMENT, UNSUPPORTED, BACKEND, TIMEOUT = 0, 1, 2, 3, 4
 EPILOGUE_RELU, EPILOGUE_RANGE = 1, 2
 NBITS_NO_DECODE_COPY = 1
+COMM_HANDLE_BYTES = 64
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(_PKG, "libovk_cuda.so")
@@ -48,6 +49,8 @@ SIGNATURES = {
     "ovk_last_kernel": (C.c_char_p, [_P]),
     "ovk_launch_count": (C.c_uint64, [_P]),
     "ovk_stream": (_P, [_P]),
+    "ovk_workspace_bytes": (_SZ, [_P]),
+    "ovk_selftest_device_timeout": (_I32, [_P]),
     "ovk_flush": (_I32, [_P]),
     "ovk_alloc": (_I32, [_P, _SZ, C.POINTER(_P)]),
     "ovk_free": (_I32, [_P, _P]),
@@ -60,6 +63,16 @@ SIGNATURES = {
     "ovk_nbits_weight_destroy": (None, [_P, _P]),
     "ovk_matmul_nbits": (_I32, [_P, _P, _P, _I32, _I64, _P, _I32]),
     "ovk_matmul_nbits_group": (_I32, [_P, _I32, C.POINTER(_P), _P, _I32, _I64, C.POINTER(_P), _I32]),
+    "ovk_comm_flag_bytes": (_SZ, []),
+    "ovk_comm_alloc": (_I32, [_P, _SZ, C.POINTER(_P)]),
+    "ovk_comm_export": (_I32, [_P, _P, _P]),
+    "ovk_comm_import": (_I32, [_P, _P, C.POINTER(_P)]),
+    "ovk_comm_release": (_I32, [_P, _P]),
+    "ovk_comm_init": (_I32, [_P, _I32, _I32, C.POINTER(_P)]),
+    "ovk_comm_set_timeout_ms": (_I32, [_P, _I32]),
+    "ovk_comm_barrier": (_I32, [_P]),
+    "ovk_allgather_cols": (_I32, [_P, _P, _I32, _I64, _I64, _I64, _I64, C.POINTER(_P)]),
+    "ovk_matmul_nbits_nsplit": (_I32, [_P, _P, _P, _I32, _I64, _I64, _I64, C.POINTER(_P), _I32]),
     "ovk_dynamic_quantize": (_I32, [_P, _P, _I64, _P, _P, _P]),
     "ovk_mmi_prepack": (_I32, [_P, _P, _I32, _I64, _I64, C.POINTER(_P)]),
     "ovk_mmi_weight_destroy": (None, [_P, _P]),
@@ -166,6 +179,14 @@ class Context:
     def launches(self) -> int:
         return int(lib().ovk_launch_count(self.h))
 
+    @property
+    def workspace_bytes(self) -> int:
+        return int(lib().ovk_workspace_bytes(self.h))
+
+    def selftest_device_timeout(self):
+        """Enqueues the wait that is meant to run out; the next flush raises with status TIMEOUT."""
+        self.check(lib().ovk_selftest_device_timeout(self.h))
+
     # ---------------------------------------------------------- MatMulNBits
     def nbits_prepack(self, b, scales, zero_points, n, k, block_size, bits=4, flags=0):
         return NBitsWeight(self, b, scales, zero_points, n, k, block_size, bits, flags)
@@ -191,6 +212,49 @@ class Context:
         yp = (_P * len(ws))(*[_ptr(o) for o in outs])
         self.check(lib().ovk_matmul_nbits_group(self.h, len(ws), wp, _ptr(a), _dtype_code(a), m, yp, _dtype_code(outs[0])))
         return outs
+
+    # --------------------------------------------- several GPUs of one box
+    def comm_alloc(self, nbytes: int) -> int:
+        """A zero-filled device buffer that other ranks may map (ovk_comm_alloc); returns its address."""
+        p = _P()
+        self.check(lib().ovk_comm_alloc(self.h, nbytes, C.byref(p)))
+        return p.value
+
+    def comm_export(self, ptr: int) -> bytes:
+        buf = C.create_string_buffer(COMM_HANDLE_BYTES)
+        self.check(lib().ovk_comm_export(self.h, _P(ptr), buf))
+        return buf.raw
+
+    def comm_import(self, handle: bytes) -> int:
+        p = _P()
+        self.check(lib().ovk_comm_import(self.h, C.c_char_p(handle), C.byref(p)))
+        return p.value
+
+    def comm_release(self, ptr: int):
+        self.check(lib().ovk_comm_release(self.h, _P(ptr)))
+
+    def comm_init(self, rank: int, world: int, flag_blocks):
+        arr = (_P * world)(*[int(b) for b in flag_blocks])
+        self.check(lib().ovk_comm_init(self.h, rank, world, arr))
+        self.rank, self.world = rank, world
+
+    def comm_set_timeout_ms(self, ms: int):
+        self.check(lib().ovk_comm_set_timeout_ms(self.h, int(ms)))
+
+    def comm_barrier(self):
+        self.check(lib().ovk_comm_barrier(self.h))
+
+    def allgather_cols(self, y_shard, m, n_shard, col0, n_total, y_peers, dtype=FLOAT16):
+        """y_shard: a [m, n_shard] tensor, or None when the block already sits in this rank's matrix."""
+        arr = (_P * len(y_peers))(*[int(p) for p in y_peers])
+        self.check(lib().ovk_allgather_cols(self.h, _ptr(y_shard), dtype if y_shard is None else _dtype_code(y_shard),
+                                            m, n_shard, col0, n_total, arr))
+
+    def matmul_nbits_nsplit(self, w: "NBitsWeight", a, col0, n_total, y_peers, y_dtype=FLOAT16):
+        """This rank's columns [col0, col0 + w.n) of Y = A x dequant(B), stored into every rank's matrix."""
+        m = a.numel() // w.k
+        arr = (_P * len(y_peers))(*[int(p) for p in y_peers])
+        self.check(lib().ovk_matmul_nbits_nsplit(self.h, w.h, _ptr(a), _dtype_code(a), m, col0, n_total, arr, y_dtype))
 
     # ------------------------------------------------- DynamicQuantizeLinear
     def dynamic_quantize(self, x):

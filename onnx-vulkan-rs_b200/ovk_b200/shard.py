@@ -112,3 +112,77 @@ def ready_handshake(store, world: int, rank: int, step: int, timeout_s: float = 
             missing.append(r)
     if missing:
         raise RankFailure(f"step {step}: ranks {missing} did not reach the exchange within {timeout_s} s")
+
+
+# ---------------------------------------------------------------------------
+# Exchange through peer memory: every rank's Y (and one flag block per rank) is
+# mapped into every process, and the kernels store into all of them.
+
+class DeviceBlock:
+    """A device buffer from ``Context.comm_alloc`` seen as a torch tensor
+    (through ``__cuda_array_interface__``; torch neither owns nor frees it)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.ptr = ptr
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+    def tensor(self, device):
+        import torch
+        return torch.as_tensor(self, device=device)
+
+
+def gather_handles(handle: bytes, world: int, group=None):
+    """Every rank's 64-byte handle, in rank order (host plumbing: one all-gather of bytes)."""
+    import torch.distributed as dist
+    if world == 1:
+        return [handle]
+    out = [None] * world
+    dist.all_gather_object(out, handle, group=group)
+    return out
+
+
+def peer_table(handles, rank: int, own_ptr: int, import_handle):
+    """Addresses of every rank's buffer as THIS process sees them: its own
+    pointer for itself, a mapping of the peer's handle for the others."""
+    if not 0 <= rank < len(handles):
+        raise ValueError(f"rank {rank} of {len(handles)}")
+    return [own_ptr if r == rank else import_handle(h) for r, h in enumerate(handles)]
+
+
+class PeerGroup:
+    """The ranks of one box as one context sees them.  ``symmetric(nbytes)``
+    allocates the same buffer on every rank and returns its address on each;
+    the constructor does that once for the flag blocks and calls
+    ``ovk_comm_init``.  Collective: every rank builds its group, and makes its
+    ``symmetric`` calls, in the same order."""
+
+    def __init__(self, ctx, rank: int, world: int, group=None):
+        import ovk_b200
+        self.ctx, self.rank, self.world, self.group = ctx, rank, world, group
+        self._mapped, self._owned = [], []
+        flags = self.symmetric(int(ovk_b200.lib().ovk_comm_flag_bytes()))
+        ctx.comm_init(rank, world, flags)
+
+    def symmetric(self, nbytes: int):
+        own = self.ctx.comm_alloc(nbytes)
+        self._owned.append(own)
+        handles = gather_handles(self.ctx.comm_export(own), self.world, self.group)
+
+        def mapped(h):
+            p = self.ctx.comm_import(h)
+            self._mapped.append(p)
+            return p
+        return peer_table(handles, self.rank, own, mapped)
+
+    def close(self):
+        import ovk_b200
+        for p in self._mapped:
+            self.ctx.comm_release(p)
+        self._mapped = []
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier(group=self.group)  # nobody frees a buffer a peer still has mapped
+        for p in self._owned:
+            self.ctx.check(ovk_b200.lib().ovk_free(self.ctx.h, p))
+        self._owned = []

@@ -97,3 +97,28 @@ def test_unaligned_activations_take_the_general_paths():
     xbuf[1:1 + x.size] = dev(x).reshape(-1)
     got = ctx().conv_integer(cw, xbuf[1:1 + x.size].reshape(x.shape), 129, 0, pads=(1, 1, 1, 1))
     assert np.array_equal(host(got), orc.conv_integer(x, wt, 129, 0, pads=(1, 1, 1, 1)))
+
+
+def test_a_device_wait_that_runs_out_is_reported_and_the_context_stays_usable():
+    """Every wait inside the kernels has a limit; when one runs out the thread
+    records a code in the context's status word and the kernel ends.  Here the
+    wait is made to run out on purpose - one thread, a barrier nothing arrives at,
+    1000 polls - and the report is followed end to end: the next flush returns
+    OVK_TIMEOUT and names the wait, the flush after that is clean, and an operator
+    on the same context is still exact."""
+    c = ovk_b200.Context(0)
+    c.selftest_device_timeout()
+    with pytest.raises(ovk_b200.OvkError) as e:
+        c.flush()
+    assert e.value.status == ovk_b200.TIMEOUT
+    assert "self-test" in e.value.message and "code 6" in e.value.message
+    c.flush()  # the status word was cleared by the report
+    a = cases.lcg_bytes_fast(200 * 256, 41).reshape(200, 256)
+    b = cases.lcg_bytes_fast(256 * 96, 43).reshape(256, 96).view(np.int8)
+    w = c.mmi_prepack(dev(b))
+    got = c.matmul_integer(w, dev(a), dev(np.array([131], dtype=np.uint8)), None)
+    c.flush()
+    assert c.last_kernel.startswith("mmi_tc")
+    assert np.array_equal(got.cpu().numpy(), orc.matmul_integer(a, b, 131, 0))
+    del w
+    c.close()

@@ -326,3 +326,52 @@ def test_quantized_residual_tail_as_nodes(hl, env):
     with pytest.raises(hl.OvkError) as err:
         env.execute(hl.Node("MaxPool", ["f"], ["g"], kernel_shape=[2, 2]))
     assert err.value.status == 2
+
+
+def test_replacing_an_initializer_rebuilds_its_prepared_weight(hl, env):
+    """Weights are prepared once per initializer NAME (cache.rs:231).  When the
+    environment replaces a tensor under that name the prepared weight must go
+    with it: a MatMulNBits weight points into the old device buffers (also those
+    of its scales), the MatMulInteger and convolution weights hold a packed copy
+    of the old bytes."""
+    # MatMulNBits: new nibbles, then new scales only
+    a, nib, zp, scale = cases.nbits_synthetic(31, 2, 128, 48, 32)
+    set_nbits(env, a, nib, zp, scale, 32)
+    node = hl.Node("MatMulNBits", ["a", "quant", "scales", "zp"], ["y"], K=128, N=48, bits=4, block_size=32)
+    env.execute(node)
+    env.host("y")
+    _, nib2, zp2, scale2 = cases.nbits_synthetic(32, 2, 128, 48, 32)
+    env.set("quant", orc.pack_nibbles(nib2, 32), initializer=True)
+    env.execute(node)
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib2, 32), scale, orc.pack_zero_points(zp), 128, 48, 32)
+    assert_close(env.host("y"), want, 1e-3, 1e-3, "after replacing the nibbles")
+    env.set("scales", scale2.reshape(-1), initializer=True)
+    env.execute(node)
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib2, 32), scale2, orc.pack_zero_points(zp), 128, 48, 32)
+    assert_close(env.host("y"), want, 1e-3, 1e-3, "after replacing the scales")
+
+    # MatMulInteger
+    xa = cases.lcg_bytes_fast(40 * 64, 3).reshape(40, 64)
+    b1 = cases.lcg_bytes_fast(64 * 24, 4).reshape(64, 24).view(np.int8)
+    b2 = cases.lcg_bytes_fast(64 * 24, 5).reshape(64, 24).view(np.int8)
+    env.set("xa", xa)
+    env.set("b", b1, initializer=True)
+    mm = hl.Node("MatMulInteger", ["xa", "b"], ["acc"])
+    env.execute(mm)
+    assert np.array_equal(env.host("acc"), orc.matmul_integer(xa, b1, 0, 0))
+    env.set("b", b2, initializer=True)
+    env.execute(mm)
+    assert np.array_equal(env.host("acc"), orc.matmul_integer(xa, b2, 0, 0))
+
+    # ConvInteger
+    x = cases.lcg_bytes_fast(32 * 12 * 12, 6).reshape(1, 32, 12, 12)
+    w1 = cases.lcg_bytes_fast(16 * 32 * 9, 7).reshape(16, 32, 3, 3).view(np.int8)
+    w2 = cases.lcg_bytes_fast(16 * 32 * 9, 8).reshape(16, 32, 3, 3).view(np.int8)
+    env.set("x", x)
+    env.set("w", w1, initializer=True)
+    cv = hl.Node("ConvInteger", ["x", "w"], ["c"], kernel_shape=[3, 3], pads=[1, 1, 1, 1])
+    env.execute(cv)
+    assert np.array_equal(env.host("c"), orc.conv_integer(x, w1, 0, 0, pads=(1, 1, 1, 1)))
+    env.set("w", w2, initializer=True)
+    env.execute(cv)
+    assert np.array_equal(env.host("c"), orc.conv_integer(x, w2, 0, 0, pads=(1, 1, 1, 1)))

@@ -10,6 +10,9 @@ from gpu_util import assert_close, ctx, dev, host
 
 pytestmark = pytest.mark.gpu
 
+# the prefill kernel with per-block scaling: CTAs take whole tiles, or runs of quantization blocks that may share a tile
+PER_BLOCK = ("nbits_gemm_tc", "nbits_gemm_tc_shared_k")
+
 
 def run_gpu(a, nib, zp, scale, k, n, bs, out_dtype=None, flags=0):
     b = dev(orc.pack_nibbles(nib, bs))
@@ -126,13 +129,11 @@ def test_refusals_match_the_reference_predicate():
 def test_prefill_against_the_oracle(k, n, bs, m):
     """M > 8 takes the tensor-core dequant-GEMM; fp16, atol=rtol=1e-3.  The
     Gemma3-shaped projections at M=512 are config 2's prefill case."""
-    if m == 512 and k * n > 1152 * 6912:
-        pytest.skip("covered by the sampled full-size test")
     a, nib, zp, scale = cases.nbits_synthetic(2, m, k, n, bs)
     got, kern = run_gpu(a, nib, zp, scale, k, n, bs)
     # blocks of 32 and 64 with fp16 scales: the scale goes into the weight as two exact fp16 terms;
     # larger blocks: integer weights, each block's partial sum scaled in f32
-    assert kern == ("nbits_gemm_tc_split" if bs <= 64 else "nbits_gemm_tc")
+    assert kern == "nbits_gemm_tc_split" if bs <= 64 else kern in PER_BLOCK
     want = orc.matmul_nbits(a, orc.pack_nibbles(nib, bs), scale, orc.pack_zero_points(zp), k, n, bs)
     assert_close(got, want, 1e-3, 1e-3, f"prefill {k}->{n} bs={bs} M={m}")
 
@@ -146,7 +147,7 @@ def test_prefill_every_token_tile_width(m, bs):
     k, n = 512, 150 * 128
     a, nib, zp, scale = cases.nbits_synthetic(5, m, k, n, bs)
     got, kern = run_gpu(a, nib, zp, scale, k, n, bs)
-    assert kern == "nbits_gemm_tc"
+    assert kern in PER_BLOCK
     cols = np.r_[0:130, 9000:9130, n - 130:n]  # the first, a middle and the last weight tiles
     want = orc.matmul_nbits(a, orc.pack_nibbles(nib[cols], bs), scale[cols], orc.pack_zero_points(zp[cols]), k,
                             cols.size, bs)
@@ -173,7 +174,7 @@ def test_prefill_small_blocks_with_f32_scales_keep_the_per_block_kernel(m, k, n,
     a, nib, zp, scale = cases.nbits_synthetic(6, m, k, n, bs)
     scale32 = (scale.astype(np.float32) * np.float32(1.0001)).astype(np.float32)
     got, kern = run_gpu(a, nib, zp, scale32, k, n, bs)
-    assert kern == "nbits_gemm_tc"
+    assert kern in PER_BLOCK
     want = orc.matmul_nbits(a, orc.pack_nibbles(nib, bs), scale32, orc.pack_zero_points(zp), k, n, bs)
     assert_close(got, want, 1e-3, 1e-3, "prefill, f32 scales")
 
@@ -183,7 +184,7 @@ def test_prefill_per_block_kernel_f32_output_and_ragged_k(m, k, n, bs):
     """K that ends inside a quantization block, f32 output (atol = rtol = 1e-4)."""
     a, nib, zp, scale = cases.nbits_synthetic(6, m, k, n, bs)
     got, kern = run_gpu(a, nib, zp, scale, k, n, bs, out_dtype=torch.float32)
-    assert kern == "nbits_gemm_tc" and got.dtype == np.float32
+    assert kern in PER_BLOCK and got.dtype == np.float32
     want = orc.matmul_nbits(a, orc.pack_nibbles(nib, bs), scale, orc.pack_zero_points(zp), k, n, bs,
                             out_dtype=np.float32)
     assert_close(got, want, 1e-4, 1e-4, "prefill f32 out, ragged K")
@@ -203,13 +204,65 @@ def test_qwen_prefill_full_size_sampled():
     m, k, n, bs = 4096, 3584, 18944, 128
     a, nib, zp, scale = cases.nbits_synthetic(5, m, k, n, bs, scale_lo=0.001, scale_hi=0.01)
     got, kern = run_gpu(a, nib, zp, scale, k, n, bs)
-    assert kern == "nbits_gemm_tc"
+    assert kern in PER_BLOCK
     rows = np.arange(5, m, 86)
     cols = np.arange(3, n, 64)
     want = orc.matmul_nbits(a[rows], orc.pack_nibbles(nib[cols], bs), scale[cols],
                             orc.pack_zero_points(zp[cols]), k, cols.size, bs)
     assert_close(got[np.ix_(rows, cols)], want, 1e-3, 1e-3, "qwen gate/up prefill")
     assert np.isfinite(got.astype(np.float32)).all()
+
+
+def _sampled(a, nib, zp, scale, k, bs, rows, cols):
+    return orc.matmul_nbits(a[rows], orc.pack_nibbles(nib[cols], bs), scale[cols], orc.pack_zero_points(zp[cols]), k,
+                            cols.size, bs)
+
+
+def test_qwen_down_projection_full_size_sampled():
+    """Config 5's down projection at M=4096: K=18944 N=3584 bs=128 - the longest K of
+    the configurations, 148 quantization blocks summed per output, where error
+    accumulated over K is largest.  48 token rows x 299 weight columns spread over
+    every tile, atol = rtol = 1e-3 (fp16 out)."""
+    m, k, n, bs = 4096, 18944, 3584, 128
+    a, nib, zp, scale = cases.nbits_synthetic(5, m, k, n, bs, scale_lo=0.001, scale_hi=0.01)
+    got, kern = run_gpu(a, nib, zp, scale, k, n, bs)
+    assert kern in PER_BLOCK
+    rows, cols = np.arange(5, m, 86), np.arange(3, n, 12)
+    assert_close(got[np.ix_(rows, cols)], _sampled(a, nib, zp, scale, k, bs, rows, cols), 1e-3, 1e-3, "qwen down prefill")
+    assert np.isfinite(got.astype(np.float32)).all()
+
+
+def test_qwen_lm_head_full_size_sampled():
+    """Config 5's lm_head at M=4096: K=3584 N=152064 bs=128 (a 1.25 GB fp16 output);
+    48 token rows x 298 weight columns spread over the 1188 weight tiles."""
+    m, k, n, bs = 4096, 3584, 152064, 128
+    a, nib, zp, scale = cases.nbits_synthetic(5, m, k, n, bs, scale_lo=0.001, scale_hi=0.01)
+    b = dev(orc.pack_nibbles(nib, bs)); s = dev(scale.reshape(-1)); z = dev(orc.pack_zero_points(zp))
+    w = ctx().nbits_prepack(b, s, z, n, k, bs)
+    y = ctx().matmul_nbits(w, dev(a))
+    assert ctx().last_kernel in PER_BLOCK
+    rows, cols = np.arange(5, m, 86), np.arange(3, n, 511)
+    ctx().flush()
+    got = y[torch.from_numpy(rows).cuda()][:, torch.from_numpy(cols).cuda()].cpu().numpy()
+    assert_close(got, _sampled(a, nib, zp, scale, k, bs, rows, cols), 1e-3, 1e-3, "qwen lm_head prefill")
+    assert bool(torch.isfinite(y).all())
+
+
+def test_gemma_lm_head_prefill_full_size_sampled():
+    """Config 2's lm_head at M=512: K=1152 N=262144 bs=32 with fp16 scales, the shape
+    the two-term-scale kernel is benchmarked on; 32 token rows x 512 weight columns
+    spread over the 2048 weight tiles, and every output finite."""
+    m, k, n, bs = 512, 1152, 262144, 32
+    a, nib, zp, scale = cases.nbits_synthetic(2, m, k, n, bs)
+    b = dev(orc.pack_nibbles(nib, bs)); s = dev(scale.reshape(-1)); z = dev(orc.pack_zero_points(zp))
+    w = ctx().nbits_prepack(b, s, z, n, k, bs)
+    y = ctx().matmul_nbits(w, dev(a))
+    assert ctx().last_kernel == "nbits_gemm_tc_split"
+    rows, cols = np.arange(3, m, 16), np.arange(5, n, 512)
+    ctx().flush()
+    got = y[torch.from_numpy(rows).cuda()][:, torch.from_numpy(cols).cuda()].cpu().numpy()
+    assert_close(got, _sampled(a, nib, zp, scale, k, bs, rows, cols), 1e-3, 1e-3, "gemma lm_head prefill")
+    assert bool(torch.isfinite(y).all())
 
 
 @pytest.mark.parametrize("shapes,m", [(((1152, 1024), (1152, 256), (1152, 256)), 1), (((1152, 6912), (1152, 6912)), 1),

@@ -90,6 +90,17 @@ def _failure_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
+def _peer_table_worker(rank, world, port, out):
+    _init(rank, world, port)
+    from ovk_b200 import shard
+    # a 64-byte handle as cudaIpcGetMemHandle would give it, here just tagged with its rank
+    handle = bytes([rank]) * 64
+    handles = shard.gather_handles(handle, world)
+    table = shard.peer_table(handles, rank, own_ptr=0x1000 + rank, import_handle=lambda h: 0x9000 + h[0])
+    out[rank] = (handles == [bytes([r]) * 64 for r in range(world)], table)
+    dist.destroy_process_group()
+
+
 def _run(worker, world=2):
     mgr = mp.Manager()
     out = mgr.dict()
@@ -122,3 +133,14 @@ def test_batch_split_conv_needs_no_exchange():
 def test_a_rank_that_fails_before_the_exchange_is_reported_on_the_host():
     out = _run(_failure_worker)
     assert "ranks [1] did not reach the exchange" in out[0]
+
+
+def test_handles_travel_in_rank_order_and_a_rank_keeps_its_own_pointer():
+    """The host plumbing of the peer-memory exchange: one all-gather of the 64-byte
+    handles; a rank's table holds its own pointer at its own index and a mapping of
+    each peer's handle elsewhere."""
+    out = _run(_peer_table_worker, world=3)
+    for rank in range(3):
+        in_order, table = out[rank]
+        assert in_order
+        assert table == [0x1000 + rank if r == rank else 0x9000 + r for r in range(3)]
