@@ -48,6 +48,11 @@ def nbits_bytes(m, k, n, bs, real_bytes=2, with_zp=True):
         m * k * real_bytes + m * n * real_bytes
 
 
+def ovk_int8_code():
+    import ovk_b200
+    return ovk_b200.INT8
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -121,14 +126,31 @@ class ClockSampler:
 
 # --------------------------------------------------------------------- GPU arm
 
-def make_weight(torch, ctx, k, n, bs, gen, scale_lo=0.002, scale_hi=0.02, rows=None):
-    """Random int4 weight in the operator layout; `rows` keeps only a column shard."""
+def weight_tensors(torch, k, n, bs, gen, scale_lo=0.002, scale_hi=0.02):
+    """Random int4 weight in the operator layout (packed nibbles, fp16 scales, packed zero points)."""
     nb = -(-k // bs)
-    n_local = n if rows is None else rows.count
-    b = torch.randint(0, 256, (n_local, nb, bs // 2), dtype=torch.uint8, device="cuda", generator=gen)
-    scales = (torch.rand((n_local * nb,), device="cuda", generator=gen) * (scale_hi - scale_lo) + scale_lo).to(torch.float16)
-    zp = torch.randint(0, 256, (n_local, (nb + 1) // 2), dtype=torch.uint8, device="cuda", generator=gen)
-    return ctx.nbits_prepack(b, scales, zp, n_local, k, bs)
+    b = torch.randint(0, 256, (n, nb, bs // 2), dtype=torch.uint8, device="cuda", generator=gen)
+    scales = (torch.rand((n * nb,), device="cuda", generator=gen) * (scale_hi - scale_lo) + scale_lo).to(torch.float16)
+    zp = torch.randint(0, 256, (n, (nb + 1) // 2), dtype=torch.uint8, device="cuda", generator=gen)
+    return b, scales, zp
+
+
+def make_weight(torch, ctx, k, n, bs, gen, scale_lo=0.002, scale_hi=0.02):
+    b, scales, zp = weight_tensors(torch, k, n, bs, gen, scale_lo, scale_hi)
+    return ctx.nbits_prepack(b, scales, zp, n, k, bs)
+
+
+def check_against_port(torch, y, a, b, scales, zp, k, bs, rows, cols):
+    """Sampled rows x columns of Y against the CPU port of the operator (outside any timed region)."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle as orc
+    nb = -(-k // bs)
+    ci, ri = torch.from_numpy(cols).cuda(), torch.from_numpy(rows).cuda()
+    want = orc.matmul_nbits(a[ri].cpu().numpy(), b[ci].cpu().numpy(), scales.reshape(-1, nb)[ci].cpu().numpy(),
+                            zp[ci].cpu().numpy(), k, cols.size, bs).astype(np.float64)
+    got = y[ri][:, ci].cpu().numpy().astype(np.float64)
+    return bool(np.all(np.abs(got - want) <= 1e-3 + 1e-3 * np.abs(want)))
 
 
 def timed(torch, dist, world, fn, iters, warm=3):
@@ -160,25 +182,69 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
     bf16_peak = peaks["bf16_tflops"]
 
     # ---- int4 prefill, Qwen2.5-7B-shaped (config 5), M = 4096, block 128
+    # One GPU: the plain operator.  More: every rank prepares the SAME seeded weight, keeps its column
+    # shard, and the shards are run three ways - the product alone, the product whose store warp writes
+    # every tile into every rank's Y (the exchange inside the kernel, peer stores over NVLink), and the
+    # product followed by an NCCL all-gather - next to the whole product on rank 0's GPU alone.
     m = 4096
-    for name, k, n in (("gate_up", 3584, 18944), ("down", 18944, 3584)):
-        sh = shard.column_shard(n, world, rank)
-        w = make_weight(torch, ctx, k, n, 128, gen, 0.001, 0.01, rows=sh)
+    pg = shard.PeerGroup(ctx, rank, world) if world > 1 else None
+    partitioned = {}
+    for name, k, n in (("gate_up", 3584, 18944), ("down", 18944, 3584), ("lm_head", 3584, 152064)):
+        if name == "lm_head" and world not in (1, 8):
+            continue  # a 1.25 GB output: timed on one GPU and at the full split only
+        b, scales, zp = weight_tensors(torch, k, n, 128, gen, 0.001, 0.01)
         a = torch.randn((m, k), device="cuda", generator=gen).to(torch.float16)
+        sh = shard.column_shard(n, world, rank)
+        bs_, ss_, zs_ = shard.slice_nbits_weight(b, scales, zp, k // 128, sh)
+        w = ctx.nbits_prepack(bs_.contiguous(), ss_.contiguous(), zs_.contiguous(), sh.count, k, 128)
         y = torch.empty((m, sh.count), dtype=torch.float16, device="cuda")
         ms_c = timed(torch, dist, world, lambda: ctx.matmul_nbits(w, a, out=y), 5)
         entry = {"M": m, "K": k, "N": n, "block_size": 128, "kernel": ctx.last_kernel, "ms_compute": ms_c,
                  "tflops_compute": 2.0 * m * k * n / (ms_c * 1e-3) / 1e12}
         entry["frac_of_measured_bf16_peak_per_gpu"] = entry["tflops_compute"] / world / bf16_peak
         if world > 1:
-            def step():
+            y_ptrs = pg.symmetric(m * n * 2)
+            y_full = shard.DeviceBlock(y_ptrs[rank], (m, n), "<f2").tensor("cuda")
+            ms_f = timed(torch, dist, world, lambda: ctx.matmul_nbits_nsplit(w, a, sh.start, n, y_ptrs), 5)
+            ctx.flush()  # a peer wait that ran out would raise here
+            rows = np.arange(7, m, 257)
+            cols = np.unique(np.r_[np.arange(5, n, max(1, n // 96)),
+                                   [shard.column_shard(n, world, r).start for r in range(world)],
+                                   [shard.column_shard(n, world, r).stop - 1 for r in range(world)]])
+            ok = check_against_port(torch, y_full, a, b, scales, zp, k, 128, rows, cols) if rank == 0 else True
+
+            def nccl_step():
                 ctx.matmul_nbits(w, a, out=y)
                 shard.all_gather_columns(y, n, world)
-            ms_e = timed(torch, dist, world, step, 5)
-            entry.update({"ms_with_all_gather": ms_e, "tflops_with_all_gather": 2.0 * m * k * n / (ms_e * 1e-3) / 1e12,
-                          "parallelism": "N-split x%d + NCCL all-gather of fp16 outputs" % world})
+            ms_n = timed(torch, dist, world, nccl_step, 3) if name != "lm_head" else None
+            # the whole product on one GPU, in the same run (rank 0 works, the others wait at the barrier)
+            ms_1 = torch.zeros(1, device="cuda")
+            if rank == 0:
+                w1 = ctx.nbits_prepack(b, scales, zp, n, k, 128)
+                y1 = torch.empty((m, n), dtype=torch.float16, device="cuda")
+                ms_1[0] = timed(torch, dist, 1, lambda: ctx.matmul_nbits(w1, a, out=y1), 5)
+                del w1, y1
+            dist.broadcast(ms_1, 0)
+            ms_1 = float(ms_1.item())
+            entry.update({"ms_with_exchange_in_kernel": ms_f, "tflops_with_exchange": 2.0 * m * k * n / (ms_f * 1e-3) / 1e12,
+                          "ms_with_nccl_all_gather": ms_n, "ms_one_gpu_same_run": ms_1,
+                          "parallelism": "N-split x%d; the kernel's store warp writes each tile into every rank's Y "
+                                         "(peer stores over NVLink), one flag per peer ends the step" % world})
+            recv = (world - 1) / world * m * n * 2
+            partitioned[name] = {"ms_one_gpu": ms_1, "ms_compute": ms_c, "ms_e2e": ms_f, "ms_e2e_nccl": ms_n,
+                                 "speedup_compute": ms_1 / ms_c, "speedup_e2e": ms_1 / ms_f,
+                                 "speedup_e2e_nccl": (ms_1 / ms_n) if ms_n else None,
+                                 "received_bytes_per_gpu": recv, "received_gbs_per_gpu": recv / (ms_f * 1e-3) / 1e9,
+                                 "parity_checked": ok, "parity_sample": "%d rows x %d columns of the gathered Y on rank 0 "
+                                 "against the CPU port, atol = rtol = 1e-3" % (rows.size, cols.size)}
+            del y_full
         out["int4_prefill_qwen7b_" + name] = entry
-        del w, a, y
+        del w, a, y, b, scales, zp, bs_, ss_, zs_
+        torch.cuda.empty_cache()
+    if pg is not None:
+        torch.cuda.synchronize()
+        pg.close()
+        out["partitioned"] = partitioned
     # ---- int4 prefill, Gemma3-1B-shaped lm_head (config 2), M = 512, block 32: rank-local
     if world == 1:
         w = make_weight(torch, ctx, HIDDEN, VOCAB, BLOCK, gen)
@@ -247,8 +313,29 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
     xa = torch.randint(0, 256, (8192, 8192), dtype=torch.uint8, device="cuda", generator=gen)
     zp8 = torch.full((1,), 128, dtype=torch.uint8, device="cuda")
     ms_b = timed(torch, dist, world, lambda: ctx.matmul_integer(big, xa, zp8, None), 5)
-    out["int8_gemm_8192"] = {"ms": ms_b, "kernel": ctx.last_kernel, "tops_per_gpu": 2.0 * 8192 ** 3 / (ms_b * 1e-3) / 1e12,
-                             "frac_of_2x_measured_bf16_peak": 2.0 * 8192 ** 3 / (ms_b * 1e-3) / 1e12 / (2 * bf16_peak)}
+    # the dense int8 peak, measured here: what back-to-back kind::i8 MMAs deliver per clock per SM, times
+    # the SMs, times the clock the GPU held while this GEMM ran (sampled by nvidia-smi during a second run)
+    mac_rate = ctx.probe_mma_rate(ovk_int8_code())
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    skip = sampler.wait_first_sample(lambda: (ctx.matmul_integer(big, xa, zp8, None), torch.cuda.synchronize()))
+    w0 = time.perf_counter()
+    while time.perf_counter() - w0 < 0.5:
+        for _ in range(4):
+            ctx.matmul_integer(big, xa, zp8, None)
+        torch.cuda.synchronize()
+    int8_clocks = sampler.stop(skip)
+    sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    mhz = int8_clocks.get("sm_mhz") or 1965.0
+    int8_peak = 2.0 * mac_rate * sm_count * mhz * 1e6 / 1e12
+    out["int8_peak_tops_measured"] = {"value": int8_peak, "mac_per_clk_per_sm": mac_rate, "sms": sm_count, "sm_mhz": mhz,
+                                      "clock_reasons": int8_clocks.get("reasons"),
+                                      "how": "2 x MAC/clk/SM of back-to-back 128x256x32 tcgen05.mma kind::i8 (ovk_probe_mma_rate) "
+                                             "x SMs x the median SM clock sampled while the 8192^3 GEMM ran"}
+    tops_b = 2.0 * 8192 ** 3 / (ms_b * 1e-3) / 1e12
+    out["int8_gemm_8192"] = {"ms": ms_b, "kernel": ctx.last_kernel, "tops_per_gpu": tops_b,
+                             "frac_of_measured_int8_peak": tops_b / int8_peak,
+                             "frac_of_2x_measured_bf16_peak": tops_b / (2 * bf16_peak)}
     del ws, xs, big, xa
 
     # ---- static int8 QLinearConv, ResNet block (config 4): batch 64 split over the ranks
@@ -288,6 +375,8 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
     ops = 2.0 * 64 * 64 * 56 * 56 * 576
     out["int8_qlinear_conv_resnet_block"] = {"batch": 64, "ms": ms_q, "kernel": conv_kernel,
                                              "tops": ops / (ms_q * 1e-3) / 1e12,
+                                             "frac_of_measured_int8_peak": ops / (ms_q * 1e-3) / 1e12 / (world * int8_peak),
+                                             "frac_of_measured_hbm": 2.0 * 64 * 64 * 56 * 56 / (ms_q * 1e-3) / 1e9 / (world * peaks["hbm_gbs"]),
                                              "algorithmic_gbs": 2.0 * 64 * 64 * 56 * 56 / (ms_q * 1e-3) / 1e9,
                                              "parallelism": "batch-split x%d, no exchange" % world if world > 1 else "single"}
     return out
@@ -552,16 +641,15 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
 
     if rank == 0:
         achieved = lm_bytes / (lm_ms * 1e-3) / 1e9
-        # dram__bytes_read.sum + dram__bytes_write.sum of one lm_head launch from the ncu capture summarised
-        # in profiles/nbits_decode_lm_head.md (174.62 MB + 3.57 MB); the layout has not changed since
-        traffic = 178.19e6
+        # dram__bytes_read.sum + dram__bytes_write.sum of one lm_head launch (174.62 MB + 4.70 MB) from an ncu
+        # capture of `bench.py --one lm_head`; the weight layout that sets it has not changed since
+        traffic = 179.32e6
         line = {
             "metric": "int4_decode_gemv_hbm_gbs", "value": world * step_bytes * args.steps / (ms_total * 1e-3) / 1e9,
             "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "gemma3-1b-int4-decode: %d layers x (q,k,v,o,gate,up,down) + lm_head, M=1, "
-                                   "bits=4 block_size=32 zero points, fp16" % args.layers,
+            "config": {"workload": WORKLOAD % args.layers,
                        "gemvs_per_step": n_gemv, "bytes_per_step": step_bytes, "launch": replay,
                        "l2": "distinct weights per GEMV, %.0f MB per step > 126 MB L2 (no flush needed)" % (step_bytes / 1e6),
                        "parallelism": "replicas (the decode GEMV is single-GPU by design)" if world > 1 else "single"},
@@ -572,15 +660,19 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
                          "ms_per_launch_inside_step": lm_in_step_ms,
                          "frac_inside_step": lm_bytes / (lm_in_step_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                          "whole_step_frac": world * step_bytes * args.steps / (ms_total * 1e-3) / 1e9 / (world * peaks["hbm_gbs"]),
-                         "frac_of_nominal_8tbs": achieved / 8000.0, "traffic": traffic},
+                         "frac_of_nominal_8tbs": achieved / 8000.0, "traffic": traffic,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on "
+                                           "this shape, captured separately (not measured in this run); 1.02 x bytes_per_launch"},
             "e2e": {"value": e2e_gbs, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps},
             "gpu_launches": launches, "clocks": clocks,
         }
         if extra is not None:
+            if "partitioned" in extra:
+                line["partitioned"] = extra.pop("partitioned")
             line["extra"] = extra
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_seconds)
+            line["cpu_baseline"] = cpu_baseline(args.layers, budget_s=args.cpu_seconds)
         print(json.dumps(line), flush=True)
 
 
@@ -626,43 +718,54 @@ def run_one(which):
 
 # --------------------------------------------------------------------- CPU arm
 
-def cpu_sample(n_cols):
-    """The lm_head GEMV restricted to its first n_cols columns, f32 (the only
-    form the reference's kernel takes), seeded."""
+WORKLOAD = ("gemma3-1b-int4-decode: %d layers x (q,k,v,o,gate,up,down) + lm_head, M=1, "
+            "bits=4 block_size=32 zero points")
+
+
+def cpu_step_inputs(layers):
+    """The decode step's 7 x layers + 1 GEMVs with distinct seeded weights, in f32 (the only form the
+    reference's kernel takes): 0.5 GB of nibbles, 0.13 GB of scales."""
     import numpy as np
     rng = np.random.Generator(np.random.PCG64(0xB200 + 0x100 * 2))
-    nb = HIDDEN // BLOCK
-    b = rng.integers(0, 256, size=(n_cols, nb, BLOCK // 2), dtype=np.uint8)
-    scales = rng.uniform(0.002, 0.02, size=n_cols * nb).astype(np.float32)
-    zp = rng.integers(0, 256, size=(n_cols, (nb + 1) // 2), dtype=np.uint8)
-    a = rng.standard_normal((1, HIDDEN), dtype=np.float32)
-    return a, b, scales, zp
+    acts = {k: rng.standard_normal((1, k), dtype=np.float32) for k in (HIDDEN, Q_OUT, FF)}
+    ops = []
+    for name, k, n in [s for _ in range(layers) for s in LAYER_SHAPES] + [LM_HEAD]:
+        nb = k // BLOCK
+        b = rng.integers(0, 256, size=(n, nb, BLOCK // 2), dtype=np.uint8)
+        scales = rng.random(n * nb, dtype=np.float32) * np.float32(0.018) + np.float32(0.002)
+        zp = rng.integers(0, 256, size=(n, (nb + 1) // 2), dtype=np.uint8)
+        ops.append((acts[k], b, scales, zp, k, n))
+    byts = sum(nbits_bytes(1, k, n, BLOCK, real_bytes=4) for *_, k, n in ops)
+    return ops, byts
 
 
-def cpu_time_once(orc, sample, n_cols):
-    a, b, scales, zp = sample
+def cpu_step(orc, ops):
     t = time.perf_counter()
-    orc.matmul_nbits_f32_shader_order(a, b, scales, zp, HIDDEN, n_cols, BLOCK)
+    for a, b, scales, zp, k, n in ops:
+        orc.matmul_nbits_f32_shader_order(a, b, scales, zp, k, n, BLOCK)
     return time.perf_counter() - t
 
 
-def cpu_baseline(budget_s=12.0):
+def cpu_describe(layers, cores):
+    return ("each step = the whole decode step, %d GEMVs over distinct weights, f32, the reference's shader "
+            "arithmetic order (its CPU port, oracle/ovk_oracle.c, %d OpenMP threads); the reference's own GPU "
+            "path needs Vulkan: unavailable on this box" % (7 * layers + 1, cores))
+
+
+def cpu_baseline(layers, budget_s=12.0):
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import oracle as orc
     cores = len(os.sched_getaffinity(0))
     orc.set_num_threads(cores)
-    n_cols = VOCAB // 4
-    sample = cpu_sample(n_cols)
-    cpu_time_once(orc, sample, n_cols)  # warm-up
+    ops, byts = cpu_step_inputs(layers)
+    cpu_step(orc, ops)  # warm-up
     times, spent = [], 0.0
     while spent < budget_s and len(times) < 50:
-        dt = cpu_time_once(orc, sample, n_cols)
+        dt = cpu_step(orc, ops)
         times.append(dt)
         spent += dt
-    byts = nbits_bytes(1, HIDDEN, n_cols, BLOCK, real_bytes=4)
     return {"value": byts / statistics.median(times) / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": "lm_head GEMV, first %d of %d columns, f32 (reference shader order, oracle/ovk_oracle.c), "
-                      "median of %d runs" % (n_cols, VOCAB, len(times))}
+            "sample": cpu_describe(layers, cores) + "; median of %d steps" % len(times)}
 
 
 def run_reference(args):
@@ -673,25 +776,19 @@ def run_reference(args):
     import oracle as orc
     cores = len(os.sched_getaffinity(0))
     orc.set_num_threads(cores)
-    n_cols = VOCAB // 4
-    sample = cpu_sample(n_cols)
+    ops, byts = cpu_step_inputs(args.layers)
     for _ in range(max(1, args.warmup)):
-        cpu_time_once(orc, sample, n_cols)
-    t = time.perf_counter()
-    for _ in range(args.steps):
-        cpu_time_once(orc, sample, n_cols)
-    total = time.perf_counter() - t
-    byts = nbits_bytes(1, HIDDEN, n_cols, BLOCK, real_bytes=4)
+        cpu_step(orc, ops)
+    total = sum(cpu_step(orc, ops) for _ in range(args.steps))
     value = byts * args.steps / total / 1e9
-    desc = ("each step = lm_head GEMV restricted to its first %d of %d columns, f32, reference shader order "
-            "(CPU port in oracle/ovk_oracle.c; the reference's own GPU path needs Vulkan: unavailable on this box)"
-            % (n_cols, VOCAB))
+    desc = cpu_describe(args.layers, cores)
     print(json.dumps({
         "impl": "reference", "metric": "int4_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s",
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "gemma3-1b-int4-decode (bounded sample)", "sample": desc},
+        "config": {"workload": WORKLOAD % args.layers, "gemvs_per_step": len(ops), "bytes_per_step": byts,
+                   "sample": desc},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0}), flush=True)

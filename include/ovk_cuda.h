@@ -93,6 +93,13 @@ OVK_API int32_t ovk_flush(ovk_ctx *ctx);
  * has no device-side waits; its failure report is the Result of flush,
  * crates/vk-compute/src/stream.rs:702.) */
 OVK_API int32_t ovk_selftest_device_timeout(ovk_ctx *ctx);
+/* Measures what the tensor core delivers: multiply-accumulates per clock per SM
+ * of back-to-back 128 x 256 tcgen05.mma over operands resident in shared
+ * memory, for dtype OVK_INT8 (kind::i8) or OVK_FLOAT16 (kind::f16).  Waits for
+ * the result.  Times SMs times the SM clock it is the dense peak the int8
+ * kernels are measured against.  (The reference measures its own ceiling the
+ * same way in crates/onnx-vulkan-core/examples/conv_integer_coop.rs; its library has no counterpart.) */
+OVK_API int32_t ovk_probe_mma_rate(ovk_ctx *ctx, int32_t dtype, double *mac_per_clk_per_sm);
 /* create_storage_buffer (buffer.rs:239) / recycle_storage_buffer (:303) */
 OVK_API int32_t ovk_alloc(ovk_ctx *ctx, size_t bytes, void **dptr);
 OVK_API int32_t ovk_free(ovk_ctx *ctx, void *dptr);
@@ -199,6 +206,30 @@ OVK_API int32_t ovk_matmul_nbits_nsplit(ovk_ctx *ctx, const ovk_nbits_weight *w,
  * stay on the device.  n = 0 writes scale 1, zero point 0 (:1949-1966). */
 OVK_API int32_t ovk_dynamic_quantize(ovk_ctx *ctx, const float *x, int64_t n, uint8_t *y,
                                      float *y_scale, uint8_t *y_zero_point);
+/* The same when the kernel that produced x has already folded its range into
+ * `range` (OVK_EPILOGUE_RANGE of the fused MatMulInteger / ConvInteger nodes):
+ * the range pass is skipped, as quantize_on_device skips it for a tensor with a
+ * computed range (interp.rs:1979-1983, ExecutionEnv::set_range execution.rs:107).
+ * `range` is a slot of four u32 (16 bytes) on the device, zero before the
+ * producer runs; this call leaves it zero again, ready for the next producer -
+ * so a folded range serves ONE quantization. */
+OVK_API int32_t ovk_dynamic_quantize_folded(ovk_ctx *ctx, const float *x, int64_t n, uint32_t *range,
+                                            uint8_t *y, float *y_scale, uint8_t *y_zero_point);
+/* interp::decomposed_gelu (interp.rs:9060-9084, shader shaders/elementwise.rs:71-118):
+ * the exact GELU as the graph spells it, Div -> Erf -> Add -> Mul -> Mul, in one
+ * pass with every step rounded on its own: e = erf(x / divisor) + offset;
+ * out = factor_first ? x * (e * factor) : (x * e) * factor, erf by the five-term
+ * rational approximation the reference uses. */
+OVK_API int32_t ovk_decomposed_gelu(ovk_ctx *ctx, const float *x, int64_t n, float divisor,
+                                    float offset, float factor, int32_t factor_first, float *out);
+/* interp::decomposed_gelu_quantize (interp.rs:9125-9150; rewrite.rs:699-735;
+ * shaders/dynamic_quantize.rs:224-247): DynamicQuantizeLinear(DecomposedGelu(x))
+ * as one node.  Both passes compute the GELU from x again, with the function
+ * ovk_decomposed_gelu applies, so the f32 GELU - the largest tensor of a
+ * transformer MLP - is never stored and every byte equals the two nodes'. */
+OVK_API int32_t ovk_decomposed_gelu_quantize(ovk_ctx *ctx, const float *x, int64_t n, float divisor,
+                                             float offset, float factor, int32_t factor_first,
+                                             uint8_t *y, float *y_scale, uint8_t *y_zero_point);
 
 /* ----------------------------------------------------------- MatMulInteger
  * packed_b (interp.rs:2712-2768, shader PACK_B shaders/matmul_integer.rs
@@ -243,8 +274,9 @@ OVK_API int32_t ovk_matmul_integer_static_scratch(ovk_ctx *ctx, const ovk_mmi_we
  * bit-identical to the unfused graph.  A step is 0 (one value) or 1 (one per
  * column), as interp::column_step (:2600-2610); other broadcasts are refused
  * (the reference runs them unfused).  range (may be NULL) is a zero-initialised
- * pair of u32 receiving the bits of max(-min,0) and max(max,0) of the stored
- * values by atomic max, for the DynamicQuantizeLinear that follows. */
+ * slot of four u32 whose first two receive the bits of max(-min,0) and
+ * max(max,0) of the stored values by atomic max, for the
+ * ovk_dynamic_quantize_folded that follows. */
 #define OVK_EPILOGUE_RELU 1u
 #define OVK_EPILOGUE_RANGE 2u
 OVK_API int32_t ovk_matmul_integer_scale_bias(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a,

@@ -9,8 +9,20 @@
 // __fdiv_rn here, IS the IEEE division, so the results are bit-equal to the
 // operator definition (tests/dynamic_quantize.rs:16-26) without it.
 #include "ovk_internal.h"
+#include "gelu.cuh"
 
 namespace {
+
+// What the passes read: x itself, or DecomposedGelu(x) computed on the fly (the
+// reference's gelu_partial / gelu_quantize shaders, shaders/dynamic_quantize.rs:224-247,
+// whose load() is the GELU: its f32 result is never stored).
+struct LoadPlain {
+    __device__ __forceinline__ float operator()(float v) const { return v; }
+};
+struct LoadGelu {
+    GeluParams g;
+    __device__ __forceinline__ float operator()(float v) const { return ovk_decomposed_gelu(v, g); }
+};
 
 __device__ __forceinline__ void fold(float v, float &mn, float &mx)
 {
@@ -21,8 +33,9 @@ __device__ __forceinline__ void fold(float v, float &mn, float &mx)
 // range[0] = bits of -min, range[1] = bits of max, both >= 0 so that unsigned
 // order is float order; the slot is zero when the kernel starts (= range [0,0]): it is zeroed when
 // the context is created and again by the last block of every quantize pass (range[2] counts them).
+template <typename Load>
 __global__ void __launch_bounds__(256)
-dql_range_kernel(const float *__restrict__ x, int64_t n, uint32_t *__restrict__ range, int vec_ok)
+dql_range_kernel(const float *__restrict__ x, int64_t n, uint32_t *__restrict__ range, int vec_ok, Load load)
 {
     OVK_PDL_LAUNCH_DEPENDENTS();
     OVK_PDL_WAIT();
@@ -38,23 +51,23 @@ dql_range_kernel(const float *__restrict__ x, int64_t n, uint32_t *__restrict__ 
         for (; i + 3 * stride < n4; i += 4 * stride) {
             const float4 v0 = __ldg(x4 + i), v1 = __ldg(x4 + i + stride), v2 = __ldg(x4 + i + 2 * stride),
                          v3 = __ldg(x4 + i + 3 * stride);
-            fold(v0.x, mn, mx); fold(v0.y, mn, mx); fold(v0.z, mn, mx); fold(v0.w, mn, mx);
-            fold(v1.x, mn, mx); fold(v1.y, mn, mx); fold(v1.z, mn, mx); fold(v1.w, mn, mx);
-            fold(v2.x, mn, mx); fold(v2.y, mn, mx); fold(v2.z, mn, mx); fold(v2.w, mn, mx);
-            fold(v3.x, mn, mx); fold(v3.y, mn, mx); fold(v3.z, mn, mx); fold(v3.w, mn, mx);
+            fold(load(v0.x), mn, mx); fold(load(v0.y), mn, mx); fold(load(v0.z), mn, mx); fold(load(v0.w), mn, mx);
+            fold(load(v1.x), mn, mx); fold(load(v1.y), mn, mx); fold(load(v1.z), mn, mx); fold(load(v1.w), mn, mx);
+            fold(load(v2.x), mn, mx); fold(load(v2.y), mn, mx); fold(load(v2.z), mn, mx); fold(load(v2.w), mn, mx);
+            fold(load(v3.x), mn, mx); fold(load(v3.y), mn, mx); fold(load(v3.z), mn, mx); fold(load(v3.w), mn, mx);
         }
         for (; i < n4; i += stride) {
             const float4 v = __ldg(x4 + i);
-            fold(v.x, mn, mx);
-            fold(v.y, mn, mx);
-            fold(v.z, mn, mx);
-            fold(v.w, mn, mx);
+            fold(load(v.x), mn, mx);
+            fold(load(v.y), mn, mx);
+            fold(load(v.z), mn, mx);
+            fold(load(v.w), mn, mx);
         }
         for (int64_t i = (n4 << 2) + tid; i < n; i += stride)
-            fold(x[i], mn, mx);
+            fold(load(x[i]), mn, mx);
     } else {
         for (int64_t i = tid; i < n; i += stride)
-            fold(x[i], mn, mx);
+            fold(load(x[i]), mn, mx);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -95,10 +108,11 @@ __device__ __forceinline__ uint32_t quant1(float v, float scale, float zp)
     return uint32_t(fminf(fmaxf(q, 0.0f), 255.0f));
 }
 
+template <typename Load>
 __global__ void __launch_bounds__(256)
 dql_quantize_kernel(const float *__restrict__ x, int64_t n, uint32_t *__restrict__ range,
                     float *__restrict__ scale_out, uint8_t *__restrict__ zp_out,
-                    uint8_t *__restrict__ y, int vec_ok)
+                    uint8_t *__restrict__ y, int vec_ok, Load load)
 {
     OVK_PDL_LAUNCH_DEPENDENTS();
     OVK_PDL_WAIT();
@@ -129,8 +143,8 @@ dql_quantize_kernel(const float *__restrict__ x, int64_t n, uint32_t *__restrict
         const float4 *x4 = reinterpret_cast<const float4 *>(x);
         uint32_t *y4 = reinterpret_cast<uint32_t *>(y);
         auto pack = [&](const float4 &v) {
-            return quant1(v.x, scale, zp) | (quant1(v.y, scale, zp) << 8) | (quant1(v.z, scale, zp) << 16) |
-                   (quant1(v.w, scale, zp) << 24);
+            return quant1(load(v.x), scale, zp) | (quant1(load(v.y), scale, zp) << 8) |
+                   (quant1(load(v.z), scale, zp) << 16) | (quant1(load(v.w), scale, zp) << 24);
         };
         int64_t i = tid;
         for (; i + 3 * stride < n4; i += 4 * stride) {
@@ -144,10 +158,10 @@ dql_quantize_kernel(const float *__restrict__ x, int64_t n, uint32_t *__restrict
         for (; i < n4; i += stride)
             y4[i] = pack(__ldg(x4 + i));
         for (int64_t i = (n4 << 2) + tid; i < n; i += stride)
-            y[i] = uint8_t(quant1(x[i], scale, zp));
+            y[i] = uint8_t(quant1(load(x[i]), scale, zp));
     } else {
         for (int64_t i = tid; i < n; i += stride)
-            y[i] = uint8_t(quant1(x[i], scale, zp));
+            y[i] = uint8_t(quant1(load(x[i]), scale, zp));
     }
 }
 
@@ -157,33 +171,88 @@ __global__ void dql_identity_kernel(float *scale_out, uint8_t *zp_out)
     zp_out[0] = 0;
 }
 
-}  // namespace
+__global__ void __launch_bounds__(256)
+gelu_kernel(const float *__restrict__ x, int64_t n, float *__restrict__ out, GeluParams g)
+{
+    OVK_PDL_LAUNCH_DEPENDENTS();
+    OVK_PDL_WAIT();
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
+        out[i] = ovk_decomposed_gelu(x[i], g);
+}
 
-extern "C" int32_t ovk_dynamic_quantize(ovk_ctx *ctx, const float *x, int64_t n, uint8_t *y,
-                                        float *y_scale, uint8_t *y_zero_point)
+// Both passes, or - when `folded` is a slot a producer has already folded the range of x into - only
+// the second one (interp.rs:1979-1983).
+template <typename Load>
+int32_t quantize_passes(ovk_ctx *ctx, const char *what, const float *x, int64_t n, uint32_t *folded, uint8_t *y,
+                        float *y_scale, uint8_t *y_zero_point, Load load)
 {
     if (!ctx)
-        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "ovk_dynamic_quantize: null context");
-    OVK_REQUIRE(ctx, n >= 0, "DynamicQuantizeLinear: negative element count");
-    OVK_REQUIRE(ctx, y_scale && y_zero_point, "DynamicQuantizeLinear: y_scale or y_zero_point is null");
-    OVK_REQUIRE(ctx, aligned_to(y_scale, 4), "DynamicQuantizeLinear: y_scale is not 4-byte aligned");
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "%s: null context", what);
+    OVK_REQUIRE(ctx, n >= 0, "%s: negative element count", what);
+    OVK_REQUIRE(ctx, y_scale && y_zero_point, "%s: y_scale or y_zero_point is null", what);
+    OVK_REQUIRE(ctx, aligned_to(y_scale, 4), "%s: y_scale is not 4-byte aligned", what);
     OVK_CUDA(ctx, cudaSetDevice(ctx->device));
     if (n == 0) {  // empty input: scale 1, zero point 0 (interp.rs:1949-1966)
         dql_identity_kernel<<<1, 1, 0, ctx->stream>>>(y_scale, y_zero_point);
         OVK_LAUNCHED(ctx, "dql_identity");
         return OVK_OK;
     }
-    OVK_REQUIRE(ctx, x && y, "DynamicQuantizeLinear: x or y is null");
-    OVK_REQUIRE(ctx, aligned_to(x, 4), "DynamicQuantizeLinear: x is not 4-byte aligned");
+    OVK_REQUIRE(ctx, x && y, "%s: x or y is null", what);
+    OVK_REQUIRE(ctx, aligned_to(x, 4), "%s: x is not 4-byte aligned", what);
+    OVK_REQUIRE(ctx, !folded || aligned_to(folded, 4), "%s: the range slot is not 4-byte aligned", what);
     const int vec_ok = aligned_to(x, 16) && aligned_to(y, 4);
     const int64_t work = vec_ok ? (n + 3) / 4 : n;
     // both passes: grid-stride, four vectors per thread and trip, at most four blocks per SM
-    unsigned blocks1 = unsigned(std::min<int64_t>(ceil_div64(work, 1024), int64_t(ctx->sm_count) * 4));
-    OVK_CUDA(ctx, ovk_launch_pdl(dql_range_kernel, dim3(blocks1), dim3(256), 0, ctx->stream, x, n, ctx->range_slot, vec_ok));
-    OVK_LAUNCHED(ctx, "dql_range");
-    unsigned blocks2 = blocks1;
-    OVK_CUDA(ctx, ovk_launch_pdl(dql_quantize_kernel, dim3(blocks2), dim3(256), 0, ctx->stream, x, n, ctx->range_slot, y_scale,
-                                 y_zero_point, y, vec_ok));
+    const unsigned blocks = unsigned(std::min<int64_t>(ceil_div64(work, 1024), int64_t(ctx->sm_count) * 4));
+    uint32_t *range = folded ? folded : ctx->range_slot;
+    if (!folded) {
+        OVK_CUDA(ctx, ovk_launch_pdl(dql_range_kernel<Load>, dim3(blocks), dim3(256), 0, ctx->stream, x, n, range, vec_ok, load));
+        OVK_LAUNCHED(ctx, "dql_range");
+    }
+    OVK_CUDA(ctx, ovk_launch_pdl(dql_quantize_kernel<Load>, dim3(blocks), dim3(256), 0, ctx->stream, x, n, range, y_scale,
+                                 y_zero_point, y, vec_ok, load));
     OVK_LAUNCHED(ctx, "dql_quantize");
     return OVK_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t ovk_dynamic_quantize(ovk_ctx *ctx, const float *x, int64_t n, uint8_t *y,
+                                        float *y_scale, uint8_t *y_zero_point)
+{
+    return quantize_passes(ctx, "DynamicQuantizeLinear", x, n, nullptr, y, y_scale, y_zero_point, LoadPlain{});
+}
+
+extern "C" int32_t ovk_dynamic_quantize_folded(ovk_ctx *ctx, const float *x, int64_t n, uint32_t *range, uint8_t *y,
+                                               float *y_scale, uint8_t *y_zero_point)
+{
+    if (ctx && !range)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "DynamicQuantizeLinear: the folded range is null");
+    return quantize_passes(ctx, "DynamicQuantizeLinear", x, n, range, y, y_scale, y_zero_point, LoadPlain{});
+}
+
+extern "C" int32_t ovk_decomposed_gelu(ovk_ctx *ctx, const float *x, int64_t n, float divisor, float offset, float factor,
+                                       int32_t factor_first, float *out)
+{
+    if (!ctx)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "DecomposedGelu: null context");
+    OVK_REQUIRE(ctx, n >= 0, "DecomposedGelu: negative element count");
+    if (n == 0)
+        return OVK_OK;
+    OVK_REQUIRE(ctx, x && out, "DecomposedGelu: x or the output is null");
+    OVK_CUDA(ctx, cudaSetDevice(ctx->device));
+    const GeluParams g = {divisor, offset, factor, factor_first ? 1 : 0};
+    const unsigned blocks = unsigned(std::min<int64_t>(ceil_div64(n, 256), int64_t(ctx->sm_count) * 8));
+    OVK_CUDA(ctx, ovk_launch_pdl(gelu_kernel, dim3(blocks), dim3(256), 0, ctx->stream, x, n, out, g));
+    OVK_LAUNCHED(ctx, "decomposed_gelu");
+    return OVK_OK;
+}
+
+extern "C" int32_t ovk_decomposed_gelu_quantize(ovk_ctx *ctx, const float *x, int64_t n, float divisor, float offset,
+                                                float factor, int32_t factor_first, uint8_t *y, float *y_scale,
+                                                uint8_t *y_zero_point)
+{
+    LoadGelu load;
+    load.g = {divisor, offset, factor, factor_first ? 1 : 0};
+    return quantize_passes(ctx, "DecomposedGeluQuantize", x, n, nullptr, y, y_scale, y_zero_point, load);
 }

@@ -72,7 +72,7 @@ constexpr int BW = 128;    // weight columns per tile (UMMA M)
 constexpr int BT = 192;    // most tokens per tile (UMMA N)
 constexpr int HALF = BT / 2;  // token rows per promotion warp
 constexpr int SLAB = 64;   // k per stage: 128 bytes of fp16
-constexpr int STAGES = 7;    // shared-memory ring: tokens + packed nibbles of a slab (TMA)
+constexpr int STAGES = 6;    // shared-memory ring: tokens + packed nibbles of a slab (TMA); eight measured the same
 constexpr int A_STAGES = 4;  // tensor-memory ring: unpacked weights of a slab
 constexpr int ACC_RING = 4;   // most accumulators in flight: 2 x 192, 3 x 128 or 4 x 96 columns
 constexpr int B_BYTES = BT * 128;
@@ -83,8 +83,8 @@ static_assert(A_BASE + A_STAGES * A_COLS <= TMEM_COLS, "tensor memory: accumulat
 constexpr int RAW_BYTES = BW * 32;  // packed nibbles of one slab: 32 bytes per weight row
 constexpr int THREADS = 20 * 32;  // five warpgroups: control, unpack x2, promotion x2
 constexpr long long WAIT_CYCLES = 2000000000ll;
-constexpr int Y_ROWS = 48;                 // token rows of one pass through the store buffer
-constexpr int Y_BYTES = Y_ROWS * BW * 2;   // one half's buffer: 48 rows x 128 fp16
+constexpr int Y_ROWS = HALF;               // token rows of a promotion half's store buffer
+constexpr int Y_BYTES = Y_ROWS * BW * 2;   // one half's buffer: 96 rows x 128 fp16
 constexpr int PART_FLOATS = HALF * BW;     // f32 partial sums one promotion half holds for a tile
 
 struct GemmParams {
@@ -117,14 +117,14 @@ struct GemmParams {
 
 // The run of units of this CTA and its walk, tile by tile.
 struct Run {
-    long long u, end;
+    uint32_t u, end;  // the host keeps tiles x units below 2^31
 };
-__device__ __forceinline__ long long run_start(const GemmParams &p, long long cta)
+__device__ __forceinline__ uint32_t run_start(const GemmParams &p, uint32_t cta)
 {
-    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    const unsigned long long tiles = (unsigned long long)p.m_tiles * p.n_tiles;
     if (p.shared_k)
-        return tiles * p.units * cta / gridDim.x;
-    return (tiles * cta / gridDim.x) * p.units;
+        return uint32_t(tiles * p.units * cta / gridDim.x);
+    return uint32_t(tiles * cta / gridDim.x) * uint32_t(p.units);
 }
 __device__ __forceinline__ Run cta_run(const GemmParams &p)
 {
@@ -133,15 +133,23 @@ __device__ __forceinline__ Run cta_run(const GemmParams &p)
     r.end = run_start(p, blockIdx.x + 1);
     return r;
 }
+// A CTA's tiles are consecutive numbers: one weight tile, the token tiles one after the other.
+// (Measured: it makes no difference whether the CTAs running together share a weight tile or a
+// token tile - both operands of these shapes stay in the L2.)
+__device__ __forceinline__ void tile_origin(const GemmParams &p, int tile, int &m_index, int &n_index)
+{
+    n_index = tile / p.m_tiles;
+    m_index = tile - n_index * p.m_tiles;
+}
 // Next item of the run: units [ub, ue) of `tile`.  Returns false at the end.
 __device__ __forceinline__ bool next_item(const GemmParams &p, Run &r, int &tile, int &ub, int &ue)
 {
     if (r.u >= r.end)
         return false;
-    tile = int(r.u / p.units);
-    ub = int(r.u - (long long)tile * p.units);
-    ue = int(min((long long)p.units, ub + (r.end - r.u)));
-    r.u += ue - ub;
+    tile = int(r.u / uint32_t(p.units));
+    ub = int(r.u - uint32_t(tile) * uint32_t(p.units));
+    ue = int(min(uint32_t(p.units), uint32_t(ub) + (r.end - r.u)));
+    r.u += uint32_t(ue - ub);
     return true;
 }
 
@@ -218,7 +226,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads)
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// What the store warp is told about one pass through a half's buffer.
+// What the store warp is told about the tile in a half's buffer.
 struct PassDesc {
     int m_base;  // token row of the buffer's first row
     int rows;    // rows of the buffer that hold results (<= 0: none); -1000000: the CTA has no more tiles
@@ -234,7 +242,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *sX = smem;                       // STAGES x 24 KB: tokens (UMMA B operand)
     uint8_t *sR = sX + STAGES * B_BYTES;      // STAGES x 4 KB: packed nibbles as loaded
-    uint8_t *sY = sR + STAGES * RAW_BYTES;    // 2 x 12 KB: results on their way out, one buffer per promotion half
+    uint8_t *sY = sR + STAGES * RAW_BYTES;    // 2 x 24 KB: results on their way out, one buffer per promotion half
     uint64_t *bars = reinterpret_cast<uint64_t *>(sY + 2 * Y_BYTES);
     uint64_t *full_x = bars;                  // TMA landed
     uint64_t *full_w = full_x + STAGES;       // [A_STAGES] the four unpack warps arrived
@@ -287,16 +295,17 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         if (lane == 0) {
             umma::prefetch_tmap(&tmAct);
             umma::prefetch_tmap(&tmRaw);
-            int seq = 0;
+            int s = 0;
+            uint32_t ph = 0;
             Run run = cta_run(p);
             int tile, ub, ue;
             bool ok = true;
             while (ok && next_item(p, run, tile, ub, ue)) {
-                const int m0 = (tile % p.m_tiles) * p.bt;
-                const int n0 = (tile / p.m_tiles) * BW;
-                for (int sl = ub * p.unit_slabs; sl < ue * p.unit_slabs; sl++, seq++) {
-                    const int s = seq % STAGES;
-                    if (!wait_parked(&empty[s], ((seq / STAGES) & 1) ^ 1)) {
+                int mi, ni;
+                tile_origin(p, tile, mi, ni);
+                const int m0 = mi * p.bt, n0 = ni * BW;
+                for (int sl = ub * p.unit_slabs; sl < ue * p.unit_slabs; sl++) {
+                    if (!wait_parked(&empty[s], ph ^ 1)) {
                         atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
                         ok = false;
                         break;
@@ -304,6 +313,10 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                     umma::mbar_expect_tx(&full_x[s], uint32_t(p.bt) * 128u + RAW_BYTES);
                     umma::tma_load_2d(sX + s * B_BYTES, &tmAct, &full_x[s], sl * SLAB, m0);
                     umma::tma_load_2d(sR + s * RAW_BYTES, &tmRaw, &full_x[s], sl * 32, n0);
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
             }
         }
@@ -419,7 +432,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         }
     } else if (warp == 3) {
         // -------------------------------------------------------------------- store
-        // Takes the passes the promotion halves leave in their buffers (half 0, half 1, half 0,
+        // Takes the tiles the promotion halves leave in their buffers (half 0, half 1, half 0,
         // ...) and writes them out: a row of the buffer is 256 contiguous bytes of a row of Y, a
         // lane moves 16 of them, and in a column split over several GPUs every 16 bytes go to
         // every rank's Y.  The stores are not waited for here; the promotion warps have long gone
@@ -457,45 +470,46 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                     }
                 }
                 const uint8_t *buf = sY + h * Y_BYTES;
-                // 48 rows x 16 chunks of 16 bytes = 24 chunks per lane, four at a time
-#pragma unroll 1
-                for (int i = 0; i < Y_ROWS * 16 / 32; i += 4) {
-                    uint4 v[4];
-#pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        const int c = lane + 32 * (i + u);
-                        v[u] = *reinterpret_cast<const uint4 *>(buf + (c >> 4) * (BW * 2) + (c & 15) * 16);
+                // A lane keeps one 16-byte column chunk (lane & 15) and walks down the rows two at a
+                // time, so a chunk costs a shared-memory load, a store and two additions; the ranks
+                // are taken one after the other, each from the same buffer.
+                const int cc = lane & 15, r0 = lane >> 4;
+                const int n = d.n0 + cc * 8;
+                const uint8_t *src0 = buf + r0 * (BW * 2) + cc * 16;
+                const size_t off0 = (size_t(d.m_base + r0) * size_t(p.ldy) + size_t(p.col0 + n)) * 2;
+                const size_t step = size_t(p.ldy) * 4;  // two rows of Y
+                if (p.vec_ok && d.n0 + BW <= p.N) {
+                    for (int r = 0; r < p.n_dst; r++) {
+                        uint8_t *dst = static_cast<uint8_t *>(p.y_dst[r]) + off0;
+                        const uint8_t *src = src0;
+#pragma unroll 4
+                        for (int row = r0; row < Y_ROWS; row += 2, src += 2 * BW * 2, dst += step) {
+                            const uint4 v = *reinterpret_cast<const uint4 *>(src);
+                            if (ok && row < d.rows)
+                                *reinterpret_cast<uint4 *>(dst) = v;
+                        }
                     }
-                    if (i + 4 == Y_ROWS * 16 / 32) {
-                        // everything of the buffer is in registers: hand it back
-                        __syncwarp();
-                        if (lane == 0)
-                            umma::mbar_arrive(&y_empty[h]);
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        const int c = lane + 32 * (i + u);
-                        const int row = c >> 4, n = d.n0 + (c & 15) * 8;
-                        if (!ok || row >= d.rows || n >= p.N)
-                            continue;
-                        const size_t off = (size_t(d.m_base + row) * size_t(p.ldy) + size_t(p.col0 + n)) * 2;
-                        if (p.vec_ok && n + 8 <= p.N) {
-#pragma unroll
-                            for (int r = 0; r < OVK_MAX_RANKS; r++)
-                                if (r < p.n_dst)
-                                    *reinterpret_cast<uint4 *>(static_cast<uint8_t *>(p.y_dst[r]) + off) = v[u];
-                        } else {
-                            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-                            for (int r = 0; r < p.n_dst; r++) {
-                                uint16_t *o = reinterpret_cast<uint16_t *>(static_cast<uint8_t *>(p.y_dst[r]) + off);
+                } else {
+                    // a tile at the ragged edge of N, or destinations that do not take 16-byte stores
+                    for (int r = 0; r < p.n_dst; r++) {
+                        uint8_t *dst = static_cast<uint8_t *>(p.y_dst[r]) + off0;
+                        const uint8_t *src = src0;
+                        for (int row = r0; row < Y_ROWS; row += 2, src += 2 * BW * 2, dst += step) {
+                            const uint4 v = *reinterpret_cast<const uint4 *>(src);
+                            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                            if (ok && row < d.rows) {
 #pragma unroll
                                 for (int e = 0; e < 8; e++)
                                     if (n + e < p.N)
-                                        o[e] = uint16_t(w[e >> 1] >> (16 * (e & 1)));
+                                        reinterpret_cast<uint16_t *>(dst)[e] = uint16_t(w[e >> 1] >> (16 * (e & 1)));
                             }
                         }
                     }
                 }
+                // everything of the buffer has been read (the stores may still be on their way): hand it back
+                __syncwarp();
+                if (lane == 0)
+                    umma::mbar_arrive(&y_empty[h]);
             }
             seq++;
         }
@@ -534,13 +548,19 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         // store of slab j is announced only after slab j + 1 has been unpacked - by then it has
         // completed and the wait costs nothing - and block indices are shifts, not divisions.
         const int bs_shift = 31 - __clz(p.bs);  // block sizes are powers of two
-        int seq = 0;       // position in the stage rings of the current item's first slab
+        int seq = 0;       // number of slabs before the current item's first one
         int pending = -1;  // A stage stored to but not yet announced
+        // ring positions are stepped, not computed (six stages: no power of two): slab g sits in stage
+        // s_g on the ring's lap of parity ph_g, and the slab A_STAGES before it likewise in s_b / ph_b
+        int g_at = 0, s_g = 0, s_b = STAGES - A_STAGES;
+        uint32_t ph_g = 0, ph_b = 1;
         bool ok = true;
         Run run = cta_run(p);
         int tile, ub, ue;
         while (ok && next_item(p, run, tile, ub, ue)) {
-            const int n = (tile / p.m_tiles) * BW + r;
+            int mi, ni;
+            tile_origin(p, tile, mi, ni);
+            const int n = ni * BW + r;
             const int sl0 = ub * p.unit_slabs, len = (ue - ub) * p.unit_slabs;
             // zero points: one byte per block, fetched one slab of this group ahead
             const uint8_t *zrow = p.zp_t + size_t(n) * p.zp_pitch;
@@ -553,14 +573,24 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
             uint32_t z_next = i < len ? zero_points(sl0 + i) : 0u;
             for (; i < len; i += 2) {
                 const int g = seq + i;
+                for (; g_at < g; g_at++) {
+                    if (++s_g == STAGES) {
+                        s_g = 0;
+                        ph_g ^= 1;
+                    }
+                    if (++s_b == STAGES) {
+                        s_b = 0;
+                        ph_b ^= 1;
+                    }
+                }
                 const uint32_t z0 = z_next & 0xffu, z1 = z_next >> 8;
                 if (i + 2 < len)
                     z_next = zero_points(sl0 + i + 2);
                 const uint32_t lo0 = z0 * 0x00010001u + 0x64006400u, hi0 = z0 * 0x00100010u + 0x54005400u;
                 const uint32_t lo1 = z1 * 0x00010001u + 0x64006400u, hi1 = z1 * 0x00100010u + 0x54005400u;
-                const int s = g % STAGES;
+                const int s = s_g;
                 // the nibbles have landed
-                if (!wait_parked(&full_x[s], (g / STAGES) & 1)) {
+                if (!wait_parked(&full_x[s], ph_g)) {
                     if (lane == 0)
                         atomicExch(p.status, OVK_DEV_TIMEOUT_TMA);
                     ok = false;
@@ -591,14 +621,14 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                 }
                 // the A stage this slab goes into was read by the MMAs of the slab A_STAGES earlier,
                 // whose completion is the `empty` barrier of that slab's shared-memory stage
-                if (g >= A_STAGES && !wait_parked(&empty[(g - A_STAGES) % STAGES], ((g - A_STAGES) / STAGES) & 1)) {
+                if (g >= A_STAGES && !wait_parked(&empty[s_b], ph_b)) {
                     if (lane == 0)
                         atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
                     ok = false;
                     break;
                 }
                 umma::tc_fence_after();
-                pending = g % A_STAGES;
+                pending = g & (A_STAGES - 1);
                 umma::tmem_st_32x32(a_lane + uint32_t(pending * A_COLS), wv);
             }
             seq += len;
@@ -622,27 +652,26 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         const int nchunks = (half_rows + 31) / 32;
         int b = 0;
         uint32_t acc_ph = 0;
-        uint32_t yseq = 0;  // passes this half has put into its buffer
-        bool ok = true;
+        uint32_t yseq = 0;  // tiles this half has put into its buffer
         bool first_item = true;
-        uint8_t *ybuf = sY + half * Y_BYTES + (q * 32 + lane) * 2;
+        bool ok = true;
         Run run = cta_run(p);
         int tile, ub, ue;
-        // one pass: 48 rows of this thread's column into the half's buffer, then the warp's arrival
-        auto put_pass = [&](const float (&acc)[HALF], int first_row, int m_base, int rows, int n0) {
+        // this thread's column of the half's token rows into the half's buffer, then the warp's arrival.
+        // The buffer was handed back when the store warp had read the previous tile out of it, a tile's
+        // time ago, so this wait is normally over before it starts.
+        auto put_tile = [&](const float (&acc)[HALF], int m_base, int rows, int n0) {
             if (ok && !wait_parked(&y_empty[half], (yseq & 1) ^ 1)) {
                 if (lane == 0)
                     atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
                 ok = false;
             }
-            if (first_row == 0) {
+            if (rows != PASS_STOP) {
+                const uint32_t ybuf = umma::smem_u32(sY) + uint32_t(half * Y_BYTES + (q * 32 + lane) * 2);
 #pragma unroll
-                for (int j = 0; j < Y_ROWS; j++)
-                    *reinterpret_cast<__half *>(ybuf + j * (BW * 2)) = __float2half_rn(acc[j]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < Y_ROWS; j++)
-                    *reinterpret_cast<__half *>(ybuf + j * (BW * 2)) = __float2half_rn(acc[Y_ROWS + j]);
+                for (int j = 0; j < HALF; j++)
+                    asm volatile("st.shared.b16 [%0], %1;" ::"r"(ybuf + j * (BW * 2)), "h"(__half_as_ushort(__float2half_rn(acc[j])))
+                                 : "memory");
             }
             if (q == 0 && lane == 0) {
                 PassDesc d;
@@ -658,11 +687,10 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
             yseq++;
         };
         while (next_item(p, run, tile, ub, ue)) {
-            const int n0 = (tile / p.m_tiles) * BW;
+            int mi, ni;
+            tile_origin(p, tile, mi, ni);
+            const int n0 = ni * BW;
             const int n = n0 + q * 32 + lane;
-            const int m0 = (tile % p.m_tiles) * p.bt + half * hw;
-            // token rows of this warp that exist (may be <= 0): its share of the tile, cut at the end of M
-            const int rows = min(p.M - m0, half_rows);
             float acc[HALF];
 #pragma unroll
             for (int j = 0; j < HALF; j++)
@@ -741,7 +769,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                     for (uint32_t c = c_first; c <= c_last; c++) {
                         // the part of CTA c is the item its run begins with, unless the run began in
                         // an earlier tile (only the first of the CTAs can)
-                        const bool begins_here = run_start(p, c) >= (long long)tile * p.units;
+                        const bool begins_here = run_start(p, c) >= uint32_t(tile) * uint32_t(p.units);
                         const float *part = p.partials + ((size_t(c) * 2 + (begins_here ? 0 : 1)) * 2 + half) * PART_FLOATS +
                                             q * 32 + lane;
 #pragma unroll
@@ -753,6 +781,9 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
             first_item = false;
             if (!store)
                 continue;
+            const int m0 = mi * p.bt + half * hw;
+            // token rows of this warp that exist (may be <= 0): its share of the tile, cut at the end of M
+            const int rows = min(p.M - m0, half_rows);
             if (p.y_f32) {
                 if (ok && n < p.N) {
                     // the MMA thread can run only two blocks ahead while this store lasts: a row
@@ -770,16 +801,13 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                     }
                 }
             } else {
-                put_pass(acc, 0, m0, min(rows, Y_ROWS), n0);
-                put_pass(acc, Y_ROWS, m0 + Y_ROWS, min(rows - Y_ROWS, Y_ROWS), n0);
+                put_tile(acc, m0, rows, n0);
             }
         }
         if (!p.y_f32) {
             float none[HALF];
-#pragma unroll
-            for (int j = 0; j < HALF; j++)
-                none[j] = 0.0f;
-            put_pass(none, 0, 0, PASS_STOP, 0);  // tells the store warp that this CTA has no more tiles
+            none[0] = 0.0f;
+            put_tile(none, 0, PASS_STOP, 0);  // tells the store warp that this CTA has no more tiles
         }
     }
     umma::tc_fence_before();

@@ -165,10 +165,84 @@ Result dynamic_quantize(Env &env, const NodeIr &node)
     OVKH_TRY(env.alloc(node.outputs[1], OVK_FLOAT, {}, &scale));
     OVKH_TRY(env.alloc(node.outputs[2], OVK_UINT8, {}, &zp));
     x = env.find(node.inputs[0]);
+    // the producer of x may have folded its range into a slot (ExecutionEnv::computed_range,
+    // execution.rs:112): the range pass is then skipped (interp.rs:1979-1983)
+    const Tensor *folded = env.find(node.inputs[0] + "/range");
+    if (folded && !folded->spent && count > 0) {
+        Result r = from_abi(env.context(),
+                            ovk_dynamic_quantize_folded(env.context(), static_cast<const float *>(x->dev), count,
+                                                        static_cast<uint32_t *>(folded->dev), static_cast<uint8_t *>(y->dev),
+                                                        static_cast<float *>(scale->dev), static_cast<uint8_t *>(zp->dev)));
+        // the quantize pass leaves the slot zero: a second quantization of the same tensor finds its range itself
+        const_cast<Tensor *>(folded)->spent = true;
+        return r;
+    }
     return from_abi(env.context(),
                     ovk_dynamic_quantize(env.context(), static_cast<const float *>(x->dev), count,
                                          static_cast<uint8_t *>(y->dev), static_cast<float *>(scale->dev),
                                          static_cast<uint8_t *>(zp->dev)));
+}
+
+// ---------------------------------------------- DecomposedGelu, DecomposedGeluQuantize
+Result scalar_f32(const Env &env, const std::string &name, const char *what, float *out);
+
+// interp::gelu_push (interp.rs:9094-9116): the three constants of the GELU, each one f32 value read
+// on the host; anything else is the form the reference replays as five elementwise nodes, which are
+// outside this layer.
+Result gelu_constants(const Env &env, const NodeIr &node, float (&c)[3])
+{
+    const Tensor *x = env.find(node.inputs[0]);
+    OVKH_ENSURE(x, "%s: x is missing", node.op.c_str());
+    bool fusable = x->dtype == OVK_FLOAT;
+    for (int i = 0; i < 3 && fusable; i++) {
+        const Tensor *t = env.find(node.inputs[1 + i]);
+        OVKH_ENSURE(t, "%s: input %d is missing", node.op.c_str(), 1 + i);
+        fusable = t->dtype == OVK_FLOAT && t->elem_count() == 1 && !t->host.empty();
+    }
+    if (!fusable)
+        return fail(OVK_UNSUPPORTED,
+                    "%s: not one pass (a non-f32 operand, or a constant that is not one value known on the host): the "
+                    "reference replays Div, Erf, Add, Mul, Mul here",
+                    node.op.c_str());
+    for (int i = 0; i < 3; i++)
+        OVKH_TRY(scalar_f32(env, node.inputs[1 + i], node.op.c_str(), &c[i]));
+    return Result{};
+}
+
+// interp::decomposed_gelu (interp.rs:9039-9084)
+Result decomposed_gelu(Env &env, const NodeIr &node)
+{
+    float c[3];
+    OVKH_TRY(gelu_constants(env, node, c));
+    const Tensor *x = env.find(node.inputs[0]);
+    const std::vector<int64_t> shape = x->shape;
+    const int64_t count = x->elem_count();
+    Tensor *out = nullptr;
+    OVKH_TRY(env.alloc(node.outputs[0], OVK_FLOAT, shape, &out));
+    x = env.find(node.inputs[0]);
+    return from_abi(env.context(),
+                    ovk_decomposed_gelu(env.context(), static_cast<const float *>(x->dev), count, c[0], c[1], c[2],
+                                        node.int_attr("factor_first", 0) == 1, static_cast<float *>(out->dev)));
+}
+
+// interp::decomposed_gelu_quantize (interp.rs:9125-9150): the GELU's inputs and attributes, the
+// quantization's three outputs
+Result decomposed_gelu_quantize(Env &env, const NodeIr &node)
+{
+    float c[3];
+    OVKH_TRY(gelu_constants(env, node, c));
+    const Tensor *x = env.find(node.inputs[0]);
+    const std::vector<int64_t> shape = x->shape;
+    const int64_t count = x->elem_count();
+    Tensor *y = nullptr, *scale = nullptr, *zp = nullptr;
+    OVKH_TRY(env.alloc(node.outputs[0], OVK_UINT8, shape, &y));
+    OVKH_TRY(env.alloc(node.outputs[1], OVK_FLOAT, {}, &scale));
+    OVKH_TRY(env.alloc(node.outputs[2], OVK_UINT8, {}, &zp));
+    x = env.find(node.inputs[0]);
+    return from_abi(env.context(),
+                    ovk_decomposed_gelu_quantize(env.context(), static_cast<const float *>(x->dev), count, c[0], c[1], c[2],
+                                                 node.int_attr("factor_first", 0) == 1, static_cast<uint8_t *>(y->dev),
+                                                 static_cast<float *>(scale->dev), static_cast<uint8_t *>(zp->dev)));
 }
 
 // --------------------------------------------------------------- MatMulInteger
@@ -256,8 +330,8 @@ Result matmul_integer_scale_bias(Env &env, const NodeIr &node)
     Tensor *range = nullptr;
     if (node.int_attr("range", 0) == 1) {  // fused_range: the slot the following DynamicQuantizeLinear reads
         flags |= OVK_EPILOGUE_RANGE;
-        OVKH_TRY(env.alloc(node.outputs[0] + "/range", OVK_INT32, {2}, &range));
-        OVKH_TRY(from_abi(env.context(), ovk_fill(env.context(), range->dev, 0, 8, 0)));
+        OVKH_TRY(env.alloc(node.outputs[0] + "/range", OVK_INT32, {4}, &range));
+        OVKH_TRY(from_abi(env.context(), ovk_fill(env.context(), range->dev, 0, 16, 0)));
     }
     std::vector<int64_t> out_shape(a->shape.begin(), a->shape.end() - 1);
     out_shape.push_back(n);
@@ -952,6 +1026,10 @@ bool is_implemented_node(const NodeIr &node)
                node.int_attr("storage_order", 0) == 0;
     if (op == "DynamicQuantizeLinear")
         return node.inputs.size() == 1 && node.outputs.size() == 3;
+    if (op == "DecomposedGelu")  // x, divisor, offset, factor (rewrite.rs:600-697)
+        return node.inputs.size() == 4 && node.outputs.size() == 1;
+    if (op == "DecomposedGeluQuantize")  // rewrite.rs:699-735
+        return node.inputs.size() == 4 && node.outputs.size() == 3;
     if (op == "MatMulInteger")
         return node.inputs.size() >= 2 && node.inputs.size() <= 4 && node.outputs.size() == 1;
     if (op == "MatMulIntegerScaleBias")
@@ -1050,6 +1128,10 @@ Result exec_dispatch(Env &env, const NodeIr &node)
         return matmul_nbits(env, node);
     if (node.op == "DynamicQuantizeLinear")
         return dynamic_quantize(env, node);
+    if (node.op == "DecomposedGelu")
+        return decomposed_gelu(env, node);
+    if (node.op == "DecomposedGeluQuantize")
+        return decomposed_gelu_quantize(env, node);
     if (node.op == "MatMulInteger")
         return matmul_integer(env, node);
     if (node.op == "MatMulIntegerScaleBias")

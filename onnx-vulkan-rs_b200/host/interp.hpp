@@ -52,6 +52,7 @@ struct Tensor {
     void *dev = nullptr;
     size_t bytes = 0;
     bool initializer = false;
+    bool spent = false;  // a folded range that its one DynamicQuantizeLinear has consumed
     std::vector<uint8_t> host;
     int64_t elem_count() const;
 };

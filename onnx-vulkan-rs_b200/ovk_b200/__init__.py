@@ -51,6 +51,7 @@ SIGNATURES = {
     "ovk_stream": (_P, [_P]),
     "ovk_workspace_bytes": (_SZ, [_P]),
     "ovk_selftest_device_timeout": (_I32, [_P]),
+    "ovk_probe_mma_rate": (_I32, [_P, _I32, C.POINTER(C.c_double)]),
     "ovk_flush": (_I32, [_P]),
     "ovk_alloc": (_I32, [_P, _SZ, C.POINTER(_P)]),
     "ovk_free": (_I32, [_P, _P]),
@@ -74,6 +75,9 @@ SIGNATURES = {
     "ovk_allgather_cols": (_I32, [_P, _P, _I32, _I64, _I64, _I64, _I64, C.POINTER(_P)]),
     "ovk_matmul_nbits_nsplit": (_I32, [_P, _P, _P, _I32, _I64, _I64, _I64, C.POINTER(_P), _I32]),
     "ovk_dynamic_quantize": (_I32, [_P, _P, _I64, _P, _P, _P]),
+    "ovk_dynamic_quantize_folded": (_I32, [_P, _P, _I64, _P, _P, _P, _P]),
+    "ovk_decomposed_gelu": (_I32, [_P, _P, _I64, C.c_float, C.c_float, C.c_float, _I32, _P]),
+    "ovk_decomposed_gelu_quantize": (_I32, [_P, _P, _I64, C.c_float, C.c_float, C.c_float, _I32, _P, _P, _P]),
     "ovk_mmi_prepack": (_I32, [_P, _P, _I32, _I64, _I64, C.POINTER(_P)]),
     "ovk_mmi_weight_destroy": (None, [_P, _P]),
     "ovk_matmul_integer": (_I32, [_P, _P, _P, _I32, _I64, _P, _P, _P]),
@@ -183,6 +187,12 @@ class Context:
     def workspace_bytes(self) -> int:
         return int(lib().ovk_workspace_bytes(self.h))
 
+    def probe_mma_rate(self, dtype=INT8) -> float:
+        """Multiply-accumulates per clock per SM of back-to-back tcgen05.mma (kind::i8 or kind::f16)."""
+        v = C.c_double()
+        self.check(lib().ovk_probe_mma_rate(self.h, dtype, C.byref(v)))
+        return v.value
+
     def selftest_device_timeout(self):
         """Enqueues the wait that is meant to run out; the next flush raises with status TIMEOUT."""
         self.check(lib().ovk_selftest_device_timeout(self.h))
@@ -257,12 +267,38 @@ class Context:
         self.check(lib().ovk_matmul_nbits_nsplit(self.h, w.h, _ptr(a), _dtype_code(a), m, col0, n_total, arr, y_dtype))
 
     # ------------------------------------------------- DynamicQuantizeLinear
-    def dynamic_quantize(self, x):
+    def dynamic_quantize(self, x, folded_range=None, out=None):
+        """interp::dynamic_quantize (interp.rs:1945).  `folded_range`: the four-u32 slot the producer of x
+        folded its range into (then only the quantize pass runs); `out`: (y, scale, zp) tensors to reuse."""
+        import torch
+        if out is None:
+            out = (torch.empty(x.shape, dtype=torch.uint8, device=x.device),
+                   torch.empty((), dtype=torch.float32, device=x.device),
+                   torch.empty((), dtype=torch.uint8, device=x.device))
+        y, scale, zp = out
+        if folded_range is None:
+            self.check(lib().ovk_dynamic_quantize(self.h, _ptr(x), x.numel(), _ptr(y), _ptr(scale), _ptr(zp)))
+        else:
+            self.check(lib().ovk_dynamic_quantize_folded(self.h, _ptr(x), x.numel(), _ptr(folded_range), _ptr(y),
+                                                         _ptr(scale), _ptr(zp)))
+        return y, scale, zp
+
+    def decomposed_gelu(self, x, divisor, offset, factor, factor_first=False):
+        """interp::decomposed_gelu (interp.rs:9060): erf(x / divisor) + offset, times x and factor."""
+        import torch
+        out = torch.empty_like(x)
+        self.check(lib().ovk_decomposed_gelu(self.h, _ptr(x), x.numel(), float(divisor), float(offset), float(factor),
+                                             int(factor_first), _ptr(out)))
+        return out
+
+    def decomposed_gelu_quantize(self, x, divisor, offset, factor, factor_first=False):
+        """interp::decomposed_gelu_quantize (interp.rs:9125): DynamicQuantizeLinear of the GELU, which is never stored."""
         import torch
         y = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
         scale = torch.empty((), dtype=torch.float32, device=x.device)
         zp = torch.empty((), dtype=torch.uint8, device=x.device)
-        self.check(lib().ovk_dynamic_quantize(self.h, _ptr(x), x.numel(), _ptr(y), _ptr(scale), _ptr(zp)))
+        self.check(lib().ovk_decomposed_gelu_quantize(self.h, _ptr(x), x.numel(), float(divisor), float(offset),
+                                                      float(factor), int(factor_first), _ptr(y), _ptr(scale), _ptr(zp)))
         return y, scale, zp
 
     # --------------------------------------------------------- MatMulInteger

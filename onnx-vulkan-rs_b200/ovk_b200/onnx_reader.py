@@ -2,7 +2,7 @@
 
 Enough to feed exported weights of the quantized matrix-product operators
 through the C ABI without any ONNX package: it walks the protobuf wire format
-of ``ModelProto -> GraphProto -> {NodeProto, TensorProto}`` (the public ONNX
+of ``ModelProto -> GraphProto -> {NodeProto, TensorProto}``, external weight files included (the public ONNX
 schema; the reference vendors it as crates/onnx-vulkan-frontend/proto/onnx.proto
 and converts it in crates/onnx-vulkan-frontend/src/convert.rs) and ignores every
 field it does not need.  It does no shape inference and follows no sub-graphs.
@@ -101,10 +101,38 @@ def _packed_varints(value, wire):
     return out
 
 
-def _tensor(buf):
+def _external_bytes(name, entries, base_dir, np_dtype, count):
+    """The bytes of a tensor kept in a file beside the model (TensorProto.external_data: location, offset,
+    length), as the reference's loader resolves them against the model's directory
+    (crates/onnx-vulkan-frontend/src/lib.rs:52-63)."""
+    import os
+    if base_dir is None:
+        raise OnnxFormatError(f"initializer {name!r} keeps its data in an external file, and the model was given as "
+                              "bytes without the directory it came from")
+    location = entries.get("location")
+    if not location:
+        raise OnnxFormatError(f"initializer {name!r}: external data without a location")
+    path = os.path.normpath(os.path.join(base_dir, location))
+    if os.path.isabs(location) or os.path.relpath(path, base_dir).startswith(".."):
+        raise OnnxFormatError(f"initializer {name!r}: external data outside the model's directory ({location!r})")
+    offset = int(entries.get("offset", "0") or 0)
+    length = int(entries["length"]) if entries.get("length") else count * np_dtype.itemsize
+    try:
+        with open(path, "rb") as fh:
+            fh.seek(offset)
+            data = fh.read(length)
+    except OSError as e:
+        raise OnnxFormatError(f"initializer {name!r}: cannot read external data {location!r}: {e}") from e
+    if len(data) != length:
+        raise OnnxFormatError(f"initializer {name!r}: external file {location!r} is short ({len(data)} of {length} bytes)")
+    return data
+
+
+def _tensor(buf, base_dir=None):
     dims, dtype, name, raw = [], 0, "", None
     floats, ints32, ints64 = [], [], []
     external = False
+    entries = {}
     for number, wire, value in _fields(buf):
         if number == 1:
             dims += _packed_varints(value, wire)
@@ -120,14 +148,22 @@ def _tensor(buf):
             name = bytes(value).decode()
         elif number == 9:
             raw = bytes(value)
+        elif number == 13 and wire == 2:  # StringStringEntryProto {key = 1, value = 2}
+            key = val = ""
+            for n2, _, v2 in _fields(value):
+                if n2 == 1:
+                    key = bytes(v2).decode()
+                elif n2 == 2:
+                    val = bytes(v2).decode()
+            entries[key] = val
         elif number == 14 and value == 1:
             external = True
-    if external:
-        raise OnnxFormatError(f"initializer {name!r} keeps its data in an external file, which this reader does not follow")
     if dtype not in _DTYPES:
         raise OnnxFormatError(f"initializer {name!r} has data type {dtype}, which this reader does not decode")
     np_dtype = np.dtype(_DTYPES[dtype])
     count = int(np.prod(dims, dtype=np.int64)) if dims else 1
+    if external:
+        raw = _external_bytes(name, entries, base_dir, np_dtype, count)
     if raw is not None:
         arr = np.frombuffer(raw, dtype=np_dtype.newbyteorder("<"))
     elif dtype == 1:
@@ -143,7 +179,7 @@ def _tensor(buf):
     return name, np.ascontiguousarray(arr.astype(np_dtype, copy=False)).reshape(dims)
 
 
-def _attribute(buf):
+def _attribute(buf, base_dir=None):
     name, kind = "", 0
     f = i = s = t = None
     ints, floats, strings = [], [], []
@@ -159,7 +195,7 @@ def _attribute(buf):
         elif number == 4:
             s = bytes(value)
         elif number == 5:
-            t = _tensor(value)[1]
+            t = _tensor(value, base_dir)[1]
         elif number == 7:
             floats += list(struct.unpack(f"<{len(value) // 4}f", bytes(value))) if wire == 2 else [struct.unpack("<f", value)[0]]
         elif number == 8:
@@ -176,7 +212,7 @@ def _attribute(buf):
     return name, ints or floats or strings or None
 
 
-def _node(buf):
+def _node(buf, base_dir=None):
     node = NodeInfo()
     for number, _, value in _fields(buf):
         if number == 1:
@@ -190,7 +226,7 @@ def _node(buf):
         elif number == 7:
             node.domain = bytes(value).decode()
         elif number == 5:
-            key, val = _attribute(value)
+            key, val = _attribute(value, base_dir)
             node.attrs[key] = val
     return node
 
@@ -202,8 +238,9 @@ def _value_name(buf):
     return ""
 
 
-def parse(data: bytes) -> Model:
-    """Parses the bytes of a ``.onnx`` file."""
+def parse(data: bytes, base_dir: str | None = None) -> Model:
+    """Parses the bytes of a ``.onnx`` file.  ``base_dir`` is the directory external weight files are
+    looked up in; without it a model that has any is refused (the reference's ``load_from_bytes(bytes, None)``)."""
     view = memoryview(data)
     graph, opsets = None, {}
     for number, wire, value in _fields(view):
@@ -224,9 +261,9 @@ def parse(data: bytes) -> Model:
         if wire != 2:
             continue
         if number == 1:
-            nodes.append(_node(value))
+            nodes.append(_node(value, base_dir))
         elif number == 5:
-            name, arr = _tensor(value)
+            name, arr = _tensor(value, base_dir)
             inits[name] = arr
         elif number == 11:
             inputs.append(_value_name(value))
@@ -236,8 +273,10 @@ def parse(data: bytes) -> Model:
 
 
 def load(path: str) -> Model:
+    """Reads a model file; external weights are resolved against its directory."""
+    import os
     with open(path, "rb") as fh:
-        return parse(fh.read())
+        return parse(fh.read(), os.path.dirname(os.path.abspath(path)))
 
 
 # ------------------------------------------------------------------ onto the host layer

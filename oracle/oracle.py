@@ -117,6 +117,32 @@ def dynamic_quantize(x):
     return y, np.float32(scale.value), int(zp.value)
 
 
+def decomposed_gelu(x, divisor, offset, factor, factor_first=False):
+    """DecomposedGelu (shaders/elementwise.rs:71-118): erf(x / divisor) + offset, times x and factor."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    lib().orc_decomposed_gelu(_p(x), C.c_size_t(x.size), C.c_float(divisor), C.c_float(offset), C.c_float(factor),
+                              C.c_int(int(factor_first)), _p(out))
+    return out
+
+
+def decomposed_gelu_quantize(x, divisor, offset, factor, factor_first=False):
+    """DynamicQuantizeLinear(DecomposedGelu(x)) (interp.rs:9125): the two nodes, one after the other."""
+    return dynamic_quantize(decomposed_gelu(x, divisor, offset, factor, factor_first))
+
+
+def erf_approx(x: float) -> float:
+    f = lib().orc_erf_approx
+    f.restype, f.argtypes = C.c_float, [C.c_float]
+    return float(f(C.c_float(x)))
+
+
+def exp_ieee(x: float) -> float:
+    f = lib().orc_exp_ieee
+    f.restype, f.argtypes = C.c_float, [C.c_float]
+    return float(f(C.c_float(x)))
+
+
 def _bytes(a):
     a = np.ascontiguousarray(a)
     assert a.dtype in (np.uint8, np.int8), a.dtype

@@ -289,6 +289,71 @@ ORC_EXPORT void orc_dynamic_quantize(const float *x, size_t n, uint8_t *y, float
     }
 }
 
+/* -------------------------------------------------------- DecomposedGelu */
+
+/*
+ * exp for the erf approximation below.  The reference's shader calls the
+ * device's exp(), which no two devices round alike; this restatement and the
+ * CUDA kernels spell it in IEEE operations only - reduction by ln 2 in two
+ * parts, a degree-7 polynomial in fused multiply-adds, scaling by exponent
+ * bits in two exact steps - so that both give the same bits.
+ */
+static inline float exp_ieee(float x)
+{
+    if (!(x > -104.0f))
+        return x != x ? x : 0.0f;
+    const float n = nearbyintf(x * 1.44269504088896341f);
+    float r = fmaf(n, -0.693145751953125f, x);
+    r = fmaf(n, -1.42860682030941723e-6f, r);
+    float p = 1.0f / 5040.0f;
+    p = fmaf(p, r, 1.0f / 720.0f);
+    p = fmaf(p, r, 1.0f / 120.0f);
+    p = fmaf(p, r, 1.0f / 24.0f);
+    p = fmaf(p, r, 1.0f / 6.0f);
+    p = fmaf(p, r, 0.5f);
+    p = fmaf(p, r, 1.0f);
+    p = fmaf(p, r, 1.0f);
+    const int e = (int)n;
+    const int e1 = e / 2, e2 = e - e1;
+    union { uint32_t u; float f; } s1, s2;
+    s1.u = (uint32_t)(e1 + 127) << 23;
+    s2.u = (uint32_t)(e2 + 127) << 23;
+    return (p * s1.f) * s2.f;
+}
+
+/* erf_approx of src/shaders/elementwise.rs:71-80 (Abramowitz & Stegun 7.1.26), each operation rounded. */
+static inline float erf_approx(float x)
+{
+    const float s = x > 0.0f ? 1.0f : (x < 0.0f ? -1.0f : 0.0f);
+    const float a = fabsf(x);
+    const float t = 1.0f / (1.0f + 0.3275911f * a);
+    float poly = t * 1.061405429f;
+    poly = t * (-1.453152027f + poly);
+    poly = t * (1.421413741f + poly);
+    poly = t * (-0.284496736f + poly);
+    poly = t * (0.254829592f + poly);
+    return s * (1.0f - poly * exp_ieee(-a * a));
+}
+
+/*
+ * decomposed_gelu of src/shaders/elementwise.rs:110-118 (host side
+ * src/interp.rs:9034-9084): e = erf(v / divisor) + offset, then the graph's
+ * order of the two products.
+ */
+ORC_EXPORT void orc_decomposed_gelu(const float *x, size_t n, float divisor, float offset, float factor,
+                                    int factor_first, float *out)
+{
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; i++) {
+        const float v = x[i];
+        const float e = erf_approx(v / divisor) + offset;
+        out[i] = factor_first ? v * (e * factor) : (v * e) * factor;
+    }
+}
+
+ORC_EXPORT float orc_erf_approx(float x) { return erf_approx(x); }
+ORC_EXPORT float orc_exp_ieee(float x) { return exp_ieee(x); }
+
 /* -------------------------------------------------------- MatMulInteger */
 
 static inline int64_t byte_val(const uint8_t *p, size_t i, int is_signed)

@@ -1,5 +1,7 @@
 """DynamicQuantizeLinear parity: bit-equal scale, equal zero point, 0 differing
 bytes (crates/onnx-vulkan-core/tests/dynamic_quantize.rs:60-76)."""
+import math
+
 import numpy as np
 import pytest
 import torch
@@ -55,3 +57,64 @@ def test_parakeet_activations(d):
     """Config 3: fp32 activations ~N(0,1) [T=1000, d_model or FF]."""
     x = cases.rng_for(3, 0).standard_normal((1000, d), dtype=np.float32)
     check(x)
+
+
+# ------------------------------------------------------------------ folded range, DecomposedGelu
+
+def test_folded_range_skips_the_range_pass_and_gives_the_same_bytes():
+    """interp.rs:1979-1983: when the producer of x folded its range into a slot, only the quantize pass
+    runs.  Here the producer is the fused MatMulInteger epilogue; the quantization that follows it equals
+    the two-pass one byte for byte, and the slot is left zero for the next producer."""
+    m, k, n = 700, 96, 330
+    a = cases.lcg_bytes_fast(m * k, 11).reshape(m, k)
+    b = cases.lcg_bytes_fast(k * n, 2).reshape(k, n).view(np.int8)
+    w = ctx().mmi_prepack(dev(b))
+    scale = dev(np.array([0.0123 * 3.1e-3], dtype=np.float32))
+    bias = dev(np.random.default_rng(5).uniform(-0.5, 0.5, n).astype(np.float32))
+    slot = torch.zeros(4, dtype=torch.int32, device="cuda")
+    x = ctx().matmul_integer_scale_bias(w, dev(a), dev(np.array([131], dtype=np.uint8)), None, scale, bias,
+                                        relu=True, range_slot=slot)
+    before = ctx().launches
+    y, s, z = ctx().dynamic_quantize(x, folded_range=slot)
+    assert ctx().launches - before == 1 and ctx().last_kernel == "dql_quantize"
+    want_y, want_s, want_z = orc.dynamic_quantize(host(x))
+    assert np.array_equal(host(y), want_y) and float(s) == float(want_s) and int(z) == want_z
+    assert slot.cpu().tolist() == [0, 0, 0, 0]
+    y2, s2, z2 = ctx().dynamic_quantize(x)  # both passes
+    assert np.array_equal(host(y2), want_y) and float(s2) == float(want_s)
+
+
+GELU = (float(np.float32(np.sqrt(2.0))), 1.0, 0.5)  # the constants of the exact GELU: x / sqrt 2, + 1, * 0.5
+
+
+@pytest.mark.parametrize("factor_first", [False, True])
+def test_decomposed_gelu_matches_the_port_bit_for_bit(factor_first):
+    """shaders/elementwise.rs:71-118: every step rounded on its own, both orders of the closing products;
+    exp spelled in IEEE operations, so the CPU port and the kernel give the same bits."""
+    x = cases.rng_for(3, 7).standard_normal((1000, 4096), dtype=np.float32) * np.float32(3.0)
+    x.reshape(-1)[:8] = [0.0, -0.0, 1e-30, -1e-30, 12.5, -12.5, 40.0, -40.0]
+    got = host(ctx().decomposed_gelu(dev(x), *GELU, factor_first=factor_first))
+    want = orc.decomposed_gelu(x, *GELU, factor_first=factor_first)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    ref = np.array([0.5 * v * (1.0 + math.erf(v / math.sqrt(2.0))) for v in x.reshape(-1)[:4096].astype(np.float64)])
+    assert np.abs(got.reshape(-1)[:4096] - ref).max() < 2e-6  # the five-term erf is good to 1.5e-7, times |x|
+
+
+@pytest.mark.parametrize("shape", [(1000, 4096), (3, 77), (1,)])
+def test_decomposed_gelu_quantize_equals_the_two_nodes(shape):
+    """interp.rs:9125-9150: the fused node's bytes, scale and zero point are those of DecomposedGelu followed
+    by DynamicQuantizeLinear - on the device, and in the CPU port."""
+    x = (cases.rng_for(3, 8).standard_normal(shape, dtype=np.float32) * np.float32(2.0)).astype(np.float32)
+    y, s, z = ctx().decomposed_gelu_quantize(dev(x), *GELU)
+    assert ctx().last_kernel == "dql_quantize"
+    g = ctx().decomposed_gelu(dev(x), *GELU)
+    y2, s2, z2 = ctx().dynamic_quantize(g)
+    assert np.array_equal(host(y), host(y2)) and float(s) == float(s2) and int(z) == int(z2)
+    want_y, want_s, want_z = orc.decomposed_gelu_quantize(x, *GELU)
+    assert np.array_equal(host(y), want_y) and float(s) == float(want_s) and int(z) == want_z
+
+
+def test_decomposed_gelu_quantize_of_nothing():
+    y, s, z = ctx().decomposed_gelu_quantize(torch.empty((0, 8), device="cuda"), *GELU)
+    ctx().flush()
+    assert float(s) == 1.0 and int(z) == 0 and y.numel() == 0

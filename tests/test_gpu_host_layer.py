@@ -375,3 +375,41 @@ def test_replacing_an_initializer_rebuilds_its_prepared_weight(hl, env):
     env.set("w", w2, initializer=True)
     env.execute(cv)
     assert np.array_equal(env.host("c"), orc.conv_integer(x, w2, 0, 0, pads=(1, 1, 1, 1)))
+
+
+def test_decomposed_gelu_quantize_node_and_the_range_a_producer_folded(hl, env):
+    """The Parakeet FF block as nodes (rewrite.rs:445-542, :699-735): MatMulIntegerScaleBias folds the range of
+    its output, the DynamicQuantizeLinear after it runs one pass; DecomposedGeluQuantize keeps the GELU's
+    inputs and attribute and the quantization's outputs."""
+    import math
+    m, k, n = 70, 96, 64
+    a = cases.lcg_bytes_fast(m * k, 5).reshape(m, k)
+    b = cases.lcg_bytes_fast(k * n, 17).reshape(k, n).view(np.int8)
+    scale = np.array([2e-3], dtype=np.float32)
+    bias = cases.rng_for(23, 1).standard_normal(n, dtype=np.float32)
+    env.set("a", a)
+    env.set("b", b, initializer=True)
+    env.set("az", np.array([121], dtype=np.uint8))
+    env.set("s", scale, initializer=True)
+    env.set("bias", bias, initializer=True)
+    env.execute(hl.Node("MatMulIntegerScaleBias", ["a", "b", "az", "", "s", "bias"], ["h"], range=1))
+    env.execute(hl.Node("DynamicQuantizeLinear", ["h"], ["hq", "hs", "hz"]))
+    assert env.last_kernel == "dql_quantize"
+    h = orc.scale_bias_epilogue(orc.matmul_integer(a, b, 121, 0), scale, 0, bias, 1)
+    assert np.array_equal(env.host("h").view(np.uint32), h.view(np.uint32))
+    want = orc.dynamic_quantize(h)
+    assert np.array_equal(env.host("hq"), want[0]) and env.host("hs").reshape(()) == want[1]
+    # the GELU of the same tensor, quantized without being stored
+    for name, v in (("c1", math.sqrt(2.0)), ("c2", 1.0), ("c3", 0.5)):
+        env.set(name, np.array(v, dtype=np.float32), initializer=True)
+    env.execute(hl.Node("DecomposedGeluQuantize", ["h", "c1", "c2", "c3"], ["gq", "gs", "gz"], factor_first=1))
+    gq, gs, gz = orc.decomposed_gelu_quantize(h, float(np.float32(math.sqrt(2.0))), 1.0, 0.5, True)
+    assert np.array_equal(env.host("gq"), gq) and env.host("gs").reshape(()) == gs and int(env.host("gz").reshape(())) == gz
+    env.execute(hl.Node("DecomposedGelu", ["h", "c1", "c2", "c3"], ["g"], factor_first=1))
+    g = orc.decomposed_gelu(h, float(np.float32(math.sqrt(2.0))), 1.0, 0.5, True)
+    assert np.array_equal(env.host("g").view(np.uint32), g.view(np.uint32))
+    # a constant that is a vector is the form the reference replays as five nodes: refused here
+    env.set("c1", np.full(n, math.sqrt(2.0), dtype=np.float32), initializer=True)
+    with pytest.raises(hl.OvkError) as err:
+        env.execute(hl.Node("DecomposedGelu", ["h", "c1", "c2", "c3"], ["g2"]))
+    assert err.value.status == 2 and "replays" in str(err.value)

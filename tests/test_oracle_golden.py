@@ -454,3 +454,34 @@ def test_quantize_dequantize_linear_per_tensor_and_per_axis():
     bias = np.array([-70000, 5, 123456], dtype=np.int32)
     assert np.array_equal(orc.dequantize_linear(bias, np.array([0.25], dtype=np.float32)),
                           bias.astype(np.float32) * np.float32(0.25))
+
+
+# ------------------------------------------------------------------ DecomposedGelu
+
+def test_decomposed_gelu_port_follows_the_shader_arithmetic():
+    """shaders/elementwise.rs:71-118, restated independently in numpy float32 step by step (with the
+    port's own exp, the one function the shader leaves to the device), and close to the exact GELU:
+    the five-term erf is good to 1.5e-7."""
+    import math
+    x = np.concatenate([np.linspace(-9, 9, 3001), [0.0, -0.0, 1e-20, 30.0, -30.0]]).astype(np.float32)
+    f = np.float32
+    for factor_first in (False, True):
+        got = orc.decomposed_gelu(x, float(f(math.sqrt(2.0))), 1.0, 0.5, factor_first)
+        v = x / f(math.sqrt(2.0))
+        s, a = np.sign(v).astype(f), np.abs(v)
+        t = f(1.0) / (f(1.0) + f(0.3275911) * a)
+        poly = t * f(1.061405429)
+        for c in (-1.453152027, 1.421413741, -0.284496736, 0.254829592):
+            poly = t * (f(c) + poly)
+        ex = np.array([orc.exp_ieee(float(-ai * ai)) for ai in a], dtype=f)
+        e = s * (f(1.0) - poly * ex) + f(1.0)
+        want = x * (e * f(0.5)) if factor_first else (x * e) * f(0.5)
+        assert np.array_equal(got.view(np.uint32), want.astype(f).view(np.uint32))
+        exact = np.array([0.5 * float(xi) * (1.0 + math.erf(float(xi) / math.sqrt(2.0))) for xi in x])
+        assert np.abs(got - exact).max() < 5e-6
+    for xv in np.linspace(-103.0, 2.0, 2001):  # exp in IEEE operations: about one ulp
+        want = math.exp(float(f(xv)))
+        assert abs(orc.exp_ieee(float(f(xv))) - want) <= 1.5 * 1.2e-7 * want + 1e-45
+    y, scale, zp = orc.decomposed_gelu_quantize(x, float(f(math.sqrt(2.0))), 1.0, 0.5)
+    y2, scale2, zp2 = orc.dynamic_quantize(orc.decomposed_gelu(x, float(f(math.sqrt(2.0))), 1.0, 0.5))
+    assert np.array_equal(y, y2) and scale == scale2 and zp == zp2
