@@ -281,62 +281,57 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
         del g, table, sc, zp, logits
 
     # ---- dynamic int8 encoder GEMMs, Parakeet-shaped (config 3): replicas
+    # One FastConformer layer's six GEMMs in the order the graph runs them, each tensor quantised ONCE:
+    #   x -> DynamicQuantizeLinear -> q, k, v (three GEMMs over the same bytes)
+    #   attention output -> DynamicQuantizeLinear -> o
+    #   FF input -> DynamicQuantizeLinear -> FF1 (1024 -> 4096, f32 out)
+    #   FF1 output -> DecomposedGeluQuantize (the f32 GELU is never stored) -> FF2 (4096 -> 1024)
     t = 1000
     layer = [(1024, 1024)] * 4 + [(1024, 4096), (4096, 1024)]
-    ws, xs, scs, bis = [], {}, [], []
+    ws, scs, bis = [], [], []
     for k, n in layer:
         ws.append(ctx.mmi_prepack(torch.randint(-127, 128, (k, n), dtype=torch.int8, device="cuda", generator=gen)))
         scs.append(torch.rand((n,), device="cuda", generator=gen) * 0.009 + 0.001)
         bis.append(torch.zeros((n,), device="cuda"))
-        if k not in xs:
-            xs[k] = torch.randn((t, k), device="cuda", generator=gen)
+    x_in, a_in, f_in = (torch.randn((t, 1024), device="cuda", generator=gen) for _ in range(3))
+    gelu_c = (float(np.float32(np.sqrt(2.0))), 1.0, 0.5)
+
+    def gemm(i, q):
+        xq, a_scale, a_zp = q
+        return ctx.matmul_integer_scale_bias(ws[i], xq, a_zp, None, scs[i], bis[i], product=a_scale.reshape(1))
 
     def layer_step():
-        for (k, n), w, sc, bi in zip(layer, ws, scs, bis):
-            xq, a_scale, a_zp = ctx.dynamic_quantize(xs[k])
-            ctx.matmul_integer_scale_bias(w, xq, a_zp, None, sc, bi, product=a_scale.reshape(1))
+        q = ctx.dynamic_quantize(x_in)
+        for i in range(3):
+            gemm(i, q)
+        gemm(3, ctx.dynamic_quantize(a_in))
+        h = gemm(4, ctx.dynamic_quantize(f_in))
+        gemm(5, ctx.decomposed_gelu_quantize(h, *gelu_c))
+    before = ctx.launches
     layer_step()
+    layer_launches = ctx.launches - before
     layer_kernel = ctx.last_kernel
     torch.cuda.synchronize()
-    # twelve launches of 5-20 us each: replayed from a graph so that the device, not Python, is timed
+    # fourteen launches of 3-15 us each: replayed from a graph so that the device, not Python, is timed
     gl = torch.cuda.CUDAGraph()
     with torch.cuda.graph(gl, stream=torch.cuda.current_stream()):
         layer_step()
     ms_l = timed(torch, dist, world, gl.replay, 10)
     del gl
     ops = sum(2.0 * t * k * n for k, n in layer)
-    out["int8_dynamic_parakeet_layer"] = {"T": t, "gemms": len(layer), "ms_per_layer": ms_l, "kernel": layer_kernel,
-                                          "tops": world * ops / (ms_l * 1e-3) / 1e12,
-                                          "note": "DynamicQuantizeLinear + MatMulInteger with the fused f32 epilogue; "
-                                                  "2-8 GOP per GEMM, latency/HBM-bound; replicas at N > 1"}
+    out["int8_dynamic_parakeet_layer"] = {"T": t, "gemms": len(layer), "launches": layer_launches, "ms_per_layer": ms_l,
+                                          "kernel": layer_kernel, "tops": world * ops / (ms_l * 1e-3) / 1e12,
+                                          "note": "3 x DynamicQuantizeLinear + DecomposedGeluQuantize + 6 x MatMulInteger with "
+                                                  "the fused f32 epilogue (q, k, v share one quantisation); 2-8 GOP per "
+                                                  "GEMM, latency/HBM-bound; replicas at N > 1"}
     big = ctx.mmi_prepack(torch.randint(-127, 128, (8192, 8192), dtype=torch.int8, device="cuda", generator=gen))
     xa = torch.randint(0, 256, (8192, 8192), dtype=torch.uint8, device="cuda", generator=gen)
     zp8 = torch.full((1,), 128, dtype=torch.uint8, device="cuda")
     ms_b = timed(torch, dist, world, lambda: ctx.matmul_integer(big, xa, zp8, None), 5)
-    # the dense int8 peak, measured here: what back-to-back kind::i8 MMAs deliver per clock per SM, times
-    # the SMs, times the clock the GPU held while this GEMM ran (sampled by nvidia-smi during a second run)
-    mac_rate = ctx.probe_mma_rate(ovk_int8_code())
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
-    skip = sampler.wait_first_sample(lambda: (ctx.matmul_integer(big, xa, zp8, None), torch.cuda.synchronize()))
-    w0 = time.perf_counter()
-    while time.perf_counter() - w0 < 0.5:
-        for _ in range(4):
-            ctx.matmul_integer(big, xa, zp8, None)
-        torch.cuda.synchronize()
-    int8_clocks = sampler.stop(skip)
-    sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
-    mhz = int8_clocks.get("sm_mhz") or 1965.0
-    int8_peak = 2.0 * mac_rate * sm_count * mhz * 1e6 / 1e12
-    out["int8_peak_tops_measured"] = {"value": int8_peak, "mac_per_clk_per_sm": mac_rate, "sms": sm_count, "sm_mhz": mhz,
-                                      "clock_reasons": int8_clocks.get("reasons"),
-                                      "how": "2 x MAC/clk/SM of back-to-back 128x256x32 tcgen05.mma kind::i8 (ovk_probe_mma_rate) "
-                                             "x SMs x the median SM clock sampled while the 8192^3 GEMM ran"}
     tops_b = 2.0 * 8192 ** 3 / (ms_b * 1e-3) / 1e12
     out["int8_gemm_8192"] = {"ms": ms_b, "kernel": ctx.last_kernel, "tops_per_gpu": tops_b,
-                             "frac_of_measured_int8_peak": tops_b / int8_peak,
                              "frac_of_2x_measured_bf16_peak": tops_b / (2 * bf16_peak)}
-    del ws, xs, big, xa
+    del ws
 
     # ---- static int8 QLinearConv, ResNet block (config 4): batch 64 split over the ranks
     bsh = shard.batch_shard(64, world, rank)
@@ -372,11 +367,60 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
                                           "algorithmic_gbs": 3.0 * qa.numel() / (ms_a * 1e-3) / 1e9,
                                           "frac_of_measured_hbm": 3.0 * qa.numel() / (ms_a * 1e-3) / 1e9 / peaks["hbm_gbs"]}
         del qa, qb
+    # the same layer inside a chain of quantized layers: activations stay channels-last in a frame that
+    # holds the zero point (the layout the kernel computes from), so a layer is ONE launch - no layout
+    # pass - and stores 16 channels per instruction into the next layer's input
+    frame = (1, 1, 1, 1)
+    cl_a = ctx.to_padded_nhwc(x, frame, 128)
+    cl_b = torch.full_like(cl_a, 128)
+    conv_cl = lambda src, dst: ctx.qlinear_conv_channels_last(wc, src, 128, 0, ratio, bias, 128, dst, frame, pads=frame)
+    conv_cl(cl_a, cl_b)
+    torch.cuda.synchronize()
+    cl_kernel = ctx.last_kernel
+    gc = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gc, stream=torch.cuda.current_stream()):
+        for _ in range(5):
+            conv_cl(cl_a, cl_b)
+            conv_cl(cl_b, cl_a)
+    ms_cl = timed(torch, dist, world, gc.replay, 10) / 10
+    del gc, gq
+    # the dense int8 peak, measured here: what back-to-back kind::i8 MMAs deliver per clock per SM, times
+    # the SMs, times the clock the GPU held while this GEMM ran (sampled by nvidia-smi during a second run)
+    mac_rate = ctx.probe_mma_rate(ovk_int8_code())
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    skip = sampler.wait_first_sample(lambda: (ctx.matmul_integer(big, xa, zp8, None), torch.cuda.synchronize()))
+    w0 = time.perf_counter()
+    while time.perf_counter() - w0 < 0.5:
+        for _ in range(4):
+            ctx.matmul_integer(big, xa, zp8, None)
+        torch.cuda.synchronize()
+    int8_clocks = sampler.stop(skip)
+    sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    mhz_sustained = int8_clocks.get("sm_mhz") or 1965.0
+    mhz_max = int8_clocks.get("sm_max_mhz") or 1965.0
+    # fractions below are against the rate at the MAXIMUM clock, which the short timed bursts run at (the
+    # smaller, stricter fraction); the rate at the clock a seconds-long run settles to is given beside it
+    int8_peak = 2.0 * mac_rate * sm_count * mhz_max * 1e6 / 1e12
+    out["int8_peak_tops_measured"] = {"value": int8_peak, "mac_per_clk_per_sm": mac_rate, "sms": sm_count, "sm_mhz": mhz_max,
+                                      "sustained": {"value": 2.0 * mac_rate * sm_count * mhz_sustained * 1e6 / 1e12,
+                                                    "sm_mhz": mhz_sustained, "clock_reasons": int8_clocks.get("reasons")},
+                                      "how": "2 x MAC/clk/SM of back-to-back 128x256x32 tcgen05.mma kind::i8 (ovk_probe_mma_rate) "
+                                             "x SMs x SM clock: the maximum clock, and the median sampled while the 8192^3 "
+                                             "GEMM ran for half a second"}
+    out["int8_gemm_8192"]["frac_of_measured_int8_peak"] = out["int8_gemm_8192"]["tops_per_gpu"] / int8_peak
+    del big, xa
     ops = 2.0 * 64 * 64 * 56 * 56 * 576
+    conv_bytes = 2.0 * 64 * 64 * 56 * 56
     out["int8_qlinear_conv_resnet_block"] = {"batch": 64, "ms": ms_q, "kernel": conv_kernel,
                                              "tops": ops / (ms_q * 1e-3) / 1e12,
                                              "frac_of_measured_int8_peak": ops / (ms_q * 1e-3) / 1e12 / (world * int8_peak),
-                                             "frac_of_measured_hbm": 2.0 * 64 * 64 * 56 * 56 / (ms_q * 1e-3) / 1e9 / (world * peaks["hbm_gbs"]),
+                                             "frac_of_measured_hbm": conv_bytes / (ms_q * 1e-3) / 1e9 / (world * peaks["hbm_gbs"]),
+                                             "channels_last_chain": {
+                                                 "ms": ms_cl, "kernel": cl_kernel, "tops": ops / (ms_cl * 1e-3) / 1e12,
+                                                 "frac_of_measured_int8_peak": ops / (ms_cl * 1e-3) / 1e12 / (world * int8_peak),
+                                                 "frac_of_measured_hbm": conv_bytes / (ms_cl * 1e-3) / 1e9 / (world * peaks["hbm_gbs"]),
+                                                 "note": "padded-NHWC in and out (ovk_qlinear_conv_layout): one launch per layer"},
                                              "algorithmic_gbs": 2.0 * 64 * 64 * 56 * 56 / (ms_q * 1e-3) / 1e9,
                                              "parallelism": "batch-split x%d, no exchange" % world if world > 1 else "single"}
     return out
@@ -710,6 +754,11 @@ def run_one(which):
         bias = torch.zeros((64,), dtype=torch.int32, device="cuda")
         ratio = np.full(64, 0.002, dtype=np.float32)
         fn = lambda: ctx.qlinear_conv(w, x, 128, 0, ratio, bias, 128, pads=(1, 1, 1, 1))
+        if which == "conv_cl":  # the same layer channels-last in and out: one launch
+            frame = (1, 1, 1, 1)
+            xa = ctx.to_padded_nhwc(x, frame, 128)
+            xb = torch.full_like(xa, 128)
+            fn = lambda: ctx.qlinear_conv_channels_last(w, xa, 128, 0, ratio, bias, 128, xb, frame, pads=frame)
     for _ in range(3):
         fn()
     ctx.flush()
@@ -808,7 +857,7 @@ def main():
     ap.add_argument("--launch", default="grouped", choices=["grouped", "branches", "serial"],
                     help="how the independent GEMVs of a layer (q|k|v, gate|up) are launched: one launch per group, "
                          "parallel graph branches, or one launch per GEMV in a single chain")
-    ap.add_argument("--one", default=None, choices=["lm_head", "prefill", "prefill32", "int8", "int8big", "conv"],
+    ap.add_argument("--one", default=None, choices=["lm_head", "prefill", "prefill32", "int8", "int8big", "conv", "conv_cl"],
                     help="run one operator three times and exit (small target for an ncu capture)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -339,6 +339,37 @@ OVK_API int32_t ovk_qlinear_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const 
                                  int32_t x_signed, const ovk_conv_params *p, int32_t x_zp,
                                  int32_t w_zp, const float *ratio_host, const int32_t *bias,
                                  int32_t y_zp, int32_t y_signed, void *y);
+/* QLinearConv over channels-last tensors.  The reference keeps activations
+ * channels-last between the layers of its tensor path (to_hwc once, then HWC
+ * from layer to layer: shaders/conv_integer.rs:485-527, interp.rs:5719-5748);
+ * here the layout is "padded NHWC": [n][h + top + bottom][w + left + right][c]
+ * with the frame holding the tensor's zero point - exactly what the
+ * tensor-core kernel computes from, so a layer that receives it skips the
+ * layout pass, and a layer that produces it writes 16 channels per store
+ * straight into the interior of the next layer's input (whose frame the caller
+ * filled once with that layer's x_zero_point = this layer's y_zero_point).
+ *  - x_layout OVK_LAYOUT_PADDED_NHWC: x is padded NHWC whose frame is p->pads;
+ *  - y_layout OVK_LAYOUT_PADDED_NHWC: y is padded NHWC with frame y_pads
+ *    {top, left, bottom, right}; only its interior is written; C_out must be a
+ *    multiple of 16.
+ * Either layout may be OVK_LAYOUT_NCHW (then this is ovk_qlinear_conv).  Taken
+ * by the stride-1, group-1, symmetric-weight kernel; other geometries are
+ * refused with OVK_UNSUPPORTED in a channels-last layout.  Same bytes as
+ * ovk_qlinear_conv. */
+#define OVK_LAYOUT_NCHW 0
+#define OVK_LAYOUT_PADDED_NHWC 1
+OVK_API int32_t ovk_qlinear_conv_layout(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x,
+                                        int32_t x_signed, int32_t x_layout, const ovk_conv_params *p,
+                                        int32_t x_zp, int32_t w_zp, const float *ratio_host,
+                                        const int32_t *bias, int32_t y_zp, int32_t y_signed, void *y,
+                                        int32_t y_layout, const int64_t *y_pads);
+/* The two ends of a channels-last chain (to_hwc, shaders/conv_integer.rs:485-527):
+ * NCHW u8/i8 [n, c, h, w] -> padded NHWC with the frame set to the byte `fill`,
+ * and back (the frame is dropped).  c a multiple of 4; out 16-byte aligned. */
+OVK_API int32_t ovk_nchw_to_padded_nhwc(ovk_ctx *ctx, const void *x, int64_t n, int64_t c, int64_t h,
+                                        int64_t w, const int64_t *pads, int32_t fill, void *out);
+OVK_API int32_t ovk_padded_nhwc_to_nchw(ovk_ctx *ctx, const void *x, int64_t n, int64_t c, int64_t h,
+                                        int64_t w, const int64_t *pads, void *out);
 /* The REQUANTIZE pass on its own (shaders/qlinear.rs:28-63): c = (i / inner) % axis_len. */
 OVK_API int32_t ovk_requantize(ovk_ctx *ctx, const int32_t *acc, int64_t count, int64_t inner,
                                int64_t axis_len, const int32_t *bias, const float *ratio,

@@ -550,10 +550,9 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         const int bs_shift = 31 - __clz(p.bs);  // block sizes are powers of two
         int seq = 0;       // number of slabs before the current item's first one
         int pending = -1;  // A stage stored to but not yet announced
-        // ring positions are stepped, not computed (six stages: no power of two): slab g sits in stage
-        // s_g on the ring's lap of parity ph_g, and the slab A_STAGES before it likewise in s_b / ph_b
-        int g_at = 0, s_g = 0, s_b = STAGES - A_STAGES;
-        uint32_t ph_g = 0, ph_b = 1;
+        // This loop is the kernel's pace-setter, so ring positions are stepped by two inside an item (six
+        // stages: no power of two) and divided out only once per item: slab g sits in stage s_g on the
+        // ring's lap of parity ph_g, and the slab A_STAGES before it likewise in s_b / ph_b.
         bool ok = true;
         Run run = cta_run(p);
         int tile, ub, ue;
@@ -571,18 +570,11 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
             };
             int i = (seq ^ group) & 1;  // the first slab of this item that this group takes
             uint32_t z_next = i < len ? zero_points(sl0 + i) : 0u;
+            int s_g = (seq + i) % STAGES, s_b = (seq + i + STAGES - A_STAGES) % STAGES;
+            uint32_t ph_g = uint32_t((seq + i) / STAGES) & 1u;
+            uint32_t ph_b = uint32_t((seq + i + STAGES - A_STAGES) / STAGES + 1) & 1u;
             for (; i < len; i += 2) {
                 const int g = seq + i;
-                for (; g_at < g; g_at++) {
-                    if (++s_g == STAGES) {
-                        s_g = 0;
-                        ph_g ^= 1;
-                    }
-                    if (++s_b == STAGES) {
-                        s_b = 0;
-                        ph_b ^= 1;
-                    }
-                }
                 const uint32_t z0 = z_next & 0xffu, z1 = z_next >> 8;
                 if (i + 2 < len)
                     z_next = zero_points(sl0 + i + 2);
@@ -630,6 +622,16 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                 umma::tc_fence_after();
                 pending = g & (A_STAGES - 1);
                 umma::tmem_st_32x32(a_lane + uint32_t(pending * A_COLS), wv);
+                s_g += 2;
+                if (s_g >= STAGES) {
+                    s_g -= STAGES;
+                    ph_g ^= 1u;
+                }
+                s_b += 2;
+                if (s_b >= STAGES) {
+                    s_b -= STAGES;
+                    ph_b ^= 1u;
+                }
             }
             seq += len;
         }

@@ -168,6 +168,14 @@ struct ConvGeom {
     int kh, kw, sh, sw, dh, dw, phb, pwb, phe, pwe;
 };
 
+// Which of the two tensor layouts a convolution call reads and writes: the operator's NCHW, or
+// channels-last inside a frame, [n][h + top + bottom][w + left + right][c], the frame holding the
+// tensor's zero point (the layout the tensor-core kernel computes from).
+struct ConvLayout {
+    int x_cl = 0, y_cl = 0;
+    int y_pads[4] = {0, 0, 0, 0};  // top, left, bottom, right frame of the output
+};
+
 struct ovk_qconv_weight {
     int64_t c_out = 0, cig = 0, kh = 0, kw = 0, group = 1;
     int32_t w_signed = 0;

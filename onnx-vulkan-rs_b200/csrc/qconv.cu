@@ -15,7 +15,8 @@
 bool ovk_qconv_tc_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, const void *x);
 int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,
                             const ConvGeom &g, int32_t x_zp, int32_t w_zp, const EpiParams &epi,
-                            void *out);
+                            void *out, const ConvLayout &lay);
+int32_t ovk_qconv_pad_nhwc(ovk_ctx *ctx, const void *x, const ConvGeom &g, int32_t fill, uint8_t *xp);
 int32_t ovk_qconv_tc_prepare_weight(ovk_ctx *ctx, ovk_qconv_weight *w);
 
 namespace {
@@ -143,9 +144,27 @@ int32_t make_geom(ovk_ctx *ctx, const ovk_qconv_weight *w, const ovk_conv_params
     return OVK_OK;
 }
 
+// [n][h + frame][w + frame][c] -> NCHW: the end of a channels-last chain.  A block takes one image row:
+// its pixels go through shared memory so that reads run along C and writes along W.
+__global__ void __launch_bounds__(256)
+unpad_nchw_kernel(const uint8_t *__restrict__ xp, uint8_t *__restrict__ out, int C, int H, int W, int HP, int WP, int pt,
+                  int pl)
+{
+    extern __shared__ uint8_t row[];  // [W][C + 1]
+    const int h = blockIdx.x, n = blockIdx.y;
+    const uint8_t *src = xp + ((size_t(n) * HP + h + pt) * WP + pl) * size_t(C);
+    for (int i = threadIdx.x; i < W * C; i += blockDim.x)
+        row[(i / C) * (C + 1) + i % C] = src[i];
+    __syncthreads();
+    for (int i = threadIdx.x; i < W * C; i += blockDim.x) {
+        const int c = i / W, w = i - c * W;
+        out[((size_t(n) * C + c) * H + h) * W + w] = row[w * (C + 1) + c];
+    }
+}
+
 int32_t run_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,
                  const ovk_conv_params *p, int32_t x_zp, int32_t w_zp, const EpiParams &epi,
-                 void *out, const char *op)
+                 void *out, const char *op, const ConvLayout &lay = ConvLayout())
 {
     if (!ctx || !w || !p)
         return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "%s: null argument", op);
@@ -159,10 +178,13 @@ int32_t run_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t
     OVK_REQUIRE(ctx, x && out, "%s: x or the output is null", op);
     OVK_CUDA(ctx, cudaSetDevice(ctx->device));
     if (ovk_qconv_tc_applies(ctx, w, g, x)) {
-        const int32_t rc_tc = ovk_qconv_tc_launch(ctx, w, x, x_signed, g, x_zp, w_zp, epi, out);
+        const int32_t rc_tc = ovk_qconv_tc_launch(ctx, w, x, x_signed, g, x_zp, w_zp, epi, out, lay);
         if (rc_tc != OVK_UNSUPPORTED)  // an asymmetric weight or no room for the stages: the direct kernel runs
             return rc_tc;
     }
+    // the direct kernel reads and writes the operator's layout only
+    OVK_REFUSE(ctx, lay.x_cl || lay.y_cl,
+               "%s: the channels-last layout is taken by the stride-1, group-1, symmetric-weight tensor-core kernel only", op);
     conv_direct_kernel<<<unsigned(ceil_div64(total, 256)), 256, 0, ctx->stream>>>(
         static_cast<const uint8_t *>(x), w->w, g, x_signed, w->w_signed, x_zp, w_zp, epi, out, total);
     OVK_LAUNCHED(ctx, "conv_direct");
@@ -269,10 +291,9 @@ int32_t ovk_conv_integer_scale_bias(ovk_ctx *ctx, const ovk_qconv_weight *w, con
     return run_conv(ctx, w, x, x_signed, p, x_zp, w_zp, epi, out, "ConvIntegerScaleBias");
 }
 
-int32_t ovk_qlinear_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,
-                         const ovk_conv_params *p, int32_t x_zp, int32_t w_zp,
-                         const float *ratio_host, const int32_t *bias, int32_t y_zp,
-                         int32_t y_signed, void *y)
+static int32_t qlinear_conv_any(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,
+                                const ovk_conv_params *p, int32_t x_zp, int32_t w_zp, const float *ratio_host,
+                                const int32_t *bias, int32_t y_zp, int32_t y_signed, void *y, const ConvLayout &lay)
 {
     if (!ctx || !w)
         return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "QLinearConv: null argument");
@@ -297,7 +318,97 @@ int32_t ovk_qlinear_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x,
     epi.ibias = bias;
     epi.y_zp = y_zp;
     epi.y_signed = y_signed;
-    return run_conv(ctx, w, x, x_signed, p, x_zp, w_zp, epi, y, "QLinearConv");
+    return run_conv(ctx, w, x, x_signed, p, x_zp, w_zp, epi, y, "QLinearConv", lay);
+}
+
+int32_t ovk_qlinear_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,
+                         const ovk_conv_params *p, int32_t x_zp, int32_t w_zp,
+                         const float *ratio_host, const int32_t *bias, int32_t y_zp,
+                         int32_t y_signed, void *y)
+{
+    return qlinear_conv_any(ctx, w, x, x_signed, p, x_zp, w_zp, ratio_host, bias, y_zp, y_signed, y, ConvLayout());
+}
+
+int32_t ovk_qlinear_conv_layout(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,
+                                int32_t x_layout, const ovk_conv_params *p, int32_t x_zp, int32_t w_zp,
+                                const float *ratio_host, const int32_t *bias, int32_t y_zp, int32_t y_signed,
+                                void *y, int32_t y_layout, const int64_t *y_pads)
+{
+    if (!ctx || !w)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "QLinearConv: null argument");
+    OVK_REQUIRE(ctx, (x_layout | 1) == 1 && (y_layout | 1) == 1, "QLinearConv: a layout is OVK_LAYOUT_NCHW or OVK_LAYOUT_PADDED_NHWC");
+    ConvLayout lay;
+    lay.x_cl = x_layout == OVK_LAYOUT_PADDED_NHWC;
+    lay.y_cl = y_layout == OVK_LAYOUT_PADDED_NHWC;
+    if (lay.y_cl) {
+        OVK_REQUIRE(ctx, y_pads, "QLinearConv: a channels-last output needs its frame (y_pads)");
+        for (int i = 0; i < 4; i++) {
+            OVK_REQUIRE(ctx, y_pads[i] >= 0 && y_pads[i] < 65536, "QLinearConv: y_pads[%d] = %lld", i, (long long)y_pads[i]);
+            lay.y_pads[i] = int(y_pads[i]);
+        }
+        OVK_REFUSE(ctx, w->c_out % 16 != 0, "QLinearConv: a channels-last output needs C_out = %lld to be a multiple of 16",
+                   (long long)w->c_out);
+        OVK_REQUIRE(ctx, aligned_to(y, 16), "QLinearConv: a channels-last output must be 16-byte aligned");
+    }
+    if (lay.x_cl)
+        OVK_REQUIRE(ctx, aligned_to(x, 16), "QLinearConv: a channels-last input must be 16-byte aligned");
+    return qlinear_conv_any(ctx, w, x, x_signed, p, x_zp, w_zp, ratio_host, bias, y_zp, y_signed, y, lay);
+}
+
+static int32_t layout_geom(ovk_ctx *ctx, const char *op, int64_t n, int64_t c, int64_t h, int64_t w, const int64_t *pads,
+                           ConvGeom *g)
+{
+    OVK_REQUIRE(ctx, pads, "%s: pads is null", op);
+    OVK_REQUIRE(ctx, n >= 0 && c > 0 && h > 0 && w > 0 && n < (1 << 24) && c < (1 << 16) && h < (1 << 20) && w < (1 << 20),
+                "%s: bad shape [%lld,%lld,%lld,%lld]", op, (long long)n, (long long)c, (long long)h, (long long)w);
+    for (int i = 0; i < 4; i++)
+        OVK_REQUIRE(ctx, pads[i] >= 0 && pads[i] < 65536, "%s: pads[%d] = %lld", op, i, (long long)pads[i]);
+    OVK_REFUSE(ctx, c % 4 != 0, "%s: %lld channels (a multiple of 4)", op, (long long)c);
+    *g = ConvGeom{};
+    g->n = int(n);
+    g->c_in = int(c);
+    g->h_in = int(h);
+    g->w_in = int(w);
+    g->phb = int(pads[0]);
+    g->pwb = int(pads[1]);
+    g->phe = int(pads[2]);
+    g->pwe = int(pads[3]);
+    return OVK_OK;
+}
+
+int32_t ovk_nchw_to_padded_nhwc(ovk_ctx *ctx, const void *x, int64_t n, int64_t c, int64_t h, int64_t w,
+                                const int64_t *pads, int32_t fill, void *out)
+{
+    if (!ctx)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "ovk_nchw_to_padded_nhwc: null context");
+    ConvGeom g;
+    int32_t rc = layout_geom(ctx, "ovk_nchw_to_padded_nhwc", n, c, h, w, pads, &g);
+    if (rc != OVK_OK || n == 0)
+        return rc;
+    OVK_REQUIRE(ctx, x && out && aligned_to(out, 16), "ovk_nchw_to_padded_nhwc: x or out is null, or out is not 16-byte aligned");
+    OVK_CUDA(ctx, cudaSetDevice(ctx->device));
+    return ovk_qconv_pad_nhwc(ctx, x, g, fill, static_cast<uint8_t *>(out));
+}
+
+int32_t ovk_padded_nhwc_to_nchw(ovk_ctx *ctx, const void *x, int64_t n, int64_t c, int64_t h, int64_t w,
+                                const int64_t *pads, void *out)
+{
+    if (!ctx)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "ovk_padded_nhwc_to_nchw: null context");
+    ConvGeom g;
+    int32_t rc = layout_geom(ctx, "ovk_padded_nhwc_to_nchw", n, c, h, w, pads, &g);
+    if (rc != OVK_OK || n == 0)
+        return rc;
+    OVK_REQUIRE(ctx, x && out, "ovk_padded_nhwc_to_nchw: x or out is null");
+    const size_t sm = size_t(w) * (c + 1);
+    OVK_REFUSE(ctx, sm > 48 * 1024, "ovk_padded_nhwc_to_nchw: rows of %lld pixels x %lld channels are too large", (long long)w,
+               (long long)c);
+    OVK_CUDA(ctx, cudaSetDevice(ctx->device));
+    unpad_nchw_kernel<<<dim3(unsigned(h), unsigned(n)), 256, sm, ctx->stream>>>(
+        static_cast<const uint8_t *>(x), static_cast<uint8_t *>(out), int(c), int(h), int(w), int(h + pads[0] + pads[2]),
+        int(w + pads[1] + pads[3]), int(pads[0]), int(pads[1]));
+    OVK_LAUNCHED(ctx, "unpad_nchw");
+    return OVK_OK;
 }
 
 int32_t ovk_requantize(ovk_ctx *ctx, const int32_t *acc, int64_t count, int64_t inner,

@@ -60,6 +60,12 @@ struct ConvTcParams {
     int nacc;
     int issuers;  // 1 or 2 MMA-issuing threads
     uint64_t magic_hpwp, magic_wp;  // ceil(2^64 / divisor), 0 for a divisor of 1
+    // requantised bytes stored channels-last into a padded image [n][h_out + frame][w_out + frame][c_out]
+    // (the input layout of the next convolution) instead of NCHW
+    int out_cl;
+    int y_wp;               // padded row of the output image, in pixels
+    int64_t y_hpwp;         // padded plane of the output image, in pixels
+    int y_pt, y_pl;         // frame above and to the left
 };
 
 __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
@@ -100,6 +106,11 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     uint32_t *s_tap_w = s_tap_a + 64;
     float *s_fbias = reinterpret_cast<float *>(s_tap_w + 64);  // present only for the scale-and-bias store
 
+    // The next kernel of the stream, if it was launched as a programmatic dependent (the next layer of a
+    // channels-last chain is), may be scheduled as SMs fall free: its launch latency and its prologue -
+    // barriers, tensor memory, its filter bank - then overlap this kernel's tail.  It reads what this
+    // kernel writes only behind its own griddepcontrol.wait, which returns when this grid has finished.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int tap = threadIdx.x; tap < p.taps && tap < 64; tap += THREADS) {
         const int off = (tap / p.kw) * p.dh * p.wp + (tap % p.kw) * p.dw;
@@ -386,6 +397,27 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                             run_neg = fmaxf(run_neg, -z);
                         }
                     }
+                } else if (p.out_cl) {
+                    // the same bytes, channels-last: this pixel's 16 channels are 16 contiguous bytes, one store
+                    uint32_t packed[4];
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4) {
+                        uint32_t word = 0;
+#pragma unroll
+                        for (int t = 0; t < 4; t++) {
+                            const int32_t acc = int32_t(r[j + t] + uint32_t(corr[j + t]));
+                            const float x = __fmul_rn(float(acc), ratio[j + t]);
+                            const float xc = fminf(fmaxf(x, clamp_lo), clamp_hi);
+                            const int32_t qv = __float_as_int(__fadd_rn(xc, 12582912.0f)) + round_fix;
+                            word |= (uint32_t(qv) & 0xffu) << (8 * t);
+                        }
+                        packed[j >> 2] = word;
+                    }
+                    uint8_t *o = static_cast<uint8_t *>(p.out) +
+                                 ((int64_t(img) * p.y_hpwp + int64_t(int(oh) + p.y_pt) * p.y_wp + (int(ow) + p.y_pl)) *
+                                      p.c_out + c0);
+                    if (nch > 0)  // C_out is a multiple of 16 here: a group exists whole or not at all
+                        *reinterpret_cast<uint4 *>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 } else {
                     uint8_t *o = static_cast<uint8_t *>(p.out) + o_base + int64_t(c0) * plane;
 #pragma unroll
@@ -651,20 +683,13 @@ bool ovk_qconv_tc_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const C
     return v_total >= 4 * BM && v_total < (int64_t(1) << 31) - 65536 && (wp * g.c_in) % 4 == 0;
 }
 
-int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed, const ConvGeom &g,
-                            int32_t x_zp, int32_t w_zp, const EpiParams &epi, void *out)
+// NCHW x -> xp[n][h + frame][w + frame][c] with the frame set to `fill` (the layout pass of the
+// convolution, also an entry point of its own).  g gives n, c_in, h_in, w_in and the four pads.
+int32_t ovk_qconv_pad_nhwc(ovk_ctx *ctx, const void *x, const ConvGeom &g, int32_t fill, uint8_t *xp)
 {
-    if (w_zp != 0)
-        return OVK_UNSUPPORTED;  // caller falls back to the direct kernel
     const int C = g.c_in;
     const int HP = g.h_in + g.phb + g.phe, WP = g.w_in + g.pwb + g.pwe;
-    const int64_t v_total = int64_t(g.n) * HP * WP;
-    const size_t xp_bytes = size_t(v_total) * C;
-    void *ws = nullptr;
-    int32_t rc = ovk_scratch(ctx, xp_bytes + 1024, &ws);
-    if (rc != OVK_OK)
-        return rc;
-    uint8_t *xp = static_cast<uint8_t *>(ws);
+    const int32_t x_zp = fill;
     const bool fast_layout = (g.w_in % 4) == 0 && (C % 16) == 0 && aligned_to(x, 4) && g.w_in <= 1024;
     if (fast_layout) {
         const int R = std::max(1, std::min(g.h_in, 256 / g.w_in));  // about 256 pixels per block
@@ -690,7 +715,36 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
             pitch, words_ok);
         OVK_LAUNCHED(ctx, "conv_pad_nhwc");
     }
+    return OVK_OK;
+}
+
+int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed, const ConvGeom &g,
+                            int32_t x_zp, int32_t w_zp, const EpiParams &epi, void *out, const ConvLayout &lay)
+{
+    if (w_zp != 0)
+        return OVK_UNSUPPORTED;  // caller falls back to the direct kernel
+    const int C = g.c_in;
+    const int HP = g.h_in + g.phb + g.phe, WP = g.w_in + g.pwb + g.pwe;
+    const int64_t v_total = int64_t(g.n) * HP * WP;
+    const uint8_t *xp = static_cast<const uint8_t *>(x);
+    if (!lay.x_cl) {
+        // the operator's NCHW: one pass rewrites it; a channels-last caller has done that once, upstream
+        const size_t xp_bytes = size_t(v_total) * C;
+        void *ws = nullptr;
+        int32_t rc = ovk_scratch(ctx, xp_bytes + 1024, &ws);
+        if (rc != OVK_OK)
+            return rc;
+        rc = ovk_qconv_pad_nhwc(ctx, x, g, x_zp, static_cast<uint8_t *>(ws));
+        if (rc != OVK_OK)
+            return rc;
+        xp = static_cast<const uint8_t *>(ws);
+    }
     ConvTcParams p = {};
+    p.out_cl = lay.y_cl;
+    p.y_pt = lay.y_pads[0];
+    p.y_pl = lay.y_pads[1];
+    p.y_wp = g.w_out + lay.y_pads[1] + lay.y_pads[3];
+    p.y_hpwp = int64_t(g.h_out + lay.y_pads[0] + lay.y_pads[2]) * p.y_wp;
     p.v_total = v_total;
     p.hpwp = HP * WP;
     p.wp = WP;

@@ -92,6 +92,10 @@ SIGNATURES = {
     "ovk_conv_integer_scale_bias": (_I32, [_P, _P, _P, _I32, C.POINTER(ConvParams), _I32, _I32, _P, _I32, _P, _I32,
                                            _P, _I32, _U32, _P, _P]),
     "ovk_qlinear_conv": (_I32, [_P, _P, _P, _I32, C.POINTER(ConvParams), _I32, _I32, _P, _P, _I32, _I32, _P]),
+    "ovk_qlinear_conv_layout": (_I32, [_P, _P, _P, _I32, _I32, C.POINTER(ConvParams), _I32, _I32, _P, _P, _I32, _I32, _P,
+                                       _I32, C.POINTER(_I64)]),
+    "ovk_nchw_to_padded_nhwc": (_I32, [_P, _P, _I64, _I64, _I64, _I64, C.POINTER(_I64), _I32, _P]),
+    "ovk_padded_nhwc_to_nchw": (_I32, [_P, _P, _I64, _I64, _I64, _I64, C.POINTER(_I64), _P]),
     "ovk_requantize": (_I32, [_P, _P, _I64, _I64, _I64, _P, _P, _I32, _I32, _P]),
     "ovk_gather_block_quantized": (_I32, [_P, _P, _P, _I32, _P, _I64, _I64, _I64, _I64, _P, _I32, _I32, _I64, _P, _I32]),
     "ovk_argmax": (_I32, [_P, _P, _I32, _I64, _I64, _I64, _P]),
@@ -408,6 +412,46 @@ class Context:
         self.check(lib().ovk_qlinear_conv(self.h, w.h, _ptr(x), int(x.dtype == torch.int8), C.byref(p),
                                           int(x_zp), int(w_zp), ratio.ctypes.data, _ptr(bias),
                                           int(y_zp), int(y_signed), _ptr(out)))
+        return out
+
+    def to_padded_nhwc(self, x, pads, fill, out=None):
+        """NCHW u8/i8 -> [n][h + top + bottom][w + left + right][c], the frame set to `fill`; pads = (top, left,
+        bottom, right)."""
+        import torch
+        n, c, h, w = x.shape
+        if out is None:
+            out = torch.empty((n, h + pads[0] + pads[2], w + pads[1] + pads[3], c), dtype=x.dtype, device=x.device)
+        self.check(lib().ovk_nchw_to_padded_nhwc(self.h, _ptr(x.contiguous()), n, c, h, w, (_I64 * 4)(*pads),
+                                                 int(fill) & 0xff, _ptr(out)))
+        return out
+
+    def from_padded_nhwc(self, xp, pads):
+        import torch
+        n, hp, wp, c = xp.shape
+        h, w = hp - pads[0] - pads[2], wp - pads[1] - pads[3]
+        out = torch.empty((n, c, h, w), dtype=xp.dtype, device=xp.device)
+        self.check(lib().ovk_padded_nhwc_to_nchw(self.h, _ptr(xp), n, c, h, w, (_I64 * 4)(*pads), _ptr(out)))
+        return out
+
+    def qlinear_conv_channels_last(self, w: "QConvWeight", x, x_zp, w_zp, ratio, bias, y_zp, out, out_pads=None,
+                                   y_signed=False, pads=(0, 0, 0, 0), dilations=(1, 1), x_nchw=False, strides=(1, 1)):
+        """QLinearConv from a padded-NHWC x (frame = `pads`, holding x_zp; or NCHW with x_nchw=True) into the
+        interior of the padded-NHWC `out` whose frame is `out_pads` (None: `out` is NCHW)."""
+        import numpy as np
+        import torch
+        if x_nchw:
+            n, c, h, wd = x.shape
+        else:
+            n, hp, wp, c = x.shape
+            h, wd = hp - pads[0] - pads[2], wp - pads[1] - pads[3]
+        ratio = np.ascontiguousarray(ratio, dtype=np.float32)
+        if ratio.size == 1:
+            ratio = np.repeat(ratio, w.c_out)
+        p = ConvParams(n, c, h, wd, (C.c_int64 * 4)(*pads), (C.c_int64 * 2)(*strides), (C.c_int64 * 2)(*dilations))
+        self.check(lib().ovk_qlinear_conv_layout(self.h, w.h, _ptr(x), int(x.dtype == torch.int8), 0 if x_nchw else 1,
+                                                 C.byref(p), int(x_zp), int(w_zp), ratio.ctypes.data, _ptr(bias),
+                                                 int(y_zp), int(y_signed), _ptr(out), 0 if out_pads is None else 1,
+                                                 None if out_pads is None else (_I64 * 4)(*out_pads)))
         return out
 
     def requantize(self, acc, inner, ratio, y_zp, bias=None, y_signed=False):

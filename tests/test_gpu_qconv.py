@@ -4,6 +4,7 @@ import os
 
 import numpy as np
 import pytest
+import torch
 
 import cases
 import oracle as orc
@@ -242,3 +243,84 @@ def test_conv_integer_scale_bias_refusals():
     with pytest.raises(ovk_b200.OvkError) as err:
         ctx().conv_integer_scale_bias(wq, x, 0, 0, dev(np.ones(6, dtype=np.float32)), ok)
     assert "step" in str(err.value)
+
+
+# ------------------------------------------------------------------ channels-last chain
+
+def _nhwc(a):
+    return np.ascontiguousarray(np.moveaxis(a, 1, -1))
+
+
+def test_layout_converters_round_trip():
+    x = cases.lcg_bytes_fast(3 * 64 * 10 * 12, 9).reshape(3, 64, 10, 12)
+    pads = (1, 2, 3, 0)
+    xp = ctx().to_padded_nhwc(dev(x), pads, 131)
+    got = host(xp)
+    assert got.shape == (3, 14, 14, 64)
+    want = np.full(got.shape, 131, dtype=np.uint8)
+    want[:, 1:11, 2:14, :] = _nhwc(x)
+    assert np.array_equal(got, want)
+    assert np.array_equal(host(ctx().from_padded_nhwc(xp, pads)), x)
+    odd = cases.lcg_bytes_fast(2 * 8 * 5 * 7, 4).reshape(2, 8, 5, 7)  # a width that is no multiple of 4: the general pass
+    xo = ctx().to_padded_nhwc(dev(odd), (1, 1, 1, 1), 7)
+    assert np.array_equal(host(ctx().from_padded_nhwc(xo, (1, 1, 1, 1))), odd)
+
+
+def test_two_layer_chain_stays_channels_last():
+    """Config 4's block twice in a row, batch 3: NCHW -> [layer 1] -> padded NHWC -> [layer 2] -> padded NHWC
+    -> NCHW.  Layer 1 pays the layout pass once; layer 2 reads what layer 1 stored - straight into the
+    interior of a buffer whose frame already holds layer 2's x_zero_point - and launches ONE kernel.  Bytes
+    equal the operator applied twice (the CPU port), and nothing outside the interior is written."""
+    x, w, w_scale, bias = _resnet_block(3)
+    w2 = cases.rng_for(4, 11).integers(-127, 128, size=(64, 64, 3, 3), dtype=np.int8)
+    ratio1 = orc.requantize_ratio(0.02, w_scale, 0.05)
+    ratio2 = orc.requantize_ratio(0.05, w_scale[::-1].copy(), 0.04)
+    wq1, wq2 = ctx().qconv_prepack(dev(w)), ctx().qconv_prepack(dev(w2))
+    frame = (1, 1, 1, 1)
+    mid = torch.full((3, 58, 58, 64), 128, dtype=torch.uint8, device="cuda")  # frame = layer 2's x_zp
+    end = torch.full((3, 58, 57, 64), 9, dtype=torch.uint8, device="cuda")   # an uneven frame (2, 0, 0, 1), value 9
+    ctx().qlinear_conv_channels_last(wq1, dev(x), 128, 0, ratio1, dev(bias), 128, mid, frame, pads=frame, x_nchw=True)
+    assert ctx().last_kernel == "qconv_tc_halo"
+    before = ctx().launches
+    ctx().qlinear_conv_channels_last(wq2, mid, 128, 0, ratio2, None, 100, end, (2, 0, 0, 1), pads=frame)
+    assert ctx().launches - before == 1 and ctx().last_kernel == "qconv_tc_halo"
+    y1 = orc.qlinear_conv(x, 0.02, 128, w, w_scale, 0, 0.05, 128, bias=bias, pads=frame)
+    y2 = orc.qlinear_conv(y1, 0.05, 128, w2, w_scale[::-1].copy(), 0, 0.04, 100, pads=frame)
+    got_mid, got_end = host(mid), host(end)
+    assert np.array_equal(got_mid[:, 1:57, 1:57, :], _nhwc(y1))
+    frame_mask = np.ones(got_mid.shape, dtype=bool)
+    frame_mask[:, 1:57, 1:57, :] = False
+    assert (got_mid[frame_mask] == 128).all()
+    assert np.array_equal(got_end[:, 2:58, 0:56, :], _nhwc(y2))
+    end_mask = np.ones(got_end.shape, dtype=bool)
+    end_mask[:, 2:58, 0:56, :] = False
+    assert (got_end[end_mask] == 9).all()
+    # the same second layer back into the operator's layout
+    nchw = torch.empty((3, 64, 56, 56), dtype=torch.uint8, device="cuda")
+    ctx().qlinear_conv_channels_last(wq2, mid, 128, 0, ratio2, None, 100, nchw, None, pads=frame)
+    assert np.array_equal(host(nchw), y2)
+    assert np.array_equal(host(ctx().from_padded_nhwc(end[:, 2:58, 0:56, :].contiguous(), (0, 0, 0, 0))), y2)
+
+
+def test_channels_last_signed_dilated_and_refusals():
+    import ovk_b200
+    x = cases.lcg_bytes_fast(2 * 32 * 18 * 22, 6).reshape(2, 32, 18, 22).view(np.int8)
+    w = cases.lcg_bytes_fast(48 * 32 * 9, 8).reshape(48, 32, 3, 3).view(np.int8)
+    w_scale = np.linspace(0.002, 0.02, 48).astype(np.float32)
+    ratio = orc.requantize_ratio(0.05, w_scale, 0.4)
+    wq = ctx().qconv_prepack(dev(w))
+    pads = (2, 0, 1, 3)
+    xp = ctx().to_padded_nhwc(dev(x), pads, -5)
+    want = orc.qlinear_conv(x, 0.05, -5, w, w_scale, 0, 0.4, -11, out_signed=True, pads=pads, dilations=(2, 2))
+    out = torch.zeros((2, want.shape[2] + 2, want.shape[3] + 2, 48), dtype=torch.int8, device="cuda")
+    ctx().qlinear_conv_channels_last(wq, xp, -5, 0, ratio, None, -11, out, (1, 1, 1, 1), y_signed=True, pads=pads,
+                                     dilations=(2, 2))
+    assert np.array_equal(host(out)[:, 1:-1, 1:-1, :], _nhwc(want))
+    with pytest.raises(ovk_b200.OvkError) as e:  # stride 2: the direct kernel's geometry, NCHW only
+        ctx().qlinear_conv_channels_last(wq, xp, -5, 0, ratio, None, -11, out, (1, 1, 1, 1), y_signed=True, pads=pads,
+                                         strides=(2, 2))
+    assert e.value.status == ovk_b200.UNSUPPORTED
+    w40 = ctx().qconv_prepack(dev(w[:40].copy()))
+    with pytest.raises(ovk_b200.OvkError) as e:  # 40 output channels are not whole 16-byte groups
+        ctx().qlinear_conv_channels_last(w40, xp, -5, 0, ratio[:40], None, -11, out, (1, 1, 1, 1), y_signed=True, pads=pads)
+    assert e.value.status == ovk_b200.UNSUPPORTED
