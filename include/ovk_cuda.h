@@ -286,6 +286,27 @@ OVK_API int32_t ovk_matmul_integer_scale_bias(ovk_ctx *ctx, const ovk_mmi_weight
                                               int32_t product_step, const float *bias,
                                               int32_t bias_step, uint32_t flags, uint32_t *range,
                                               float *out);
+/* The same products for up to four weights that read the SAME A - the q, k and
+ * v projections over one DynamicQuantizeLinear result: out_j = A x B_j with the
+ * members' own column constants.  One launch when every member takes the
+ * 128-row tensor-core tiles (then a member's tiles are just more tiles of the
+ * same grid, which also fills the SMs better than three narrow products), one
+ * call per member otherwise; results are those of separate calls.  scale_step
+ * and bias_step apply to every member; product is one value (NULL: none); no
+ * range is folded.  No counterpart in the reference, whose interpreter
+ * dispatches MatMulInteger nodes one at a time (interp.rs:1071). */
+OVK_API int32_t ovk_matmul_integer_group(ovk_ctx *ctx, int32_t count,
+                                         const ovk_mmi_weight *const *weights, const void *a,
+                                         int32_t a_signed, int64_t m, const void *a_zp,
+                                         const void *b_zp, int32_t *const *outs);
+OVK_API int32_t ovk_matmul_integer_scale_bias_group(ovk_ctx *ctx, int32_t count,
+                                                    const ovk_mmi_weight *const *weights,
+                                                    const void *a, int32_t a_signed, int64_t m,
+                                                    const void *a_zp, const void *b_zp,
+                                                    const float *const *scales, int32_t scale_step,
+                                                    const float *product, int32_t product_step,
+                                                    const float *const *biases, int32_t bias_step,
+                                                    uint32_t flags, float *const *outs);
 /* interp::qlinear_matmul (interp.rs:4845-4875): MatMulInteger then
  * requantize(inner = 1, axis_len = ratio_len); ratio is a device array of
  * ratio_len (1 or N) floats computed by the caller as (a_scale*b_scale)/y_scale. */

@@ -10,6 +10,9 @@
 #include "epilogue.cuh"
 
 bool ovk_mmi_tc_applies(const ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int64_t m);
+int32_t ovk_mmi_tc_launch_group(ovk_ctx *ctx, int count, const ovk_mmi_weight *const *ws, const void *a, int32_t a_signed,
+                                int64_t m, const void *a_zp, const void *b_zp, const EpiParams *epis, void *const *outs);
+bool ovk_mmi_wants_large_tiles(const ovk_ctx *ctx, const ovk_mmi_weight *w, int64_t m);
 int32_t ovk_mmi_tc_launch(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int32_t a_signed,
                           int64_t m, const void *a_zp, const void *b_zp, const EpiParams &epi,
                           void *out);
@@ -236,6 +239,76 @@ int32_t ovk_matmul_integer_scale_bias(ovk_ctx *ctx, const ovk_mmi_weight *w, con
     epi.flags = flags;
     epi.range = range;
     return run_mmi(ctx, w, a, a_signed, m, a_zp, b_zp, epi, out, "MatMulIntegerScaleBias");
+}
+
+// Several weights over the same A (the q, k and v projections of an attention block).  One launch
+// when every member takes the 128-row tensor-core tiles and the members agree on K and on the
+// signedness of B; one call per member otherwise.  Results are those of separate calls.
+static int32_t run_mmi_group(ovk_ctx *ctx, int32_t count, const ovk_mmi_weight *const *ws, const void *a, int32_t a_signed,
+                             int64_t m, const void *a_zp, const void *b_zp, const EpiParams *epis, void *const *outs,
+                             const char *op)
+{
+    if (!ctx || !ws || !outs)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "%s: null argument", op);
+    OVK_REQUIRE(ctx, count >= 1 && count <= 4, "%s: a group of %d weights (1 to 4)", op, count);
+    for (int j = 0; j < count; j++)
+        OVK_REQUIRE(ctx, ws[j] && (outs[j] || m == 0), "%s: member %d of the group is null", op, j);
+    for (int j = 1; j < count; j++)
+        OVK_REQUIRE(ctx, ws[j]->k == ws[0]->k, "%s: member %d of the group has K=%lld, member 0 K=%lld", op, j,
+                    (long long)ws[j]->k, (long long)ws[0]->k);
+    bool together = count > 1 && m > 0 && a && ws[0]->k <= 33025 && !(epis[0].flags & OVK_EPILOGUE_RANGE);
+    for (int j = 0; together && j < count; j++)
+        together = ws[j]->n > 0 && ws[j]->b_signed == ws[0]->b_signed && ovk_mmi_tc_applies(ctx, ws[j], a, m) &&
+                   !ovk_mmi_wants_large_tiles(ctx, ws[j], m);
+    if (together) {
+        OVK_CUDA(ctx, cudaSetDevice(ctx->device));
+        return ovk_mmi_tc_launch_group(ctx, count, ws, a, a_signed, m, a_zp, b_zp, epis, outs);
+    }
+    for (int j = 0; j < count; j++) {
+        const int32_t rc = run_mmi(ctx, ws[j], a, a_signed, m, a_zp, b_zp, epis[j], outs[j], op);
+        if (rc != OVK_OK)
+            return rc;
+    }
+    return OVK_OK;
+}
+
+int32_t ovk_matmul_integer_group(ovk_ctx *ctx, int32_t count, const ovk_mmi_weight *const *weights, const void *a,
+                                 int32_t a_signed, int64_t m, const void *a_zp, const void *b_zp, int32_t *const *outs)
+{
+    EpiParams epis[4] = {};
+    for (int j = 0; j < 4; j++)
+        epis[j].mode = EPI_RAW;
+    return run_mmi_group(ctx, count, weights, a, a_signed, m, a_zp, b_zp, epis, reinterpret_cast<void *const *>(outs),
+                         "MatMulInteger");
+}
+
+int32_t ovk_matmul_integer_scale_bias_group(ovk_ctx *ctx, int32_t count, const ovk_mmi_weight *const *weights,
+                                            const void *a, int32_t a_signed, int64_t m, const void *a_zp, const void *b_zp,
+                                            const float *const *scales, int32_t scale_step, const float *product,
+                                            int32_t product_step, const float *const *biases, int32_t bias_step,
+                                            uint32_t flags, float *const *outs)
+{
+    if (!ctx || !scales || !biases)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "MatMulIntegerScaleBias: null argument");
+    OVK_REQUIRE(ctx, count >= 1 && count <= 4, "MatMulIntegerScaleBias: a group of %d weights (1 to 4)", count);
+    OVK_REFUSE(ctx, (scale_step | bias_step | product_step) & ~1,
+               "MatMulIntegerScaleBias: a scale, product or bias that broadcasts over rows is not fused");
+    OVK_REFUSE(ctx, flags & OVK_EPILOGUE_RANGE, "MatMulIntegerScaleBias: a group folds no range (its members are different tensors)");
+    OVK_REFUSE(ctx, product && product_step != 0, "MatMulIntegerScaleBias: the second scale factor of a group is one value");
+    EpiParams epis[4] = {};
+    for (int j = 0; j < count; j++) {
+        OVK_REQUIRE(ctx, scales[j] && biases[j], "MatMulIntegerScaleBias: scale or bias of member %d is null", j);
+        epis[j].mode = EPI_SCALE;
+        epis[j].scale = scales[j];
+        epis[j].scale_step = scale_step;
+        epis[j].product = product;
+        epis[j].product_step = 0;
+        epis[j].fbias = biases[j];
+        epis[j].bias_step = bias_step;
+        epis[j].flags = flags;
+    }
+    return run_mmi_group(ctx, count, weights, a, a_signed, m, a_zp, b_zp, epis, reinterpret_cast<void *const *>(outs),
+                         "MatMulIntegerScaleBias");
 }
 
 int32_t ovk_qlinear_matmul(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int32_t a_signed,

@@ -32,6 +32,28 @@ constexpr int A_BYTES = BM * BK;
 constexpr int THREADS = 224;  // TMA, issuer 0, four epilogue warps, issuer 1
 constexpr long long WAIT_CYCLES = 2000000000ll;  // about a second
 
+// Several weights over the same A in one launch (q, k and v of an attention block): the tiles of all
+// members form one list, a tile looks up its member, and only the columns' constants, the packed
+// weight and the output differ.
+constexpr int MAX_GROUP = 4;
+struct TcMember {
+    const int32_t *colsum;
+    const float *scale, *product, *fbias;
+    void *out;
+    int N;
+    int tile_end;  // number of column tiles of this member and those before it
+};
+struct TmGroup {
+    CUtensorMap m[MAX_GROUP];
+};
+// What the epilogue needs to know about the columns it stores.
+struct ColView {
+    const int32_t *colsum;
+    const float *scale, *product, *fbias;
+    void *out;
+    int N;
+};
+
 struct TcParams {
     int64_t M;
     int N, K, num_kb;
@@ -43,7 +65,45 @@ struct TcParams {
     void *out;
     int vec_ok;  // output rows may be written with 16-byte (int32/f32) or 4-byte (u8) stores
     int *status;
+    int members;  // 0: one weight (the fields above); else the group below
+    TcMember mem[MAX_GROUP];
 };
+
+__device__ __forceinline__ int column_tiles(const TcParams &p, int bn)
+{
+    return p.members ? p.mem[p.members - 1].tile_end : (p.N + bn - 1) / bn;
+}
+// Column tile `nt` of the launch: which member it belongs to and where its columns start there.
+__device__ __forceinline__ int member_of(const TcParams &p, int nt, int bn, int &n0)
+{
+    int j = 0, first = 0;
+    while (j + 1 < p.members && nt >= p.mem[j].tile_end) {
+        first = p.mem[j].tile_end;
+        j++;
+    }
+    n0 = (nt - first) * bn;
+    return j;
+}
+__device__ __forceinline__ ColView columns_of(const TcParams &p, int j)
+{
+    ColView v;
+    if (p.members) {
+        v.colsum = p.mem[j].colsum;
+        v.scale = p.mem[j].scale;
+        v.product = p.mem[j].product;
+        v.fbias = p.mem[j].fbias;
+        v.out = p.mem[j].out;
+        v.N = p.mem[j].N;
+    } else {
+        v.colsum = p.colsum;
+        v.scale = p.epi.scale;
+        v.product = p.epi.product;
+        v.fbias = p.epi.fbias;
+        v.out = p.out;
+        v.N = p.N;
+    }
+    return v;
+}
 
 __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
 {
@@ -75,8 +135,8 @@ __device__ __forceinline__ bool wait_parked(uint64_t *bar, uint32_t parity)
 // the zero-point terms, then the store selected by EpiParams.  `hand_back` gets this warp's arrival
 // as soon as the last columns have been read, before they are processed.
 template <int BN>
-__device__ __forceinline__ void epilogue_columns(const TcParams &p, uint32_t taddr, uint64_t *hand_back, int lane,
-                                                 int64_t row, bool row_ok, int n0, uint32_t row_term, int32_t za,
+__device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColView &v, uint32_t taddr, uint64_t *hand_back,
+                                                 int lane, int64_t row, bool row_ok, int n0, uint32_t row_term, int32_t za,
                                                  float &run_max, float &run_neg)
 {
     const bool vec4 = p.vec_ok != 0;
@@ -91,7 +151,7 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, uint32_t tad
             if (lane == 0)
                 umma::mbar_arrive(hand_back);
         }
-        if (n0 + c0 >= p.N)  // the same for every lane of the warp
+        if (n0 + c0 >= v.N)  // the same for every lane of the warp
             continue;
         const int col0 = n0 + c0;
         // Every thread of the warp needs the constants of the same 32 columns (a thread is a row).
@@ -100,15 +160,15 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, uint32_t tad
         // dequantising store several times as long as the int32 one.  All lanes take part, rows past
         // M included; only the stores are predicated.
         const int col_l = col0 + lane;
-        const bool col_ok = col_l < p.N;
-        const int32_t cs_l = col_ok ? p.colsum[col_l] : 0;
+        const bool col_ok = col_l < v.N;
+        const int32_t cs_l = col_ok ? v.colsum[col_l] : 0;
         float s_l = 0.0f, b_l = 0.0f;
         int32_t ib_l = 0;
         if (p.epi.mode == EPI_SCALE && col_ok) {
-            s_l = p.epi.scale[col_l * p.epi.scale_step];
-            if (p.epi.product)
-                s_l = __fmul_rn(s_l, p.epi.product[col_l * p.epi.product_step]);
-            b_l = p.epi.fbias[col_l * p.epi.bias_step];
+            s_l = v.scale[col_l * p.epi.scale_step];
+            if (v.product)
+                s_l = __fmul_rn(s_l, v.product[col_l * p.epi.product_step]);
+            b_l = v.fbias[col_l * p.epi.bias_step];
         } else if (p.epi.mode == EPI_REQUANT && col_ok) {
             s_l = p.epi.ratio[col_l * p.epi.ratio_step];
             ib_l = p.epi.ibias ? p.epi.ibias[col_l] : 0;
@@ -117,15 +177,15 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, uint32_t tad
         for (int j = 0; j < 32; j++)
             r[j] = r[j] - uint32_t(za) * uint32_t(__shfl_sync(0xffffffffu, cs_l, j)) + row_term;
         if (p.epi.mode == EPI_RAW) {
-            int32_t *o = static_cast<int32_t *>(p.out) + row * p.N + col0;
+            int32_t *o = static_cast<int32_t *>(v.out) + row * v.N + col0;
             if (!row_ok) {
                 // a row past M: nothing to store (no divergent `continue`: the next tcgen05.ld is warp-wide)
-            } else if (vec4 && col0 + 32 <= p.N) {
+            } else if (vec4 && col0 + 32 <= v.N) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
                     *reinterpret_cast<int4 *>(o + j) = make_int4(r[j], r[j + 1], r[j + 2], r[j + 3]);
             } else {
-                for (int j = 0; j < 32 && col0 + j < p.N; j++)
+                for (int j = 0; j < 32 && col0 + j < v.N; j++)
                     o[j] = int32_t(r[j]);
             }
         } else if (p.epi.mode == EPI_SCALE) {
@@ -137,19 +197,19 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, uint32_t tad
                 const float sj = __shfl_sync(0xffffffffu, s_l, j), bj = __shfl_sync(0xffffffffu, b_l, j);
                 const float z = __fadd_rn(__fmul_rn(float(int32_t(r[j])), sj), bj);
                 f[j] = relu ? fmaxf(z, 0.0f) : z;
-                if (row_ok && col0 + j < p.N) {
+                if (row_ok && col0 + j < v.N) {
                     run_max = fmaxf(run_max, f[j]);
                     run_neg = fmaxf(run_neg, -f[j]);
                 }
             }
-            float *o = static_cast<float *>(p.out) + row * p.N + col0;
+            float *o = static_cast<float *>(v.out) + row * v.N + col0;
             if (!row_ok) {
-            } else if (vec4 && col0 + 32 <= p.N) {
+            } else if (vec4 && col0 + 32 <= v.N) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
                     *reinterpret_cast<float4 *>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
             } else {
-                for (int j = 0; j < 32 && col0 + j < p.N; j++)
+                for (int j = 0; j < 32 && col0 + j < v.N; j++)
                     o[j] = f[j];
             }
         } else {
@@ -164,14 +224,14 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, uint32_t tad
                 qv = p.epi.y_signed ? max(-128, min(127, qv)) : max(0, min(255, qv));
                 q8[j] = uint32_t(qv) & 0xffu;
             }
-            uint8_t *o = static_cast<uint8_t *>(p.out) + row * p.N + col0;
+            uint8_t *o = static_cast<uint8_t *>(v.out) + row * v.N + col0;
             if (!row_ok) {
-            } else if (vec4 && col0 + 32 <= p.N) {
+            } else if (vec4 && col0 + 32 <= v.N) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
                     *reinterpret_cast<uint32_t *>(o + j) = q8[j] | (q8[j + 1] << 8) | (q8[j + 2] << 16) | (q8[j + 3] << 24);
             } else {
-                for (int j = 0; j < 32 && col0 + j < p.N; j++)
+                for (int j = 0; j < 32 && col0 + j < v.N; j++)
                     o[j] = uint8_t(q8[j]);
             }
         }
@@ -186,7 +246,7 @@ template <int BN> constexpr size_t smem_for()
 
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
-mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TcParams p)
+mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ TmGroup tmBs, const __grid_constant__ TcParams p)
 {
     constexpr int STAGES = stages_for<BN>();
     constexpr int B_BYTES = BN * BK;
@@ -203,7 +263,7 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     OVK_PDL_LAUNCH_DEPENDENTS();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // persistent: tiles are taken round robin, N fastest so that CTAs running together share rows of A
-    const int n_tiles = (p.N + BN - 1) / BN;
+    const int n_tiles = column_tiles(p, BN);
     const int total_tiles = n_tiles * int((p.M + BM - 1) / BM);
 
     if (threadIdx.x == 0) {
@@ -231,11 +291,14 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     if (warp == 0) {
         if (lane == 0) {
             umma::prefetch_tmap(&tmA);
-            umma::prefetch_tmap(&tmB);
+            for (int j = 0; j < max(p.members, 1); j++)
+                umma::prefetch_tmap(&tmBs.m[j]);
             int s = 0;
             uint32_t ph = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-                const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+                const int m0 = (tile / n_tiles) * BM;
+                int n0;
+                const CUtensorMap *tmB = &tmBs.m[member_of(p, tile % n_tiles, BN, n0)];
                 for (int kb = 0; kb < p.num_kb; kb++) {
                     if (!wait_parked(&empty[s], ph ^ 1)) {
                         atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
@@ -244,7 +307,7 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     }
                     umma::mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
                     umma::tma_load_2d(sA + s * A_BYTES, &tmA, &full[s], kb * BK, m0);
-                    umma::tma_load_2d(sB + s * B_BYTES, &tmB, &full[s], kb * BK, n0);
+                    umma::tma_load_2d(sB + s * B_BYTES, tmB, &full[s], kb * BK, n0);
                     if (++s == STAGES) {
                         s = 0;
                         ph ^= 1;
@@ -337,7 +400,8 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         uint32_t acc_ph = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int64_t m0 = int64_t(tile / n_tiles) * BM;
-            const int n0 = (tile % n_tiles) * BN;
+            int n0;
+            const ColView cols = columns_of(p, member_of(p, tile % n_tiles, BN, n0));
             if (ready && !wait_parked(&acc_full[b], acc_ph)) {
                 ready = false;
                 if (lane == 0)
@@ -348,7 +412,7 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             const bool row_ok = ready && row < p.M;
             const uint32_t row_term = uint32_t(p.K) * uint32_t(za) * uint32_t(zb) -
                                       ((zb != 0 && p.rowsum && row_ok) ? uint32_t(zb) * uint32_t(p.rowsum[row]) : 0u);
-            epilogue_columns<BN>(p, tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BN), &acc_empty[b], lane, row,
+            epilogue_columns<BN>(p, cols, tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BN), &acc_empty[b], lane, row,
                                  row_ok, n0, row_term, za, run_max, run_neg);
             if (++b == 2) {
                 b = 0;
@@ -524,8 +588,8 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const bool row_ok = ready && row < p.M;
             const uint32_t row_term = uint32_t(p.K) * uint32_t(za) * uint32_t(zb) -
                                       ((zb != 0 && p.rowsum && row_ok) ? uint32_t(zb) * uint32_t(p.rowsum[row]) : 0u);
-            epilogue_columns<BN2>(p, tmem_base + (uint32_t(q * 32) << 16) + uint32_t(half * BN2), acc_empty, lane, row,
-                                  row_ok, n0, row_term, za, run_max, run_neg);
+            epilogue_columns<BN2>(p, columns_of(p, 0), tmem_base + (uint32_t(q * 32) << 16) + uint32_t(half * BN2), acc_empty,
+                                  lane, row, row_ok, n0, row_term, za, run_max, run_neg);
             acc_ph ^= 1;
         }
         if (p.epi.mode == EPI_SCALE)
@@ -565,19 +629,46 @@ mmi_rowsum_kernel(const uint8_t *__restrict__ a, int64_t M, int K, int a_signed,
 }
 
 template <int BN>
-int32_t launch(ovk_ctx *ctx, const CUtensorMap &tmA, const ovk_mmi_weight *w, const TcParams &p)
+int32_t launch(ovk_ctx *ctx, const CUtensorMap &tmA, const ovk_mmi_weight *const *ws, int count, TcParams p)
 {
-    CUtensorMap tmB;
-    if (!ovk_make_tmap_2d(&tmB, w->bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(w->k_pad), uint64_t(w->n_pad),
-                          uint64_t(w->k_pad), BK, BN, CU_TENSOR_MAP_SWIZZLE_128B))
-        return ovk_fail(ctx, OVK_BACKEND, "MatMulInteger: cuTensorMapEncodeTiled failed for the packed weight");
+    TmGroup tmBs = {};
+    int64_t col_tiles = 0;
+    for (int j = 0; j < count; j++) {
+        if (!ovk_make_tmap_2d(&tmBs.m[j], ws[j]->bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(ws[j]->k_pad),
+                              uint64_t(ws[j]->n_pad), uint64_t(ws[j]->k_pad), BK, BN, CU_TENSOR_MAP_SWIZZLE_128B))
+            return ovk_fail(ctx, OVK_BACKEND, "MatMulInteger: cuTensorMapEncodeTiled failed for the packed weight");
+        col_tiles += ceil_div64(ws[j]->n, BN);
+        if (p.members)
+            p.mem[j].tile_end = int(col_tiles);
+    }
     OVK_CUDA(ctx, cudaFuncSetAttribute(mmi_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        int(smem_for<BN>())));
-    const int64_t tiles = ceil_div64(p.N, BN) * ceil_div64(p.M, BM);
+    const int64_t tiles = col_tiles * ceil_div64(p.M, BM);
     const unsigned grid = unsigned(std::min<int64_t>(tiles, ctx->sm_count));
-    OVK_CUDA(ctx, ovk_launch_pdl(mmi_tc_kernel<BN>, dim3(grid), dim3(THREADS), smem_for<BN>(), ctx->stream, tmA, tmB, p));
+    OVK_CUDA(ctx, ovk_launch_pdl(mmi_tc_kernel<BN>, dim3(grid), dim3(THREADS), smem_for<BN>(), ctx->stream, tmA, tmBs, p));
     OVK_LAUNCHED(ctx, BN == 256 ? "mmi_tc_128x256" : (BN == 128 ? "mmi_tc_128x128" : "mmi_tc_128x64"));
     return OVK_OK;
+}
+
+// Largest tile that still gives every SM a CTA; the smallest one otherwise
+// (the reference picks 64x64 blocks under 64 workgroups, shaders/matmul_integer.rs:467-487).
+int32_t launch_by_fill(ovk_ctx *ctx, const CUtensorMap &tmA, const ovk_mmi_weight *const *ws, int count, const TcParams &p)
+{
+    const int64_t mt = ceil_div64(p.M, BM);
+    auto col_tiles = [&](int bn) {
+        int64_t t = 0;
+        for (int j = 0; j < count; j++)
+            t += ceil_div64(ws[j]->n, bn);
+        return t;
+    };
+    int64_t narrowest = ws[0]->n;
+    for (int j = 1; j < count; j++)
+        narrowest = std::min(narrowest, ws[j]->n);
+    if (narrowest >= 256 && mt * col_tiles(256) >= ctx->sm_count)
+        return launch<256>(ctx, tmA, ws, count, p);
+    if (narrowest >= 128 && mt * col_tiles(128) >= ctx->sm_count)
+        return launch<128>(ctx, tmA, ws, count, p);
+    return launch<64>(ctx, tmA, ws, count, p);
 }
 
 // 256 x 256 tiles: chosen for long K (the epilogue is not overlapped) and enough tiles to keep the
@@ -611,6 +702,8 @@ bool wants256(const ovk_ctx *ctx, const ovk_mmi_weight *w, int64_t m)
 }
 
 }  // namespace
+
+bool ovk_mmi_wants_large_tiles(const ovk_ctx *ctx, const ovk_mmi_weight *w, int64_t m) { return wants256(ctx, w, m); }
 
 // The tensor-core tiles need whole 16-byte rows of A for TMA and enough work
 // to fill a tile; everything else stays on the small-shape kernel
@@ -656,14 +749,52 @@ int32_t ovk_mmi_tc_launch(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, 
     if (!ovk_make_tmap_2d(&tmA, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(w->k), uint64_t(m), uint64_t(w->k), BK,
                           BM, CU_TENSOR_MAP_SWIZZLE_128B))
         return ovk_fail(ctx, OVK_BACKEND, "MatMulInteger: cuTensorMapEncodeTiled failed for A");
-    // Largest tile that still gives every SM a CTA; the smallest one otherwise
-    // (the reference picks 64x64 blocks under 64 workgroups, shaders/matmul_integer.rs:467-487).
-    const int64_t mt = ceil_div64(m, BM);
-    if (w->n >= 256 && mt * ceil_div64(w->n, 256) >= ctx->sm_count)
-        return launch<256>(ctx, tmA, w, p);
-    if (w->n >= 128 && mt * ceil_div64(w->n, 128) >= ctx->sm_count)
-        return launch<128>(ctx, tmA, w, p);
-    return launch<64>(ctx, tmA, w, p);
+    return launch_by_fill(ctx, tmA, &w, 1, p);
+}
+
+// Up to four weights over the same A in one launch.  The caller has checked that every member takes
+// the tensor-core kernel and shares K and the signedness of B; epis[j] / outs[j] are member j's.
+int32_t ovk_mmi_tc_launch_group(ovk_ctx *ctx, int count, const ovk_mmi_weight *const *ws, const void *a, int32_t a_signed,
+                                int64_t m, const void *a_zp, const void *b_zp, const EpiParams *epis, void *const *outs)
+{
+    TcParams p = {};
+    p.M = m;
+    p.N = int(ws[0]->n);
+    p.K = int(ws[0]->k);
+    p.num_kb = int(ceil_div64(ws[0]->k, BK));
+    p.a_zp = a_zp;
+    p.b_zp = b_zp;
+    p.a_signed = a_signed ? 1 : 0;
+    p.b_signed = ws[0]->b_signed;
+    p.epi = epis[0];
+    p.status = ctx->dev_status;
+    p.members = count;
+    p.vec_ok = 1;
+    for (int j = 0; j < count; j++) {
+        p.mem[j].colsum = ws[j]->colsum;
+        p.mem[j].scale = epis[j].scale;
+        p.mem[j].product = epis[j].product;
+        p.mem[j].fbias = epis[j].fbias;
+        p.mem[j].out = outs[j];
+        p.mem[j].N = int(ws[j]->n);
+        p.vec_ok = p.vec_ok && (ws[j]->n % 4) == 0 && aligned_to(outs[j], 16);
+    }
+    if (b_zp) {
+        void *ws_rows = nullptr;
+        int32_t rc = ovk_scratch(ctx, size_t(m) * sizeof(int32_t), &ws_rows);
+        if (rc != OVK_OK)
+            return rc;
+        p.rowsum = static_cast<int32_t *>(ws_rows);
+        OVK_CUDA(ctx, ovk_launch_pdl(mmi_rowsum_kernel, dim3(unsigned(ceil_div64(m * 32, 256))), dim3(256), 0, ctx->stream,
+                                     static_cast<const uint8_t *>(a), m, p.K, p.a_signed, b_zp, p.b_signed,
+                                     static_cast<int32_t *>(ws_rows)));
+        OVK_LAUNCHED(ctx, "mmi_rowsum");
+    }
+    CUtensorMap tmA;
+    if (!ovk_make_tmap_2d(&tmA, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(ws[0]->k), uint64_t(m), uint64_t(ws[0]->k), BK,
+                          BM, CU_TENSOR_MAP_SWIZZLE_128B))
+        return ovk_fail(ctx, OVK_BACKEND, "MatMulInteger: cuTensorMapEncodeTiled failed for A");
+    return launch_by_fill(ctx, tmA, ws, count, p);
 }
 
 // ---------------------------------------------------------------------------
@@ -742,10 +873,5 @@ extern "C" int32_t ovk_matmul_integer_static_scratch(ovk_ctx *ctx, const ovk_mmi
     if (!ovk_make_tmap_2d(&tmA, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(w->k), uint64_t(m), uint64_t(w->k), BK,
                           BM, CU_TENSOR_MAP_SWIZZLE_128B))
         return ovk_fail(ctx, OVK_BACKEND, "MatMulInteger (static scratch): cuTensorMapEncodeTiled failed for A");
-    const int64_t mt = ceil_div64(m, BM);
-    if (w->n >= 256 && mt * ceil_div64(w->n, 256) >= ctx->sm_count)
-        return launch<256>(ctx, tmA, w, p);
-    if (w->n >= 128 && mt * ceil_div64(w->n, 128) >= ctx->sm_count)
-        return launch<128>(ctx, tmA, w, p);
-    return launch<64>(ctx, tmA, w, p);
+    return launch_by_fill(ctx, tmA, &w, 1, p);
 }

@@ -84,6 +84,9 @@ SIGNATURES = {
     "ovk_matmul_integer_static_scratch": (_I32, [_P, _P, _P, _I32, _I64, _P, _P, _P]),
     "ovk_matmul_integer_scale_bias": (_I32, [_P, _P, _P, _I32, _I64, _P, _P, _P, _I32, _P, _I32, _P,
                                              _I32, _U32, _P, _P]),
+    "ovk_matmul_integer_group": (_I32, [_P, _I32, C.POINTER(_P), _P, _I32, _I64, _P, _P, C.POINTER(_P)]),
+    "ovk_matmul_integer_scale_bias_group": (_I32, [_P, _I32, C.POINTER(_P), _P, _I32, _I64, _P, _P, C.POINTER(_P), _I32,
+                                                   _P, _I32, C.POINTER(_P), _I32, _U32, C.POINTER(_P)]),
     "ovk_qlinear_matmul": (_I32, [_P, _P, _P, _I32, _I64, _P, _P, _P, _I64, _I32, _I32, _P]),
     "ovk_qconv_prepack": (_I32, [_P, _P, _I32, _I64, _I64, _I64, _I64, _I64, C.POINTER(_P)]),
     "ovk_qconv_weight_destroy": (None, [_P, _P]),
@@ -341,6 +344,30 @@ class Context:
             _ptr(scale), step(scale), _ptr(product), step(product), _ptr(bias), step(bias), flags,
             _ptr(range_slot), _ptr(out)))
         return out
+
+    def matmul_integer_group(self, ws, a, a_zp=None, b_zp=None):
+        """Several weights over the same A (q | k | v): one launch where the tensor-core tiles apply."""
+        import torch
+        m = a.numel() // max(ws[0].k, 1)
+        outs = [torch.empty(tuple(a.shape[:-1]) + (w.n,), dtype=torch.int32, device=a.device) for w in ws]
+        wp, op = (_P * len(ws))(*[w.h for w in ws]), (_P * len(ws))(*[_ptr(o) for o in outs])
+        self.check(lib().ovk_matmul_integer_group(self.h, len(ws), wp, _ptr(a), int(a.dtype == torch.int8), m, _ptr(a_zp),
+                                                  _ptr(b_zp), op))
+        return outs
+
+    def matmul_integer_scale_bias_group(self, ws, a, a_zp, b_zp, scales, biases, product=None, relu=False):
+        """The fused Cast, Mul, Add [, Relu] epilogue for several weights over the same A; scales[j] / biases[j]
+        are member j's, all of one value or all of one per column; `product` is one value."""
+        import torch
+        m = a.numel() // max(ws[0].k, 1)
+        outs = [torch.empty(tuple(a.shape[:-1]) + (w.n,), dtype=torch.float32, device=a.device) for w in ws]
+        n = len(ws)
+        step = lambda ts: 0 if all(t.numel() == 1 for t in ts) else (1 if all(t.numel() == w.n for t, w in zip(ts, ws)) else 2)
+        arr = lambda ts: (_P * n)(*[_ptr(t) for t in ts])
+        self.check(lib().ovk_matmul_integer_scale_bias_group(
+            self.h, n, (_P * n)(*[w.h for w in ws]), _ptr(a), int(a.dtype == torch.int8), m, _ptr(a_zp), _ptr(b_zp),
+            arr(scales), step(scales), _ptr(product), 0, arr(biases), step(biases), EPILOGUE_RELU if relu else 0, arr(outs)))
+        return outs
 
     def qlinear_matmul(self, w: "MmiWeight", a, a_zp, b_zp, ratio, y_zp, y_signed=False):
         import torch

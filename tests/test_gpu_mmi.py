@@ -206,3 +206,29 @@ def test_short_k_many_tiles_two_issuers(m, k, n):
         assert ctx().last_kernel.startswith("mmi_tc"), ctx().last_kernel
         ctx().flush()
         assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("m,k,ns,b_zp", [(1000, 1024, (1024, 1024, 1024), None), (300, 256, (130, 64, 200), -7),
+                                          (40, 96, (48, 330), None), (7, 12, (5, 9), 3)])
+def test_group_of_weights_over_the_same_a(m, k, ns, b_zp):
+    """q | k | v over one quantised tensor: one launch where the tensor-core tiles apply (ragged member widths
+    included), one call per member otherwise; int32 results and the fused f32 epilogue are those of separate calls."""
+    a = cases.lcg_bytes_fast(m * k, 31).reshape(m, k)
+    bs = [cases.lcg_bytes_fast(k * n, 40 + j).reshape(k, n).view(np.int8) for j, n in enumerate(ns)]
+    ws = [ctx().mmi_prepack(dev(b)) for b in bs]
+    azp = zp_dev(131, False)
+    bzp = None if b_zp is None else zp_dev(b_zp, True)
+    before = ctx().launches
+    outs = ctx().matmul_integer_group(ws, dev(a), azp, bzp)
+    launched = ctx().launches - before
+    if m >= 16 and min(ns) >= 16:
+        assert launched == (1 if b_zp is None else 2) and ctx().last_kernel.startswith("mmi_tc")
+    for b, o in zip(bs, outs):
+        assert np.array_equal(host(o), orc.matmul_integer(a, b, 131, b_zp or 0))
+    scales = [dev(np.random.default_rng(j).uniform(1e-3, 1e-2, n).astype(np.float32)) for j, n in enumerate(ns)]
+    biases = [dev(np.random.default_rng(9 + j).standard_normal(n).astype(np.float32)) for j, n in enumerate(ns)]
+    prod = dev(np.array([0.0123], dtype=np.float32))
+    fused = ctx().matmul_integer_scale_bias_group(ws, dev(a), azp, bzp, scales, biases, product=prod, relu=True)
+    for w, s, bi, o in zip(ws, scales, biases, fused):
+        alone = ctx().matmul_integer_scale_bias(w, dev(a), azp, bzp, s, bi, product=prod, relu=True)
+        assert np.array_equal(host(o).view(np.uint32), host(alone).view(np.uint32))
