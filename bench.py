@@ -515,7 +515,7 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
     # The whole step is one CUDA graph.  A second graph of the same step has the
     # lm_head launch between two event-record nodes: it is replayed after the
     # timed region to read that launch's duration from inside a step.
-    graph, probe, replay = None, None, "eager launches"
+    graph, probe, layers_only, replay = None, None, None, "eager launches"
     g0 = torch.cuda.Event(enable_timing=True, external=True)
     g1 = torch.cuda.Event(enable_timing=True, external=True)
     if not args.no_graph:
@@ -530,11 +530,17 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
                 g0.record(stream)
                 ctx.matmul_nbits(lm, acts[HIDDEN], out=outs[VOCAB])
                 g1.record(stream)
+            # the step without its last launch: the difference of the two replays is what the lm_head costs
+            # inside a step with nothing fencing it (the event-record nodes above forbid the overlap of its
+            # weight streaming with the previous launch's tail, which the step really has)
+            layers_only = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(layers_only, stream=stream):
+                layers_eager()
             replay = "one CUDA graph replay per step (%s)" % {
                 "grouped": "q|k|v and gate|up as one launch each", "branches": "q|k|v and gate|up on parallel branches",
                 "serial": "one launch per GEMV in one chain"}[args.launch]
         except Exception as e:  # capture refused: fall back to eager launches, say so
-            graph, replay = None, "eager launches (graph capture failed: %s)" % str(e)[:80]
+            graph, layers_only, replay = None, None, "eager launches (graph capture failed: %s)" % str(e)[:80]
             torch.cuda.synchronize()
 
     lm_samples = []
@@ -609,6 +615,20 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
         lm_in_step_ms = statistics.median(lm_times)
     else:
         lm_in_step_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in lm_samples)
+    # (a') the step with and without the lm_head launch, unfenced
+    lm_marginal_ms = None
+    if graph is not None and layers_only is not None:
+        def replay_ms(g, n=20):
+            g.replay()
+            torch.cuda.synchronize()
+            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            r0.record()
+            for _ in range(n):
+                g.replay()
+            r1.record()
+            torch.cuda.synchronize()
+            return r0.elapsed_time(r1) / n
+        lm_marginal_ms = replay_ms(graph) - replay_ms(layers_only)
     # (b) back to back: a graph of launches over distinct copies of the weight (3 x 175 MB > L2),
     #     one event pair around the replays; consecutive launches overlap their ramps
     lm_copies = [lm] + [make_weight(torch, ctx, LM_HEAD[1], LM_HEAD[2], BLOCK, gen) for _ in range(2)]
@@ -678,7 +698,7 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
     peaks, peak_kind = measured_peaks()
     extra = None
     if not args.no_extra:
-        del ops, lm, graph, probe
+        del ops, lm, graph, probe, layers_only
         torch.cuda.empty_cache()
         extra = extra_workloads(torch, dist, ctx, world, rank, gen, peaks)
 
@@ -702,6 +722,9 @@ def _run_gpu_on_stream(args, torch, dist, ovk_b200, world, rank, local, stream):
                          "timing": lm_how + ", one CUDA event pair",
                          "ms_per_launch_inside_step": lm_in_step_ms,
                          "frac_inside_step": lm_bytes / (lm_in_step_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                         "ms_marginal_inside_step": lm_marginal_ms,
+                         "frac_marginal_inside_step": (lm_bytes / (lm_marginal_ms * 1e-3) / 1e9 / peaks["hbm_gbs"])
+                         if lm_marginal_ms and lm_marginal_ms > 0 else None,
                          "whole_step_frac": world * step_bytes * args.steps / (ms_total * 1e-3) / 1e9 / (world * peaks["hbm_gbs"]),
                          "frac_of_nominal_8tbs": achieved / 8000.0, "traffic": traffic,
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on "

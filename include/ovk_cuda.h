@@ -286,6 +286,21 @@ OVK_API int32_t ovk_matmul_integer_scale_bias(ovk_ctx *ctx, const ovk_mmi_weight
                                               int32_t product_step, const float *bias,
                                               int32_t bias_step, uint32_t flags, uint32_t *range,
                                               float *out);
+/* interp::integer_scale_bias_unfused (interp.rs:2630-2665): what the reference
+ * runs when a scale, product or bias broadcasts over rows and the fused node
+ * does not apply - Cast, Mul, Add [, Relu] over the int32 result of
+ * ovk_matmul_integer / ovk_conv_integer, here as one pass:
+ *   out[r][c] = fl(fl(float(acc[r][c]) * s) + bias),  s = scale or fl(scale * product),
+ * every operand addressed by (row stride, column stride) in elements: {0, 0} one
+ * value, {0, 1} one per column, {1, 0} one per row, {cols, 1} a full matrix.
+ * Same bits as the separate nodes.  No range is folded (flags: OVK_EPILOGUE_RELU only). */
+OVK_API int32_t ovk_integer_scale_bias_unfused(ovk_ctx *ctx, const int32_t *acc, int64_t rows,
+                                               int64_t cols, const float *scale,
+                                               int64_t scale_row_stride, int64_t scale_col_stride,
+                                               const float *product, int64_t product_row_stride,
+                                               int64_t product_col_stride, const float *bias,
+                                               int64_t bias_row_stride, int64_t bias_col_stride,
+                                               uint32_t flags, float *out);
 /* The same products for up to four weights that read the SAME A - the q, k and
  * v projections over one DynamicQuantizeLinear result: out_j = A x B_j with the
  * members' own column constants.  One launch when every member takes the

@@ -121,6 +121,28 @@ mmi_small_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ bt,
         epi_fold_range(epi, run_max, run_neg);
 }
 
+// Cast, Mul, Add [, Relu] over an int32 matrix with operands that broadcast in any of the two
+// directions: out[r][c] = fl(fl(float(acc[r][c]) * s) + bias), s = scale or fl(scale * product), each
+// operand addressed by (row stride, column stride) in elements.  The nodes the reference runs when a
+// scale or bias broadcasts over rows and the fused store does not apply (interp.rs:2630-2665).
+__global__ void __launch_bounds__(256)
+scale_bias_broadcast_kernel(const int32_t *__restrict__ acc, int64_t rows, int64_t cols, const float *__restrict__ scale,
+                            int64_t srs, int64_t scs, const float *__restrict__ product, int64_t prs, int64_t pcs,
+                            const float *__restrict__ bias, int64_t brs, int64_t bcs, int relu, float *__restrict__ out)
+{
+    OVK_PDL_LAUNCH_DEPENDENTS();
+    OVK_PDL_WAIT();
+    const int64_t total = rows * cols;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t r = i / cols, c = i - r * cols;
+        float s = scale[r * srs + c * scs];
+        if (product)
+            s = __fmul_rn(s, product[r * prs + c * pcs]);
+        const float z = __fadd_rn(__fmul_rn(float(acc[i]), s), bias[r * brs + c * bcs]);
+        out[i] = relu ? fmaxf(z, 0.0f) : z;
+    }
+}
+
 int32_t run_mmi(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int32_t a_signed, int64_t m,
                 const void *a_zp, const void *b_zp, const EpiParams &epi, void *out,
                 const char *op)
@@ -309,6 +331,30 @@ int32_t ovk_matmul_integer_scale_bias_group(ovk_ctx *ctx, int32_t count, const o
     }
     return run_mmi_group(ctx, count, weights, a, a_signed, m, a_zp, b_zp, epis, reinterpret_cast<void *const *>(outs),
                          "MatMulIntegerScaleBias");
+}
+
+int32_t ovk_integer_scale_bias_unfused(ovk_ctx *ctx, const int32_t *acc, int64_t rows, int64_t cols, const float *scale,
+                                       int64_t scale_row_stride, int64_t scale_col_stride, const float *product,
+                                       int64_t product_row_stride, int64_t product_col_stride, const float *bias,
+                                       int64_t bias_row_stride, int64_t bias_col_stride, uint32_t flags, float *out)
+{
+    if (!ctx)
+        return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "ovk_integer_scale_bias_unfused: null context");
+    OVK_REQUIRE(ctx, rows >= 0 && cols >= 0, "Cast/Mul/Add: a negative shape");
+    OVK_REFUSE(ctx, flags & OVK_EPILOGUE_RANGE, "Cast/Mul/Add: the unfused nodes fold no range (the quantization that follows makes its own pass)");
+    if (rows == 0 || cols == 0)
+        return OVK_OK;
+    OVK_REQUIRE(ctx, acc && scale && bias && out, "Cast/Mul/Add: a tensor is null");
+    OVK_REQUIRE(ctx, scale_row_stride >= 0 && scale_col_stride >= 0 && bias_row_stride >= 0 && bias_col_stride >= 0 &&
+                         product_row_stride >= 0 && product_col_stride >= 0,
+                "Cast/Mul/Add: a negative stride");
+    OVK_CUDA(ctx, cudaSetDevice(ctx->device));
+    const unsigned blocks = unsigned(std::min<int64_t>(ceil_div64(rows * cols, 256), int64_t(ctx->sm_count) * 8));
+    OVK_CUDA(ctx, ovk_launch_pdl(scale_bias_broadcast_kernel, dim3(blocks), dim3(256), 0, ctx->stream, acc, rows, cols, scale,
+                                 scale_row_stride, scale_col_stride, product, product_row_stride, product_col_stride, bias,
+                                 bias_row_stride, bias_col_stride, int(flags & OVK_EPILOGUE_RELU), out));
+    OVK_LAUNCHED(ctx, "scale_bias_broadcast");
+    return OVK_OK;
 }
 
 int32_t ovk_qlinear_matmul(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int32_t a_signed,

@@ -111,6 +111,36 @@ int column_step(const std::vector<int64_t> &shape, int64_t n, size_t rank)
     return shape.back() == n ? 1 : -1;
 }
 
+// How an operand of shape `shape` broadcasts over an output [.., rows, n] whose leading dimensions are
+// folded into `rows`: (row stride, column stride) in elements, or false when it does neither of one
+// value / one per column / one per row / a full matrix.
+bool broadcast_strides(const std::vector<int64_t> &shape, const std::vector<int64_t> &out_shape, int64_t *rs, int64_t *cs)
+{
+    if (shape.size() > out_shape.size())
+        return false;
+    const int64_t n = out_shape.back();
+    const int64_t last = shape.empty() ? 1 : shape.back();
+    if (last != 1 && last != n)
+        return false;
+    *cs = last == n && n != 1 ? 1 : 0;
+    bool all_one = true, all_equal = true;
+    const size_t lead = out_shape.size() - 1, have = shape.empty() ? 0 : shape.size() - 1;
+    for (size_t i = 0; i < lead; i++) {  // leading dimensions, right-aligned
+        const int64_t od = out_shape[lead - 1 - i];
+        const int64_t sd = i < have ? shape[have - 1 - i] : 1;
+        all_one = all_one && sd == 1;
+        all_equal = all_equal && sd == od;
+    }
+    if (all_one) {
+        *rs = 0;
+        return true;
+    }
+    if (!all_equal)
+        return false;
+    *rs = *cs ? n : 1;
+    return true;
+}
+
 // ------------------------------------------------------------------ MatMulNBits
 // interp::matmul_nbits (interp.rs:6429-6561)
 Result matmul_nbits(Env &env, const NodeIr &node)
@@ -317,10 +347,41 @@ Result matmul_integer_scale_bias(Env &env, const NodeIr &node)
     const size_t rank = a->shape.size();
     const int ss = column_step(scale->shape, n, rank), bs = column_step(bias->shape, n, rank);
     const int ps = prod ? column_step(prod->shape, n, rank) : 0;
-    if (ss < 0 || bs < 0 || ps < 0 || scale->dtype != OVK_FLOAT || bias->dtype != OVK_FLOAT || a->dtype != OVK_UINT8)
-        return fail(OVK_UNSUPPORTED,
-                    "MatMulIntegerScaleBias: not fused (a scale, product or bias that broadcasts over rows, or a "
-                    "signed A): the reference runs MatMulInteger, Cast, Mul, Add as separate nodes here");
+    if (scale->dtype != OVK_FLOAT || bias->dtype != OVK_FLOAT || (prod && prod->dtype != OVK_FLOAT))
+        return fail(OVK_UNSUPPORTED, "MatMulIntegerScaleBias: scale, product and bias must be float32");
+    if (ss < 0 || bs < 0 || ps < 0 || a->dtype != OVK_UINT8) {
+        // interp::integer_scale_bias_unfused (interp.rs:2630-2665): a scale, product or bias that broadcasts over
+        // rows (or a signed A) is not fused; MatMulInteger runs, then Cast, Mul, Add [, Relu] in one pass with
+        // general broadcasting.  No range is folded: the quantization that follows makes its own pass.
+        std::vector<int64_t> out_shape(a->shape.begin(), a->shape.end() - 1);
+        out_shape.push_back(n);
+        int64_t srs, scs, brs, bcs, prs = 0, pcs = 0;
+        if (!broadcast_strides(scale->shape, out_shape, &srs, &scs) || !broadcast_strides(bias->shape, out_shape, &brs, &bcs) ||
+            (prod && !broadcast_strides(prod->shape, out_shape, &prs, &pcs)))
+            return fail(OVK_UNSUPPORTED, "MatMulIntegerScaleBias: a scale, product or bias that broadcasts neither over "
+                                         "rows nor over columns");
+        const void *a_zp, *b_zp;
+        OVKH_TRY(scalar_zp_dev(env, node, 2, &a_zp));
+        OVKH_TRY(scalar_zp_dev(env, node, 3, &b_zp));
+        const std::string acc_name = node.outputs[0] + "/acc";
+        Tensor *acc = nullptr, *out = nullptr;
+        OVKH_TRY(env.alloc(acc_name, OVK_INT32, out_shape, &acc));
+        OVKH_TRY(env.alloc(node.outputs[0], OVK_FLOAT, out_shape, &out));
+        acc = const_cast<Tensor *>(env.find(acc_name));
+        a = env.find(node.inputs[0]);
+        scale = env.find(node.inputs[4]);
+        bias = env.find(node.inputs[5]);
+        prod = node.present(6) ? env.find(node.inputs[6]) : nullptr;
+        OVKH_TRY(from_abi(env.context(), ovk_matmul_integer(env.context(), w, a->dev, a->dtype == OVK_INT8, m, a_zp, b_zp,
+                                                            static_cast<int32_t *>(acc->dev))));
+        return from_abi(env.context(),
+                        ovk_integer_scale_bias_unfused(env.context(), static_cast<const int32_t *>(acc->dev), m, n,
+                                                       static_cast<const float *>(scale->dev), srs, scs,
+                                                       prod ? static_cast<const float *>(prod->dev) : nullptr, prs, pcs,
+                                                       static_cast<const float *>(bias->dev), brs, bcs,
+                                                       node.int_attr("relu", 0) == 1 ? OVK_EPILOGUE_RELU : 0u,
+                                                       static_cast<float *>(out->dev)));
+    }
     const void *a_zp, *b_zp;
     OVKH_TRY(scalar_zp_dev(env, node, 2, &a_zp));
     OVKH_TRY(scalar_zp_dev(env, node, 3, &b_zp));

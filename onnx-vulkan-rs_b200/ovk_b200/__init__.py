@@ -84,6 +84,7 @@ SIGNATURES = {
     "ovk_matmul_integer_static_scratch": (_I32, [_P, _P, _P, _I32, _I64, _P, _P, _P]),
     "ovk_matmul_integer_scale_bias": (_I32, [_P, _P, _P, _I32, _I64, _P, _P, _P, _I32, _P, _I32, _P,
                                              _I32, _U32, _P, _P]),
+    "ovk_integer_scale_bias_unfused": (_I32, [_P, _P, _I64, _I64, _P, _I64, _I64, _P, _I64, _I64, _P, _I64, _I64, _U32, _P]),
     "ovk_matmul_integer_group": (_I32, [_P, _I32, C.POINTER(_P), _P, _I32, _I64, _P, _P, C.POINTER(_P)]),
     "ovk_matmul_integer_scale_bias_group": (_I32, [_P, _I32, C.POINTER(_P), _P, _I32, _I64, _P, _P, C.POINTER(_P), _I32,
                                                    _P, _I32, C.POINTER(_P), _I32, _U32, C.POINTER(_P)]),

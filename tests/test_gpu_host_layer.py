@@ -105,11 +105,57 @@ def test_matmul_integer_scale_bias(hl, env, relu, col_scale):
     assert np.array_equal(env.host("y").view(np.uint32), want.view(np.uint32))
 
 
-def test_scale_bias_row_broadcast_is_left_to_the_unfused_nodes(hl, env):
-    """interp.rs:2600-2610: a scale that broadcasts over rows has no column step."""
+# (A shape, N, W int8?, scale kind, relu): the layers of tests/matmul_integer_epilogue.rs that the reference does NOT
+# fuse (:423, :471, :517, :596, :722) - a scale over rows - which run as MatMulInteger, Cast, Mul, Add [, Relu]
+UNFUSED_LAYERS = [((64, 32), 32, False, "rows", False), ((40, 3), 24, False, "rows", False),
+                  ((64, 32), 32, False, "rows", True), ((48, 36), 40, False, "rows_x_cols", True),
+                  ((2, 5, 16), 12, True, "rows3", False)]
+
+
+@pytest.mark.parametrize("a_shape,n,w_int8,kind,relu", UNFUSED_LAYERS)
+def test_scale_over_rows_runs_the_unfused_nodes(hl, env, a_shape, n, w_int8, kind, relu):
+    """interp.rs:2600-2665: a scale that broadcasts over rows has no column step, so the fused store does not
+    apply and the node runs MatMulInteger then Cast, Mul, Add [, Relu] - same bits as the separate nodes."""
+    k = a_shape[-1]
+    rows = int(np.prod(a_shape[:-1]))
+    a = cases.lcg_bytes_fast(rows * k, 3).reshape(a_shape)
+    b = cases.lcg_bytes_fast(k * n, 2).reshape(k, n)
+    b = b.view(np.int8) if w_int8 else b
+    rng = np.random.default_rng(rows + n)
+    bias = rng.uniform(-0.5, 0.5, n).astype(np.float32)
+    inputs = ["a", "b", "az", "bz", "s", "bias"]
+    if kind == "rows":
+        scale = rng.uniform(1e-3, 2e-2, (rows, 1)).astype(np.float32)
+        s_full = np.broadcast_to(scale, (rows, n))
+    elif kind == "rows3":
+        scale = rng.uniform(1e-3, 2e-2, a_shape[:-1] + (1,)).astype(np.float32)
+        s_full = np.broadcast_to(scale.reshape(rows, 1), (rows, n))
+    else:  # a per-row scale times a per-column second factor, multiplied first (:722)
+        scale = rng.uniform(1e-3, 2e-2, (rows, 1)).astype(np.float32)
+        prod = rng.uniform(0.5, 2.0, n).astype(np.float32)
+        env.set("p", prod, initializer=True)
+        inputs.append("p")
+        s_full = (np.broadcast_to(scale, (rows, n)) * prod[None, :]).astype(np.float32)
+    env.set("a", a)
+    env.set("b", b, initializer=True)
+    env.set("az", np.array([131], dtype=np.uint8))
+    env.set("bz", np.array([-7], dtype=np.int8) if w_int8 else np.array([121], dtype=np.uint8))
+    env.set("s", scale, initializer=True)
+    env.set("bias", bias, initializer=True)
+    env.execute(hl.Node("MatMulIntegerScaleBias", inputs, ["y"], relu=int(relu)))
+    assert env.last_kernel == "scale_bias_broadcast"
+    acc = orc.matmul_integer(a.reshape(rows, k), b, 131, -7 if w_int8 else 121)
+    want = (acc.astype(np.float32) * s_full).astype(np.float32) + bias[None, :]
+    want = np.maximum(want, np.float32(0)) if relu else want
+    got = env.host("y")
+    assert got.shape == tuple(a_shape[:-1]) + (n,)
+    assert np.array_equal(got.reshape(rows, n).view(np.uint32), want.astype(np.float32).view(np.uint32))
+
+
+def test_a_scale_that_broadcasts_neither_way_is_refused(hl, env):
     env.set("a", np.zeros((4, 8), dtype=np.uint8))
     env.set("b", np.zeros((8, 6), dtype=np.int8), initializer=True)
-    env.set("s", np.ones((4, 1), dtype=np.float32), initializer=True)
+    env.set("s", np.ones((2, 1), dtype=np.float32), initializer=True)  # 2 rows against 4
     env.set("bias", np.zeros(6, dtype=np.float32), initializer=True)
     with pytest.raises(hl.OvkError) as err:
         env.execute(hl.Node("MatMulIntegerScaleBias", ["a", "b", "", "", "s", "bias"], ["y"]))
