@@ -188,6 +188,15 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
     # product followed by an NCCL all-gather - next to the whole product on rank 0's GPU alone.
     m = 4096
     pg = shard.PeerGroup(ctx, rank, world) if world > 1 else None
+    # a second context of this rank for the multicast variant (its own flag blocks and call numbers)
+    sg, ctx_mc, mc_error = None, None, None
+    if world > 1:
+        try:
+            import ovk_b200
+            ctx_mc = ovk_b200.Context(torch.cuda.current_device())
+            sg = shard.SymmetricGroup(ctx_mc, rank, world)
+        except Exception as e:
+            sg, mc_error = None, "symmetric memory: " + str(e)[:160]
     partitioned = {}
     for name, k, n in (("gate_up", 3584, 18944), ("down", 18944, 3584), ("lm_head", 3584, 152064)):
         if name == "lm_head" and world not in (1, 8):
@@ -213,6 +222,29 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
                                    [shard.column_shard(n, world, r).stop - 1 for r in range(world)]])
             ok = check_against_port(torch, y_full, a, b, scales, zp, k, 128, rows, cols) if rank == 0 else True
 
+            # the exchange alone (the column block already in place): what the links take without any product
+            ms_x = timed(torch, dist, world, lambda: ctx.allgather_cols(None, m, sh.count, sh.start, n, y_ptrs), 5)
+            # the same two through a multicast mapping of the ranks' matrices, where the box offers one: a tile
+            # leaves this GPU's links once and the NVSwitch delivers it to every rank
+            ms_fm = ms_xm = None
+            ok_m = None
+            if sg is not None:
+                try:
+                    ym_ptrs, ym_mc = sg.symmetric(m * n * 2)
+                except Exception as e:  # no symmetric memory on this box: say so, keep the peer-store figures
+                    ym_mc, mc_error = 0, str(e)[:120]
+                if not ym_mc:
+                    mc_error = mc_error or "no multicast mapping on this box"
+                if ym_mc:
+                    ym_full = shard.DeviceBlock(ym_ptrs[rank], (m, n), "<f2").tensor("cuda")
+                    ms_fm = timed(torch, dist, world,
+                                  lambda: ctx_mc.matmul_nbits_nsplit(w, a, sh.start, n, ym_ptrs, multicast=ym_mc), 5)
+                    ctx_mc.flush()
+                    ok_m = check_against_port(torch, ym_full, a, b, scales, zp, k, 128, rows, cols) if rank == 0 else True
+                    ms_xm = timed(torch, dist, world,
+                                  lambda: ctx_mc.allgather_cols(None, m, sh.count, sh.start, n, ym_ptrs, multicast=ym_mc), 5)
+                    del ym_full
+
             def nccl_step():
                 ctx.matmul_nbits(w, a, out=y)
                 shard.all_gather_columns(y, n, world)
@@ -226,12 +258,16 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
                 del w1, y1
             dist.broadcast(ms_1, 0)
             ms_1 = float(ms_1.item())
+            recv = (world - 1) / world * m * n * 2
             entry.update({"ms_with_exchange_in_kernel": ms_f, "tflops_with_exchange": 2.0 * m * k * n / (ms_f * 1e-3) / 1e12,
-                          "ms_with_nccl_all_gather": ms_n, "ms_one_gpu_same_run": ms_1,
+                          "ms_with_nccl_all_gather": ms_n, "ms_exchange_alone": ms_x, "ms_one_gpu_same_run": ms_1,
                           "parallelism": "N-split x%d; the kernel's store warp writes each tile into every rank's Y "
                                          "(peer stores over NVLink), one flag per peer ends the step" % world})
-            recv = (world - 1) / world * m * n * 2
             partitioned[name] = {"ms_one_gpu": ms_1, "ms_compute": ms_c, "ms_e2e": ms_f, "ms_e2e_nccl": ms_n,
+                                 "ms_exchange_alone": ms_x, "exchange_alone_gbs_per_gpu": recv / (ms_x * 1e-3) / 1e9,
+                                 "ms_e2e_multicast": ms_fm, "ms_exchange_alone_multicast": ms_xm,
+                                 "speedup_e2e_multicast": (ms_1 / ms_fm) if ms_fm else None,
+                                 "parity_checked_multicast": ok_m, "multicast_unavailable": mc_error,
                                  "speedup_compute": ms_1 / ms_c, "speedup_e2e": ms_1 / ms_f,
                                  "speedup_e2e_nccl": (ms_1 / ms_n) if ms_n else None,
                                  "received_bytes_per_gpu": recv, "received_gbs_per_gpu": recv / (ms_f * 1e-3) / 1e9,
@@ -241,6 +277,8 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
         out["int4_prefill_qwen7b_" + name] = entry
         del w, a, y, b, scales, zp, bs_, ss_, zs_
         torch.cuda.empty_cache()
+    if sg is not None:
+        sg.close()
     if pg is not None:
         torch.cuda.synchronize()
         pg.close()

@@ -186,6 +186,18 @@ OVK_API int32_t ovk_comm_barrier(ovk_ctx *ctx);
 OVK_API int32_t ovk_allgather_cols(ovk_ctx *ctx, const void *y_shard, int32_t dtype, int64_t m,
                                    int64_t n_shard, int64_t col0, int64_t n_total,
                                    void *const *y_peers);
+/* The same exchange with one store per 16 bytes instead of one per rank:
+ * y_multicast is a multicast mapping of the ranks' matrices (NVLink SHARP: an
+ * address the NVSwitch resolves to the same offset of every rank's buffer, set
+ * up by the host with the driver's multicast objects, or taken from a runtime
+ * that has - torch's symmetric memory gives one).  A block leaves this GPU's
+ * links once and the switch delivers it to every rank, this one included.
+ * y_peers is still needed (the flags and the ragged-edge stores use plain peer
+ * mappings); NULL for y_multicast is ovk_allgather_cols. */
+OVK_API int32_t ovk_allgather_cols_multicast(ovk_ctx *ctx, const void *y_shard, int32_t dtype,
+                                             int64_t m, int64_t n_shard, int64_t col0,
+                                             int64_t n_total, void *const *y_peers,
+                                             void *y_multicast);
 /* MatMulNBits split over weight columns: w holds columns [col0, col0 + N_w) of
  * the operator's weight (a plain slice of its three tensors), A is the whole
  * [m, K] activation matrix on every rank, and the call leaves the whole
@@ -198,6 +210,14 @@ OVK_API int32_t ovk_allgather_cols(ovk_ctx *ctx, const void *y_shard, int32_t dt
 OVK_API int32_t ovk_matmul_nbits_nsplit(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
                                         int32_t a_dtype, int64_t m, int64_t col0, int64_t n_total,
                                         void *const *y_peers, int32_t y_dtype);
+/* The same with the tiles stored through a multicast mapping of the ranks'
+ * matrices (see ovk_allgather_cols_multicast): one store per 16 bytes from the
+ * kernel's store warp, whatever the number of ranks. */
+OVK_API int32_t ovk_matmul_nbits_nsplit_multicast(ovk_ctx *ctx, const ovk_nbits_weight *w,
+                                                  const void *a, int32_t a_dtype, int64_t m,
+                                                  int64_t col0, int64_t n_total,
+                                                  void *const *y_peers, void *y_multicast,
+                                                  int32_t y_dtype);
 
 /* ------------------------------------------------- DynamicQuantizeLinear
  * interp::dynamic_quantize / quantize_on_device (interp.rs:1945-2085) with the

@@ -35,6 +35,7 @@ struct GatherParams {
     int elem_bytes;
     int vec16;               // every address involved is a multiple of 16
     int skip_self;           // the block already sits in this rank's full matrix
+    uint8_t *mc;             // multicast mapping of every rank's full matrix, or null
     int *status;
 };
 
@@ -63,10 +64,16 @@ allgather_cols_kernel(OvkCommView c, GatherParams p)
                 const int64_t r = i / per_row, ch = i - r * per_row;
                 const uint4 v = *reinterpret_cast<const uint4 *>(p.src + r * p.src_pitch + (ch << 4));
                 const size_t off = size_t(r) * p.dst_pitch + p.dst_col + (size_t(ch) << 4);
-#pragma unroll
-                for (int d = 0; d < OVK_MAX_RANKS; d++)
-                    if (d < c.world && !(p.skip_self && d == c.rank))
+                if (p.mc) {  // one store, delivered to every rank by the switch
+                    comm::st_multicast16(p.mc + off, v);
+                    continue;
+                }
+                // ranks run in step: each starts behind itself, so that no rank's links take everybody's stores at once
+                for (int j = 0; j < c.world; j++) {
+                    const int d = c.rank + 1 + j < c.world ? c.rank + 1 + j : c.rank + 1 + j - c.world;
+                    if (!(p.skip_self && d == c.rank))
                         *reinterpret_cast<uint4 *>(p.dst[d] + off) = v;
+                }
             }
         } else {
             // ragged or unaligned blocks: element by element (2 or 4 bytes)
@@ -144,7 +151,7 @@ int32_t ovk_comm_wait_done(ovk_ctx *ctx, const OvkCommView &view)
 // The exchange on prepared arguments; `view` is this call's epoch (already taken).
 int32_t ovk_comm_gather_cols(ovk_ctx *ctx, const OvkCommView &view, const void *src, size_t src_pitch, int elem_bytes,
                              int64_t m, int64_t n_shard, int64_t col0, int64_t n_total, void *const *y_peers,
-                             bool skip_self)
+                             bool skip_self, void *y_multicast)
 {
     GatherParams p = {};
     p.src = static_cast<const uint8_t *>(src);
@@ -163,6 +170,7 @@ int32_t ovk_comm_gather_cols(ovk_ctx *ctx, const OvkCommView &view, const void *
         vec = vec && aligned_to(y_peers[r], 16);
     }
     p.vec16 = vec;
+    p.mc = vec && aligned_to(y_multicast, 16) ? static_cast<uint8_t *>(y_multicast) : nullptr;
     // A copy needs few SMs to fill NVLink; the rest stay free for whatever follows on other streams.
     const int64_t chunks = m * (vec ? p.row_bytes / 16 : n_shard);
     const unsigned grid = unsigned(std::max<int64_t>(1, std::min<int64_t>(ceil_div64(chunks, COPY_THREADS * 4), 64)));
@@ -271,6 +279,12 @@ int32_t ovk_comm_barrier(ovk_ctx *ctx)
 int32_t ovk_allgather_cols(ovk_ctx *ctx, const void *y_shard, int32_t dtype, int64_t m, int64_t n_shard, int64_t col0,
                            int64_t n_total, void *const *y_peers)
 {
+    return ovk_allgather_cols_multicast(ctx, y_shard, dtype, m, n_shard, col0, n_total, y_peers, nullptr);
+}
+
+int32_t ovk_allgather_cols_multicast(ovk_ctx *ctx, const void *y_shard, int32_t dtype, int64_t m, int64_t n_shard,
+                                     int64_t col0, int64_t n_total, void *const *y_peers, void *y_multicast)
+{
     if (!ctx || !y_peers)
         return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "ovk_allgather_cols: null argument");
     OVK_REQUIRE(ctx, ctx->comm.world >= 1, "ovk_allgather_cols: ovk_comm_init has not been called");
@@ -287,7 +301,8 @@ int32_t ovk_allgather_cols(ovk_ctx *ctx, const void *y_shard, int32_t dtype, int
     const bool in_place = y_shard == nullptr;
     const void *src = in_place ? static_cast<const uint8_t *>(y_peers[ctx->comm.rank]) + size_t(col0) * es : y_shard;
     const size_t pitch = size_t(in_place ? n_total : n_shard) * es;
-    return ovk_comm_gather_cols(ctx, v, src, pitch, es, m, n_shard, col0, n_total, y_peers, in_place);
+    // a multicast store also writes this rank's own copy, so an in-place block is simply written again
+    return ovk_comm_gather_cols(ctx, v, src, pitch, es, m, n_shard, col0, n_total, y_peers, in_place, y_multicast);
 }
 
 }  // extern "C"

@@ -51,6 +51,16 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
     return v;
 }
 
+// One 16-byte store to the same offset of EVERY rank's buffer: the address is a multicast mapping of the
+// ranks' buffers, the store crosses this GPU's links once and the NVSwitch delivers it to all of them
+// (this GPU's own copy included).
+__device__ __forceinline__ void st_multicast16(void *mc_addr, uint4 v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+
 // Called by one whole warp: lane d stores the epoch into slot `rank` of peer d's array.
 __device__ __forceinline__ void announce(const OvkCommView &c, bool done_flag, int lane)
 {

@@ -20,10 +20,10 @@ int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, i
                        int64_t m, void *y, int32_t y_dtype);
 bool ovk_nbits_gemm_is_per_block(const ovk_ctx *ctx, const ovk_nbits_weight *w);
 int32_t ovk_nbits_gemm_into(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int64_t m, void *const *y_dst,
-                            int n_dst, int64_t ldy, int64_t col0, int32_t y_dtype, const OvkCommView *view);
+                            int n_dst, int64_t ldy, int64_t col0, int32_t y_dtype, const OvkCommView *view, void *y_multicast);
 int32_t ovk_comm_gather_cols(ovk_ctx *ctx, const OvkCommView &view, const void *src, size_t src_pitch, int elem_bytes,
                              int64_t m, int64_t n_shard, int64_t col0, int64_t n_total, void *const *y_peers,
-                             bool skip_self);
+                             bool skip_self, void *y_multicast);
 
 extern "C" {
 
@@ -143,6 +143,13 @@ int32_t ovk_matmul_nbits_group(ovk_ctx *ctx, int32_t count, const ovk_nbits_weig
 int32_t ovk_matmul_nbits_nsplit(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype, int64_t m,
                                 int64_t col0, int64_t n_total, void *const *y_peers, int32_t y_dtype)
 {
+    return ovk_matmul_nbits_nsplit_multicast(ctx, w, a, a_dtype, m, col0, n_total, y_peers, nullptr, y_dtype);
+}
+
+int32_t ovk_matmul_nbits_nsplit_multicast(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype, int64_t m,
+                                          int64_t col0, int64_t n_total, void *const *y_peers, void *y_multicast,
+                                          int32_t y_dtype)
+{
     if (!ctx || !w || !y_peers)
         return ovk_fail(ctx, OVK_INVALID_ARGUMENT, "ovk_matmul_nbits_nsplit: null argument");
     const int world = ctx->comm.world, rank = ctx->comm.rank;
@@ -162,27 +169,27 @@ int32_t ovk_matmul_nbits_nsplit(ovk_ctx *ctx, const ovk_nbits_weight *w, const v
     void *own = y_peers[rank];
     void *own_block = static_cast<uint8_t *>(own) + size_t(col0) * es;
     if (m == 0)
-        return ovk_comm_gather_cols(ctx, view, own_block, size_t(n_total) * es, es, 0, w->n, col0, n_total, y_peers, true);
+        return ovk_comm_gather_cols(ctx, view, own_block, size_t(n_total) * es, es, 0, w->n, col0, n_total, y_peers, true, y_multicast);
     const bool prefill = ovk_nbits_gemm_applies(ctx, w, m, a_dtype, y_dtype, a, own_block);
     if (prefill && ovk_nbits_gemm_is_per_block(ctx, w) && y_dtype == OVK_FLOAT16) {
-        int32_t rc = ovk_nbits_gemm_into(ctx, w, a, m, y_peers, world, n_total, col0, y_dtype, &view);
+        int32_t rc = ovk_nbits_gemm_into(ctx, w, a, m, y_peers, world, n_total, col0, y_dtype, &view, y_multicast);
         if (rc != OVK_OK)
             return rc;
         return world > 1 ? ovk_comm_wait_done(ctx, view) : OVK_OK;
     }
     if (prefill) {
         void *dst[1] = {own};
-        int32_t rc = ovk_nbits_gemm_into(ctx, w, a, m, dst, 1, n_total, col0, y_dtype, nullptr);
+        int32_t rc = ovk_nbits_gemm_into(ctx, w, a, m, dst, 1, n_total, col0, y_dtype, nullptr, nullptr);
         if (rc != OVK_OK)
             return rc;
-        return ovk_comm_gather_cols(ctx, view, own_block, size_t(n_total) * es, es, m, w->n, col0, n_total, y_peers, true);
+        return ovk_comm_gather_cols(ctx, view, own_block, size_t(n_total) * es, es, m, w->n, col0, n_total, y_peers, true, y_multicast);
     }
     // kernels that write a contiguous [m, N] result: through a temporary
     void *tmp = nullptr;
     OVK_CUDA(ctx, cudaMallocAsync(&tmp, size_t(m) * w->n * es + 256, ctx->stream));
     int32_t rc = ovk_matmul_nbits(ctx, w, a, a_dtype, m, tmp, y_dtype);
     if (rc == OVK_OK)
-        rc = ovk_comm_gather_cols(ctx, view, tmp, size_t(w->n) * es, es, m, w->n, col0, n_total, y_peers, false);
+        rc = ovk_comm_gather_cols(ctx, view, tmp, size_t(w->n) * es, es, m, w->n, col0, n_total, y_peers, false, y_multicast);
     cudaFreeAsync(tmp, ctx->stream);
     return rc;
 }

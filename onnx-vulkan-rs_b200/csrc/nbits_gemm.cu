@@ -103,6 +103,7 @@ struct GemmParams {
     int *status;
     // where results go: n_dst matrices of row pitch ldy elements, this launch's columns starting at col0
     void *y_dst[OVK_MAX_RANKS];
+    void *y_mc;            // multicast mapping of all n_dst matrices (one store reaches every rank), or null
     int n_dst, ldy, col0;
     int vec_ok;            // every destination takes 16-byte stores at multiples of 8 columns
     OvkCommView comm;      // used when n_dst > 1
@@ -478,8 +479,25 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                 const uint8_t *src0 = buf + r0 * (BW * 2) + cc * 16;
                 const size_t off0 = (size_t(d.m_base + r0) * size_t(p.ldy) + size_t(p.col0 + n)) * 2;
                 const size_t step = size_t(p.ldy) * 4;  // two rows of Y
-                if (p.vec_ok && d.n0 + BW <= p.N) {
-                    for (int r = 0; r < p.n_dst; r++) {
+                // The ranks are taken in an order that starts behind this rank and differs from CTA to CTA:
+                // ranks run in step, and if every CTA of every rank began with rank 0, rank 0's links would
+                // take the whole box's stores while the others' idled (measured at 4 ranks: 480 GB/s received
+                // per GPU instead of ...).
+                const int first = exchange ? (p.comm.rank + 1 + int(blockIdx.x)) % p.n_dst : 0;
+                if (p.y_mc && p.vec_ok && d.n0 + BW <= p.N) {
+                    // one multicast store per chunk: it leaves over this GPU's links once and the switch
+                    // delivers it to every rank, this one included
+                    uint8_t *dst = static_cast<uint8_t *>(p.y_mc) + off0;
+                    const uint8_t *src = src0;
+#pragma unroll 4
+                    for (int row = r0; row < Y_ROWS; row += 2, src += 2 * BW * 2, dst += step) {
+                        const uint4 v = *reinterpret_cast<const uint4 *>(src);
+                        if (ok && row < d.rows)
+                            comm::st_multicast16(dst, v);
+                    }
+                } else if (p.vec_ok && d.n0 + BW <= p.N) {
+                    for (int j = 0; j < p.n_dst; j++) {
+                        const int r = first + j < p.n_dst ? first + j : first + j - p.n_dst;
                         uint8_t *dst = static_cast<uint8_t *>(p.y_dst[r]) + off0;
                         const uint8_t *src = src0;
 #pragma unroll 4
@@ -491,7 +509,8 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                     }
                 } else {
                     // a tile at the ragged edge of N, or destinations that do not take 16-byte stores
-                    for (int r = 0; r < p.n_dst; r++) {
+                    for (int j = 0; j < p.n_dst; j++) {
+                        const int r = first + j < p.n_dst ? first + j : first + j - p.n_dst;
                         uint8_t *dst = static_cast<uint8_t *>(p.y_dst[r]) + off0;
                         const uint8_t *src = src0;
                         for (int row = r0; row < Y_ROWS; row += 2, src += 2 * BW * 2, dst += step) {
@@ -972,7 +991,7 @@ bool ovk_nbits_gemm_is_per_block(const ovk_ctx *ctx, const ovk_nbits_weight *w)
 // Y[:, col0 : col0 + N] = A x dequant(B) in each of the n_dst matrices of row pitch ldy
 // (n_dst > 1: fp16 only, `view` describes the ranks and the call's epoch).
 int32_t ovk_nbits_gemm_into(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, int64_t m, void *const *y_dst,
-                            int n_dst, int64_t ldy, int64_t col0, int32_t y_dtype, const OvkCommView *view)
+                            int n_dst, int64_t ldy, int64_t col0, int32_t y_dtype, const OvkCommView *view, void *y_multicast)
 {
     // small blocks with fp16 scales: the scale goes into the weight (exactly, as two fp16 terms)
     if (ovk_nbits_gemm_split_applies(ctx, wc)) {
@@ -1028,6 +1047,7 @@ int32_t ovk_nbits_gemm_into(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void
     }
     if (view)
         p.comm = *view;
+    p.y_mc = n_dst > 1 && aligned_to(y_multicast, 16) ? y_multicast : nullptr;
     p.units = units;
     p.unit_slabs = unit_slabs;
     p.unit_blocks = bs >= SLAB ? 1 : SLAB / bs;
@@ -1055,5 +1075,5 @@ int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void *a, 
 {
     (void)a_dtype;
     void *dst[1] = {y};
-    return ovk_nbits_gemm_into(ctx, wc, a, m, dst, 1, wc->n, 0, y_dtype, nullptr);
+    return ovk_nbits_gemm_into(ctx, wc, a, m, dst, 1, wc->n, 0, y_dtype, nullptr, nullptr);
 }

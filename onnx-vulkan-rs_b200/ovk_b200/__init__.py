@@ -74,6 +74,8 @@ SIGNATURES = {
     "ovk_comm_barrier": (_I32, [_P]),
     "ovk_allgather_cols": (_I32, [_P, _P, _I32, _I64, _I64, _I64, _I64, C.POINTER(_P)]),
     "ovk_matmul_nbits_nsplit": (_I32, [_P, _P, _P, _I32, _I64, _I64, _I64, C.POINTER(_P), _I32]),
+    "ovk_matmul_nbits_nsplit_multicast": (_I32, [_P, _P, _P, _I32, _I64, _I64, _I64, C.POINTER(_P), _P, _I32]),
+    "ovk_allgather_cols_multicast": (_I32, [_P, _P, _I32, _I64, _I64, _I64, _I64, C.POINTER(_P), _P]),
     "ovk_dynamic_quantize": (_I32, [_P, _P, _I64, _P, _P, _P]),
     "ovk_dynamic_quantize_folded": (_I32, [_P, _P, _I64, _P, _P, _P, _P]),
     "ovk_decomposed_gelu": (_I32, [_P, _P, _I64, C.c_float, C.c_float, C.c_float, _I32, _P]),
@@ -262,17 +264,20 @@ class Context:
     def comm_barrier(self):
         self.check(lib().ovk_comm_barrier(self.h))
 
-    def allgather_cols(self, y_shard, m, n_shard, col0, n_total, y_peers, dtype=FLOAT16):
-        """y_shard: a [m, n_shard] tensor, or None when the block already sits in this rank's matrix."""
+    def allgather_cols(self, y_shard, m, n_shard, col0, n_total, y_peers, dtype=FLOAT16, multicast=None):
+        """y_shard: a [m, n_shard] tensor, or None when the block already sits in this rank's matrix.
+        multicast: a multicast mapping of the ranks' matrices (one store reaches every rank), or None."""
         arr = (_P * len(y_peers))(*[int(p) for p in y_peers])
-        self.check(lib().ovk_allgather_cols(self.h, _ptr(y_shard), dtype if y_shard is None else _dtype_code(y_shard),
-                                            m, n_shard, col0, n_total, arr))
+        self.check(lib().ovk_allgather_cols_multicast(self.h, _ptr(y_shard),
+                                                      dtype if y_shard is None else _dtype_code(y_shard),
+                                                      m, n_shard, col0, n_total, arr, _P(multicast) if multicast else None))
 
-    def matmul_nbits_nsplit(self, w: "NBitsWeight", a, col0, n_total, y_peers, y_dtype=FLOAT16):
+    def matmul_nbits_nsplit(self, w: "NBitsWeight", a, col0, n_total, y_peers, y_dtype=FLOAT16, multicast=None):
         """This rank's columns [col0, col0 + w.n) of Y = A x dequant(B), stored into every rank's matrix."""
         m = a.numel() // w.k
         arr = (_P * len(y_peers))(*[int(p) for p in y_peers])
-        self.check(lib().ovk_matmul_nbits_nsplit(self.h, w.h, _ptr(a), _dtype_code(a), m, col0, n_total, arr, y_dtype))
+        self.check(lib().ovk_matmul_nbits_nsplit_multicast(self.h, w.h, _ptr(a), _dtype_code(a), m, col0, n_total, arr,
+                                                           _P(multicast) if multicast else None, y_dtype))
 
     # ------------------------------------------------- DynamicQuantizeLinear
     def dynamic_quantize(self, x, folded_range=None, out=None):

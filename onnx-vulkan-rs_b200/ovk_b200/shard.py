@@ -186,3 +186,37 @@ class PeerGroup:
         for p in self._owned:
             self.ctx.check(ovk_b200.lib().ovk_free(self.ctx.h, p))
         self._owned = []
+
+
+class SymmetricGroup:
+    """The same as PeerGroup on buffers from ``torch.distributed._symmetric_memory``, which also
+    gives a MULTICAST mapping of a buffer where the box has NVLink SHARP: an address whose stores the
+    NVSwitch delivers to the same offset of every rank's buffer.  ``symmetric(nbytes)`` returns
+    (addresses per rank, multicast address or 0).  torch owns the buffers; the library only gets
+    addresses."""
+
+    def __init__(self, ctx, rank: int, world: int, group=None):
+        import torch.distributed as dist
+        import ovk_b200
+        self.ctx, self.rank, self.world = ctx, rank, world
+        self.group = group if group is not None else dist.group.WORLD
+        self._keep = []
+        flags, _ = self.symmetric(int(ovk_b200.lib().ovk_comm_flag_bytes()))
+        ctx.comm_init(rank, world, flags)
+
+    def symmetric(self, nbytes: int):
+        import torch
+        import torch.distributed._symmetric_memory as symm_mem
+        t = symm_mem.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+        t.zero_()
+        handle = symm_mem.rendezvous(t, self.group)
+        self._keep.append((t, handle))
+        return [int(p) for p in handle.buffer_ptrs], int(handle.multicast_ptr or 0)  # 0: the box has no NVLink SHARP
+
+    def close(self):
+        import torch
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self._keep = []
