@@ -69,40 +69,78 @@ struct TcParams {
     TcMember mem[MAX_GROUP];
 };
 
+// Accesses to the member table use constant indices (unrolled loops, a switch), so that the parameter block
+// is read where it lies and no copy of it is made.
 __device__ __forceinline__ int column_tiles(const TcParams &p, int bn)
 {
-    return p.members ? p.mem[p.members - 1].tile_end : (p.N + bn - 1) / bn;
+    if (!p.members)
+        return (p.N + bn - 1) / bn;
+    int t = p.mem[0].tile_end;
+#pragma unroll
+    for (int i = 1; i < MAX_GROUP; i++)
+        if (i < p.members)
+            t = p.mem[i].tile_end;
+    return t;
 }
 // Column tile `nt` of the launch: which member it belongs to and where its columns start there.
 __device__ __forceinline__ int member_of(const TcParams &p, int nt, int bn, int &n0)
 {
     int j = 0, first = 0;
-    while (j + 1 < p.members && nt >= p.mem[j].tile_end) {
-        first = p.mem[j].tile_end;
-        j++;
-    }
+#pragma unroll
+    for (int i = 0; i + 1 < MAX_GROUP; i++)
+        if (i + 1 < p.members && nt >= p.mem[i].tile_end) {
+            first = p.mem[i].tile_end;
+            j = i + 1;
+        }
     n0 = (nt - first) * bn;
     return j;
 }
-__device__ __forceinline__ ColView columns_of(const TcParams &p, int j)
+__device__ __forceinline__ ColView view_of(const TcMember &m)
 {
     ColView v;
-    if (p.members) {
-        v.colsum = p.mem[j].colsum;
-        v.scale = p.mem[j].scale;
-        v.product = p.mem[j].product;
-        v.fbias = p.mem[j].fbias;
-        v.out = p.mem[j].out;
-        v.N = p.mem[j].N;
-    } else {
-        v.colsum = p.colsum;
-        v.scale = p.epi.scale;
-        v.product = p.epi.product;
-        v.fbias = p.epi.fbias;
-        v.out = p.out;
-        v.N = p.N;
-    }
+    v.colsum = m.colsum;
+    v.scale = m.scale;
+    v.product = m.product;
+    v.fbias = m.fbias;
+    v.out = m.out;
+    v.N = m.N;
     return v;
+}
+__device__ __forceinline__ ColView columns_of(const TcParams &p, int j)
+{
+    if (p.members) {
+        switch (j) {
+        case 1:
+            return view_of(p.mem[1]);
+        case 2:
+            return view_of(p.mem[2]);
+        case 3:
+            return view_of(p.mem[3]);
+        default:
+            return view_of(p.mem[0]);
+        }
+    }
+    ColView v;
+    v.colsum = p.colsum;
+    v.scale = p.epi.scale;
+    v.product = p.epi.product;
+    v.fbias = p.epi.fbias;
+    v.out = p.out;
+    v.N = p.N;
+    return v;
+}
+__device__ __forceinline__ const CUtensorMap *map_of(const TmGroup &g, int j)
+{
+    switch (j) {
+    case 1:
+        return &g.m[1];
+    case 2:
+        return &g.m[2];
+    case 3:
+        return &g.m[3];
+    default:
+        return &g.m[0];
+    }
 }
 
 __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity)
@@ -139,6 +177,9 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
                                                  int lane, int64_t row, bool row_ok, int n0, uint32_t row_term, int32_t za,
                                                  float &run_max, float &run_neg)
 {
+    // (The ragged-edge store loops below are unrolled by pragma: left to itself the compiler indexed the
+    // 32 accumulators at run time there, which put all of them in local memory - every int8 kernel ran
+    // 8-28 % slower.)
     const bool vec4 = p.vec_ok != 0;
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -185,8 +226,10 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
                 for (int j = 0; j < 32; j += 4)
                     *reinterpret_cast<int4 *>(o + j) = make_int4(r[j], r[j + 1], r[j + 2], r[j + 3]);
             } else {
-                for (int j = 0; j < 32 && col0 + j < v.N; j++)
-                    o[j] = int32_t(r[j]);
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    if (col0 + j < v.N)
+                        o[j] = int32_t(r[j]);
             }
         } else if (p.epi.mode == EPI_SCALE) {
             // fl(fl(float(acc) * s) + bias) [Relu], as epi_scale_value computes it
@@ -209,8 +252,10 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
                 for (int j = 0; j < 32; j += 4)
                     *reinterpret_cast<float4 *>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
             } else {
-                for (int j = 0; j < 32 && col0 + j < v.N; j++)
-                    o[j] = f[j];
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    if (col0 + j < v.N)
+                        o[j] = f[j];
             }
         } else {
             // sat(rne(f32(acc + bias) * ratio) + y_zp), as epi_requant_value computes it
@@ -231,8 +276,10 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
                 for (int j = 0; j < 32; j += 4)
                     *reinterpret_cast<uint32_t *>(o + j) = q8[j] | (q8[j + 1] << 8) | (q8[j + 2] << 16) | (q8[j + 3] << 24);
             } else {
-                for (int j = 0; j < 32 && col0 + j < v.N; j++)
-                    o[j] = uint8_t(q8[j]);
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    if (col0 + j < v.N)
+                        o[j] = uint8_t(q8[j]);
             }
         }
     }
@@ -291,14 +338,16 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ T
     if (warp == 0) {
         if (lane == 0) {
             umma::prefetch_tmap(&tmA);
-            for (int j = 0; j < max(p.members, 1); j++)
-                umma::prefetch_tmap(&tmBs.m[j]);
+#pragma unroll
+            for (int j = 0; j < MAX_GROUP; j++)
+                if (j < max(p.members, 1))
+                    umma::prefetch_tmap(&tmBs.m[j]);
             int s = 0;
             uint32_t ph = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
                 const int m0 = (tile / n_tiles) * BM;
                 int n0;
-                const CUtensorMap *tmB = &tmBs.m[member_of(p, tile % n_tiles, BN, n0)];
+                const CUtensorMap *tmB = map_of(tmBs, member_of(p, tile % n_tiles, BN, n0));
                 for (int kb = 0; kb < p.num_kb; kb++) {
                     if (!wait_parked(&empty[s], ph ^ 1)) {
                         atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
@@ -446,7 +495,8 @@ constexpr int THREADS2 = 11 * 32;  // TMA, issuer 0, eight epilogue warps, issue
 constexpr size_t SMEM2 = size_t(STAGES2) * (A2_BYTES + B2_BYTES) + 1024 + 256;
 
 __global__ void __launch_bounds__(THREADS2, 1)
-mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TcParams p)
+mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ TcParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *sA = smem;

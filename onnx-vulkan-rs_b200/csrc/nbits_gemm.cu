@@ -479,10 +479,9 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                 const uint8_t *src0 = buf + r0 * (BW * 2) + cc * 16;
                 const size_t off0 = (size_t(d.m_base + r0) * size_t(p.ldy) + size_t(p.col0 + n)) * 2;
                 const size_t step = size_t(p.ldy) * 4;  // two rows of Y
-                // The ranks are taken in an order that starts behind this rank and differs from CTA to CTA:
-                // ranks run in step, and if every CTA of every rank began with rank 0, rank 0's links would
-                // take the whole box's stores while the others' idled (measured at 4 ranks: 480 GB/s received
-                // per GPU instead of ...).
+                // The ranks are taken in an order that starts behind this rank and differs from CTA to CTA, so
+                // that the ranks, which run in step, do not all store into the same peer at once.  (Measured at
+                // 4 ranks it made no difference - the switch spreads the load - but it costs nothing.)
                 const int first = exchange ? (p.comm.rank + 1 + int(blockIdx.x)) % p.n_dst : 0;
                 if (p.y_mc && p.vec_ok && d.n0 + BW <= p.N) {
                     // one multicast store per chunk: it leaves over this GPU's links once and the switch
