@@ -51,6 +51,14 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
     return v;
 }
 
+// the same, for a word only blocks of this GPU write
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // One 16-byte store to the same offset of EVERY rank's buffer: the address is a multicast mapping of the
 // ranks' buffers, the store crosses this GPU's links once and the NVSwitch delivers it to all of them
 // (this GPU's own copy included).

@@ -133,6 +133,7 @@ int32_t ovk_flush(ovk_ctx *ctx)
     int st = ctx->host_status[0];
     if (st != OVK_DEV_OK) {
         OVK_CUDA(ctx, cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream));
+        OVK_CUDA(ctx, cudaMemsetAsync(ctx->range_slot, 0, 256, ctx->stream));  // a launch that gave up may have left counts
         if (st == OVK_DEV_BAD_INDEX)
             return ovk_fail(ctx, OVK_INVALID_ARGUMENT,
                             "GatherBlockQuantized: an index read on the device fell outside the table "
@@ -142,6 +143,7 @@ int32_t ovk_flush(ovk_ctx *ctx)
                         : st == OVK_DEV_TIMEOUT_MMA  ? "tensor core never signalled"
                         : st == OVK_DEV_TIMEOUT_SLOT ? "pipeline stage never freed"
                         : st == OVK_DEV_TIMEOUT_PEER ? "a peer GPU never signalled"
+                        : st == OVK_DEV_TIMEOUT_GRID ? "a block of the same launch never arrived"
                                                      : "self-test wait on a barrier nothing arrives at");
     }
     return OVK_OK;

@@ -1,4 +1,5 @@
-// DynamicQuantizeLinear: range pass + quantize pass, both on the device.
+// DynamicQuantizeLinear: range pass + quantize pass, both on the device - as two launches, or, when
+// the tensor fits in the registers of one block per SM, as ONE launch whose blocks meet at a counter.
 //
 // Follows interp::quantize_on_device (crates/onnx-vulkan-core/src/interp.rs
 // :1977-2085) and the two shaders of src/shaders/dynamic_quantize.rs: PARTIAL
@@ -165,6 +166,107 @@ dql_quantize_kernel(const float *__restrict__ x, int64_t n, uint32_t *__restrict
     }
 }
 
+// Both passes in one launch.  Every thread keeps its (loaded, for the GELU form already transformed)
+// values in registers: up to VPT vectors of four, so x is read once and the GELU is evaluated once.
+// Between the passes the blocks meet at a counter: slot[0], slot[1] take the folded range, slot[2]
+// counts arrivals, slot[3] departures; the block that leaves last zeroes all four for the next call.
+// The launch has at most one block per SM and a block waits for nothing but its siblings, which wait
+// for nothing but a free SM, so the meeting cannot deadlock; the wait is bounded all the same and a
+// limit that runs out is reported through the status word (the bytes are then quantized with whatever
+// range had arrived).
+constexpr int ONE_PASS_THREADS = 1024;
+constexpr int ONE_PASS_VPT_MAX = 8;
+
+template <typename Load, int VPT>
+__global__ void __launch_bounds__(ONE_PASS_THREADS, 1)
+dql_one_pass_kernel(const float4 *__restrict__ x4, int64_t n4, uint32_t *__restrict__ slot, float *__restrict__ scale_out,
+                    uint8_t *__restrict__ zp_out, uint32_t *__restrict__ y4, Load load, int *status, long long wait_cycles)
+{
+    OVK_PDL_LAUNCH_DEPENDENTS();
+    OVK_PDL_WAIT();
+    const int64_t first = int64_t(blockIdx.x) * ONE_PASS_THREADS + threadIdx.x;
+    const int64_t stride = int64_t(gridDim.x) * ONE_PASS_THREADS;
+    float4 v[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {  // every load is issued before the first value is used
+        const int64_t i = first + j * stride;
+        v[j] = i < n4 ? __ldg(x4 + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    float mn = 0.0f, mx = 0.0f;  // 0 is always part of the range
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        if (first + j * stride < n4) {
+            v[j].x = load(v[j].x);
+            v[j].y = load(v[j].y);
+            v[j].z = load(v[j].z);
+            v[j].w = load(v[j].w);
+            fold(v[j].x, mn, mx);
+            fold(v[j].y, mn, mx);
+            fold(v[j].z, mn, mx);
+            fold(v[j].w, mn, mx);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    __shared__ float smn[32], smx[32], s_scale, s_zp;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) {
+        smn[warp] = mn;
+        smx[warp] = mx;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        mn = smn[lane];
+        mx = smx[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+        if (lane == 0) {
+            atomicMax(slot + 0, __float_as_uint(-mn) & 0x7fffffffu);
+            atomicMax(slot + 1, __float_as_uint(mx) & 0x7fffffffu);
+            __threadfence();
+            atomicAdd(slot + 2, 1u);
+            const long long t0 = clock64();
+            while (comm::ld_acquire_gpu(slot + 2) < gridDim.x) {
+                if (clock64() - t0 > wait_cycles) {
+                    atomicExch(status, OVK_DEV_TIMEOUT_GRID);
+                    break;
+                }
+                __nanosleep(32);
+            }
+            float scale, zp;
+            const uint32_t folded[2] = {__ldcg(slot + 0), __ldcg(slot + 1)};
+            scale_zp_from_range(folded, scale, zp);
+            s_scale = scale;
+            s_zp = zp;
+            if (blockIdx.x == 0) {
+                scale_out[0] = scale;
+                zp_out[0] = uint8_t(zp);
+            }
+            if (atomicAdd(slot + 3, 1u) == gridDim.x - 1) {
+                slot[0] = 0u;
+                slot[1] = 0u;
+                slot[2] = 0u;
+                slot[3] = 0u;
+            }
+        }
+    }
+    __syncthreads();
+    const float scale = s_scale, zp = s_zp;
+#pragma unroll
+    for (int j = 0; j < VPT; j++) {
+        const int64_t i = first + j * stride;
+        if (i < n4)
+            y4[i] = quant1(v[j].x, scale, zp) | (quant1(v[j].y, scale, zp) << 8) | (quant1(v[j].z, scale, zp) << 16) |
+                    (quant1(v[j].w, scale, zp) << 24);
+    }
+}
+
 __global__ void dql_identity_kernel(float *scale_out, uint8_t *zp_out)
 {
     scale_out[0] = 1.0f;
@@ -205,6 +307,27 @@ int32_t quantize_passes(ovk_ctx *ctx, const char *what, const float *x, int64_t 
     // both passes: grid-stride, four vectors per thread and trip, at most four blocks per SM
     const unsigned blocks = unsigned(std::min<int64_t>(ceil_div64(work, 1024), int64_t(ctx->sm_count) * 4));
     uint32_t *range = folded ? folded : ctx->range_slot;
+    if (!folded && vec_ok && n % 4 == 0) {
+        const int64_t n4 = n / 4;
+        const int64_t grid = std::min<int64_t>(ctx->sm_count, ceil_div64(n4, ONE_PASS_THREADS));
+        const int64_t per_thread = ceil_div64(n4, grid * ONE_PASS_THREADS);
+        if (per_thread <= ONE_PASS_VPT_MAX) {
+            uint32_t *slot = ctx->range_slot + 4;  // four words of its own, zero between calls
+            const float4 *x4 = reinterpret_cast<const float4 *>(x);
+            uint32_t *y4 = reinterpret_cast<uint32_t *>(y);
+            const long long limit = 2000000000ll;  // about a second
+#define OVK_ONE_PASS(V)                                                                                               \
+    OVK_CUDA(ctx, ovk_launch_pdl(dql_one_pass_kernel<Load, V>, dim3(unsigned(grid)), dim3(ONE_PASS_THREADS), 0, ctx->stream, \
+                                 x4, n4, slot, y_scale, y_zero_point, y4, load, ctx->dev_status, limit))
+            if (per_thread <= 1) OVK_ONE_PASS(1);
+            else if (per_thread <= 2) OVK_ONE_PASS(2);
+            else if (per_thread <= 4) OVK_ONE_PASS(4);
+            else OVK_ONE_PASS(8);
+#undef OVK_ONE_PASS
+            OVK_LAUNCHED(ctx, "dql_one_pass");
+            return OVK_OK;
+        }
+    }
     if (!folded) {
         OVK_CUDA(ctx, ovk_launch_pdl(dql_range_kernel<Load>, dim3(blocks), dim3(256), 0, ctx->stream, x, n, range, vec_ok, load));
         OVK_LAUNCHED(ctx, "dql_range");

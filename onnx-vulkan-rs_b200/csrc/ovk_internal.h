@@ -24,6 +24,7 @@ enum : int {
     OVK_DEV_BAD_INDEX = 4,     // a gather index read on the device fell outside the table
     OVK_DEV_TIMEOUT_PEER = 5,  // a flag another GPU writes never reached the expected value
     OVK_DEV_TIMEOUT_SELFTEST = 6,  // ovk_selftest_device_timeout: the wait that is meant to run out
+    OVK_DEV_TIMEOUT_GRID = 7,      // a block gave up waiting for the other blocks of its own launch
 };
 
 struct ovk_ctx {
@@ -36,7 +37,7 @@ struct ovk_ctx {
     const char *last_kernel = "";
     uint64_t launches = 0;
     // device scratch owned by the context
-    uint32_t *range_slot = nullptr;  // 2 x u32: bits of -min, max (DynamicQuantizeLinear)
+    uint32_t *range_slot = nullptr;  // 64 x u32, zero between calls: folded range and block counters of DynamicQuantizeLinear
     int *dev_status = nullptr;       // sticky error word written by bounded waits
     int *host_status = nullptr;      // pinned mirror read by ovk_flush
     float *params = nullptr;         // OVK_PARAM_FLOATS floats: per-call constants (requantize ratios)

@@ -26,7 +26,6 @@
 #include "epilogue.cuh"
 #include "umma.cuh"
 
-#include <cstdlib>
 
 namespace {
 
@@ -640,17 +639,6 @@ conv_pack_w_kernel(const uint8_t *__restrict__ w, uint8_t *__restrict__ wt, int3
         wsum[co] = red[0];
 }
 
-int conv_mode()
-{
-    // OVK_CONV_TAPS=1 selects one TMA load per tap instead of one halo tile per pixel tile
-    static int mode = -1;
-    if (mode < 0) {
-        const char *e = getenv("OVK_CONV_TAPS");
-        mode = (e && e[0] == '1') ? 0 : 1;
-    }
-    return mode;
-}
-
 }  // namespace
 
 int32_t ovk_qconv_tc_prepare_weight(ovk_ctx *ctx, ovk_qconv_weight *w)
@@ -761,7 +749,8 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
     p.sw_layout = p.kch == 128 ? umma::LAYOUT_SW128 : (p.kch == 64 ? umma::LAYOUT_SW64 : umma::LAYOUT_SW32);
     p.sbo = 8 * p.kch;
     const int max_off = (g.kh - 1) * g.dh * WP + (g.kw - 1) * g.dw;
-    p.halo = conv_mode() == 1 && p.chunks == 1 && BM + max_off <= 256;
+    // one halo tile per pixel tile when all taps of a tile fit one TMA box (256 rows); one load per tap otherwise
+    p.halo = p.chunks == 1 && BM + max_off <= 256;
     p.halo_rows = p.halo ? BM + max_off : BM;
     p.a_stage = uint32_t((size_t(p.halo_rows) * p.kch + 1023) & ~size_t(1023));
     p.w_slice = uint32_t((size_t(p.co_pad) * p.kch + 1023) & ~size_t(1023));

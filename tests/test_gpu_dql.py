@@ -59,6 +59,29 @@ def test_parakeet_activations(d):
     check(x)
 
 
+# ------------------------------------------------------------------ one launch or two
+
+def test_one_launch_up_to_the_register_capacity_then_two():
+    """A tensor of whole 16-byte vectors that fits eight vectors per thread of one 1024-thread block per SM
+    is quantized by ONE launch (the blocks meet at a counter between the passes); one vector more, a
+    length that is no multiple of four, or an unaligned view take the two launches.  Same bytes, scale
+    and zero point either way, and repeated calls find the counters zero again."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    cap = sms * 1024 * 8 * 4
+    rng = cases.rng_for(3, 99)
+    for n, kernel, launches in ((4, "dql_one_pass", 1), (4096, "dql_one_pass", 1), (1024 * 1000, "dql_one_pass", 1),
+                                (cap, "dql_one_pass", 1), (cap + 4, "dql_quantize", 2), (4098, "dql_quantize", 2)):
+        x = rng.standard_normal(n, dtype=np.float32) * np.float32(2.5)
+        x[n // 2] = -11.0
+        want_y, want_s, want_z = orc.dynamic_quantize(x)
+        for _ in range(3):
+            before = ctx().launches
+            y, s, z = ctx().dynamic_quantize(dev(x))
+            assert ctx().launches - before == launches and ctx().last_kernel == kernel, n
+            assert np.array_equal(host(y), want_y) and float(host(s)) == float(want_s) and int(host(z)) == want_z, n
+    ctx().flush()  # raises if a wait ran out
+
+
 # ------------------------------------------------------------------ folded range, DecomposedGelu
 
 def test_folded_range_skips_the_range_pass_and_gives_the_same_bytes():
@@ -106,7 +129,8 @@ def test_decomposed_gelu_quantize_equals_the_two_nodes(shape):
     by DynamicQuantizeLinear - on the device, and in the CPU port."""
     x = (cases.rng_for(3, 8).standard_normal(shape, dtype=np.float32) * np.float32(2.0)).astype(np.float32)
     y, s, z = ctx().decomposed_gelu_quantize(dev(x), *GELU)
-    assert ctx().last_kernel == "dql_quantize"
+    # a whole number of 16-byte vectors that fits the registers of one block per SM: one launch
+    assert ctx().last_kernel == ("dql_one_pass" if x.size % 4 == 0 else "dql_quantize")
     g = ctx().decomposed_gelu(dev(x), *GELU)
     y2, s2, z2 = ctx().dynamic_quantize(g)
     assert np.array_equal(host(y), host(y2)) and float(s) == float(s2) and int(z) == int(z2)
