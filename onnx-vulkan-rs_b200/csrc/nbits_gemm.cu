@@ -120,18 +120,20 @@ struct GemmParams {
 struct Run {
     uint32_t u, end;  // the host keeps tiles x units below 2^31
 };
-__device__ __forceinline__ uint32_t run_start(const GemmParams &p, uint32_t cta)
+// `cta` of `grid`: the CTA's number and the grid's size - or, when two CTAs work as a pair on tiles of
+// twice the width, the pair's number and the number of pairs.
+__device__ __forceinline__ uint32_t run_start(const GemmParams &p, uint32_t cta, uint32_t grid)
 {
     const unsigned long long tiles = (unsigned long long)p.m_tiles * p.n_tiles;
     if (p.shared_k)
-        return uint32_t(tiles * p.units * cta / gridDim.x);
-    return uint32_t(tiles * cta / gridDim.x) * uint32_t(p.units);
+        return uint32_t(tiles * p.units * cta / grid);
+    return uint32_t(tiles * cta / grid) * uint32_t(p.units);
 }
-__device__ __forceinline__ Run cta_run(const GemmParams &p)
+__device__ __forceinline__ Run cta_run(const GemmParams &p, uint32_t cta, uint32_t grid)
 {
     Run r;
-    r.u = run_start(p, blockIdx.x);
-    r.end = run_start(p, blockIdx.x + 1);
+    r.u = run_start(p, cta, grid);
+    r.end = run_start(p, cta + 1, grid);
     return r;
 }
 // A CTA's tiles are consecutive numbers: one weight tile, the token tiles one after the other.
@@ -236,6 +238,13 @@ struct PassDesc {
 };
 constexpr int PASS_STOP = -1000000;
 
+// PAIR: launched in clusters of two.  The pair computes tiles of 256 weight columns - CTA `crank` owns
+// columns crank * 128 .. + 127 of the tile, in its own tensor memory, exactly as a single CTA owns its
+// 128 - by tcgen05.mma.cta_group::2, which reads the token operand half from each CTA's shared memory:
+// each CTA loads only half of the token rows of a slab, which halves what the L2 has to deliver per
+// MMA.  One thread of CTA 0 issues; the unpack and promotion warps of both CTAs announce themselves at
+// CTA 0's barriers, and the completion of the MMAs is signalled to the barriers of both.
+template <bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
 nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_constant__ CUtensorMap tmRaw,
                   const __grid_constant__ GemmParams p)
@@ -257,6 +266,9 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
     PassDesc *s_desc = reinterpret_cast<PassDesc *>(tmem_slot + 4);  // [2]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t crank = PAIR ? umma::cluster_rank() : 0u;
+    const uint32_t vcta = PAIR ? blockIdx.x >> 1 : blockIdx.x, vgrid = PAIR ? gridDim.x >> 1 : gridDim.x;
+    constexpr int WIDE = PAIR ? 2 : 1;  // 128-column tiles per tile number
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -264,10 +276,10 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
             umma::mbar_init(&empty[s], 1);
         }
         for (int s = 0; s < A_STAGES; s++)
-            umma::mbar_init(&full_w[s], 4);  // one arrival per unpack warp
+            umma::mbar_init(&full_w[s], PAIR ? 8 : 4);  // one arrival per unpack warp (of both CTAs)
         for (int b = 0; b < ACC_RING; b++) {
             umma::mbar_init(&acc_full[b], 1);
-            umma::mbar_init(&acc_empty[b], 8);
+            umma::mbar_init(&acc_empty[b], PAIR ? 16 : 8);
         }
         for (int h = 0; h < 2; h++) {
             umma::mbar_init(&y_full[h], 4);  // one arrival per promotion warp of the half
@@ -276,11 +288,19 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         umma::fence_barrier_init();
     }
     if (warp == 1) {
-        umma::tmem_alloc(tmem_slot, TMEM_COLS);
-        umma::tmem_relinquish();
+        if constexpr (PAIR) {
+            umma::tmem_alloc_pair(tmem_slot, TMEM_COLS);
+            umma::tmem_relinquish_pair();
+        } else {
+            umma::tmem_alloc(tmem_slot, TMEM_COLS);
+            umma::tmem_relinquish();
+        }
     }
     umma::tc_fence_before();
-    __syncthreads();
+    if constexpr (PAIR)
+        umma::cluster_sync_all();  // the other CTA's barriers are initialised before anything arrives there
+    else
+        __syncthreads();
     umma::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -298,20 +318,22 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
             umma::prefetch_tmap(&tmRaw);
             int s = 0;
             uint32_t ph = 0;
-            Run run = cta_run(p);
+            Run run = cta_run(p, vcta, vgrid);
             int tile, ub, ue;
             bool ok = true;
             while (ok && next_item(p, run, tile, ub, ue)) {
                 int mi, ni;
                 tile_origin(p, tile, mi, ni);
-                const int m0 = mi * p.bt, n0 = ni * BW;
+                // a pair: this CTA's half of the tile's token rows, and its own 128 weight rows
+                const int tok_rows = PAIR ? p.bt / 2 : p.bt;
+                const int m0 = mi * p.bt + int(crank) * (PAIR ? tok_rows : 0), n0 = (ni * WIDE + int(crank)) * BW;
                 for (int sl = ub * p.unit_slabs; sl < ue * p.unit_slabs; sl++) {
                     if (!wait_parked(&empty[s], ph ^ 1)) {
                         atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
                         ok = false;
                         break;
                     }
-                    umma::mbar_expect_tx(&full_x[s], uint32_t(p.bt) * 128u + RAW_BYTES);
+                    umma::mbar_expect_tx(&full_x[s], uint32_t(tok_rows) * 128u + RAW_BYTES);
                     umma::tma_load_2d(sX + s * B_BYTES, &tmAct, &full_x[s], sl * SLAB, m0);
                     umma::tma_load_2d(sR + s * RAW_BYTES, &tmRaw, &full_x[s], sl * 32, n0);
                     if (++s == STAGES) {
@@ -336,15 +358,15 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         // item to the next exactly as it does from tile to tile.
         const int me = warp - 1;
         const int issuers = p.bs >= SLAB ? 2 : 1;  // smaller blocks: two per slab, one issuer
-        if (me < issuers) {
+        if (me < issuers && crank == 0) {
             const bool leader = umma::elect_one();
-            const uint32_t idesc = umma::instr_desc(1 /*f32*/, 0 /*f16*/, 0 /*f16*/, BW, p.bt);
+            const uint32_t idesc = umma::instr_desc(1 /*f32*/, 0 /*f16*/, 0 /*f16*/, BW * WIDE, p.bt);
             const uint32_t desc_hi = ((1024u >> 4) & 0x3fffu) | (1u << 14) | (umma::LAYOUT_SW128 << 29);
             const uint32_t x16 = umma::smem_u32(sX) >> 4;
             int s = 0, a = 0, b = 0, slab_in_block = 0, owner = 0;
             uint32_t a_ph = 0, acc_ph = 0;
             bool ok = true;
-            Run run = cta_run(p);
+            Run run = cta_run(p, vcta, vgrid);
             int tile, ub, ue;
             while (ok && next_item(p, run, tile, ub, ue)) {
                 for (int sl = ub * p.unit_slabs; sl < ue * p.unit_slabs && ok; sl++) {
@@ -374,13 +396,23 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                             umma::tc_fence_after();
                             const uint32_t d = tmem_base + uint32_t(b * p.acc_stride);
                             if (leader) {
-                                umma::mma_f16_ts(d, a_t, x_lo, desc_hi, idesc, first ? 0u : 1u);
-                                umma::mma_f16_ts(d, a_t + 8, x_lo + 2, desc_hi, idesc, 1u);
-                                umma::mma_f16_ts(d, a_t + 16, x_lo + 4, desc_hi, idesc, 1u);
-                                umma::mma_f16_ts(d, a_t + 24, x_lo + 6, desc_hi, idesc, 1u);
-                                umma::mma_commit(&empty[s]);
-                                if (last)
-                                    umma::mma_commit(&acc_full[b]);
+                                if constexpr (PAIR) {
+                                    umma::mma_f16_ts_pair(d, a_t, x_lo, desc_hi, idesc, first ? 0u : 1u);
+                                    umma::mma_f16_ts_pair(d, a_t + 8, x_lo + 2, desc_hi, idesc, 1u);
+                                    umma::mma_f16_ts_pair(d, a_t + 16, x_lo + 4, desc_hi, idesc, 1u);
+                                    umma::mma_f16_ts_pair(d, a_t + 24, x_lo + 6, desc_hi, idesc, 1u);
+                                    umma::mma_commit_pair(&empty[s]);
+                                    if (last)
+                                        umma::mma_commit_pair(&acc_full[b]);
+                                } else {
+                                    umma::mma_f16_ts(d, a_t, x_lo, desc_hi, idesc, first ? 0u : 1u);
+                                    umma::mma_f16_ts(d, a_t + 8, x_lo + 2, desc_hi, idesc, 1u);
+                                    umma::mma_f16_ts(d, a_t + 16, x_lo + 4, desc_hi, idesc, 1u);
+                                    umma::mma_f16_ts(d, a_t + 24, x_lo + 6, desc_hi, idesc, 1u);
+                                    umma::mma_commit(&empty[s]);
+                                    if (last)
+                                        umma::mma_commit(&acc_full[b]);
+                                }
                             }
                         }
                         if (last) {
@@ -566,18 +598,26 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         // store of slab j is announced only after slab j + 1 has been unpacked - by then it has
         // completed and the wait costs nothing - and block indices are shifts, not divisions.
         const int bs_shift = 31 - __clz(p.bs);  // block sizes are powers of two
+        // where this warp announces an A stage: the issuing CTA's barrier
+        const uint32_t full_w_at = PAIR ? umma::mbar_in_cta(&full_w[0], 0) : 0u;
+        auto announce = [&](int stage) {
+            if constexpr (PAIR)
+                umma::mbar_arrive_cluster(full_w_at + uint32_t(stage) * 8u);
+            else
+                umma::mbar_arrive(&full_w[stage]);
+        };
         int seq = 0;       // number of slabs before the current item's first one
         int pending = -1;  // A stage stored to but not yet announced
         // This loop is the kernel's pace-setter, so ring positions are stepped by two inside an item (six
         // stages: no power of two) and divided out only once per item: slab g sits in stage s_g on the
         // ring's lap of parity ph_g, and the slab A_STAGES before it likewise in s_b / ph_b.
         bool ok = true;
-        Run run = cta_run(p);
+        Run run = cta_run(p, vcta, vgrid);
         int tile, ub, ue;
         while (ok && next_item(p, run, tile, ub, ue)) {
             int mi, ni;
             tile_origin(p, tile, mi, ni);
-            const int n = ni * BW + r;
+            const int n = (ni * WIDE + int(crank)) * BW + r;
             const int sl0 = ub * p.unit_slabs, len = (ue - ub) * p.unit_slabs;
             // zero points: one byte per block, fetched one slab of this group ahead
             const uint8_t *zrow = p.zp_t + size_t(n) * p.zp_pitch;
@@ -614,7 +654,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                     // shared-memory atomics
                     __syncwarp();
                     if (lane == 0)
-                        umma::mbar_arrive(&full_w[pending]);
+                        announce(pending);
                 }
                 const uint4 *raw = reinterpret_cast<const uint4 *>(sR + s * RAW_BYTES + r * 32);
                 const uint4 c0 = raw[0], c1 = raw[1];
@@ -640,6 +680,16 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                 umma::tc_fence_after();
                 pending = g & (A_STAGES - 1);
                 umma::tmem_st_32x32(a_lane + uint32_t(pending * A_COLS), wv);
+                if constexpr (PAIR) {
+                    // across the pair an announcement takes longer to arrive, so it leaves at once (measured:
+                    // 4 % faster than announcing a slab late, which is the faster way within one CTA)
+                    umma::tmem_st_wait();
+                    umma::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0)
+                        announce(pending);
+                    pending = -1;
+                }
                 s_g += 2;
                 if (s_g >= STAGES) {
                     s_g -= STAGES;
@@ -658,7 +708,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
             umma::tc_fence_before();
             __syncwarp();
             if (lane == 0)
-                umma::mbar_arrive(&full_w[pending]);
+                announce(pending);
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
@@ -672,10 +722,11 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         const int nchunks = (half_rows + 31) / 32;
         int b = 0;
         uint32_t acc_ph = 0;
+        const uint32_t acc_empty_at = PAIR ? umma::mbar_in_cta(&acc_empty[0], 0) : 0u;  // the issuing CTA's barrier
         uint32_t yseq = 0;  // tiles this half has put into its buffer
         bool first_item = true;
         bool ok = true;
-        Run run = cta_run(p);
+        Run run = cta_run(p, vcta, vgrid);
         int tile, ub, ue;
         // this thread's column of the half's token rows into the half's buffer, then the warp's arrival.
         // The buffer was handed back when the store warp had read the previous tile out of it, a tile's
@@ -709,7 +760,7 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         while (next_item(p, run, tile, ub, ue)) {
             int mi, ni;
             tile_origin(p, tile, mi, ni);
-            const int n0 = ni * BW;
+            const int n0 = (ni * WIDE + int(crank)) * BW;
             const int n = n0 + q * 32 + lane;
             float acc[HALF];
 #pragma unroll
@@ -736,8 +787,12 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                     if (c == nchunks - 1) {  // everything of this accumulator has been read: hand it back
                         umma::tc_fence_before();
                         __syncwarp();
-                        if (lane == 0)
-                            umma::mbar_arrive(&acc_empty[b]);
+                        if (lane == 0) {
+                            if constexpr (PAIR)
+                                umma::mbar_arrive_cluster(acc_empty_at + uint32_t(b) * 8u);
+                            else
+                                umma::mbar_arrive(&acc_empty[b]);
+                        }
                     }
 #pragma unroll
                     for (int j = 0; j < 32; j++)
@@ -767,13 +822,14 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                     // one holding its last
                     const long long total = (long long)p.m_tiles * p.n_tiles * p.units;
                     const long long x0 = (long long)tile * p.units, x1 = x0 + p.units - 1;
-                    const long long c_first = ((x0 + 1) * gridDim.x + total - 1) / total - 1;
-                    const long long c_last = ((x1 + 1) * gridDim.x + total - 1) / total - 1;
+                    const long long c_first = ((x0 + 1) * vgrid + total - 1) / total - 1;
+                    const long long c_last = ((x1 + 1) * vgrid + total - 1) / total - 1;
                     const uint32_t parts = uint32_t(c_last - c_first + 1);
-                    const uint32_t before = atomicAdd(&p.counters[tile], 1u);
+                    uint32_t *counter = p.counters + size_t(tile) * WIDE + crank;  // each 128-column tile has its own
+                    const uint32_t before = atomicAdd(counter, 1u);
                     const bool last = before + 1u == parts;
                     if (last)
-                        p.counters[tile] = 0;  // zero again for the next launch
+                        *counter = 0;  // zero again for the next launch
                     __threadfence();
                     s_count[0] = last ? uint32_t(c_first) : 0xffffffffu;
                     s_count[1] = uint32_t(c_last);
@@ -789,8 +845,9 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
                     for (uint32_t c = c_first; c <= c_last; c++) {
                         // the part of CTA c is the item its run begins with, unless the run began in
                         // an earlier tile (only the first of the CTAs can)
-                        const bool begins_here = run_start(p, c) >= uint32_t(tile) * uint32_t(p.units);
-                        const float *part = p.partials + ((size_t(c) * 2 + (begins_here ? 0 : 1)) * 2 + half) * PART_FLOATS +
+                        const bool begins_here = run_start(p, c, vgrid) >= uint32_t(tile) * uint32_t(p.units);
+                        const size_t holder = size_t(c) * WIDE + crank;  // the CTA of pair c with this CTA's columns
+                        const float *part = p.partials + ((holder * 2 + (begins_here ? 0 : 1)) * 2 + half) * PART_FLOATS +
                                             q * 32 + lane;
 #pragma unroll
                         for (int j = 0; j < HALF; j++)
@@ -831,9 +888,15 @@ nbits_gemm_kernel(const __grid_constant__ CUtensorMap tmAct, const __grid_consta
         }
     }
     umma::tc_fence_before();
-    __syncthreads();
-    if (warp == 1)
-        umma::tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (PAIR) {
+        umma::cluster_sync_all();  // the other CTA's MMAs write this CTA's tensor memory too
+        if (warp == 1)
+            umma::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    } else {
+        __syncthreads();
+        if (warp == 1)
+            umma::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
 }
 
 // ------------------------------------------------------------------- prepack
@@ -889,7 +952,7 @@ int32_t ovk_nbits_gemm_prepack(ovk_ctx *ctx, ovk_nbits_weight *w)
 {
     if (w->gemm_w)
         return OVK_OK;
-    const int64_t n_pad = ceil_div64(w->n, BW) * BW;
+    const int64_t n_pad = ceil_div64(w->n, 2 * BW) * (2 * BW);  // whole tiles of a pair of CTAs
     const int64_t k_src = w->n_blocks * w->block_size;  // the operator layout pads K to whole blocks
     const int64_t k_pad = ceil_div64(k_src, SLAB) * SLAB;
     const int64_t nb_pad = ceil_div64(k_pad, w->block_size);
@@ -947,33 +1010,68 @@ struct Plan {
     int bt;
     bool shared_k;
     unsigned grid;
+    double cost;
 };
-Plan plan_launch(const ovk_ctx *ctx, int64_t m, int n_tiles, int units, int unit_slabs)
+// `sms`: how many CTAs (or pairs of CTAs) run at once; `slab_fixed`: the part of a slab's time that
+// does not grow with the tile's tokens.
+Plan plan_launch(int sms, double slab_fixed, int64_t m, int n_tiles, int units, int unit_slabs, int counters_per_tile)
 {
-    const int sms = ctx->sm_count;
-    Plan best = {BT, false, 1};
+    Plan best = {BT, false, 1, 0.0};
     double best_cost = 0;
     bool have = false;
     for (int bt = BT; bt >= 96; bt -= 32) {
         const int64_t tiles = ceil_div64(m, bt) * n_tiles;
-        const double slab = 285 + bt;
+        const double slab = slab_fixed + bt;
         const double whole = double(ceil_div64(tiles, sms)) * units * unit_slabs * slab;
         if (!have || whole < 0.97 * best_cost) {
-            best = {bt, false, unsigned(std::min<int64_t>(tiles, sms))};
+            best = {bt, false, unsigned(std::min<int64_t>(tiles, sms)), whole};
             best_cost = whole;
             have = true;
         }
         const int64_t total_units = tiles * units;
         const int64_t grid = std::min<int64_t>(sms, total_units);
-        if (tiles <= OVK_TILE_COUNTERS && units > 1 && grid > 0) {
+        if (tiles * counters_per_tile <= OVK_TILE_COUNTERS && units > 1 && grid > 0) {
             const double shared = (double(ceil_div64(total_units, grid)) * unit_slabs + 8.0) * slab;
             if (shared < 0.95 * best_cost) {
-                best = {bt, true, unsigned(grid)};
+                best = {bt, true, unsigned(grid), shared};
                 best_cost = shared;
             }
         }
     }
     return best;
+}
+
+#ifndef OVK_NBITS_PAIRS
+#define OVK_NBITS_PAIRS 1
+#endif
+// How many pairs of CTAs of the pair kernel the GPU runs at once (0: none - clusters unavailable).
+int pair_capacity(ovk_ctx *ctx)
+{
+    if (ctx->nbits_pairs >= 0)
+        return ctx->nbits_pairs;
+    ctx->nbits_pairs = 0;
+    if (cudaFuncSetAttribute(nbits_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gemm_smem())) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(ctx->sm_count & ~1));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = gemm_smem();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, nbits_gemm_kernel<true>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    ctx->nbits_pairs = clusters;
+    return clusters;
 }
 
 bool ovk_nbits_gemm_split_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w);
@@ -1002,15 +1100,30 @@ int32_t ovk_nbits_gemm_into(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void
     int32_t rc = ovk_nbits_gemm_prepack(ctx, w);
     if (rc != OVK_OK)
         return rc;
-    const int n_tiles = int(w->gemm_n_pad / BW);
+    int n_tiles = int(ceil_div64(w->n, BW));
     const int bs = int(w->block_size);
     const int unit_slabs = bs >= SLAB ? bs / SLAB : 1;
     const int units = int(w->gemm_k_pad / SLAB) / unit_slabs;
-    const Plan plan = plan_launch(ctx, m, n_tiles, units, unit_slabs);
+    Plan plan = plan_launch(ctx->sm_count, 285.0, m, n_tiles, units, unit_slabs, 1);
+    // Pairs of CTAs on tiles of 256 columns: every CTA loads half the token rows of a slab.
+    bool pair = false;
+    if (OVK_NBITS_PAIRS && bs >= SLAB && pair_capacity(ctx) > 0) {
+        const int pairs = pair_capacity(ctx);
+        const int wide_tiles = int(ceil_div64(w->n, 2 * BW));
+        // Measured on 4096 tokens, blocks of 128: 464 against 488 us at K=3584 N=18944, 553 against 606 us at
+        // K=18944 N=3584, equal at N=2368; blocks of 64 and 256 gain 18-21 %.  Only a weight whose last
+        // wide tile would be mostly padding stays with single CTAs.
+        if (2 * wide_tiles == n_tiles || n_tiles >= 15) {
+            plan = plan_launch(pairs, 285.0, m, wide_tiles, units, unit_slabs, 2);
+            plan.grid *= 2;
+            n_tiles = wide_tiles;
+            pair = true;
+        }
+    }
     const int bt = plan.bt;
     CUtensorMap tmAct;
     if (!ovk_make_tmap_2d(&tmAct, a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, uint64_t(w->k), uint64_t(m), uint64_t(w->k) * 2,
-                          SLAB, uint32_t(bt), CU_TENSOR_MAP_SWIZZLE_128B))
+                          SLAB, uint32_t(pair ? bt / 2 : bt), CU_TENSOR_MAP_SWIZZLE_128B))
         return ovk_fail(ctx, OVK_BACKEND, "MatMulNBits: cuTensorMapEncodeTiled failed for A");
     CUtensorMap tmRaw;
     if (!ovk_make_tmap_2d(&tmRaw, w->gemm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(w->gemm_k_pad / 2),
@@ -1063,8 +1176,25 @@ int32_t ovk_nbits_gemm_into(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void
         p.partials = static_cast<float *>(ws);
         p.counters = ctx->tile_counters;
     }
-    OVK_CUDA(ctx, cudaFuncSetAttribute(nbits_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gemm_smem())));
-    nbits_gemm_kernel<<<plan.grid, THREADS, gemm_smem(), ctx->stream>>>(tmAct, tmRaw, p);
+    if (pair) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(plan.grid);
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = gemm_smem();
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        OVK_CUDA(ctx, cudaLaunchKernelEx(&cfg, nbits_gemm_kernel<true>, tmAct, tmRaw, p));
+        OVK_LAUNCHED(ctx, plan.shared_k ? "nbits_gemm_tc_pair_shared_k" : "nbits_gemm_tc_pair");
+        return OVK_OK;
+    }
+    OVK_CUDA(ctx, cudaFuncSetAttribute(nbits_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gemm_smem())));
+    nbits_gemm_kernel<false><<<plan.grid, THREADS, gemm_smem(), ctx->stream>>>(tmAct, tmRaw, p);
     OVK_LAUNCHED(ctx, plan.shared_k ? "nbits_gemm_tc_shared_k" : "nbits_gemm_tc");
     return OVK_OK;
 }

@@ -11,7 +11,7 @@ from gpu_util import assert_close, ctx, dev, host
 pytestmark = pytest.mark.gpu
 
 # the prefill kernel with per-block scaling: CTAs take whole tiles, or runs of quantization blocks that may share a tile
-PER_BLOCK = ("nbits_gemm_tc", "nbits_gemm_tc_shared_k")
+PER_BLOCK = ("nbits_gemm_tc", "nbits_gemm_tc_shared_k", "nbits_gemm_tc_pair", "nbits_gemm_tc_pair_shared_k")
 
 
 def run_gpu(a, nib, zp, scale, k, n, bs, out_dtype=None, flags=0):
