@@ -172,10 +172,11 @@ __device__ __forceinline__ bool wait_parked(uint64_t *bar, uint32_t parity)
 // The columns of one accumulator row block: tcgen05.ld 32 columns at a time (one row per thread),
 // the zero-point terms, then the store selected by EpiParams.  `hand_back` gets this warp's arrival
 // as soon as the last columns have been read, before they are processed.
+// (`hand_back_at`: the same barrier by its address in the cluster's window, when it lives in the other CTA of a pair.)
 template <int BN>
 __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColView &v, uint32_t taddr, uint64_t *hand_back,
                                                  int lane, int64_t row, bool row_ok, int n0, uint32_t row_term, int32_t za,
-                                                 float &run_max, float &run_neg)
+                                                 float &run_max, float &run_neg, uint32_t hand_back_at = 0)
 {
     // (The ragged-edge store loops below are unrolled by pragma: left to itself the compiler indexed the
     // 32 accumulators at run time there, which put all of them in local memory - every int8 kernel ran
@@ -189,8 +190,12 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
         if (c0 + 32 == BN) {  // the whole accumulator has been read: hand it back
             umma::tc_fence_before();
             __syncwarp();
-            if (lane == 0)
-                umma::mbar_arrive(hand_back);
+            if (lane == 0) {
+                if (hand_back_at)
+                    umma::mbar_arrive_cluster(hand_back_at);
+                else
+                    umma::mbar_arrive(hand_back);
+            }
         }
         if (n0 + c0 >= v.N)  // the same for every lane of the warp
             continue;
@@ -494,6 +499,13 @@ constexpr int A2_BYTES = BM2 * BK2, B2_BYTES = BN2 * BK2;
 constexpr int THREADS2 = 11 * 32;  // TMA, issuer 0, eight epilogue warps, issuer 1
 constexpr size_t SMEM2 = size_t(STAGES2) * (A2_BYTES + B2_BYTES) + 1024 + 256;
 
+// PAIR: clusters of two CTAs on tiles of 512 x 256.  CTA `crank` owns rows crank * 256 .. + 255 of the tile (its A
+// stage, its accumulators, its epilogue, exactly as a single CTA owns its 256) but loads only HALF of the
+// B stage: tcgen05.mma.cta_group::2 (M = 256: 128 rows from each CTA) reads B half from each CTA's shared
+// memory, so a CTA pulls 24 KB instead of 32 KB out of the L2 per K step - the L2, not the tensor core,
+// paces this kernel.  Both CTAs' loads are counted at CTA 0's `full` barrier, one thread pair of CTA 0
+// issues, completions are signalled to the barriers of both CTAs.
+template <bool PAIR>
 __global__ void __launch_bounds__(THREADS2, 1)
 mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ TcParams p)
@@ -510,8 +522,11 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     OVK_PDL_LAUNCH_DEPENDENTS();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t crank = PAIR ? umma::cluster_rank() : 0u;
+    const int vcta = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x), vgrid = PAIR ? int(gridDim.x >> 1) : int(gridDim.x);
+    constexpr int TM = PAIR ? 2 * BM2 : BM2;  // rows of a tile number
     const int n_tiles = (p.N + BN2 - 1) / BN2;
-    const int total_tiles = n_tiles * int((p.M + BM2 - 1) / BM2);
+    const int total_tiles = n_tiles * int((p.M + TM - 1) / TM);
     const int num_kb = (p.K + BK2 - 1) / BK2;
 
     if (threadIdx.x == 0) {
@@ -520,16 +535,24 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             umma::mbar_init(&empty[s], 1);
         }
         umma::mbar_init(acc_full, 2);  // one arrival per issuing thread
-        umma::mbar_init(acc_empty, 8);
+        umma::mbar_init(acc_empty, PAIR ? 16 : 8);
         umma::mbar_init(started, 1);
         umma::fence_barrier_init();
     }
     if (warp == 1) {
-        umma::tmem_alloc(tmem_slot, 512);
-        umma::tmem_relinquish();
+        if constexpr (PAIR) {
+            umma::tmem_alloc_pair(tmem_slot, 512);
+            umma::tmem_relinquish_pair();
+        } else {
+            umma::tmem_alloc(tmem_slot, 512);
+            umma::tmem_relinquish();
+        }
     }
     umma::tc_fence_before();
-    __syncthreads();
+    if constexpr (PAIR)
+        umma::cluster_sync_all();  // the other CTA's barriers are initialised before anything is counted there
+    else
+        __syncthreads();
     umma::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     OVK_PDL_WAIT();  // barriers and tensor memory were set up while the previous kernel drained
@@ -540,13 +563,26 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             umma::prefetch_tmap(&tmB);
             int s = 0;
             uint32_t ph = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-                const int m0 = (tile / n_tiles) * BM2, n0 = (tile % n_tiles) * BN2;
+            const uint32_t full_at = PAIR ? umma::mbar_in_cta(&full[0], 0) : 0u;  // CTA 0 counts both CTAs' bytes
+            for (int tile = vcta; tile < total_tiles; tile += vgrid) {
+                const int m0 = (tile / n_tiles) * TM + int(crank) * BM2;
+                const int n0 = (tile % n_tiles) * BN2 + (PAIR ? int(crank) * (BN2 / 2) : 0);
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!wait_parked(&empty[s], ph ^ 1)) {
                         atomicExch(p.status, OVK_DEV_TIMEOUT_SLOT);
                         tile = total_tiles;
                         break;
+                    }
+                    if constexpr (PAIR) {
+                        if (crank == 0)
+                            umma::mbar_expect_tx(&full[s], 2 * (A2_BYTES + B2_BYTES / 2));
+                        umma::tma_load_2d_pair(sA + s * A2_BYTES, &tmA, full_at + uint32_t(s) * 8u, kb * BK2, m0);
+                        umma::tma_load_2d_pair(sB + s * B2_BYTES, &tmB, full_at + uint32_t(s) * 8u, kb * BK2, n0);
+                        if (++s == STAGES2) {
+                            s = 0;
+                            ph ^= 1;
+                        }
+                        continue;
                     }
                     umma::mbar_expect_tx(&full[s], A2_BYTES + B2_BYTES);
                     umma::tma_load_2d(sA + s * A2_BYTES, &tmA, &full[s], kb * BK2, m0);
@@ -560,9 +596,9 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
     } else if (warp == 1 || warp == 10) {
         // two issuing threads on alternate K stages, as in mmi_tc_kernel
-        if (lane == 0) {
+        if (lane == 0 && crank == 0) {
             const int me = warp == 1 ? 0 : 1;
-            const uint32_t idesc = umma::instr_desc(2, p.a_signed ? 1 : 0, p.b_signed ? 1 : 0, 128, BN2);
+            const uint32_t idesc = umma::instr_desc(2, p.a_signed ? 1 : 0, p.b_signed ? 1 : 0, PAIR ? 256 : 128, BN2);
             // 64-byte rows, 64B swizzle: 512 bytes between 8-row groups
             const uint32_t desc_hi = ((512u >> 4) & 0x3fffu) | (1u << 14) | (umma::LAYOUT_SW64 << 29);
             const uint32_t a16 = (umma::smem_u32(sA) >> 4) | (1u << 16), b16 = (umma::smem_u32(sB) >> 4) | (1u << 16);
@@ -570,7 +606,7 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             bool ok = true;
             int s = 0;
             uint32_t ph = 0, acc_ph = 0, turn = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int tile = vcta; tile < total_tiles && ok; tile += vgrid) {
                 if (!wait_bounded(acc_empty, acc_ph ^ 1)) {
                     atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
                     break;
@@ -593,15 +629,26 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         const uint32_t a_lo = a16 + uint32_t(s) * (A2_BYTES >> 4);
                         const uint32_t b_lo = b16 + uint32_t(s) * (B2_BYTES >> 4);
                         const uint32_t acc = kb != 0;
-                        umma::mma_i8_lohi(tmem_base, a_lo, desc_hi, b_lo, desc_hi, idesc, acc);
-                        umma::mma_i8_lohi(tmem_base + BN2, a_lo + HALF, desc_hi, b_lo, desc_hi, idesc, acc);
+                        if constexpr (PAIR) {
+                            umma::mma_i8_lohi_pair(tmem_base, a_lo, desc_hi, b_lo, desc_hi, idesc, acc);
+                            umma::mma_i8_lohi_pair(tmem_base + BN2, a_lo + HALF, desc_hi, b_lo, desc_hi, idesc, acc);
+                        } else {
+                            umma::mma_i8_lohi(tmem_base, a_lo, desc_hi, b_lo, desc_hi, idesc, acc);
+                            umma::mma_i8_lohi(tmem_base + BN2, a_lo + HALF, desc_hi, b_lo, desc_hi, idesc, acc);
+                        }
                         if (kb == 0) {
                             umma::tc_fence_before();  // orders both overwriting MMAs before the other thread's (see mmi_tc_kernel)
                             umma::mbar_arrive(started);
                         }
-                        umma::mma_i8_lohi(tmem_base, a_lo + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
-                        umma::mma_i8_lohi(tmem_base + BN2, a_lo + HALF + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
-                        umma::mma_commit(&empty[s]);
+                        if constexpr (PAIR) {
+                            umma::mma_i8_lohi_pair(tmem_base, a_lo + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
+                            umma::mma_i8_lohi_pair(tmem_base + BN2, a_lo + HALF + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
+                            umma::mma_commit_pair(&empty[s]);
+                        } else {
+                            umma::mma_i8_lohi(tmem_base, a_lo + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
+                            umma::mma_i8_lohi(tmem_base + BN2, a_lo + HALF + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
+                            umma::mma_commit(&empty[s]);
+                        }
                         issued = true;
                     }
                     if (++s == STAGES2) {
@@ -610,23 +657,33 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     }
                 }
                 if (ok) {
-                    if (issued)
-                        umma::mma_commit(acc_full);
-                    else
-                        umma::mbar_arrive(acc_full);
+                    if constexpr (PAIR) {
+                        if (issued) {
+                            umma::mma_commit_pair(acc_full);
+                        } else {
+                            umma::mbar_arrive(acc_full);
+                            umma::mbar_arrive_cluster(umma::mbar_in_cta(acc_full, 1));
+                        }
+                    } else {
+                        if (issued)
+                            umma::mma_commit(acc_full);
+                        else
+                            umma::mbar_arrive(acc_full);
+                    }
                 }
                 acc_ph ^= 1;
             }
         }
-    } else {
+    } else if (warp >= 2 && warp < 10) {
         const int q = warp & 3;           // tensor-memory lane quarter this warp may read
-        const int half = (warp - 2) >> 2;  // upper or lower 128 rows of the tile
+        const int half = (warp - 2) >> 2;  // upper or lower 128 rows of this CTA's rows of the tile
+        const uint32_t acc_empty_at = PAIR ? umma::mbar_in_cta(acc_empty, 0) : 0u;
         const int32_t za = load_zp(p.a_zp, p.a_signed), zb = load_zp(p.b_zp, p.b_signed);
         float run_max = 0.0f, run_neg = 0.0f;
         bool ready = true;
         uint32_t acc_ph = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            const int64_t m0 = int64_t(tile / n_tiles) * BM2 + half * 128;
+        for (int tile = vcta; tile < total_tiles; tile += vgrid) {
+            const int64_t m0 = int64_t(tile / n_tiles) * TM + int64_t(crank) * BM2 + half * 128;
             const int n0 = (tile % n_tiles) * BN2;
             if (ready && !wait_parked(acc_full, acc_ph)) {
                 ready = false;
@@ -639,16 +696,22 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint32_t row_term = uint32_t(p.K) * uint32_t(za) * uint32_t(zb) -
                                       ((zb != 0 && p.rowsum && row_ok) ? uint32_t(zb) * uint32_t(p.rowsum[row]) : 0u);
             epilogue_columns<BN2>(p, columns_of(p, 0), tmem_base + (uint32_t(q * 32) << 16) + uint32_t(half * BN2), acc_empty,
-                                  lane, row, row_ok, n0, row_term, za, run_max, run_neg);
+                                  lane, row, row_ok, n0, row_term, za, run_max, run_neg, acc_empty_at);
             acc_ph ^= 1;
         }
         if (p.epi.mode == EPI_SCALE)
             epi_fold_range(p.epi, run_max, run_neg);
     }
     umma::tc_fence_before();
-    __syncthreads();
-    if (warp == 1)
-        umma::tmem_dealloc(tmem_base, 512);
+    if constexpr (PAIR) {
+        umma::cluster_sync_all();  // the other CTA's MMAs write this CTA's tensor memory too
+        if (warp == 1)
+            umma::tmem_dealloc_pair(tmem_base, 512);
+    } else {
+        __syncthreads();
+        if (warp == 1)
+            umma::tmem_dealloc(tmem_base, 512);
+    }
 }
 
 // sum_k a[m][k] per row, needed only when the weight's zero point is not 0:
@@ -723,18 +786,73 @@ int32_t launch_by_fill(ovk_ctx *ctx, const CUtensorMap &tmA, const ovk_mmi_weigh
 
 // 256 x 256 tiles: chosen for long K (the epilogue is not overlapped) and enough tiles to keep the
 // SMs in whole waves.
+#ifndef OVK_MMI_PAIRS
+#define OVK_MMI_PAIRS 1
+#endif
+// How many pairs of CTAs of the pair kernel the GPU runs at once (0: clusters unavailable).
+int pair_capacity(ovk_ctx *ctx)
+{
+    if (ctx->mmi_pairs >= 0)
+        return ctx->mmi_pairs;
+    ctx->mmi_pairs = 0;
+    if (cudaFuncSetAttribute(mmi_tc256_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM2)) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(ctx->sm_count & ~1));
+    cfg.blockDim = dim3(THREADS2);
+    cfg.dynamicSmemBytes = SMEM2;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, mmi_tc256_kernel<true>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    ctx->mmi_pairs = clusters;
+    return clusters;
+}
+
 int32_t launch256(ovk_ctx *ctx, const void *a, const ovk_mmi_weight *w, const TcParams &p)
 {
+    const int pairs = OVK_MMI_PAIRS ? pair_capacity(ctx) : 0;
+    const bool pair = pairs > 0 && p.M > BM2;  // at least two row blocks to share a B tile
     CUtensorMap tmA, tmB;
     if (!ovk_make_tmap_2d(&tmA, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(w->k), uint64_t(p.M), uint64_t(w->k), BK2,
                           BM2, CU_TENSOR_MAP_SWIZZLE_64B) ||
         !ovk_make_tmap_2d(&tmB, w->bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(w->k_pad), uint64_t(w->n_pad),
-                          uint64_t(w->k_pad), BK2, BN2, CU_TENSOR_MAP_SWIZZLE_64B))
+                          uint64_t(w->k_pad), BK2, pair ? BN2 / 2 : BN2, CU_TENSOR_MAP_SWIZZLE_64B))
         return ovk_fail(ctx, OVK_BACKEND, "MatMulInteger: cuTensorMapEncodeTiled failed (256 x 256 tiles)");
-    OVK_CUDA(ctx, cudaFuncSetAttribute(mmi_tc256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM2)));
+    if (pair) {
+        const int64_t tiles = ceil_div64(p.N, BN2) * ceil_div64(p.M, 2 * BM2);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2u * unsigned(std::min<int64_t>(tiles, pairs)));
+        cfg.blockDim = dim3(THREADS2);
+        cfg.dynamicSmemBytes = SMEM2;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+        OVK_CUDA(ctx, cudaLaunchKernelEx(&cfg, mmi_tc256_kernel<true>, tmA, tmB, p));
+        OVK_LAUNCHED(ctx, "mmi_tc_pair_512x256");
+        return OVK_OK;
+    }
+    OVK_CUDA(ctx, cudaFuncSetAttribute(mmi_tc256_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM2)));
     const int64_t tiles = ceil_div64(p.N, BN2) * ceil_div64(p.M, BM2);
     const unsigned grid = unsigned(std::min<int64_t>(tiles, ctx->sm_count));
-    OVK_CUDA(ctx, ovk_launch_pdl(mmi_tc256_kernel, dim3(grid), dim3(THREADS2), SMEM2, ctx->stream, tmA, tmB, p));
+    OVK_CUDA(ctx, ovk_launch_pdl(mmi_tc256_kernel<false>, dim3(grid), dim3(THREADS2), SMEM2, ctx->stream, tmA, tmB, p));
     OVK_LAUNCHED(ctx, "mmi_tc_256x256");
     return OVK_OK;
 }

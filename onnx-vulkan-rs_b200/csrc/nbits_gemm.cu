@@ -1107,7 +1107,10 @@ int32_t ovk_nbits_gemm_into(ovk_ctx *ctx, const ovk_nbits_weight *wc, const void
     Plan plan = plan_launch(ctx->sm_count, 285.0, m, n_tiles, units, unit_slabs, 1);
     // Pairs of CTAs on tiles of 256 columns: every CTA loads half the token rows of a slab.
     bool pair = false;
-    if (OVK_NBITS_PAIRS && bs >= SLAB && pair_capacity(ctx) > 0) {
+    // A launch that stores into three or more ranks is bound by the exchange, and there pairs lose: at 4 ranks
+    // the fused gate/up shard took 0.351 ms on pairs against 0.235 ms on single CTAs (at 2 ranks 0.260 against
+    // 0.276 ms).
+    if (OVK_NBITS_PAIRS && bs >= SLAB && n_dst <= 2 && pair_capacity(ctx) > 0) {
         const int pairs = pair_capacity(ctx);
         const int wide_tiles = int(ceil_div64(w->n, 2 * BW));
         // Measured on 4096 tokens, blocks of 128: 464 against 488 us at K=3584 N=18944, 553 against 606 us at

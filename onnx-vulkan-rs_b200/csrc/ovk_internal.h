@@ -55,6 +55,7 @@ struct ovk_ctx {
     // MatMulNBits prefill with K ranges shared between CTAs: one arrival counter per output tile,
     // zero between launches (the CTA that arrives last at a tile resets it)
     uint32_t *tile_counters = nullptr;
+    int mmi_pairs = -1;    // the same for the 256-row MatMulInteger kernel
     int nbits_pairs = -1;  // pairs of CTAs the MatMulNBits prefill kernel can run at once (-1: not asked yet)
 };
 constexpr int OVK_TILE_COUNTERS = 65536;

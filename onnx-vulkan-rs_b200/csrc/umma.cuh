@@ -102,6 +102,15 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *t, uin
         ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(t)), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
+// The load of one CTA of a pair: the bytes land in this CTA's shared memory, their arrival is counted at
+// a barrier given by its address in the cluster's window (mbar_in_cta), which may be the other CTA's.
+__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *t, uint32_t bar_cluster_addr, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(t)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *t, uint64_t *bar, int x, int y, int z)
 {
     asm volatile(
@@ -298,6 +307,18 @@ __device__ __forceinline__ void mma_commit_pair(uint64_t *bar)
         "{\n\t.reg .b16 m;\n\tmov.b16 m, 3;\n\t"
         "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}"
         ::"r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void mma_i8_lohi_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                 uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // The mbarrier gets one arrival when every MMA issued so far by this thread has finished.

@@ -176,16 +176,19 @@ def test_accumulator_overflow_guard():
         ctx().matmul_integer(w, torch.zeros((1, 33026), dtype=torch.uint8, device="cuda"))
 
 
-@pytest.mark.parametrize("m,k,n,a_signed,b_signed", [(1000, 2064, 9470, 0, 1), (1024, 2048, 9472, 1, 0)])
+@pytest.mark.parametrize("m,k,n,a_signed,b_signed", [(1000, 2064, 9470, 0, 1), (1024, 2048, 9472, 1, 0),
+                                                     (2300, 2048, 7500, 0, 1)])
 def test_large_product_takes_256_tiles(m, k, n, a_signed, b_signed):
-    """Long K and exactly one wave of 256 x 256 tiles: ragged edges in M, N and K, both zero points."""
+    """Long K and whole waves of 256-row blocks: ragged edges in M, N and K, both zero points.  Where the GPU runs
+    clusters, two CTAs share each 512 x 256 tile (tcgen05.mma.cta_group::2, half of the B stage loaded by each): the
+    last tile's second CTA has rows past M (1000 = 512 + 488) or none at all (2300 = 4 x 512 + 252)."""
     a = cases.lcg_bytes_fast(m * k, 19).reshape(m, k)
     b = cases.lcg_bytes_fast(k * n, 23).reshape(k, n)
     a = a.view(np.int8) if a_signed else a
     b = b.view(np.int8) if b_signed else b
     azp, bzp = (-5 if a_signed else 131), (-7 if b_signed else 121)
     got, kernel = run_mmi(a, b, azp, bzp)
-    assert kernel == "mmi_tc_256x256"
+    assert kernel in ("mmi_tc_256x256", "mmi_tc_pair_512x256")
     assert np.array_equal(got, orc.matmul_integer(a, b, azp, bzp))
 
 
