@@ -138,6 +138,26 @@ def test_prefill_against_the_oracle(k, n, bs, m):
     assert_close(got, want, 1e-3, 1e-3, f"prefill {k}->{n} bs={bs} M={m}")
 
 
+@pytest.mark.parametrize("n", [1793, 1921, 2049, 2368, 4000])
+@pytest.mark.parametrize("m,bs", [(200, 128), (97, 64), (130, 256)])
+def test_prefill_on_pairs_of_ctas_with_a_ragged_last_tile(n, m, bs):
+    """Pairs of CTAs compute tiles of 256 weight columns (tcgen05.mma.cta_group::2); widths whose last tile leaves
+    the second CTA of the pair one column (1921 = 15 x 128 + 1), nothing at all (1793, 2049), half a tile (2368) or
+    a ragged piece (4000), with token counts whose halves are ragged too.  Blocks of 64 take f32 scales here, which
+    keep them on the per-block kernel.  Every output against the CPU port."""
+    k = 512
+    a, nib, zp, scale = cases.nbits_synthetic(11, m, k, n, bs)
+    if bs == 64:
+        scale = scale.astype(np.float32)
+    got, kern = run_gpu(a, nib, zp, scale, k, n, bs)
+    assert kern in PER_BLOCK
+    import torch
+    if torch.cuda.get_device_capability(0)[0] >= 9:
+        assert "pair" in kern, kern
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, bs), scale, orc.pack_zero_points(zp), k, n, bs)
+    assert_close(got, want, 1e-3, 1e-3, f"pair prefill N={n} M={m} bs={bs}")
+
+
 @pytest.mark.parametrize("m,bs", [(90, 128), (150, 128), (190, 128), (200, 128), (385, 128), (200, 256)])
 def test_prefill_every_token_tile_width(m, bs):
     """The per-block kernel picks 96, 128, 160 or 192 tokens per tile (with 4, 3,
