@@ -158,6 +158,21 @@ def test_prefill_on_pairs_of_ctas_with_a_ragged_last_tile(n, m, bs):
     assert_close(got, want, 1e-3, 1e-3, f"pair prefill N={n} M={m} bs={bs}")
 
 
+def test_prefill_repeats_bit_for_bit():
+    """The same product a hundred times: barriers that cross a pair of CTAs, K ranges shared between CTAs and the
+    fixed order of their partial sums leave no room for a result that depends on timing."""
+    import torch
+    for m, k, n, bs in ((700, 1024, 2368, 128), (333, 2048, 4000, 256)):
+        a, nib, zp, scale = cases.nbits_synthetic(13, m, k, n, bs)
+        w = ctx().nbits_prepack(dev(orc.pack_nibbles(nib, bs)), dev(scale.reshape(-1)), dev(orc.pack_zero_points(zp)), n, k, bs)
+        x = dev(a)
+        first = ctx().matmul_nbits(w, x).clone()
+        assert ctx().last_kernel in PER_BLOCK
+        for _ in range(100):
+            assert torch.equal(ctx().matmul_nbits(w, x), first)
+        ctx().flush()
+
+
 @pytest.mark.parametrize("m,bs", [(90, 128), (150, 128), (190, 128), (200, 128), (385, 128), (200, 256)])
 def test_prefill_every_token_tile_width(m, bs):
     """The per-block kernel picks 96, 128, 160 or 192 tokens per tile (with 4, 3,
