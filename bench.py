@@ -350,10 +350,14 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
     layer_kernel = ctx.last_kernel
     torch.cuda.synchronize()
     # a dozen launches of 3-15 us each: replayed from a graph so that the device, not Python, is timed
+    # (ten layers per replay, as the layers of an encoder follow each other: one replay of a single layer is
+    # half launch latency of the graph itself)
+    layers_per_replay = 10
     gl = torch.cuda.CUDAGraph()
     with torch.cuda.graph(gl, stream=torch.cuda.current_stream()):
-        layer_step()
-    ms_l = timed(torch, dist, world, gl.replay, 10)
+        for _ in range(layers_per_replay):
+            layer_step()
+    ms_l = timed(torch, dist, world, gl.replay, 10) / layers_per_replay
     del gl
     ops = sum(2.0 * t * k * n for k, n in layer)
     out["int8_dynamic_parakeet_layer"] = {"T": t, "gemms": len(layer), "launches": layer_launches, "ms_per_layer": ms_l,

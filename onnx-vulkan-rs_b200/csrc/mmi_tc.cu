@@ -64,6 +64,7 @@ struct TcParams {
     EpiParams epi;
     void *out;
     int vec_ok;  // output rows may be written with 16-byte (int32/f32) or 4-byte (u8) stores
+    int tma_out; // 32-bit results leave through shared memory and bulk tensor stores (whole 128-byte lines)
     int *status;
     int members;  // 0: one weight (the fields above); else the group below
     TcMember mem[MAX_GROUP];
@@ -169,6 +170,49 @@ __device__ __forceinline__ bool wait_parked(uint64_t *bar, uint32_t parity)
     }
 }
 
+// 32-bit results on their way out.  A thread holds one row of 32 columns; stored from registers that is one
+// 16-byte piece per row and instruction, 32 rows apart in memory - measured ~2.3 TB/s over the whole GPU, which
+// is what paced the products of a few GOP.  Instead the warp lays its 32 x 32 block down in shared memory (rows of
+// 128 bytes, 16-byte pieces XOR-swizzled by the row so that the 32 lanes spread over all banks) and one lane
+// hands it to the bulk tensor store, which writes whole lines and clips the block at the ends of M and N.
+struct OutStage {
+    uint8_t *buf;            // this warp's `depth` buffers of 4 KB, 1024-byte aligned; null: stores from registers
+    const CUtensorMap *map;  // the output as a [M][N] tensor of 32-bit elements, box 32 x 32, 128-byte swizzle
+    int depth;               // 1 or 2 buffers
+    int seq;                 // blocks stored so far
+};
+__device__ __forceinline__ void stage_out_block(OutStage &st, const uint32_t (&v)[32], int lane, int col0, int row0, bool live)
+{
+    // the buffer about to be written has been read by the store that used it last
+    if (st.seq >= st.depth && lane == 0) {
+        if (st.depth == 2)
+            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        else
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    }
+    __syncwarp();
+    uint8_t *buf = st.buf + (st.depth == 2 ? (st.seq & 1) * 4096 : 0);
+    const uint32_t row = umma::smem_u32(buf) + uint32_t(lane) * 128u;
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row + uint32_t((j ^ (lane & 7)) << 4)), "r"(v[4 * j]),
+                     "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                     : "memory");
+    umma::fence_proxy_async();  // the bulk store reads through the async proxy
+    __syncwarp();
+    if (lane == 0 && live) {
+        umma::tma_store_2d(st.map, buf, col0, row0);
+        umma::tma_store_commit();
+    }
+    st.seq++;
+}
+// before the warp leaves: its stores have completed
+__device__ __forceinline__ void stage_out_drain(const OutStage &st, int lane)
+{
+    if (st.buf && lane == 0)
+        umma::tma_store_wait_all();
+}
+
 // The columns of one accumulator row block: tcgen05.ld 32 columns at a time (one row per thread),
 // the zero-point terms, then the store selected by EpiParams.  `hand_back` gets this warp's arrival
 // as soon as the last columns have been read, before they are processed.
@@ -176,7 +220,8 @@ __device__ __forceinline__ bool wait_parked(uint64_t *bar, uint32_t parity)
 template <int BN>
 __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColView &v, uint32_t taddr, uint64_t *hand_back,
                                                  int lane, int64_t row, bool row_ok, int n0, uint32_t row_term, int32_t za,
-                                                 float &run_max, float &run_neg, uint32_t hand_back_at = 0)
+                                                 float &run_max, float &run_neg, OutStage &st, bool live,
+                                                 uint32_t hand_back_at = 0)
 {
     // (The ragged-edge store loops below are unrolled by pragma: left to itself the compiler indexed the
     // 32 accumulators at run time there, which put all of them in local memory - every int8 kernel ran
@@ -224,7 +269,9 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
             r[j] = r[j] - uint32_t(za) * uint32_t(__shfl_sync(0xffffffffu, cs_l, j)) + row_term;
         if (p.epi.mode == EPI_RAW) {
             int32_t *o = static_cast<int32_t *>(v.out) + row * v.N + col0;
-            if (!row_ok) {
+            if (st.buf) {
+                stage_out_block(st, r, lane, col0, int(row) - lane, live);
+            } else if (!row_ok) {
                 // a row past M: nothing to store (no divergent `continue`: the next tcgen05.ld is warp-wide)
             } else if (vec4 && col0 + 32 <= v.N) {
 #pragma unroll
@@ -251,7 +298,13 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
                 }
             }
             float *o = static_cast<float *>(v.out) + row * v.N + col0;
-            if (!row_ok) {
+            if (st.buf) {
+                uint32_t bits[32];
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    bits[j] = __float_as_uint(f[j]);
+                stage_out_block(st, bits, lane, col0, int(row) - lane, live);
+            } else if (!row_ok) {
             } else if (vec4 && col0 + 32 <= v.N) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
@@ -291,14 +344,17 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
 }
 
 template <int BN> constexpr int stages_for() { return BN == 256 ? 4 : (BN == 128 ? 6 : 8); }
+constexpr int OUT_STAGE_BYTES = 4 * 2 * 4096;  // four epilogue warps, two 32 x 32 blocks of 32-bit results each
 template <int BN> constexpr size_t smem_for()
 {
-    return size_t(stages_for<BN>()) * (A_BYTES + BN * BK) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    return size_t(stages_for<BN>()) * (A_BYTES + BN * BK) + 1024 /*alignment slack*/ + 256 /*barriers*/ + OUT_STAGE_BYTES +
+           1024 /*its alignment*/;
 }
 
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
-mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ TmGroup tmBs, const __grid_constant__ TcParams p)
+mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ TmGroup tmBs, const __grid_constant__ TmGroup tmYs,
+              const __grid_constant__ TcParams p)
 {
     constexpr int STAGES = stages_for<BN>();
     constexpr int B_BYTES = BN * BK;
@@ -311,6 +367,7 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ T
     uint64_t *acc_empty = acc_full + 2;    // [2] the four epilogue warps have read it
     uint64_t *started = acc_empty + 2;     // [2] the tile's first (overwriting) MMA has been issued
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(started + 2);
+    uint8_t *out_stage = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(tmem_slot + 2) + 1023) & ~uintptr_t(1023));
 
     OVK_PDL_LAUNCH_DEPENDENTS();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -449,13 +506,16 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ T
         const int q = warp & 3;
         const int32_t za = load_zp(p.a_zp, p.a_signed), zb = load_zp(p.b_zp, p.b_signed);
         float run_max = 0.0f, run_neg = 0.0f;
+        OutStage st = {p.tma_out ? out_stage + (warp - 2) * 2 * 4096 : nullptr, nullptr, 2, 0};
         bool ready = true;
         int b = 0;
         uint32_t acc_ph = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int64_t m0 = int64_t(tile / n_tiles) * BM;
             int n0;
-            const ColView cols = columns_of(p, member_of(p, tile % n_tiles, BN, n0));
+            const int member = member_of(p, tile % n_tiles, BN, n0);
+            const ColView cols = columns_of(p, member);
+            st.map = map_of(tmYs, member);
             if (ready && !wait_parked(&acc_full[b], acc_ph)) {
                 ready = false;
                 if (lane == 0)
@@ -467,12 +527,13 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ T
             const uint32_t row_term = uint32_t(p.K) * uint32_t(za) * uint32_t(zb) -
                                       ((zb != 0 && p.rowsum && row_ok) ? uint32_t(zb) * uint32_t(p.rowsum[row]) : 0u);
             epilogue_columns<BN>(p, cols, tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BN), &acc_empty[b], lane, row,
-                                 row_ok, n0, row_term, za, run_max, run_neg);
+                                 row_ok, n0, row_term, za, run_max, run_neg, st, ready);
             if (++b == 2) {
                 b = 0;
                 acc_ph ^= 1;
             }
         }
+        stage_out_drain(st, lane);
         if (p.epi.mode == EPI_SCALE)
             epi_fold_range(p.epi, run_max, run_neg);
     }
@@ -497,7 +558,7 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ T
 constexpr int BM2 = 256, BN2 = 256, BK2 = 64, STAGES2 = 6;
 constexpr int A2_BYTES = BM2 * BK2, B2_BYTES = BN2 * BK2;
 constexpr int THREADS2 = 11 * 32;  // TMA, issuer 0, eight epilogue warps, issuer 1
-constexpr size_t SMEM2 = size_t(STAGES2) * (A2_BYTES + B2_BYTES) + 1024 + 256;
+constexpr size_t SMEM2 = size_t(STAGES2) * (A2_BYTES + B2_BYTES) + 1024 + 256 + 8 * 4096 /*one block per epilogue warp*/ + 1024;
 
 // PAIR: clusters of two CTAs on tiles of 512 x 256.  CTA `crank` owns rows crank * 256 .. + 255 of the tile (its A
 // stage, its accumulators, its epilogue, exactly as a single CTA owns its 256) but loads only HALF of the
@@ -508,17 +569,21 @@ constexpr size_t SMEM2 = size_t(STAGES2) * (A2_BYTES + B2_BYTES) + 1024 + 256;
 template <bool PAIR>
 __global__ void __launch_bounds__(THREADS2, 1)
 mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ TcParams p)
+                 const __grid_constant__ CUtensorMap tmY, const __grid_constant__ TcParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *sA = smem;
+    // a CTA of a pair holds half of a B stage, which leaves room for a second staging block per epilogue warp
+    constexpr int B_STAGE = PAIR ? B2_BYTES / 2 : B2_BYTES;
+    constexpr int OUT_DEPTH = PAIR ? 2 : 1;
     uint8_t *sB = smem + STAGES2 * A2_BYTES;
-    uint64_t *full = reinterpret_cast<uint64_t *>(sB + STAGES2 * B2_BYTES);
+    uint64_t *full = reinterpret_cast<uint64_t *>(sB + STAGES2 * B_STAGE);
     uint64_t *empty = full + STAGES2;
     uint64_t *acc_full = empty + STAGES2;  // the tile's accumulators are complete
     uint64_t *acc_empty = acc_full + 1;    // the eight epilogue warps have read them
     uint64_t *started = acc_empty + 1;     // the tile's first (overwriting) MMAs have been issued
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(started + 1);
+    uint8_t *out_stage = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(tmem_slot + 2) + 1023) & ~uintptr_t(1023));
 
     OVK_PDL_LAUNCH_DEPENDENTS();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -577,7 +642,7 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         if (crank == 0)
                             umma::mbar_expect_tx(&full[s], 2 * (A2_BYTES + B2_BYTES / 2));
                         umma::tma_load_2d_pair(sA + s * A2_BYTES, &tmA, full_at + uint32_t(s) * 8u, kb * BK2, m0);
-                        umma::tma_load_2d_pair(sB + s * B2_BYTES, &tmB, full_at + uint32_t(s) * 8u, kb * BK2, n0);
+                        umma::tma_load_2d_pair(sB + s * B_STAGE, &tmB, full_at + uint32_t(s) * 8u, kb * BK2, n0);
                         if (++s == STAGES2) {
                             s = 0;
                             ph ^= 1;
@@ -586,7 +651,7 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     }
                     umma::mbar_expect_tx(&full[s], A2_BYTES + B2_BYTES);
                     umma::tma_load_2d(sA + s * A2_BYTES, &tmA, &full[s], kb * BK2, m0);
-                    umma::tma_load_2d(sB + s * B2_BYTES, &tmB, &full[s], kb * BK2, n0);
+                    umma::tma_load_2d(sB + s * B_STAGE, &tmB, &full[s], kb * BK2, n0);
                     if (++s == STAGES2) {
                         s = 0;
                         ph ^= 1;
@@ -627,7 +692,7 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                         }
                         umma::tc_fence_after();
                         const uint32_t a_lo = a16 + uint32_t(s) * (A2_BYTES >> 4);
-                        const uint32_t b_lo = b16 + uint32_t(s) * (B2_BYTES >> 4);
+                        const uint32_t b_lo = b16 + uint32_t(s) * (B_STAGE >> 4);
                         const uint32_t acc = kb != 0;
                         if constexpr (PAIR) {
                             umma::mma_i8_lohi_pair(tmem_base, a_lo, desc_hi, b_lo, desc_hi, idesc, acc);
@@ -680,6 +745,7 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t acc_empty_at = PAIR ? umma::mbar_in_cta(acc_empty, 0) : 0u;
         const int32_t za = load_zp(p.a_zp, p.a_signed), zb = load_zp(p.b_zp, p.b_signed);
         float run_max = 0.0f, run_neg = 0.0f;
+        OutStage st = {p.tma_out ? out_stage + (warp - 2) * OUT_DEPTH * 4096 : nullptr, &tmY, OUT_DEPTH, 0};
         bool ready = true;
         uint32_t acc_ph = 0;
         for (int tile = vcta; tile < total_tiles; tile += vgrid) {
@@ -696,9 +762,10 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint32_t row_term = uint32_t(p.K) * uint32_t(za) * uint32_t(zb) -
                                       ((zb != 0 && p.rowsum && row_ok) ? uint32_t(zb) * uint32_t(p.rowsum[row]) : 0u);
             epilogue_columns<BN2>(p, columns_of(p, 0), tmem_base + (uint32_t(q * 32) << 16) + uint32_t(half * BN2), acc_empty,
-                                  lane, row, row_ok, n0, row_term, za, run_max, run_neg, acc_empty_at);
+                                  lane, row, row_ok, n0, row_term, za, run_max, run_neg, st, ready, acc_empty_at);
             acc_ph ^= 1;
         }
+        stage_out_drain(st, lane);
         if (p.epi.mode == EPI_SCALE)
             epi_fold_range(p.epi, run_max, run_neg);
     }
@@ -741,10 +808,22 @@ mmi_rowsum_kernel(const uint8_t *__restrict__ a, int64_t M, int K, int a_signed,
         rowsum[row] = s;
 }
 
+// The output of one weight as a [M][N] tensor of 32-bit elements for the bulk stores of the epilogue.
+bool out_map(CUtensorMap *map, void *out, int64_t m, int64_t n, bool f32)
+{
+    return ovk_make_tmap_2d(map, out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_INT32, uint64_t(n),
+                            uint64_t(m), uint64_t(n) * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 template <int BN>
 int32_t launch(ovk_ctx *ctx, const CUtensorMap &tmA, const ovk_mmi_weight *const *ws, int count, TcParams p)
 {
-    TmGroup tmBs = {};
+    TmGroup tmBs = {}, tmYs = {};
+    // 32-bit results (int32, or f32 after scale and bias) of rows that take 16-byte accesses leave by bulk stores
+    p.tma_out = p.vec_ok && p.epi.mode != EPI_REQUANT;
+    for (int j = 0; j < count && p.tma_out; j++)
+        if (!out_map(&tmYs.m[j], p.members ? p.mem[j].out : p.out, p.M, ws[j]->n, p.epi.mode == EPI_SCALE))
+            p.tma_out = 0;
     int64_t col_tiles = 0;
     for (int j = 0; j < count; j++) {
         if (!ovk_make_tmap_2d(&tmBs.m[j], ws[j]->bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(ws[j]->k_pad),
@@ -758,7 +837,7 @@ int32_t launch(ovk_ctx *ctx, const CUtensorMap &tmA, const ovk_mmi_weight *const
                                        int(smem_for<BN>())));
     const int64_t tiles = col_tiles * ceil_div64(p.M, BM);
     const unsigned grid = unsigned(std::min<int64_t>(tiles, ctx->sm_count));
-    OVK_CUDA(ctx, ovk_launch_pdl(mmi_tc_kernel<BN>, dim3(grid), dim3(THREADS), smem_for<BN>(), ctx->stream, tmA, tmBs, p));
+    OVK_CUDA(ctx, ovk_launch_pdl(mmi_tc_kernel<BN>, dim3(grid), dim3(THREADS), smem_for<BN>(), ctx->stream, tmA, tmBs, tmYs, p));
     OVK_LAUNCHED(ctx, BN == 256 ? "mmi_tc_128x256" : (BN == 128 ? "mmi_tc_128x128" : "mmi_tc_128x64"));
     return OVK_OK;
 }
@@ -819,8 +898,10 @@ int pair_capacity(ovk_ctx *ctx)
     return clusters;
 }
 
-int32_t launch256(ovk_ctx *ctx, const void *a, const ovk_mmi_weight *w, const TcParams &p)
+int32_t launch256(ovk_ctx *ctx, const void *a, const ovk_mmi_weight *w, TcParams p)
 {
+    CUtensorMap tmY = {};
+    p.tma_out = p.vec_ok && p.epi.mode != EPI_REQUANT && out_map(&tmY, p.out, p.M, w->n, p.epi.mode == EPI_SCALE);
     const int pairs = OVK_MMI_PAIRS ? pair_capacity(ctx) : 0;
     const bool pair = pairs > 0 && p.M > BM2;  // at least two row blocks to share a B tile
     CUtensorMap tmA, tmB;
@@ -845,14 +926,14 @@ int32_t launch256(ovk_ctx *ctx, const void *a, const ovk_mmi_weight *w, const Tc
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 2;
-        OVK_CUDA(ctx, cudaLaunchKernelEx(&cfg, mmi_tc256_kernel<true>, tmA, tmB, p));
+        OVK_CUDA(ctx, cudaLaunchKernelEx(&cfg, mmi_tc256_kernel<true>, tmA, tmB, tmY, p));
         OVK_LAUNCHED(ctx, "mmi_tc_pair_512x256");
         return OVK_OK;
     }
     OVK_CUDA(ctx, cudaFuncSetAttribute(mmi_tc256_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM2)));
     const int64_t tiles = ceil_div64(p.N, BN2) * ceil_div64(p.M, BM2);
     const unsigned grid = unsigned(std::min<int64_t>(tiles, ctx->sm_count));
-    OVK_CUDA(ctx, ovk_launch_pdl(mmi_tc256_kernel<false>, dim3(grid), dim3(THREADS2), SMEM2, ctx->stream, tmA, tmB, p));
+    OVK_CUDA(ctx, ovk_launch_pdl(mmi_tc256_kernel<false>, dim3(grid), dim3(THREADS2), SMEM2, ctx->stream, tmA, tmB, tmY, p));
     OVK_LAUNCHED(ctx, "mmi_tc_256x256");
     return OVK_OK;
 }
