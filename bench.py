@@ -365,6 +365,28 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
                                           "note": "3 x DynamicQuantizeLinear + DecomposedGeluQuantize + 6 x MatMulInteger with "
                                                   "the fused f32 epilogue (q, k, v share one quantisation and one launch); "
                                                   "2-8 GOP per GEMM, latency/HBM-bound; replicas at N > 1"}
+    # the convolution module of the same encoder layer: pointwise 1024 -> 2048, depthwise k=9, pointwise 1024 -> 1024
+    # (ConvIntegerScaleBias over [1, C, 1, T]); pointwise layers run as filters x image on the MatMulInteger kernels
+    conv_mod = {}
+    for name, c_in, c_out, kw, group in (("pointwise_1024_2048", 1024, 2048, 1, 1), ("depthwise_k9", 1024, 1024, 9, 1024),
+                                         ("pointwise_1024_1024", 1024, 1024, 1, 1)):
+        wc = ctx.qconv_prepack(torch.randint(-127, 128, (c_out, c_in // group, 1, kw), dtype=torch.int8, device="cuda",
+                                             generator=gen), group=group)
+        xc = torch.randint(0, 256, (1, c_in, 1, t), dtype=torch.uint8, device="cuda", generator=gen)
+        sc_c = torch.rand((c_out,), device="cuda", generator=gen) * 0.009 + 0.001
+        bi_c = torch.zeros((c_out,), device="cuda")
+        pads_c = (0, kw // 2, 0, kw // 2)
+        fn_c = lambda: ctx.conv_integer_scale_bias(wc, xc, 128, 0, sc_c, bi_c, pads=pads_c)
+        fn_c()
+        kern_c = ctx.last_kernel
+        torch.cuda.synchronize()
+        gc_ = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gc_, stream=torch.cuda.current_stream()):
+            for _ in range(10):
+                fn_c()
+        conv_mod[name] = {"us": timed(torch, dist, world, gc_.replay, 10) / 10 * 1e3, "kernel": kern_c}
+        del gc_, wc, xc
+    out["int8_parakeet_conv_module"] = {"T": t, **conv_mod}
     big = ctx.mmi_prepack(torch.randint(-127, 128, (8192, 8192), dtype=torch.int8, device="cuda", generator=gen))
     xa = torch.randint(0, 256, (8192, 8192), dtype=torch.uint8, device="cuda", generator=gen)
     zp8 = torch.full((1,), 128, dtype=torch.uint8, device="cuda")

@@ -31,6 +31,9 @@ struct EpiParams {
     const int32_t *ibias;
     int y_zp;
     int y_signed;
+    // 1: the per-channel constants above belong to the ROWS of the product, not its columns (a pointwise
+    // convolution computed as filters x pixels, whose rows are the output channels)
+    int by_row;
 };
 
 __device__ __forceinline__ int32_t load_zp(const void *p, int is_signed)

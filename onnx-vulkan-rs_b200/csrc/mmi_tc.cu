@@ -227,6 +227,21 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
     // 32 accumulators at run time there, which put all of them in local memory - every int8 kernel ran
     // 8-28 % slower.)
     const bool vec4 = p.vec_ok != 0;
+    // constants that belong to this thread's row rather than to the columns (EpiParams::by_row)
+    const bool by_row = p.epi.by_row != 0;
+    float s_row = 0.0f, b_row = 0.0f;
+    int32_t ib_row = 0;
+    if (by_row && row_ok) {
+        if (p.epi.mode == EPI_SCALE) {
+            s_row = v.scale[row * p.epi.scale_step];
+            if (v.product)
+                s_row = __fmul_rn(s_row, v.product[row * p.epi.product_step]);
+            b_row = v.fbias[row * p.epi.bias_step];
+        } else if (p.epi.mode == EPI_REQUANT) {
+            s_row = p.epi.ratio[row * p.epi.ratio_step];
+            ib_row = p.epi.ibias ? p.epi.ibias[row] : 0;
+        }
+    }
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -255,7 +270,9 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
         const int32_t cs_l = col_ok ? v.colsum[col_l] : 0;
         float s_l = 0.0f, b_l = 0.0f;
         int32_t ib_l = 0;
-        if (p.epi.mode == EPI_SCALE && col_ok) {
+        if (by_row) {
+            // nothing to fetch per column
+        } else if (p.epi.mode == EPI_SCALE && col_ok) {
             s_l = v.scale[col_l * p.epi.scale_step];
             if (v.product)
                 s_l = __fmul_rn(s_l, v.product[col_l * p.epi.product_step]);
@@ -289,7 +306,8 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
             float f[32];
 #pragma unroll
             for (int j = 0; j < 32; j++) {
-                const float sj = __shfl_sync(0xffffffffu, s_l, j), bj = __shfl_sync(0xffffffffu, b_l, j);
+                const float sj = by_row ? s_row : __shfl_sync(0xffffffffu, s_l, j);
+                const float bj = by_row ? b_row : __shfl_sync(0xffffffffu, b_l, j);
                 const float z = __fadd_rn(__fmul_rn(float(int32_t(r[j])), sj), bj);
                 f[j] = relu ? fmaxf(z, 0.0f) : z;
                 if (row_ok && col0 + j < v.N) {
@@ -320,8 +338,8 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
             uint32_t q8[32];
 #pragma unroll
             for (int j = 0; j < 32; j++) {
-                const float ratio = __shfl_sync(0xffffffffu, s_l, j);
-                const int32_t acc = int32_t(r[j] + uint32_t(__shfl_sync(0xffffffffu, ib_l, j)));
+                const float ratio = by_row ? s_row : __shfl_sync(0xffffffffu, s_l, j);
+                const int32_t acc = int32_t(r[j] + uint32_t(by_row ? ib_row : __shfl_sync(0xffffffffu, ib_l, j)));
                 const float rr = rintf(__fmul_rn(float(acc), ratio));
                 int32_t qv = int32_t(uint32_t(__float2int_rn(rr)) + uint32_t(p.epi.y_zp));
                 qv = p.epi.y_signed ? max(-128, min(127, qv)) : max(0, min(255, qv));
@@ -954,6 +972,10 @@ bool wants256(const ovk_ctx *ctx, const ovk_mmi_weight *w, int64_t m)
 
 bool ovk_mmi_wants_large_tiles(const ovk_ctx *ctx, const ovk_mmi_weight *w, int64_t m) { return wants256(ctx, w, m); }
 
+int32_t ovk_mmi_tc_launch_with_row_sums(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int32_t a_signed, int64_t m,
+                                        const void *a_zp, const void *b_zp, const EpiParams &epi, void *out,
+                                        const int32_t *row_sums);
+
 // The tensor-core tiles need whole 16-byte rows of A for TMA and enough work
 // to fill a tile; everything else stays on the small-shape kernel
 // (the split the reference makes with coop_applies, shaders/matmul_integer.rs:501-512).
@@ -966,6 +988,15 @@ bool ovk_mmi_tc_applies(const ovk_ctx *ctx, const ovk_mmi_weight *w, const void 
 
 int32_t ovk_mmi_tc_launch(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int32_t a_signed, int64_t m,
                           const void *a_zp, const void *b_zp, const EpiParams &epi, void *out)
+{
+    return ovk_mmi_tc_launch_with_row_sums(ctx, w, a, a_signed, m, a_zp, b_zp, epi, out, nullptr);
+}
+
+// `row_sums`: sum over k of a[m][k] for every row, when the caller already has them (A is a constant of the
+// graph); null: they are computed here when the weight's zero point may be non-zero.
+int32_t ovk_mmi_tc_launch_with_row_sums(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int32_t a_signed, int64_t m,
+                                        const void *a_zp, const void *b_zp, const EpiParams &epi, void *out,
+                                        const int32_t *row_sums)
 {
     TcParams p = {};
     p.M = m;
@@ -981,7 +1012,9 @@ int32_t ovk_mmi_tc_launch(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, 
     p.out = out;
     p.vec_ok = (w->n % 4) == 0 && aligned_to(out, epi.mode == EPI_REQUANT ? 4 : 16);
     p.status = ctx->dev_status;
-    if (b_zp) {
+    if (b_zp && row_sums) {
+        p.rowsum = row_sums;
+    } else if (b_zp) {
         void *ws = nullptr;
         int32_t rc = ovk_scratch(ctx, size_t(m) * sizeof(int32_t), &ws);
         if (rc != OVK_OK)

@@ -18,6 +18,10 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
                             void *out, const ConvLayout &lay);
 int32_t ovk_qconv_pad_nhwc(ovk_ctx *ctx, const void *x, const ConvGeom &g, int32_t fill, uint8_t *xp);
 int32_t ovk_qconv_tc_prepare_weight(ovk_ctx *ctx, ovk_qconv_weight *w);
+bool ovk_mmi_tc_applies(const ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int64_t m);
+int32_t ovk_mmi_tc_launch_with_row_sums(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int32_t a_signed, int64_t m,
+                                        const void *a_zp, const void *b_zp, const EpiParams &epi, void *out,
+                                        const int32_t *row_sums);
 
 namespace {
 
@@ -162,6 +166,122 @@ unpad_nchw_kernel(const uint8_t *__restrict__ xp, uint8_t *__restrict__ out, int
     }
 }
 
+// One image [C][P] of bytes -> [P][C] (pixels become rows with their channels contiguous): 64 x 64 tiles
+// through shared memory, 32-bit accesses on both sides where the rows allow it.
+__global__ void __launch_bounds__(256)
+pixels_major_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ out, int C, int P, int words_ok)
+{
+    __shared__ uint8_t tile[64][68];  // [channel][pixel], rows padded against bank conflicts
+    const int c0 = blockIdx.y * 64, p0 = blockIdx.x * 64;
+    const int t = threadIdx.x;
+    for (int i = 0; i < 4; i++) {
+        const int c = c0 + (t >> 4) + 16 * i, pp = p0 + 4 * (t & 15);
+        uint32_t v = 0;
+        if (c < C) {
+            if (words_ok && pp + 4 <= P) {
+                v = *reinterpret_cast<const uint32_t *>(x + size_t(c) * P + pp);
+            } else {
+                for (int e = 0; e < 4; e++)
+                    if (pp + e < P)
+                        v |= uint32_t(x[size_t(c) * P + pp + e]) << (8 * e);
+            }
+        }
+        *reinterpret_cast<uint32_t *>(&tile[(t >> 4) + 16 * i][4 * (t & 15)]) = v;
+    }
+    __syncthreads();
+    for (int i = 0; i < 4; i++) {
+        const int pp = (t >> 4) + 16 * i, cc = 4 * (t & 15);
+        if (p0 + pp < P && c0 + cc < C) {  // C is a multiple of 16: a group of four channels exists whole
+            const uint32_t v = uint32_t(tile[cc][pp]) | (uint32_t(tile[cc + 1][pp]) << 8) | (uint32_t(tile[cc + 2][pp]) << 16) |
+                               (uint32_t(tile[cc + 3][pp]) << 24);
+            *reinterpret_cast<uint32_t *>(out + size_t(p0 + pp) * C + c0 + cc) = v;
+        }
+    }
+}
+
+// sum of a filter's weights, one warp per filter (the zero-point term of the pointwise product)
+__global__ void __launch_bounds__(256)
+filter_sums_kernel(const uint8_t *__restrict__ w, int c_out, int k, int w_signed, int32_t *__restrict__ sums)
+{
+    const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (row >= c_out)
+        return;
+    int32_t s = 0;
+    for (int i = lane; i < k; i += 32)
+        s += sx8(w[size_t(row) * k + i], w_signed);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0)
+        sums[row] = s;
+}
+
+// A pointwise convolution (1 x 1 filters, stride 1, no padding, one group) is the product
+// filters [C_out][C_in] x image [C_in][pixels]: the MatMulInteger tensor-core kernels compute it with the
+// filter bank as the row operand - its operator layout is exactly that - and the image, turned to
+// [pixels][C_in] by one small pass, in the place of the packed weight.  The result [C_out][pixels] is the
+// operator's NCHW output as it stands; the per-channel constants of the epilogue belong to the rows
+// (EpiParams::by_row).  The convolution kernel keeps a whole filter bank in shared memory and so stops at
+// 256 filters of 112 KB; the encoder's pointwise layers (1024 -> 2048 over a thousand frames) are past
+// both, and on the one-output-per-thread kernel took 6.5 ms each.
+bool pointwise_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, int32_t w_zp, const ConvLayout &lay)
+{
+    if (g.kh != 1 || g.kw != 1 || g.sh != 1 || g.sw != 1 || g.group != 1 || g.phb || g.phe || g.pwb || g.pwe)
+        return false;
+    if (lay.x_cl || lay.y_cl || w_zp != 0 || w->w_taps)  // (a bank the convolution kernel holds stays there)
+        return false;
+    ovk_mmi_weight image = {};
+    image.k = g.c_in;
+    image.n = int64_t(g.h_in) * g.w_in;
+    return ovk_mmi_tc_applies(ctx, &image, w->w, g.c_out);
+}
+
+int32_t run_pointwise(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, int32_t x_signed, const ConvGeom &g,
+                      int32_t x_zp, EpiParams epi, void *out, size_t out_elem)
+{
+    ovk_qconv_weight *w = const_cast<ovk_qconv_weight *>(wc);  // the filter sums are built at first use
+    const int64_t pixels = int64_t(g.h_in) * g.w_in;
+    if (!w->wsum) {
+        OVK_CUDA(ctx, cudaMalloc(&w->wsum, size_t(g.c_out) * sizeof(int32_t)));
+        filter_sums_kernel<<<unsigned(ceil_div64(int64_t(g.c_out) * 32, 256)), 256, 0, ctx->stream>>>(w->w, g.c_out, g.c_in,
+                                                                                                     w->w_signed, w->wsum);
+        OVK_LAUNCHED(ctx, "conv_filter_sums");
+    }
+    const size_t image_bytes = size_t(pixels) * g.c_in;
+    void *ws = nullptr;
+    int32_t rc = ovk_scratch(ctx, image_bytes + 256, &ws);
+    if (rc != OVK_OK)
+        return rc;
+    uint8_t *turned = static_cast<uint8_t *>(ws);
+    // the image's zero point where the kernels read zero points: in device memory
+    uint8_t *zp_dev = reinterpret_cast<uint8_t *>(ctx->range_slot + 40);
+    if (x_zp != 0)
+        OVK_CUDA(ctx, cudaMemsetAsync(zp_dev, x_zp & 0xff, 1, ctx->stream));
+    ovk_mmi_weight image = {};
+    image.k = g.c_in;
+    image.n = pixels;
+    image.k_pad = g.c_in;  // rows of the turned image, no padding: the bulk loads fill what lies outside with zeros
+    image.n_pad = pixels;
+    image.b_signed = x_signed ? 1 : 0;
+    image.bt = turned;
+    // column sums enter only multiplied by the filters' zero point, which is 0 here: any readable words do
+    image.colsum = reinterpret_cast<int32_t *>(turned);
+    epi.by_row = 1;
+    const int words_ok = (pixels % 4) == 0 && aligned_to(x, 4);
+    for (int img = 0; img < g.n; img++) {
+        const uint8_t *xi = static_cast<const uint8_t *>(x) + size_t(img) * g.c_in * pixels;
+        pixels_major_kernel<<<dim3(unsigned(ceil_div64(pixels, 64)), unsigned(ceil_div64(g.c_in, 64))), 256, 0, ctx->stream>>>(
+            xi, turned, g.c_in, int(pixels), words_ok);
+        OVK_LAUNCHED(ctx, "conv_pixels_major");
+        rc = ovk_mmi_tc_launch_with_row_sums(ctx, &image, w->w, w->w_signed, g.c_out, nullptr, x_zp != 0 ? zp_dev : nullptr,
+                                             epi, static_cast<uint8_t *>(out) + size_t(img) * g.c_out * pixels * out_elem,
+                                             w->wsum);
+        if (rc != OVK_OK)
+            return rc;
+    }
+    return OVK_OK;
+}
+
 int32_t run_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t x_signed,
                  const ovk_conv_params *p, int32_t x_zp, int32_t w_zp, const EpiParams &epi,
                  void *out, const char *op, const ConvLayout &lay = ConvLayout())
@@ -177,6 +297,9 @@ int32_t run_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t
         return OVK_OK;
     OVK_REQUIRE(ctx, x && out, "%s: x or the output is null", op);
     OVK_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (pointwise_applies(ctx, w, g, w_zp, lay))
+        return run_pointwise(ctx, w, x, x_signed, g, x_zp, epi, out,
+                             epi.mode == EPI_REQUANT ? sizeof(uint8_t) : sizeof(int32_t));
     if (ovk_qconv_tc_applies(ctx, w, g, x)) {
         const int32_t rc_tc = ovk_qconv_tc_launch(ctx, w, x, x_signed, g, x_zp, w_zp, epi, out, lay);
         if (rc_tc != OVK_UNSUPPORTED)  // an asymmetric weight or no room for the stages: the direct kernel runs

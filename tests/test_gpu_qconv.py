@@ -213,6 +213,48 @@ def test_conv_integer_scale_bias_is_bit_identical_to_the_four_nodes(c_in, c_out,
     assert np.array_equal(host(got).view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("c_in,c_out,hw,batch,xs", [(256, 320, (1, 1000), 1, False), (128, 272, (20, 50), 2, True),
+                                                    (96, 300, (7, 33), 1, False), (1024, 2048, (1, 1000), 1, False)])
+def test_pointwise_convolution_takes_the_matmul_kernels(c_in, c_out, hw, batch, xs):
+    """A 1 x 1, stride-1, unpadded convolution with more filters than the convolution kernel holds in shared
+    memory (the encoder's pointwise layers, 1024 -> 2048 over a thousand frames) is the product filters x image
+    on the MatMulInteger tensor-core kernels, the image turned to pixels-major first and the per-channel
+    constants applied by row.  int32 accumulators, the fused scale and bias (per channel, with Relu and the range
+    fold) and the requantised bytes all equal the CPU port bit for bit; pixel counts that are no multiple of
+    four (7 x 33) take the register stores and byte loads."""
+    import torch
+    big = c_in * c_out * hw[0] * hw[1] > 5e8  # the largest case: sampled channels only on the CPU
+    rng = np.random.default_rng(c_in + c_out)
+    x = rng.integers(0, 256, size=(batch, c_in, *hw), dtype=np.uint8)
+    wt = rng.integers(-127, 128, size=(c_out, c_in, 1, 1), dtype=np.int8)
+    x = x.view(np.int8) if xs else x
+    x_zp = -5 if xs else 131
+    wq = ctx().qconv_prepack(dev(wt))
+    got = ctx().conv_integer(wq, dev(x), x_zp, 0)
+    assert ctx().last_kernel.startswith("mmi_tc"), ctx().last_kernel
+    rows = np.arange(0, c_out, 97) if big else np.arange(c_out)
+    want = orc.conv_integer(x, wt[rows], x_zp, 0)
+    assert np.array_equal(host(got)[:, rows], want)
+    scale = rng.uniform(1e-5, 1e-4, c_out).astype(np.float32)
+    bias = rng.uniform(-0.5, 0.5, c_out).astype(np.float32)
+    for relu in (False, True):
+        slot = torch.zeros(2, dtype=torch.int32, device="cuda")
+        f = ctx().conv_integer_scale_bias(wq, dev(x), x_zp, 0, dev(scale), dev(bias), relu=relu, range_slot=slot)
+        assert ctx().last_kernel.startswith("mmi_tc"), ctx().last_kernel
+        want_f = _fused_oracle(want, scale[rows], bias[rows], relu=relu)
+        assert np.array_equal(host(f)[:, rows].view(np.uint32), want_f.view(np.uint32))
+        if not big:
+            lo_hi = host(slot).view(np.float32)
+            assert lo_hi[0] == max(-want_f.min(), 0.0) and lo_hi[1] == max(want_f.max(), 0.0)
+    w_scale = rng.uniform(0.001, 0.01, size=c_out).astype(np.float32)
+    ibias = rng.integers(-1000, 1001, size=c_out, dtype=np.int32)
+    ratio = orc.requantize_ratio(0.02, w_scale, 0.9)
+    q = ctx().qlinear_conv(wq, dev(x), x_zp, 0, ratio, dev(ibias), 3)
+    assert ctx().last_kernel.startswith("mmi_tc"), ctx().last_kernel
+    want_q = orc.requantize(want, hw[0] * hw[1], ratio[rows], 3, bias=ibias[rows])
+    assert np.array_equal(host(q)[:, rows], want_q)
+
+
 def test_conv_integer_scale_bias_relu_range_and_batch():
     """Relu and the range slot of the DynamicQuantizeLinear that follows, batch 3, on both kernels."""
     import torch
