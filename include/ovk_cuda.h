@@ -409,8 +409,8 @@ OVK_API int32_t ovk_qlinear_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const 
  *    {top, left, bottom, right}; only its interior is written; C_out must be a
  *    multiple of 16.
  * Either layout may be OVK_LAYOUT_NCHW (then this is ovk_qlinear_conv).  Taken
- * by the stride-1, group-1, symmetric-weight kernel; other geometries are
- * refused with OVK_UNSUPPORTED in a channels-last layout.  Same bytes as
+ * by the group-1, symmetric-weight tensor-core kernel (strides up to 4);
+ * other geometries are refused with OVK_UNSUPPORTED in a channels-last layout.  Same bytes as
  * ovk_qlinear_conv. */
 #define OVK_LAYOUT_NCHW 0
 #define OVK_LAYOUT_PADDED_NHWC 1

@@ -224,11 +224,16 @@ filter_sums_kernel(const uint8_t *__restrict__ w, int c_out, int k, int w_signed
 // (EpiParams::by_row).  The convolution kernel keeps a whole filter bank in shared memory and so stops at
 // 256 filters of 112 KB; the encoder's pointwise layers (1024 -> 2048 over a thousand frames) are past
 // both, and on the one-output-per-thread kernel took 6.5 ms each.
+#ifndef OVK_POINTWISE_MAX_IMAGES
+#define OVK_POINTWISE_MAX_IMAGES 4
+#endif
 bool pointwise_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, int32_t w_zp, const ConvLayout &lay)
 {
     if (g.kh != 1 || g.kw != 1 || g.sh != 1 || g.sw != 1 || g.group != 1 || g.phb || g.phe || g.pwb || g.pwe)
         return false;
-    if (lay.x_cl || lay.y_cl || w_zp != 0 || w->w_taps)  // (a bank the convolution kernel holds stays there)
+    // (a bank the convolution kernel holds in shared memory at once stays there, and so does a batch of
+    // images: the product below is one launch pair per image)
+    if (lay.x_cl || lay.y_cl || w_zp != 0 || w->whole_bank || g.n > OVK_POINTWISE_MAX_IMAGES)
         return false;
     ovk_mmi_weight image = {};
     image.k = g.c_in;
@@ -307,7 +312,7 @@ int32_t run_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t
     }
     // the direct kernel reads and writes the operator's layout only
     OVK_REFUSE(ctx, lay.x_cl || lay.y_cl,
-               "%s: the channels-last layout is taken by the stride-1, group-1, symmetric-weight tensor-core kernel only", op);
+               "%s: the channels-last layout is taken by the group-1, symmetric-weight tensor-core kernel (strides up to 4) only", op);
     conv_direct_kernel<<<unsigned(ceil_div64(total, 256)), 256, 0, ctx->stream>>>(
         static_cast<const uint8_t *>(x), w->w, g, x_signed, w->w_signed, x_zp, w_zp, epi, out, total);
     OVK_LAUNCHED(ctx, "conv_direct");

@@ -1,5 +1,8 @@
-// ConvInteger / QLinearConv on tcgen05 kind::i8: a stride-1, group-1
-// convolution as a sum of SHIFTED GEMMs over a padded channels-last image.
+// ConvInteger / QLinearConv on tcgen05 kind::i8: a group-1 convolution as a sum
+// of SHIFTED GEMMs over a padded channels-last image.  Strides (up to 4) are taken
+// by forming the products at every position and storing those on the stride
+// lattice; a filter bank too large for shared memory by several launches of as
+// many filters as fit.
 //
 // The reference takes this shape (batch > 1) through its blocked implicit-GEMM
 // ladder with split-K and a separate REQUANTIZE pass
@@ -39,7 +42,12 @@ constexpr size_t W_SMEM_MAX = 112 * 1024;
 struct ConvTcParams {
     int64_t v_total;   // N * HP * WP
     int hpwp, wp;      // padded plane and row
-    int h_out, w_out, c_out, co_pad;
+    int h_out, w_out, c_out, co_pad;  // c_out / co_pad: the filters of THIS launch (a bank too large for shared
+                                      // memory is taken in several launches of as many filters as fit)
+    int c_out_total;                  // channels of the output tensor
+    int sh, sw;                       // strides: the products are computed at every position of the padded grid and
+                                      // only the positions on the stride lattice are stored (2 x 2: a quarter)
+    int w_tap_rows;                   // rows between two taps in the packed filter bank (all filters, padded)
     int taps, kw, dh, dw;
     int kch;           // bytes of K per slice (min(C_in, 128))
     int chunks;        // C_in / kch
@@ -171,7 +179,7 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
             umma::mbar_expect_tx(w_full, uint32_t(slices) * uint32_t(p.co_pad) * uint32_t(p.kch));
             for (int sl = 0; sl < slices; sl++) {
                 const int tap = sl / p.chunks, ch = sl % p.chunks;
-                umma::tma_load_2d(sWt + size_t(sl) * p.w_slice, &tmW, w_full, ch * p.kch, tap * p.co_pad);
+                umma::tma_load_2d(sWt + size_t(sl) * p.w_slice, &tmW, w_full, ch * p.kch, tap * p.w_tap_rows);
             }
             // launched with programmatic stream serialization: everything above ran while the layout
             // pass was still draining; its output is read from here on
@@ -335,10 +343,17 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
             const uint32_t v = uint32_t(tile) * BM + q * 32 + lane;
             const uint32_t img = p.magic_hpwp ? uint32_t(__umul64hi(uint64_t(v), p.magic_hpwp)) : v;
             const uint32_t rem = v - img * uint32_t(p.hpwp);
-            const uint32_t oh = p.magic_wp ? uint32_t(__umul64hi(uint64_t(rem), p.magic_wp)) : rem;
-            const uint32_t ow = rem - oh * uint32_t(p.wp);
-            const bool valid = ok && int64_t(v) < p.v_total && int(oh) < p.h_out && int(ow) < p.w_out;
-            const int64_t o_base = int64_t(img) * p.c_out * plane + int64_t(oh) * p.w_out + ow;
+            uint32_t oh = p.magic_wp ? uint32_t(__umul64hi(uint64_t(rem), p.magic_wp)) : rem;
+            uint32_t ow = rem - oh * uint32_t(p.wp);
+            bool on_lattice = true;
+            if (p.sh != 1 || p.sw != 1) {
+                const uint32_t qh = oh / uint32_t(p.sh), qw = ow / uint32_t(p.sw);
+                on_lattice = qh * uint32_t(p.sh) == oh && qw * uint32_t(p.sw) == ow;
+                oh = qh;
+                ow = qw;
+            }
+            const bool valid = ok && on_lattice && int64_t(v) < p.v_total && int(oh) < p.h_out && int(ow) < p.w_out;
+            const int64_t o_base = int64_t(img) * p.c_out_total * plane + int64_t(oh) * p.w_out + ow;
             // this warp's last column group: after reading it the accumulator is handed back
             int last_c0 = -1;
             for (int c0 = cs * 16; c0 < p.co_pad; c0 += CS * 16)
@@ -414,7 +429,7 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                     }
                     uint8_t *o = static_cast<uint8_t *>(p.out) +
                                  ((int64_t(img) * p.y_hpwp + int64_t(int(oh) + p.y_pt) * p.y_wp + (int(ow) + p.y_pl)) *
-                                      p.c_out + c0);
+                                      p.c_out_total + c0);
                     if (nch > 0)  // C_out is a multiple of 16 here: a group exists whole or not at all
                         *reinterpret_cast<uint4 *>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 } else {
@@ -644,11 +659,13 @@ conv_pack_w_kernel(const uint8_t *__restrict__ w, uint8_t *__restrict__ wt, int3
 int32_t ovk_qconv_tc_prepare_weight(ovk_ctx *ctx, ovk_qconv_weight *w)
 {
     const int64_t c_in = w->cig, taps = w->kh * w->kw;
-    if (w->group != 1 || (c_in != 32 && c_in != 64 && c_in % 128 != 0) || w->c_out > 256 || taps > 64)
+    if (w->group != 1 || (c_in != 32 && c_in != 64 && c_in % 128 != 0) || taps > 64)
         return OVK_OK;  // the direct kernel takes these
     const int64_t co_pad = ceil_div64(w->c_out, 32) * 32;
-    if (size_t(taps) * co_pad * c_in > W_SMEM_MAX)
+    // at least 32 filters at a time must fit beside two pixel stages (a launch takes as many as fit)
+    if (size_t(taps) * 32 * c_in > W_SMEM_MAX + 48 * 1024)
         return OVK_OK;
+    w->whole_bank = w->c_out <= 256 && size_t(taps) * co_pad * c_in <= W_SMEM_MAX;
     OVK_CUDA(ctx, cudaMalloc(&w->w_taps, size_t(taps) * co_pad * c_in));
     OVK_CUDA(ctx, cudaMalloc(&w->wsum, size_t(co_pad) * sizeof(int32_t)));
     conv_pack_w_kernel<<<unsigned(co_pad), 256, 0, ctx->stream>>>(w->w, w->w_taps, w->wsum, int(w->c_out), int(co_pad),
@@ -658,13 +675,13 @@ int32_t ovk_qconv_tc_prepare_weight(ovk_ctx *ctx, ovk_qconv_weight *w)
     return OVK_OK;
 }
 
-// Stride 1, group 1, a filter bank that fits in shared memory, symmetric
-// weights (w_zp = 0 is checked at launch); everything else takes the direct kernel.
+// One group, channel counts the K slices take, strides up to 4 (computed at every position, stored on the
+// stride lattice), symmetric weights (w_zp = 0 is checked at launch); everything else takes the direct kernel.
 bool ovk_qconv_tc_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, const void *x)
 {
     (void)ctx;
     (void)x;
-    if (!w->w_taps || g.sh != 1 || g.sw != 1 || g.group != 1)
+    if (!w->w_taps || g.group != 1 || g.sh > 4 || g.sw > 4)
         return false;
     const int64_t hp = int64_t(g.h_in) + g.phb + g.phe, wp = int64_t(g.w_in) + g.pwb + g.pwe;
     const int64_t v_total = int64_t(g.n) * hp * wp;
@@ -738,8 +755,10 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
     p.wp = WP;
     p.h_out = g.h_out;
     p.w_out = g.w_out;
-    p.c_out = g.c_out;
-    p.co_pad = int(w->c_out_pad);
+    p.c_out_total = g.c_out;
+    p.sh = g.sh;
+    p.sw = g.sw;
+    p.w_tap_rows = int(w->c_out_pad);
     p.taps = g.kh * g.kw;
     p.kw = g.kw;
     p.dh = g.dh;
@@ -753,46 +772,75 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
     p.halo = p.chunks == 1 && BM + max_off <= 256;
     p.halo_rows = p.halo ? BM + max_off : BM;
     p.a_stage = uint32_t((size_t(p.halo_rows) * p.kch + 1023) & ~size_t(1023));
-    p.w_slice = uint32_t((size_t(p.co_pad) * p.kch + 1023) & ~size_t(1023));
-    const size_t w_bytes = size_t(p.taps) * p.chunks * p.w_slice;
     const size_t epi_extra = epi.mode == EPI_SCALE ? 1024 : 0;  // the per-channel float bias
-    const size_t avail = ctx->smem_optin - w_bytes - 1024 - 2048 - 512 - epi_extra;
-    p.stages = int(std::min<size_t>(MAX_STAGES, avail / p.a_stage));
-    if (p.stages < 2)
+    const size_t fixed = 1024 + 2048 + 512 + epi_extra;
+    auto bank_bytes = [&](int filters) {
+        return size_t(p.taps) * p.chunks * ((size_t(filters) * p.kch + 1023) & ~size_t(1023));
+    };
+    // Filters per launch: the whole bank when it fits beside two pixel stages (four where that costs no extra
+    // launch), else as many multiples of 32 (at most 256, the widest MMA) as do; the launches differ only in the
+    // filters, constants and output channels they address.
+    int per_launch = std::min(256, int(w->c_out_pad));
+    while (per_launch > 32 && bank_bytes(per_launch) + 2 * p.a_stage + fixed > ctx->smem_optin)
+        per_launch -= 32;
+    if (bank_bytes(per_launch) + 2 * p.a_stage + fixed > ctx->smem_optin)
         return OVK_UNSUPPORTED;
-    // With two issuers taking alternate tiles every stage and accumulator must always come back to
-    // the same issuer (a waiter may be at most one phase behind its barrier): an even ring, one load
-    // per tile.  Otherwise one thread issues everything.
-    p.issuers = 1;
-    if (p.halo) {
-        p.stages &= ~1;
-        p.issuers = MMA_WARPS;
-    }
     p.x_signed = x_signed ? 1 : 0;
     p.w_signed = w->w_signed;
     p.x_zp = x_zp;
-    p.wsum = w->wsum;
-    p.epi = epi;
-    p.out = out;
     p.status = ctx->dev_status;
     p.m_tiles = int(ceil_div64(v_total, BM));
     p.magic_hpwp = p.hpwp > 1 ? ~uint64_t(0) / uint64_t(p.hpwp) + 1 : 0;
     p.magic_wp = p.wp > 1 ? ~uint64_t(0) / uint64_t(p.wp) + 1 : 0;
-    p.nacc = 2;
-    while (p.nacc * 2 <= MAX_ACC && p.nacc * 2 * p.co_pad <= 512)
-        p.nacc *= 2;
     const CUtensorMapSwizzle swz = p.kch == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                                 : (p.kch == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
-    CUtensorMap tmX, tmW;
+    CUtensorMap tmX;
     if (!ovk_make_tmap_2d(&tmX, xp, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(C), uint64_t(v_total), uint64_t(C),
-                          uint32_t(p.kch), uint32_t(p.halo_rows), swz) ||
-        !ovk_make_tmap_2d(&tmW, w->w_taps, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(C), uint64_t(p.taps) * p.co_pad,
-                          uint64_t(C), uint32_t(p.kch), uint32_t(p.co_pad), swz))
+                          uint32_t(p.kch), uint32_t(p.halo_rows), swz))
         return ovk_fail(ctx, OVK_BACKEND, "ConvInteger: cuTensorMapEncodeTiled failed");
-    const size_t smem = w_bytes + size_t(p.stages) * p.a_stage + 512 + 2048 + 512 + epi_extra;
-    OVK_CUDA(ctx, cudaFuncSetAttribute(qconv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    const unsigned grid = unsigned(std::min<int>(p.m_tiles, ctx->sm_count));
-    {
+    const size_t out_elem = epi.mode == EPI_REQUANT ? 1 : 4;
+    const int64_t plane = int64_t(g.h_out) * g.w_out;
+    for (int co0 = 0; co0 < g.c_out; co0 += per_launch) {
+        p.c_out = std::min(per_launch, g.c_out - co0);
+        p.co_pad = (p.c_out + 31) / 32 * 32;
+        p.w_slice = uint32_t((size_t(p.co_pad) * p.kch + 1023) & ~size_t(1023));
+        const size_t w_bytes = size_t(p.taps) * p.chunks * p.w_slice;
+        const size_t avail = ctx->smem_optin - w_bytes - fixed;
+        p.stages = int(std::min<size_t>(MAX_STAGES, avail / p.a_stage));
+        if (p.stages < 2)
+            return OVK_UNSUPPORTED;
+        // With two issuers taking alternate tiles every stage and accumulator must always come back to
+        // the same issuer (a waiter may be at most one phase behind its barrier): an even ring, one load
+        // per tile.  Otherwise one thread issues everything.
+        p.issuers = 1;
+        if (p.halo) {
+            p.stages &= ~1;
+            p.issuers = MMA_WARPS;
+        }
+        // this launch's filters: their sums, constants and output channels
+        p.wsum = w->wsum + co0;
+        p.epi = epi;
+        if (epi.ibias)
+            p.epi.ibias = epi.ibias + co0;
+        if (epi.ratio)
+            p.epi.ratio = epi.ratio + size_t(co0) * epi.ratio_step;
+        if (epi.scale)
+            p.epi.scale = epi.scale + size_t(co0) * epi.scale_step;
+        if (epi.product)
+            p.epi.product = epi.product + size_t(co0) * epi.product_step;
+        if (epi.fbias)
+            p.epi.fbias = epi.fbias + size_t(co0) * epi.bias_step;
+        p.out = static_cast<uint8_t *>(out) + (lay.y_cl ? size_t(co0) : size_t(co0) * plane * out_elem);
+        p.nacc = 2;
+        while (p.nacc * 2 <= MAX_ACC && p.nacc * 2 * p.co_pad <= 512)
+            p.nacc *= 2;
+        CUtensorMap tmW;
+        if (!ovk_make_tmap_2d(&tmW, w->w_taps + size_t(co0) * C, CU_TENSOR_MAP_DATA_TYPE_UINT8, uint64_t(C),
+                              uint64_t(p.taps) * w->c_out_pad - co0, uint64_t(C), uint32_t(p.kch), uint32_t(p.co_pad), swz))
+            return ovk_fail(ctx, OVK_BACKEND, "ConvInteger: cuTensorMapEncodeTiled failed");
+        const size_t smem = w_bytes + size_t(p.stages) * p.a_stage + 512 + 2048 + 512 + epi_extra;
+        OVK_CUDA(ctx, cudaFuncSetAttribute(qconv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        const unsigned grid = unsigned(std::min<int>(p.m_tiles, ctx->sm_count));
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(grid);
         cfg.blockDim = dim3(THREADS);
@@ -804,7 +852,7 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         OVK_CUDA(ctx, cudaLaunchKernelEx(&cfg, qconv_tc_kernel, tmX, tmW, p));
+        OVK_LAUNCHED(ctx, p.halo ? "qconv_tc_halo" : "qconv_tc_taps");
     }
-    OVK_LAUNCHED(ctx, p.halo ? "qconv_tc_halo" : "qconv_tc_taps");
     return OVK_OK;
 }

@@ -121,8 +121,8 @@ def test_requantize_pass_matches():
 
 def test_resnet_block_takes_the_tensor_core_kernel():
     """Which kernel ran (the role of pipeline_keys in
-    crates/onnx-vulkan-core/tests/conv_integer_im2col.rs:163-178): stride 1,
-    group 1, symmetric weights -> tcgen05; an asymmetric weight or a stride -> direct."""
+    crates/onnx-vulkan-core/tests/conv_integer_im2col.rs:163-178): group 1,
+    symmetric weights, strides up to 4 -> tcgen05; an asymmetric weight or a longer stride -> direct."""
     x, w, w_scale, bias = _resnet_block(2)
     wq = ctx().qconv_prepack(dev(w))
     ctx().conv_integer(wq, dev(x), 128, 0, pads=(1, 1, 1, 1))
@@ -130,6 +130,8 @@ def test_resnet_block_takes_the_tensor_core_kernel():
     ctx().conv_integer(wq, dev(x), 128, 5, pads=(1, 1, 1, 1))
     assert ctx().last_kernel == "conv_direct"
     ctx().conv_integer(wq, dev(x), 128, 0, pads=(1, 1, 1, 1), strides=(2, 2))
+    assert ctx().last_kernel.startswith("qconv_tc")
+    ctx().conv_integer(wq, dev(x), 128, 0, pads=(1, 1, 1, 1), strides=(5, 5))
     assert ctx().last_kernel == "conv_direct"
 
 
@@ -159,6 +161,68 @@ def test_tensor_core_geometries(c_in, c_out, h, w, k, dil, pads, xs):
     assert ctx().last_kernel.startswith("qconv_tc"), ctx().last_kernel
     want = orc.conv_integer(x, wt, x_zp, 0, dilations=(dil, dil), pads=pads)
     assert np.array_equal(host(got), want)
+
+
+@pytest.mark.parametrize("c_in,c_out,h,w,k,batch", [(128, 320, 14, 14, 3, 5), (256, 288, 9, 11, 3, 5), (128, 128, 28, 28, 3, 6),
+                                                    (256, 600, 14, 14, 1, 6), (512, 96, 7, 7, 3, 8)])
+def test_filter_banks_larger_than_shared_memory_take_several_launches(c_in, c_out, h, w, k, batch):
+    """A bank that does not fit in shared memory beside the pixel stages (3 x 3 over 128 and more channels, the
+    deeper stages of a ResNet) is taken in launches of as many filters as fit, multiples of 32 up to 256: every
+    launch addresses its own filters, sums, constants and output channels.  int32 accumulators, the fused f32 store
+    with per-channel constants and the requantised bytes (NCHW, and channels-last where C_out allows) equal the CPU
+    port; the launch count says how the bank was cut."""
+    rng = np.random.default_rng(c_in * 7 + c_out)
+    x = rng.integers(0, 256, size=(batch, c_in, h, w), dtype=np.uint8)
+    wt = rng.integers(-127, 128, size=(c_out, c_in, k, k), dtype=np.int8)
+    pads = (k // 2,) * 4
+    wq = ctx().qconv_prepack(dev(wt))
+    before = ctx().launches
+    got = ctx().conv_integer(wq, dev(x), 131, 0, pads=pads)
+    assert ctx().last_kernel.startswith("qconv_tc"), ctx().last_kernel
+    launches = ctx().launches - before - 1  # the layout pass
+    if k * k * c_in * ((c_out + 31) // 32 * 32) > 200 * 1024:
+        assert launches >= 2, launches
+    want = orc.conv_integer(x, wt, 131, 0, pads=pads)
+    assert np.array_equal(host(got), want)
+    scale = rng.uniform(1e-5, 1e-4, c_out).astype(np.float32)
+    bias = rng.uniform(-0.5, 0.5, c_out).astype(np.float32)
+    f = ctx().conv_integer_scale_bias(wq, dev(x), 131, 0, dev(scale), dev(bias), relu=True, pads=pads)
+    assert np.array_equal(host(f).view(np.uint32), _fused_oracle(want, scale, bias, relu=True).view(np.uint32))
+    w_scale = rng.uniform(0.001, 0.01, size=c_out).astype(np.float32)
+    ibias = rng.integers(-1000, 1001, size=c_out, dtype=np.int32)
+    ratio = orc.requantize_ratio(0.02, w_scale, 0.9)
+    want_q = orc.requantize(want, h * w, ratio, 3, bias=ibias)
+    q = ctx().qlinear_conv(wq, dev(x), 131, 0, ratio, dev(ibias), 3, pads=pads)
+    assert np.array_equal(host(q), want_q)
+    if c_out % 16 == 0:
+        frame = (1, 2, 0, 1)
+        out = torch.full((batch, h + frame[0] + frame[2], w + frame[1] + frame[3], c_out), 77, dtype=torch.uint8, device="cuda")
+        ctx().qlinear_conv_channels_last(wq, dev(x), 131, 0, ratio, dev(ibias), 3, out, frame, pads=pads, x_nchw=True)
+        inner = host(out)[:, frame[0]:frame[0] + h, frame[1]:frame[1] + w, :]
+        assert np.array_equal(np.moveaxis(inner, -1, 1), want_q)
+        o = host(out)
+        assert (o[:, :frame[0]] == 77).all() and (o[:, :, :frame[1]] == 77).all() and (o[:, :, frame[1] + w:] == 77).all()
+
+
+@pytest.mark.parametrize("c_in,c_out,h,w,k,strides,pads", [(64, 64, 56, 56, 3, (2, 2), (1, 1, 1, 1)), (128, 96, 29, 31, 3, (2, 1), (1, 0, 1, 2)),
+                                                           (256, 320, 28, 28, 1, (2, 2), (0, 0, 0, 0)), (32, 48, 25, 40, 5, (3, 2), (2, 2, 2, 2)),
+                                                           (64, 64, 30, 30, 3, (4, 4), (0, 0, 0, 0))])
+def test_strided_convolutions_on_the_tensor_core_kernel(c_in, c_out, h, w, k, strides, pads):
+    """Strides up to 4 (the stage transitions and downsampling layers of a ResNet): the tensor-core kernel forms the
+    products at every position of the padded grid and stores those on the stride lattice.  int32 and requantised
+    bytes against the CPU port, odd sizes, different strides along H and W, several launches of a large bank."""
+    rng = np.random.default_rng(c_in + c_out + k)
+    x = rng.integers(0, 256, size=(3, c_in, h, w), dtype=np.uint8)
+    wt = rng.integers(-127, 128, size=(c_out, c_in, k, k), dtype=np.int8)
+    wq = ctx().qconv_prepack(dev(wt))
+    got = ctx().conv_integer(wq, dev(x), 129, 0, pads=pads, strides=strides)
+    assert ctx().last_kernel.startswith("qconv_tc"), ctx().last_kernel
+    want = orc.conv_integer(x, wt, 129, 0, strides=strides, pads=pads)
+    assert host(got).shape == want.shape and np.array_equal(host(got), want)
+    ratio = orc.requantize_ratio(0.02, rng.uniform(0.001, 0.01, size=c_out).astype(np.float32), 0.9)
+    ibias = rng.integers(-1000, 1001, size=c_out, dtype=np.int32)
+    q = ctx().qlinear_conv(wq, dev(x), 129, 0, ratio, dev(ibias), 3, pads=pads, strides=strides)
+    assert np.array_equal(host(q), orc.requantize(want, want.shape[2] * want.shape[3], ratio, 3, bias=ibias))
 
 
 def _fused_layer(c_in, c_out, hw, k, x_signed, w_signed):
@@ -264,7 +328,7 @@ def test_conv_integer_scale_bias_relu_range_and_batch():
     scale = rng.uniform(1e-5, 1e-4, 40).astype(np.float32)
     bias = rng.uniform(-0.5, 0.5, 40).astype(np.float32)
     wq = ctx().qconv_prepack(dev(wt))
-    for strides, kernel in (((1, 1), "qconv_tc"), ((2, 2), "conv_direct")):
+    for strides, kernel in (((1, 1), "qconv_tc"), ((2, 2), "qconv_tc"), ((5, 5), "conv_direct")):
         for relu in (False, True):
             slot = torch.zeros(2, dtype=torch.int32, device="cuda")
             got = ctx().conv_integer_scale_bias(wq, dev(x), 128, 0, dev(scale), dev(bias), relu=relu, range_slot=slot,
@@ -358,9 +422,9 @@ def test_channels_last_signed_dilated_and_refusals():
     ctx().qlinear_conv_channels_last(wq, xp, -5, 0, ratio, None, -11, out, (1, 1, 1, 1), y_signed=True, pads=pads,
                                      dilations=(2, 2))
     assert np.array_equal(host(out)[:, 1:-1, 1:-1, :], _nhwc(want))
-    with pytest.raises(ovk_b200.OvkError) as e:  # stride 2: the direct kernel's geometry, NCHW only
+    with pytest.raises(ovk_b200.OvkError) as e:  # stride 5: the direct kernel's geometry, NCHW only
         ctx().qlinear_conv_channels_last(wq, xp, -5, 0, ratio, None, -11, out, (1, 1, 1, 1), y_signed=True, pads=pads,
-                                         strides=(2, 2))
+                                         strides=(5, 5))
     assert e.value.status == ovk_b200.UNSUPPORTED
     w40 = ctx().qconv_prepack(dev(w[:40].copy()))
     with pytest.raises(ovk_b200.OvkError) as e:  # 40 output channels are not whole 16-byte groups
