@@ -18,6 +18,8 @@ bool ovk_nbits_gemm_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int64
                             int32_t y_dtype, const void *a, const void *y);
 int32_t ovk_nbits_gemm(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int32_t a_dtype,
                        int64_t m, void *y, int32_t y_dtype);
+bool ovk_nbits_gemm_f32_applies(const ovk_ctx *ctx, const ovk_nbits_weight *w, int64_t m, const void *a, const void *y);
+int32_t ovk_nbits_gemm_f32(ovk_ctx *ctx, const ovk_nbits_weight *w, const float *a, int64_t m, void *y, int32_t y_dtype);
 bool ovk_nbits_gemm_is_per_block(const ovk_ctx *ctx, const ovk_nbits_weight *w);
 int32_t ovk_nbits_gemm_into(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a, int64_t m, void *const *y_dst,
                             int n_dst, int64_t ldy, int64_t col0, int32_t y_dtype, const OvkCommView *view, void *y_multicast);
@@ -100,6 +102,8 @@ int32_t ovk_matmul_nbits(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
         return ovk_nbits_decode(ctx, w, a, a_dtype, m, y, y_dtype);
     if (ovk_nbits_gemm_applies(ctx, w, m, a_dtype, y_dtype, a, y))
         return ovk_nbits_gemm(ctx, w, a, a_dtype, m, y, y_dtype);
+    if (a_dtype == OVK_FLOAT && ovk_nbits_gemm_f32_applies(ctx, w, m, a, y))
+        return ovk_nbits_gemm_f32(ctx, w, static_cast<const float *>(a), m, y, y_dtype);
     return ovk_nbits_rows(ctx, w, a, a_dtype, m, y, y_dtype);
 }
 

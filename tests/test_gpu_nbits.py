@@ -225,6 +225,33 @@ def test_prefill_per_block_kernel_f32_output_and_ragged_k(m, k, n, bs):
     assert_close(got, want, 1e-4, 1e-4, "prefill f32 out, ragged K")
 
 
+@pytest.mark.parametrize("k,n,bs,f32_scales", [(1152, 1024, 32, False), (512, 384, 64, True), (3584, 512, 128, False),
+                                               (1024, 200, 256, True), (2048, 2048, 32, True)])
+@pytest.mark.parametrize("m", [9, 130, 512])
+def test_prefill_with_f32_activations_takes_the_tensor_core_kernels(k, n, bs, f32_scales, m):
+    """The reference computes in f32 and its models feed f32 activations: at M > 8 every row is split into two
+    fp16 rows (hi + lo after a power-of-two normalisation, ~22 bits, as the decode kernel does), the prefill kernel
+    runs over twice the rows, and a last pass adds the pairs.  Against the CPU port at the f32 tolerance, with rows
+    of very different magnitudes, a row of zeros, and both output types."""
+    a, nib, zp, scale = cases.nbits_synthetic(17, m, k, n, bs, real=np.float32)
+    a = a.astype(np.float32)
+    a[1] *= np.float32(3.0e4)
+    a[2] *= np.float32(2.0e-6)
+    a[3] = 0.0
+    scale = scale.astype(np.float32 if f32_scales else np.float16)
+    got, kern = run_gpu(a, nib, zp, scale, k, n, bs)
+    assert kern == "nbits_join_rows", kern
+    want = orc.matmul_nbits(a, orc.pack_nibbles(nib, bs), scale, orc.pack_zero_points(zp), k, n, bs)
+    assert got.dtype == np.float32
+    # the reference's tolerance, 1e-4 * max(|want|, 1) for rows of N(0,1) activations
+    # (tests/matmul_nbits.rs:159-164), with the 1 scaled to the row: its root mean square output
+    rms = np.maximum(np.sqrt((want.astype(np.float64) ** 2).mean(axis=1, keepdims=True)), 1e-30)
+    assert np.all(np.abs(got - want) <= 1e-4 * np.maximum(np.abs(want), rms)), (np.abs(got - want) / rms).max()
+    got16, _ = run_gpu(a[4:], nib, zp, scale, k, n, bs, out_dtype=torch.float16)
+    assert got16.dtype == np.float16
+    assert_close(got16, want[4:], 2e-3, 2e-3, "f32 activations, fp16 output")
+
+
 def test_prefill_ragged_k_and_f32_activations_fall_back_to_the_general_kernel():
     a, nib, zp, scale = cases.nbits_synthetic(6, 20, 100, 48, 32, real=np.float32)
     got, kern = run_gpu(a, nib, zp, scale, 100, 48, 32)
