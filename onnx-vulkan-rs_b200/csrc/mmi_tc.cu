@@ -982,7 +982,10 @@ int32_t ovk_mmi_tc_launch_with_row_sums(ovk_ctx *ctx, const ovk_mmi_weight *w, c
 bool ovk_mmi_tc_applies(const ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int64_t m)
 {
     (void)ctx;
-    return m >= 16 && w->n >= 16 && w->k >= 32 && (w->k % 16) == 0 && aligned_to(a, 16) &&
+    // (a few rows over a large weight - an int8 decode step - stream the weight through the tensor-core kernel
+    // too: the one-output-per-thread kernel reads it at a fortieth of the memory bandwidth)
+    const bool rows_ok = m >= 16 || (m >= 1 && w->k * w->n >= (int64_t(1) << 20));
+    return rows_ok && w->n >= 16 && w->k >= 32 && (w->k % 16) == 0 && aligned_to(a, 16) &&
            m < (int64_t(1) << 31) - BM && ceil_div64(m, BM) * ceil_div64(w->n, 64) < (int64_t(1) << 31);
 }
 

@@ -28,6 +28,22 @@ def test_small_case_both_zero_points():
     assert np.array_equal(got, orc.matmul_integer(a, b, 37, 211))
 
 
+@pytest.mark.parametrize("m", [1, 3, 15])
+@pytest.mark.parametrize("a_signed,b_signed", [(False, True), (True, False)])
+def test_a_few_rows_over_a_large_weight_take_the_tensor_core_kernel(m, a_signed, b_signed):
+    """An int8 decode step (1 to 15 rows against a weight of a million elements and more) streams the weight through
+    the tensor-core kernel, whose bulk loads fill the rows of A that do not exist with zeros; both zero points, exact."""
+    k, n = 1024, 1100
+    a = cases.lcg_bytes_fast(m * k, 31).reshape(m, k)
+    b = cases.lcg_bytes_fast(k * n, 37).reshape(k, n)
+    a = a.view(np.int8) if a_signed else a
+    b = b.view(np.int8) if b_signed else b
+    azp, bzp = (-5 if a_signed else 131), (-7 if b_signed else 121)
+    got, kernel = run_mmi(a, b, azp, bzp)
+    assert kernel.startswith("mmi_tc"), kernel
+    assert np.array_equal(got, orc.matmul_integer(a, b, azp, bzp))
+
+
 @pytest.mark.parametrize("m,k,n", [(20, 64, 18), (150, 96, 90), (129, 128, 257), (300, 256, 130)])
 def test_tile_straddling_shapes(m, k, n):
     """tests/matmul_integer_variants.rs:161-244 plus shapes around the 128-wide tiles."""
