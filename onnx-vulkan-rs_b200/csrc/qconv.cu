@@ -18,6 +18,7 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
                             void *out, const ConvLayout &lay);
 int32_t ovk_qconv_pad_nhwc(ovk_ctx *ctx, const void *x, const ConvGeom &g, int32_t fill, uint8_t *xp);
 int32_t ovk_qconv_tc_prepare_weight(ovk_ctx *ctx, ovk_qconv_weight *w);
+int ovk_qconv_tc_launches(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, const void *x);
 bool ovk_mmi_tc_applies(const ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int64_t m);
 int32_t ovk_mmi_tc_launch_with_row_sums(ovk_ctx *ctx, const ovk_mmi_weight *w, const void *a, int32_t a_signed, int64_t m,
                                         const void *a_zp, const void *b_zp, const EpiParams &epi, void *out,
@@ -216,69 +217,104 @@ filter_sums_kernel(const uint8_t *__restrict__ w, int c_out, int k, int w_signed
         sums[row] = s;
 }
 
-// A pointwise convolution (1 x 1 filters, stride 1, no padding, one group) is the product
-// filters [C_out][C_in] x image [C_in][pixels]: the MatMulInteger tensor-core kernels compute it with the
-// filter bank as the row operand - its operator layout is exactly that - and the image, turned to
-// [pixels][C_in] by one small pass, in the place of the packed weight.  The result [C_out][pixels] is the
-// operator's NCHW output as it stands; the per-channel constants of the epilogue belong to the rows
-// (EpiParams::by_row).  The convolution kernel keeps a whole filter bank in shared memory and so stops at
-// 256 filters of 112 KB; the encoder's pointwise layers (1024 -> 2048 over a thousand frames) are past
-// both, and on the one-output-per-thread kernel took 6.5 ms each.
-#ifndef OVK_POINTWISE_MAX_IMAGES
-#define OVK_POINTWISE_MAX_IMAGES 4
-#endif
-bool pointwise_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, int32_t w_zp, const ConvLayout &lay)
+// One image -> its patch matrix [output pixels][C_in * KH * KW], a patch in the order the operator lays a
+// filter out (channel, then row, then column), positions in the padding holding the image's zero point so
+// that they contribute (zp - zp) * w = 0.  One byte per thread: this route is for matrices of a few MB.
+__global__ void __launch_bounds__(256)
+patches_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ out, ConvGeom g, int x_zp)
 {
-    if (g.kh != 1 || g.kw != 1 || g.sh != 1 || g.sw != 1 || g.group != 1 || g.phb || g.phe || g.pwb || g.pwe)
-        return false;
-    // (a bank the convolution kernel holds in shared memory at once stays there, and so does a batch of
-    // images: the product below is one launch pair per image)
-    if (lay.x_cl || lay.y_cl || w_zp != 0 || w->whole_bank || g.n > OVK_POINTWISE_MAX_IMAGES)
-        return false;
-    ovk_mmi_weight image = {};
-    image.k = g.c_in;
-    image.n = int64_t(g.h_in) * g.w_in;
-    return ovk_mmi_tc_applies(ctx, &image, w->w, g.c_out);
+    const int taps = g.kh * g.kw, K = g.c_in * taps;
+    const int64_t total = int64_t(g.h_out) * g.w_out * K;
+    for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
+        const int pix = int(i / K), kk = int(i - int64_t(pix) * K);
+        const int c = kk / taps, t = kk - c * taps, r = t / g.kw, s2 = t - r * g.kw;
+        const int oh = pix / g.w_out, ow = pix - oh * g.w_out;
+        const int ih = oh * g.sh - g.phb + r * g.dh, iw = ow * g.sw - g.pwb + s2 * g.dw;
+        out[i] = (ih >= 0 && ih < g.h_in && iw >= 0 && iw < g.w_in) ? x[(size_t(c) * g.h_in + ih) * g.w_in + iw] : uint8_t(x_zp);
+    }
 }
 
-int32_t run_pointwise(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, int32_t x_signed, const ConvGeom &g,
-                      int32_t x_zp, EpiParams epi, void *out, size_t out_elem)
+// A convolution as the product filters [C_out][K] x patches [K][pixels], K = C_in * KH * KW - the route the
+// reference takes at batch 1 (to_hwc + im2col + its cooperative-matrix GEMM, src/shaders/conv_integer.rs:374-527).
+// The filter bank in the operator's own layout is the row operand of the MatMulInteger tensor-core kernels;
+// the patch matrix of one image, [pixels][K], takes the place of the packed weight (a view: no copy, no
+// padding, the bulk loads zero-fill what lies outside); the result [C_out][pixels] is the NCHW output as it
+// stands, and the per-channel constants of the epilogue belong to the rows (EpiParams::by_row).  For a 1 x 1,
+// stride-1, unpadded layer the patch matrix is the image turned pixels-major.
+// Taken when the convolution kernel would need three launches or more for the filter bank (one per 32-256
+// filters that fit in shared memory) or does not take the geometry at all, for up to four images whose patch matrices stay small: the pointwise layers of
+// the dynamic-int8 encoder (1024 -> 2048 over a thousand frames: 6.5 ms on the one-output-per-thread kernel
+// they used to take) and the last stages of a ResNet at batch 1 (512 -> 512 3 x 3 on 7 x 7: 0.55 ms).
+#ifndef OVK_GEMM_ROUTE_MAX_IMAGES
+#define OVK_GEMM_ROUTE_MAX_IMAGES 4
+#endif
+constexpr int64_t GEMM_ROUTE_MAX_BYTES = int64_t(32) << 20;
+
+bool gemm_route_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, int32_t w_zp, const ConvLayout &lay,
+                        const void *x)
+{
+    if (g.group != 1 || lay.x_cl || lay.y_cl || w_zp != 0 || g.n > OVK_GEMM_ROUTE_MAX_IMAGES)
+        return false;
+    // the convolution kernel in one launch - two for filters larger than 1 x 1 - is the faster way
+    // (128 -> 128 3 x 3 on 28 x 28: 12 against 21 us; 1024 -> 256 1 x 1 on 14 x 14 in two launches: 33 against 15 us)
+    const int conv_launches = ovk_qconv_tc_launches(ctx, w, g, x);
+    if (conv_launches == 1 || (conv_launches == 2 && g.kh * g.kw > 1))
+        return false;
+    const int64_t K = int64_t(g.c_in) * g.kh * g.kw, pixels = int64_t(g.h_out) * g.w_out;
+    if (pixels * K > GEMM_ROUTE_MAX_BYTES)
+        return false;
+    ovk_mmi_weight patches = {};
+    patches.k = K;
+    patches.n = pixels;
+    return ovk_mmi_tc_applies(ctx, &patches, w->w, g.c_out);
+}
+
+int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, int32_t x_signed, const ConvGeom &g,
+                       int32_t x_zp, EpiParams epi, void *out, size_t out_elem)
 {
     ovk_qconv_weight *w = const_cast<ovk_qconv_weight *>(wc);  // the filter sums are built at first use
-    const int64_t pixels = int64_t(g.h_in) * g.w_in;
+    const int K = g.c_in * g.kh * g.kw;
+    const int64_t pixels = int64_t(g.h_out) * g.w_out;
     if (!w->wsum) {
         OVK_CUDA(ctx, cudaMalloc(&w->wsum, size_t(g.c_out) * sizeof(int32_t)));
-        filter_sums_kernel<<<unsigned(ceil_div64(int64_t(g.c_out) * 32, 256)), 256, 0, ctx->stream>>>(w->w, g.c_out, g.c_in,
+        filter_sums_kernel<<<unsigned(ceil_div64(int64_t(g.c_out) * 32, 256)), 256, 0, ctx->stream>>>(w->w, g.c_out, K,
                                                                                                      w->w_signed, w->wsum);
         OVK_LAUNCHED(ctx, "conv_filter_sums");
     }
-    const size_t image_bytes = size_t(pixels) * g.c_in;
     void *ws = nullptr;
-    int32_t rc = ovk_scratch(ctx, image_bytes + 256, &ws);
+    int32_t rc = ovk_scratch(ctx, size_t(pixels) * K + 256, &ws);
     if (rc != OVK_OK)
         return rc;
-    uint8_t *turned = static_cast<uint8_t *>(ws);
+    uint8_t *patches_dev = static_cast<uint8_t *>(ws);
     // the image's zero point where the kernels read zero points: in device memory
     uint8_t *zp_dev = reinterpret_cast<uint8_t *>(ctx->range_slot + 40);
     if (x_zp != 0)
         OVK_CUDA(ctx, cudaMemsetAsync(zp_dev, x_zp & 0xff, 1, ctx->stream));
-    ovk_mmi_weight image = {};
-    image.k = g.c_in;
-    image.n = pixels;
-    image.k_pad = g.c_in;  // rows of the turned image, no padding: the bulk loads fill what lies outside with zeros
-    image.n_pad = pixels;
-    image.b_signed = x_signed ? 1 : 0;
-    image.bt = turned;
+    ovk_mmi_weight patches = {};
+    patches.k = K;
+    patches.n = pixels;
+    patches.k_pad = K;
+    patches.n_pad = pixels;
+    patches.b_signed = x_signed ? 1 : 0;
+    patches.bt = patches_dev;
     // column sums enter only multiplied by the filters' zero point, which is 0 here: any readable words do
-    image.colsum = reinterpret_cast<int32_t *>(turned);
+    patches.colsum = reinterpret_cast<int32_t *>(patches_dev);
     epi.by_row = 1;
-    const int words_ok = (pixels % 4) == 0 && aligned_to(x, 4);
+    const bool turn_only = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && !g.phb && !g.phe && !g.pwb && !g.pwe;
+    const int64_t in_pixels = int64_t(g.h_in) * g.w_in;
+    const int words_ok = (in_pixels % 4) == 0 && aligned_to(x, 4);
     for (int img = 0; img < g.n; img++) {
-        const uint8_t *xi = static_cast<const uint8_t *>(x) + size_t(img) * g.c_in * pixels;
-        pixels_major_kernel<<<dim3(unsigned(ceil_div64(pixels, 64)), unsigned(ceil_div64(g.c_in, 64))), 256, 0, ctx->stream>>>(
-            xi, turned, g.c_in, int(pixels), words_ok);
-        OVK_LAUNCHED(ctx, "conv_pixels_major");
-        rc = ovk_mmi_tc_launch_with_row_sums(ctx, &image, w->w, w->w_signed, g.c_out, nullptr, x_zp != 0 ? zp_dev : nullptr,
+        const uint8_t *xi = static_cast<const uint8_t *>(x) + size_t(img) * g.c_in * in_pixels;
+        if (turn_only) {
+            pixels_major_kernel<<<dim3(unsigned(ceil_div64(pixels, 64)), unsigned(ceil_div64(g.c_in, 64))), 256, 0, ctx->stream>>>(
+                xi, patches_dev, g.c_in, int(pixels), words_ok);
+            OVK_LAUNCHED(ctx, "conv_pixels_major");
+        } else {
+            const unsigned blocks = unsigned(std::min<int64_t>(ceil_div64(pixels * K, 256), int64_t(ctx->sm_count) * 32));
+            patches_kernel<<<blocks, 256, 0, ctx->stream>>>(xi, patches_dev, g, x_zp);
+            OVK_LAUNCHED(ctx, "conv_patches");
+        }
+        rc = ovk_mmi_tc_launch_with_row_sums(ctx, &patches, w->w, w->w_signed, g.c_out, nullptr, x_zp != 0 ? zp_dev : nullptr,
                                              epi, static_cast<uint8_t *>(out) + size_t(img) * g.c_out * pixels * out_elem,
                                              w->wsum);
         if (rc != OVK_OK)
@@ -302,9 +338,9 @@ int32_t run_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t
         return OVK_OK;
     OVK_REQUIRE(ctx, x && out, "%s: x or the output is null", op);
     OVK_CUDA(ctx, cudaSetDevice(ctx->device));
-    if (pointwise_applies(ctx, w, g, w_zp, lay))
-        return run_pointwise(ctx, w, x, x_signed, g, x_zp, epi, out,
-                             epi.mode == EPI_REQUANT ? sizeof(uint8_t) : sizeof(int32_t));
+    if (gemm_route_applies(ctx, w, g, w_zp, lay, x))
+        return run_gemm_route(ctx, w, x, x_signed, g, x_zp, epi, out,
+                              epi.mode == EPI_REQUANT ? sizeof(uint8_t) : sizeof(int32_t));
     if (ovk_qconv_tc_applies(ctx, w, g, x)) {
         const int32_t rc_tc = ovk_qconv_tc_launch(ctx, w, x, x_signed, g, x_zp, w_zp, epi, out, lay);
         if (rc_tc != OVK_UNSUPPORTED)  // an asymmetric weight or no room for the stages: the direct kernel runs

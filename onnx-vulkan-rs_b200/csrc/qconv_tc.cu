@@ -685,7 +685,29 @@ bool ovk_qconv_tc_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const C
         return false;
     const int64_t hp = int64_t(g.h_in) + g.phb + g.phe, wp = int64_t(g.w_in) + g.pwb + g.pwe;
     const int64_t v_total = int64_t(g.n) * hp * wp;
-    return v_total >= 4 * BM && v_total < (int64_t(1) << 31) - 65536 && (wp * g.c_in) % 4 == 0;
+    // (small images too: a 7 x 7 plane is one tile, and even one launch per 32 filters beats one thread per output)
+    return v_total >= 1 && v_total < (int64_t(1) << 31) - 65536 && (wp * g.c_in) % 4 == 0;
+}
+
+// How many launches ovk_qconv_tc_launch would need for this geometry (the filter bank taken in slices that fit
+// in shared memory beside two pixel stages), 0 when the kernel does not take it at all.
+int ovk_qconv_tc_launches(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, const void *x)
+{
+    if (!ovk_qconv_tc_applies(ctx, w, g, x))
+        return 0;
+    const int C = g.c_in, kch = std::min(C, 128), chunks = C / kch, taps = g.kh * g.kw;
+    const int WP = g.w_in + g.pwb + g.pwe;
+    const int max_off = (g.kh - 1) * g.dh * WP + (g.kw - 1) * g.dw;
+    const bool halo = chunks == 1 && BM + max_off <= 256;
+    const size_t a_stage = (size_t(halo ? BM + max_off : BM) * kch + 1023) & ~size_t(1023);
+    const size_t fixed = 1024 + 2048 + 512 + 1024;
+    auto bank_bytes = [&](int filters) { return size_t(taps) * chunks * ((size_t(filters) * kch + 1023) & ~size_t(1023)); };
+    int per_launch = std::min(256, int(w->c_out_pad));
+    while (per_launch > 32 && bank_bytes(per_launch) + 2 * a_stage + fixed > ctx->smem_optin)
+        per_launch -= 32;
+    if (bank_bytes(per_launch) + 2 * a_stage + fixed > ctx->smem_optin)
+        return 0;
+    return int(ceil_div64(g.c_out, per_launch));
 }
 
 // NCHW x -> xp[n][h + frame][w + frame][c] with the frame set to `fill` (the layout pass of the

@@ -132,6 +132,9 @@ def test_resnet_block_takes_the_tensor_core_kernel():
     ctx().conv_integer(wq, dev(x), 128, 0, pads=(1, 1, 1, 1), strides=(2, 2))
     assert ctx().last_kernel.startswith("qconv_tc")
     ctx().conv_integer(wq, dev(x), 128, 0, pads=(1, 1, 1, 1), strides=(5, 5))
+    assert ctx().last_kernel.startswith("mmi_tc")  # two images: filters x patches on the MatMulInteger kernels
+    x9, _, _, _ = _resnet_block(9)
+    ctx().conv_integer(wq, dev(x9), 128, 0, pads=(1, 1, 1, 1), strides=(5, 5))
     assert ctx().last_kernel == "conv_direct"
 
 
@@ -216,12 +219,62 @@ def test_strided_convolutions_on_the_tensor_core_kernel(c_in, c_out, h, w, k, st
     wt = rng.integers(-127, 128, size=(c_out, c_in, k, k), dtype=np.int8)
     wq = ctx().qconv_prepack(dev(wt))
     got = ctx().conv_integer(wq, dev(x), 129, 0, pads=pads, strides=strides)
-    assert ctx().last_kernel.startswith("qconv_tc"), ctx().last_kernel
+    assert ctx().last_kernel.startswith(("qconv_tc", "mmi_tc")), ctx().last_kernel
     want = orc.conv_integer(x, wt, 129, 0, strides=strides, pads=pads)
     assert host(got).shape == want.shape and np.array_equal(host(got), want)
     ratio = orc.requantize_ratio(0.02, rng.uniform(0.001, 0.01, size=c_out).astype(np.float32), 0.9)
     ibias = rng.integers(-1000, 1001, size=c_out, dtype=np.int32)
     q = ctx().qlinear_conv(wq, dev(x), 129, 0, ratio, dev(ibias), 3, pads=pads, strides=strides)
+    assert np.array_equal(host(q), orc.requantize(want, want.shape[2] * want.shape[3], ratio, 3, bias=ibias))
+
+
+@pytest.mark.parametrize("c_in,c_out,hw,k,batch", [(256, 256, 14, 3, 1), (512, 512, 7, 3, 1), (2048, 512, 7, 1, 8), (64, 64, 5, 3, 1),
+                                                   (32, 32, 1, 1, 1), (128, 40, 3, 3, 2)])
+def test_small_images_stay_on_the_tensor_core_kernel(c_in, c_out, hw, k, batch):
+    """The last stages of a ResNet at batch 1 (14 x 14 and 7 x 7 planes: one or two pixel tiles, banks of up to
+    2.4 MB in launches of 32-256 filters), down to a single pixel: int32 and requantised bytes against the CPU port."""
+    rng = np.random.default_rng(c_in + c_out + hw)
+    x = rng.integers(0, 256, size=(batch, c_in, hw, hw), dtype=np.uint8)
+    wt = rng.integers(-127, 128, size=(c_out, c_in, k, k), dtype=np.int8)
+    pads = (k // 2,) * 4
+    wq = ctx().qconv_prepack(dev(wt))
+    got = ctx().conv_integer(wq, dev(x), 131, 0, pads=pads)
+    assert ctx().last_kernel.startswith(("qconv_tc", "mmi_tc")), ctx().last_kernel
+    want = orc.conv_integer(x, wt, 131, 0, pads=pads)
+    assert np.array_equal(host(got), want)
+    ratio = orc.requantize_ratio(0.02, rng.uniform(0.001, 0.01, size=c_out).astype(np.float32), 0.9)
+    ibias = rng.integers(-1000, 1001, size=c_out, dtype=np.int32)
+    q = ctx().qlinear_conv(wq, dev(x), 131, 0, ratio, dev(ibias), 3, pads=pads)
+    assert np.array_equal(host(q), orc.requantize(want, hw * hw, ratio, 3, bias=ibias))
+
+
+@pytest.mark.parametrize("c_in,c_out,h,w,k,strides,dil,pads,batch", [
+    (80, 80, 40, 40, 3, (1, 1), 1, (1, 1, 1, 1), 2),       # a channel count the convolution kernel does not take
+    (96, 300, 17, 23, 3, (2, 2), 1, (1, 1, 1, 1), 1),      # strided, odd sizes
+    (48, 272, 20, 20, 3, (1, 2), 2, (2, 1, 2, 3), 3),      # dilated, uneven pads, different strides
+    (512, 512, 7, 7, 3, (1, 1), 1, (1, 1, 1, 1), 1),       # the last stage of a ResNet, one image
+    (16, 64, 30, 30, 5, (3, 3), 1, (2, 2, 2, 2), 4),
+])
+def test_convolution_as_filters_times_patches(c_in, c_out, h, w, k, strides, dil, pads, batch):
+    """Up to four images whose filter bank the convolution kernel cannot hold at once: the patch matrix of an image
+    (any stride, dilation and padding; padding positions hold the zero point) times the filter bank on the
+    MatMulInteger tensor-core kernels, constants by row.  All three stores against the CPU port."""
+    rng = np.random.default_rng(c_in * 3 + c_out + h)
+    x = rng.integers(0, 256, size=(batch, c_in, h, w), dtype=np.uint8)
+    wt = rng.integers(-127, 128, size=(c_out, c_in, k, k), dtype=np.int8)
+    wq = ctx().qconv_prepack(dev(wt))
+    kw = dict(pads=pads, strides=strides, dilations=(dil, dil))
+    got = ctx().conv_integer(wq, dev(x), 77, 0, **kw)
+    assert ctx().last_kernel.startswith("mmi_tc"), ctx().last_kernel
+    want = orc.conv_integer(x, wt, 77, 0, **kw)
+    assert host(got).shape == want.shape and np.array_equal(host(got), want)
+    scale = rng.uniform(1e-5, 1e-4, c_out).astype(np.float32)
+    bias = rng.uniform(-0.5, 0.5, c_out).astype(np.float32)
+    f = ctx().conv_integer_scale_bias(wq, dev(x), 77, 0, dev(scale), dev(bias), relu=True, **kw)
+    assert np.array_equal(host(f).view(np.uint32), _fused_oracle(want, scale, bias, relu=True).view(np.uint32))
+    ratio = orc.requantize_ratio(0.02, rng.uniform(0.001, 0.01, size=c_out).astype(np.float32), 0.9)
+    ibias = rng.integers(-1000, 1001, size=c_out, dtype=np.int32)
+    q = ctx().qlinear_conv(wq, dev(x), 77, 0, ratio, dev(ibias), 3, **kw)
     assert np.array_equal(host(q), orc.requantize(want, want.shape[2] * want.shape[3], ratio, 3, bias=ibias))
 
 
@@ -243,7 +296,7 @@ def _fused_oracle(acc, scale, bias, product=None, relu=False):
 
 
 @pytest.mark.parametrize("c_in,c_out,hw,k,stride,pad,ws,xs,per_channel_scale,kernel", [
-    (64, 40, (20, 20), 3, 1, 1, True, False, False, "conv_direct"),
+    (64, 40, (20, 20), 3, 1, 1, True, False, False, "qconv_tc"),
     (32, 24, (15, 15), 3, 2, 1, False, True, True, "conv_direct"),
     (64, 48, (24, 24), 1, 1, 0, True, False, False, "qconv_tc"),
     (64, 1, (24, 24), 1, 1, 0, True, False, False, ""),
@@ -328,7 +381,7 @@ def test_conv_integer_scale_bias_relu_range_and_batch():
     scale = rng.uniform(1e-5, 1e-4, 40).astype(np.float32)
     bias = rng.uniform(-0.5, 0.5, 40).astype(np.float32)
     wq = ctx().qconv_prepack(dev(wt))
-    for strides, kernel in (((1, 1), "qconv_tc"), ((2, 2), "qconv_tc"), ((5, 5), "conv_direct")):
+    for strides, kernel in (((1, 1), "qconv_tc"), ((2, 2), "qconv_tc"), ((5, 5), "mmi_tc")):
         for relu in (False, True):
             slot = torch.zeros(2, dtype=torch.int32, device="cuda")
             got = ctx().conv_integer_scale_bias(wq, dev(x), 128, 0, dev(scale), dev(bias), relu=relu, range_slot=slot,
