@@ -186,6 +186,7 @@ struct ovk_qconv_weight {
     uint8_t *w_taps = nullptr;  // [KH*KW, C_out_pad, C_in] tap-major copy for the tensor path (group 1)
     int32_t *wsum = nullptr;    // [C_out_pad] sum of all weights of a filter (group 1)
     int64_t c_out_pad = 0;
+    uint8_t *w_rows16 = nullptr;  // [C_out][K rounded up to 16] zero-padded rows, built when K is no multiple of 16
     bool whole_bank = false;    // the tensor-core convolution kernel holds all filters in shared memory at once
     // the last requantisation ratios uploaded for this filter bank (a content-keyed
     // parameter cache, as interp::param_buffer in the reference): constants of the

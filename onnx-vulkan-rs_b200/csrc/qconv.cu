@@ -220,17 +220,33 @@ filter_sums_kernel(const uint8_t *__restrict__ w, int c_out, int k, int w_signed
 // One image -> its patch matrix [output pixels][C_in * KH * KW], a patch in the order the operator lays a
 // filter out (channel, then row, then column), positions in the padding holding the image's zero point so
 // that they contribute (zp - zp) * w = 0.  One byte per thread: this route is for matrices of a few MB.
+// (`pitch` >= K: rows padded to whole 16-byte units; the padding is written as 0 and meets zero filter bytes.)
 __global__ void __launch_bounds__(256)
-patches_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ out, ConvGeom g, int x_zp)
+patches_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ out, ConvGeom g, int x_zp, int pitch)
 {
     const int taps = g.kh * g.kw, K = g.c_in * taps;
-    const int64_t total = int64_t(g.h_out) * g.w_out * K;
+    const int64_t total = int64_t(g.h_out) * g.w_out * pitch;
     for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
-        const int pix = int(i / K), kk = int(i - int64_t(pix) * K);
+        const int pix = int(i / pitch), kk = int(i - int64_t(pix) * pitch);
+        if (kk >= K) {
+            out[i] = 0;
+            continue;
+        }
         const int c = kk / taps, t = kk - c * taps, r = t / g.kw, s2 = t - r * g.kw;
         const int oh = pix / g.w_out, ow = pix - oh * g.w_out;
         const int ih = oh * g.sh - g.phb + r * g.dh, iw = ow * g.sw - g.pwb + s2 * g.dw;
         out[i] = (ih >= 0 && ih < g.h_in && iw >= 0 && iw < g.w_in) ? x[(size_t(c) * g.h_in + ih) * g.w_in + iw] : uint8_t(x_zp);
+    }
+}
+
+// filters [C_out][K] -> [C_out][pitch], the tail of every row zero (K is no multiple of 16: 7 x 7 over 3 channels)
+__global__ void __launch_bounds__(256)
+pad_filter_rows_kernel(const uint8_t *__restrict__ w, uint8_t *__restrict__ out, int c_out, int K, int pitch)
+{
+    const int64_t total = int64_t(c_out) * pitch;
+    for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
+        const int row = int(i / pitch), kk = int(i - int64_t(row) * pitch);
+        out[i] = kk < K ? w[size_t(row) * K + kk] : uint8_t(0);
     }
 }
 
@@ -253,33 +269,46 @@ constexpr int64_t GEMM_ROUTE_MAX_BYTES = int64_t(32) << 20;
 bool gemm_route_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, int32_t w_zp, const ConvLayout &lay,
                         const void *x)
 {
-    if (g.group != 1 || lay.x_cl || lay.y_cl || w_zp != 0 || g.n > OVK_GEMM_ROUTE_MAX_IMAGES)
+    if (g.group != 1 || lay.x_cl || lay.y_cl || w_zp != 0)
         return false;
     // the convolution kernel in one launch - two for filters larger than 1 x 1 - is the faster way
-    // (128 -> 128 3 x 3 on 28 x 28: 12 against 21 us; 1024 -> 256 1 x 1 on 14 x 14 in two launches: 33 against 15 us)
+    // (128 -> 128 3 x 3 on 28 x 28: 12 against 21 us; 1024 -> 256 1 x 1 on 14 x 14 in two launches: 33 against 15 us),
+    // and so it is for more than a few images, one product per image being what this route costs; where the
+    // convolution kernel does not take the geometry at all (the 7 x 7 stem over 3 channels) any batch comes here
     const int conv_launches = ovk_qconv_tc_launches(ctx, w, g, x);
-    if (conv_launches == 1 || (conv_launches == 2 && g.kh * g.kw > 1))
+    if (conv_launches == 1 || (conv_launches == 2 && g.kh * g.kw > 1) || (conv_launches > 0 && g.n > OVK_GEMM_ROUTE_MAX_IMAGES))
         return false;
-    const int64_t K = int64_t(g.c_in) * g.kh * g.kw, pixels = int64_t(g.h_out) * g.w_out;
+    const int64_t K = (int64_t(g.c_in) * g.kh * g.kw + 15) / 16 * 16, pixels = int64_t(g.h_out) * g.w_out;
     if (pixels * K > GEMM_ROUTE_MAX_BYTES)
         return false;
     ovk_mmi_weight patches = {};
     patches.k = K;
     patches.n = pixels;
-    return ovk_mmi_tc_applies(ctx, &patches, w->w, g.c_out);
+    return ovk_mmi_tc_applies(ctx, &patches, w->w, g.c_out);  // (a padded copy of the filters is as well aligned)
 }
 
 int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, int32_t x_signed, const ConvGeom &g,
                        int32_t x_zp, EpiParams epi, void *out, size_t out_elem)
 {
     ovk_qconv_weight *w = const_cast<ovk_qconv_weight *>(wc);  // the filter sums are built at first use
-    const int K = g.c_in * g.kh * g.kw;
+    const int K_true = g.c_in * g.kh * g.kw;
+    const int K = (K_true + 15) / 16 * 16;  // rows of both operands in whole 16-byte units
     const int64_t pixels = int64_t(g.h_out) * g.w_out;
     if (!w->wsum) {
         OVK_CUDA(ctx, cudaMalloc(&w->wsum, size_t(g.c_out) * sizeof(int32_t)));
-        filter_sums_kernel<<<unsigned(ceil_div64(int64_t(g.c_out) * 32, 256)), 256, 0, ctx->stream>>>(w->w, g.c_out, K,
+        filter_sums_kernel<<<unsigned(ceil_div64(int64_t(g.c_out) * 32, 256)), 256, 0, ctx->stream>>>(w->w, g.c_out, K_true,
                                                                                                      w->w_signed, w->wsum);
         OVK_LAUNCHED(ctx, "conv_filter_sums");
+    }
+    const uint8_t *filters = w->w;
+    if (K != K_true) {
+        if (!w->w_rows16) {
+            OVK_CUDA(ctx, cudaMalloc(&w->w_rows16, size_t(g.c_out) * K));
+            pad_filter_rows_kernel<<<unsigned(ceil_div64(int64_t(g.c_out) * K, 256)), 256, 0, ctx->stream>>>(w->w, w->w_rows16,
+                                                                                                             g.c_out, K_true, K);
+            OVK_LAUNCHED(ctx, "conv_pad_filter_rows");
+        }
+        filters = w->w_rows16;
     }
     void *ws = nullptr;
     int32_t rc = ovk_scratch(ctx, size_t(pixels) * K + 256, &ws);
@@ -300,7 +329,7 @@ int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, 
     // column sums enter only multiplied by the filters' zero point, which is 0 here: any readable words do
     patches.colsum = reinterpret_cast<int32_t *>(patches_dev);
     epi.by_row = 1;
-    const bool turn_only = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && !g.phb && !g.phe && !g.pwb && !g.pwe;
+    const bool turn_only = K == K_true && g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && !g.phb && !g.phe && !g.pwb && !g.pwe;
     const int64_t in_pixels = int64_t(g.h_in) * g.w_in;
     const int words_ok = (in_pixels % 4) == 0 && aligned_to(x, 4);
     for (int img = 0; img < g.n; img++) {
@@ -311,10 +340,10 @@ int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, 
             OVK_LAUNCHED(ctx, "conv_pixels_major");
         } else {
             const unsigned blocks = unsigned(std::min<int64_t>(ceil_div64(pixels * K, 256), int64_t(ctx->sm_count) * 32));
-            patches_kernel<<<blocks, 256, 0, ctx->stream>>>(xi, patches_dev, g, x_zp);
+            patches_kernel<<<blocks, 256, 0, ctx->stream>>>(xi, patches_dev, g, x_zp, K);
             OVK_LAUNCHED(ctx, "conv_patches");
         }
-        rc = ovk_mmi_tc_launch_with_row_sums(ctx, &patches, w->w, w->w_signed, g.c_out, nullptr, x_zp != 0 ? zp_dev : nullptr,
+        rc = ovk_mmi_tc_launch_with_row_sums(ctx, &patches, filters, w->w_signed, g.c_out, nullptr, x_zp != 0 ? zp_dev : nullptr,
                                              epi, static_cast<uint8_t *>(out) + size_t(img) * g.c_out * pixels * out_elem,
                                              w->wsum);
         if (rc != OVK_OK)
@@ -406,6 +435,7 @@ void ovk_qconv_weight_destroy(ovk_ctx *ctx, ovk_qconv_weight *w)
     cudaFree(w->w);
     cudaFree(w->w_taps);
     cudaFree(w->wsum);
+    cudaFree(w->w_rows16);
     cudaFree(w->ratio_dev);
     delete w;
 }
