@@ -221,13 +221,18 @@ filter_sums_kernel(const uint8_t *__restrict__ w, int c_out, int k, int w_signed
 // filter out (channel, then row, then column), positions in the padding holding the image's zero point so
 // that they contribute (zp - zp) * w = 0.  One byte per thread: this route is for matrices of a few MB.
 // (`pitch` >= K: rows padded to whole 16-byte units; the padding is written as 0 and meets zero filter bytes.)
+// (`images`: that many consecutive images, their patch rows one image after the other.)
 __global__ void __launch_bounds__(256)
-patches_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ out, ConvGeom g, int x_zp, int pitch)
+patches_kernel(const uint8_t *__restrict__ x0, uint8_t *__restrict__ out, ConvGeom g, int x_zp, int pitch, int images)
 {
     const int taps = g.kh * g.kw, K = g.c_in * taps;
-    const int64_t total = int64_t(g.h_out) * g.w_out * pitch;
+    const int plane = g.h_out * g.w_out;
+    const int64_t total = int64_t(images) * plane * pitch;
     for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
-        const int pix = int(i / pitch), kk = int(i - int64_t(pix) * pitch);
+        const int64_t row = i / pitch;
+        const int kk = int(i - row * pitch);
+        const int img = int(row / plane), pix = int(row - int64_t(img) * plane);
+        const uint8_t *x = x0 + size_t(img) * g.c_in * g.h_in * g.w_in;
         if (kk >= K) {
             out[i] = 0;
             continue;
@@ -236,6 +241,20 @@ patches_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ out, ConvGeo
         const int oh = pix / g.w_out, ow = pix - oh * g.w_out;
         const int ih = oh * g.sh - g.phb + r * g.dh, iw = ow * g.sw - g.pwb + s2 * g.dw;
         out[i] = (ih >= 0 && ih < g.h_in && iw >= 0 && iw < g.w_in) ? x[(size_t(c) * g.h_in + ih) * g.w_in + iw] : uint8_t(x_zp);
+    }
+}
+
+// [C_out][images * plane] -> [images][C_out][plane]: the product over several images' patches back to NCHW
+template <typename T>
+__global__ void __launch_bounds__(256)
+unbatch_kernel(const T *__restrict__ d, T *__restrict__ out, int c_out, int images, int plane)
+{
+    const int64_t total = int64_t(images) * c_out * plane;
+    for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
+        const int pix = int(i % plane);
+        const int64_t t = i / plane;
+        const int co = int(t % c_out), img = int(t / c_out);
+        out[i] = d[(size_t(co) * images + img) * plane + pix];
     }
 }
 
@@ -310,20 +329,24 @@ int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, 
         }
         filters = w->w_rows16;
     }
+    // Images per product: as many as keep the patch matrix under its limit.  Several images' patches are one
+    // matrix [images * pixels][K]; their product [C_out][images * pixels] is then put back image by image.
+    const int group = int(std::max<int64_t>(1, std::min<int64_t>(g.n, GEMM_ROUTE_MAX_BYTES / (pixels * K))));
+    const size_t patch_bytes = (size_t(group) * pixels * K + 255) & ~size_t(255);
+    const size_t d_bytes = group > 1 ? (size_t(g.c_out) * group * pixels * out_elem + 255) & ~size_t(255) : 0;
     void *ws = nullptr;
-    int32_t rc = ovk_scratch(ctx, size_t(pixels) * K + 256, &ws);
+    int32_t rc = ovk_scratch(ctx, patch_bytes + d_bytes + 256, &ws);
     if (rc != OVK_OK)
         return rc;
     uint8_t *patches_dev = static_cast<uint8_t *>(ws);
+    uint8_t *d_dev = patches_dev + patch_bytes;
     // the image's zero point where the kernels read zero points: in device memory
     uint8_t *zp_dev = reinterpret_cast<uint8_t *>(ctx->range_slot + 40);
     if (x_zp != 0)
         OVK_CUDA(ctx, cudaMemsetAsync(zp_dev, x_zp & 0xff, 1, ctx->stream));
     ovk_mmi_weight patches = {};
     patches.k = K;
-    patches.n = pixels;
     patches.k_pad = K;
-    patches.n_pad = pixels;
     patches.b_signed = x_signed ? 1 : 0;
     patches.bt = patches_dev;
     // column sums enter only multiplied by the filters' zero point, which is 0 here: any readable words do
@@ -332,22 +355,35 @@ int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, 
     const bool turn_only = K == K_true && g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && !g.phb && !g.phe && !g.pwb && !g.pwe;
     const int64_t in_pixels = int64_t(g.h_in) * g.w_in;
     const int words_ok = (in_pixels % 4) == 0 && aligned_to(x, 4);
-    for (int img = 0; img < g.n; img++) {
+    for (int img = 0; img < g.n; img += group) {
+        const int images = std::min(group, g.n - img);
         const uint8_t *xi = static_cast<const uint8_t *>(x) + size_t(img) * g.c_in * in_pixels;
-        if (turn_only) {
+        if (turn_only && images == 1) {
             pixels_major_kernel<<<dim3(unsigned(ceil_div64(pixels, 64)), unsigned(ceil_div64(g.c_in, 64))), 256, 0, ctx->stream>>>(
                 xi, patches_dev, g.c_in, int(pixels), words_ok);
             OVK_LAUNCHED(ctx, "conv_pixels_major");
         } else {
-            const unsigned blocks = unsigned(std::min<int64_t>(ceil_div64(pixels * K, 256), int64_t(ctx->sm_count) * 32));
-            patches_kernel<<<blocks, 256, 0, ctx->stream>>>(xi, patches_dev, g, x_zp, K);
+            const unsigned blocks = unsigned(std::min<int64_t>(ceil_div64(int64_t(images) * pixels * K, 256), int64_t(ctx->sm_count) * 32));
+            patches_kernel<<<blocks, 256, 0, ctx->stream>>>(xi, patches_dev, g, x_zp, K, images);
             OVK_LAUNCHED(ctx, "conv_patches");
         }
+        patches.n = int64_t(images) * pixels;
+        patches.n_pad = patches.n;
+        uint8_t *dst = static_cast<uint8_t *>(out) + size_t(img) * g.c_out * pixels * out_elem;
         rc = ovk_mmi_tc_launch_with_row_sums(ctx, &patches, filters, w->w_signed, g.c_out, nullptr, x_zp != 0 ? zp_dev : nullptr,
-                                             epi, static_cast<uint8_t *>(out) + size_t(img) * g.c_out * pixels * out_elem,
-                                             w->wsum);
+                                             epi, images > 1 ? d_dev : dst, w->wsum);
         if (rc != OVK_OK)
             return rc;
+        if (images > 1) {
+            const int64_t total = int64_t(images) * g.c_out * pixels;
+            const unsigned blocks = unsigned(std::min<int64_t>(ceil_div64(total, 256), int64_t(ctx->sm_count) * 32));
+            if (out_elem == 1)
+                unbatch_kernel<uint8_t><<<blocks, 256, 0, ctx->stream>>>(d_dev, dst, g.c_out, images, int(pixels));
+            else
+                unbatch_kernel<uint32_t><<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const uint32_t *>(d_dev),
+                                                                        reinterpret_cast<uint32_t *>(dst), g.c_out, images, int(pixels));
+            OVK_LAUNCHED(ctx, "conv_unbatch");
+        }
     }
     return OVK_OK;
 }

@@ -13,6 +13,8 @@ from gpu_util import ctx, dev, host
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+# last kernel of the filters x patches route: the product itself, or the pass that puts several images' results back
+GEMM_ROUTE = ("mmi_tc", "conv_unbatch")
 
 
 @pytest.mark.parametrize("c_in,c_out,h,w,stride,dil,pads,xs,ws", [
@@ -132,10 +134,10 @@ def test_resnet_block_takes_the_tensor_core_kernel():
     ctx().conv_integer(wq, dev(x), 128, 0, pads=(1, 1, 1, 1), strides=(2, 2))
     assert ctx().last_kernel.startswith("qconv_tc")
     ctx().conv_integer(wq, dev(x), 128, 0, pads=(1, 1, 1, 1), strides=(5, 5))
-    assert ctx().last_kernel.startswith("mmi_tc")  # two images: filters x patches on the MatMulInteger kernels
+    assert ctx().last_kernel.startswith(GEMM_ROUTE)  # two images: filters x patches on the MatMulInteger kernels
     x9, _, _, _ = _resnet_block(9)
     ctx().conv_integer(wq, dev(x9), 128, 0, pads=(1, 1, 1, 1), strides=(5, 5))
-    assert ctx().last_kernel.startswith("mmi_tc")  # any batch, where the convolution kernel does not take the geometry
+    assert ctx().last_kernel.startswith(GEMM_ROUTE)  # any batch, where the convolution kernel does not take the geometry
 
 
 @pytest.mark.parametrize("c_in,c_out,h,w,k,dil,pads,xs", [
@@ -219,7 +221,7 @@ def test_strided_convolutions_on_the_tensor_core_kernel(c_in, c_out, h, w, k, st
     wt = rng.integers(-127, 128, size=(c_out, c_in, k, k), dtype=np.int8)
     wq = ctx().qconv_prepack(dev(wt))
     got = ctx().conv_integer(wq, dev(x), 129, 0, pads=pads, strides=strides)
-    assert ctx().last_kernel.startswith(("qconv_tc", "mmi_tc")), ctx().last_kernel
+    assert ctx().last_kernel.startswith(("qconv_tc",) + GEMM_ROUTE), ctx().last_kernel
     want = orc.conv_integer(x, wt, 129, 0, strides=strides, pads=pads)
     assert host(got).shape == want.shape and np.array_equal(host(got), want)
     ratio = orc.requantize_ratio(0.02, rng.uniform(0.001, 0.01, size=c_out).astype(np.float32), 0.9)
@@ -239,7 +241,7 @@ def test_small_images_stay_on_the_tensor_core_kernel(c_in, c_out, hw, k, batch):
     pads = (k // 2,) * 4
     wq = ctx().qconv_prepack(dev(wt))
     got = ctx().conv_integer(wq, dev(x), 131, 0, pads=pads)
-    assert ctx().last_kernel.startswith(("qconv_tc", "mmi_tc")), ctx().last_kernel
+    assert ctx().last_kernel.startswith(("qconv_tc",) + GEMM_ROUTE), ctx().last_kernel
     want = orc.conv_integer(x, wt, 131, 0, pads=pads)
     assert np.array_equal(host(got), want)
     ratio = orc.requantize_ratio(0.02, rng.uniform(0.001, 0.01, size=c_out).astype(np.float32), 0.9)
@@ -267,7 +269,7 @@ def test_convolution_as_filters_times_patches(c_in, c_out, h, w, k, strides, dil
     wq = ctx().qconv_prepack(dev(wt))
     kw = dict(pads=pads, strides=strides, dilations=(dil, dil))
     got = ctx().conv_integer(wq, dev(x), 77, 0, **kw)
-    assert ctx().last_kernel.startswith("mmi_tc"), ctx().last_kernel
+    assert ctx().last_kernel.startswith(GEMM_ROUTE), ctx().last_kernel
     want = orc.conv_integer(x, wt, 77, 0, **kw)
     assert host(got).shape == want.shape and np.array_equal(host(got), want)
     scale = rng.uniform(1e-5, 1e-4, c_out).astype(np.float32)
@@ -350,7 +352,7 @@ def test_pointwise_convolution_takes_the_matmul_kernels(c_in, c_out, hw, batch, 
     x_zp = -5 if xs else 131
     wq = ctx().qconv_prepack(dev(wt))
     got = ctx().conv_integer(wq, dev(x), x_zp, 0)
-    assert ctx().last_kernel.startswith("mmi_tc"), ctx().last_kernel
+    assert ctx().last_kernel.startswith(GEMM_ROUTE), ctx().last_kernel
     rows = np.arange(0, c_out, 97) if big else np.arange(c_out)
     want = orc.conv_integer(x, wt[rows], x_zp, 0)
     assert np.array_equal(host(got)[:, rows], want)
@@ -359,7 +361,7 @@ def test_pointwise_convolution_takes_the_matmul_kernels(c_in, c_out, hw, batch, 
     for relu in (False, True):
         slot = torch.zeros(2, dtype=torch.int32, device="cuda")
         f = ctx().conv_integer_scale_bias(wq, dev(x), x_zp, 0, dev(scale), dev(bias), relu=relu, range_slot=slot)
-        assert ctx().last_kernel.startswith("mmi_tc"), ctx().last_kernel
+        assert ctx().last_kernel.startswith(GEMM_ROUTE), ctx().last_kernel
         want_f = _fused_oracle(want, scale[rows], bias[rows], relu=relu)
         assert np.array_equal(host(f)[:, rows].view(np.uint32), want_f.view(np.uint32))
         if not big:
@@ -369,7 +371,7 @@ def test_pointwise_convolution_takes_the_matmul_kernels(c_in, c_out, hw, batch, 
     ibias = rng.integers(-1000, 1001, size=c_out, dtype=np.int32)
     ratio = orc.requantize_ratio(0.02, w_scale, 0.9)
     q = ctx().qlinear_conv(wq, dev(x), x_zp, 0, ratio, dev(ibias), 3)
-    assert ctx().last_kernel.startswith("mmi_tc"), ctx().last_kernel
+    assert ctx().last_kernel.startswith(GEMM_ROUTE), ctx().last_kernel
     want_q = orc.requantize(want, hw[0] * hw[1], ratio[rows], 3, bias=ibias[rows])
     assert np.array_equal(host(q)[:, rows], want_q)
 
@@ -383,7 +385,7 @@ def test_conv_integer_scale_bias_relu_range_and_batch():
     scale = rng.uniform(1e-5, 1e-4, 40).astype(np.float32)
     bias = rng.uniform(-0.5, 0.5, 40).astype(np.float32)
     wq = ctx().qconv_prepack(dev(wt))
-    for strides, kernel in (((1, 1), "qconv_tc"), ((2, 2), "qconv_tc"), ((5, 5), "mmi_tc")):
+    for strides, kernel in (((1, 1), "qconv_tc"), ((2, 2), "qconv_tc"), ((5, 5), GEMM_ROUTE)):
         for relu in (False, True):
             slot = torch.zeros(2, dtype=torch.int32, device="cuda")
             got = ctx().conv_integer_scale_bias(wq, dev(x), 128, 0, dev(scale), dev(bias), relu=relu, range_slot=slot,
