@@ -244,6 +244,25 @@ patches_kernel(const uint8_t *__restrict__ x0, uint8_t *__restrict__ out, ConvGe
     }
 }
 
+// sum of every patch row (the term the filters' zero point multiplies), one warp per row
+__global__ void __launch_bounds__(256)
+patch_sums_kernel(const uint8_t *__restrict__ patches, int64_t rows, int pitch, int x_signed, int32_t *__restrict__ sums)
+{
+    const int64_t row = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows)
+        return;
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(patches + size_t(row) * pitch);  // pitch is a multiple of 16
+    int32_t s = 0;
+    for (int i = lane; i < pitch / 4; i += 32)
+        s = x_signed ? __dp4a(int(w[i]), int(0x01010101), s) : int32_t(__dp4a(w[i], 0x01010101u, uint32_t(s)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0)
+        sums[row] = s;
+}
+
 // [C_out][images * plane] -> [images][C_out][plane]: the product over several images' patches back to NCHW
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -288,13 +307,17 @@ constexpr int64_t GEMM_ROUTE_MAX_BYTES = int64_t(32) << 20;
 bool gemm_route_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, int32_t w_zp, const ConvLayout &lay,
                         const void *x)
 {
-    if (g.group != 1 || lay.x_cl || lay.y_cl || w_zp != 0)
+    if (g.group != 1 || lay.x_cl || lay.y_cl)
+        return false;
+    // (an asymmetric weight brings the term w_zp * sum of the patch; with K padded to 16-byte rows the padding
+    // would enter K * w_zp * x_zp, so that combination stays with the direct kernel)
+    if (w_zp != 0 && (g.c_in * g.kh * g.kw) % 16 != 0)
         return false;
     // the convolution kernel in one launch - two for filters larger than 1 x 1 - is the faster way
     // (128 -> 128 3 x 3 on 28 x 28: 12 against 21 us; 1024 -> 256 1 x 1 on 14 x 14 in two launches: 33 against 15 us),
     // and so it is for more than a few images, one product per image being what this route costs; where the
     // convolution kernel does not take the geometry at all (the 7 x 7 stem over 3 channels) any batch comes here
-    const int conv_launches = ovk_qconv_tc_launches(ctx, w, g, x);
+    const int conv_launches = w_zp != 0 ? 0 : ovk_qconv_tc_launches(ctx, w, g, x);  // symmetric weights only, there
     if (conv_launches == 1 || (conv_launches == 2 && g.kh * g.kw > 1) || (conv_launches > 0 && g.n > OVK_GEMM_ROUTE_MAX_IMAGES))
         return false;
     const int64_t K = (int64_t(g.c_in) * g.kh * g.kw + 15) / 16 * 16, pixels = int64_t(g.h_out) * g.w_out;
@@ -307,7 +330,7 @@ bool gemm_route_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const Con
 }
 
 int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, int32_t x_signed, const ConvGeom &g,
-                       int32_t x_zp, EpiParams epi, void *out, size_t out_elem)
+                       int32_t x_zp, int32_t w_zp, EpiParams epi, void *out, size_t out_elem)
 {
     ovk_qconv_weight *w = const_cast<ovk_qconv_weight *>(wc);  // the filter sums are built at first use
     const int K_true = g.c_in * g.kh * g.kw;
@@ -334,23 +357,27 @@ int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, 
     const int group = int(std::max<int64_t>(1, std::min<int64_t>(g.n, GEMM_ROUTE_MAX_BYTES / (pixels * K))));
     const size_t patch_bytes = (size_t(group) * pixels * K + 255) & ~size_t(255);
     const size_t d_bytes = group > 1 ? (size_t(g.c_out) * group * pixels * out_elem + 255) & ~size_t(255) : 0;
+    const size_t sums_bytes = w_zp != 0 ? (size_t(group) * pixels * sizeof(int32_t) + 255) & ~size_t(255) : 0;
     void *ws = nullptr;
-    int32_t rc = ovk_scratch(ctx, patch_bytes + d_bytes + 256, &ws);
+    int32_t rc = ovk_scratch(ctx, patch_bytes + d_bytes + sums_bytes + 256, &ws);
     if (rc != OVK_OK)
         return rc;
     uint8_t *patches_dev = static_cast<uint8_t *>(ws);
     uint8_t *d_dev = patches_dev + patch_bytes;
-    // the image's zero point where the kernels read zero points: in device memory
+    int32_t *sums_dev = reinterpret_cast<int32_t *>(d_dev + d_bytes);
+    // the zero points where the kernels read zero points: in device memory (the image's, then the filters')
     uint8_t *zp_dev = reinterpret_cast<uint8_t *>(ctx->range_slot + 40);
     if (x_zp != 0)
         OVK_CUDA(ctx, cudaMemsetAsync(zp_dev, x_zp & 0xff, 1, ctx->stream));
+    if (w_zp != 0)
+        OVK_CUDA(ctx, cudaMemsetAsync(zp_dev + 1, w_zp & 0xff, 1, ctx->stream));
     ovk_mmi_weight patches = {};
     patches.k = K;
     patches.k_pad = K;
     patches.b_signed = x_signed ? 1 : 0;
     patches.bt = patches_dev;
-    // column sums enter only multiplied by the filters' zero point, which is 0 here: any readable words do
-    patches.colsum = reinterpret_cast<int32_t *>(patches_dev);
+    // column sums enter only multiplied by the filters' zero point: when that is 0 any readable words do
+    patches.colsum = w_zp != 0 ? sums_dev : reinterpret_cast<int32_t *>(patches_dev);
     epi.by_row = 1;
     const bool turn_only = K == K_true && g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && !g.phb && !g.phe && !g.pwb && !g.pwe;
     const int64_t in_pixels = int64_t(g.h_in) * g.w_in;
@@ -369,9 +396,14 @@ int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, 
         }
         patches.n = int64_t(images) * pixels;
         patches.n_pad = patches.n;
+        if (w_zp != 0) {
+            patch_sums_kernel<<<unsigned(ceil_div64(patches.n * 32, 256)), 256, 0, ctx->stream>>>(patches_dev, patches.n, K, x_signed,
+                                                                                                  sums_dev);
+            OVK_LAUNCHED(ctx, "conv_patch_sums");
+        }
         uint8_t *dst = static_cast<uint8_t *>(out) + size_t(img) * g.c_out * pixels * out_elem;
-        rc = ovk_mmi_tc_launch_with_row_sums(ctx, &patches, filters, w->w_signed, g.c_out, nullptr, x_zp != 0 ? zp_dev : nullptr,
-                                             epi, images > 1 ? d_dev : dst, w->wsum);
+        rc = ovk_mmi_tc_launch_with_row_sums(ctx, &patches, filters, w->w_signed, g.c_out, w_zp != 0 ? zp_dev + 1 : nullptr,
+                                             x_zp != 0 ? zp_dev : nullptr, epi, images > 1 ? d_dev : dst, w->wsum);
         if (rc != OVK_OK)
             return rc;
         if (images > 1) {
@@ -404,7 +436,7 @@ int32_t run_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t
     OVK_REQUIRE(ctx, x && out, "%s: x or the output is null", op);
     OVK_CUDA(ctx, cudaSetDevice(ctx->device));
     if (gemm_route_applies(ctx, w, g, w_zp, lay, x))
-        return run_gemm_route(ctx, w, x, x_signed, g, x_zp, epi, out,
+        return run_gemm_route(ctx, w, x, x_signed, g, x_zp, w_zp, epi, out,
                               epi.mode == EPI_REQUANT ? sizeof(uint8_t) : sizeof(int32_t));
     if (ovk_qconv_tc_applies(ctx, w, g, x)) {
         const int32_t rc_tc = ovk_qconv_tc_launch(ctx, w, x, x_signed, g, x_zp, w_zp, epi, out, lay);

@@ -124,13 +124,14 @@ def test_requantize_pass_matches():
 def test_resnet_block_takes_the_tensor_core_kernel():
     """Which kernel ran (the role of pipeline_keys in
     crates/onnx-vulkan-core/tests/conv_integer_im2col.rs:163-178): group 1,
-    symmetric weights, strides up to 4 -> tcgen05; an asymmetric weight or a longer stride -> direct."""
+    symmetric weights, strides up to 4 -> the tcgen05 convolution kernel; an asymmetric weight or a longer
+    stride -> filters x patches on the tcgen05 MatMulInteger kernels."""
     x, w, w_scale, bias = _resnet_block(2)
     wq = ctx().qconv_prepack(dev(w))
     ctx().conv_integer(wq, dev(x), 128, 0, pads=(1, 1, 1, 1))
     assert ctx().last_kernel.startswith("qconv_tc")
     ctx().conv_integer(wq, dev(x), 128, 5, pads=(1, 1, 1, 1))
-    assert ctx().last_kernel == "conv_direct"
+    assert ctx().last_kernel.startswith(GEMM_ROUTE)  # an asymmetric weight: filters x patches, with the patches' sums
     ctx().conv_integer(wq, dev(x), 128, 0, pads=(1, 1, 1, 1), strides=(2, 2))
     assert ctx().last_kernel.startswith("qconv_tc")
     ctx().conv_integer(wq, dev(x), 128, 0, pads=(1, 1, 1, 1), strides=(5, 5))
@@ -301,11 +302,12 @@ def _fused_oracle(acc, scale, bias, product=None, relu=False):
 
 @pytest.mark.parametrize("c_in,c_out,hw,k,stride,pad,ws,xs,per_channel_scale,kernel", [
     (64, 40, (20, 20), 3, 1, 1, True, False, False, "qconv_tc"),
-    (32, 24, (15, 15), 3, 2, 1, False, True, True, "conv_direct"),
+    (32, 24, (15, 15), 3, 2, 1, False, True, True, "mmi_tc"),
     (64, 48, (24, 24), 1, 1, 0, True, False, False, "qconv_tc"),
     (64, 1, (24, 24), 1, 1, 0, True, False, False, ""),
     (256, 32, (88, 88), 3, 1, 1, True, False, False, "qconv_tc"),
-    (4096, 16, (10, 13), 7, 1, 3, False, False, True, "conv_direct"),
+    (4096, 16, (10, 13), 7, 1, 3, False, False, True, "mmi_tc"),
+    (24, 20, (15, 15), 3, 1, 1, False, False, True, "conv_direct"),
 ])
 def test_conv_integer_scale_bias_is_bit_identical_to_the_four_nodes(c_in, c_out, hw, k, stride, pad, ws, xs,
                                                                     per_channel_scale, kernel):
