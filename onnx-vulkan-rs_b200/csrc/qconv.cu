@@ -87,6 +87,54 @@ conv_direct_kernel(const uint8_t *__restrict__ x, const uint8_t *__restrict__ w,
         epi_fold_range(epi, fmaxf(v, 0.0f), fmaxf(-v, 0.0f));
 }
 
+// Depthwise convolution (one filter per channel, group = C_in = C_out): a block takes 256 consecutive outputs
+// of ONE plane, so the channel - and with it the filter, which goes to shared memory once, and all the
+// per-channel constants - is the block's, a thread needs one division for its row, and neighbouring threads read
+// neighbouring input bytes.  Same arithmetic and epilogue as the direct kernel.
+constexpr int DW_MAX_TAPS = 128;
+__global__ void __launch_bounds__(256)
+conv_depthwise_kernel(const uint8_t *__restrict__ x, const uint8_t *__restrict__ w, ConvGeom g, int x_signed, int w_signed,
+                      int32_t x_zp, int32_t w_zp, EpiParams epi, void *out)
+{
+    __shared__ int32_t taps[DW_MAX_TAPS];
+    const int plane_out = g.h_out * g.w_out;
+    const int pc = blockIdx.y;  // image * C + channel
+    const int c = pc % g.c_out;
+    const int ntaps = g.kh * g.kw;
+    for (int i = threadIdx.x; i < ntaps; i += 256)
+        taps[i] = sx8(w[size_t(c) * ntaps + i], w_signed) - w_zp;
+    __syncthreads();
+    const int pix = blockIdx.x * 256 + threadIdx.x;
+    float v = 0.0f;
+    if (pix < plane_out) {
+        const int oh = pix / g.w_out, ow = pix - oh * g.w_out;
+        const uint8_t *xp = x + size_t(pc) * g.h_in * g.w_in;
+        int32_t acc = 0;
+        for (int r = 0; r < g.kh; r++) {
+            const int ih = oh * g.sh - g.phb + r * g.dh;
+            if (ih < 0 || ih >= g.h_in)
+                continue;
+            for (int s2 = 0; s2 < g.kw; s2++) {
+                const int iw = ow * g.sw - g.pwb + s2 * g.dw;
+                if (iw < 0 || iw >= g.w_in)
+                    continue;
+                acc += (sx8(xp[size_t(ih) * g.w_in + iw], x_signed) - x_zp) * taps[r * g.kw + s2];
+            }
+        }
+        const size_t o = size_t(pc) * plane_out + pix;
+        if (epi.mode == EPI_RAW) {
+            static_cast<int32_t *>(out)[o] = acc;
+        } else if (epi.mode == EPI_SCALE) {
+            v = epi_scale_value(epi, c, float(acc));
+            static_cast<float *>(out)[o] = v;
+        } else {
+            static_cast<uint8_t *>(out)[o] = uint8_t(epi_requant_value(epi, c, acc));
+        }
+    }
+    if (epi.mode == EPI_SCALE)
+        epi_fold_range(epi, fmaxf(v, 0.0f), fmaxf(-v, 0.0f));
+}
+
 // REQUANTIZE on its own (shaders/qlinear.rs:28-63): four outputs per thread.
 __global__ void __launch_bounds__(256)
 requantize_kernel(const int32_t *__restrict__ acc, int64_t n, int64_t inner, int64_t axis_len,
@@ -446,6 +494,12 @@ int32_t run_conv(ovk_ctx *ctx, const ovk_qconv_weight *w, const void *x, int32_t
     // the direct kernel reads and writes the operator's layout only
     OVK_REFUSE(ctx, lay.x_cl || lay.y_cl,
                "%s: the channels-last layout is taken by the group-1, symmetric-weight tensor-core kernel (strides up to 4) only", op);
+    if (g.group == g.c_in && g.c_out == g.c_in && g.kh * g.kw <= DW_MAX_TAPS && int64_t(g.n) * g.c_out < 65536) {
+        conv_depthwise_kernel<<<dim3(unsigned(ceil_div64(int64_t(g.h_out) * g.w_out, 256)), unsigned(g.n * g.c_out)), 256, 0,
+                                ctx->stream>>>(static_cast<const uint8_t *>(x), w->w, g, x_signed, w->w_signed, x_zp, w_zp, epi, out);
+        OVK_LAUNCHED(ctx, "conv_depthwise");
+        return OVK_OK;
+    }
     conv_direct_kernel<<<unsigned(ceil_div64(total, 256)), 256, 0, ctx->stream>>>(
         static_cast<const uint8_t *>(x), w->w, g, x_signed, w->w_signed, x_zp, w_zp, epi, out, total);
     OVK_LAUNCHED(ctx, "conv_direct");

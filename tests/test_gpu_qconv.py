@@ -101,6 +101,38 @@ def test_grouped_and_depthwise(group, c_in, c_out):
     assert np.array_equal(host(got), want)
 
 
+@pytest.mark.parametrize("c,h,w,kh,kw,strides,dil,pads,batch,w_zp", [
+    (144, 28, 31, 3, 3, (2, 2), 1, (1, 1, 1, 1), 3, 0),
+    (1024, 1, 1000, 1, 9, (1, 1), 1, (0, 4, 0, 4), 1, 0),   # the encoder's depthwise layer
+    (32, 19, 17, 5, 3, (1, 2), 2, (4, 2, 4, 2), 2, 9),
+])
+def test_depthwise_convolutions_have_a_kernel_of_their_own(c, h, w, kh, kw, strides, dil, pads, batch, w_zp):
+    """One filter per channel: a block owns one plane, its filter in shared memory.  All three stores against the
+    CPU port (strides, dilation, uneven pads, an asymmetric weight)."""
+    rng = np.random.default_rng(c + h + kw)
+    x = rng.integers(0, 256, size=(batch, c, h, w), dtype=np.uint8)
+    wt = rng.integers(-127, 128, size=(c, 1, kh, kw), dtype=np.int8)
+    wq = ctx().qconv_prepack(dev(wt), group=c)
+    kwargs = dict(pads=pads, strides=strides, dilations=(dil, dil))
+    got = ctx().conv_integer(wq, dev(x), 131, w_zp, **kwargs)
+    assert ctx().last_kernel == "conv_depthwise"
+    want = orc.conv_integer(x, wt, 131, w_zp, group=c, **kwargs)
+    assert np.array_equal(host(got), want)
+    scale = rng.uniform(1e-4, 1e-3, c).astype(np.float32)
+    bias = rng.uniform(-0.5, 0.5, c).astype(np.float32)
+    slot = torch.zeros(2, dtype=torch.int32, device="cuda")
+    f = ctx().conv_integer_scale_bias(wq, dev(x), 131, w_zp, dev(scale), dev(bias), relu=True, range_slot=slot, **kwargs)
+    want_f = _fused_oracle(want, scale, bias, relu=True)
+    assert np.array_equal(host(f).view(np.uint32), want_f.view(np.uint32))
+    lo_hi = host(slot).view(np.float32)
+    assert lo_hi[0] == max(-want_f.min(), 0.0) and lo_hi[1] == max(want_f.max(), 0.0)
+    if w_zp == 0:
+        ratio = orc.requantize_ratio(0.02, rng.uniform(0.001, 0.01, size=c).astype(np.float32), 0.05)
+        ibias = rng.integers(-1000, 1001, size=c, dtype=np.int32)
+        q = ctx().qlinear_conv(wq, dev(x), 131, 0, ratio, dev(ibias), 3, **kwargs)
+        assert np.array_equal(host(q), orc.requantize(want, want.shape[2] * want.shape[3], ratio, 3, bias=ibias))
+
+
 def test_signed_output_and_one_dimensional_conv():
     x = cases.lcg_bytes_fast(3 * 8 * 40, 6).reshape(3, 8, 40, 1).view(np.int8)
     w = cases.lcg_bytes_fast(12 * 8 * 5, 8).reshape(12, 8, 5, 1).view(np.int8)
