@@ -270,25 +270,43 @@ filter_sums_kernel(const uint8_t *__restrict__ w, int c_out, int k, int w_signed
 // that they contribute (zp - zp) * w = 0.  One byte per thread: this route is for matrices of a few MB.
 // (`pitch` >= K: rows padded to whole 16-byte units; the padding is written as 0 and meets zero filter bytes.)
 // (`images`: that many consecutive images, their patch rows one image after the other.)
+// A thread builds 16 consecutive bytes of a patch row and stores them at once, stepping (channel, row, column)
+// from byte to byte instead of dividing for each.
 __global__ void __launch_bounds__(256)
 patches_kernel(const uint8_t *__restrict__ x0, uint8_t *__restrict__ out, ConvGeom g, int x_zp, int pitch, int images)
 {
     const int taps = g.kh * g.kw, K = g.c_in * taps;
     const int plane = g.h_out * g.w_out;
-    const int64_t total = int64_t(images) * plane * pitch;
+    const int chunks = pitch >> 4;  // pitch is a multiple of 16
+    const int64_t total = int64_t(images) * plane * chunks;
+    const size_t in_plane = size_t(g.h_in) * g.w_in;
     for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
-        const int64_t row = i / pitch;
-        const int kk = int(i - row * pitch);
+        const int64_t row = i / chunks;
+        const int kk0 = int(i - row * chunks) << 4;
         const int img = int(row / plane), pix = int(row - int64_t(img) * plane);
-        const uint8_t *x = x0 + size_t(img) * g.c_in * g.h_in * g.w_in;
-        if (kk >= K) {
-            out[i] = 0;
-            continue;
-        }
-        const int c = kk / taps, t = kk - c * taps, r = t / g.kw, s2 = t - r * g.kw;
         const int oh = pix / g.w_out, ow = pix - oh * g.w_out;
-        const int ih = oh * g.sh - g.phb + r * g.dh, iw = ow * g.sw - g.pwb + s2 * g.dw;
-        out[i] = (ih >= 0 && ih < g.h_in && iw >= 0 && iw < g.w_in) ? x[(size_t(c) * g.h_in + ih) * g.w_in + iw] : uint8_t(x_zp);
+        const int ih0 = oh * g.sh - g.phb, iw0 = ow * g.sw - g.pwb;
+        int c = kk0 / taps, t = kk0 - c * taps;
+        int r = t / g.kw, s2 = t - r * g.kw;
+        const uint8_t *xc = x0 + (size_t(img) * g.c_in + c) * in_plane;
+        uint32_t words[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 16; e++) {
+            uint32_t byte = 0;
+            if (kk0 + e < K) {
+                const int ih = ih0 + r * g.dh, iw = iw0 + s2 * g.dw;
+                byte = (ih >= 0 && ih < g.h_in && iw >= 0 && iw < g.w_in) ? xc[size_t(ih) * g.w_in + iw] : uint32_t(x_zp & 0xff);
+                if (++s2 == g.kw) {
+                    s2 = 0;
+                    if (++r == g.kh) {
+                        r = 0;
+                        xc += in_plane;
+                    }
+                }
+            }
+            words[e >> 2] |= byte << (8 * (e & 3));
+        }
+        *reinterpret_cast<uint4 *>(out + size_t(row) * pitch + kk0) = make_uint4(words[0], words[1], words[2], words[3]);
     }
 }
 
