@@ -384,7 +384,10 @@ bool gemm_route_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const Con
     // and so it is for more than a few images, one product per image being what this route costs; where the
     // convolution kernel does not take the geometry at all (the 7 x 7 stem over 3 channels) any batch comes here
     const int conv_launches = w_zp != 0 ? 0 : ovk_qconv_tc_launches(ctx, w, g, x);  // symmetric weights only, there
-    if (conv_launches == 1 || (conv_launches == 2 && g.kh * g.kw > 1) || (conv_launches > 0 && g.n > OVK_GEMM_ROUTE_MAX_IMAGES))
+    // (measured at 8 and 64 images: this route wins while images x output pixels stay small - 7 x 7 planes at 64
+    // images 340 -> 60 us, 14 x 14 at 8 images 56 -> 27 us - and loses beyond: 14 x 14 at 64 images 69 -> 92 us)
+    const bool few = g.n <= OVK_GEMM_ROUTE_MAX_IMAGES || int64_t(g.n) * g.h_out * g.w_out <= 3200;
+    if (conv_launches == 1 || (conv_launches == 2 && g.kh * g.kw > 1) || (conv_launches > 0 && !few))
         return false;
     const int64_t K = (int64_t(g.c_in) * g.kh * g.kw + 15) / 16 * 16, pixels = int64_t(g.h_out) * g.w_out;
     if (pixels * K > GEMM_ROUTE_MAX_BYTES)

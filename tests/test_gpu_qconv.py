@@ -201,8 +201,8 @@ def test_tensor_core_geometries(c_in, c_out, h, w, k, dil, pads, xs):
     assert np.array_equal(host(got), want)
 
 
-@pytest.mark.parametrize("c_in,c_out,h,w,k,batch", [(128, 320, 14, 14, 3, 5), (256, 288, 9, 11, 3, 5), (128, 128, 28, 28, 3, 6),
-                                                    (256, 600, 14, 14, 1, 6), (512, 96, 7, 7, 3, 8)])
+@pytest.mark.parametrize("c_in,c_out,h,w,k,batch", [(128, 320, 30, 30, 3, 5), (256, 288, 30, 31, 3, 5), (128, 128, 28, 28, 3, 6),
+                                                    (256, 600, 30, 30, 1, 6), (512, 96, 21, 21, 3, 8)])
 def test_filter_banks_larger_than_shared_memory_take_several_launches(c_in, c_out, h, w, k, batch):
     """A bank that does not fit in shared memory beside the pixel stages (3 x 3 over 128 and more channels, the
     deeper stages of a ResNet) is taken in launches of as many filters as fit, multiples of 32 up to 256: every
