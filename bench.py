@@ -486,7 +486,56 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
                                                  "note": "padded-NHWC in and out (ovk_qlinear_conv_layout): one launch per layer"},
                                              "algorithmic_gbs": 2.0 * 64 * 64 * 56 * 56 / (ms_q * 1e-3) / 1e9,
                                              "parallelism": "batch-split x%d, no exchange" % world if world > 1 else "single"}
+    if world == 1:
+        out["int8_resnet50_convolutions"] = resnet50_convolutions(torch, dist, ctx, gen)
     return out
+
+
+# (input channels, output channels, filter, stride, input height = width, how many such layers) of ResNet-50 v1.5
+RESNET50_LAYERS = [
+    (3, 64, 7, 2, 224, 1),
+    (64, 64, 1, 1, 56, 1), (64, 64, 3, 1, 56, 3), (64, 256, 1, 1, 56, 4), (256, 64, 1, 1, 56, 2),
+    (256, 128, 1, 1, 56, 1), (128, 128, 3, 2, 56, 1), (128, 512, 1, 1, 28, 4), (512, 128, 1, 1, 28, 3), (128, 128, 3, 1, 28, 3),
+    (256, 512, 1, 2, 56, 1),
+    (512, 256, 1, 1, 28, 1), (256, 256, 3, 2, 28, 1), (256, 1024, 1, 1, 14, 6), (1024, 256, 1, 1, 14, 5), (256, 256, 3, 1, 14, 5),
+    (512, 1024, 1, 2, 28, 1),
+    (1024, 512, 1, 1, 14, 1), (512, 512, 3, 2, 14, 1), (512, 2048, 1, 1, 7, 3), (2048, 512, 1, 1, 7, 2), (512, 512, 3, 1, 7, 2),
+    (1024, 2048, 1, 2, 14, 1),
+]
+
+
+def resnet50_convolutions(torch, dist, ctx, gen, batch=64):
+    """Every convolution layer of a ResNet-50 as QLinearConv (uint8 in and out, int8 symmetric per-channel weights),
+    batch 64, each shape timed from a graph replay and weighted by how often the network has it: the layers beyond
+    config 4's block - large filter banks, strides, 7 x 7 planes, the 3-channel stem."""
+    import numpy as np
+    total_us, layers, slowest = 0.0, 0, ("", 0.0)
+    kernels = {}
+    for c_in, c_out, k, stride, hw, count in RESNET50_LAYERS:
+        w = ctx.qconv_prepack(torch.randint(-127, 128, (c_out, c_in, k, k), dtype=torch.int8, device="cuda", generator=gen))
+        x = torch.randint(0, 256, (batch, c_in, hw, hw), dtype=torch.uint8, device="cuda", generator=gen)
+        bias = torch.zeros((c_out,), dtype=torch.int32, device="cuda")
+        ratio = np.full(c_out, 0.002, dtype=np.float32)
+        pad = k // 2
+        ho = (hw + 2 * pad - k) // stride + 1
+        y = torch.empty((batch, c_out, ho, ho), dtype=torch.uint8, device="cuda")
+        fn = lambda: ctx.qlinear_conv(w, x, 128, 0, ratio, bias, 128, pads=(pad,) * 4, strides=(stride, stride), out=y)
+        fn()
+        kern = ctx.last_kernel
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=torch.cuda.current_stream()):
+            for _ in range(3):
+                fn()
+        us = timed(torch, dist, 1, g.replay, 5) / 3 * 1e3
+        del g, w, x, y
+        total_us += us * count
+        layers += count
+        kernels[kern] = kernels.get(kern, 0) + count
+        if us > slowest[1]:
+            slowest = ("%d->%d %dx%d s%d on %dx%d" % (c_in, c_out, k, k, stride, hw, hw), us)
+    return {"batch": batch, "layers": layers, "ms_all_layers": total_us / 1e3, "slowest_layer": slowest[0],
+            "slowest_layer_us": slowest[1], "layers_by_last_kernel": kernels}
 
 
 def run_gpu(args):
