@@ -213,39 +213,89 @@ __device__ __forceinline__ void stage_out_drain(const OutStage &st, int lane)
         umma::tma_store_wait_all();
 }
 
+// What the epilogue fetches from global memory for one block of 32 columns - lane l those of column col0 + l.
+// None of it depends on the accumulator, so it is requested a block ahead (the first block's before the wait for
+// the accumulator): fetched where it is used, each block of every tile exposed a full memory latency to the one
+// warp of its scheduler, and a product with the Cast-Mul-Add epilogue took twice the time of the plain one.
+struct ColConsts {
+    int32_t cs;  // column sum of B (only read where A has a zero point)
+    float s, b;  // EPI_SCALE: scale [* product], bias;  EPI_REQUANT: s = ratio
+    int32_t ib;  // EPI_REQUANT: integer bias
+};
+__device__ __forceinline__ ColConsts col_consts(const TcParams &p, const ColView &v, int col_l, int32_t za)
+{
+    ColConsts c = {0, 0.0f, 0.0f, 0};
+    if (col_l >= v.N)
+        return c;
+    if (za != 0)
+        c.cs = v.colsum[col_l];
+    if (p.epi.by_row) {
+        // the constants belong to the rows
+    } else if (p.epi.mode == EPI_SCALE) {
+        c.s = v.scale[col_l * p.epi.scale_step];
+        if (v.product)
+            c.s = __fmul_rn(c.s, v.product[col_l * p.epi.product_step]);
+        c.b = v.fbias[col_l * p.epi.bias_step];
+    } else if (p.epi.mode == EPI_REQUANT) {
+        c.s = p.epi.ratio[col_l * p.epi.ratio_step];
+        c.ib = p.epi.ibias ? p.epi.ibias[col_l] : 0;
+    }
+    return c;
+}
+// ... and for the thread's row: the term of B's zero point and the constants of EpiParams::by_row
+struct RowConsts {
+    uint32_t row_term;
+    float s, b;
+    int32_t ib;
+};
+__device__ __forceinline__ RowConsts row_consts(const TcParams &p, const ColView &v, int64_t row, int32_t za, int32_t zb)
+{
+    RowConsts c = {uint32_t(p.K) * uint32_t(za) * uint32_t(zb), 0.0f, 0.0f, 0};
+    if (row >= p.M)
+        return c;
+    if (zb != 0 && p.rowsum)
+        c.row_term -= uint32_t(zb) * uint32_t(p.rowsum[row]);
+    if (p.epi.by_row) {
+        if (p.epi.mode == EPI_SCALE) {
+            c.s = v.scale[row * p.epi.scale_step];
+            if (v.product)
+                c.s = __fmul_rn(c.s, v.product[row * p.epi.product_step]);
+            c.b = v.fbias[row * p.epi.bias_step];
+        } else if (p.epi.mode == EPI_REQUANT) {
+            c.s = p.epi.ratio[row * p.epi.ratio_step];
+            c.ib = p.epi.ibias ? p.epi.ibias[row] : 0;
+        }
+    }
+    return c;
+}
+
 // The columns of one accumulator row block: tcgen05.ld 32 columns at a time (one row per thread),
 // the zero-point terms, then the store selected by EpiParams.  `hand_back` gets this warp's arrival
 // as soon as the last columns have been read, before they are processed.
 // (`hand_back_at`: the same barrier by its address in the cluster's window, when it lives in the other CTA of a pair.)
 template <int BN>
 __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColView &v, uint32_t taddr, uint64_t *hand_back,
-                                                 int lane, int64_t row, bool row_ok, int n0, uint32_t row_term, int32_t za,
-                                                 float &run_max, float &run_neg, OutStage &st, bool live,
+                                                 int lane, int64_t row, bool row_ok, int n0, const RowConsts &rc, ColConsts cur,
+                                                 int32_t za, float &run_max, float &run_neg, OutStage &st, bool live,
                                                  uint32_t hand_back_at = 0)
 {
+    const uint32_t row_term = rc.row_term;
     // (The ragged-edge store loops below are unrolled by pragma: left to itself the compiler indexed the
     // 32 accumulators at run time there, which put all of them in local memory - every int8 kernel ran
     // 8-28 % slower.)
     const bool vec4 = p.vec_ok != 0;
     // constants that belong to this thread's row rather than to the columns (EpiParams::by_row)
     const bool by_row = p.epi.by_row != 0;
-    float s_row = 0.0f, b_row = 0.0f;
-    int32_t ib_row = 0;
-    if (by_row && row_ok) {
-        if (p.epi.mode == EPI_SCALE) {
-            s_row = v.scale[row * p.epi.scale_step];
-            if (v.product)
-                s_row = __fmul_rn(s_row, v.product[row * p.epi.product_step]);
-            b_row = v.fbias[row * p.epi.bias_step];
-        } else if (p.epi.mode == EPI_REQUANT) {
-            s_row = p.epi.ratio[row * p.epi.ratio_step];
-            ib_row = p.epi.ibias ? p.epi.ibias[row] : 0;
-        }
-    }
+    const float s_row = rc.s, b_row = rc.b;
+    const int32_t ib_row = rc.ib;
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
         umma::tmem_ld_32x32(taddr + uint32_t(c0), r);
+        // the next block's constants travel while this one is worked on
+        const ColConsts here = cur;
+        if (c0 + 32 < BN)
+            cur = col_consts(p, v, n0 + c0 + 32 + lane, za);
         umma::tmem_ld_wait();
         if (c0 + 32 == BN) {  // the whole accumulator has been read: hand it back
             umma::tc_fence_before();
@@ -265,25 +315,17 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
         // loop below takes them by shuffle; a load per element from every thread made the
         // dequantising store several times as long as the int32 one.  All lanes take part, rows past
         // M included; only the stores are predicated.
-        const int col_l = col0 + lane;
-        const bool col_ok = col_l < v.N;
-        const int32_t cs_l = col_ok ? v.colsum[col_l] : 0;
-        float s_l = 0.0f, b_l = 0.0f;
-        int32_t ib_l = 0;
-        if (by_row) {
-            // nothing to fetch per column
-        } else if (p.epi.mode == EPI_SCALE && col_ok) {
-            s_l = v.scale[col_l * p.epi.scale_step];
-            if (v.product)
-                s_l = __fmul_rn(s_l, v.product[col_l * p.epi.product_step]);
-            b_l = v.fbias[col_l * p.epi.bias_step];
-        } else if (p.epi.mode == EPI_REQUANT && col_ok) {
-            s_l = p.epi.ratio[col_l * p.epi.ratio_step];
-            ib_l = p.epi.ibias ? p.epi.ibias[col_l] : 0;
-        }
+        const int32_t cs_l = here.cs, ib_l = here.ib;
+        const float s_l = here.s, b_l = here.b;
+        if (za != 0) {
 #pragma unroll
-        for (int j = 0; j < 32; j++)
-            r[j] = r[j] - uint32_t(za) * uint32_t(__shfl_sync(0xffffffffu, cs_l, j)) + row_term;
+            for (int j = 0; j < 32; j++)
+                r[j] = r[j] - uint32_t(za) * uint32_t(__shfl_sync(0xffffffffu, cs_l, j)) + row_term;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                r[j] += row_term;
+        }
         if (p.epi.mode == EPI_RAW) {
             int32_t *o = static_cast<int32_t *>(v.out) + row * v.N + col0;
             if (st.buf) {
@@ -340,17 +382,28 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
             for (int j = 0; j < 32; j++) {
                 const float ratio = by_row ? s_row : __shfl_sync(0xffffffffu, s_l, j);
                 const int32_t acc = int32_t(r[j] + uint32_t(by_row ? ib_row : __shfl_sync(0xffffffffu, ib_l, j)));
-                const float rr = rintf(__fmul_rn(float(acc), ratio));
-                int32_t qv = int32_t(uint32_t(__float2int_rn(rr)) + uint32_t(p.epi.y_zp));
+                // (the conversion rounds to nearest even itself: the same value as converting rintf of it)
+                int32_t qv = int32_t(uint32_t(__float2int_rn(__fmul_rn(float(acc), ratio))) + uint32_t(p.epi.y_zp));
                 qv = p.epi.y_signed ? max(-128, min(127, qv)) : max(0, min(255, qv));
                 q8[j] = uint32_t(qv) & 0xffu;
             }
             uint8_t *o = static_cast<uint8_t *>(v.out) + row * v.N + col0;
             if (!row_ok) {
             } else if (vec4 && col0 + 32 <= v.N) {
+                uint32_t w8[8];
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                    *reinterpret_cast<uint32_t *>(o + j) = q8[j] | (q8[j + 1] << 8) | (q8[j + 2] << 16) | (q8[j + 3] << 24);
+                for (int j = 0; j < 8; j++)
+                    w8[j] = q8[4 * j] | (q8[4 * j + 1] << 8) | (q8[4 * j + 2] << 16) | (q8[4 * j + 3] << 24);
+                // a thread's 32 bytes are one sector of its row: as two 16-byte stores where the row allows it
+                // (as eight 4-byte ones the same product took 1.6 times as long as with its 32-bit results)
+                if ((reinterpret_cast<uintptr_t>(o) & 15u) == 0) {
+                    *reinterpret_cast<uint4 *>(o) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+                    *reinterpret_cast<uint4 *>(o + 16) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        *reinterpret_cast<uint32_t *>(o + 4 * j) = w8[j];
+                }
             } else {
 #pragma unroll
                 for (int j = 0; j < 32; j++)
@@ -534,18 +587,19 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ T
             const int member = member_of(p, tile % n_tiles, BN, n0);
             const ColView cols = columns_of(p, member);
             st.map = map_of(tmYs, member);
+            // what the epilogue reads from memory is asked for before the accumulator is waited for
+            const int64_t row = m0 + q * 32 + lane;
+            const RowConsts rc = row_consts(p, cols, row, za, zb);
+            const ColConsts first = col_consts(p, cols, n0 + lane, za);
             if (ready && !wait_parked(&acc_full[b], acc_ph)) {
                 ready = false;
                 if (lane == 0)
                     atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
             }
             umma::tc_fence_after();
-            const int64_t row = m0 + q * 32 + lane;
             const bool row_ok = ready && row < p.M;
-            const uint32_t row_term = uint32_t(p.K) * uint32_t(za) * uint32_t(zb) -
-                                      ((zb != 0 && p.rowsum && row_ok) ? uint32_t(zb) * uint32_t(p.rowsum[row]) : 0u);
             epilogue_columns<BN>(p, cols, tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BN), &acc_empty[b], lane, row,
-                                 row_ok, n0, row_term, za, run_max, run_neg, st, ready);
+                                 row_ok, n0, rc, first, za, run_max, run_neg, st, ready);
             if (++b == 2) {
                 b = 0;
                 acc_ph ^= 1;
@@ -769,18 +823,19 @@ mmi_tc256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int tile = vcta; tile < total_tiles; tile += vgrid) {
             const int64_t m0 = int64_t(tile / n_tiles) * TM + int64_t(crank) * BM2 + half * 128;
             const int n0 = (tile % n_tiles) * BN2;
+            const int64_t row = m0 + q * 32 + lane;
+            const ColView cols = columns_of(p, 0);
+            const RowConsts rc = row_consts(p, cols, row, za, zb);
+            const ColConsts first = col_consts(p, cols, n0 + lane, za);
             if (ready && !wait_parked(acc_full, acc_ph)) {
                 ready = false;
                 if (lane == 0)
                     atomicExch(p.status, OVK_DEV_TIMEOUT_MMA);
             }
             umma::tc_fence_after();
-            const int64_t row = m0 + q * 32 + lane;
             const bool row_ok = ready && row < p.M;
-            const uint32_t row_term = uint32_t(p.K) * uint32_t(za) * uint32_t(zb) -
-                                      ((zb != 0 && p.rowsum && row_ok) ? uint32_t(zb) * uint32_t(p.rowsum[row]) : 0u);
-            epilogue_columns<BN2>(p, columns_of(p, 0), tmem_base + (uint32_t(q * 32) << 16) + uint32_t(half * BN2), acc_empty,
-                                  lane, row, row_ok, n0, row_term, za, run_max, run_neg, st, ready, acc_empty_at);
+            epilogue_columns<BN2>(p, cols, tmem_base + (uint32_t(q * 32) << 16) + uint32_t(half * BN2), acc_empty,
+                                  lane, row, row_ok, n0, rc, first, za, run_max, run_neg, st, ready, acc_empty_at);
             acc_ph ^= 1;
         }
         stage_out_drain(st, lane);

@@ -538,11 +538,17 @@ __device__ __forceinline__ void transpose4x4(uint32_t a, uint32_t b, uint32_t c,
     out[3] = prmt(ab_hi, cd_hi, 0x7632);
 }
 
+// (Channels in groups of `cgroup` over blockIdx.z: a block's shared memory is then a few tens of KB whatever C
+// is, several blocks share an SM, and their loads are in flight together - with all 512 channels of a 28 x 28
+// image in one block the pass ran at a tenth of the memory's rate.  A group writes 128 contiguous bytes of
+// every pixel.  The frame is written by the blocks of the first group.)
 __global__ void __launch_bounds__(256)
-conv_pad_nhwc_fast_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ xp, int C, int H, int W, int HP, int WP,
-                          int pt, int pl, uint32_t zp_byte, int R, int pitch_words)
+conv_pad_nhwc_fast_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ xp, int C_all, int H, int W, int HP, int WP,
+                          int pt, int pl, uint32_t zp_byte, int R, int pitch_words, int cgroup)
 {
-    extern __shared__ __align__(16) uint32_t slab[];  // [C][pitch_words]
+    extern __shared__ __align__(16) uint32_t slab[];  // [channels of the group][pitch_words]
+    const int c_begin = blockIdx.z * cgroup;
+    const int C = min(cgroup, C_all - c_begin);  // the channels this block turns
     // the convolution kernel may start its prologue (barriers, tensor memory, filter bank) now; it
     // reads this kernel's output only after griddepcontrol.wait
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -556,45 +562,51 @@ conv_pad_nhwc_fast_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ x
     // (a run is at most 64 words; four channels are fetched before anything is stored, so that a
     // warp has eight loads in flight instead of one)
     const size_t ch_stride = size_t(H) * W / 4;  // words between channels
-    const uint32_t *src0 = reinterpret_cast<const uint32_t *>(x + (size_t(n) * C * H + h0) * W);
-    const bool has0 = lane < words_per_ch, has1 = lane + 32 < words_per_ch;
-    for (int c = warp * 4; c < C; c += nwarps * 4) {
-        uint32_t v[4][2];
+    const uint32_t *src0 = reinterpret_cast<const uint32_t *>(x + ((size_t(n) * C_all + c_begin) * H + h0) * W);
+    // (rows wider than 256 pixels are a run of more than 64 words: taken 64 words at a time)
+    for (int w0 = 0; w0 < words_per_ch; w0 += 64) {
+        const bool has0 = w0 + lane < words_per_ch, has1 = w0 + lane + 32 < words_per_ch;
+        for (int c = warp * 4; c < C; c += nwarps * 4) {
+            uint32_t v[4][2];
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const uint32_t *src = src0 + size_t(c + k) * ch_stride;
-            v[k][0] = (c + k < C && has0) ? __ldg(src + lane) : 0u;
-            v[k][1] = (c + k < C && has1) ? __ldg(src + lane + 32) : 0u;
-        }
+            for (int k = 0; k < 4; k++) {
+                const uint32_t *src = src0 + size_t(c + k) * ch_stride + w0;
+                v[k][0] = (c + k < C && has0) ? __ldg(src + lane) : 0u;
+                v[k][1] = (c + k < C && has1) ? __ldg(src + lane + 32) : 0u;
+            }
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            if (c + k < C && has0)
-                slab[(c + k) * pitch_words + lane] = v[k][0];
-            if (c + k < C && has1)
-                slab[(c + k) * pitch_words + lane + 32] = v[k][1];
+            for (int k = 0; k < 4; k++) {
+                if (c + k < C && has0)
+                    slab[(c + k) * pitch_words + w0 + lane] = v[k][0];
+                if (c + k < C && has1)
+                    slab[(c + k) * pitch_words + w0 + lane + 32] = v[k][1];
+            }
         }
     }
     // ---- the padding this block owns: left/right columns of its rows (a warp per row), and the
     // rows above the first / below the last group
-    uint8_t *img = xp + size_t(n) * HP * WP * C;
+    uint8_t *img = xp + size_t(n) * HP * WP * C_all;
     const int c16 = C / 16;
-    const int pr = WP - pl - W;  // padding columns on the right
-    for (int r = warp; r < rows; r += nwarps) {
-        uint4 *row = reinterpret_cast<uint4 *>(img + size_t(pt + h0 + r) * WP * C);
-        for (int i = lane; i < pl * c16; i += 32)
-            row[i] = zp16;
-        uint4 *right = row + size_t(pl + W) * c16;
-        for (int i = lane; i < pr * c16; i += 32)
-            right[i] = zp16;
-    }
-    if (blockIdx.x == 0)
-        for (int i = threadIdx.x; i < pt * WP * c16; i += blockDim.x)
-            reinterpret_cast<uint4 *>(img)[i] = zp16;
-    if (h0 + rows == H) {
-        const int below = HP - pt - H;
-        uint4 *dst = reinterpret_cast<uint4 *>(img + size_t(pt + H) * WP * C);
-        for (int i = threadIdx.x; i < below * WP * c16; i += blockDim.x)
-            dst[i] = zp16;
+    if (blockIdx.z == 0) {
+        const int all16 = C_all / 16;
+        const int pr = WP - pl - W;  // padding columns on the right
+        for (int r = warp; r < rows; r += nwarps) {
+            uint4 *row = reinterpret_cast<uint4 *>(img + size_t(pt + h0 + r) * WP * C_all);
+            for (int i = lane; i < pl * all16; i += 32)
+                row[i] = zp16;
+            uint4 *right = row + size_t(pl + W) * all16;
+            for (int i = lane; i < pr * all16; i += 32)
+                right[i] = zp16;
+        }
+        if (blockIdx.x == 0)
+            for (int i = threadIdx.x; i < pt * WP * all16; i += blockDim.x)
+                reinterpret_cast<uint4 *>(img)[i] = zp16;
+        if (h0 + rows == H) {
+            const int below = HP - pt - H;
+            uint4 *dst = reinterpret_cast<uint4 *>(img + size_t(pt + H) * WP * C_all);
+            for (int i = threadIdx.x; i < below * WP * all16; i += blockDim.x)
+                dst[i] = zp16;
+        }
     }
     __syncthreads();
     // ---- transpose and write
@@ -619,10 +631,10 @@ conv_pad_nhwc_fast_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ x
         for (int g = 0; g < 4; g++)
             transpose4x4(src[(4 * g) * pitch_words], src[(4 * g + 1) * pitch_words], src[(4 * g + 2) * pitch_words],
                          src[(4 * g + 3) * pitch_words], t[g]);
-        uint8_t *dst = img + (size_t(pt + h0 + r) * WP + pl + qw * 4) * C + cq * 16;
+        uint8_t *dst = img + (size_t(pt + h0 + r) * WP + pl + qw * 4) * C_all + c_begin + cq * 16;
 #pragma unroll
         for (int px = 0; px < 4; px++)
-            *reinterpret_cast<uint4 *>(dst + size_t(px) * C) = make_uint4(t[0][px], t[1][px], t[2][px], t[3][px]);
+            *reinterpret_cast<uint4 *>(dst + size_t(px) * C_all) = make_uint4(t[0][px], t[1][px], t[2][px], t[3][px]);
     }
 }
 
@@ -717,17 +729,28 @@ int32_t ovk_qconv_pad_nhwc(ovk_ctx *ctx, const void *x, const ConvGeom &g, int32
     const int C = g.c_in;
     const int HP = g.h_in + g.phb + g.phe, WP = g.w_in + g.pwb + g.pwe;
     const int32_t x_zp = fill;
-    const bool fast_layout = (g.w_in % 4) == 0 && (C % 16) == 0 && aligned_to(x, 4) && g.w_in <= 1024;
+    // Without a frame the image's pixels are one run per channel, and the rows need not be told apart: a
+    // 14 x 14 plane, whose rows of 14 bytes are no whole words, is turned as one row of 196 pixels.
+    int h_in = g.h_in, w_in = g.w_in;
+    if (HP == g.h_in && WP == g.w_in && (g.w_in % 4) != 0 && (int64_t(g.h_in) * g.w_in) % 4 == 0 &&
+        int64_t(g.h_in) * g.w_in <= 1024) {
+        w_in = g.h_in * g.w_in;
+        h_in = 1;
+    }
+    const bool fast_layout = (w_in % 4) == 0 && (C % 16) == 0 && aligned_to(x, 4) && w_in <= 1024 && g.n <= 65535;
     if (fast_layout) {
-        const int R = std::max(1, std::min(g.h_in, 256 / g.w_in));  // about 256 pixels per block
-        const int pitch_words = R * g.w_in / 4 + 1;
-        const size_t sm = size_t(C) * pitch_words * 4;
+        const int R = std::max(1, std::min(h_in, 256 / w_in));  // about 256 pixels per block
+        const int pitch_words = R * w_in / 4 + 1;
+        const int cgroup = std::min(C, 128);
+        const size_t sm = size_t(cgroup) * pitch_words * 4;
         if (sm > 48 * 1024)
             OVK_CUDA(ctx, cudaFuncSetAttribute(conv_pad_nhwc_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sm)));
-        OVK_REQUIRE(ctx, sm <= ctx->smem_optin, "ConvInteger: %d channels are too many for the layout pass", C);
-        conv_pad_nhwc_fast_kernel<<<dim3(unsigned(ceil_div64(g.h_in, R)), unsigned(g.n)), 256, sm, ctx->stream>>>(
-            static_cast<const uint8_t *>(x), xp, C, g.h_in, g.w_in, HP, WP, g.phb, g.pwb, uint32_t(x_zp) & 0xffu, R,
-            pitch_words);
+        OVK_REQUIRE(ctx, sm <= ctx->smem_optin && ceil_div64(C, cgroup) <= 65535,
+                    "ConvInteger: %d channels are too many for the layout pass", C);
+        const bool flat = h_in != g.h_in;
+        conv_pad_nhwc_fast_kernel<<<dim3(unsigned(ceil_div64(h_in, R)), unsigned(g.n), unsigned(ceil_div64(C, cgroup))), 256, sm,
+                                    ctx->stream>>>(static_cast<const uint8_t *>(x), xp, C, h_in, w_in, flat ? h_in : HP,
+                                                   flat ? w_in : WP, g.phb, g.pwb, uint32_t(x_zp) & 0xffu, R, pitch_words, cgroup);
         OVK_LAUNCHED(ctx, "conv_pad_nhwc_fast");
     } else {
         const int pitch = ((g.w_in + 3) & ~3) + 4;

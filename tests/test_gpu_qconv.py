@@ -183,13 +183,18 @@ def test_resnet_block_takes_the_tensor_core_kernel():
     (64, 128, 30, 30, 3, 1, (1, 1, 1, 1), False),
     (64, 256, 30, 30, 1, 1, (0, 0, 0, 0), False),
     (32, 200, 40, 36, 1, 1, (0, 0, 0, 0), True),
+    (32, 32, 5, 320, 3, 1, (1, 1, 1, 1), False),
+    (256, 64, 14, 14, 1, 1, (0, 0, 0, 0), False),
+    (384, 64, 28, 28, 1, 1, (0, 0, 0, 0), True),
 ])
 def test_tensor_core_geometries(c_in, c_out, h, w, k, dil, pads, xs):
     """Channel counts 32/64/128/256 (one to two K slices per tap), dilation,
     uneven pads, pointwise and 5x5 filters, signed x, C_out off the tile size,
     and 128 / 200 / 256 output channels: four, two and two accumulators in
     flight, so the epilogue warps of a lane quarter split into four or two tile
-    groups, over several tiles per CTA."""
+    groups, over several tiles per CTA.  The last rows are for the layout pass
+    in front of the kernel: rows wider than 256 pixels, an unpadded plane whose
+    rows are no whole words (turned as one row), three channel groups."""
     x = cases.lcg_bytes_fast(3 * c_in * h * w, 21).reshape(3, c_in, h, w)
     wt = cases.lcg_bytes_fast(c_out * c_in * k * k, 23).reshape(c_out, c_in, k, k).view(np.int8)
     x = x.view(np.int8) if xs else x
