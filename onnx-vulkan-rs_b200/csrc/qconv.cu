@@ -310,6 +310,64 @@ patches_kernel(const uint8_t *__restrict__ x0, uint8_t *__restrict__ out, ConvGe
     }
 }
 
+// The same matrix built a row of output pixels at a time: the input rows that row of patches looks at - all
+// channels, with their frame of zero-point bytes - are laid down in shared memory once (coalesced reads, the
+// bounds decided there), and the patch rows are assembled from shared memory (the 7 x 7 stem of a
+// ResNet).  Taken when those rows are few and long and fit in 48 KB.
+__global__ void __launch_bounds__(256)
+patches_rows_kernel(const uint8_t *__restrict__ x0, uint8_t *__restrict__ out, ConvGeom g, int x_zp, int pitch, int wpad)
+{
+    extern __shared__ uint8_t rows[];  // [c_in][kh][wpad], column 0 = input column -pwb
+    const int oh = blockIdx.x, img = blockIdx.y;
+    const int taps = g.kh * g.kw, K = g.c_in * taps;
+    const size_t in_plane = size_t(g.h_in) * g.w_in;
+    const uint8_t *xi = x0 + size_t(img) * g.c_in * in_plane;
+    const int ih0 = oh * g.sh - g.phb;
+    const int lines = g.c_in * g.kh;
+    const uint8_t zp = uint8_t(x_zp & 0xff);
+    // a warp per line of the slab, its lanes along the line
+    for (int line = threadIdx.x >> 5; line < lines; line += 8) {
+        const int c = line / g.kh, r = line - c * g.kh;
+        const int ih = ih0 + r * g.dh;
+        const bool inside = ih >= 0 && ih < g.h_in;
+        const uint8_t *src = xi + size_t(c) * in_plane + size_t(inside ? ih : 0) * g.w_in;
+        uint8_t *dst = rows + size_t(line) * wpad;
+        for (int i = threadIdx.x & 31; i < wpad; i += 32) {
+            const int iw = i - g.pwb;
+            dst[i] = (inside && iw >= 0 && iw < g.w_in) ? src[iw] : zp;
+        }
+    }
+    __syncthreads();
+    // A thread owns one 32-bit word of the patch row - its four positions in the slab are worked out once - and
+    // walks along the output pixels with it; the threads of a patch row write its words side by side.
+    // (Sixteen bytes per thread with (channel, row, column) stepped from byte to byte cost four times the
+    // instructions, and the pass was bound by them.)
+    const int words = pitch >> 2, per_pass = 256 / words;  // pitch <= 1024
+    const int word = threadIdx.x % words, sub = threadIdx.x / words;
+    if (sub >= per_pass)
+        return;
+    int off[4];
+    uint32_t mask = 0;
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const int kk = word * 4 + e;
+        off[e] = 0;
+        if (kk < K) {
+            const int c = kk / taps, t = kk - c * taps;
+            const int r = t / g.kw, s2 = t - r * g.kw;
+            off[e] = (c * g.kh + r) * wpad + s2 * g.dw;
+            mask |= 0xffu << (8 * e);
+        }
+    }
+    uint32_t *out_row = reinterpret_cast<uint32_t *>(out + (size_t(img) * g.h_out + oh) * g.w_out * size_t(pitch));
+    for (int ow = sub; ow < g.w_out; ow += per_pass) {
+        const uint8_t *base = rows + ow * g.sw;
+        const uint32_t v = uint32_t(base[off[0]]) | (uint32_t(base[off[1]]) << 8) | (uint32_t(base[off[2]]) << 16) |
+                           (uint32_t(base[off[3]]) << 24);
+        out_row[size_t(ow) * words + word] = v & mask;
+    }
+}
+
 // sum of every patch row (the term the filters' zero point multiplies), one warp per row
 __global__ void __launch_bounds__(256)
 patch_sums_kernel(const uint8_t *__restrict__ patches, int64_t rows, int pitch, int x_signed, int32_t *__restrict__ sums)
@@ -381,6 +439,9 @@ pad_filter_rows_kernel(const uint8_t *__restrict__ w, uint8_t *__restrict__ out,
 #ifndef OVK_GEMM_ROUTE_MAX_IMAGES
 #define OVK_GEMM_ROUTE_MAX_IMAGES 4
 #endif
+#ifndef OVK_GEMM_ROUTE_FEW_PIXELS
+#define OVK_GEMM_ROUTE_FEW_PIXELS 3200
+#endif
 constexpr int64_t GEMM_ROUTE_MAX_BYTES = int64_t(32) << 20;
 
 bool gemm_route_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const ConvGeom &g, int32_t w_zp, const ConvLayout &lay,
@@ -399,8 +460,13 @@ bool gemm_route_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const Con
     const int conv_launches = w_zp != 0 ? 0 : ovk_qconv_tc_launches(ctx, w, g, x);  // symmetric weights only, there
     // (measured at 8 and 64 images: this route wins while images x output pixels stay small - 7 x 7 planes at 64
     // images 340 -> 60 us, 14 x 14 at 8 images 56 -> 27 us - and loses beyond: 14 x 14 at 64 images 69 -> 92 us)
-    const bool few = g.n <= OVK_GEMM_ROUTE_MAX_IMAGES || int64_t(g.n) * g.h_out * g.w_out <= 3200;
-    if (conv_launches == 1 || (conv_launches == 2 && g.kh * g.kw > 1) || (conv_launches > 0 && !few))
+    // (a strided filter larger than 1 x 1 is computed at every position by the convolution kernel and kept
+    // on the stride lattice only: against it this route holds on for stride x stride times as many pixels -
+    // 256 -> 256 3 x 3 stride 2 on 28 x 28 at 64 images: 175 -> 85 us)
+    const bool few_kept = g.kh * g.kw > 1 && g.sh * g.sw >= 4 && conv_launches >= 3 &&
+                          int64_t(g.n) * g.h_out * g.w_out <= int64_t(OVK_GEMM_ROUTE_FEW_PIXELS) * g.sh * g.sw;
+    const bool few = g.n <= OVK_GEMM_ROUTE_MAX_IMAGES || int64_t(g.n) * g.h_out * g.w_out <= OVK_GEMM_ROUTE_FEW_PIXELS;
+    if (conv_launches == 1 || (conv_launches == 2 && g.kh * g.kw > 1) || (conv_launches > 0 && !few && !few_kept))
         return false;
     const int64_t K = (int64_t(g.c_in) * g.kh * g.kw + 15) / 16 * 16, pixels = int64_t(g.h_out) * g.w_out;
     if (pixels * K > GEMM_ROUTE_MAX_BYTES)
@@ -472,8 +538,16 @@ int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, 
                 xi, patches_dev, g.c_in, int(pixels), words_ok);
             OVK_LAUNCHED(ctx, "conv_pixels_major");
         } else {
-            const unsigned blocks = unsigned(std::min<int64_t>(ceil_div64(int64_t(images) * pixels * K, 256), int64_t(ctx->sm_count) * 32));
-            patches_kernel<<<blocks, 256, 0, ctx->stream>>>(xi, patches_dev, g, x_zp, K, images);
+            const int wpad = g.w_in + g.pwb + g.pwe;
+            const size_t slab = size_t(g.c_in) * g.kh * wpad;
+            // (few, long lines: with the 1536 lines of 9 bytes of a 512-channel 3 x 3 layer on 7 x 7 the fill
+            // of the slab is a chain of short loads and the pass takes three times as long as the plain one)
+            if (slab <= 48 * 1024 && g.c_in * g.kh <= 64 && wpad >= 64 && K <= 1024 && g.h_out <= 65535 && images <= 65535) {
+                patches_rows_kernel<<<dim3(unsigned(g.h_out), unsigned(images)), 256, slab, ctx->stream>>>(xi, patches_dev, g, x_zp, K, wpad);
+            } else {
+                const unsigned blocks = unsigned(std::min<int64_t>(ceil_div64(int64_t(images) * pixels * K, 256), int64_t(ctx->sm_count) * 32));
+                patches_kernel<<<blocks, 256, 0, ctx->stream>>>(xi, patches_dev, g, x_zp, K, images);
+            }
             OVK_LAUNCHED(ctx, "conv_patches");
         }
         patches.n = int64_t(images) * pixels;

@@ -296,6 +296,7 @@ def test_small_images_stay_on_the_tensor_core_kernel(c_in, c_out, hw, k, batch):
     (16, 64, 30, 30, 5, (3, 3), 1, (2, 2, 2, 2), 4),
     (3, 64, 64, 64, 7, (2, 2), 1, (3, 3, 3, 3), 6),        # the stem: K = 147 padded to 160, any batch
     (20, 48, 19, 19, 1, (1, 1), 1, (0, 0, 0, 0), 2),       # 1 x 1 over a channel count that is no multiple of 16
+    (4, 64, 70, 66, 5, (2, 3), 2, (3, 1, 4, 2), 3),        # few long rows (patches built a row of pixels at a time), dilated
 ])
 def test_convolution_as_filters_times_patches(c_in, c_out, h, w, k, strides, dil, pads, batch):
     """Up to four images whose filter bank the convolution kernel cannot hold at once: the patch matrix of an image
