@@ -447,6 +447,8 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
             conv_cl(cl_b, cl_a)
     ms_cl = timed(torch, dist, world, gc.replay, 10) / 10
     del gc, gq
+    # (before the half-second loop below, which leaves the GPU at its power-capped clock for a while)
+    resnet = resnet50_convolutions(torch, dist, ctx, gen) if world == 1 else None
     # the dense int8 peak, measured here: what back-to-back kind::i8 MMAs deliver per clock per SM, times
     # the SMs, times the clock the GPU held while this GEMM ran (sampled by nvidia-smi during a second run)
     mac_rate = ctx.probe_mma_rate(ovk_int8_code())
@@ -486,8 +488,8 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
                                                  "note": "padded-NHWC in and out (ovk_qlinear_conv_layout): one launch per layer"},
                                              "algorithmic_gbs": 2.0 * 64 * 64 * 56 * 56 / (ms_q * 1e-3) / 1e9,
                                              "parallelism": "batch-split x%d, no exchange" % world if world > 1 else "single"}
-    if world == 1:
-        out["int8_resnet50_convolutions"] = resnet50_convolutions(torch, dist, ctx, gen)
+    if resnet is not None:
+        out["int8_resnet50_convolutions"] = resnet
     return out
 
 
