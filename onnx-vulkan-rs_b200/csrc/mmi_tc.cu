@@ -29,7 +29,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 128;  // bytes of K per stage = one 128-byte swizzle row
 constexpr int A_BYTES = BM * BK;
-constexpr int THREADS = 224;  // TMA, issuer 0, four epilogue warps, issuer 1
+constexpr int THREADS = 352;  // TMA, issuer 0, four epilogue warps, issuer 1, four more epilogue warps
 constexpr long long WAIT_CYCLES = 2000000000ll;  // about a second
 
 // Several weights over the same A in one launch (q, k and v of an attention block): the tiles of all
@@ -277,8 +277,10 @@ template <int BN>
 __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColView &v, uint32_t taddr, uint64_t *hand_back,
                                                  int lane, int64_t row, bool row_ok, int n0, const RowConsts &rc, ColConsts cur,
                                                  int32_t za, float &run_max, float &run_neg, OutStage &st, bool live,
-                                                 uint32_t hand_back_at = 0)
+                                                 uint32_t hand_back_at = 0, int c_first = 0, int c_step = 32)
 {
+    // (`c_first`, `c_step`: the blocks of 32 columns this warp takes - all of them, or every other one where two
+    // warps share a lane quarter)
     const uint32_t row_term = rc.row_term;
     // (The ragged-edge store loops below are unrolled by pragma: left to itself the compiler indexed the
     // 32 accumulators at run time there, which put all of them in local memory - every int8 kernel ran
@@ -289,15 +291,15 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
     const float s_row = rc.s, b_row = rc.b;
     const int32_t ib_row = rc.ib;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
+    for (int c0 = c_first; c0 < BN; c0 += c_step) {
         uint32_t r[32];
         umma::tmem_ld_32x32(taddr + uint32_t(c0), r);
         // the next block's constants travel while this one is worked on
         const ColConsts here = cur;
-        if (c0 + 32 < BN)
-            cur = col_consts(p, v, n0 + c0 + 32 + lane, za);
+        if (c0 + c_step < BN)
+            cur = col_consts(p, v, n0 + c0 + c_step + lane, za);
         umma::tmem_ld_wait();
-        if (c0 + 32 == BN) {  // the whole accumulator has been read: hand it back
+        if (c0 + c_step >= BN) {  // this warp has read its part of the accumulator: hand it back
             umma::tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -415,7 +417,7 @@ __device__ __forceinline__ void epilogue_columns(const TcParams &p, const ColVie
 }
 
 template <int BN> constexpr int stages_for() { return BN == 256 ? 4 : (BN == 128 ? 6 : 8); }
-constexpr int OUT_STAGE_BYTES = 4 * 2 * 4096;  // four epilogue warps, two 32 x 32 blocks of 32-bit results each
+constexpr int OUT_STAGE_BYTES = 8 * 4096;  // eight epilogue warps, a 32 x 32 block of 32-bit results each (the pair kernel: its own split)
 template <int BN> constexpr size_t smem_for()
 {
     return size_t(stages_for<BN>()) * (A_BYTES + BN * BK) + 1024 /*alignment slack*/ + 256 /*barriers*/ + OUT_STAGE_BYTES +
@@ -435,7 +437,7 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ T
     uint64_t *full = reinterpret_cast<uint64_t *>(sB + STAGES * B_BYTES);
     uint64_t *empty = full + STAGES;
     uint64_t *acc_full = empty + STAGES;   // [2] a tile's accumulator is complete
-    uint64_t *acc_empty = acc_full + 2;    // [2] the four epilogue warps have read it
+    uint64_t *acc_empty = acc_full + 2;    // [2] the eight epilogue warps have read it
     uint64_t *started = acc_empty + 2;     // [2] the tile's first (overwriting) MMA has been issued
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(started + 2);
     uint8_t *out_stage = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(tmem_slot + 2) + 1023) & ~uintptr_t(1023));
@@ -453,7 +455,7 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ T
         }
         for (int b = 0; b < 2; b++) {
             umma::mbar_init(&acc_full[b], 2);  // one arrival per issuing thread
-            umma::mbar_init(&acc_empty[b], 4);
+            umma::mbar_init(&acc_empty[b], 8);
             umma::mbar_init(&started[b], 1);
         }
         umma::fence_barrier_init();
@@ -573,11 +575,16 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ T
             }
         }
     } else {
-        // Epilogue: warp w may read tensor-memory lanes 32*(w % 4) .. +31.
+        // Epilogue: warp w may read tensor-memory lanes 32*(w % 4) .. +31.  Two warps per lane quarter (2-5 and
+        // 7-10), one on the even and one on the odd blocks of 32 columns: the products of a few GOP are paced
+        // by this part (conversions, shuffles, stores; the MMAs of a short K are over long before), and one
+        // warp per scheduler left most of its issue slots to dependency stalls.
         const int q = warp & 3;
+        const int ew = warp < 6 ? warp - 2 : warp - 3;  // 0..7
+        const int c_first = (ew >> 2) * 32;
         const int32_t za = load_zp(p.a_zp, p.a_signed), zb = load_zp(p.b_zp, p.b_signed);
         float run_max = 0.0f, run_neg = 0.0f;
-        OutStage st = {p.tma_out ? out_stage + (warp - 2) * 2 * 4096 : nullptr, nullptr, 2, 0};
+        OutStage st = {p.tma_out ? out_stage + ew * 4096 : nullptr, nullptr, 1, 0};
         bool ready = true;
         int b = 0;
         uint32_t acc_ph = 0;
@@ -590,7 +597,7 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ T
             // what the epilogue reads from memory is asked for before the accumulator is waited for
             const int64_t row = m0 + q * 32 + lane;
             const RowConsts rc = row_consts(p, cols, row, za, zb);
-            const ColConsts first = col_consts(p, cols, n0 + lane, za);
+            const ColConsts first = col_consts(p, cols, n0 + c_first + lane, za);
             if (ready && !wait_parked(&acc_full[b], acc_ph)) {
                 ready = false;
                 if (lane == 0)
@@ -599,7 +606,7 @@ mmi_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ T
             umma::tc_fence_after();
             const bool row_ok = ready && row < p.M;
             epilogue_columns<BN>(p, cols, tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b * BN), &acc_empty[b], lane, row,
-                                 row_ok, n0, rc, first, za, run_max, run_neg, st, ready);
+                                 row_ok, n0, rc, first, za, run_max, run_neg, st, ready, 0, c_first, 64);
             if (++b == 2) {
                 b = 0;
                 acc_ph ^= 1;
