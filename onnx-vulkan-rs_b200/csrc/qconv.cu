@@ -401,6 +401,21 @@ unbatch_kernel(const T *__restrict__ d, T *__restrict__ out, int c_out, int imag
     }
 }
 
+// ... and a warp per plane, for planes of any size (7 x 7): no division per byte
+__global__ void __launch_bounds__(256)
+unbatch_planes_kernel(const uint8_t *__restrict__ d, uint8_t *__restrict__ out, int c_out, int images, int plane_bytes)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t planes = int64_t(images) * c_out;
+    for (int64_t w = (int64_t(blockIdx.x) * 256 + threadIdx.x) >> 5; w < planes; w += int64_t(gridDim.x) * 8) {
+        const int co = int(w % c_out), img = int(w / c_out);
+        const uint8_t *src = d + (size_t(co) * images + img) * plane_bytes;
+        uint8_t *dst = out + size_t(w) * plane_bytes;
+        for (int i = lane; i < plane_bytes; i += 32)
+            dst[i] = src[i];
+    }
+}
+
 // the same in 16-byte pieces, for planes that are whole pieces (a byte at a time the pass ran at 0.5 TB/s)
 __global__ void __launch_bounds__(256)
 unbatch_pieces_kernel(const uint4 *__restrict__ d, uint4 *__restrict__ out, int c_out, int images, int pieces)
@@ -570,6 +585,9 @@ int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, 
                 const unsigned vblocks = unsigned(std::min<int64_t>(ceil_div64(total * int64_t(out_elem) / 16, 256), int64_t(ctx->sm_count) * 32));
                 unbatch_pieces_kernel<<<vblocks, 256, 0, ctx->stream>>>(reinterpret_cast<const uint4 *>(d_dev), reinterpret_cast<uint4 *>(dst),
                                                                        g.c_out, images, pieces);
+            } else if (pixels * int64_t(out_elem) <= 1024) {
+                const unsigned pblocks = unsigned(std::min<int64_t>(ceil_div64(int64_t(images) * g.c_out, 8), int64_t(ctx->sm_count) * 32));
+                unbatch_planes_kernel<<<pblocks, 256, 0, ctx->stream>>>(d_dev, dst, g.c_out, images, int(pixels * int64_t(out_elem)));
             } else if (out_elem == 1)
                 unbatch_kernel<uint8_t><<<blocks, 256, 0, ctx->stream>>>(d_dev, dst, g.c_out, images, int(pixels));
             else

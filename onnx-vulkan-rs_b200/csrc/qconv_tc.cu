@@ -613,28 +613,34 @@ conv_pad_nhwc_fast_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ x
     // one item = (pixel quad, group of 16 channels); the threads of a quad are neighbours so that
     // they write one pixel's contiguous bytes.  c16 is a power of two for the channel counts the
     // tensor path takes (32, 64, 128, 256, ...) or small; the row of a quad comes from one multiply.
-    const int quads_per_row = W / 4;
-    const int quads = rows * quads_per_row;
-    const uint32_t inv_qpr = (65536u + uint32_t(quads_per_row) - 1u) / uint32_t(quads_per_row);  // quads < 2^10
+    // (Rows that are no whole words - 14 pixels - are taken in groups whose run is: a quad of the run may then
+    // straddle two rows, and every pixel of it finds its own row.)
+    const int quads = rows * W / 4;
+    const uint32_t inv_w = (65536u + uint32_t(W) - 1u) / uint32_t(W);  // pixels of a group < 2^10 + 2^8
     const bool c16_pow2 = (c16 & (c16 - 1)) == 0;
     const int c16_shift = 31 - __clz(c16);
     for (int i = threadIdx.x; i < quads * c16; i += blockDim.x) {
         const int quad = c16_pow2 ? i >> c16_shift : i / c16;
         const int cq = i - quad * c16;
-        int r = int((uint32_t(quad) * inv_qpr) >> 16);
-        if (r * quads_per_row > quad)
-            r--;  // the rounded-up reciprocal overshoots by at most one
-        const int qw = quad - r * quads_per_row;
         const uint32_t *src = slab + (cq * 16) * pitch_words + quad;
         uint32_t t[4][4];
 #pragma unroll
         for (int g = 0; g < 4; g++)
             transpose4x4(src[(4 * g) * pitch_words], src[(4 * g + 1) * pitch_words], src[(4 * g + 2) * pitch_words],
                          src[(4 * g + 3) * pitch_words], t[g]);
-        uint8_t *dst = img + (size_t(pt + h0 + r) * WP + pl + qw * 4) * C_all + c_begin + cq * 16;
+        int r = int((uint32_t(quad * 4) * inv_w) >> 16);
+        if (r * W > quad * 4)
+            r--;  // the rounded-up reciprocal overshoots by at most one
+        int w = quad * 4 - r * W;
 #pragma unroll
-        for (int px = 0; px < 4; px++)
-            *reinterpret_cast<uint4 *>(dst + size_t(px) * C_all) = make_uint4(t[0][px], t[1][px], t[2][px], t[3][px]);
+        for (int px = 0; px < 4; px++) {
+            uint8_t *dst = img + (size_t(pt + h0 + r) * WP + pl + w) * C_all + c_begin + cq * 16;
+            *reinterpret_cast<uint4 *>(dst) = make_uint4(t[0][px], t[1][px], t[2][px], t[3][px]);
+            if (++w == W) {
+                w = 0;
+                r++;
+            }
+        }
     }
 }
 
@@ -737,9 +743,12 @@ int32_t ovk_qconv_pad_nhwc(ovk_ctx *ctx, const void *x, const ConvGeom &g, int32
         w_in = g.h_in * g.w_in;
         h_in = 1;
     }
-    const bool fast_layout = (w_in % 4) == 0 && (C % 16) == 0 && aligned_to(x, 4) && w_in <= 1024 && g.n <= 65535;
+    // rows per block: about 256 pixels, and a whole number of words (W = 14: an even number of rows)
+    const int row_unit = (w_in % 4) == 0 ? 1 : ((w_in % 2) == 0 ? 2 : 4);
+    const bool fast_layout = (int64_t(h_in) * w_in) % 4 == 0 && h_in % row_unit == 0 && (C % 16) == 0 && aligned_to(x, 4) &&
+                             w_in <= (row_unit == 1 ? 1024 : 128) && g.n <= 65535;
     if (fast_layout) {
-        const int R = std::max(1, std::min(h_in, 256 / w_in));  // about 256 pixels per block
+        const int R = std::max(row_unit, std::min(h_in, 256 / w_in) / row_unit * row_unit);
         const int pitch_words = R * w_in / 4 + 1;
         const int cgroup = std::min(C, 128);
         const size_t sm = size_t(cgroup) * pitch_words * 4;

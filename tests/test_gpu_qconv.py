@@ -186,6 +186,8 @@ def test_resnet_block_takes_the_tensor_core_kernel():
     (32, 32, 5, 320, 3, 1, (1, 1, 1, 1), False),
     (256, 64, 14, 14, 1, 1, (0, 0, 0, 0), False),
     (384, 64, 28, 28, 1, 1, (0, 0, 0, 0), True),
+    (128, 64, 14, 14, 3, 1, (1, 1, 1, 1), False),
+    (64, 32, 8, 7, 3, 1, (1, 2, 1, 0), True),
 ])
 def test_tensor_core_geometries(c_in, c_out, h, w, k, dil, pads, xs):
     """Channel counts 32/64/128/256 (one to two K slices per tap), dilation,
@@ -194,7 +196,8 @@ def test_tensor_core_geometries(c_in, c_out, h, w, k, dil, pads, xs):
     flight, so the epilogue warps of a lane quarter split into four or two tile
     groups, over several tiles per CTA.  The last rows are for the layout pass
     in front of the kernel: rows wider than 256 pixels, an unpadded plane whose
-    rows are no whole words (turned as one row), three channel groups."""
+    rows are no whole words (turned as one row), three channel groups, padded
+    planes with rows of 14 and of 7 bytes (taken two and four rows at a time)."""
     x = cases.lcg_bytes_fast(3 * c_in * h * w, 21).reshape(3, c_in, h, w)
     wt = cases.lcg_bytes_fast(c_out * c_in * k * k, 23).reshape(c_out, c_in, k, k).view(np.int8)
     x = x.view(np.int8) if xs else x
