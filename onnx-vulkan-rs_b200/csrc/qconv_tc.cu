@@ -45,6 +45,7 @@ struct ConvTcParams {
     int h_out, w_out, c_out, co_pad;  // c_out / co_pad: the filters of THIS launch (a bank too large for shared
                                       // memory is taken in several launches of as many filters as fit)
     int c_out_total;                  // channels of the output tensor
+    int slice_filters;                // > 0: blockIdx.y numbers equal slices of that many filters, all in one launch
     int sh, sw;                       // strides: the products are computed at every position of the padded grid and
                                       // only the positions on the stride lattice are stored (2 x 2: a quarter)
     int w_tap_rows;                   // rows between two taps in the packed filter bank (all filters, padded)
@@ -119,6 +120,9 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     // kernel writes only behind its own griddepcontrol.wait, which returns when this grid has finished.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // A bank cut into equal slices is one launch, a row of the grid per slice: the slices' CTAs fill the SMs
+    // together (98 pixel tiles x 4 slices: 2.7 rounds of the GPU instead of 4 launches of 98 CTAs each).
+    const int co0 = p.slice_filters > 0 ? int(blockIdx.y) * p.slice_filters : 0;
     for (int tap = threadIdx.x; tap < p.taps && tap < 64; tap += THREADS) {
         const int off = (tap / p.kw) * p.dh * p.wp + (tap % p.kw) * p.dw;
         s_tap_a[tap] = uint32_t(off) * uint32_t(p.kch) >> 4;
@@ -128,22 +132,23 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         int32_t corr = 0;
         float ratio = 0.0f;
         if (co < p.c_out) {
-            corr = int32_t(0u - uint32_t(p.x_zp) * uint32_t(p.wsum[co]));
+            const int ch = co0 + co;  // the filter's number in the whole bank
+            corr = int32_t(0u - uint32_t(p.x_zp) * uint32_t(p.wsum[ch]));
             if (p.epi.mode == EPI_REQUANT) {
                 if (p.epi.ibias)
-                    corr = int32_t(uint32_t(corr) + uint32_t(p.epi.ibias[co]));
-                ratio = p.epi.ratio[co * p.epi.ratio_step];
+                    corr = int32_t(uint32_t(corr) + uint32_t(p.epi.ibias[ch]));
+                ratio = p.epi.ratio[ch * p.epi.ratio_step];
             } else if (p.epi.mode == EPI_SCALE) {
                 // s = scale or fl(scale * product), as epi_scale_value computes it per element
-                ratio = p.epi.scale[co * p.epi.scale_step];
+                ratio = p.epi.scale[ch * p.epi.scale_step];
                 if (p.epi.product)
-                    ratio = __fmul_rn(ratio, p.epi.product[co * p.epi.product_step]);
+                    ratio = __fmul_rn(ratio, p.epi.product[ch * p.epi.product_step]);
             }
         }
         s_corr[co] = corr;
         s_ratio[co] = ratio;
         if (p.epi.mode == EPI_SCALE)
-            s_fbias[co] = co < p.c_out ? p.epi.fbias[co * p.epi.bias_step] : 0.0f;
+            s_fbias[co] = co < p.c_out ? p.epi.fbias[(co0 + co) * p.epi.bias_step] : 0.0f;
     }
     const int nacc = p.nacc;  // power of two
     uint32_t tmem_cols = 32;
@@ -179,7 +184,7 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
             umma::mbar_expect_tx(w_full, uint32_t(slices) * uint32_t(p.co_pad) * uint32_t(p.kch));
             for (int sl = 0; sl < slices; sl++) {
                 const int tap = sl / p.chunks, ch = sl % p.chunks;
-                umma::tma_load_2d(sWt + size_t(sl) * p.w_slice, &tmW, w_full, ch * p.kch, tap * p.w_tap_rows);
+                umma::tma_load_2d(sWt + size_t(sl) * p.w_slice, &tmW, w_full, ch * p.kch, tap * p.w_tap_rows + co0);
             }
             // launched with programmatic stream serialization: everything above ran while the layout
             // pass was still draining; its output is read from here on
@@ -353,7 +358,7 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                 ow = qw;
             }
             const bool valid = ok && on_lattice && int64_t(v) < p.v_total && int(oh) < p.h_out && int(ow) < p.w_out;
-            const int64_t o_base = int64_t(img) * p.c_out_total * plane + int64_t(oh) * p.w_out + ow;
+            const int64_t o_base = (int64_t(img) * p.c_out_total + co0) * plane + int64_t(oh) * p.w_out + ow;
             // this warp's last column group: after reading it the accumulator is handed back
             int last_c0 = -1;
             for (int c0 = cs * 16; c0 < p.co_pad; c0 += CS * 16)
@@ -429,7 +434,7 @@ qconv_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                     }
                     uint8_t *o = static_cast<uint8_t *>(p.out) +
                                  ((int64_t(img) * p.y_hpwp + int64_t(int(oh) + p.y_pt) * p.y_wp + (int(ow) + p.y_pl)) *
-                                      p.c_out_total + c0);
+                                      p.c_out_total + co0 + c0);
                     if (nch > 0)  // C_out is a multiple of 16 here: a group exists whole or not at all
                         *reinterpret_cast<uint4 *>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 } else {
@@ -854,7 +859,18 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
         return ovk_fail(ctx, OVK_BACKEND, "ConvInteger: cuTensorMapEncodeTiled failed");
     const size_t out_elem = epi.mode == EPI_REQUANT ? 1 : 4;
     const int64_t plane = int64_t(g.h_out) * g.w_out;
-    for (int co0 = 0; co0 < g.c_out; co0 += per_launch) {
+    // (a slightly narrower slice that divides the bank - 512 filters as 4 x 128 rather than 160 + 160 + 160 + 32 - keeps
+    // the slices equal, which is what the single launch below needs)
+    if (g.c_out > per_launch)
+        for (int f = per_launch; f >= 32 && 2 * f > per_launch; f -= 32)
+            if (g.c_out % f == 0) {
+                per_launch = f;
+                break;
+            }
+    // equal slices go as one launch, a row of the grid each; a bank with a narrower last slice as one launch per slice
+    const bool merged = g.c_out > per_launch && g.c_out % per_launch == 0 && g.c_out / per_launch <= 65535;
+    p.slice_filters = merged ? per_launch : 0;
+    for (int co0 = 0; co0 < g.c_out; co0 += merged ? g.c_out : per_launch) {
         p.c_out = std::min(per_launch, g.c_out - co0);
         p.co_pad = (p.c_out + 31) / 32 * 32;
         p.w_slice = uint32_t((size_t(p.co_pad) * p.kch + 1023) & ~size_t(1023));
@@ -896,7 +912,7 @@ int32_t ovk_qconv_tc_launch(ovk_ctx *ctx, const ovk_qconv_weight *w, const void 
         OVK_CUDA(ctx, cudaFuncSetAttribute(qconv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         const unsigned grid = unsigned(std::min<int>(p.m_tiles, ctx->sm_count));
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(grid);
+        cfg.gridDim = dim3(grid, merged ? unsigned(g.c_out / per_launch) : 1u);
         cfg.blockDim = dim3(THREADS);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = ctx->stream;
