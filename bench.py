@@ -261,8 +261,11 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
             recv = (world - 1) / world * m * n * 2
             entry.update({"ms_with_exchange_in_kernel": ms_f, "tflops_with_exchange": 2.0 * m * k * n / (ms_f * 1e-3) / 1e12,
                           "ms_with_nccl_all_gather": ms_n, "ms_exchange_alone": ms_x, "ms_one_gpu_same_run": ms_1,
-                          "parallelism": "N-split x%d; the kernel's store warp writes each tile into every rank's Y "
-                                         "(peer stores over NVLink), one flag per peer ends the step" % world})
+                          "parallelism": ("N-split x%d; the kernel's store warp writes each tile into every rank's Y "
+                                          "(peer stores over NVLink), one flag per peer ends the step" % world) if world <= 4 else
+                                         ("N-split x%d; beyond four ranks the library runs the product into the rank's own Y and "
+                                          "then its all-gather kernel (peer stores over NVLink) - 'ms_with_exchange_in_kernel' "
+                                          "is that whole call" % world)})
             partitioned[name] = {"ms_one_gpu": ms_1, "ms_compute": ms_c, "ms_e2e": ms_f, "ms_e2e_nccl": ms_n,
                                  "ms_exchange_alone": ms_x, "exchange_alone_gbs_per_gpu": recv / (ms_x * 1e-3) / 1e9,
                                  "ms_e2e_multicast": ms_fm, "ms_exchange_alone_multicast": ms_xm,

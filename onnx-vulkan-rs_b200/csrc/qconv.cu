@@ -273,7 +273,8 @@ filter_sums_kernel(const uint8_t *__restrict__ w, int c_out, int k, int w_signed
 // A thread builds 16 consecutive bytes of a patch row and stores them at once, stepping (channel, row, column)
 // from byte to byte instead of dividing for each.
 __global__ void __launch_bounds__(256)
-patches_kernel(const uint8_t *__restrict__ x0, uint8_t *__restrict__ out, ConvGeom g, int x_zp, int pitch, int images)
+patches_kernel(const uint8_t *__restrict__ x0, uint8_t *__restrict__ out, ConvGeom g, int x_zp, int pitch, int images,
+               uint32_t pad_byte)
 {
     const int taps = g.kh * g.kw, K = g.c_in * taps;
     const int plane = g.h_out * g.w_out;
@@ -292,7 +293,7 @@ patches_kernel(const uint8_t *__restrict__ x0, uint8_t *__restrict__ out, ConvGe
         uint32_t words[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
         for (int e = 0; e < 16; e++) {
-            uint32_t byte = 0;
+            uint32_t byte = pad_byte;  // beyond K: 0, or the zero point where the filters' padding holds theirs
             if (kk0 + e < K) {
                 const int ih = ih0 + r * g.dh, iw = iw0 + s2 * g.dw;
                 byte = (ih >= 0 && ih < g.h_in && iw >= 0 && iw < g.w_in) ? xc[size_t(ih) * g.w_in + iw] : uint32_t(x_zp & 0xff);
@@ -315,7 +316,8 @@ patches_kernel(const uint8_t *__restrict__ x0, uint8_t *__restrict__ out, ConvGe
 // bounds decided there), and the patch rows are assembled from shared memory (the 7 x 7 stem of a
 // ResNet).  Taken when those rows are few and long and fit in 48 KB.
 __global__ void __launch_bounds__(256)
-patches_rows_kernel(const uint8_t *__restrict__ x0, uint8_t *__restrict__ out, ConvGeom g, int x_zp, int pitch, int wpad)
+patches_rows_kernel(const uint8_t *__restrict__ x0, uint8_t *__restrict__ out, ConvGeom g, int x_zp, int pitch, int wpad,
+                    uint32_t pad_byte)
 {
     extern __shared__ uint8_t rows[];  // [c_in][kh][wpad], column 0 = input column -pwb
     const int oh = blockIdx.x, img = blockIdx.y;
@@ -364,7 +366,7 @@ patches_rows_kernel(const uint8_t *__restrict__ x0, uint8_t *__restrict__ out, C
         const uint8_t *base = rows + ow * g.sw;
         const uint32_t v = uint32_t(base[off[0]]) | (uint32_t(base[off[1]]) << 8) | (uint32_t(base[off[2]]) << 16) |
                            (uint32_t(base[off[3]]) << 24);
-        out_row[size_t(ow) * words + word] = v & mask;
+        out_row[size_t(ow) * words + word] = (v & mask) | (~mask & (pad_byte * 0x01010101u));
     }
 }
 
@@ -429,14 +431,14 @@ unbatch_pieces_kernel(const uint4 *__restrict__ d, uint4 *__restrict__ out, int 
     }
 }
 
-// filters [C_out][K] -> [C_out][pitch], the tail of every row zero (K is no multiple of 16: 7 x 7 over 3 channels)
+// filters [C_out][K] -> [C_out][pitch], the tail of every row `fill` (K is no multiple of 16: 7 x 7 over 3 channels)
 __global__ void __launch_bounds__(256)
-pad_filter_rows_kernel(const uint8_t *__restrict__ w, uint8_t *__restrict__ out, int c_out, int K, int pitch)
+pad_filter_rows_kernel(const uint8_t *__restrict__ w, uint8_t *__restrict__ out, int c_out, int K, int pitch, uint8_t fill)
 {
     const int64_t total = int64_t(c_out) * pitch;
     for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x) * 256) {
         const int row = int(i / pitch), kk = int(i - int64_t(row) * pitch);
-        out[i] = kk < K ? w[size_t(row) * K + kk] : uint8_t(0);
+        out[i] = kk < K ? w[size_t(row) * K + kk] : fill;
     }
 }
 
@@ -463,10 +465,6 @@ bool gemm_route_applies(const ovk_ctx *ctx, const ovk_qconv_weight *w, const Con
                         const void *x)
 {
     if (g.group != 1 || lay.x_cl || lay.y_cl)
-        return false;
-    // (an asymmetric weight brings the term w_zp * sum of the patch; with K padded to 16-byte rows the padding
-    // would enter K * w_zp * x_zp, so that combination stays with the direct kernel)
-    if (w_zp != 0 && (g.c_in * g.kh * g.kw) % 16 != 0)
         return false;
     // the convolution kernel in one launch - two for filters larger than 1 x 1 - is the faster way
     // (128 -> 128 3 x 3 on 28 x 28: 12 against 21 us; 1024 -> 256 1 x 1 on 14 x 14 in two launches: 33 against 15 us),
@@ -506,11 +504,17 @@ int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, 
         OVK_LAUNCHED(ctx, "conv_filter_sums");
     }
     const uint8_t *filters = w->w;
-    if (K != K_true) {
+    // An asymmetric weight over rows padded to 16 bytes: with zero padding the terms of the zero points
+    // (K * w_zp * x_zp, w_zp * sum of a patch, x_zp * sum of a filter) would count the padding.  The padding of
+    // both operands holds the operand's own zero point instead - (x_zp - x_zp) * (w_zp - w_zp) = 0 - and the sums
+    // are taken over the padded rows; that copy of the filters depends on the call's w_zp and lives in the
+    // scratch buffer (C_out x K bytes: 10 KB for the 7 x 7 stem).
+    const bool zp_padding = w_zp != 0 && K != K_true;
+    if (K != K_true && !zp_padding) {
         if (!w->w_rows16) {
             OVK_CUDA(ctx, cudaMalloc(&w->w_rows16, size_t(g.c_out) * K));
             pad_filter_rows_kernel<<<unsigned(ceil_div64(int64_t(g.c_out) * K, 256)), 256, 0, ctx->stream>>>(w->w, w->w_rows16,
-                                                                                                             g.c_out, K_true, K);
+                                                                                                             g.c_out, K_true, K, uint8_t(0));
             OVK_LAUNCHED(ctx, "conv_pad_filter_rows");
         }
         filters = w->w_rows16;
@@ -521,13 +525,28 @@ int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, 
     const size_t patch_bytes = (size_t(group) * pixels * K + 255) & ~size_t(255);
     const size_t d_bytes = group > 1 ? (size_t(g.c_out) * group * pixels * out_elem + 255) & ~size_t(255) : 0;
     const size_t sums_bytes = w_zp != 0 ? (size_t(group) * pixels * sizeof(int32_t) + 255) & ~size_t(255) : 0;
+    const size_t fpad_bytes = zp_padding ? (size_t(g.c_out) * K + 255) & ~size_t(255) : 0;
+    const size_t fsum_bytes = zp_padding ? (size_t(g.c_out) * sizeof(int32_t) + 255) & ~size_t(255) : 0;
     void *ws = nullptr;
-    int32_t rc = ovk_scratch(ctx, patch_bytes + d_bytes + sums_bytes + 256, &ws);
+    int32_t rc = ovk_scratch(ctx, patch_bytes + d_bytes + sums_bytes + fpad_bytes + fsum_bytes + 256, &ws);
     if (rc != OVK_OK)
         return rc;
     uint8_t *patches_dev = static_cast<uint8_t *>(ws);
     uint8_t *d_dev = patches_dev + patch_bytes;
     int32_t *sums_dev = reinterpret_cast<int32_t *>(d_dev + d_bytes);
+    const int32_t *filter_sums = w->wsum;
+    if (zp_padding) {
+        uint8_t *fpad = reinterpret_cast<uint8_t *>(sums_dev) + sums_bytes;
+        int32_t *fsum = reinterpret_cast<int32_t *>(fpad + fpad_bytes);
+        pad_filter_rows_kernel<<<unsigned(ceil_div64(int64_t(g.c_out) * K, 256)), 256, 0, ctx->stream>>>(w->w, fpad, g.c_out, K_true, K,
+                                                                                                         uint8_t(w_zp & 0xff));
+        OVK_LAUNCHED(ctx, "conv_pad_filter_rows");
+        filter_sums_kernel<<<unsigned(ceil_div64(int64_t(g.c_out) * 32, 256)), 256, 0, ctx->stream>>>(fpad, g.c_out, K, w->w_signed, fsum);
+        OVK_LAUNCHED(ctx, "conv_filter_sums");
+        filters = fpad;
+        filter_sums = fsum;
+    }
+    const uint32_t pad_byte = zp_padding ? uint32_t(x_zp) & 0xffu : 0u;
     // the zero points where the kernels read zero points: in device memory (the image's, then the filters')
     uint8_t *zp_dev = reinterpret_cast<uint8_t *>(ctx->range_slot + 40);
     if (x_zp != 0)
@@ -558,10 +577,11 @@ int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, 
             // (few, long lines: with the 1536 lines of 9 bytes of a 512-channel 3 x 3 layer on 7 x 7 the fill
             // of the slab is a chain of short loads and the pass takes three times as long as the plain one)
             if (slab <= 48 * 1024 && g.c_in * g.kh <= 64 && wpad >= 64 && K <= 1024 && g.h_out <= 65535 && images <= 65535) {
-                patches_rows_kernel<<<dim3(unsigned(g.h_out), unsigned(images)), 256, slab, ctx->stream>>>(xi, patches_dev, g, x_zp, K, wpad);
+                patches_rows_kernel<<<dim3(unsigned(g.h_out), unsigned(images)), 256, slab, ctx->stream>>>(xi, patches_dev, g, x_zp, K, wpad,
+                                                                                                           pad_byte);
             } else {
                 const unsigned blocks = unsigned(std::min<int64_t>(ceil_div64(int64_t(images) * pixels * K, 256), int64_t(ctx->sm_count) * 32));
-                patches_kernel<<<blocks, 256, 0, ctx->stream>>>(xi, patches_dev, g, x_zp, K, images);
+                patches_kernel<<<blocks, 256, 0, ctx->stream>>>(xi, patches_dev, g, x_zp, K, images, pad_byte);
             }
             OVK_LAUNCHED(ctx, "conv_patches");
         }
@@ -574,7 +594,7 @@ int32_t run_gemm_route(ovk_ctx *ctx, const ovk_qconv_weight *wc, const void *x, 
         }
         uint8_t *dst = static_cast<uint8_t *>(out) + size_t(img) * g.c_out * pixels * out_elem;
         rc = ovk_mmi_tc_launch_with_row_sums(ctx, &patches, filters, w->w_signed, g.c_out, w_zp != 0 ? zp_dev + 1 : nullptr,
-                                             x_zp != 0 ? zp_dev : nullptr, epi, images > 1 ? d_dev : dst, w->wsum);
+                                             x_zp != 0 ? zp_dev : nullptr, epi, images > 1 ? d_dev : dst, filter_sums);
         if (rc != OVK_OK)
             return rc;
         if (images > 1) {

@@ -323,6 +323,16 @@ def test_convolution_as_filters_times_patches(c_in, c_out, h, w, k, strides, dil
     ibias = rng.integers(-1000, 1001, size=c_out, dtype=np.int32)
     q = ctx().qlinear_conv(wq, dev(x), 77, 0, ratio, dev(ibias), 3, **kw)
     assert np.array_equal(host(q), orc.requantize(want, want.shape[2] * want.shape[3], ratio, 3, bias=ibias))
+    # an asymmetric weight (uint8 filters, zero point 119): the same route, the patches' sums from one more pass;
+    # where K is padded to 16-byte rows the padding of both operands holds the operand's zero point
+    wu = wt.view(np.uint8)
+    wqu = ctx().qconv_prepack(dev(wu))
+    got_u = ctx().conv_integer(wqu, dev(x), 77, 119, **kw)
+    assert ctx().last_kernel.startswith(GEMM_ROUTE), ctx().last_kernel
+    want_u = orc.conv_integer(x, wu, 77, 119, **kw)
+    assert np.array_equal(host(got_u), want_u)
+    q_u = ctx().qlinear_conv(wqu, dev(x), 77, 119, ratio, dev(ibias), 3, **kw)
+    assert np.array_equal(host(q_u), orc.requantize(want_u, want.shape[2] * want.shape[3], ratio, 3, bias=ibias))
 
 
 def _fused_layer(c_in, c_out, hw, k, x_signed, w_signed):
@@ -349,7 +359,7 @@ def _fused_oracle(acc, scale, bias, product=None, relu=False):
     (64, 1, (24, 24), 1, 1, 0, True, False, False, ""),
     (256, 32, (88, 88), 3, 1, 1, True, False, False, "qconv_tc"),
     (4096, 16, (10, 13), 7, 1, 3, False, False, True, "mmi_tc"),
-    (24, 20, (15, 15), 3, 1, 1, False, False, True, "conv_direct"),
+    (24, 20, (15, 15), 3, 1, 1, False, False, True, "mmi_tc"),  # asymmetric weights, K = 216 padded to 224 with the zero points
 ])
 def test_conv_integer_scale_bias_is_bit_identical_to_the_four_nodes(c_in, c_out, hw, k, stride, pad, ws, xs,
                                                                     per_channel_scale, kernel):
