@@ -204,8 +204,9 @@ OVK_API int32_t ovk_allgather_cols_multicast(ovk_ctx *ctx, const void *y_shard, 
  * Y [m, n_total] in every rank's y_peers[r].  For fp16 results of the prefill
  * kernel with per-block scaling (block sizes 128 and 256, or f32 scales) the
  * kernel's own store warp writes each finished tile into every rank's matrix,
- * so the exchange overlaps the product; other forms compute the block and then
- * run the exchange of ovk_allgather_cols.  Results are those of ovk_matmul_nbits
+ * so the exchange overlaps the product (up to four ranks: with more peers per
+ * store warp the two steps measured faster one after the other); other forms
+ * compute the block and then run the exchange of ovk_allgather_cols.  Results are those of ovk_matmul_nbits
  * on the unsplit weight (the same kernel on the same columns). */
 OVK_API int32_t ovk_matmul_nbits_nsplit(ovk_ctx *ctx, const ovk_nbits_weight *w, const void *a,
                                         int32_t a_dtype, int64_t m, int64_t col0, int64_t n_total,
