@@ -23,6 +23,12 @@
 namespace {
 
 constexpr int COPY_THREADS = 256;
+// CTAs of the exchange kernel, at most: measured at 2 ranks (77.6 MB to the one peer) 64 CTAs deliver 310 GB/s,
+// 148 467 GB/s, 296 520 GB/s, 592 and 1184 534 GB/s - the stores in flight, not the links, set the rate below two
+// CTAs per SM.
+#ifndef OVK_GATHER_MAX_CTAS
+#define OVK_GATHER_MAX_CTAS 296
+#endif
 
 struct GatherParams {
     const uint8_t *src;      // this rank's column block
@@ -171,9 +177,8 @@ int32_t ovk_comm_gather_cols(ovk_ctx *ctx, const OvkCommView &view, const void *
     }
     p.vec16 = vec;
     p.mc = vec && aligned_to(y_multicast, 16) ? static_cast<uint8_t *>(y_multicast) : nullptr;
-    // A copy needs few SMs to fill NVLink; the rest stay free for whatever follows on other streams.
     const int64_t chunks = m * (vec ? p.row_bytes / 16 : n_shard);
-    const unsigned grid = unsigned(std::max<int64_t>(1, std::min<int64_t>(ceil_div64(chunks, COPY_THREADS * 4), 64)));
+    const unsigned grid = unsigned(std::max<int64_t>(1, std::min<int64_t>(ceil_div64(chunks, COPY_THREADS * 4), OVK_GATHER_MAX_CTAS)));
     allgather_cols_kernel<<<grid, COPY_THREADS, 0, ctx->stream>>>(view, p);
     OVK_LAUNCHED(ctx, "allgather_cols");
     return ovk_comm_wait_done(ctx, view);
