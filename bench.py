@@ -328,25 +328,7 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
     #   FF input -> DynamicQuantizeLinear -> FF1 (1024 -> 4096, f32 out)
     #   FF1 output -> DecomposedGeluQuantize (the f32 GELU is never stored) -> FF2 (4096 -> 1024)
     t = 1000
-    layer = [(1024, 1024)] * 4 + [(1024, 4096), (4096, 1024)]
-    ws, scs, bis = [], [], []
-    for k, n in layer:
-        ws.append(ctx.mmi_prepack(torch.randint(-127, 128, (k, n), dtype=torch.int8, device="cuda", generator=gen)))
-        scs.append(torch.rand((n,), device="cuda", generator=gen) * 0.009 + 0.001)
-        bis.append(torch.zeros((n,), device="cuda"))
-    x_in, a_in, f_in = (torch.randn((t, 1024), device="cuda", generator=gen) for _ in range(3))
-    gelu_c = (float(np.float32(np.sqrt(2.0))), 1.0, 0.5)
-
-    def gemm(i, q):
-        xq, a_scale, a_zp = q
-        return ctx.matmul_integer_scale_bias(ws[i], xq, a_zp, None, scs[i], bis[i], product=a_scale.reshape(1))
-
-    def layer_step():
-        xq, a_scale, a_zp = ctx.dynamic_quantize(x_in)
-        ctx.matmul_integer_scale_bias_group(ws[:3], xq, a_zp, None, scs[:3], bis[:3], product=a_scale.reshape(1))
-        gemm(3, ctx.dynamic_quantize(a_in))
-        h = gemm(4, ctx.dynamic_quantize(f_in))
-        gemm(5, ctx.decomposed_gelu_quantize(h, *gelu_c))
+    layer, layer_step = parakeet_layer(torch, ctx, gen, t)
     before = ctx.launches
     layer_step()
     layer_launches = ctx.launches - before
@@ -397,7 +379,7 @@ def extra_workloads(torch, dist, ctx, world, rank, gen, peaks):
     tops_b = 2.0 * 8192 ** 3 / (ms_b * 1e-3) / 1e12
     out["int8_gemm_8192"] = {"ms": ms_b, "kernel": ctx.last_kernel, "tops_per_gpu": tops_b,
                              "frac_of_2x_measured_bf16_peak": tops_b / (2 * bf16_peak)}
-    del ws
+    del layer_step  # and with it the layer's weights
 
     # ---- static int8 QLinearConv, ResNet block (config 4): batch 64 split over the ranks
     bsh = shard.batch_shard(64, world, rank)
@@ -507,6 +489,32 @@ RESNET50_LAYERS = [
     (1024, 512, 1, 1, 14, 1), (512, 512, 3, 2, 14, 1), (512, 2048, 1, 1, 7, 3), (2048, 512, 1, 1, 7, 2), (512, 512, 3, 1, 7, 2),
     (1024, 2048, 1, 2, 14, 1),
 ]
+
+
+def parakeet_layer(torch, ctx, gen, t=1000):
+    """The six GEMMs of one FastConformer layer (d = 1024, FF = 4096) in the order the graph runs them, each tensor
+    quantised once; returns the (K, N) list and a function that enqueues the layer."""
+    import numpy as np
+    layer = [(1024, 1024)] * 4 + [(1024, 4096), (4096, 1024)]
+    ws, scs, bis = [], [], []
+    for k, n in layer:
+        ws.append(ctx.mmi_prepack(torch.randint(-127, 128, (k, n), dtype=torch.int8, device="cuda", generator=gen)))
+        scs.append(torch.rand((n,), device="cuda", generator=gen) * 0.009 + 0.001)
+        bis.append(torch.zeros((n,), device="cuda"))
+    x_in, a_in, f_in = (torch.randn((t, 1024), device="cuda", generator=gen) for _ in range(3))
+    gelu_c = (float(np.float32(np.sqrt(2.0))), 1.0, 0.5)
+
+    def gemm(i, q):
+        xq, a_scale, a_zp = q
+        return ctx.matmul_integer_scale_bias(ws[i], xq, a_zp, None, scs[i], bis[i], product=a_scale.reshape(1))
+
+    def layer_step():
+        xq, a_scale, a_zp = ctx.dynamic_quantize(x_in)
+        ctx.matmul_integer_scale_bias_group(ws[:3], xq, a_zp, None, scs[:3], bis[:3], product=a_scale.reshape(1))
+        gemm(3, ctx.dynamic_quantize(a_in))
+        h = gemm(4, ctx.dynamic_quantize(f_in))
+        gemm(5, ctx.decomposed_gelu_quantize(h, *gelu_c))
+    return layer, layer_step
 
 
 def resnet50_convolutions(torch, dist, ctx, gen, batch=64):
@@ -888,6 +896,8 @@ def run_one(which):
         a = torch.randint(0, 256, (d, d), dtype=torch.uint8, device="cuda", generator=gen)
         zp = torch.full((1,), 128, dtype=torch.uint8, device="cuda")
         fn = lambda: ctx.matmul_integer(w, a, zp, None)
+    elif which == "parakeet":
+        _, fn = parakeet_layer(torch, ctx, gen)
     else:
         w = ctx.qconv_prepack(torch.randint(-127, 128, (64, 64, 3, 3), dtype=torch.int8, device="cuda", generator=gen))
         x = torch.randint(0, 256, (64, 64, 56, 56), dtype=torch.uint8, device="cuda", generator=gen)
@@ -997,7 +1007,7 @@ def main():
     ap.add_argument("--launch", default="grouped", choices=["grouped", "branches", "serial"],
                     help="how the independent GEMVs of a layer (q|k|v, gate|up) are launched: one launch per group, "
                          "parallel graph branches, or one launch per GEMV in a single chain")
-    ap.add_argument("--one", default=None, choices=["lm_head", "prefill", "prefill32", "int8", "int8big", "conv", "conv_cl"],
+    ap.add_argument("--one", default=None, choices=["lm_head", "prefill", "prefill32", "int8", "int8big", "conv", "conv_cl", "parakeet"],
                     help="run one operator three times and exit (small target for an ncu capture)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

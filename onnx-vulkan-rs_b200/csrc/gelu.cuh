@@ -24,7 +24,12 @@ __device__ __forceinline__ float ovk_exp_ieee(float x)
 {
     if (!(x > -104.0f))
         return x != x ? x : 0.0f;
-    const float n = rintf(__fmul_rn(x, 1.44269504088896341f));
+    // n = rint(x * log2 e) and its integer, without the quarter-rate rounding and conversion instructions: for
+    // |t| < 2^22 the sum t + 1.5 * 2^23 is rounded to an integer (to nearest even, as rintf rounds), its low
+    // mantissa bits are that integer, and subtracting the constant again is exact.
+    const float shifted = __fadd_rn(__fmul_rn(x, 1.44269504088896341f), 12582912.0f);
+    const float n = __fsub_rn(shifted, 12582912.0f);
+    const int e = __float_as_int(shifted) - 0x4B400000;
     float r = fmaf(n, -0.693145751953125f, x);        // ln 2, high part (exact product for |n| < 2^11)
     r = fmaf(n, -1.42860682030941723e-6f, r);         // ln 2, low part
     float p = 1.0f / 5040.0f;
@@ -35,8 +40,11 @@ __device__ __forceinline__ float ovk_exp_ieee(float x)
     p = fmaf(p, r, 0.5f);
     p = fmaf(p, r, 1.0f);
     p = fmaf(p, r, 1.0f);
-    // p * 2^n in two exact steps, so that results below the normal range round once, as a denormal
-    const int e = int(n);
+    // p * 2^e.  p lies in [0.70, 1.42] (|r| <= 0.35), so while e >= -125 the product is a normal number and the
+    // scaling is exact: the exponent field takes e.  Below that - arguments under -86.6, where the result is a
+    // denormal - two exact-or-once-rounded steps, so that the result rounds once.
+    if (e >= -125)
+        return __int_as_float(__float_as_int(p) + e * 8388608);  // e * 2^23: into the exponent field
     const int e1 = e / 2, e2 = e - e1;
     union { uint32_t u; float f; } s1, s2;
     s1.u = uint32_t(e1 + 127) << 23;
@@ -48,7 +56,8 @@ __device__ __forceinline__ float ovk_erf_approx(float x)
 {
     const float s = x > 0.0f ? 1.0f : (x < 0.0f ? -1.0f : 0.0f);  // sign(): 0 for 0
     const float a = fabsf(x);
-    const float t = __fdiv_rn(1.0f, __fadd_rn(1.0f, __fmul_rn(0.3275911f, a)));
+    // (the correctly rounded reciprocal is the correctly rounded quotient 1 / d: the same bits, half the instructions)
+    const float t = __frcp_rn(__fadd_rn(1.0f, __fmul_rn(0.3275911f, a)));
     float poly = __fmul_rn(t, 1.061405429f);
     poly = __fmul_rn(t, __fadd_rn(-1.453152027f, poly));
     poly = __fmul_rn(t, __fadd_rn(1.421413741f, poly));

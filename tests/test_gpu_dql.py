@@ -116,6 +116,10 @@ def test_decomposed_gelu_matches_the_port_bit_for_bit(factor_first):
     exp spelled in IEEE operations, so the CPU port and the kernel give the same bits."""
     x = cases.rng_for(3, 7).standard_normal((1000, 4096), dtype=np.float32) * np.float32(3.0)
     x.reshape(-1)[:8] = [0.0, -0.0, 1e-30, -1e-30, 12.5, -12.5, 40.0, -40.0]
+    # arguments whose exp(-a * a) is a denormal or underflows (a * a from 82 to 110): the scaling by 2^e in two steps
+    sweep = np.linspace(12.8, 14.9, 512, dtype=np.float32)
+    x.reshape(-1)[8:8 + 512] = sweep
+    x.reshape(-1)[520:520 + 512] = -sweep
     got = host(ctx().decomposed_gelu(dev(x), *GELU, factor_first=factor_first))
     want = orc.decomposed_gelu(x, *GELU, factor_first=factor_first)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
